@@ -1,0 +1,198 @@
+"""Per-kernel microbenchmarks on one GPU: this package's sm_100a kernels next to the library
+call they replace (cuBLAS via torch.matmul, flash-attn 2 varlen), timed with CUDA events after
+warm-up, inputs larger than L2 or an L2 flush between iterations.
+
+    python -m nanoplm_b200.bench.kernel_bench [--tokens 65536] [--what gemm,attn,elementwise]
+
+Prints one JSON object per measurement.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+BF = torch.bfloat16
+
+
+def _flush_buf():
+    return torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+
+def time_fn(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s = torch.cuda.Event(enable_timing=True)
+        e = torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm(T, peaks):
+    from nanoplm_b200.ops import kernels as k
+    flush = _flush_buf()
+    shapes = [  # (name, M, N, K, a_mn, b_mn, epi)
+        ("qkv_fwd", T, 3072, 1024, False, False, k.EPI_STORE),
+        ("attn_out_fwd_add", T, 1024, 1024, False, False, k.EPI_ADD),
+        ("mlp_up_fwd_swiglu", T, 4096, 1024, False, False, k.EPI_SWIGLU),
+        ("mlp_up_fwd", T, 4096, 1024, False, False, k.EPI_STORE),
+        ("mlp_down_fwd_add", T, 1024, 2048, False, False, k.EPI_ADD),
+        ("qkv_dgrad", T, 1024, 3072, False, True, k.EPI_STORE),
+        ("mlp_up_dgrad", T, 1024, 4096, False, True, k.EPI_STORE),
+        ("mlp_down_dgrad", T, 2048, 1024, False, True, k.EPI_STORE),
+        ("qkv_wgrad", 3072, 1024, T, True, True, k.EPI_ATOMIC_F32),
+        ("attn_out_wgrad", 1024, 1024, T, True, True, k.EPI_ATOMIC_F32),
+        ("mlp_up_wgrad", 4096, 1024, T, True, True, k.EPI_ATOMIC_F32),
+        ("mlp_down_wgrad", 1024, 2048, T, True, True, k.EPI_ATOMIC_F32),
+    ]
+    for name, M, N, K, a_mn, b_mn, epi in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(BF)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(BF)
+        aux = torch.randn(M, N, device="cuda").to(BF) if epi in (k.EPI_ADD, k.EPI_SWIGLU) else None
+        out = None
+        splits = 1
+        if epi == k.EPI_ATOMIC_F32:
+            out = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+            splits = k.wgrad_splits(M, N, K)
+        for bn in (256, 128):
+            if epi == k.EPI_ATOMIC_F32:
+                splits = k.wgrad_splits(M, N, K, bn)
+            ms = time_fn(lambda: k.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=epi, out=out, aux=aux,
+                                        splits=splits, bn=bn), flush=flush)
+            tf = 2.0 * M * N * K / ms / 1e9
+            print(json.dumps({"kernel": "gemm_bf16_tcgen05", "case": name, "bn": bn, "splits": splits,
+                              "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
+                              "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 3)}))
+        af = a.t() if a_mn else a
+        bf_ = b if b_mn else b.t()
+        ms = time_fn(lambda: torch.matmul(af, bf_), flush=flush)
+        tf = 2.0 * M * N * K / ms / 1e9
+        print(json.dumps({"kernel": "cublas(torch.matmul)", "case": name, "ms": round(ms, 4),
+                          "tflops": round(tf, 1)}))
+    k.check_status()
+
+
+def _packed_batch(T, lo=20, hi=512, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    lens, tot = [], 0
+    while tot < T:
+        n = int(torch.randint(lo, hi + 1, (1,), generator=g))
+        n = min(n, T - tot)
+        lens.append(n)
+        tot += n
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    return lens, torch.tensor(cu, dtype=torch.int32, device="cuda")
+
+
+def bench_attn(T, peaks):
+    from nanoplm_b200.ops import kernels as k
+    H, D = 16, 64
+    lens, cu = _packed_batch(T)
+    flops_pairs = {-1: sum(n * n for n in lens),
+                   64: sum(sum(min(n, i + 65) - max(0, i - 64) for i in range(n)) for n in lens)}
+    qkv = torch.randn(T, 3 * H * D, device="cuda").to(BF)
+    dout = torch.randn(T, H * D, device="cuda").to(BF)
+    ss, se = k.seq_bounds(cu, T)
+    flush = _flush_buf()
+    try:
+        from flash_attn import flash_attn_varlen_func
+    except Exception:  # pragma: no cover
+        flash_attn_varlen_func = None
+    for window in (-1, 64):
+        fwd_flops = 4.0 * flops_pairs[window] * D * H
+        ms = time_fn(lambda: k.fa_fwd(qkv, ss, se, H, D, window, 0.125), flush=flush)
+        print(json.dumps({"kernel": "fa_varlen_fwd", "window": window, "T": T, "ms": round(ms, 4),
+                          "tflops": round(fwd_flops / ms / 1e9, 1)}))
+        out, lse = k.fa_fwd(qkv, ss, se, H, D, window, 0.125)
+        ms = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125), flush=flush)
+        print(json.dumps({"kernel": "fa_varlen_bwd", "window": window, "T": T, "ms": round(ms, 4),
+                          "tflops": round(2.5 * fwd_flops / ms / 1e9, 1)}))
+        if flash_attn_varlen_func is not None:
+            q, kk, v = qkv.view(T, 3, H, D).unbind(1)
+            q = q.contiguous().requires_grad_(True)
+            kk = kk.contiguous().requires_grad_(True)
+            v = v.contiguous().requires_grad_(True)
+            mx = max(lens)
+            ws = (-1, -1) if window < 0 else (window, window)
+            f = lambda: flash_attn_varlen_func(q, kk, v, cu, cu, mx, mx, softmax_scale=0.125, window_size=ws)
+            ms = time_fn(f, flush=flush)
+            print(json.dumps({"kernel": "flash_attn2_fwd", "window": window, "ms": round(ms, 4),
+                              "tflops": round(fwd_flops / ms / 1e9, 1)}))
+            o = f()
+            do = dout.view(T, H, D)
+            ms = time_fn(lambda: torch.autograd.grad(o, (q, kk, v), do, retain_graph=True), flush=flush)
+            print(json.dumps({"kernel": "flash_attn2_bwd", "window": window, "ms": round(ms, 4),
+                              "tflops": round(2.5 * fwd_flops / ms / 1e9, 1)}))
+    k.check_status()
+
+
+def bench_elementwise(T, peaks):
+    from nanoplm_b200.ops import kernels as k
+    C, I = 1024, 2048
+    x = torch.randn(T, C, device="cuda").to(BF)
+    w = torch.ones(C, device="cuda").to(BF)
+    dy = torch.randn(T, C, device="cuda").to(BF)
+    hbm = peaks["hbm_gbs"]
+
+    def report(name, ms, nbytes):
+        gbs = nbytes / ms / 1e6
+        print(json.dumps({"kernel": name, "ms": round(ms, 4), "GBps": round(gbs, 1),
+                          "frac_of_measured_hbm": round(gbs / hbm, 3)}))
+
+    ms = time_fn(lambda: k.norm_fwd(x, w, 1e-5))
+    report("layernorm_fwd", ms, 2 * T * C * 2)
+    y, mean, rstd = k.norm_fwd(x, w, 1e-5)
+    dw = torch.zeros(C, device="cuda")
+    ms = time_fn(lambda: k.norm_bwd(dy, x, w, mean, rstd, dres=dy, dw=dw))
+    report("layernorm_bwd", ms, 4 * T * C * 2)
+    pre = torch.randn(T, 2 * I, device="cuda").to(BF)
+    ms = time_fn(lambda: k.swiglu_fwd(pre))
+    report("swiglu_fwd", ms, 3 * T * I * 2)
+    do = torch.randn(T, I, device="cuda").to(BF)
+    ms = time_fn(lambda: k.swiglu_bwd(pre, do))
+    report("swiglu_bwd", ms, 5 * T * I * 2)
+    qkv = torch.randn(T, 3 * C, device="cuda").to(BF)
+    pos = torch.randint(0, 512, (T,), device="cuda", dtype=torch.int32)
+    cos = torch.randn(1024, 32, device="cuda")
+    sin = torch.randn(1024, 32, device="cuda")
+    ms = time_fn(lambda: k.rope_(qkv, pos, cos, sin, 16, 64))
+    report("rope", ms, 4 * T * C * 2)
+    n = 168_888_352
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    pb = torch.empty(n, dtype=BF, device="cuda")
+    hyper = torch.tensor([1e-3, 0.9, 0.999, 1e-8, 0.0, 0.1, 0.001, 1.0, 1.0], device="cuda")
+    ss = torch.ones(1, device="cuda")
+    ms = time_fn(lambda: k.adamw_(p, m, v, g, pb, hyper, ss))
+    report("adamw", ms, n * (4 * 4 + 3 * 4 + 2))
+    k.check_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=65536)
+    ap.add_argument("--what", default="gemm,attn,elementwise")
+    args = ap.parse_args()
+    from nanoplm_b200.utils.peaks import measured_peaks
+    peaks = measured_peaks()
+    for what in args.what.split(","):
+        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise}[what](args.tokens, peaks)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,778 @@
+// Varlen (cu_seqlens) flash attention for sm_100a, head_dim 64, non-causal, optional symmetric
+// sliding window, on packed activations qkv[T][3][H][64] (bf16).
+//
+// Both kernels tile the FLAT token axis in blocks of 128, whatever the sequence boundaries are:
+// a 128-token tile may hold several short sequences (or a slice of a long one). The key range
+// it needs is [start of the first sequence in the tile, end of the last one), clipped by the
+// window, and each row masks keys outside its own sequence / window. Short proteins therefore
+// do not waste tensor-core tiles on padding.
+//
+//   forward : S = Q K^T (tcgen05, fp32 in TMEM) -> online softmax in registers (one thread per
+//             row) -> P (bf16) to swizzled shared memory -> O_part = P V (tcgen05) -> registers.
+//   backward: per 128-key tile, loop over query tiles: S^T = K Q^T, dP^T = V dO^T (TMEM) ->
+//             P^T, dS^T (bf16, shared) -> dV += P^T dO, dK += dS^T Q (TMEM-resident across the
+//             loop), dQ_part = dS K -> fp32 atomics into a dq accumulator.
+//
+// Replaces flash_attn_varlen_func as called by the reference
+// (src/nanoplm/pretraining/models/modern_bert/modeling.py:331-366) with window (-1,-1) or
+// (64,64); mask semantics match its SDPA route (modeling.py:142-156): |q - k| <= window.
+//
+// All operand tiles are [128 rows][64 bf16] = [128][128 B] with the 128-byte swizzle, loaded by
+// one TMA box each; the same tile serves as a K-major operand (contraction over head_dim) and
+// as an MN-major operand (contraction over tokens).
+#include "common.cuh"
+
+namespace nplm {
+
+constexpr int FA_T = 128;          // tile of tokens (queries and keys)
+constexpr int FA_D = 64;           // head dim
+constexpr int FA_TILE_BYTES = FA_T * FA_D * 2;  // 16 KB
+constexpr float LOG2E = 1.4426950408889634f;
+
+// byte offset of 16-byte chunk `chunk` (0..7) of row `r` inside a [rows][128 B] swizzled tile
+__device__ __forceinline__ uint32_t swz(int r, int chunk) {
+  return static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4));
+}
+
+// ---------------------------------------------------------------------------- seq bounds
+// seq_start[t], seq_end[t] from cu_seqlens (n_seq + 1 entries, may contain empty sequences)
+__global__ void seq_bounds_kernel(const int* __restrict__ cu, int n_seq, int* __restrict__ s_start,
+                                  int* __restrict__ s_end, int T) {
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x) {
+    // last i in [0, n_seq) with cu[i] <= t
+    int lo = 0, hi = n_seq;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (cu[mid] <= t) lo = mid; else hi = mid;
+    }
+    int a = cu[lo], b = cu[lo + 1];
+    if (t < a || t >= b) {  // token not covered by any sequence: attends to itself only
+      a = t;
+      b = t + 1;
+    }
+    s_start[t] = a;
+    s_end[t] = b;
+  }
+}
+
+// ---------------------------------------------------------------------------- forward
+struct FaFwdArgs {
+  __nv_bfloat16* out;   // [T][H*64]
+  float* lse;           // [H][T] natural-log LSE of the scaled scores
+  const int* seq_start;
+  const int* seq_end;
+  int T, H, window;     // window < 0: unlimited
+  float scale;
+  int* status;
+};
+
+constexpr int FA_FWD_SMEM = FA_TILE_BYTES * (1 + 2 + 2) + 2 * FA_TILE_BYTES + 256;
+
+__global__ void __launch_bounds__(128, 2)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaFwdArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
+    return;
+  }
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + FA_TILE_BYTES;       // 2 buffers
+  uint8_t* sV = smem + 3 * FA_TILE_BYTES;   // 2 buffers
+  uint8_t* sP = smem + 5 * FA_TILE_BYTES;   // [2 column blocks][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * FA_TILE_BYTES);
+  uint64_t* bar_q = bars;
+  uint64_t* bar_kv = bars + 1;  // [2]
+  uint64_t* bar_s = bars + 3;
+  uint64_t* bar_o = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int T = args.T, H = args.H, w = args.window;
+  const int t0 = blockIdx.x * FA_T;
+  const int h = blockIdx.y;
+  const int HD = H * FA_D;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(&bar_kv[0], 1);
+    mbar_init(&bar_kv[1], 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmQKV);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;        // 128 columns
+  const uint32_t tO = tmem_base + 128;  // 64 columns
+
+  const int row = t0 + tid;
+  const bool row_ok = row < T;
+  int lo = 0, hi = 0;  // this row attends to keys [lo, hi)
+  if (row_ok) {
+    lo = args.seq_start[row];
+    hi = args.seq_end[row];
+    if (w >= 0) {
+      lo = max(lo, row - w);
+      hi = min(hi, row + w + 1);
+    }
+  }
+  const int last = min(t0 + FA_T - 1, T - 1);
+  int kv_lo = args.seq_start[t0];
+  int kv_hi = args.seq_end[last];
+  if (w >= 0) {
+    kv_lo = max(kv_lo, t0 - w);
+    kv_hi = min(kv_hi, last + w + 1);
+  }
+  const int n_kv = kv_hi > kv_lo ? (kv_hi - kv_lo + FA_T - 1) / FA_T : 0;
+
+  constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
+  const int colQ = h * FA_D, colK = HD + h * FA_D, colV = 2 * HD + h * FA_D;
+
+  auto issue_s = [&](int buf) {
+    const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + buf * FA_TILE_BYTES);
+#pragma unroll
+    for (int k = 0; k < FA_D / 16; ++k)
+      umma_bf16(tS, make_smem_desc(qa + k * 32, 16, 1024), make_smem_desc(ka + k * 32, 16, 1024),
+                idesc_s, k > 0 ? 1u : 0u);
+    umma_commit(bar_s);
+  };
+
+  if (tid == 0 && n_kv > 0) {
+    mbar_arrive_expect_tx(bar_q, FA_TILE_BYTES);
+    tma_load_2d(sQ, &tmQKV, bar_q, colQ, t0);
+    mbar_arrive_expect_tx(&bar_kv[0], 2 * FA_TILE_BYTES);
+    tma_load_2d(sK, &tmQKV, &bar_kv[0], colK, kv_lo);
+    tma_load_2d(sV, &tmQKV, &bar_kv[0], colV, kv_lo);
+    if (mbar_wait(bar_q, 0) && mbar_wait(&bar_kv[0], 0)) {
+      tc_fence_after();
+      issue_s(0);
+    } else {
+      atomicExch(args.status, ST_TIMEOUT_FULL);
+      *abort_flag = 1;
+    }
+  }
+
+  const float sl2 = args.scale * LOG2E;
+  float m_run = -1e30f, l_run = 0.f;
+  float o[FA_D];
+#pragma unroll
+  for (int e = 0; e < FA_D; ++e) o[e] = 0.f;
+
+  bool alive = true;
+  for (int j = 0; j < n_kv && alive; ++j) {
+    const int buf = j & 1;
+    const int kv0 = kv_lo + j * FA_T;
+    if (tid == 0 && j + 1 < n_kv) {
+      mbar_arrive_expect_tx(&bar_kv[buf ^ 1], 2 * FA_TILE_BYTES);
+      tma_load_2d(sK + (buf ^ 1) * FA_TILE_BYTES, &tmQKV, &bar_kv[buf ^ 1], colK, kv0 + FA_T);
+      tma_load_2d(sV + (buf ^ 1) * FA_TILE_BYTES, &tmQKV, &bar_kv[buf ^ 1], colV, kv0 + FA_T);
+    }
+    bool ok = mbar_wait(bar_s, j & 1);
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+      if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+      alive = false;
+      break;
+    }
+    tc_fence_after();
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+
+    // pass 1: row maximum over the valid keys of this tile
+    float tmax = -1e30f;
+#pragma unroll 1
+    for (int c = 0; c < FA_T; c += 32) {
+      uint32_t r[32];
+      tmem_ld32(tS + lane_addr + c, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int col = kv0 + c + e;
+        if (col >= lo && col < hi) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+      }
+    }
+    const float m_new = fmaxf(m_run, tmax);
+    const float alpha = exp2f((m_run - m_new) * sl2);
+    const float moff = m_new * sl2;
+    float psum = 0.f;
+    // pass 2: probabilities -> bf16 -> swizzled shared memory (A operand of P V)
+#pragma unroll 1
+    for (int c = 0; c < FA_T; c += 32) {
+      uint32_t r[32];
+      tmem_ld32(tS + lane_addr + c, r);
+      tmem_ld_wait();
+      uint32_t packed[16];
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        const int col = kv0 + c + e;
+        float p0 = 0.f, p1 = 0.f;
+        if (col >= lo && col < hi) p0 = exp2f(fmaf(__uint_as_float(r[e]), sl2, -moff));
+        if (col + 1 >= lo && col + 1 < hi) p1 = exp2f(fmaf(__uint_as_float(r[e + 1]), sl2, -moff));
+        psum += p0 + p1;
+        packed[e >> 1] = pack_bf16x2(p0, p1);
+      }
+      uint8_t* blk = sP + (c >> 6) * FA_TILE_BYTES;
+      const int chunk0 = ((c >> 5) & 1) * 4;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        *reinterpret_cast<uint4*>(blk + swz(tid, chunk0 + q)) =
+            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      }
+    }
+    l_run = l_run * alpha + psum;
+    m_run = m_new;
+#pragma unroll
+    for (int e = 0; e < FA_D; ++e) o[e] *= alpha;
+
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t pa = smem_u32(sP), va = smem_u32(sV + buf * FA_TILE_BYTES);
+#pragma unroll
+      for (int k = 0; k < FA_T / 16; ++k)
+        umma_bf16(tO, make_smem_desc(pa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                  make_smem_desc(va + k * 2048, 8192, 1024), idesc_o, k > 0 ? 1u : 0u);
+      umma_commit(bar_o);
+      if (j + 1 < n_kv) {
+        if (mbar_wait(&bar_kv[buf ^ 1], ((j + 1) >> 1) & 1)) {
+          tc_fence_after();
+          issue_s(buf ^ 1);
+        } else {
+          atomicExch(args.status, ST_TIMEOUT_FULL);
+          *abort_flag = 1;
+        }
+      }
+    }
+    ok = mbar_wait(bar_o, j & 1);
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+      if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+      alive = false;
+      break;
+    }
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < FA_D; c += 32) {
+      uint32_t r[32];
+      tmem_ld32(tO + lane_addr + c, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) o[c + e] += __uint_as_float(r[e]);
+    }
+    tc_fence_before();
+  }
+
+  if (row_ok && alive) {
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* dst = args.out + static_cast<size_t>(row) * HD + h * FA_D;
+#pragma unroll
+    for (int e = 0; e < FA_D; e += 8) {
+      uint4 u;
+      uint32_t* p = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) p[q] = pack_bf16x2(o[e + 2 * q] * inv, o[e + 2 * q + 1] * inv);
+      *reinterpret_cast<uint4*>(dst + e) = u;
+    }
+    args.lse[static_cast<size_t>(h) * T + row] =
+        l_run > 0.f ? m_run * args.scale + __logf(l_run) : 0.f;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ---------------------------------------------------------------------------- backward
+// delta[h][t] = sum_d dO[t,h,d] * O[t,h,d]; also clears nothing (dq accumulator is cleared by
+// the host wrapper with a memset).
+__global__ void __launch_bounds__(256)
+fa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                float* __restrict__ delta, int T, int H) {
+  // 8 threads per (t, h): each handles 8 of the 64 channels
+  const long long total = static_cast<long long>(T) * H * 8;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int sub = static_cast<int>(idx & 7);
+    const long long th = idx >> 3;
+    const int h = static_cast<int>(th % H);
+    const int t = static_cast<int>(th / H);
+    const size_t off = (static_cast<size_t>(t) * H + h) * FA_D + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + off);
+    const uint4 b = *reinterpret_cast<const uint4*>(dout + off);
+    const uint32_t* pa = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* pb = reinterpret_cast<const uint32_t*>(&b);
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 x = unpack_bf16x2(pa[q]);
+      const float2 y = unpack_bf16x2(pb[q]);
+      s += x.x * y.x + x.y * y.y;
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (sub == 0) delta[static_cast<size_t>(h) * T + t] = s;
+  }
+}
+
+struct FaBwdArgs {
+  __nv_bfloat16* dqkv;   // [T][3][H][64]: the kernel writes the dK and dV parts
+  float* dq_acc;         // [T][H*64] fp32, zero-initialised by the caller
+  const float* lse;      // [H][T]
+  const float* delta;    // [H][T]
+  const int* seq_start;
+  const int* seq_end;
+  int T, H, window;
+  float scale;
+  int* status;
+};
+
+// smem: K, V, Q[2], dO[2] (16 KB each) + P^T (32 KB) + dS^T (32 KB) + lse/delta (2*2*128 fp32)
+constexpr int FA_BWD_SMEM = 6 * FA_TILE_BYTES + 4 * FA_TILE_BYTES + 2048 + 256;
+
+__global__ void __launch_bounds__(256, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+              const FaBwdArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
+    return;
+  }
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + FA_TILE_BYTES;
+  uint8_t* sQ = smem + 2 * FA_TILE_BYTES;    // 2 buffers
+  uint8_t* sdO = smem + 4 * FA_TILE_BYTES;   // 2 buffers
+  uint8_t* sPT = smem + 6 * FA_TILE_BYTES;   // [2 q blocks][128 kv rows][128 B]
+  uint8_t* sdST = smem + 8 * FA_TILE_BYTES;  // same layout
+  float* s_lse = reinterpret_cast<float*>(smem + 10 * FA_TILE_BYTES);  // [2][128]
+  float* s_delta = s_lse + 256;                                        // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 10 * FA_TILE_BYTES + 2048);
+  uint64_t* bar_kv = bars;
+  uint64_t* bar_q = bars + 1;  // [2]
+  uint64_t* bar_s = bars + 3;
+  uint64_t* bar_g = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int quarter = warp & 3;
+  const int half = warp >> 2;
+  const int T = args.T, H = args.H, w = args.window;
+  const int kv0 = blockIdx.x * FA_T;
+  const int h = blockIdx.y;
+  const int HD = H * FA_D;
+
+  if (tid == 0) {
+    mbar_init(bar_kv, 1);
+    mbar_init(&bar_q[0], 1);
+    mbar_init(&bar_q[1], 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_g, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmQKV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;         // S^T   [kv][q] 128 cols
+  const uint32_t tdP = tmem_base + 128;  // dP^T  [kv][q] 128 cols
+  const uint32_t tdQ = tmem_base + 256;  // dQ    [q][d]   64 cols
+  const uint32_t tdK = tmem_base + 320;  // dK    [kv][d]  64 cols
+  const uint32_t tdV = tmem_base + 384;  // dV    [kv][d]  64 cols
+
+  const int krow_local = quarter * 32 + lane;
+  const int krow = kv0 + krow_local;
+  const bool krow_ok = krow < T;
+  int lo = 0, hi = 0;  // this key is attended by queries [lo, hi)
+  if (krow_ok) {
+    lo = args.seq_start[krow];
+    hi = args.seq_end[krow];
+    if (w >= 0) {
+      lo = max(lo, krow - w);
+      hi = min(hi, krow + w + 1);
+    }
+  }
+  const int last = min(kv0 + FA_T - 1, T - 1);
+  int q_lo = args.seq_start[kv0];
+  int q_hi = args.seq_end[last];
+  if (w >= 0) {
+    q_lo = max(q_lo, kv0 - w);
+    q_hi = min(q_hi, last + w + 1);
+  }
+  const int n_q = q_hi > q_lo ? (q_hi - q_lo + FA_T - 1) / FA_T : 0;
+
+  constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_kv = make_idesc_bf16(128, 64, 0, 1);  // A K-major, B MN-major
+  constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, 1, 1);  // A MN-major, B MN-major
+  const int colQ = h * FA_D, colK = HD + h * FA_D, colV = 2 * HD + h * FA_D;
+  const float sl2 = args.scale * LOG2E;
+
+  auto load_q_tile = [&](int buf, int q0) {
+    mbar_arrive_expect_tx(&bar_q[buf], 2 * FA_TILE_BYTES);
+    tma_load_2d(sQ + buf * FA_TILE_BYTES, &tmQKV, &bar_q[buf], colQ, q0);
+    tma_load_2d(sdO + buf * FA_TILE_BYTES, &tmDO, &bar_q[buf], h * FA_D, q0);
+  };
+  auto issue_s = [&](int buf) {
+    const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+    const uint32_t qa = smem_u32(sQ + buf * FA_TILE_BYTES), da = smem_u32(sdO + buf * FA_TILE_BYTES);
+#pragma unroll
+    for (int k = 0; k < FA_D / 16; ++k)
+      umma_bf16(tS, make_smem_desc(ka + k * 32, 16, 1024), make_smem_desc(qa + k * 32, 16, 1024),
+                idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+    for (int k = 0; k < FA_D / 16; ++k)
+      umma_bf16(tdP, make_smem_desc(va + k * 32, 16, 1024), make_smem_desc(da + k * 32, 16, 1024),
+                idesc_s, k > 0 ? 1u : 0u);
+    umma_commit(bar_s);
+  };
+  auto load_stats = [&](int buf, int q0) {
+    if (tid < 128) {
+      const int q = q0 + tid;
+      s_lse[buf * 128 + tid] = q < T ? args.lse[static_cast<size_t>(h) * T + q] * LOG2E : 0.f;
+    } else {
+      const int q = q0 + tid - 128;
+      s_delta[buf * 128 + tid - 128] = q < T ? args.delta[static_cast<size_t>(h) * T + q] : 0.f;
+    }
+  };
+
+  if (n_q > 0) {
+    load_stats(0, q_lo);
+    if (tid == 0) {
+      mbar_arrive_expect_tx(bar_kv, 2 * FA_TILE_BYTES);
+      tma_load_2d(sK, &tmQKV, bar_kv, colK, kv0);
+      tma_load_2d(sV, &tmQKV, bar_kv, colV, kv0);
+      load_q_tile(0, q_lo);
+      if (mbar_wait(bar_kv, 0) && mbar_wait(&bar_q[0], 0)) {
+        tc_fence_after();
+        issue_s(0);
+      } else {
+        atomicExch(args.status, ST_TIMEOUT_FULL);
+        *abort_flag = 1;
+      }
+    }
+  }
+
+  bool alive = true;
+  for (int j = 0; j < n_q; ++j) {
+    const int buf = j & 1;
+    const int q0 = q_lo + j * FA_T;
+    if (j + 1 < n_q) {
+      load_stats(buf ^ 1, q0 + FA_T);
+      if (tid == 0) load_q_tile(buf ^ 1, q0 + FA_T);
+    }
+    __syncthreads();  // stats of tile j visible (written one iteration ahead, or before the loop)
+    bool ok = mbar_wait(bar_s, j & 1);
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+      if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+      alive = false;
+      break;
+    }
+    tc_fence_after();
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    // this thread: key row krow_local, query columns [half*64, half*64+64)
+#pragma unroll 1
+    for (int c = 0; c < 64; c += 32) {
+      const int cbase = half * 64 + c;
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS + lane_addr + cbase, rs);
+      tmem_ld32(tdP + lane_addr + cbase, rp);
+      tmem_ld_wait();
+      uint32_t pk[16], dk[16];
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        float p[2], ds[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int qc = cbase + e + u;
+          const int q = q0 + qc;
+          float pv = 0.f;
+          if (q >= lo && q < hi)
+            pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -s_lse[buf * 128 + qc]));
+          p[u] = pv;
+          ds[u] = pv * (__uint_as_float(rp[e + u]) - s_delta[buf * 128 + qc]);
+        }
+        pk[e >> 1] = pack_bf16x2(p[0], p[1]);
+        dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
+      }
+      const int chunk0 = (c >> 5) * 4;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint32_t off = half * FA_TILE_BYTES + swz(krow_local, chunk0 + q4);
+        *reinterpret_cast<uint4*>(sPT + off) =
+            make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        *reinterpret_cast<uint4*>(sdST + off) =
+            make_uint4(dk[4 * q4], dk[4 * q4 + 1], dk[4 * q4 + 2], dk[4 * q4 + 3]);
+      }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t pa = smem_u32(sPT), sa = smem_u32(sdST);
+      const uint32_t qa = smem_u32(sQ + buf * FA_TILE_BYTES), da = smem_u32(sdO + buf * FA_TILE_BYTES);
+      const uint32_t ka = smem_u32(sK);
+#pragma unroll
+      for (int k = 0; k < FA_T / 16; ++k) {  // dV[kv][d] += P^T[kv][q] dO[q][d]
+        umma_bf16(tdV, make_smem_desc(pa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                  make_smem_desc(da + k * 2048, 8192, 1024), idesc_kv, (j > 0 || k > 0) ? 1u : 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < FA_T / 16; ++k) {  // dK[kv][d] += dS^T[kv][q] Q[q][d]
+        umma_bf16(tdK, make_smem_desc(sa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                  make_smem_desc(qa + k * 2048, 8192, 1024), idesc_kv, (j > 0 || k > 0) ? 1u : 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < FA_T / 16; ++k) {  // dQ[q][d] = dS[q][kv] K[kv][d]
+        umma_bf16(tdQ, make_smem_desc(sa + k * 2048, FA_TILE_BYTES, 1024),
+                  make_smem_desc(ka + k * 2048, 8192, 1024), idesc_dq, k > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_g);
+      if (j + 1 < n_q) {
+        if (mbar_wait(&bar_q[buf ^ 1], ((j + 1) >> 1) & 1)) {
+          tc_fence_after();
+          issue_s(buf ^ 1);
+        } else {
+          atomicExch(args.status, ST_TIMEOUT_FULL);
+          *abort_flag = 1;
+        }
+      }
+    }
+    ok = mbar_wait(bar_g, j & 1);
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+      if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+      alive = false;
+      break;
+    }
+    tc_fence_after();
+    {
+      // dQ tile: lane = query row, this thread adds channels [half*32, half*32+32)
+      uint32_t r[32];
+      tmem_ld32(tdQ + lane_addr + half * 32, r);
+      tmem_ld_wait();
+      const int q = q0 + krow_local;
+      if (q < T && q < q_hi) {
+        float* dst = args.dq_acc + static_cast<size_t>(q) * HD + h * FA_D + half * 32;
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          atomicAdd(reinterpret_cast<float4*>(dst + e),
+                    make_float4(__uint_as_float(r[e]) * args.scale, __uint_as_float(r[e + 1]) * args.scale,
+                                __uint_as_float(r[e + 2]) * args.scale,
+                                __uint_as_float(r[e + 3]) * args.scale));
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();  // dQ columns and the P^T / dS^T buffers may be overwritten from here on
+  }
+
+  if (alive && krow_ok) {
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    __nv_bfloat16* dk_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 1) * HD + h * FA_D + half * 32;
+    __nv_bfloat16* dv_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 2) * HD + h * FA_D + half * 32;
+    if (n_q > 0) {
+      uint32_t rk[32], rv[32];
+      tmem_ld32(tdK + lane_addr + half * 32, rk);
+      tmem_ld32(tdV + lane_addr + half * 32, rv);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; e += 8) {
+        uint4 uk, uv;
+        uint32_t* pk = reinterpret_cast<uint32_t*>(&uk);
+        uint32_t* pv = reinterpret_cast<uint32_t*>(&uv);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          pk[q] = pack_bf16x2(__uint_as_float(rk[e + 2 * q]) * args.scale,
+                              __uint_as_float(rk[e + 2 * q + 1]) * args.scale);
+          pv[q] = pack_bf16x2(__uint_as_float(rv[e + 2 * q]), __uint_as_float(rv[e + 2 * q + 1]));
+        }
+        *reinterpret_cast<uint4*>(dk_dst + e) = uk;
+        *reinterpret_cast<uint4*>(dv_dst + e) = uv;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; e += 8) {
+        *reinterpret_cast<uint4*>(dk_dst + e) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv_dst + e) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// dq (fp32 accumulator) -> bf16 into the q part of dqkv[T][3][H][64]
+__global__ void __launch_bounds__(256)
+fa_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int T,
+                   int HD) {
+  const int vec = HD >> 3;
+  const long long total = static_cast<long long>(T) * vec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / vec);
+    const int c = static_cast<int>(i % vec) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(dq_acc + static_cast<size_t>(t) * HD + c);
+    const float4 b = *reinterpret_cast<const float4*>(dq_acc + static_cast<size_t>(t) * HD + c + 4);
+    uint4 u = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
+                         pack_bf16x2(b.z, b.w));
+    *reinterpret_cast<uint4*>(dqkv + static_cast<size_t>(t) * 3 * HD + c) = u;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn fa_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows = T, cols contiguous; box = [128 rows][64 cols]
+static int fa_make_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows) {
+  EncodeTiledFn fn = fa_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {FA_D, FA_T};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+}  // namespace nplm
+
+using namespace nplm;
+
+extern "C" int nplm_seq_bounds(const int* cu_seqlens, int n_seq, int* seq_start, int* seq_end,
+                               int T, cudaStream_t st) {
+  if (T <= 0 || n_seq <= 0) return 0;
+  seq_bounds_kernel<<<(T + 255) / 256, 256, 0, st>>>(cu_seqlens, n_seq, seq_start, seq_end, T);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_fa_fwd(const void* qkv, void* out, float* lse, const int* seq_start,
+                           const int* seq_end, int T, int H, int D, int window, float scale,
+                           int* status, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D != FA_D) return -3;
+  if (reinterpret_cast<uintptr_t>(qkv) & 15) return -3;
+  CUtensorMap tm;
+  int rc = fa_make_map(&tm, qkv, static_cast<uint64_t>(3) * H * D, T);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FA_FWD_SMEM));
+    configured = true;
+  }
+  FaFwdArgs a;
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.lse = lse;
+  a.seq_start = seq_start;
+  a.seq_end = seq_end;
+  a.T = T;
+  a.H = H;
+  a.window = window;
+  a.scale = scale;
+  a.status = status;
+  dim3 grid((T + FA_T - 1) / FA_T, H);
+  fa_fwd_kernel<<<grid, 128, FA_FWD_SMEM, st>>>(tm, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dq_acc: caller-provided fp32 scratch [T][H*D]; it is cleared here. delta: fp32 scratch [H][T].
+extern "C" int nplm_fa_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
+                           void* dqkv, float* dq_acc, float* delta, const int* seq_start,
+                           const int* seq_end, int T, int H, int D, int window, float scale,
+                           int* status, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D != FA_D) return -3;
+  CUtensorMap tmQKV, tmDO;
+  int rc = fa_make_map(&tmQKV, qkv, static_cast<uint64_t>(3) * H * D, T);
+  if (rc) return rc;
+  rc = fa_make_map(&tmDO, dout, static_cast<uint64_t>(H) * D, T);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FA_BWD_SMEM));
+    configured = true;
+  }
+  const int HD = H * D;
+  NPLM_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * HD * sizeof(float), st));
+  {
+    const long long total = static_cast<long long>(T) * H * 8;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    fa_delta_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout),
+        delta, T, H);
+  }
+  FaBwdArgs a;
+  a.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  a.dq_acc = dq_acc;
+  a.lse = lse;
+  a.delta = delta;
+  a.seq_start = seq_start;
+  a.seq_end = seq_end;
+  a.T = T;
+  a.H = H;
+  a.window = window;
+  a.scale = scale;
+  a.status = status;
+  dim3 grid((T + FA_T - 1) / FA_T, H);
+  fa_bwd_kernel<<<grid, 256, FA_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  {
+    const long long total = static_cast<long long>(T) * (HD / 8);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    fa_dq_store_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+        dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), T, HD);
+  }
+  return static_cast<int>(cudaGetLastError());
+}

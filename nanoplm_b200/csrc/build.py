@@ -1,0 +1,91 @@
+"""Builds the sm_100a kernels into in-tree shared objects with plain nvcc.
+
+Each ``.cu`` file becomes ``nanoplm_b200/_lib/lib<name>.so`` exposing a C ABI (``extern "C"``
+functions taking raw device pointers and a ``cudaStream_t``); ``nanoplm_b200.ops._lib`` loads them
+with ctypes. nvcc cross-compiles without a GPU, so the build also works on a CPU-only machine.
+
+Run ``python -m nanoplm_b200.csrc.build`` (add ``-v`` for ptxas register / shared-memory usage).
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+LIB_DIR = CSRC.parent / "_lib"
+
+SOURCES = [
+    "gemm_tcgen05.cu",
+    "elementwise.cu",
+    "attention.cu",
+    "extras.cu",
+    "comm.cu",
+    "fp8.cu",
+    "noalloc.cu",
+]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "--use_fast_math",
+    "-Xcompiler", "-fPIC",
+    "-shared",
+]
+
+
+def nvcc_path() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; set NVCC or install the CUDA toolkit")
+    return cand
+
+
+def _digest(src: Path) -> str:
+    h = hashlib.sha256()
+    h.update(src.read_bytes())
+    for hdr in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
+        h.update(hdr.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def lib_path(name: str) -> Path:
+    return LIB_DIR / f"lib{Path(name).stem}.so"
+
+
+def build_one(name: str, verbose: bool = False, force: bool = False) -> Path:
+    src = CSRC / name
+    out = lib_path(name)
+    stamp = out.with_suffix(".sha")
+    digest = _digest(src)
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+        return out
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    cmd = [nvcc_path(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(out), str(src)]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {name}:\n{proc.stdout}\n{proc.stderr}")
+    if verbose:
+        sys.stderr.write(proc.stderr)
+    stamp.write_text(digest)
+    return out
+
+
+def build_all(verbose: bool = False, force: bool = False) -> list[Path]:
+    names = [n for n in SOURCES if (CSRC / n).exists()]
+    with ThreadPoolExecutor(max_workers=min(8, len(names))) as ex:
+        return list(ex.map(lambda n: build_one(n, verbose, force), names))
+
+
+if __name__ == "__main__":
+    v = "-v" in sys.argv
+    f = "-f" in sys.argv
+    for p in build_all(verbose=v, force=f):
+        print(p)

@@ -1,0 +1,534 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline,
+// tcgen05.mma with fp32 accumulators in TMEM (double-buffered so the epilogue of tile i
+// overlaps the main loop of tile i+1), fused epilogues.
+//
+//   C[M,N] (+)= op(A) * op(B)^T
+//     a_mn = 0 : A stored [M][K] row-major (K contiguous)   -> K-major operand
+//     a_mn = 1 : A stored [K][M] row-major (M contiguous)   -> MN-major operand
+//     b_mn = 0 : B stored [N][K] row-major                  -> K-major operand
+//     b_mn = 1 : B stored [K][N] row-major                  -> MN-major operand
+//   With these four forms forward (x W^T), dgrad (dY W) and wgrad (dY^T X) all run
+//   without a transposed copy of any tensor.
+//
+// Replaces the cuBLAS calls behind nn.Linear in the reference
+// (src/nanoplm/pretraining/models/modern_bert/modeling.py:281-302,340,366,559).
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (each owns the TMEM lane quarter warp_idx % 4).
+#include "common.cuh"
+
+namespace nplm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+enum : int {
+  EPI_STORE = 0,       // C(bf16) = acc
+  EPI_ADD = 1,         // C(bf16) = acc + R(bf16)
+  EPI_ATOMIC_F32 = 2,  // C(fp32) += acc   (split-K capable; used for weight gradients)
+  EPI_GELU = 3,        // C(bf16) = gelu(acc), also writes the pre-activation to R when R != null
+  EPI_STORE_F32 = 4,   // C(fp32) = acc
+  EPI_SWIGLU = 5,      // B tile = [value rows | gate rows]; C(bf16, N/2 wide) = silu(gate)*value,
+                       // pre-activations (bf16, N wide) written to R
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+struct GemmArgs {
+  void* C;
+  const __nv_bfloat16* R;  // residual (EPI_ADD) or pre-activation output (EPI_GELU / EPI_SWIGLU)
+  int M, N, K;
+  int ldc, ldr;
+  int splits;
+  int swiglu_half;  // EPI_SWIGLU: row offset of the gate half inside B (= N/2)
+  int* status;
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs args) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int M = args.M, N = args.N, K = args.K;
+  // For EPI_SWIGLU the logical tile covers BN/2 value columns and BN/2 gate columns.
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int n_extent = (EPI == EPI_SWIGLU) ? args.swiglu_half : N;
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (n_extent + TILE_N - 1) / TILE_N;
+  const int num_kb = (K + BK - 1) / BK;
+  const int splits = args.splits;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  const int total_work = num_m * num_n * splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int split = w % splits;
+        const int tile = w / splits;
+        const int m0 = (tile / num_n) * BM;
+        const int n0 = (tile % num_n) * TILE_N;
+        const int kb0 = split * kb_per;
+        const int kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            atomicExch(args.status, ST_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int g = 0; g < BM / 64; ++g)
+              tma_load_2d(sa + g * (BK * 128), &tmA, &full_bar[stage], m0 + g * 64, k0);
+          }
+          if constexpr (EPI == EPI_SWIGLU) {
+            // value rows then gate rows, both K-major
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+            tma_load_2d(sb + (BN / 2) * 128, &tmB, &full_bar[stage], k0, args.swiglu_half + n0);
+          } else if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int g = 0; g < BN / 64; ++g)
+              tma_load_2d(sb + g * (BK * 128), &tmB, &full_bar[stage], n0 + g * 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int split = w % splits;
+        const int kb0 = split * kb_per;
+        const int kb1 = min(num_kb, kb0 + kb_per);
+        if (kb0 >= kb1) continue;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) {
+          atomicExch(args.status, ST_TIMEOUT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            atomicExch(args.status, ST_TIMEOUT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * (UMMA_K * 128), BK * 128, 1024)
+                                     : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                                     : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      const int split = w % splits;
+      const int tile = w / splits;
+      const int m0 = (tile / num_n) * BM;
+      const int n0 = (tile % num_n) * TILE_N;
+      const int kb0 = split * kb_per;
+      const int kb1 = min(num_kb, kb0 + kb_per);
+      if (kb0 >= kb1) continue;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
+        if (lane == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < M;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+
+      if constexpr (EPI == EPI_SWIGLU) {
+        __nv_bfloat16* Cb = reinterpret_cast<__nv_bfloat16*>(args.C);
+        __nv_bfloat16* Pb = const_cast<__nv_bfloat16*>(args.R);
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t v[32], g[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld32(taddr + BN / 2 + c, g);
+          tmem_ld_wait();
+          if (c + 32 >= BN / 2) {
+            // last read of this accumulator: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          const int col = n0 + c;
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < n_extent) {
+                uint4 ov, pv, pg;
+                uint32_t* o = reinterpret_cast<uint32_t*>(&ov);
+                uint32_t* p1 = reinterpret_cast<uint32_t*>(&pv);
+                uint32_t* p2 = reinterpret_cast<uint32_t*>(&pg);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float v0 = __uint_as_float(v[j + 2 * e]), v1 = __uint_as_float(v[j + 2 * e + 1]);
+                  const float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
+                  p1[e] = pack_bf16x2(v0, v1);
+                  p2[e] = pack_bf16x2(g0, g1);
+                  // activation is computed from the bf16-rounded pre-activations so that the
+                  // backward pass (which only sees the stored bf16 values) is consistent
+                  const float2 vr = unpack_bf16x2(p1[e]);
+                  const float2 gr = unpack_bf16x2(p2[e]);
+                  const float s0 = gr.x / (1.0f + __expf(-gr.x));
+                  const float s1 = gr.y / (1.0f + __expf(-gr.y));
+                  o[e] = pack_bf16x2(s0 * vr.x, s1 * vr.y);
+                }
+                *reinterpret_cast<uint4*>(Cb + static_cast<size_t>(row) * args.ldc + col + j) = ov;
+                if (Pb != nullptr) {
+                  *reinterpret_cast<uint4*>(Pb + static_cast<size_t>(row) * args.ldr + col + j) = pv;
+                  *reinterpret_cast<uint4*>(Pb + static_cast<size_t>(row) * args.ldr +
+                                            args.swiglu_half + col + j) = pg;
+                }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c, r);
+          tmem_ld_wait();
+          if (c + 32 >= BN) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          const int col = n0 + c;
+          if (row_ok) {
+            if constexpr (EPI == EPI_ATOMIC_F32 || EPI == EPI_STORE_F32) {
+              float* Cf = reinterpret_cast<float*>(args.C) + static_cast<size_t>(row) * args.ldc;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                if (col + j < N) {
+                  float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                         __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                  if constexpr (EPI == EPI_ATOMIC_F32) {
+                    atomicAdd(reinterpret_cast<float4*>(Cf + col + j), v);
+                  } else {
+                    *reinterpret_cast<float4*>(Cf + col + j) = v;
+                  }
+                }
+              }
+            } else {
+              __nv_bfloat16* Cb =
+                  reinterpret_cast<__nv_bfloat16*>(args.C) + static_cast<size_t>(row) * args.ldc;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (col + j < N) {
+                  uint4 ov;
+                  uint32_t* o = reinterpret_cast<uint32_t*>(&ov);
+                  if constexpr (EPI == EPI_ADD) {
+                    const uint4 rv = *reinterpret_cast<const uint4*>(
+                        args.R + static_cast<size_t>(row) * args.ldr + col + j);
+                    const uint32_t* rr = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 f = unpack_bf16x2(rr[e]);
+                      o[e] = pack_bf16x2(__uint_as_float(r[j + 2 * e]) + f.x,
+                                         __uint_as_float(r[j + 2 * e + 1]) + f.y);
+                    }
+                  } else if constexpr (EPI == EPI_GELU) {
+                    uint4 pv;
+                    uint32_t* p = reinterpret_cast<uint32_t*>(&pv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      p[e] = pack_bf16x2(__uint_as_float(r[j + 2 * e]),
+                                         __uint_as_float(r[j + 2 * e + 1]));
+                      const float2 f = unpack_bf16x2(p[e]);
+                      o[e] = pack_bf16x2(gelu_erf(f.x), gelu_erf(f.y));
+                    }
+                    if (args.R != nullptr) {
+                      *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(args.R) +
+                                                static_cast<size_t>(row) * args.ldr + col + j) = pv;
+                    }
+                  } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                      o[e] = pack_bf16x2(__uint_as_float(r[j + 2 * e]),
+                                         __uint_as_float(r[j + 2 * e + 1]));
+                  }
+                  *reinterpret_cast<uint4*>(Cb + col + j) = ov;
+                }
+              }
+            }
+          }
+        }
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map, 128-byte swizzle. inner = contiguous extent, outer = rows.
+static int make_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer,
+                       int elem_bytes) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_elems * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt =
+      elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int g_num_sms = 0;
+
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
+                  int max_ctas, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured = true;
+  }
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int n_extent = (EPI == EPI_SWIGLU) ? args.swiglu_half : args.N;
+  const int num_m = (args.M + BM - 1) / BM;
+  const int num_n = (n_extent + TILE_N - 1) / TILE_N;
+  const int total = num_m * num_n * args.splits;
+  int grid = total < num_sms() ? total : num_sms();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, args);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace nplm
+
+using namespace nplm;
+
+// C ABI entry point. Returns 0 on success, a cudaError_t (>0) or a negative code for bad
+// arguments. `status` is a device int the kernel writes a non-zero code to if a bounded wait
+// ran out. `max_ctas` (0 = all SMs) caps the grid so a concurrent communication kernel keeps
+// some SMs.
+extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
+                              int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn,
+                              int epi, int splits, int bn, int max_ctas, int* status,
+                              cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))
+    return -3;
+  if (a_mn && (M % 64)) return -4;
+  if (b_mn && (N % 64)) return -4;
+  if (epi == EPI_SWIGLU && (b_mn || (N % 2) || ((N / 2) % 8))) return -4;
+  if ((epi == EPI_ATOMIC_F32 || epi == EPI_STORE_F32) ? (N % 4 || ldc % 4) : (N % 8 || ldc % 8))
+    return -5;
+  if (bn != 128 && bn != 256) return -6;
+  const int num_kb = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > num_kb) splits = num_kb;
+  if (epi != EPI_ATOMIC_F32) splits = 1;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = make_map_2d(&tmA, A, K, M, lda, BK, BM, 2);
+  else
+    rc = make_map_2d(&tmA, A, M, K, lda, 64, BK, 2);
+  if (rc) return rc;
+  if (epi == EPI_SWIGLU)
+    rc = make_map_2d(&tmB, B, K, N, ldb, BK, bn / 2, 2);
+  else if (!b_mn)
+    rc = make_map_2d(&tmB, B, K, N, ldb, BK, bn, 2);
+  else
+    rc = make_map_2d(&tmB, B, N, K, ldb, 64, BK, 2);
+  if (rc) return rc;
+
+  GemmArgs args;
+  args.C = C;
+  args.R = reinterpret_cast<const __nv_bfloat16*>(R);
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.ldr = ldr;
+  args.splits = splits;
+  args.swiglu_half = N / 2;
+  args.status = status;
+
+#define NPLM_DISPATCH_EPI(BN_, AMN_, BMN_)                                                   \
+  switch (epi) {                                                                             \
+    case EPI_STORE: return launch<BN_, AMN_, BMN_, EPI_STORE>(tmA, tmB, args, max_ctas, stream); \
+    case EPI_ADD: return launch<BN_, AMN_, BMN_, EPI_ADD>(tmA, tmB, args, max_ctas, stream);     \
+    case EPI_ATOMIC_F32:                                                                     \
+      return launch<BN_, AMN_, BMN_, EPI_ATOMIC_F32>(tmA, tmB, args, max_ctas, stream);      \
+    case EPI_STORE_F32:                                                                      \
+      return launch<BN_, AMN_, BMN_, EPI_STORE_F32>(tmA, tmB, args, max_ctas, stream);       \
+    default: break;                                                                          \
+  }
+
+  if (epi == EPI_GELU) {
+    if (a_mn || b_mn) return -7;
+    if (bn == 256) return launch<256, false, false, EPI_GELU>(tmA, tmB, args, max_ctas, stream);
+    return launch<128, false, false, EPI_GELU>(tmA, tmB, args, max_ctas, stream);
+  }
+  if (epi == EPI_SWIGLU) {
+    if (a_mn || b_mn) return -7;
+    if (bn == 256) return launch<256, false, false, EPI_SWIGLU>(tmA, tmB, args, max_ctas, stream);
+    return launch<128, false, false, EPI_SWIGLU>(tmA, tmB, args, max_ctas, stream);
+  }
+  if (bn == 256) {
+    if (!a_mn && !b_mn) { NPLM_DISPATCH_EPI(256, false, false) }
+    else if (!a_mn && b_mn) { NPLM_DISPATCH_EPI(256, false, true) }
+    else if (a_mn && b_mn) { NPLM_DISPATCH_EPI(256, true, true) }
+    else { NPLM_DISPATCH_EPI(256, true, false) }
+  } else {
+    if (!a_mn && !b_mn) { NPLM_DISPATCH_EPI(128, false, false) }
+    else if (!a_mn && b_mn) { NPLM_DISPATCH_EPI(128, false, true) }
+    else if (a_mn && b_mn) { NPLM_DISPATCH_EPI(128, true, true) }
+    else { NPLM_DISPATCH_EPI(128, true, false) }
+  }
+  return -8;
+}

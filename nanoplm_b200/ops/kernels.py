@@ -1,0 +1,319 @@
+"""Thin tensor-level wrappers over the C ABI of the sm_100a kernels (no autograd here).
+
+Every function takes CUDA tensors, checks shapes / dtypes / contiguity, launches on the current
+stream and returns output tensors. ``nanoplm_b200.ops.functional`` builds differentiable ops on top.
+"""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong
+
+import torch
+
+from . import _lib
+from ._lib import check_rc, count_launch, lib, ptr, status_word, stream_ptr
+
+EPI_STORE, EPI_ADD, EPI_ATOMIC_F32, EPI_GELU, EPI_STORE_F32, EPI_SWIGLU = 0, 1, 2, 3, 4, 5
+
+_BF16 = torch.bfloat16
+
+
+def _chk(t: torch.Tensor, dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _rowmajor(t: torch.Tensor, name: str) -> int:
+    """Returns the row stride of a 2-D tensor whose last dim is contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with a contiguous last dim")
+    return t.stride(0)
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         epi: int = EPI_STORE, out: torch.Tensor | None = None, aux: torch.Tensor | None = None,
+         splits: int = 1, bn: int | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """C[M,N] (+)= op(A) op(B)^T on tcgen05 tensor cores.
+
+    a: [M,K] (a_mn=False) or [K,M] (a_mn=True); b: [N,K] (b_mn=False) or [K,N] (b_mn=True).
+    epi: EPI_STORE / EPI_ADD (aux = residual) / EPI_ATOMIC_F32 (out fp32, accumulated in place) /
+    EPI_GELU (aux = optional pre-activation output) / EPI_STORE_F32 / EPI_SWIGLU (out is N/2 wide,
+    aux = optional [M,N] pre-activation output).
+    """
+    _chk(a, _BF16, "a")
+    _chk(b, _BF16, "b")
+    lda, ldb = _rowmajor(a, "a"), _rowmajor(b, "b")
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"inner dims differ: {K} vs {Kb}")
+    out_cols = N // 2 if epi == EPI_SWIGLU else N
+    f32_out = epi in (EPI_ATOMIC_F32, EPI_STORE_F32)
+    if out is None:
+        if epi == EPI_ATOMIC_F32:
+            raise ValueError("EPI_ATOMIC_F32 needs an fp32 accumulator passed as out")
+        out = torch.empty((M, out_cols), dtype=torch.float32 if f32_out else _BF16, device=a.device)
+    _chk(out, torch.float32 if f32_out else _BF16, "out")
+    if tuple(out.shape) != (M, out_cols):
+        raise ValueError(f"out has shape {tuple(out.shape)}, expected {(M, out_cols)}")
+    ldc = _rowmajor(out, "out")
+    ldr = 0
+    if aux is not None:
+        _chk(aux, _BF16, "aux")
+        ldr = _rowmajor(aux, "aux")
+        if tuple(aux.shape) != (M, N):
+            raise ValueError(f"aux has shape {tuple(aux.shape)}, expected {(M, N)}")
+    elif epi == EPI_ADD:
+        raise ValueError("EPI_ADD needs the residual passed as aux")
+    if bn is None:
+        bn = 256 if (N >= 256 or epi == EPI_SWIGLU) else 128
+    rc = lib("gemm_tcgen05").nplm_gemm_bf16(
+        ptr(a), ptr(b), ptr(out), ptr(aux), c_int(M), c_int(N), c_int(K), c_int(lda), c_int(ldb),
+        c_int(ldc), c_int(ldr), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi), c_int(splits),
+        c_int(bn), c_int(max_ctas), ptr(status_word(a.device)), stream_ptr())
+    check_rc(rc, "gemm_bf16")
+    count_launch()
+    return out
+
+
+def wgrad_splits(n_out: int, k_in: int, tokens: int, bn: int = 256) -> int:
+    """Split-K factor that fills ~148 SMs for a weight-gradient GEMM [n_out, k_in] over `tokens`."""
+    tiles = ((n_out + 127) // 128) * ((k_in + bn - 1) // bn)
+    kb = (tokens + 63) // 64
+    s = max(1, min(148 // max(1, tiles), kb // 8 if kb >= 8 else 1))
+    return max(1, s)
+
+
+# --------------------------------------------------------------------------- norms
+def norm_fwd(x: torch.Tensor, w: torch.Tensor | None, eps: float, rms: bool = False,
+             ids: torch.Tensor | None = None):
+    """LayerNorm (no bias) / RMSNorm over the last dim. With ids, rows are table[ids] (embedding).
+
+    Returns (y, mean, rstd); mean is None for RMSNorm.
+    """
+    _chk(x, _BF16, "x")
+    C = x.shape[-1]
+    if ids is not None:
+        _chk(ids, torch.int32, "ids")
+        T = ids.numel()
+    else:
+        T = x.numel() // C
+    x2 = x.reshape(-1, C)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = torch.empty((T, C), dtype=_BF16, device=x.device)
+    mean = None if rms else torch.empty(T, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    rc = lib("elementwise").nplm_norm_fwd(ptr(x2), ptr(ids), ptr(w), ptr(y), ptr(mean), ptr(rstd),
+                                          c_int(T), c_int(C), c_float(eps), c_int(int(rms)),
+                                          stream_ptr())
+    check_rc(rc, "norm_fwd")
+    count_launch()
+    return y, mean, rstd
+
+
+def norm_bwd(dy, x, w, mean, rstd, *, rms=False, dres=None, dw=None, ids=None, dtable=None):
+    """Backward of norm_fwd. dw (fp32 [C]) and dtable (fp32 [V,C]) are accumulated in place.
+
+    Returns dx (None in embedding mode)."""
+    C = dy.shape[-1]
+    T = dy.numel() // C
+    dy2 = dy.reshape(T, C)
+    if not dy2.is_contiguous():
+        dy2 = dy2.contiguous()
+    dx = None if ids is not None else torch.empty((T, C), dtype=_BF16, device=dy.device)
+    rc = lib("elementwise").nplm_norm_bwd(
+        ptr(dy2), ptr(x), ptr(ids), ptr(w), ptr(mean), ptr(rstd), ptr(dres), ptr(dx), ptr(dw),
+        ptr(dtable), c_int(T), c_int(C), c_int(int(rms)), stream_ptr())
+    check_rc(rc, "norm_bwd")
+    count_launch()
+    return dx
+
+
+# --------------------------------------------------------------------------- rope / swiglu / act
+def rope_(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, H: int,
+          D: int, backward: bool = False) -> torch.Tensor:
+    """In-place rotary embedding on the q and k parts of qkv [T, 3*H*D]."""
+    _chk(qkv, _BF16, "qkv")
+    _chk(pos, torch.int32, "pos")
+    T = qkv.shape[0]
+    rc = lib("elementwise").nplm_rope(ptr(qkv), ptr(pos), ptr(cos), ptr(sin), c_int(T), c_int(H),
+                                      c_int(D), c_int(int(backward)), stream_ptr())
+    check_rc(rc, "rope")
+    count_launch()
+    return qkv
+
+
+def swiglu_fwd(pre: torch.Tensor) -> torch.Tensor:
+    T, two_i = pre.shape
+    out = torch.empty((T, two_i // 2), dtype=_BF16, device=pre.device)
+    rc = lib("elementwise").nplm_swiglu_fwd(ptr(pre), ptr(out), c_longlong(T), c_int(two_i // 2),
+                                            stream_ptr())
+    check_rc(rc, "swiglu_fwd")
+    count_launch()
+    return out
+
+
+def swiglu_bwd(pre: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
+    T, two_i = pre.shape
+    dpre = torch.empty_like(pre)
+    rc = lib("elementwise").nplm_swiglu_bwd(ptr(pre), ptr(dout), ptr(dpre), c_longlong(T),
+                                            c_int(two_i // 2), stream_ptr())
+    check_rc(rc, "swiglu_bwd")
+    count_launch()
+    return dpre
+
+
+_ACT = {"gelu": 0, "relu": 1, "silu": 2}
+
+
+def act_fwd(pre: torch.Tensor, act: str) -> torch.Tensor:
+    out = torch.empty_like(pre)
+    rc = lib("elementwise").nplm_act_fwd(ptr(pre), ptr(out), c_longlong(pre.numel()),
+                                         c_int(_ACT[act]), stream_ptr())
+    check_rc(rc, "act_fwd")
+    count_launch()
+    return out
+
+
+def act_bwd(pre: torch.Tensor, dout: torch.Tensor, act: str) -> torch.Tensor:
+    dpre = torch.empty_like(pre)
+    rc = lib("elementwise").nplm_act_bwd(ptr(pre), ptr(dout), ptr(dpre), c_longlong(pre.numel()),
+                                         c_int(_ACT[act]), stream_ptr())
+    check_rc(rc, "act_bwd")
+    count_launch()
+    return dpre
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    n, C = idx.numel(), src.shape[1]
+    dst = torch.empty((n, C), dtype=_BF16, device=src.device)
+    rc = lib("elementwise").nplm_gather_rows(ptr(src), ptr(idx), ptr(dst), c_int(n), c_int(C),
+                                             stream_ptr())
+    check_rc(rc, "gather_rows")
+    count_launch()
+    return dst
+
+
+def scatter_rows_(dst: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    n, C = idx.numel(), src.shape[1]
+    rc = lib("elementwise").nplm_scatter_rows(ptr(src), ptr(idx), ptr(dst), c_int(n), c_int(C),
+                                              stream_ptr())
+    check_rc(rc, "scatter_rows")
+    count_launch()
+    return dst
+
+
+# --------------------------------------------------------------------------- cross entropy
+def ce_fwd(h, W, bias, labels, inv_count, want_logits=False):
+    n, C = h.shape
+    V = W.shape[0]
+    dlogits = torch.empty((n, 32), dtype=torch.float32, device=h.device)
+    logits = torch.empty((n, V), dtype=torch.float32, device=h.device) if want_logits else None
+    loss = torch.zeros(1, dtype=torch.float32, device=h.device)
+    rc = lib("elementwise").nplm_ce_fwd(ptr(h), ptr(W), ptr(bias), ptr(labels), ptr(inv_count),
+                                        ptr(dlogits), ptr(logits), ptr(loss), c_int(n), c_int(C),
+                                        c_int(V), stream_ptr())
+    check_rc(rc, "ce_fwd")
+    count_launch()
+    return loss, dlogits, logits
+
+
+def ce_bwd(h, W, dlogits, gscale, dW, dbias):
+    n, C = h.shape
+    V = W.shape[0]
+    dh = torch.empty_like(h)
+    rc = lib("elementwise").nplm_ce_bwd(ptr(h), ptr(W), ptr(dlogits), ptr(gscale), ptr(dh), ptr(dW),
+                                        ptr(dbias), c_int(n), c_int(C), c_int(V), stream_ptr())
+    check_rc(rc, "ce_bwd")
+    count_launch()
+    return dh
+
+
+# --------------------------------------------------------------------------- optimizer
+def sumsq_(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    rc = lib("elementwise").nplm_sumsq(ptr(x), c_longlong(x.numel()), ptr(out), stream_ptr())
+    check_rc(rc, "sumsq")
+    count_launch()
+    return out
+
+
+def adamw_(p, m, v, g, p_bf16, hyper, sumsq, zero_grad=True) -> None:
+    rc = lib("elementwise").nplm_adamw(ptr(p), ptr(m), ptr(v), ptr(g), ptr(p_bf16), ptr(hyper),
+                                       ptr(sumsq), c_longlong(p.numel()), c_int(int(zero_grad)),
+                                       stream_ptr())
+    check_rc(rc, "adamw")
+    count_launch()
+
+
+def cast_f32_bf16_(src: torch.Tensor, dst: torch.Tensor) -> None:
+    rc = lib("elementwise").nplm_cast_f32_bf16(ptr(src), ptr(dst), c_longlong(src.numel()),
+                                               stream_ptr())
+    check_rc(rc, "cast")
+    count_launch()
+
+
+def masked_mse(s, t, valid, inv_count, want_grad=True):
+    T, C = s.shape
+    ds = torch.empty_like(s) if want_grad else None
+    loss = torch.zeros(1, dtype=torch.float32, device=s.device)
+    rc = lib("elementwise").nplm_masked_mse(ptr(s), ptr(t), ptr(valid), ptr(inv_count), ptr(ds),
+                                            ptr(loss), c_int(T), c_int(C), stream_ptr())
+    check_rc(rc, "masked_mse")
+    count_launch()
+    return loss, ds
+
+
+# --------------------------------------------------------------------------- attention
+def seq_bounds(cu_seqlens: torch.Tensor, T: int):
+    _chk(cu_seqlens, torch.int32, "cu_seqlens")
+    s = torch.empty(T, dtype=torch.int32, device=cu_seqlens.device)
+    e = torch.empty(T, dtype=torch.int32, device=cu_seqlens.device)
+    rc = lib("attention").nplm_seq_bounds(ptr(cu_seqlens), c_int(cu_seqlens.numel() - 1), ptr(s),
+                                          ptr(e), c_int(T), stream_ptr())
+    check_rc(rc, "seq_bounds")
+    count_launch()
+    return s, e
+
+
+def fa_fwd(qkv, seq_start, seq_end, H, D, window, scale):
+    _chk(qkv, _BF16, "qkv")
+    T = qkv.shape[0]
+    out = torch.empty((T, H * D), dtype=_BF16, device=qkv.device)
+    lse = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
+    rc = lib("attention").nplm_fa_fwd(ptr(qkv), ptr(out), ptr(lse), ptr(seq_start), ptr(seq_end),
+                                      c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                      ptr(status_word(qkv.device)), stream_ptr())
+    check_rc(rc, "fa_fwd")
+    count_launch()
+    return out, lse
+
+
+def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=None, delta=None):
+    T = qkv.shape[0]
+    dqkv = torch.empty_like(qkv)
+    if dq_acc is None:
+        dq_acc = torch.empty((T, H * D), dtype=torch.float32, device=qkv.device)
+    if delta is None:
+        delta = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
+    if not dout.is_contiguous():
+        dout = dout.contiguous()
+    rc = lib("attention").nplm_fa_bwd(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
+                                      ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
+                                      c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                      ptr(status_word(qkv.device)), stream_ptr())
+    check_rc(rc, "fa_bwd")
+    count_launch(4)
+    return dqkv
+
+
+def check_status() -> None:
+    _lib.check_status()

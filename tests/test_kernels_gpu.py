@@ -1,0 +1,334 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+BF = torch.bfloat16
+
+
+def _k():
+    from nanoplm_b200.ops import kernels
+    return kernels
+
+
+def _randn(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(BF)
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
+    a = a.float()
+    b = b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert torch.allclose(a, b, rtol=rtol, atol=atol * max(1.0, ref)), f"{what}: max err {err} (ref max {ref})"
+
+
+# ------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (384, 512, 320), (300, 264, 200),
+                                   (1000, 1024, 1024), (4096, 3072, 1024)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_kk(M, N, K, bn, cuda_status):
+    k = _k()
+    a, b = _randn(M, K), _randn(N, K)
+    c = k.gemm(a, b, bn=bn)
+    ref = a.float() @ b.float().t()
+    _close(c, ref, what=f"gemm {M}x{N}x{K} bn{bn}")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 320, 200), (1024, 1024, 4096)])
+def test_gemm_majors(a_mn, b_mn, M, N, K, cuda_status):
+    k = _k()
+    a = _randn(K, M) if a_mn else _randn(M, K)
+    b = _randn(K, N) if b_mn else _randn(N, K)
+    for bn in (128, 256):
+        c = k.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn)
+        af = a.float().t() if a_mn else a.float()
+        bf = b.float() if b_mn else b.float().t()
+        _close(c, af @ bf, what=f"gemm majors a_mn={a_mn} b_mn={b_mn} {M}x{N}x{K} bn{bn}")
+
+
+def test_gemm_epilogues(cuda_status):
+    k = _k()
+    M, N, K = 512, 768, 256
+    a, b = _randn(M, K), _randn(N, K, scale=0.1)
+    ref = a.float() @ b.float().t()
+    res = _randn(M, N)
+    _close(k.gemm(a, b, epi=k.EPI_ADD, aux=res), ref + res.float(), what="epi add")
+    _close(k.gemm(a, b, epi=k.EPI_STORE_F32), ref, what="epi f32")
+    pre = torch.empty(M, N, dtype=BF, device="cuda")
+    out = k.gemm(a, b, epi=k.EPI_GELU, aux=pre)
+    _close(pre, ref, what="gelu pre")
+    _close(out, F.gelu(pre.float()), what="gelu out")
+    # swiglu: b = [value rows | gate rows]
+    pre2 = torch.empty(M, N, dtype=BF, device="cuda")
+    out2 = k.gemm(a, b, epi=k.EPI_SWIGLU, aux=pre2)
+    _close(pre2, ref, what="swiglu pre")
+    v, g = pre2.float().chunk(2, dim=-1)
+    _close(out2, F.silu(g) * v, what="swiglu out")
+    assert out2.shape == (M, N // 2)
+
+
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_gemm_wgrad_atomic(splits, cuda_status):
+    k = _k()
+    T, N, K = 2048, 256, 384          # dW[N,K] = dY[T,N]^T X[T,K]
+    dy, x = _randn(T, N, scale=0.1), _randn(T, K)
+    acc = torch.ones(N, K, dtype=torch.float32, device="cuda")
+    k.gemm(dy, x, a_mn=True, b_mn=True, epi=k.EPI_ATOMIC_F32, out=acc, splits=splits)
+    ref = 1.0 + dy.float().t() @ x.float()
+    _close(acc, ref, what=f"wgrad splits={splits}")
+
+
+def test_gemm_strided_views(cuda_status):
+    """Operands that are column slices of a wider buffer (row stride > width)."""
+    k = _k()
+    big = _randn(512, 1024)
+    a = big[:, 128:384]                 # [512, 256], row stride 1024
+    b = _randn(192, 256)
+    out_big = torch.zeros(512, 512, dtype=BF, device="cuda")
+    out = out_big[:, 64:256]
+    k.gemm(a, b, out=out)
+    _close(out, a.float() @ b.float().t(), what="strided")
+    assert out_big[:, :64].abs().max().item() == 0 and out_big[:, 256:].abs().max().item() == 0
+
+
+# ------------------------------------------------------------------------------- norms
+@pytest.mark.parametrize("C", [128, 768, 1024])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fwd_bwd(C, rms, cuda_status):
+    k = _k()
+    T = 777
+    x = _randn(T, C)
+    w = (1 + 0.1 * torch.randn(C, device="cuda")).to(BF)
+    dy = _randn(T, C)
+    dres = _randn(T, C)
+    y, mean, rstd = k.norm_fwd(x, w, 1e-5, rms=rms)
+    xf = x.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    if rms:
+        ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    else:
+        ref = F.layer_norm(xf, (C,), wf, None, 1e-5)
+    _close(y, ref, what="norm fwd")
+    ref.backward(dy.float())
+    dw = torch.zeros(C, dtype=torch.float32, device="cuda")
+    dx = k.norm_bwd(dy, x, w, mean, rstd, rms=rms, dres=dres, dw=dw)
+    _close(dx, xf.grad + dres.float(), what="norm dx")
+    _close(dw, wf.grad, rtol=3e-2, atol=3e-2, what="norm dw")
+
+
+def test_embed_norm(cuda_status):
+    k = _k()
+    V, C, T = 32, 1024, 3000
+    table = _randn(V, C, scale=0.02)
+    w = (1 + 0.1 * torch.randn(C, device="cuda")).to(BF)
+    ids = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+    y, mean, rstd = k.norm_fwd(table, w, 1e-5, ids=ids)
+    tf = table.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    ref = F.layer_norm(F.embedding(ids.long(), tf), (C,), wf, None, 1e-5)
+    _close(y, ref, what="embed fwd")
+    dy = _randn(T, C)
+    ref.backward(dy.float())
+    dtable = torch.zeros(V, C, dtype=torch.float32, device="cuda")
+    dw = torch.zeros(C, dtype=torch.float32, device="cuda")
+    k.norm_bwd(dy, table, w, mean, rstd, ids=ids, dtable=dtable, dw=dw)
+    _close(dtable, tf.grad, rtol=3e-2, atol=3e-2, what="embed dtable")
+    _close(dw, wf.grad, rtol=3e-2, atol=3e-2, what="embed dw")
+
+
+# ------------------------------------------------------------------------------- rope / swiglu / act
+def _rope_ref(x, cos, sin):
+    x1, x2 = x.chunk(2, dim=-1)
+    rot = torch.cat((-x2, x1), dim=-1)
+    return x * cos + rot * sin
+
+
+def test_rope(cuda_status):
+    k = _k()
+    T, H, D = 1000, 4, 64
+    qkv = _randn(T, 3 * H * D)
+    pos = torch.randint(0, 512, (T,), device="cuda", dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    fr = torch.outer(torch.arange(512, device="cuda").float(), inv)
+    cos, sin = fr.cos().contiguous(), fr.sin().contiguous()
+    ref = qkv.float().view(T, 3, H, D).clone()
+    c = torch.cat((cos, cos), -1)[pos.long()][:, None, :]
+    s = torch.cat((sin, sin), -1)[pos.long()][:, None, :]
+    ref[:, 0] = _rope_ref(ref[:, 0], c, s)
+    ref[:, 1] = _rope_ref(ref[:, 1], c, s)
+    orig = qkv.clone()
+    k.rope_(qkv, pos, cos, sin, H, D)
+    _close(qkv.view(T, 3, H, D), ref, what="rope fwd")
+    # backward of a rotation is the inverse rotation
+    k.rope_(qkv, pos, cos, sin, H, D, backward=True)
+    _close(qkv, orig, what="rope bwd")
+
+
+def test_swiglu_and_act(cuda_status):
+    k = _k()
+    T, I = 500, 256
+    pre = _randn(T, 2 * I)
+    dout = _randn(T, I)
+    pf = pre.float().requires_grad_(True)
+    v, g = pf.chunk(2, -1)
+    ref = F.silu(g) * v
+    _close(k.swiglu_fwd(pre), ref, what="swiglu fwd")
+    ref.backward(dout.float())
+    _close(k.swiglu_bwd(pre, dout), pf.grad, what="swiglu bwd")
+    for name, fn in (("gelu", F.gelu), ("relu", F.relu), ("silu", F.silu)):
+        p = _randn(T, I)
+        pf = p.float().requires_grad_(True)
+        r = fn(pf)
+        _close(k.act_fwd(p, name), r, what=f"{name} fwd")
+        r.backward(dout.float())
+        _close(k.act_bwd(p, dout, name), pf.grad, what=f"{name} bwd")
+
+
+def test_gather_scatter(cuda_status):
+    k = _k()
+    src = _randn(1000, 256)
+    idx = torch.randperm(1000, device="cuda")[:300].to(torch.int32)
+    g = k.gather_rows(src, idx)
+    assert torch.equal(g, src[idx.long()])
+    dst = torch.zeros(1000, 256, dtype=BF, device="cuda")
+    k.scatter_rows_(dst, idx, g)
+    ref = torch.zeros_like(dst)
+    ref[idx.long()] = g
+    assert torch.equal(dst, ref)
+
+
+# ------------------------------------------------------------------------------- cross entropy
+@pytest.mark.parametrize("V", [32, 28])
+def test_cross_entropy(V, cuda_status):
+    k = _k()
+    n, C = 3001, 1024
+    h = _randn(n, C)
+    W = _randn(V, C, scale=0.05)
+    bias = _randn(V, scale=0.1)
+    labels = torch.randint(0, V, (n,), device="cuda", dtype=torch.int32)
+    labels[::7] = -100
+    nvalid = (labels >= 0).sum().float()
+    inv = (1.0 / nvalid).reshape(1)
+    loss, dlogits, logits = k.ce_fwd(h, W, bias, labels, inv, want_logits=True)
+    hf, Wf, bf = h.float().requires_grad_(True), W.float().requires_grad_(True), bias.float().requires_grad_(True)
+    ref_logits = hf @ Wf.t() + bf
+    ref = F.cross_entropy(ref_logits, labels.long(), ignore_index=-100)
+    _close(logits, ref_logits, what="ce logits")
+    assert abs(loss.item() - ref.item()) < 2e-3 * max(1, abs(ref.item())), (loss.item(), ref.item())
+    (ref * 0.5).backward()
+    gs = torch.full((1,), 0.5, device="cuda")
+    dW = torch.zeros(V, C, dtype=torch.float32, device="cuda")
+    db = torch.zeros(V, dtype=torch.float32, device="cuda")
+    dh = k.ce_bwd(h, W, dlogits, gs, dW, db)
+    _close(dh, hf.grad, rtol=3e-2, atol=3e-2, what="ce dh")
+    _close(dW, Wf.grad, rtol=3e-2, atol=3e-2, what="ce dW")
+    _close(db, bf.grad, rtol=3e-2, atol=3e-2, what="ce dbias")
+
+
+# ------------------------------------------------------------------------------- optimizer
+def test_adamw_and_sumsq(cuda_status):
+    k = _k()
+    n = 100_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda") * 3
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    pb = torch.empty(n, dtype=BF, device="cuda")
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1)
+    ss = torch.zeros(1, device="cuda")
+    k.sumsq_(g, ss)
+    assert abs(ss.item() - g.double().pow(2).sum().item()) / ss.item() < 1e-4
+    for step in range(1, 4):
+        ref_p.grad = g.clone()
+        torch.nn.utils.clip_grad_norm_([ref_p], 1.0)
+        opt.step()
+        hyper = torch.tensor([1e-2, 0.9, 0.999, 1e-8, 0.1, 1 - 0.9 ** step, 1 - 0.999 ** step, 1.0, 1.0],
+                             device="cuda")
+        gg = g.clone()
+        k.adamw_(p, m, v, gg, pb, hyper, ss, zero_grad=True)
+        assert gg.abs().max().item() == 0
+    _close(p, ref_p.detach(), rtol=1e-4, atol=1e-5, what="adamw p")
+    _close(pb, ref_p.detach(), what="adamw bf16 copy")
+
+
+def test_masked_mse(cuda_status):
+    k = _k()
+    T, C = 999, 1024
+    s, t = _randn(T, C), _randn(T, C)
+    valid = (torch.rand(T, device="cuda") > 0.3).to(torch.int32)
+    inv = (1.0 / valid.sum().clamp(min=1).float()).reshape(1)
+    loss, ds = k.masked_mse(s, t, valid, inv)
+    sf = s.float().requires_grad_(True)
+    ref = (((sf - t.float()) ** 2) * valid[:, None].float()).sum() / valid.sum().clamp(min=1)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) / ref.item() < 1e-3
+    _close(ds, sf.grad, what="mse grad")
+
+
+# ------------------------------------------------------------------------------- attention
+def _attn_ref(qkv, cu, H, D, window, scale):
+    """Dense masked softmax attention in fp32; returns out [T, H*D] and leaves autograd on."""
+    T = qkv.shape[0]
+    q, kk, v = qkv.view(T, 3, H, D).unbind(1)
+    seq_id = torch.zeros(T, dtype=torch.long, device=qkv.device)
+    for i in range(len(cu) - 1):
+        seq_id[cu[i]:cu[i + 1]] = i
+    pos = torch.arange(T, device=qkv.device)
+    mask = seq_id[:, None] == seq_id[None, :]
+    if window >= 0:
+        mask &= (pos[:, None] - pos[None, :]).abs() <= window
+    s = torch.einsum("thd,shd->hts", q, kk) * scale
+    s = s.masked_fill(~mask[None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("hts,shd->thd", p, v).reshape(T, H * D)
+
+
+@pytest.mark.parametrize("lens", [[128], [50, 200, 6, 300, 77], [512, 512], [1, 2, 3, 700, 20, 20, 20, 20, 190]])
+@pytest.mark.parametrize("window", [-1, 64])
+def test_attention_fwd_bwd(lens, window, cuda_status):
+    k = _k()
+    H, D = 4, 64
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    qkv = _randn(T, 3 * H * D)
+    scale = D ** -0.5
+    ss, se = k.seq_bounds(cu_t, T)
+    out, lse = k.fa_fwd(qkv, ss, se, H, D, window, scale)
+    qf = qkv.float().requires_grad_(True)
+    ref = _attn_ref(qf, cu, H, D, window, scale)
+    _close(out, ref, what=f"attn fwd {lens} w={window}")
+    dout = _randn(T, H * D)
+    ref.backward(dout.float())
+    dqkv = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, scale)
+    _close(dqkv, qf.grad, rtol=3e-2, atol=3e-2, what=f"attn bwd {lens} w={window}")
+
+
+def test_attention_determinism_and_big(cuda_status):
+    k = _k()
+    H, D = 16, 64
+    g = torch.Generator().manual_seed(1)
+    lens = torch.randint(20, 513, (60,), generator=g).tolist()
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    qkv = _randn(T, 3 * H * D)
+    ss, se = k.seq_bounds(cu_t, T)
+    o1, l1 = k.fa_fwd(qkv, ss, se, H, D, -1, 0.125)
+    o2, l2 = k.fa_fwd(qkv, ss, se, H, D, -1, 0.125)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    # compare one head against the dense oracle
+    sub = qkv.view(T, 3, H, D)[:, :, :2].reshape(T, 3 * 2 * D).contiguous()
+    ref = _attn_ref(sub.float(), cu, 2, D, -1, 0.125)
+    _close(o1.view(T, H, D)[:, :2].reshape(T, 2 * D), ref, what="attn big")
