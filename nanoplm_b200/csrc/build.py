@@ -78,10 +78,33 @@ def build_one(name: str, verbose: bool = False, force: bool = False) -> Path:
     return out
 
 
+HOST_SOURCES = ["packer.cpp"]
+
+
+def build_host(name: str, force: bool = False) -> Path:
+    """Builds a host-only C++ source (no CUDA) with g++."""
+    src = CSRC / name
+    out = lib_path(name)
+    stamp = out.with_suffix(".sha")
+    digest = hashlib.sha256(src.read_bytes()).hexdigest()
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+        return out
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-o", str(out), str(src)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"g++ failed for {name}:\n{proc.stdout}\n{proc.stderr}")
+    stamp.write_text(digest)
+    return out
+
+
 def build_all(verbose: bool = False, force: bool = False) -> list[Path]:
     names = [n for n in SOURCES if (CSRC / n).exists()]
     with ThreadPoolExecutor(max_workers=min(8, len(names))) as ex:
-        return list(ex.map(lambda n: build_one(n, verbose, force), names))
+        libs = list(ex.map(lambda n: build_one(n, verbose, force), names))
+    libs += [build_host(n, force) for n in HOST_SOURCES if (CSRC / n).exists()]
+    return libs
 
 
 if __name__ == "__main__":

@@ -42,10 +42,11 @@ def lib(name: str) -> ctypes.CDLL:
     with _LOCK:
         if name in _LIBS:
             return _LIBS[name]
-        src = f"{name}.cu"
+        host = (_build.CSRC / f"{name}.cpp").exists()
+        src = f"{name}.cpp" if host else f"{name}.cu"
         path = _build.lib_path(src)
         if not path.exists():
-            path = _build.build_one(src)
+            path = _build.build_host(src) if host else _build.build_one(src)
         handle = ctypes.CDLL(str(path))
         _LIBS[name] = handle
         return handle

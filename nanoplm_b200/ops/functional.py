@@ -1,0 +1,423 @@
+"""Differentiable ops of the encoder.
+
+Every op has two implementations behind one function:
+  * CUDA tensors run the hand-written sm_100a kernels (``nanoplm_b200.ops.kernels``) through a
+    ``torch.autograd.Function`` with an explicit backward;
+  * CPU tensors run a plain fp32 PyTorch restatement. That restatement is the numerical oracle of
+    the kernel tests and what the CPU plumbing configuration trains with.
+
+Weight gradients on CUDA: when a parameter carries a ``main_grad`` attribute (fp32, a view into the
+flat gradient buffer of the sharded optimizer) the weight-gradient GEMM accumulates into it
+directly from its epilogue (split-K, fp32 atomics) and autograd receives no ``.grad`` for that
+parameter. Without ``main_grad`` a regular gradient is returned.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import kernels as K
+
+BF = torch.bfloat16
+
+
+def _has_main_grad(p) -> bool:
+    return getattr(p, "main_grad", None) is not None
+
+
+def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
+    """dW[N,K] = dy2[T,N]^T x2[T,K]; accumulates into w.main_grad or returns a bf16 gradient."""
+    T, N = dy2.shape
+    Kd = x2.shape[1]
+    if N % 64 == 0 and Kd % 64 == 0:
+        if _has_main_grad(w):
+            K.gemm(dy2, x2, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=w.main_grad,
+                   splits=K.wgrad_splits(N, Kd, T))
+            return None
+        acc = torch.zeros((N, Kd), dtype=torch.float32, device=w.device)
+        K.gemm(dy2, x2, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=acc,
+               splits=K.wgrad_splits(N, Kd, T))
+        return acc.to(w.dtype)
+    g = dy2.float().t() @ x2.float()
+    if _has_main_grad(w):
+        w.main_grad.add_(g)
+        return None
+    return g.to(w.dtype)
+
+
+def _param_grad(p, g32: torch.Tensor):
+    """Routes a small fp32 gradient (norm weights, biases) to main_grad or returns it."""
+    if _has_main_grad(p):
+        p.main_grad.add_(g32.view_as(p.main_grad))
+        return None
+    return g32.to(p.dtype).view_as(p)
+
+
+# ------------------------------------------------------------------------------------- linear
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, residual, act):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not (x2.stride(1) == 1 and x2.stride(0) % 8 == 0):
+            x2 = x2.contiguous()
+        pre = None
+        if act == "gelu":
+            pre = torch.empty((x2.shape[0], w.shape[0]), dtype=BF, device=x.device)
+            y = K.gemm(x2, w, epi=K.EPI_GELU, aux=pre)
+        elif act == "swiglu":
+            pre = torch.empty((x2.shape[0], w.shape[0]), dtype=BF, device=x.device)
+            y = K.gemm(x2, w, epi=K.EPI_SWIGLU, aux=pre)
+        elif residual is not None:
+            y = K.gemm(x2, w, epi=K.EPI_ADD, aux=residual.reshape(-1, w.shape[0]))
+        else:
+            y = K.gemm(x2, w)
+        if bias is not None:
+            y += bias
+        ctx.save_for_backward(x2, w, pre)
+        ctx.act = act
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.bias_ref = bias
+        ctx.x_shape = x.shape
+        out_cols = y.shape[1]
+        return y.view(*x.shape[:-1], out_cols)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, pre = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if ctx.act == "gelu":
+            dpre = K.act_bwd(pre, dy2, "gelu")
+        elif ctx.act == "swiglu":
+            dpre = K.swiglu_bwd(pre, dy2)
+        else:
+            dpre = dy2
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm(dpre, w, b_mn=True).view(ctx.x_shape)
+        dw = _wgrad(dpre, x2, w) if ctx.needs_input_grad[1] else None
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _param_grad(ctx.bias_ref, dpre.float().sum(0))
+        dres = dy if ctx.has_res else None
+        return dx, dw, db, dres, None
+
+
+def linear(x, w, bias=None, residual=None, act: str | None = None):
+    """y = act(x w^T + bias) + residual.  act: None | "gelu" | "swiglu" (w rows = [value | gate],
+    output is half as wide). residual and act are mutually exclusive."""
+    if x.is_cuda:
+        if w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.dtype == BF:
+            if act == "swiglu" and bias is not None:
+                y = _LinearFn.apply(x, w, bias, None, None)
+                return swiglu(y)
+            return _LinearFn.apply(x, w, bias, residual, act)
+    y = F.linear(x, w, bias)
+    if act == "gelu":
+        y = F.gelu(y)
+    elif act == "swiglu":
+        v, g = y.chunk(2, dim=-1)
+        y = F.silu(g) * v
+    if residual is not None:
+        y = y + residual
+    return y
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pre):
+        p2 = pre.reshape(-1, pre.shape[-1]).contiguous()
+        ctx.save_for_backward(p2)
+        ctx.shape = pre.shape
+        return K.swiglu_fwd(p2).view(*pre.shape[:-1], pre.shape[-1] // 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (p2,) = ctx.saved_tensors
+        return K.swiglu_bwd(p2, dy.reshape(-1, dy.shape[-1]).contiguous()).view(ctx.shape)
+
+
+def swiglu(pre):
+    """pre = [value | gate] -> silu(gate) * value (reference: modeling.py:301-302)."""
+    if pre.is_cuda and pre.dtype == BF:
+        return _SwigluFn.apply(pre)
+    v, g = pre.chunk(2, dim=-1)
+    return F.silu(g) * v
+
+
+class _ActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pre, name):
+        p = pre.contiguous()
+        ctx.save_for_backward(p)
+        ctx.name = name
+        return K.act_fwd(p, name)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (p,) = ctx.saved_tensors
+        return K.act_bwd(p, dy.contiguous(), ctx.name), None
+
+
+def activation(x, name: str):
+    if x.is_cuda and x.dtype == BF and x.numel() % 8 == 0 and name in ("gelu", "relu", "silu"):
+        return _ActFn.apply(x, name)
+    return {"gelu": F.gelu, "relu": F.relu, "silu": F.silu, "tanh": torch.tanh}[name](x)
+
+
+# ------------------------------------------------------------------------------------- norms
+class _NormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, rms):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y, mean, rstd = K.norm_fwd(x2, w, eps, rms=rms)
+        ctx.save_for_backward(x2, w, mean, rstd)
+        ctx.rms = rms
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, mean, rstd = ctx.saved_tensors
+        dw = None
+        if w is not None and ctx.needs_input_grad[1]:
+            dw = w.main_grad if _has_main_grad(w) else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dx = K.norm_bwd(dy, x2, w, mean, rstd, rms=ctx.rms, dw=dw)
+        if dw is not None:
+            dw = None if _has_main_grad(w) else dw.to(w.dtype)
+        return dx.view(ctx.shape), dw, None, None
+
+
+def norm(x, w, eps: float = 1e-5, rms: bool = False):
+    """LayerNorm without bias (reference encoder norms) or RMSNorm (T5LayerNorm) over the last dim."""
+    if x.is_cuda and x.dtype == BF and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096:
+        return _NormFn.apply(x, w, eps, rms)
+    xf = x.float()
+    if rms:
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        if w is not None:
+            y = y * w.float()
+    else:
+        y = F.layer_norm(xf, (x.shape[-1],), None if w is None else w.float(), None, eps)
+    return y.to(x.dtype)
+
+
+class _EmbedNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table, w, eps, rms):
+        ids32 = ids.to(torch.int32).contiguous()
+        y, mean, rstd = K.norm_fwd(table, w, eps, rms=rms, ids=ids32)
+        ctx.save_for_backward(ids32, table, w, mean, rstd)
+        ctx.rms = rms
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ids32, table, w, mean, rstd = ctx.saved_tensors
+        dt = table.main_grad if _has_main_grad(table) else torch.zeros(table.shape, dtype=torch.float32,
+                                                                      device=table.device)
+        dw = w.main_grad if _has_main_grad(w) else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        K.norm_bwd(dy, table, w, mean, rstd, rms=ctx.rms, ids=ids32, dtable=dt, dw=dw)
+        return (None, None if _has_main_grad(table) else dt.to(table.dtype),
+                None if _has_main_grad(w) else dw.to(w.dtype), None, None)
+
+
+def embed_norm(ids, table, w, eps: float = 1e-5, rms: bool = False):
+    """norm(table[ids]) for flat ids (reference: modeling.py:222-223)."""
+    if table.is_cuda and table.dtype == BF and table.shape[1] % 8 == 0 and table.shape[1] <= 4096:
+        return _EmbedNormFn.apply(ids, table, w, eps, rms)
+    return norm(F.embedding(ids.long(), table), w, eps, rms)
+
+
+# ------------------------------------------------------------------------------------- rope
+def rope_tables(max_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin [max_pos, head_dim/2] fp32 (the reference table is these halves repeated twice,
+    modeling.py:241-261)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    fr = torch.outer(torch.arange(max_pos, dtype=torch.float32, device=device), inv)
+    return fr.cos().contiguous(), fr.sin().contiguous()
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, pos, cos, sin, H, D):
+        ctx.save_for_backward(pos, cos, sin)
+        ctx.hd = (H, D)
+        K.rope_(qkv, pos, cos, sin, H, D)
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, d):
+        pos, cos, sin = ctx.saved_tensors
+        d = d.contiguous()
+        K.rope_(d, pos, cos, sin, *ctx.hd, backward=True)
+        return d, None, None, None, None, None
+
+
+def rope_qkv(qkv, pos, cos, sin, H: int, D: int):
+    """Rotates the q and k parts of qkv [T, 3*H*D] (rotate-half convention, fp32 math)."""
+    if qkv.is_cuda and qkv.dtype == BF and D % 16 == 0:
+        return _RopeFn.apply(qkv, pos, cos, sin, H, D)
+    T = qkv.shape[0]
+    x = qkv.view(T, 3, H, D)
+    c = torch.cat((cos, cos), -1)[pos.long()][:, None, :]
+    s = torch.cat((sin, sin), -1)[pos.long()][:, None, :]
+
+    def rot(t):
+        tf = t.float()
+        t1, t2 = tf.chunk(2, dim=-1)
+        return (tf * c + torch.cat((-t2, t1), -1) * s).to(t.dtype)
+
+    return torch.stack((rot(x[:, 0]), rot(x[:, 1]), x[:, 2]), dim=1).reshape(T, 3 * H * D)
+
+
+# ------------------------------------------------------------------------------------- attention
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, seq_start, seq_end, H, D, window, scale):
+        out, lse = K.fa_fwd(qkv, seq_start, seq_end, H, D, window, scale)
+        ctx.save_for_backward(qkv, out, lse, seq_start, seq_end)
+        ctx.cfg = (H, D, window, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, ss, se = ctx.saved_tensors
+        H, D, window, scale = ctx.cfg
+        dqkv = K.fa_bwd(qkv, out, dout.contiguous(), lse, ss, se, H, D, window, scale)
+        return dqkv, None, None, None, None, None, None
+
+
+def seq_bounds(cu_seqlens: torch.Tensor, T: int):
+    """Per-token [start, end) of the sequence each flat token belongs to."""
+    if cu_seqlens.is_cuda:
+        return K.seq_bounds(cu_seqlens.to(torch.int32), T)
+    cu = cu_seqlens.long()
+    t = torch.arange(T)
+    idx = torch.searchsorted(cu, t, right=True) - 1
+    idx = idx.clamp(0, len(cu) - 2)
+    a, b = cu[idx], cu[idx + 1]
+    bad = (t < a) | (t >= b)
+    a = torch.where(bad, t, a)
+    b = torch.where(bad, t + 1, b)
+    return a.to(torch.int32), b.to(torch.int32)
+
+
+def attention_varlen(qkv, seq_start, seq_end, H: int, D: int, window: int, scale: float):
+    """Non-causal attention inside each packed sequence; window >= 0 limits |q - k| <= window."""
+    if qkv.is_cuda and qkv.dtype == BF and D == 64:
+        return _AttnFn.apply(qkv, seq_start, seq_end, H, D, window, scale)
+    T = qkv.shape[0]
+    q, k, v = qkv.view(T, 3, H, D).unbind(1)
+    pos = torch.arange(T, device=qkv.device)
+    mask = (pos[None, :] >= seq_start.long()[:, None]) & (pos[None, :] < seq_end.long()[:, None])
+    if window >= 0:
+        mask &= (pos[:, None] - pos[None, :]).abs() <= window
+    s = torch.einsum("thd,shd->hts", q.float(), k.float()) * scale
+    s = s.masked_fill(~mask[None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("hts,shd->thd", p, v.float()).reshape(T, H * D).to(qkv.dtype)
+
+
+# ------------------------------------------------------------------------------------- gather
+class _GatherFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, idx):
+        ctx.save_for_backward(idx)
+        ctx.rows = x.shape[0]
+        return K.gather_rows(x, idx)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        dx = torch.zeros((ctx.rows, dy.shape[1]), dtype=dy.dtype, device=dy.device)
+        K.scatter_rows_(dx, idx, dy.contiguous())
+        return dx, None
+
+
+def gather_rows(x, idx):
+    """x[idx] for unique row indices (int32)."""
+    if x.is_cuda and x.dtype == BF and x.shape[1] % 8 == 0:
+        return _GatherFn.apply(x.contiguous(), idx.to(torch.int32))
+    return x[idx.long()]
+
+
+# ------------------------------------------------------------------------------------- loss
+class _CEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, W, bias, labels, want_logits):
+        n_valid = (labels >= 0).sum().clamp(min=1).float()
+        inv = (1.0 / n_valid).reshape(1)
+        loss, dlogits, logits = K.ce_fwd(h, W, bias, labels, inv, want_logits)
+        ctx.save_for_backward(h, W, dlogits)
+        ctx.bias_ref = bias
+        ctx.w_ref = W
+        ctx.mark_non_differentiable(*([logits] if logits is not None else []))
+        if logits is None:
+            logits = torch.empty(0, device=h.device)
+        return loss.squeeze(0), logits
+
+    @staticmethod
+    def backward(ctx, dloss, _dlogits):
+        h, W, dlogits = ctx.saved_tensors
+        bias = ctx.bias_ref
+        V = W.shape[0]
+        dW = W.main_grad if _has_main_grad(W) else torch.zeros(W.shape, dtype=torch.float32, device=W.device)
+        db = None
+        if bias is not None:
+            db = bias.main_grad if _has_main_grad(bias) else torch.zeros(V, dtype=torch.float32, device=W.device)
+        gs = dloss.float().reshape(1).contiguous()
+        dh = K.ce_bwd(h, W, dlogits, gs, dW, db)
+        gW = None if _has_main_grad(W) else dW.to(W.dtype)
+        gb = None
+        if bias is not None:
+            gb = None if _has_main_grad(bias) else db.to(bias.dtype)
+        return dh, gW, gb, None, None
+
+
+def mlm_cross_entropy(h, W, bias, labels, want_logits: bool = False):
+    """mean_{labels != -100} CE(h W^T + bias, labels). Returns (loss, logits or None).
+
+    Fused kernel for vocabularies of at most 32 entries (decoder GEMM, log-sum-exp, loss and
+    dlogits in one pass; reference: modeling.py:659-664)."""
+    if h.is_cuda and h.dtype == BF and W.shape[0] <= 32 and h.shape[1] % 8 == 0 and h.shape[1] <= 4096:
+        loss, logits = _CEFn.apply(h.contiguous(), W, bias, labels.to(torch.int32).contiguous(), want_logits)
+        return loss, (logits if want_logits else None)
+    logits = F.linear(h, W, bias)
+    loss = F.cross_entropy(logits.float(), labels.long(), ignore_index=-100)
+    return loss, (logits if want_logits else None)
+
+
+class _MSEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, s, t, valid):
+        v32 = None if valid is None else valid.to(torch.int32).contiguous()
+        n = (v32.sum() if v32 is not None else torch.tensor(s.shape[0], device=s.device)).clamp(min=1).float()
+        inv = (1.0 / n).reshape(1)
+        loss, ds = K.masked_mse(s, t, v32, inv, want_grad=True)
+        ctx.save_for_backward(ds)
+        return loss.squeeze(0)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (ds,) = ctx.saved_tensors
+        return ds * dloss.to(ds.dtype), None, None
+
+
+def masked_mse(student, teacher, valid=None):
+    """sum over features, mean over valid tokens of (student - teacher)^2
+    (reference: src/nanoplm/distillation/trainer.py:30-40). Inputs are [T, C]."""
+    if student.is_cuda and student.dtype == BF and student.shape[1] % 8 == 0:
+        return _MSEFn.apply(student.contiguous(), teacher.to(BF).contiguous(), valid)
+    d = (student.float() - teacher.float()) ** 2
+    if valid is not None:
+        m = valid.to(d.dtype)[:, None]
+        return (d * m).sum() / m.sum().clamp(min=1)
+    return d.sum() / max(1, student.shape[0])
