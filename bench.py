@@ -1,0 +1,376 @@
+"""Headline benchmark: MLM pretraining tokens/sec of the default 1024x16 encoder (bf16, sequence-
+packed varlen batches of 65 536 flat tokens per GPU per micro-batch, 2^20 flat tokens per optimizer
+step over all GPUs, AdamW + gradient clipping), on synthetic protein data with random-init weights.
+
+    python bench.py --gpus N --steps K --warmup W [--impl own|reference]
+
+N > 1 is launched as `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...`.
+Rank 0 prints ONE JSON line. `value` = real (non-padding) tokens per second over all GPUs for K
+optimizer steps, timed on the device with CUDA events between barrier + synchronize pairs, maximum
+over ranks. `e2e` is the same metric through `nanoplm_b200.runtime.pretrain.TrainStep` with every
+micro-batch copied from pinned host memory and the loss read back every step.
+
+`--impl reference` runs the unmodified reference package installed under baseline/_ref through its
+own `run_pure_pretraining` (FSDP2 / torch.compile / flash-attn path) on the same synthetic data and
+batch geometry; the only instrumentation is a wrapper around `torch.optim.AdamW.step` that records
+CUDA events at the boundaries of the timed steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+MODEL = dict(hidden_size=1024, intermediate_size=2048, num_hidden_layers=16, num_attention_heads=16,
+             vocab_size=32, max_position_embeddings=1024)
+MAX_SEQ_LEN = 512            # tokens per sequence including </s>; lengths uniform in [20, 512]
+MIN_SEQ_LEN = 20
+TARGET_ROWS = 128            # 128 rows x 512 = 65 536 flat tokens per micro-batch per GPU
+SEQS_PER_MICRO = 208         # mean 55.3 K real tokens; 4.5 sigma below the 128-row capacity
+MICRO_PER_STEP = 16          # 16 x 65 536 = 2^20 flat tokens per optimizer step (all GPUs together)
+MLM_PROB = 0.15
+BASELINE_VALUE = None        # the reference publishes no throughput number
+
+
+# ----------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.samples, self._stop, self._t = gpu_index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._t is not None:
+            self._t.join(timeout=6)
+        sm, mx, reasons = [], 0.0, set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------- data
+def make_sequences(n: int, seed: int):
+    """uint8 token arrays (residues + </s>), total length uniform in [MIN_SEQ_LEN, MAX_SEQ_LEN]."""
+    from nanoplm_b200.data.synthetic import synthetic_token_sequences
+    return synthetic_token_sequences(n, MIN_SEQ_LEN - 1, MAX_SEQ_LEN - 1, seed)
+
+
+def write_shard_dataset(out_dir: Path, n_train: int, n_val: int, seed: int) -> int:
+    """Writes the dataset in the shard + manifest format both frameworks read; returns the number of
+    real training tokens."""
+    import numpy as np
+    from nanoplm_b200.data.manifest import PretrainManifest, write_manifest
+    total = 0
+    for split, n, s in (("train", n_train, seed), ("val", n_val, seed + 1)):
+        d = out_dir / split
+        d.mkdir(parents=True, exist_ok=True)
+        seqs = make_sequences(n, s)
+        if split == "train":
+            total = int(sum(len(x) for x in seqs))
+        np.concatenate(seqs).astype(np.uint8).tofile(d / "shard_0000.bin")
+        np.save(d / "shard_0000.idx.npy", np.asarray([len(x) for x in seqs], dtype=np.int32))
+    write_manifest(out_dir, PretrainManifest(
+        pipeline_mode="pretrain", seqs_num=n_train + n_val, min_seq_len=MIN_SEQ_LEN, max_seq_len=MAX_SEQ_LEN,
+        val_ratio=n_val / (n_train + n_val), train_dir="train", val_dir="val", train_sequences=n_train,
+        val_sequences=n_val, sharded=True, samples_per_shard=max(n_train, n_val)))
+    return total
+
+
+def config_block(n_gpus: int, accum: int) -> dict:
+    return {"model": "nanoPLM default encoder: hidden 1024, intermediate 2048, 16 layers, 16 heads, "
+                     "vocab 32, SwiGLU, RoPE, global/local(+-64) attention, 168.9 M parameters",
+            "global_batch": MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN, "seq_len": MAX_SEQ_LEN,
+            "micro_batch_flat_tokens": TARGET_ROWS * MAX_SEQ_LEN, "sequences_per_micro_batch": SEQS_PER_MICRO,
+            "grad_accum": accum, "parallelism": f"dp{n_gpus}" + ("-sharded-optimizer" if n_gpus > 1 else ""),
+            "optimizer": "adamw lr 1e-3, clip 1.0", "mlm_probability": MLM_PROB,
+            "tokens_counted": "real (non-padding) tokens; the flat batch also holds the padding tail",
+            "l2_policy": "inputs larger than L2: every layer streams >= 128 MB of activations per micro-batch"}
+
+
+# ----------------------------------------------------------------------------------- own arm
+def run_own(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.collators import PackingCollator
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.ops import _lib
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime.pretrain import TrainStep, init_distributed, move_batch, set_seed
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    device, rank, world, local_rank = init_distributed(True)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}; launch with torch.distributed.run")
+    if MICRO_PER_STEP % world:
+        raise SystemExit("gpus must divide 16")
+    accum = MICRO_PER_STEP // world
+    K, W = args.steps, args.warmup
+    set_seed(42)
+    tok = ProtTokenizer()
+    model = ProtEncoderMLM(ModelConfig(**MODEL), tok)
+    engine = ShardedEngine(model, AdamWHyper(lr=1e-3, max_grad_norm=1.0), device,
+                           compute_dtype=torch.bfloat16, fused_comm=not args.no_fused_comm)
+    model.train()
+    total_steps = W + 2 * K
+    sched = WarmupLinearSchedule(1e-3, max(1, total_steps // 20), total_steps * 50)
+    stepper = TrainStep(model, engine, sched, device)
+
+    # every rank packs its own micro-batches (pinned host memory)
+    n_micro = (W + K) * accum
+    seqs = make_sequences(n_micro * SEQS_PER_MICRO, 1234 + rank)
+    coll = PackingCollator(tok, MAX_SEQ_LEN, MLM_PROB, target_rows=TARGET_ROWS, batch_size=SEQS_PER_MICRO,
+                           seed=99 + rank)
+    host, real_tokens = [], []
+    for i in range(n_micro):
+        ex = [{"input_ids": torch.from_numpy(s)} for s in seqs[i * SEQS_PER_MICRO:(i + 1) * SEQS_PER_MICRO]]
+        b = coll(ex)
+        real_tokens.append(int(b.pop("num_real_tokens")))
+        b.pop("labels")            # masked_idx / masked_labels carry the same information
+        host.append({k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in b.items()})
+    steps_host = [host[s * accum:(s + 1) * accum] for s in range(W + K)]
+    steps_tok = [sum(real_tokens[s * accum:(s + 1) * accum]) for s in range(W + K)]
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for s in range(W):
+        stepper.step_from_host(steps_host[s])
+    timed_host = steps_host[W:]
+    timed_dev = [[move_batch(b, device) for b in st] for st in timed_host]
+    tokens_timed = sum(steps_tok[W:])
+    tok_t = torch.tensor([float(tokens_timed)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(tok_t)
+    global_tokens = float(tok_t.item())
+
+    # ---- device-timed region ------------------------------------------------------------
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sync_all()
+    if sampler:
+        sampler.start()
+    launches0 = _lib.launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for st in timed_dev:
+        stepper.step_on_device(st)
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1)
+    launches = _lib.launches() - launches0
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end-to-end region (H2D every micro-batch, loss read back every step) -----------------
+    stepper.h2d_bytes = stepper.d2h_bytes = 0
+    sync_all()
+    t0 = time.perf_counter()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    last_loss = None
+    for st in timed_host:
+        last_loss = stepper.step_from_host(st)
+    g1.record()
+    sync_all()
+    e2e_ms = max(g0.elapsed_time(g1), 1e3 * (time.perf_counter() - t0))
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    _lib.check_status()
+    value = global_tokens / (ms / 1e3)
+    res = {"metric": "mlm_pretrain_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+           "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+           "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
+           "data": "synthetic (seeded amino-acid sequences, random-init weights)", "impl": "own",
+           "config": config_block(world, accum), "clocks": clocks,
+           "e2e": {"value": global_tokens / (e2e_ms / 1e3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": stepper.h2d_bytes // K, "d2h_bytes_per_step": stepper.d2h_bytes // K,
+                   "ms_per_step": e2e_ms / K},
+           "gpu_launches": launches, "final_loss": last_loss,
+           "raw_tokens_per_sec": K * MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN / (ms / 1e3),
+           "fused_comm": engine.fused is not None, "loaded_libs": [Path(p).name for p in _lib.loaded_libraries()]}
+    if world > 1:
+        dist.destroy_process_group()
+    return res if rank == 0 else {}
+
+
+# ----------------------------------------------------------------------------------- reference arm
+def _stub_missing_modules():
+    """Placeholders for third-party packages the reference imports at module level but does not use
+    on the pretraining path (they are absent from this image)."""
+    import importlib
+    import types
+    for name, attrs in (("IPython", {"get_ipython": lambda: None}), ("h5py", {"File": object}),
+                        ("Bio", {}), ("Bio.SeqIO", {})):
+        try:
+            importlib.import_module(name)
+        except Exception:
+            m = types.ModuleType(name)
+            for k, v in attrs.items():
+                setattr(m, k, v)
+            sys.modules[name] = m
+    if "Bio" in sys.modules and "Bio.SeqIO" in sys.modules:
+        setattr(sys.modules["Bio"], "SeqIO", sys.modules["Bio.SeqIO"])
+
+
+def run_reference(args) -> dict:
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "nanoplm").exists():
+        return {"impl": "reference", "unavailable": "baseline/_ref/nanoplm not installed on this machine"}
+    import torch
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+    os.environ["WANDB_MODE"] = "disabled"
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        return {"impl": "reference", "unavailable": f"--gpus {args.gpus} but WORLD_SIZE is {world}"}
+    accum = MICRO_PER_STEP // world
+    K, W = args.steps, args.warmup
+    work = Path(tempfile.mkdtemp(prefix=f"nplm_ref_r{rank}_"))
+    os.chdir(work)                      # the reference opens output/logs/pipeline.log in the cwd on import
+    sys.path.insert(0, str(ref_dir))
+    _stub_missing_modules()
+    try:
+        import torch.distributed as dist
+        import nanoplm.pretraining.pure_pipeline as pp
+        from nanoplm.pretraining.config import PretrainingConfig, PureTorchConfig
+        from nanoplm.pretraining.models.modern_bert.model import ProtModernBertMLMConfig
+        from nanoplm.pretraining.models.modern_bert.pure_model import PureProtModernBertMLM
+    except Exception as exc:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"[:300]}
+
+    n_train = (W + K) * accum * SEQS_PER_MICRO * world
+    total_real = write_shard_dataset(work / "data", n_train, SEQS_PER_MICRO * world, seed=1234)
+    cfg = PretrainingConfig(
+        dataset_dir=str(work / "data"), ckp_dir=str(work / "ckpt"), micro_batch_size=SEQS_PER_MICRO,
+        num_epochs=1, warmup_ratio=0.05, optimizer="adamw", adam_learning_rate=1e-3,
+        global_batch_size=MICRO_PER_STEP * SEQS_PER_MICRO * MAX_SEQ_LEN, bf16=True, tf32=True,
+        mlm_probability=MLM_PROB, logging_steps=1, eval_steps=10 ** 9, save_steps=10 ** 9, seed=42,
+        num_workers="auto", prefetch_factor=2, multi_gpu=world > 1, world_size=world,
+        project_name="bench")
+    pt = PureTorchConfig(use_compile=True, use_packing=True, target_packed_rows=TARGET_ROWS)
+    torch.manual_seed(42)
+    model = PureProtModernBertMLM(ProtModernBertMLMConfig(
+        hidden_size=MODEL["hidden_size"], intermediate_size=MODEL["intermediate_size"],
+        num_hidden_layers=MODEL["num_hidden_layers"], num_attention_heads=MODEL["num_attention_heads"],
+        vocab_size=32, max_position_embeddings=MODEL["max_position_embeddings"]))
+
+    state = {"n": 0, "ms": None, "clocks": None}
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    orig_step = torch.optim.AdamW.step
+
+    def sync_all():
+        if world > 1 and dist.is_initialized():
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_step(self, *a, **kw):
+        out = orig_step(self, *a, **kw)
+        state["n"] += 1
+        if state["n"] == W:
+            sync_all()
+            if sampler:
+                sampler.start()
+            ev0.record()
+        elif state["n"] == W + K:
+            ev1.record()
+            sync_all()
+            state["ms"] = ev0.elapsed_time(ev1)
+            if sampler:
+                state["clocks"] = sampler.stop()
+        return out
+
+    torch.optim.AdamW.step = timed_step
+    # the final evaluation / checkpoint of the reference run after the timed steps are not needed
+    try:
+        pp.run_pure_pretraining(model, cfg, pt, None)
+    except Exception as exc:  # noqa: BLE001
+        if state["ms"] is None:
+            return {"impl": "reference", "unavailable": f"reference run failed: {type(exc).__name__}: {exc}"[:300]}
+    finally:
+        torch.optim.AdamW.step = orig_step
+    if state["ms"] is None:
+        return {"impl": "reference", "unavailable": f"reference finished after {state['n']} optimizer steps, "
+                                                    f"expected {W + K}"}
+    ms = state["ms"]
+    if world > 1 and dist.is_initialized():
+        t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    tokens = total_real * K / (W + K)      # one epoch consumes every sequence once; K of W+K steps are timed
+    value = tokens / (ms / 1e3)
+    res = {"metric": "mlm_pretrain_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+           "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+           "vs_baseline": None, "dtype": "bf16", "impl": "reference",
+           "data": "synthetic (seeded amino-acid sequences, random-init weights)",
+           "config": config_block(world, accum), "clocks": state["clocks"],
+           "e2e": {"value": value, "unit": "tokens/s", "note": "the reference path already includes its "
+                   "DataLoader, host->device copies and per-micro-step loss.item() reads"},
+           "raw_tokens_per_sec": K * MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN / (ms / 1e3)}
+    return res if rank == 0 else {}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("own", "reference"), default="own")
+    ap.add_argument("--no-fused-comm", action="store_true", help="use NCCL collectives in the optimizer step")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    res = run_reference(args) if args.impl == "reference" else run_own(args)
+    if res:
+        sys.stdout.flush()
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,7 +41,9 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B), written swizzled, read by TMA stores
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
 struct GemmArgs {
@@ -54,21 +56,47 @@ struct GemmArgs {
   int* status;
 };
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
+// Writes 32 rows x 64 bf16 columns held by one warp (lane = row, packed[0..31] = the 64 values of
+// that row) through a swizzled shared-memory buffer with one TMA store. Two buffers per warp
+// alternate; a buffer is reused once the store issued two calls earlier has read it. Rows and
+// columns beyond the tensor are clipped by the TMA unit.
+__device__ __forceinline__ void stage_store_bf16(uint8_t* stage, int& toggle, const CUtensorMap* tm,
+                                                 const uint32_t (&packed)[32], int x, int y, int lane) {
+  if (lane == 0) tma_store_wait_read<1>();
+  __syncwarp();
+  uint8_t* buf = stage + toggle * 4096;
+  toggle ^= 1;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tm, buf, x, y);
+    tma_store_commit();
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI, bool TMA_EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  const GemmArgs args) {
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint8_t* epi_stage = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES + S::EPI_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tfull_bar = bars + 2 * STAGES;
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* res_bar = bars + 2 * STAGES + 4;  // [4 warps][2 buffers], residual tiles (EPI_ADD)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -94,6 +122,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 4);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(&res_bar[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -101,6 +130,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if constexpr (TMA_EPI) {
+      tma_prefetch_desc(&tmC);
+      tma_prefetch_desc(&tmR);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 2 * BN);
@@ -218,6 +251,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quarter = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int stage_toggle = 0;       // which of this warp's two staging buffers is next
+    uint32_t res_phase = 0;     // parity bits of this warp's two residual barriers
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const int split = w % splits;
       const int tile = w / splits;
@@ -236,7 +271,149 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool row_ok = row < M;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 
-      if constexpr (EPI == EPI_SWIGLU) {
+      if constexpr (TMA_EPI) {
+        // ---- shared-memory staged epilogue, 64 output columns per step, one TMA store each
+        uint8_t* stage = epi_stage + quarter * 8192;
+        const int y0 = m0 + quarter * 32;
+        const bool rows_in = y0 < M;
+        if constexpr (EPI == EPI_SWIGLU) {
+          constexpr int NCH = BN / 2 / 64;
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            uint32_t pv[32], pg[32], po[32];
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              uint32_t v[32], g[32];
+              tmem_ld32(taddr + c * 64 + hlf * 32, v);
+              tmem_ld32(taddr + BN / 2 + c * 64 + hlf * 32, g);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const uint32_t a = pack_bf16x2(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+                const uint32_t b = pack_bf16x2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1]));
+                const float2 vr = unpack_bf16x2(a);
+                const float2 gr = unpack_bf16x2(b);
+                pv[hlf * 16 + e] = a;
+                pg[hlf * 16 + e] = b;
+                po[hlf * 16 + e] = pack_bf16x2(gr.x / (1.0f + __expf(-gr.x)) * vr.x,
+                                               gr.y / (1.0f + __expf(-gr.y)) * vr.y);
+              }
+            }
+            if (c == NCH - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+            }
+            const int x = n0 + c * 64;
+            if (rows_in && x < n_extent) {
+              stage_store_bf16(stage, stage_toggle, &tmC, po, x, y0, lane);
+              if (args.R != nullptr) {
+                stage_store_bf16(stage, stage_toggle, &tmR, pv, x, y0, lane);
+                stage_store_bf16(stage, stage_toggle, &tmR, pg, args.swiglu_half + x, y0, lane);
+              }
+            }
+          }
+        } else {
+          constexpr int NCH = BN / 64;
+          if constexpr (EPI == EPI_ADD) {
+            // residual tile of chunk 0 (issued before the accumulator wait would be even better;
+            // the tile is already in L2 in the encoder, where the residual is the block input)
+            if (lane == 0 && rows_in && n0 < N) {
+              tma_store_wait_read<0>();
+              mbar_arrive_expect_tx(&res_bar[quarter * 2 + stage_toggle], 4096);
+              tma_load_2d(stage + stage_toggle * 4096, &tmR, &res_bar[quarter * 2 + stage_toggle], n0, y0);
+            }
+            __syncwarp();
+          }
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            uint32_t packed[32];
+            float f[64];
+            {
+              uint32_t r0[32], r1[32];
+              tmem_ld32(taddr + c * 64, r0);
+              tmem_ld32(taddr + c * 64 + 32, r1);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                f[e] = __uint_as_float(r0[e]);
+                f[32 + e] = __uint_as_float(r1[e]);
+              }
+            }
+            if (c == NCH - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+            }
+            const int x = n0 + c * 64;
+            const bool active = rows_in && x < N;
+            if constexpr (EPI == EPI_ADD) {
+              const int buf = stage_toggle;
+              // prefetch the residual of the next chunk into the other buffer
+              if (lane == 0 && rows_in && c + 1 < NCH && x + 64 < N) {
+                tma_store_wait_read<0>();
+                mbar_arrive_expect_tx(&res_bar[quarter * 2 + (buf ^ 1)], 4096);
+                tma_load_2d(stage + (buf ^ 1) * 4096, &tmR, &res_bar[quarter * 2 + (buf ^ 1)], x + 64, y0);
+              }
+              if (active) {
+                const bool got = mbar_wait(&res_bar[quarter * 2 + buf], (res_phase >> buf) & 1u);
+                res_phase ^= (1u << buf);
+                if (!got) {
+                  if (lane == 0) atomicExch(args.status, ST_TIMEOUT_MISC);
+                } else {
+                  uint8_t* rb = stage + buf * 4096;
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const uint4 rv = *reinterpret_cast<const uint4*>(rb + lane * 128 + ((j ^ (lane & 7)) << 4));
+                    const uint32_t* rr = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 t = unpack_bf16x2(rr[e]);
+                      f[j * 8 + 2 * e] += t.x;
+                      f[j * 8 + 2 * e + 1] += t.y;
+                    }
+                  }
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) packed[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
+                // in-place: the buffer that held the residual now holds the result
+                __syncwarp();
+                uint8_t* ob = stage + buf * 4096;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  *reinterpret_cast<uint4*>(ob + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                      make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_2d(&tmC, ob, x, y0);
+                  tma_store_commit();
+                }
+                stage_toggle ^= 1;
+              }
+            } else if constexpr (EPI == EPI_GELU) {
+              if (active) {
+                uint32_t pre[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  pre[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
+                  const float2 t = unpack_bf16x2(pre[e]);
+                  packed[e] = pack_bf16x2(gelu_erf(t.x), gelu_erf(t.y));
+                }
+                stage_store_bf16(stage, stage_toggle, &tmC, packed, x, y0, lane);
+                if (args.R != nullptr) stage_store_bf16(stage, stage_toggle, &tmR, pre, x, y0, lane);
+              }
+            } else {
+              if (active) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) packed[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
+                stage_store_bf16(stage, stage_toggle, &tmC, packed, x, y0, lane);
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_SWIGLU) {
         __nv_bfloat16* Cb = reinterpret_cast<__nv_bfloat16*>(args.C);
         __nv_bfloat16* Pb = const_cast<__nv_bfloat16*>(args.R);
 #pragma unroll 1
@@ -361,6 +538,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acc_phase ^= 1;
       }
     }
+    if constexpr (TMA_EPI) {
+      if (lane == 0) tma_store_wait<0>();
+      __syncwarp();
+    }
   }
 
   // ---------------------------------------------------------------- teardown
@@ -422,11 +603,17 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
-                  int max_ctas, cudaStream_t stream) {
+struct GemmMaps {
+  CUtensorMap A, B, C, R;
+  bool tma_epi;
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI, bool TMA_EPI>
+static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
+  const CUtensorMap& tmA = maps.A;
+  const CUtensorMap& tmB = maps.B;
   using S = GemmSmem<BN>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, TMA_EPI>;
   static bool configured = false;
   if (!configured) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
@@ -440,8 +627,16 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs
   int grid = total < num_sms() ? total : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, args);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, maps.C, maps.R, args);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch(const GemmMaps& maps, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
+  if constexpr (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_GELU || EPI == EPI_SWIGLU) {
+    if (maps.tma_epi) return launch_impl<BN, A_MN, B_MN, EPI, true>(maps, args, max_ctas, stream);
+  }
+  return launch_impl<BN, A_MN, B_MN, EPI, false>(maps, args, max_ctas, stream);
 }
 
 }  // namespace nplm
@@ -454,8 +649,8 @@ using namespace nplm;
 // some SMs.
 extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
                               int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn,
-                              int epi, int splits, int bn, int max_ctas, int* status,
-                              cudaStream_t stream) {
+                              int epi, int splits, int bn, int max_ctas, int direct_epilogue,
+                              int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))
@@ -471,7 +666,9 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
   if (splits > num_kb) splits = num_kb;
   if (epi != EPI_ATOMIC_F32) splits = 1;
 
-  CUtensorMap tmA, tmB;
+  GemmMaps maps;
+  CUtensorMap& tmA = maps.A;
+  CUtensorMap& tmB = maps.B;
   int rc;
   if (!a_mn)
     rc = make_map_2d(&tmA, A, K, M, lda, BK, BM, 2);
@@ -485,6 +682,22 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
   else
     rc = make_map_2d(&tmB, B, N, K, ldb, 64, BK, 2);
   if (rc) return rc;
+  // staged (TMA store) epilogue for the bf16 outputs; maps C / R describe [32 rows][64 cols] boxes
+  maps.tma_epi = !direct_epilogue &&
+                 (epi == EPI_STORE || epi == EPI_ADD || epi == EPI_GELU || epi == EPI_SWIGLU) &&
+                 !(epi == EPI_ADD && (R == nullptr || (reinterpret_cast<uintptr_t>(R) & 15) || (ldr % 8)));
+  maps.C = tmA;
+  maps.R = tmA;
+  if (maps.tma_epi) {
+    const int out_cols = epi == EPI_SWIGLU ? N / 2 : N;
+    rc = make_map_2d(&maps.C, C, out_cols, M, ldc, 64, 32, 2);
+    if (rc) return rc;
+    if (R != nullptr) {
+      if ((reinterpret_cast<uintptr_t>(R) & 15) || (ldr % 8)) return -3;
+      rc = make_map_2d(&maps.R, R, N, M, ldr, 64, 32, 2);
+      if (rc) return rc;
+    }
+  }
 
   GemmArgs args;
   args.C = C;
@@ -500,24 +713,24 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
 
 #define NPLM_DISPATCH_EPI(BN_, AMN_, BMN_)                                                   \
   switch (epi) {                                                                             \
-    case EPI_STORE: return launch<BN_, AMN_, BMN_, EPI_STORE>(tmA, tmB, args, max_ctas, stream); \
-    case EPI_ADD: return launch<BN_, AMN_, BMN_, EPI_ADD>(tmA, tmB, args, max_ctas, stream);     \
+    case EPI_STORE: return launch<BN_, AMN_, BMN_, EPI_STORE>(maps, args, max_ctas, stream); \
+    case EPI_ADD: return launch<BN_, AMN_, BMN_, EPI_ADD>(maps, args, max_ctas, stream);     \
     case EPI_ATOMIC_F32:                                                                     \
-      return launch<BN_, AMN_, BMN_, EPI_ATOMIC_F32>(tmA, tmB, args, max_ctas, stream);      \
+      return launch<BN_, AMN_, BMN_, EPI_ATOMIC_F32>(maps, args, max_ctas, stream);      \
     case EPI_STORE_F32:                                                                      \
-      return launch<BN_, AMN_, BMN_, EPI_STORE_F32>(tmA, tmB, args, max_ctas, stream);       \
+      return launch<BN_, AMN_, BMN_, EPI_STORE_F32>(maps, args, max_ctas, stream);       \
     default: break;                                                                          \
   }
 
   if (epi == EPI_GELU) {
     if (a_mn || b_mn) return -7;
-    if (bn == 256) return launch<256, false, false, EPI_GELU>(tmA, tmB, args, max_ctas, stream);
-    return launch<128, false, false, EPI_GELU>(tmA, tmB, args, max_ctas, stream);
+    if (bn == 256) return launch<256, false, false, EPI_GELU>(maps, args, max_ctas, stream);
+    return launch<128, false, false, EPI_GELU>(maps, args, max_ctas, stream);
   }
   if (epi == EPI_SWIGLU) {
     if (a_mn || b_mn) return -7;
-    if (bn == 256) return launch<256, false, false, EPI_SWIGLU>(tmA, tmB, args, max_ctas, stream);
-    return launch<128, false, false, EPI_SWIGLU>(tmA, tmB, args, max_ctas, stream);
+    if (bn == 256) return launch<256, false, false, EPI_SWIGLU>(maps, args, max_ctas, stream);
+    return launch<128, false, false, EPI_SWIGLU>(maps, args, max_ctas, stream);
   }
   if (bn == 256) {
     if (!a_mn && !b_mn) { NPLM_DISPATCH_EPI(256, false, false) }

@@ -34,13 +34,15 @@ def _rowmajor(t: torch.Tensor, name: str) -> int:
 # --------------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          epi: int = EPI_STORE, out: torch.Tensor | None = None, aux: torch.Tensor | None = None,
-         splits: int = 1, bn: int | None = None, max_ctas: int = 0) -> torch.Tensor:
+         splits: int = 1, bn: int | None = None, max_ctas: int = 0,
+         direct_epilogue: bool = False) -> torch.Tensor:
     """C[M,N] (+)= op(A) op(B)^T on tcgen05 tensor cores.
 
     a: [M,K] (a_mn=False) or [K,M] (a_mn=True); b: [N,K] (b_mn=False) or [K,N] (b_mn=True).
     epi: EPI_STORE / EPI_ADD (aux = residual) / EPI_ATOMIC_F32 (out fp32, accumulated in place) /
     EPI_GELU (aux = optional pre-activation output) / EPI_STORE_F32 / EPI_SWIGLU (out is N/2 wide,
-    aux = optional [M,N] pre-activation output).
+    aux = optional [M,N] pre-activation output). bf16 outputs leave through shared memory and
+    TMA stores; direct_epilogue=True selects per-thread global stores instead.
     """
     _chk(a, _BF16, "a")
     _chk(b, _BF16, "b")
@@ -78,18 +80,27 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     rc = lib("gemm_tcgen05").nplm_gemm_bf16(
         ptr(a), ptr(b), ptr(out), ptr(aux), c_int(M), c_int(N), c_int(K), c_int(lda), c_int(ldb),
         c_int(ldc), c_int(ldr), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi), c_int(splits),
-        c_int(bn), c_int(max_ctas), ptr(status_word(a.device)), stream_ptr())
+        c_int(bn), c_int(max_ctas), c_int(int(direct_epilogue)), ptr(status_word(a.device)),
+        stream_ptr())
     check_rc(rc, "gemm_bf16")
     count_launch()
     return out
 
 
-def wgrad_splits(n_out: int, k_in: int, tokens: int, bn: int = 256) -> int:
-    """Split-K factor that fills ~148 SMs for a weight-gradient GEMM [n_out, k_in] over `tokens`."""
+def wgrad_splits(n_out: int, k_in: int, tokens: int, bn: int = 256, sms: int = 148) -> int:
+    """Split-K factor for a weight-gradient GEMM [n_out, k_in] reduced over `tokens`: the smallest
+    factor (<= 8) whose work items fill the last wave of `sms` CTAs best."""
     tiles = ((n_out + 127) // 128) * ((k_in + bn - 1) // bn)
     kb = (tokens + 63) // 64
-    s = max(1, min(148 // max(1, tiles), kb // 8 if kb >= 8 else 1))
-    return max(1, s)
+    best, best_eff = 1, 0.0
+    for s in range(1, 9):
+        if s > 1 and kb // s < 16:
+            break
+        work = tiles * s
+        eff = work / (((work + sms - 1) // sms) * sms)
+        if eff > best_eff + 0.02:
+            best, best_eff = s, eff
+    return best
 
 
 # --------------------------------------------------------------------------- norms

@@ -1,0 +1,136 @@
+"""Checkpoints in the reference's layout (src/nanoplm/pretraining/pure_pipeline.py:235-331):
+
+    <run>/checkpoint-<step>/{pytorch_model.bin, optimizer.pt, scheduler.pt, rng_state.pth,
+                             training_state.json}
+
+`pytorch_model.bin` holds the full fp32 state dict under the reference's parameter names (tied
+decoder.weight included); `optimizer.pt` is a torch.optim.AdamW state dict with full tensors in the
+reference's parameter order. Loading accepts `_orig_mod.`-prefixed keys. Differences: the directory
+is written under a temporary name and renamed, so a crash never leaves a half-written checkpoint;
+optionally every rank also writes its own optimizer slice (`shard-<rank>.pt` + `index.json`) for a
+resume that needs no gather/scatter.
+"""
+from __future__ import annotations
+
+import json
+import os
+import random
+import shutil
+from pathlib import Path
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from nanoplm_b200.utils.logging import logger
+
+MODEL_FILE = "pytorch_model.bin"
+OPT_FILE = "optimizer.pt"
+SCHED_FILE = "scheduler.pt"
+RNG_FILE = "rng_state.pth"
+STATE_FILE = "training_state.json"
+
+
+def _barrier():
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+
+
+def save_checkpoint(engine, scheduler, global_step: int, epoch: int, output_dir: str,
+                    logging_steps: int, eval_steps: int, save_steps: int, is_main: bool = True,
+                    sharded: bool = False, extra_state: Optional[dict] = None) -> Path:
+    final = Path(output_dir) / f"checkpoint-{global_step}"
+    tmp = Path(output_dir) / f".tmp-checkpoint-{global_step}"
+    model_sd = engine.full_state_dict_model()       # collective
+    opt_sd = engine.optimizer_state_dict()          # collective
+    if is_main:
+        if tmp.exists():
+            shutil.rmtree(tmp)
+        tmp.mkdir(parents=True, exist_ok=True)
+    _barrier()
+    if sharded:
+        torch.save(engine.shard_state(), tmp / f"shard-{engine.rank}.pt")
+    if is_main:
+        torch.save(model_sd, tmp / MODEL_FILE)
+        torch.save(opt_sd, tmp / OPT_FILE)
+        torch.save(scheduler.state_dict(), tmp / SCHED_FILE)
+        torch.save({
+            "torch_rng": torch.random.get_rng_state(),
+            "cuda_rng": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else [],
+            "numpy_rng": np.random.get_state(),
+            "python_rng": random.getstate(),
+        }, tmp / RNG_FILE)
+        state = {"global_step": global_step, "epoch": epoch, "logging_steps": logging_steps,
+                 "eval_steps": eval_steps, "save_steps": save_steps}
+        if extra_state:
+            state.update(extra_state)
+        (tmp / STATE_FILE).write_text(json.dumps(state, indent=2), encoding="utf-8")
+        if sharded:
+            (tmp / "index.json").write_text(json.dumps(
+                {"world_size": engine.world, "total": engine.total, "shard": engine.shard,
+                 "files": [f"shard-{r}.pt" for r in range(engine.world)]}, indent=2), encoding="utf-8")
+    _barrier()
+    if is_main:
+        if final.exists():
+            shutil.rmtree(final)
+        os.replace(tmp, final)
+        logger.info(f"Checkpoint saved -> {final}")
+    _barrier()
+    return final
+
+
+def load_checkpoint(engine, scheduler, checkpoint_dir: str, restore_rng: bool = True) -> tuple[int, int]:
+    ckp = Path(checkpoint_dir)
+    if not ckp.exists():
+        raise FileNotFoundError(f"Checkpoint directory does not exist: {ckp}")
+    index = ckp / "index.json"
+    used_shards = False
+    if index.exists():
+        meta = json.loads(index.read_text())
+        mine = ckp / f"shard-{engine.rank}.pt"
+        if meta.get("world_size") == engine.world and meta.get("total") == engine.total and mine.exists():
+            engine.load_shard_state(torch.load(mine, map_location="cpu", weights_only=True))
+            used_shards = True
+    if not used_shards:
+        model_path = ckp / MODEL_FILE
+        if not model_path.exists():
+            raise FileNotFoundError(f"{MODEL_FILE} not found in {ckp}")
+        engine.load_model_state_dict(torch.load(model_path, map_location="cpu", weights_only=True))
+        opt_path = ckp / OPT_FILE
+        if opt_path.exists():
+            try:
+                engine.load_optimizer_state_dict(torch.load(opt_path, map_location="cpu", weights_only=True))
+            except Exception as exc:  # truncated / foreign optimizer file: keep the weights, restart moments
+                logger.warning(f"Could not load optimizer state ({exc}); optimizer moments start from zero.")
+    sched_path = ckp / SCHED_FILE
+    if sched_path.exists():
+        scheduler.load_state_dict(torch.load(sched_path, map_location="cpu", weights_only=False))
+    rng_path = ckp / RNG_FILE
+    if restore_rng and rng_path.exists():
+        rng = torch.load(rng_path, map_location="cpu", weights_only=False)
+        torch.random.set_rng_state(rng["torch_rng"])
+        if torch.cuda.is_available() and rng.get("cuda_rng"):
+            try:
+                torch.cuda.set_rng_state_all(rng["cuda_rng"])
+            except Exception:
+                pass
+        np.random.set_state(rng["numpy_rng"])
+        random.setstate(rng["python_rng"])
+    state_path = ckp / STATE_FILE
+    if state_path.exists():
+        st = json.loads(state_path.read_text(encoding="utf-8"))
+        return int(st.get("global_step", 0)), int(st.get("epoch", 0))
+    return 0, 0
+
+
+def latest_checkpoint(run_dir: str | Path) -> Optional[Path]:
+    best, best_step = None, -1
+    for d in Path(run_dir).glob("checkpoint-*"):
+        try:
+            s = int(d.name.split("-")[1])
+        except (IndexError, ValueError):
+            continue
+        if s > best_step and (d / STATE_FILE).exists():
+            best, best_step = d, s
+    return best

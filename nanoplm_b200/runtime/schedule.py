@@ -1,0 +1,103 @@
+"""Learning-rate schedules.
+
+`WarmupLinearSchedule` is the reference pretraining schedule (pure_pipeline.py:150-172): linear
+warm-up over `warmup_steps`, then linear decay to zero at `total_steps`; a warm-up value >= 1 is an
+absolute step count, a value < 1 a ratio (rounded up). `make_distill_schedule` covers the four
+schedules of the distillation pipeline (distillation/pipeline.py:396-446). State dicts carry
+`last_epoch` / `base_lrs` like torch's LambdaLR, so `scheduler.pt` files are interchangeable.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable
+
+
+def get_warmup_steps(total_steps: int, warmup_value: float) -> int:
+    if warmup_value >= 1:
+        return int(warmup_value)
+    return math.ceil(total_steps * warmup_value)
+
+
+def num_update_steps_per_epoch(loader_len: int, grad_accum: int) -> int:
+    if loader_len <= 0:
+        return 1
+    return max(1, math.ceil(loader_len / max(1, grad_accum)))
+
+
+class LambdaSchedule:
+    def __init__(self, base_lr: float, fn: Callable[[int], float]):
+        self.base_lrs = [float(base_lr)]
+        self.fn = fn
+        self.last_epoch = 0
+
+    def get_lr(self) -> float:
+        return self.base_lrs[0] * self.fn(self.last_epoch)
+
+    def get_last_lr(self) -> list[float]:
+        return [self.get_lr()]
+
+    def step(self) -> None:
+        self.last_epoch += 1
+
+    def state_dict(self) -> dict:
+        return {"base_lrs": list(self.base_lrs), "last_epoch": self.last_epoch,
+                "_step_count": self.last_epoch + 1, "_last_lr": self.get_last_lr(),
+                "lr_lambdas": [None]}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.last_epoch = int(sd.get("last_epoch", 0))
+        if sd.get("base_lrs"):
+            self.base_lrs = [float(sd["base_lrs"][0])]
+
+
+class WarmupLinearSchedule(LambdaSchedule):
+    def __init__(self, base_lr: float, warmup_steps: int, total_steps: int):
+        def fn(step: int) -> float:
+            if step < warmup_steps:
+                return step / max(1, warmup_steps)
+            return max(0.0, (total_steps - step) / max(1, total_steps - warmup_steps))
+        super().__init__(base_lr, fn)
+        self.warmup_steps, self.total_steps = warmup_steps, total_steps
+
+
+def make_distill_schedule(name: str, base_lr: float, warmup_steps: int, total_steps: int,
+                          **kwargs) -> LambdaSchedule:
+    name = name.lower()
+
+    def warm(step: int):
+        return step / max(1, warmup_steps) if step < warmup_steps else None
+
+    if name == "cosine":
+        cycles = float(kwargs.get("num_cycles", 0.5))
+
+        def fn(step):
+            w = warm(step)
+            if w is not None:
+                return w
+            prog = (step - warmup_steps) / max(1, total_steps - warmup_steps)
+            return max(0.0, 0.5 * (1.0 + math.cos(math.pi * cycles * 2.0 * prog)))
+    elif name == "linear":
+        def fn(step):
+            w = warm(step)
+            if w is not None:
+                return w
+            return max(0.0, (total_steps - step) / max(1, total_steps - warmup_steps))
+    elif name == "polynomial":
+        power = float(kwargs.get("power", 1.0))
+        lr_end = float(kwargs.get("lr_end", 1e-7))
+
+        def fn(step):
+            w = warm(step)
+            if w is not None:
+                return w
+            if step > total_steps:
+                return lr_end / base_lr
+            rem = 1 - (step - warmup_steps) / max(1, total_steps - warmup_steps)
+            return ((base_lr - lr_end) * rem ** power + lr_end) / base_lr
+    elif name == "constant":
+        def fn(step):
+            w = warm(step)
+            return 1.0 if w is None else w
+    else:
+        raise ValueError(f"Unknown lr_scheduler: {name}. Supported: cosine, linear, polynomial, constant")
+    return LambdaSchedule(base_lr, fn)

@@ -31,12 +31,13 @@ def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (384, 512, 320), (300, 264, 200),
                                    (1000, 1024, 1024), (4096, 3072, 1024)])
 @pytest.mark.parametrize("bn", [128, 256])
-def test_gemm_kk(M, N, K, bn, cuda_status):
+@pytest.mark.parametrize("direct", [False, True])
+def test_gemm_kk(M, N, K, bn, direct, cuda_status):
     k = _k()
     a, b = _randn(M, K), _randn(N, K)
-    c = k.gemm(a, b, bn=bn)
+    c = k.gemm(a, b, bn=bn, direct_epilogue=direct)
     ref = a.float() @ b.float().t()
-    _close(c, ref, what=f"gemm {M}x{N}x{K} bn{bn}")
+    _close(c, ref, what=f"gemm {M}x{N}x{K} bn{bn} direct={direct}")
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
@@ -52,25 +53,40 @@ def test_gemm_majors(a_mn, b_mn, M, N, K, cuda_status):
         _close(c, af @ bf, what=f"gemm majors a_mn={a_mn} b_mn={b_mn} {M}x{N}x{K} bn{bn}")
 
 
-def test_gemm_epilogues(cuda_status):
+@pytest.mark.parametrize("direct", [False, True])
+@pytest.mark.parametrize("M,N,K", [(512, 768, 256), (1000, 1200, 192), (77, 144, 64)])
+def test_gemm_epilogues(direct, M, N, K, cuda_status):
     k = _k()
-    M, N, K = 512, 768, 256
     a, b = _randn(M, K), _randn(N, K, scale=0.1)
     ref = a.float() @ b.float().t()
     res = _randn(M, N)
-    _close(k.gemm(a, b, epi=k.EPI_ADD, aux=res), ref + res.float(), what="epi add")
+    for bn in (128, 256):
+        _close(k.gemm(a, b, epi=k.EPI_ADD, aux=res, bn=bn, direct_epilogue=direct), ref + res.float(),
+               what=f"epi add bn{bn}")
+        pre = torch.zeros(M, N, dtype=BF, device="cuda")
+        out = k.gemm(a, b, epi=k.EPI_GELU, aux=pre, bn=bn, direct_epilogue=direct)
+        _close(pre, ref, what="gelu pre")
+        _close(out, F.gelu(pre.float()), what="gelu out")
+        # swiglu: b = [value rows | gate rows]
+        pre2 = torch.zeros(M, N, dtype=BF, device="cuda")
+        out2 = k.gemm(a, b, epi=k.EPI_SWIGLU, aux=pre2, bn=bn, direct_epilogue=direct)
+        _close(pre2, ref, what=f"swiglu pre bn{bn}")
+        v, g = pre2.float().chunk(2, dim=-1)
+        _close(out2, F.silu(g) * v, what=f"swiglu out bn{bn}")
+        assert out2.shape == (M, N // 2)
     _close(k.gemm(a, b, epi=k.EPI_STORE_F32), ref, what="epi f32")
-    pre = torch.empty(M, N, dtype=BF, device="cuda")
-    out = k.gemm(a, b, epi=k.EPI_GELU, aux=pre)
-    _close(pre, ref, what="gelu pre")
-    _close(out, F.gelu(pre.float()), what="gelu out")
-    # swiglu: b = [value rows | gate rows]
-    pre2 = torch.empty(M, N, dtype=BF, device="cuda")
-    out2 = k.gemm(a, b, epi=k.EPI_SWIGLU, aux=pre2)
-    _close(pre2, ref, what="swiglu pre")
-    v, g = pre2.float().chunk(2, dim=-1)
-    _close(out2, F.silu(g) * v, what="swiglu out")
-    assert out2.shape == (M, N // 2)
+
+
+def test_gemm_output_canaries(cuda_status):
+    """The staged epilogue must not write outside [M, N] of a larger allocation."""
+    k = _k()
+    M, N, K = 200, 136, 128
+    a, b = _randn(M, K), _randn(N, K)
+    big = torch.full((M + 64, N + 120), 7.0, dtype=BF, device="cuda")
+    out = big[:M, :N]
+    k.gemm(a, b, out=out)
+    _close(out, a.float() @ b.float().t(), what="canary result")
+    assert (big[M:, :] == 7).all() and (big[:, N:] == 7).all()
 
 
 @pytest.mark.parametrize("splits", [1, 3, 8])
