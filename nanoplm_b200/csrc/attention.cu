@@ -105,7 +105,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaFwdArgs args) {
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmQKV);
   }
-  if (warp == 0) {
+  if (warp == 1) {
+    __syncwarp();
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
@@ -292,8 +293,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaFwdArgs args) {
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 1) {
     tc_fence_after();
+    __syncwarp();
     tmem_dealloc(tmem_base, 256);
   }
 }
@@ -324,9 +326,10 @@ fa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __rest
       const float2 y = unpack_bf16x2(pb[q]);
       s += x.x * y.x + x.y * y.y;
     }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    const uint32_t gmask = 0xffu << (threadIdx.x & 24);  // the 8 lanes that share this (t, h)
+    s += __shfl_xor_sync(gmask, s, 1);
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 4);
     if (sub == 0) delta[static_cast<size_t>(h) * T + t] = s;
   }
 }
@@ -392,7 +395,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
   }
-  if (warp == 0) {
+  if (warp == 1) {
+    __syncwarp();
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -594,15 +598,22 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     __syncthreads();  // dQ columns and the P^T / dS^T buffers may be overwritten from here on
   }
 
-  if (alive && krow_ok) {
+  if (alive) {
+    // tcgen05.ld is warp-aligned: every lane of the warp executes it, rows past T only skip the
+    // global stores.
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    __nv_bfloat16* dk_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 1) * HD + h * FA_D + half * 32;
-    __nv_bfloat16* dv_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 2) * HD + h * FA_D + half * 32;
+    uint32_t rk[32], rv[32];
     if (n_q > 0) {
-      uint32_t rk[32], rv[32];
       tmem_ld32(tdK + lane_addr + half * 32, rk);
       tmem_ld32(tdV + lane_addr + half * 32, rv);
       tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) rk[e] = rv[e] = 0u;
+    }
+    if (krow_ok) {
+      __nv_bfloat16* dk_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 1) * HD + h * FA_D + half * 32;
+      __nv_bfloat16* dv_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 2) * HD + h * FA_D + half * 32;
 #pragma unroll
       for (int e = 0; e < 32; e += 8) {
         uint4 uk, uv;
@@ -617,19 +628,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
         *reinterpret_cast<uint4*>(dk_dst + e) = uk;
         *reinterpret_cast<uint4*>(dv_dst + e) = uv;
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 32; e += 8) {
-        *reinterpret_cast<uint4*>(dk_dst + e) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv_dst + e) = make_uint4(0, 0, 0, 0);
-      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 1) {
     tc_fence_after();
+    __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }
 }

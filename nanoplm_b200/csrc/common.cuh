@@ -77,14 +77,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false when the limit ran out. A short burst of blocking try_wait calls
+// covers the common case; after that the loop polls with the non-blocking test_wait and reads
+// the clock every few polls, so the bound holds whatever the hardware's try_wait time-out is.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
+#pragma unroll 1
+  for (int i = 0; i < 8; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+  while (!mbar_test_wait(bar, parity)) {
+    if ((++spins & 0xf) == 0) {
       if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+      __nanosleep(64);
     }
   }
   return true;

@@ -455,6 +455,11 @@ ce_bwd_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restri
       continue;
     }
     if (lane < V) atomicAdd(&sdb[lane], dl);
+    // broadcast every dlogit to every lane first: the shuffles need the whole warp, the channel
+    // loop below does not run on lanes whose channels lie beyond C
+    float dv[32];
+#pragma unroll
+    for (int v = 0; v < 32; ++v) dv[v] = __shfl_sync(0xffffffffu, dl, v);
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int i = c * 256 + lane * 8;
@@ -463,14 +468,17 @@ ce_bwd_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restri
         load8(h + static_cast<size_t>(row) * C + i, hv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = 0.f;
-        for (int v = 0; v < V; ++v) {
-          const float d = __shfl_sync(0xffffffffu, dl, v);
-          float wv[8];
-          load8(W + static_cast<size_t>(v) * C + i, wv);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            o[e] += d * wv[e];
-            atomicAdd(&sdW[v * C + i + e], d * hv[e]);
+        for (int v = 0; v < 32; ++v) {
+          if (v < V) {
+            const float d = dv[v];
+            float wv[8];
+            load8(W + static_cast<size_t>(v) * C + i, wv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              o[e] += d * wv[e];
+              atomicAdd(&sdW[v * C + i + e], d * hv[e]);
+            }
           }
         }
         store8(dh + static_cast<size_t>(row) * C + i, o);

@@ -23,6 +23,13 @@ from . import kernels as K
 BF = torch.bfloat16
 
 
+def _as_shape(y: torch.Tensor, shape) -> torch.Tensor:
+    """y reshaped to `shape`; returns y itself (not a view object) when the shape already matches, so
+    that a later in-place op on a custom Function's output stays legal for autograd."""
+    shape = tuple(shape)
+    return y if tuple(y.shape) == shape else y.view(shape)
+
+
 def _has_main_grad(p) -> bool:
     return getattr(p, "main_grad", None) is not None
 
@@ -81,8 +88,7 @@ class _LinearFn(torch.autograd.Function):
         ctx.has_res = residual is not None
         ctx.bias_ref = bias
         ctx.x_shape = x.shape
-        out_cols = y.shape[1]
-        return y.view(*x.shape[:-1], out_cols)
+        return _as_shape(y, (*x.shape[:-1], y.shape[1]))
 
     @staticmethod
     def backward(ctx, dy):
@@ -98,7 +104,7 @@ class _LinearFn(torch.autograd.Function):
             dpre = dy2
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = K.gemm(dpre, w, b_mn=True).view(ctx.x_shape)
+            dx = _as_shape(K.gemm(dpre, w, b_mn=True), ctx.x_shape)
         dw = _wgrad(dpre, x2, w) if ctx.needs_input_grad[1] else None
         db = None
         if ctx.has_bias and ctx.needs_input_grad[2]:
@@ -133,12 +139,12 @@ class _SwigluFn(torch.autograd.Function):
         p2 = pre.reshape(-1, pre.shape[-1]).contiguous()
         ctx.save_for_backward(p2)
         ctx.shape = pre.shape
-        return K.swiglu_fwd(p2).view(*pre.shape[:-1], pre.shape[-1] // 2)
+        return _as_shape(K.swiglu_fwd(p2), (*pre.shape[:-1], pre.shape[-1] // 2))
 
     @staticmethod
     def backward(ctx, dy):
         (p2,) = ctx.saved_tensors
-        return K.swiglu_bwd(p2, dy.reshape(-1, dy.shape[-1]).contiguous()).view(ctx.shape)
+        return _as_shape(K.swiglu_bwd(p2, dy.reshape(-1, dy.shape[-1]).contiguous()), ctx.shape)
 
 
 def swiglu(pre):
@@ -180,7 +186,7 @@ class _NormFn(torch.autograd.Function):
         ctx.save_for_backward(x2, w, mean, rstd)
         ctx.rms = rms
         ctx.shape = x.shape
-        return y.view(x.shape)
+        return _as_shape(y, x.shape)
 
     @staticmethod
     def backward(ctx, dy):
@@ -191,7 +197,7 @@ class _NormFn(torch.autograd.Function):
         dx = K.norm_bwd(dy, x2, w, mean, rstd, rms=ctx.rms, dw=dw)
         if dw is not None:
             dw = None if _has_main_grad(w) else dw.to(w.dtype)
-        return dx.view(ctx.shape), dw, None, None
+        return _as_shape(dx, ctx.shape), dw, None, None
 
 
 def norm(x, w, eps: float = 1e-5, rms: bool = False):

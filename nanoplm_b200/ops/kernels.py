@@ -89,11 +89,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 def wgrad_splits(n_out: int, k_in: int, tokens: int, bn: int = 256, sms: int = 148) -> int:
     """Split-K factor for a weight-gradient GEMM [n_out, k_in] reduced over `tokens`: the smallest
-    factor (<= 8) whose work items fill the last wave of `sms` CTAs best."""
+    factor (<= 4) whose work items fill the last wave of `sms` CTAs best."""
     tiles = ((n_out + 127) // 128) * ((k_in + bn - 1) // bn)
     kb = (tokens + 63) // 64
     best, best_eff = 1, 0.0
-    for s in range(1, 9):
+    for s in range(1, 5):
         if s > 1 and kb // s < 16:
             break
         work = tiles * s
