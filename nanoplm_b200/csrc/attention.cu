@@ -782,3 +782,51 @@ extern "C" int nplm_fa_bwd(const void* qkv, const void* out, const void* dout, c
   }
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------- no-allocation entry
+#include "attention_noalloc.h"
+
+// Scratch of the allocation-free entry point: [dq accumulator | per-row statistics]. File scope,
+// so it exists once per device that loads this library and lives until the process exits.
+static __device__ __align__(256) float g_noalloc_scratch[NPLM_NOALLOC_MAX_DQ_FLOATS + NPLM_NOALLOC_MAX_STAT_FLOATS];
+
+extern "C" const char* nplm_fa_bwd_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case NPLM_NOALLOC_TOO_LARGE:
+      return "problem too large for the built-in scratch: need T*H*D <= 4 Mi and T*H <= 64 Ki floats";
+    case NPLM_NOALLOC_SYMBOL_LOOKUP_FAILED:
+      return "cudaGetSymbolAddress failed for the built-in scratch array";
+    case -3: return "unsupported head dimension or misaligned pointer";
+    default: return code > 0 ? "CUDA runtime error (cudaError_t)" : "rejected arguments";
+  }
+}
+
+extern "C" int nplm_fa_bwd_noalloc(const void* qkv, const void* out, const void* dout, const float* lse,
+                                   void* dqkv, const int* seq_start, const int* seq_end, int T, int H,
+                                   int D, int window, float scale, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || D <= 0) return -3;
+  const size_t need_dq = static_cast<size_t>(T) * H * D;
+  const size_t need_stat = static_cast<size_t>(T) * H;
+  if (need_dq > NPLM_NOALLOC_MAX_DQ_FLOATS || need_stat > NPLM_NOALLOC_MAX_STAT_FLOATS)
+    return NPLM_NOALLOC_TOO_LARGE;
+  // The array's name is only a host-side handle: the kernels need its device address, which
+  // differs per device, so it is looked up once per device with that device current.
+  constexpr int MAX_DEVICES = 64;
+  static float* device_ptr[MAX_DEVICES] = {nullptr};
+  int dev = 0;
+  NPLM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return NPLM_NOALLOC_SYMBOL_LOOKUP_FAILED;
+  if (device_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess || p == nullptr)
+      return NPLM_NOALLOC_SYMBOL_LOOKUP_FAILED;
+    device_ptr[dev] = p;
+  }
+  float* dq_acc = device_ptr[dev];
+  float* delta = device_ptr[dev] + NPLM_NOALLOC_MAX_DQ_FLOATS;
+  // nplm_fa_bwd clears dq_acc on `stream` (cudaMemsetAsync) and overwrites delta before use.
+  return nplm_fa_bwd(qkv, out, dout, lse, dqkv, dq_acc, delta, seq_start, seq_end, T, H, D, window,
+                     scale, status, stream);
+}
