@@ -1,0 +1,110 @@
+"""Optimizer step with the collectives fused into the kernels (reduce-scatter + gradient norm,
+AdamW + all-gather push) over symmetric memory. See nanoplm_b200/csrc/comm.cu.
+
+`FusedShardedStep.try_create` allocates the gradient buffer, the parameter buffer and the flag /
+slot words in symmetric memory (torch.distributed._symmetric_memory: CUDA VMM allocations whose
+handles are exchanged once over the bootstrap process group and mapped into every rank). If that
+is not possible on the machine (no peer access, more than 8 ranks, symmetric memory unavailable) it
+returns None and the engine keeps using NCCL collectives.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_int, c_longlong, c_uint, c_void_p
+
+import torch
+import torch.distributed as dist
+
+from nanoplm_b200.ops._lib import CommTimeout, check_rc, count_launch, lib, ptr, status_word, stream_ptr
+from nanoplm_b200.utils.logging import logger
+
+MAX_PEERS = 8
+
+
+def _ptr_array(ptrs):
+    arr = (c_void_p * len(ptrs))()
+    for i, p in enumerate(ptrs):
+        arr[i] = c_void_p(int(p))
+    return arr
+
+
+class SymmetricBuffer:
+    """A tensor allocated identically on every rank, with the peers' device addresses."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group):
+        import torch.distributed._symmetric_memory as symm
+        self.tensor = symm.empty(numel, dtype=dtype, device=device)
+        self.tensor.zero_()
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.ptr_array = _ptr_array(self.ptrs)
+
+
+class FusedShardedStep:
+    def __init__(self, engine, grads: SymmetricBuffer, params: SymmetricBuffer, words: SymmetricBuffer,
+                 barrier_timeout_s: float = 20.0):
+        self.e = engine
+        self.grads, self.params, self.words = grads, params, words
+        self.world, self.rank = engine.world, engine.rank
+        self.epoch = 0
+        self.timeout = barrier_timeout_s
+        dev = engine.device
+        self.shard_grad = torch.zeros(engine.shard, dtype=torch.float32, device=dev)
+        self.partial = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        # words layout per rank: [0:8] barrier flags (uint32), [8:16] partial sums (float32 bits)
+        self.flag_ptrs = _ptr_array(words.ptrs)
+        self.slot_ptrs = _ptr_array([p + 8 * 4 for p in words.ptrs])
+        self.local_slots = words.tensor.view(torch.float32)[8:16]
+        self._lib = lib("comm")
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def allocate(total: int, world: int, device: torch.device, group, compute_dtype):
+        """Returns (grads, params, words) symmetric buffers or None when unavailable."""
+        if world > MAX_PEERS or compute_dtype != torch.bfloat16:
+            return None
+        try:
+            g = group if group is not None else dist.group.WORLD
+            grads = SymmetricBuffer(total, torch.float32, device, g)
+            params = SymmetricBuffer(total, torch.bfloat16, device, g)
+            words = SymmetricBuffer(16, torch.int32, device, g)
+            ok = torch.ones(1, device=device)
+        except Exception as exc:  # noqa: BLE001
+            logger.warning(f"symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL collectives")
+            ok = torch.zeros(1, device=device)
+            grads = params = words = None
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() < 1:
+            return None
+        return grads, params, words
+
+    # ------------------------------------------------------------------ step
+    def barrier(self) -> None:
+        self.epoch += 1
+        rc = self._lib.nplm_peer_barrier(self.flag_ptrs, c_int(self.rank), c_int(self.world),
+                                         c_uint(self.epoch & 0xFFFFFFFF), c_double(self.timeout),
+                                         ptr(status_word(self.e.device)), stream_ptr())
+        check_rc(rc, "peer_barrier")
+        count_launch()
+
+    def step(self, lr: float, grad_scale: float) -> torch.Tensor:
+        e = self.e
+        self.barrier()                                   # every rank's gradients are final
+        self.partial.zero_()
+        rc = self._lib.nplm_rs_sumsq(self.grads.ptr_array, c_int(self.world), c_longlong(e.lo),
+                                     c_longlong(e.shard), ptr(self.shard_grad), ptr(self.partial), stream_ptr())
+        check_rc(rc, "rs_sumsq")
+        rc = self._lib.nplm_publish(self.slot_ptrs, c_int(self.rank), c_int(self.world), ptr(self.partial),
+                                    stream_ptr())
+        check_rc(rc, "publish")
+        self.barrier()                                   # partial sums exchanged, peers done reading my gradients
+        e.main_grad.zero_()
+        rc = self._lib.nplm_adamw_push(ptr(e.master), ptr(e.exp_avg), ptr(e.exp_avg_sq), ptr(self.shard_grad),
+                                       self.params.ptr_array, c_int(self.world), c_longlong(e.lo),
+                                       c_longlong(e.shard), c_longlong(e.decay_end), ptr(e._hyper_dev[0]),
+                                       ptr(self.local_slots), ptr(self.norm), stream_ptr())
+        check_rc(rc, "adamw_push")
+        count_launch(3)
+        self.barrier()                                   # every rank's parameter buffer is complete
+        return self.norm[0]

@@ -106,8 +106,15 @@ class ShardedEngine:
         self.lo, self.hi = self.rank * self.shard, (self.rank + 1) * self.shard
 
         dev = self.device
-        self.flat_params = torch.zeros(self.total, dtype=self.compute_dtype, device=dev)
-        self.main_grad = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        sym = None
+        if fused_comm and self.on_cuda and self.distributed:
+            from nanoplm_b200.comm.fused_optimizer import FusedShardedStep
+            sym = FusedShardedStep.allocate(self.total, self.world, dev, self.pg, self.compute_dtype)
+        if sym is not None:   # gradients and parameters live in peer-mapped memory
+            self.main_grad, self.flat_params = sym[0].tensor, sym[1].tensor
+        else:
+            self.flat_params = torch.zeros(self.total, dtype=self.compute_dtype, device=dev)
+            self.main_grad = torch.zeros(self.total, dtype=torch.float32, device=dev)
         self.master = torch.zeros(self.shard, dtype=torch.float32, device=dev)
         self.exp_avg = torch.zeros(self.shard, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(self.shard, dtype=torch.float32, device=dev)
@@ -126,9 +133,9 @@ class ShardedEngine:
         self.flat_params.copy_(full_master.to(self.compute_dtype))
         del full_master
         self._rebind()
-        if fused_comm and self.on_cuda and self.distributed:
-            from nanoplm_b200.comm.fused_optimizer import FusedShardedStep
-            self.fused = FusedShardedStep.try_create(self)
+        if sym is not None:
+            self.fused = FusedShardedStep(self, *sym)
+            dist.barrier(group=self.pg)
 
     # ---- parameter views ------------------------------------------------------------------
     def _rebind(self) -> None:

@@ -1,0 +1,123 @@
+"""Sharded engine over CPU ranks (gloo): 2-rank training must follow the 1-rank trajectory, and
+checkpoints written by a sharded run must load in a single-process run (and vice versa)."""
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _make_model():
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    torch.manual_seed(0)
+    cfg = ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+                      max_position_embeddings=128)
+    m = ProtEncoderMLM(cfg, ProtTokenizer())
+    with torch.no_grad():
+        for layer in m.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.05)
+            layer.mlp.Wo.weight.normal_(0, 0.05)
+    return m
+
+
+def _batches(n):
+    from nanoplm_b200.data.collators import PackingCollator
+    from nanoplm_b200.data.synthetic import synthetic_token_sequences
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    tok = ProtTokenizer()
+    out = []
+    for i in range(n):
+        seqs = synthetic_token_sequences(8, 10, 60, seed=100 + i)
+        coll = PackingCollator(tok, 64, 0.3, target_rows=8, batch_size=8, seed=i)
+        b = coll([{"input_ids": torch.from_numpy(s)} for s in seqs])
+        b.pop("num_real_tokens")
+        out.append(b)
+    return out
+
+
+def _train(rank, world, port, tmp, result_q):
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.pretrain import TrainStep
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    if world > 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    model = _make_model()
+    eng = ShardedEngine(model, AdamWHyper(lr=5e-3, weight_decay=0.01), torch.device("cpu"))
+    sch = WarmupLinearSchedule(5e-3, 2, 100)
+    st = TrainStep(model, eng, sch, "cpu")
+    batches = _batches(8)
+    losses = []
+    for step in range(4):
+        mine = batches[2 * step:2 * step + 2][rank::world]     # each rank takes its share of 2 micro-batches
+        losses.append(st.step_from_host(mine))
+    if world > 1:
+        t = torch.tensor(losses)
+        dist.all_reduce(t)
+        losses = (t / world).tolist()
+    ckpt.save_checkpoint(eng, sch, 4, 0, tmp, 1, 10, 10, is_main=rank == 0, sharded=world > 1)
+    sd = eng.full_state_dict_model()
+    if rank == 0:
+        torch.save((world, losses, {k: v.clone() for k, v in sd.items()}), os.path.join(tmp, "result.pt"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _run(world, tmp):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_train, args=(r, world, port, tmp, None)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    return torch.load(os.path.join(tmp, "result.pt"))
+
+
+def test_two_rank_training_matches_single_rank(tmp_path):
+    d1, d2 = str(tmp_path / "w1"), str(tmp_path / "w2")
+    os.makedirs(d1)
+    os.makedirs(d2)
+    _, l1, sd1 = _run(1, d1)
+    _, l2, sd2 = _run(2, d2)
+    for a, b in zip(l1, l2):
+        assert abs(a - b) < 1e-4, (l1, l2)
+    for k in sd1:
+        assert torch.allclose(sd1[k], sd2[k], atol=2e-5), k
+    # files of the reference layout exist, plus the per-rank shards of the sharded run
+    for name in ("pytorch_model.bin", "optimizer.pt", "scheduler.pt", "rng_state.pth", "training_state.json"):
+        assert os.path.exists(os.path.join(d2, "checkpoint-4", name))
+    assert os.path.exists(os.path.join(d2, "checkpoint-4", "shard-1.pt"))
+    assert os.path.exists(os.path.join(d2, "checkpoint-4", "index.json"))
+
+    # a checkpoint written by 2 ranks resumes in 1 process (full-tensor path) with identical state
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    model = _make_model()
+    eng = ShardedEngine(model, AdamWHyper(lr=5e-3, weight_decay=0.01), torch.device("cpu"))
+    sch = WarmupLinearSchedule(5e-3, 2, 100)
+    step, epoch = ckpt.load_checkpoint(eng, sch, os.path.join(d2, "checkpoint-4"))
+    assert (step, epoch) == (4, 0) and eng.step_count == 4 and sch.last_epoch == 4
+    sd = eng.full_state_dict_model()
+    for k in sd1:
+        assert torch.allclose(sd[k], sd2[k], atol=1e-7), k
+    opt = torch.load(os.path.join(d2, "checkpoint-4", "optimizer.pt"))
+    assert len(opt["param_groups"]) == 2 and opt["param_groups"][1]["weight_decay"] == 0.0
+    n_params = sum(len(g["params"]) for g in opt["param_groups"])
+    assert n_params == len(eng.slots) and len(opt["state"]) == n_params
