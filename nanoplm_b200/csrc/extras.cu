@@ -1,0 +1,333 @@
+// Kernels for the optional encoder blocks: varlen depthwise convolution and hyper-connection
+// (mHC) stream mixing. The reference has neither; semantics are defined here.
+//
+// Varlen depthwise conv (kernel size KS, odd, "same" centring): for packed tokens x[T][C],
+//   y[t][c] = bias[c] + sum_{k} w[c][k] * x[t + k - KS/2][c]   over taps that stay inside the
+// sequence of token t (seq_start[t] <= t + k - KS/2 < seq_end[t]); taps that would cross a
+// sequence boundary contribute zero.
+//   dx[t][c] = sum_k w[c][k] * dy[t - (k - KS/2)][c]            (same boundary rule, flipped taps)
+//   dw[c][k] = sum_t dy[t][c] * x[t + k - KS/2][c],  dbias[c] = sum_t dy[t][c]
+//
+// mHC mixing on streams X[T][n][C] with per-token coefficients:
+//   read : h[t][:]     = sum_i alpha[t][i] * X[t][i][:]
+//   write: Xn[t][i][:] = sum_j R[t][i][j] * X[t][j][:] + beta[t][i] * y[t][:]
+// plus the backward of both (gradients w.r.t. X, y and the coefficients).
+#include "common.cuh"
+
+namespace nplm {
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 t = unpack_bf16x2(w[e]);
+    f[2 * e] = t.x;
+    f[2 * e + 1] = t.y;
+  }
+}
+
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+constexpr int MAX_KS = 9;
+
+// flip = 0: forward (tap k reads t + k - r);  flip = 1: input gradient (tap k reads t - (k - r))
+__global__ void __launch_bounds__(256)
+dwconv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+              const __nv_bfloat16* __restrict__ bias, const int* __restrict__ s_start,
+              const int* __restrict__ s_end, __nv_bfloat16* __restrict__ y, int T, int C, int KS, int flip) {
+  const int vec = C >> 3;
+  const int r = KS >> 1;
+  const long long total = static_cast<long long>(T) * vec;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / vec);
+    const int c = static_cast<int>(idx % vec) * 8;
+    const int a = s_start[t], b = s_end[t];
+    float acc[8];
+    if (bias != nullptr && !flip) {
+      ld8(bias + c, acc);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    }
+    for (int k = 0; k < KS; ++k) {
+      const int src = flip ? t - (k - r) : t + (k - r);
+      if (src < a || src >= b) continue;
+      float xv[8];
+      ld8(x + static_cast<size_t>(src) * C + c, xv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += xv[e] * __bfloat162float(w[(c + e) * KS + k]);
+    }
+    st8(y + static_cast<size_t>(t) * C + c, acc);
+  }
+}
+
+// dw[c][k] += sum_t dy[t][c] x[t+k-r][c];  dbias[c] += sum_t dy[t][c]. One block handles a slab of
+// tokens for 32 channels x 8 token lanes and reduces through shared memory before the atomics.
+__global__ void __launch_bounds__(256)
+dwconv_bwd_w_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                    const int* __restrict__ s_start, const int* __restrict__ s_end,
+                    float* __restrict__ dw, float* __restrict__ dbias, int T, int C, int KS,
+                    int tokens_per_block) {
+  __shared__ float red[8][32][MAX_KS + 1];
+  const int cl = threadIdx.x & 31;       // channel lane
+  const int tl = threadIdx.x >> 5;       // token lane
+  const int c = blockIdx.y * 32 + cl;
+  const int r = KS >> 1;
+  float acc[MAX_KS + 1];
+#pragma unroll
+  for (int k = 0; k <= MAX_KS; ++k) acc[k] = 0.f;
+  const int t0 = blockIdx.x * tokens_per_block;
+  const int t1 = min(T, t0 + tokens_per_block);
+  if (c < C) {
+    for (int t = t0 + tl; t < t1; t += 8) {
+      const float g = __bfloat162float(dy[static_cast<size_t>(t) * C + c]);
+      const int a = s_start[t], b = s_end[t];
+      acc[MAX_KS] += g;
+#pragma unroll
+      for (int k = 0; k < MAX_KS; ++k) {
+        if (k < KS) {
+          const int src = t + k - r;
+          if (src >= a && src < b) acc[k] += g * __bfloat162float(x[static_cast<size_t>(src) * C + c]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k <= MAX_KS; ++k) red[tl][cl][k] = acc[k];
+  __syncthreads();
+  if (tl == 0 && c < C) {
+    for (int k = 0; k <= MAX_KS; ++k) {
+      float s = 0.f;
+      for (int j = 0; j < 8; ++j) s += red[j][cl][k];
+      if (k < KS) atomicAdd(&dw[c * KS + k], s);
+      else if (k == MAX_KS && dbias != nullptr) atomicAdd(&dbias[c], s);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------- mHC
+constexpr int MAX_STREAMS = 8;
+
+// h[t][:] = sum_i alpha[t][i] X[t][i][:]
+__global__ void __launch_bounds__(256)
+mhc_read_kernel(const __nv_bfloat16* __restrict__ X, const float* __restrict__ alpha,
+                __nv_bfloat16* __restrict__ h, int T, int n, int C) {
+  const int vec = C >> 3;
+  const long long total = static_cast<long long>(T) * vec;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / vec);
+    const int c = static_cast<int>(idx % vec) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < n; ++i) {
+      float xv[8];
+      ld8(X + (static_cast<size_t>(t) * n + i) * C + c, xv);
+      const float a = alpha[t * n + i];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += a * xv[e];
+    }
+    st8(h + static_cast<size_t>(t) * C + c, acc);
+  }
+}
+
+// Xn[t][i][:] = sum_j R[t][i][j] X[t][j][:] + beta[t][i] y[t][:]
+__global__ void __launch_bounds__(256)
+mhc_write_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ y,
+                 const float* __restrict__ R, const float* __restrict__ beta,
+                 __nv_bfloat16* __restrict__ Xn, int T, int n, int C) {
+  const int vec = C >> 3;
+  const long long total = static_cast<long long>(T) * vec;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / vec);
+    const int c = static_cast<int>(idx % vec) * 8;
+    float xv[MAX_STREAMS][8], yv[8];
+    for (int j = 0; j < n; ++j) ld8(X + (static_cast<size_t>(t) * n + j) * C + c, xv[j]);
+    ld8(y + static_cast<size_t>(t) * C + c, yv);
+    for (int i = 0; i < n; ++i) {
+      float acc[8];
+      const float b = beta[t * n + i];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = b * yv[e];
+      for (int j = 0; j < n; ++j) {
+        const float rr = R[(t * n + i) * n + j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += rr * xv[j][e];
+      }
+      st8(Xn + (static_cast<size_t>(t) * n + i) * C + c, acc);
+    }
+  }
+}
+
+// Backward of read and / or write, one warp per token (dXn == null: read part only, dh == null:
+// write part only; outputs of the missing part are not touched):
+//   given dXn[t][i][:] (gradient of the written streams) and dh[t][:] (gradient of the read),
+//   dX[t][j][:]  = sum_i R[t][i][j] dXn[t][i][:] + alpha[t][j] dh[t][:]
+//   dy[t][:]     = sum_i beta[t][i] dXn[t][i][:]
+//   dR[t][i][j]  = <dXn[t][i], X[t][j]>,  dbeta[t][i] = <dXn[t][i], y[t]>,  dalpha[t][j] = <dh[t], X[t][j]>
+__global__ void __launch_bounds__(256)
+mhc_bwd_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ y,
+               const float* __restrict__ R, const float* __restrict__ alpha, const float* __restrict__ beta,
+               const __nv_bfloat16* __restrict__ dXn, const __nv_bfloat16* __restrict__ dh,
+               __nv_bfloat16* __restrict__ dX, __nv_bfloat16* __restrict__ dy, float* __restrict__ dR,
+               float* __restrict__ dalpha, float* __restrict__ dbeta, int T, int n, int C) {
+  const int lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  const bool has_w = dXn != nullptr, has_r = dh != nullptr;
+  for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
+    float sR[MAX_STREAMS][MAX_STREAMS], sB[MAX_STREAMS], sA[MAX_STREAMS];
+#pragma unroll
+    for (int i = 0; i < MAX_STREAMS; ++i) {
+      sB[i] = sA[i] = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAX_STREAMS; ++j) sR[i][j] = 0.f;
+    }
+    for (int c = lane * 8; c < C; c += 256) {
+      float xv[MAX_STREAMS][8], gv[MAX_STREAMS][8], yv[8], hv[8];
+#pragma unroll
+      for (int j = 0; j < MAX_STREAMS; ++j) {
+        if (j < n) {
+          ld8(X + (static_cast<size_t>(t) * n + j) * C + c, xv[j]);
+          if (has_w) {
+            ld8(dXn + (static_cast<size_t>(t) * n + j) * C + c, gv[j]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) gv[j][e] = 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) yv[e] = hv[e] = 0.f;
+      if (has_w) ld8(y + static_cast<size_t>(t) * C + c, yv);
+      if (has_r) ld8(dh + static_cast<size_t>(t) * C + c, hv);
+      float dyv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < MAX_STREAMS; ++i) {
+        if (i < n) {
+          const float b = has_w ? beta[t * n + i] : 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            dyv[e] += b * gv[i][e];
+            sB[i] += gv[i][e] * yv[e];
+            sA[i] += hv[e] * xv[i][e];
+          }
+#pragma unroll
+          for (int j = 0; j < MAX_STREAMS; ++j) {
+            if (j < n) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) sR[i][j] += gv[i][e] * xv[j][e];
+            }
+          }
+        }
+      }
+      if (has_w) st8(dy + static_cast<size_t>(t) * C + c, dyv);
+#pragma unroll
+      for (int j = 0; j < MAX_STREAMS; ++j) {
+        if (j < n) {
+          float o[8];
+          const float a = has_r ? alpha[t * n + j] : 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = a * hv[e];
+#pragma unroll
+          for (int i = 0; i < MAX_STREAMS; ++i) {
+            if (i < n) {
+              const float rr = has_w ? R[(t * n + i) * n + j] : 0.f;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] += rr * gv[i][e];
+            }
+          }
+          st8(dX + (static_cast<size_t>(t) * n + j) * C + c, o);
+        }
+      }
+    }
+    // warp reductions happen on every lane, outside any lane-dependent branch
+#pragma unroll
+    for (int i = 0; i < MAX_STREAMS; ++i) {
+      const float b = warp_sum(sB[i]);
+      const float a = warp_sum(sA[i]);
+      if (lane == 0 && i < n) {
+        if (has_w) dbeta[t * n + i] = b;
+        if (has_r) dalpha[t * n + i] = a;
+      }
+#pragma unroll
+      for (int j = 0; j < MAX_STREAMS; ++j) {
+        const float v = warp_sum(sR[i][j]);
+        if (lane == 0 && i < n && j < n && has_w) dR[(t * n + i) * n + j] = v;
+      }
+    }
+  }
+}
+
+static int grid_for(long long work, int threads) {
+  long long b = (work + threads - 1) / threads;
+  if (b > 148LL * 16) b = 148LL * 16;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+}  // namespace nplm
+
+using namespace nplm;
+
+extern "C" int nplm_dwconv(const void* x, const void* w, const void* bias, const int* s_start,
+                           const int* s_end, void* y, int T, int C, int KS, int flip, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if ((C % 8) || KS < 1 || KS > MAX_KS || !(KS & 1)) return -3;
+  dwconv_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
+      reinterpret_cast<const __nv_bfloat16*>(bias), s_start, s_end, reinterpret_cast<__nv_bfloat16*>(y), T, C,
+      KS, flip);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_dwconv_bwd_w(const void* x, const void* dy, const int* s_start, const int* s_end,
+                                 float* dw, float* dbias, int T, int C, int KS, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (KS < 1 || KS > MAX_KS || !(KS & 1)) return -3;
+  const int tokens_per_block = 512;
+  dim3 grid((T + tokens_per_block - 1) / tokens_per_block, (C + 31) / 32);
+  dwconv_bwd_w_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                            reinterpret_cast<const __nv_bfloat16*>(dy), s_start, s_end, dw,
+                                            dbias, T, C, KS, tokens_per_block);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_mhc_read(const void* X, const float* alpha, void* h, int T, int n, int C, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if ((C % 8) || n < 1 || n > MAX_STREAMS) return -3;
+  mhc_read_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(X), alpha, reinterpret_cast<__nv_bfloat16*>(h), T, n, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_mhc_write(const void* X, const void* y, const float* R, const float* beta, void* Xn,
+                              int T, int n, int C, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if ((C % 8) || n < 1 || n > MAX_STREAMS) return -3;
+  mhc_write_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(X), reinterpret_cast<const __nv_bfloat16*>(y), R, beta,
+      reinterpret_cast<__nv_bfloat16*>(Xn), T, n, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_mhc_bwd(const void* X, const void* y, const float* R, const float* alpha,
+                            const float* beta, const void* dXn, const void* dh, void* dX, void* dy,
+                            float* dR, float* dalpha, float* dbeta, int T, int n, int C, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if ((C % 8) || n < 1 || n > MAX_STREAMS) return -3;
+  int blocks = (T + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  mhc_bwd_kernel<<<blocks, 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(X), reinterpret_cast<const __nv_bfloat16*>(y), R, alpha, beta,
+      reinterpret_cast<const __nv_bfloat16*>(dXn), reinterpret_cast<const __nv_bfloat16*>(dh),
+      reinterpret_cast<__nv_bfloat16*>(dX), reinterpret_cast<__nv_bfloat16*>(dy), dR, dalpha, dbeta, T, n, C);
+  return static_cast<int>(cudaGetLastError());
+}

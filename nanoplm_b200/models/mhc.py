@@ -1,0 +1,106 @@
+"""Manifold-constrained hyper-connections (mHC): n parallel residual streams X[T, n, C].
+
+Per sub-layer (attention or MLP) and per token:
+    z      = rmsnorm(mean_i X_i)                                  (what the coefficient net sees)
+    alpha  = softmax(a + s_a * tanh(W_a z))            [n]        read weights
+    beta   = 2 * sigmoid(b + s_b * tanh(W_b z))        [n]        write weights
+    R      = sinkhorn(exp(r + s_r * tanh(W_r z)))      [n, n]     residual mixing, projected onto the
+                                                                  doubly-stochastic matrices (the
+                                                                  "manifold constraint")
+    h      = sum_i alpha_i X_i                         read
+    X_i   <- sum_j R_ij X_j + beta_i f(h)              write
+Static parts start at the plain-residual solution (alpha uniform, beta = 1, R = identity) and the
+dynamic scales s_* start at 0.01, so a fresh model behaves like an ordinary pre-norm residual
+network whose streams are n copies of the embedding; the streams are summed before the final norm.
+The reference has no hyper-connections; the stream mixing runs in nanoplm_b200/csrc/extras.cu.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from nanoplm_b200.ops import kernels as K
+
+
+def sinkhorn(logits: torch.Tensor, iters: int) -> torch.Tensor:
+    """Projects exp(logits) [..., n, n] towards a doubly-stochastic matrix (log-domain Sinkhorn)."""
+    x = logits
+    for _ in range(max(1, iters)):
+        x = x - torch.logsumexp(x, dim=-1, keepdim=True)
+        x = x - torch.logsumexp(x, dim=-2, keepdim=True)
+    return x.exp()
+
+
+class _ReadFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, alpha):
+        X = X.contiguous()
+        alpha = alpha.float().contiguous()
+        ctx.save_for_backward(X, alpha)
+        return K.mhc_read(X, alpha)
+
+    @staticmethod
+    def backward(ctx, dh):
+        X, alpha = ctx.saved_tensors
+        dX, _, _, dalpha, _ = K.mhc_bwd(X, None, None, alpha, None, None, dh.contiguous())
+        return dX, dalpha
+
+
+class _WriteFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, y, R, beta):
+        X, y = X.contiguous(), y.contiguous()
+        R, beta = R.float().contiguous(), beta.float().contiguous()
+        ctx.save_for_backward(X, y, R, beta)
+        return K.mhc_write(X, y, R, beta)
+
+    @staticmethod
+    def backward(ctx, dXn):
+        X, y, R, beta = ctx.saved_tensors
+        dX, dy, dR, _, dbeta = K.mhc_bwd(X, y, R, None, beta, dXn.contiguous(), None)
+        return dX, dy, dR, dbeta
+
+
+def mhc_read(X, alpha):
+    if X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 8:
+        return _ReadFn.apply(X, alpha)
+    return torch.einsum("ti,tic->tc", alpha.to(X.dtype), X)
+
+
+def mhc_write(X, y, R, beta):
+    if X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 8:
+        return _WriteFn.apply(X, y, R, beta)
+    return torch.einsum("tij,tjc->tic", R.to(X.dtype), X) + beta.to(X.dtype)[:, :, None] * y[:, None, :]
+
+
+class HyperConnection(nn.Module):
+    def __init__(self, dim: int, n: int, sinkhorn_iters: int = 5, eps: float = 1e-5):
+        super().__init__()
+        self.n, self.iters, self.eps = n, sinkhorn_iters, eps
+        self.coef_norm_weight = nn.Parameter(torch.ones(dim))
+        self.coef_proj = nn.Linear(dim, 2 * n + n * n, bias=False)
+        nn.init.normal_(self.coef_proj.weight, 0.0, 0.02)
+        self.static_alpha = nn.Parameter(torch.zeros(n))
+        self.static_beta = nn.Parameter(torch.zeros(n))            # 2*sigmoid(0) = 1
+        self.static_res = nn.Parameter(torch.eye(n) * 6.0 - 3.0)   # sinkhorn(exp(.)) ~ identity
+        self.dyn_scale = nn.Parameter(torch.full((3,), 0.01))
+
+    def coefficients(self, X):
+        n = self.n
+        z = X.float().mean(dim=1)
+        z = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + self.eps) * self.coef_norm_weight.float()
+        d = torch.tanh(F.linear(z, self.coef_proj.weight.float()))
+        s = self.dyn_scale.float()
+        alpha = torch.softmax(self.static_alpha.float() + s[0] * d[:, :n], dim=-1)
+        beta = 2.0 * torch.sigmoid(self.static_beta.float() + s[1] * d[:, n:2 * n])
+        R = sinkhorn(self.static_res.float() + s[2] * d[:, 2 * n:].reshape(-1, n, n), self.iters)
+        return alpha, beta, R
+
+    def read(self, X):
+        alpha, beta, R = self.coefficients(X)
+        return mhc_read(X, alpha), (beta, R)
+
+    def write(self, X, y, state):
+        beta, R = state
+        return mhc_write(X, y, R, beta)

@@ -1,0 +1,181 @@
+"""T5-style encoder teacher (ProtT5-XL shape by default: 24 layers, d_model 1024, 32 heads of 128,
+d_ff 16384, ReLU feed-forward, RMS layer norms, relative-position bias with 32 buckets shared by all
+layers, no attention scaling). Inference only.
+
+Module / parameter names equal HF `T5EncoderModel` (`shared`, `encoder.block.N.layer.0.SelfAttention.
+{q,k,v,o}`, `...relative_attention_bias`, `layer.1.DenseReluDense.{wi,wo}`, `layer_norm`,
+`encoder.final_layer_norm`), so `Rostlab/prot_t5_xl_uniref50` weights load with `load_state_dict`;
+benchmarks and offline machines use `random_init=True`. The reference wraps HF's implementation and
+torch.compile (src/nanoplm/distillation/models/teacher/prott5.py:14-70); here the linear layers run
+on the tcgen05 GEMM (ReLU and residual adds fused where the epilogue allows) and the norms on the
+RMSNorm kernel. The bias-added attention uses PyTorch SDPA (a library call).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from nanoplm_b200.config.schema import TeacherConfig
+from nanoplm_b200.data.tokenizer import TeacherTokenizer
+from nanoplm_b200.ops import functional as ops
+
+
+class _Lin(nn.Module):
+    def __init__(self, i, o):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(o, i))
+
+    def forward(self, x, residual=None):
+        return ops.linear(x, self.weight, None, residual=residual)
+
+
+class _T5Norm(nn.Module):
+    def __init__(self, d, eps):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(d))
+        self.eps = eps
+
+    def forward(self, x):
+        return ops.norm(x, self.weight, self.eps, rms=True)
+
+
+def relative_position_bucket(rel: torch.Tensor, num_buckets: int, max_distance: int) -> torch.Tensor:
+    """Bidirectional T5 bucketing of relative positions (key - query)."""
+    nb = num_buckets // 2
+    ret = (rel > 0).long() * nb
+    n = rel.abs()
+    max_exact = nb // 2
+    is_small = n < max_exact
+    large = max_exact + (torch.log(n.float().clamp(min=1) / max_exact) / math.log(max_distance / max_exact)
+                         * (nb - max_exact)).long()
+    large = torch.minimum(large, torch.full_like(large, nb - 1))
+    return ret + torch.where(is_small, n, large)
+
+
+class SelfAttention(nn.Module):
+    def __init__(self, cfg: TeacherConfig, has_bias: bool):
+        super().__init__()
+        inner = cfg.num_heads * cfg.d_kv
+        self.h, self.dk = cfg.num_heads, cfg.d_kv
+        self.q, self.k, self.v = _Lin(cfg.d_model, inner), _Lin(cfg.d_model, inner), _Lin(cfg.d_model, inner)
+        self.o = _Lin(inner, cfg.d_model)
+        self.cfg = cfg
+        if has_bias:
+            self.relative_attention_bias = nn.Embedding(cfg.relative_attention_num_buckets, cfg.num_heads)
+
+    def compute_bias(self, S: int, device) -> torch.Tensor:
+        pos = torch.arange(S, device=device)
+        buckets = relative_position_bucket(pos[None, :] - pos[:, None], self.cfg.relative_attention_num_buckets,
+                                           self.cfg.relative_attention_max_distance)
+        return self.relative_attention_bias(buckets).permute(2, 0, 1)[None]     # [1, H, S, S]
+
+    def forward(self, x, bias, residual):
+        B, S, _ = x.shape
+        x2 = x.reshape(B * S, -1)
+        q = self.q(x2).view(B, S, self.h, self.dk).transpose(1, 2)
+        k = self.k(x2).view(B, S, self.h, self.dk).transpose(1, 2)
+        v = self.v(x2).view(B, S, self.h, self.dk).transpose(1, 2)
+        y = F.scaled_dot_product_attention(q, k, v, attn_mask=bias.to(q.dtype), scale=1.0)
+        y = y.transpose(1, 2).reshape(B * S, self.h * self.dk)
+        return self.o(y, residual=residual.reshape(B * S, -1)).view(B, S, -1)
+
+
+class _AttnLayer(nn.Module):
+    def __init__(self, cfg, has_bias):
+        super().__init__()
+        self.SelfAttention = SelfAttention(cfg, has_bias)
+        self.layer_norm = _T5Norm(cfg.d_model, cfg.layer_norm_epsilon)
+
+    def forward(self, x, bias):
+        return self.SelfAttention(self.layer_norm(x), bias, residual=x)
+
+
+class _DenseReluDense(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.wi, self.wo = _Lin(cfg.d_model, cfg.d_ff), _Lin(cfg.d_ff, cfg.d_model)
+
+    def forward(self, x2, residual):
+        return self.wo(ops.activation(self.wi(x2), "relu"), residual=residual)
+
+
+class _FFLayer(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.DenseReluDense = _DenseReluDense(cfg)
+        self.layer_norm = _T5Norm(cfg.d_model, cfg.layer_norm_epsilon)
+
+    def forward(self, x):
+        B, S, C = x.shape
+        return self.DenseReluDense(self.layer_norm(x).reshape(B * S, C), x.reshape(B * S, C)).view(B, S, C)
+
+
+class _Block(nn.Module):
+    def __init__(self, cfg, has_bias):
+        super().__init__()
+        self.layer = nn.ModuleList([_AttnLayer(cfg, has_bias), _FFLayer(cfg)])
+
+    def forward(self, x, bias):
+        return self.layer[1](self.layer[0](x, bias))
+
+
+class _Stack(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.block = nn.ModuleList([_Block(cfg, i == 0) for i in range(cfg.num_layers)])
+        self.final_layer_norm = _T5Norm(cfg.d_model, cfg.layer_norm_epsilon)
+
+
+class T5EncoderTeacher(nn.Module):
+    def __init__(self, cfg: Optional[TeacherConfig] = None, random_init: bool = True, seed: int = 0):
+        super().__init__()
+        self.cfg = cfg or TeacherConfig()
+        self.tokenizer = TeacherTokenizer(self.cfg.vocab_size)
+        self.shared = nn.Embedding(self.cfg.vocab_size, self.cfg.d_model)
+        self.encoder = _Stack(self.cfg)
+        if random_init:
+            g = torch.Generator().manual_seed(seed)
+            with torch.no_grad():
+                for name, p in self.named_parameters():
+                    if p.ndim >= 2:
+                        p.copy_(torch.randn(p.shape, generator=g) * (p.shape[-1] ** -0.5))
+        for p in self.parameters():
+            p.requires_grad_(False)
+        self.eval()
+
+    @classmethod
+    def from_pretrained(cls, name_or_path: str, cfg: Optional[TeacherConfig] = None) -> "T5EncoderTeacher":
+        """Loads HF T5EncoderModel weights (needs the files locally or network access)."""
+        from transformers import T5EncoderModel
+        hf = T5EncoderModel.from_pretrained(name_or_path)
+        c = hf.config
+        cfg = cfg or TeacherConfig(vocab_size=c.vocab_size, d_model=c.d_model, d_kv=c.d_kv, d_ff=c.d_ff,
+                                   num_layers=c.num_layers, num_heads=c.num_heads,
+                                   relative_attention_num_buckets=c.relative_attention_num_buckets,
+                                   relative_attention_max_distance=c.relative_attention_max_distance,
+                                   layer_norm_epsilon=c.layer_norm_epsilon, name=name_or_path)
+        m = cls(cfg, random_init=False)
+        sd = {k: v for k, v in hf.state_dict().items() if k != "encoder.embed_tokens.weight"}
+        m.load_state_dict(sd, strict=True)
+        return m
+
+    @staticmethod
+    def preprocess(seq: str) -> str:
+        return TeacherTokenizer.preprocess(seq)
+
+    @torch.no_grad()
+    def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """(B, S) token ids -> (B, S, d_model) last hidden state."""
+        B, S = input_ids.shape
+        x = self.shared(input_ids)
+        bias = self.encoder.block[0].layer[0].SelfAttention.compute_bias(S, input_ids.device)
+        if attention_mask is not None:
+            neg = torch.finfo(torch.float32).min
+            bias = bias.float() + (1.0 - attention_mask[:, None, None, :].float()) * neg
+        for blk in self.encoder.block:
+            x = blk(x, bias)
+        return self.encoder.final_layer_norm(x)

@@ -328,3 +328,60 @@ def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=
 
 def check_status() -> None:
     _lib.check_status()
+
+
+# --------------------------------------------------------------------------- conv / mHC
+def dwconv(x, w, bias, seq_start, seq_end, flip=False):
+    T, C = x.shape
+    KS = w.shape[1]
+    y = torch.empty_like(x)
+    rc = lib("extras").nplm_dwconv(ptr(x), ptr(w), ptr(bias), ptr(seq_start), ptr(seq_end), ptr(y), c_int(T),
+                                   c_int(C), c_int(KS), c_int(int(flip)), stream_ptr())
+    check_rc(rc, "dwconv")
+    count_launch()
+    return y
+
+
+def dwconv_bwd_w(x, dy, seq_start, seq_end, dw, dbias):
+    T, C = x.shape
+    KS = dw.shape[1]
+    rc = lib("extras").nplm_dwconv_bwd_w(ptr(x), ptr(dy), ptr(seq_start), ptr(seq_end), ptr(dw), ptr(dbias),
+                                         c_int(T), c_int(C), c_int(KS), stream_ptr())
+    check_rc(rc, "dwconv_bwd_w")
+    count_launch()
+
+
+def mhc_read(X, alpha):
+    T, n, C = X.shape
+    h = torch.empty((T, C), dtype=_BF16, device=X.device)
+    rc = lib("extras").nplm_mhc_read(ptr(X), ptr(alpha), ptr(h), c_int(T), c_int(n), c_int(C), stream_ptr())
+    check_rc(rc, "mhc_read")
+    count_launch()
+    return h
+
+
+def mhc_write(X, y, R, beta):
+    T, n, C = X.shape
+    Xn = torch.empty_like(X)
+    rc = lib("extras").nplm_mhc_write(ptr(X), ptr(y), ptr(R), ptr(beta), ptr(Xn), c_int(T), c_int(n), c_int(C),
+                                      stream_ptr())
+    check_rc(rc, "mhc_write")
+    count_launch()
+    return Xn
+
+
+def mhc_bwd(X, y, R, alpha, beta, dXn, dh):
+    """Backward of write (dXn given) and / or read (dh given). Returns (dX, dy, dR, dalpha, dbeta)."""
+    T, n, C = X.shape
+    dev = X.device
+    dX = torch.empty_like(X)
+    dy = torch.empty((T, C), dtype=_BF16, device=dev) if dXn is not None else None
+    dR = torch.empty((T, n, n), dtype=torch.float32, device=dev) if dXn is not None else None
+    dbeta = torch.empty((T, n), dtype=torch.float32, device=dev) if dXn is not None else None
+    dalpha = torch.empty((T, n), dtype=torch.float32, device=dev) if dh is not None else None
+    rc = lib("extras").nplm_mhc_bwd(ptr(X), ptr(y), ptr(R), ptr(alpha), ptr(beta), ptr(dXn), ptr(dh), ptr(dX),
+                                    ptr(dy), ptr(dR), ptr(dalpha), ptr(dbeta), c_int(T), c_int(n), c_int(C),
+                                    stream_ptr())
+    check_rc(rc, "mhc_bwd")
+    count_launch()
+    return dX, dy, dR, dalpha, dbeta

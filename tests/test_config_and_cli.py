@@ -1,0 +1,145 @@
+"""YAML loaders, templates and the CLI end to end on CPU (data from-yaml with the built-in stage
+runner -> pretrain from-yaml -> resume; distill from-yaml with a tiny random-init teacher)."""
+import json
+import os
+from pathlib import Path
+
+import pytest
+import yaml
+from click.testing import CliRunner
+
+from nanoplm_b200.cli import cli
+from nanoplm_b200.config import (ConfigError, load_model_config, load_pretrain_config, load_resume_config,
+                                 resolve_pure_torch_config)
+from nanoplm_b200.config.templates import DISTILL_YAML, PARAMS_YAML, PRETRAIN_YAML
+from nanoplm_b200.data.synthetic import write_synthetic_fasta
+
+
+def test_templates_load_with_the_strict_loaders():
+    raw = yaml.safe_load(PRETRAIN_YAML)
+    m = load_model_config(raw["model"])
+    assert (m.hidden_size, m.num_hidden_layers, m.vocab_size) == (1024, 16, 32)
+    p = load_pretrain_config(raw["pretraining"])
+    assert p.adam_learning_rate == 1e-3 and p.global_batch_size == 2 ** 20 and p.mlm_probability == 0.3
+    enabled, pt = resolve_pure_torch_config(raw)
+    assert enabled and pt.use_packing and pt.target_packed_rows is None
+    assert set(yaml.safe_load(PARAMS_YAML)) == {"data_params", "pretrain_config", "distillation_config", "data_dirs"}
+    assert set(yaml.safe_load(DISTILL_YAML)) == {"model", "distillation", "resume"}
+
+
+def test_loader_rules():
+    base = yaml.safe_load(PRETRAIN_YAML)
+    model = dict(base["model"])
+    model.pop("vocab_size")
+    with pytest.raises(ConfigError, match="Missing required model configuration keys: vocab_size"):
+        load_model_config(model)
+    with pytest.raises(ConfigError, match="Unexpected model configuration keys: bogus"):
+        load_model_config({**base["model"], "bogus": 1})
+    ok = load_model_config({**base["model"], "conv_kernel_size": 7, "mhc_streams": 4,
+                            "moe": {"num_experts": 8, "top_k": 2}})
+    assert ok.conv_kernel_size == 7 and ok.moe.enabled and ok.is_moe_layer(1) and not ok.is_moe_layer(0)
+    pre = dict(base["pretraining"])
+    with pytest.raises(ConfigError, match="gradient_accumulation_steps is inferred"):
+        load_pretrain_config({**pre, "gradient_accumulation_steps": 4})
+    with pytest.raises(ConfigError, match="dataset_dir is required"):
+        load_pretrain_config({k: v for k, v in pre.items() if k != "dataset_dir"})
+    with pytest.raises(ConfigError, match="Unexpected training configuration keys: nope"):
+        load_pretrain_config({**pre, "nope": 1})
+    legacy = {k: v for k, v in pre.items() if k not in ("adam_learning_rate", "adam_weight_decay")}
+    cfg = load_pretrain_config({**legacy, "learning_rate": "3e-4", "weight_decay": "0.01", "bf16": "false"})
+    assert cfg.adam_learning_rate == 3e-4 and cfg.adam_weight_decay == 0.01 and cfg.bf16 is False
+    with pytest.raises(ConfigError, match="Invalid adam_beta1"):
+        load_pretrain_config({**pre, "adam_beta1": "abc"})
+    assert load_resume_config(None).is_resume is False
+    with pytest.raises(ConfigError, match="does not exist"):
+        load_resume_config({"is_resume": True, "checkpoint_dir": "/nonexistent/ckpt"})
+    with pytest.raises(ConfigError, match="missing"):
+        load_resume_config({"is_resume": True})
+
+
+def _write_params(tmp: Path, mode: str, on_the_fly=False):
+    params = yaml.safe_load(PARAMS_YAML)
+    params["data_params"].update(pipeline_mode=mode, seqs_num=60, min_seq_len=10, max_seq_len=64, val_ratio=0.2)
+    params["pretrain_config"].update(output_dir="out/shards", samples_per_shard=20, max_workers=1)
+    params["distillation_config"].update(output_dir="out/kd", on_the_fly=on_the_fly)
+    params["data_dirs"].update(url="unused", compressed_fasta="raw/x.fasta.gz", extracted_fasta="raw/x.fasta",
+                               shuffled_fasta="raw/x_shuf.fasta", filtered_fasta="raw/x_filt.fasta",
+                               splitted_fasta_dir="raw/split")
+    (tmp / "params.yaml").write_text(yaml.safe_dump(params))
+    write_synthetic_fasta(tmp / "raw" / "x.fasta", 120, 5, 80, seed=11)
+
+
+def test_cli_data_pretrain_resume_cycle(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("WANDB_MODE", "disabled")
+    runner = CliRunner()
+    r = runner.invoke(cli, ["data", "get-yaml", str(tmp_path)])
+    assert r.exit_code == 0 and (tmp_path / "dvc.yaml").exists()
+    assert runner.invoke(cli, ["data", "get-yaml", str(tmp_path)]).exit_code != 0       # no overwrite
+    _write_params(tmp_path, "pretrain")
+    r = runner.invoke(cli, ["data", "from-yaml", "params.yaml", "--runner", "builtin"])
+    assert r.exit_code == 0, r.output
+    manifest = yaml.safe_load((tmp_path / "out" / "shards" / ".data_manifest").read_text())
+    assert manifest["pipeline_mode"] == "pretrain" and manifest["train_sequences"] == 48 and manifest["val_sequences"] == 12
+
+    r = runner.invoke(cli, ["pretrain", "get-yaml", "pretrain.yaml"])
+    assert r.exit_code == 0
+    cfg = yaml.safe_load((tmp_path / "pretrain.yaml").read_text())
+    cfg["model"].update(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+                        max_position_embeddings=128)
+    cfg["pretraining"].update(dataset_dir="out/shards", ckp_dir="ckpt", micro_batch_size=8, global_batch_size=8 * 64,
+                              num_epochs=2, logging_steps=1, eval_steps=3, save_steps=3, num_workers=0, bf16=False)
+    cfg["pure_torch"].update(use_packing=True, target_packed_rows=5)
+    (tmp_path / "pretrain.yaml").write_text(yaml.safe_dump(cfg))
+    r = runner.invoke(cli, ["pretrain", "from-yaml", "pretrain.yaml"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    run = next((tmp_path / "ckpt").glob("run-*"))
+    ck = sorted(p.name for p in run.glob("checkpoint-*"))
+    assert ck == ["checkpoint-12", "checkpoint-3", "checkpoint-6", "checkpoint-9"]
+    for f in ("pytorch_model.bin", "optimizer.pt", "scheduler.pt", "rng_state.pth", "training_state.json"):
+        assert (run / "checkpoint-6" / f).exists()
+    assert json.loads((run / "checkpoint-6" / "training_state.json").read_text())["global_step"] == 6
+    lines = [json.loads(l) for l in (run / "metrics.jsonl").read_text().splitlines()]
+    assert any("eval/loss" in l for l in lines) and any("train/tokens_per_sec" in l for l in lines)
+
+    # resume from step 6 with one extra epoch: continues in the same run dir, later checkpoints archived
+    cfg["resume"] = {"is_resume": True, "checkpoint_dir": str(run / "checkpoint-6"), "extra_epochs": 1}
+    (tmp_path / "pretrain.yaml").write_text(yaml.safe_dump(cfg))
+    r = runner.invoke(cli, ["pretrain", "from-yaml", "pretrain.yaml"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    assert (run / ".resume_counter").read_text() == "1"
+    archived = list(run.glob("archived_*"))
+    assert len(archived) == 1 and sorted(p.name for p in archived[0].iterdir()) == ["checkpoint-12", "checkpoint-9"]
+    assert (run / "checkpoint-18").exists()                                            # 3 epochs x 6 steps
+
+    bad = dict(cfg)
+    bad["pretraining"] = {**cfg["pretraining"], "gradient_accumulation_steps": 2}
+    (tmp_path / "bad.yaml").write_text(yaml.safe_dump(bad))
+    r = runner.invoke(cli, ["pretrain", "from-yaml", "bad.yaml"])
+    assert r.exit_code != 0 and "inferred" in r.output
+    assert runner.invoke(cli, ["pretrain", "from-yaml", "missing.yaml"]).exit_code != 0
+
+
+def test_cli_distillation_on_the_fly(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("WANDB_MODE", "disabled")
+    runner = CliRunner()
+    _write_params(tmp_path, "distillation", on_the_fly=True)
+    r = runner.invoke(cli, ["data", "from-yaml", "params.yaml", "--runner", "builtin"])
+    assert r.exit_code == 0, r.output
+    assert yaml.safe_load((tmp_path / "out" / "kd" / ".data_manifest").read_text())["on_the_fly"] is True
+    assert runner.invoke(cli, ["distill", "get-yaml", "distill.yaml"]).exit_code == 0
+    cfg = yaml.safe_load((tmp_path / "distill.yaml").read_text())
+    cfg["model"].update(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2)
+    cfg["distillation"].update(dataset_dir="out/kd", ckp_dir="dckpt", num_epochs=2, batch_size=8, logging_steps=1,
+                               eval_steps=4, save_steps=6, bf16=False, teacher_random_init=True,
+                               teacher={"d_model": 1024, "d_kv": 16, "d_ff": 64, "num_layers": 1, "num_heads": 4})
+    (tmp_path / "distill.yaml").write_text(yaml.safe_dump(cfg))
+    r = runner.invoke(cli, ["distill", "from-yaml", "distill.yaml"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    run = next((tmp_path / "dckpt").glob("run-*"))
+    assert (run / "training_config.json").exists() and (run / "model.safetensors").exists()
+    assert (run / "checkpoint-6" / "model.safetensors").exists() and (run / "checkpoint-12" / "optimizer.pt").exists()
+    lines = [json.loads(l) for l in (run / "metrics.jsonl").read_text().splitlines()]
+    train = [l["train/loss"] for l in lines if "train/loss" in l]
+    assert train[-1] < train[0]

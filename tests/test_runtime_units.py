@@ -1,0 +1,125 @@
+"""Schedules, batch arithmetic, run-directory bookkeeping, heartbeat watchdog, sampler fast-forward."""
+import math
+import os
+import time
+from pathlib import Path
+
+import pytest
+import torch
+
+from nanoplm_b200.runtime.pretrain import ResumableDistributedSampler
+from nanoplm_b200.runtime.run_dirs import (archive_future_checkpoints, compute_batch_setup, get_num_workers,
+                                           prepare_run_and_steps)
+from nanoplm_b200.runtime.schedule import (WarmupLinearSchedule, get_warmup_steps, make_distill_schedule,
+                                           num_update_steps_per_epoch)
+from nanoplm_b200.runtime.watchdog import Heartbeat, RankFailure, check_or_raise, find_stalled
+
+
+def test_warmup_linear_schedule_matches_torch_lambda_lr():
+    import torch.optim as optim
+    from torch.optim.lr_scheduler import LambdaLR
+    warm, total = 5, 40
+    p = torch.nn.Parameter(torch.zeros(1))
+    opt = optim.SGD([p], lr=1e-3)
+
+    def lam(step):
+        if step < warm:
+            return step / max(1, warm)
+        return max(0.0, (total - step) / max(1, total - warm))
+    ref = LambdaLR(opt, lam)
+    mine = WarmupLinearSchedule(1e-3, warm, total)
+    for _ in range(45):
+        assert abs(mine.get_lr() - ref.get_last_lr()[0]) < 1e-12
+        opt.step()
+        ref.step()
+        mine.step()
+    sd = mine.state_dict()
+    other = WarmupLinearSchedule(1e-3, warm, total)
+    other.load_state_dict(sd)
+    assert other.last_epoch == 45 and other.get_lr() == mine.get_lr()
+    other.load_state_dict(ref.state_dict())          # a torch LambdaLR state dict loads as well
+    assert other.last_epoch == 45
+    assert get_warmup_steps(100, 0.05) == 5 and get_warmup_steps(100, 7) == 7 and get_warmup_steps(101, 0.05) == 6
+    assert num_update_steps_per_epoch(10, 4) == 3 and num_update_steps_per_epoch(0, 4) == 1
+
+
+def test_distillation_schedules():
+    for name in ("cosine", "linear", "polynomial", "constant"):
+        s = make_distill_schedule(name, 1e-3, 10, 100)
+        lrs = []
+        for _ in range(100):
+            lrs.append(s.get_lr())
+            s.step()
+        assert lrs[0] == 0 and abs(lrs[10] - 1e-3) < 1e-12 and all(a <= b + 1e-15 for a, b in zip(lrs[:10], lrs[1:11]))
+        if name != "constant":
+            assert lrs[-1] < 0.1e-3
+        else:
+            assert lrs[-1] == 1e-3
+    with pytest.raises(ValueError):
+        make_distill_schedule("bogus", 1e-3, 1, 10)
+
+
+def test_batch_setup_and_workers():
+    b = compute_batch_setup(2 ** 20, 32, 512, 1)
+    assert b.grad_accum_steps == 64 and b.global_batch_size_samples == 2048 and b.achieved_global_batch_tokens == 2 ** 20
+    assert compute_batch_setup(2 ** 20, 32, 512, 8).grad_accum_steps == 8
+    assert compute_batch_setup(1000, 32, 512, 8).grad_accum_steps == 1
+    with pytest.raises(ValueError):
+        compute_batch_setup(0, 32, 512, 1)
+    assert get_num_workers(3, 1) == 3 and get_num_workers("2", 1) == 2 and get_num_workers("auto", 2) >= 1
+    with pytest.raises(ValueError):
+        get_num_workers(-1, 1)
+    with pytest.raises(ValueError):
+        get_num_workers("many", 1)
+
+
+def test_run_naming_resume_counter_and_archive(tmp_path):
+    plan = prepare_run_and_steps(str(tmp_path), 3, 10, 50, 100, False, "", None, 1000, 100)
+    assert plan.run_name.startswith("run-") and Path(plan.output_dir, "run_name.txt").read_text() == plan.run_name
+    assert (plan.logging_steps, plan.eval_steps, plan.save_steps) == (10, 30, 30)      # clamped to total steps
+    plan2 = prepare_run_and_steps(str(tmp_path), 3, 10, 50, 100, False, "", None, 1000, 100)
+    assert plan2.run_name == plan.run_name + "-2"
+    run = Path(plan.output_dir)
+    for s in (10, 20, 30):
+        (run / f"checkpoint-{s}").mkdir()
+    r = prepare_run_and_steps(str(tmp_path), 3, 10, 50, 100, True, str(run / "checkpoint-10"), 2, 1000, 100)
+    assert r.run_name == plan.run_name and r.wandb_run_name == plan.run_name + "-re1" and r.num_epochs == 5
+    assert r.resume_step == 10 and (run / ".resume_counter").read_text() == "1"
+    arch = list(run.glob("archived_*"))
+    assert len(arch) == 1 and sorted(p.name for p in arch[0].iterdir()) == ["checkpoint-20", "checkpoint-30"]
+    r2 = prepare_run_and_steps(str(tmp_path), 3, 10, 50, 100, True, str(run / "checkpoint-10"), None, 1000, 100)
+    assert r2.wandb_run_name.endswith("-re2")
+    assert archive_future_checkpoints(run, 10) is None
+
+
+def test_sampler_partition_and_fast_forward():
+    n, world = 103, 4
+    seen = []
+    for r in range(world):
+        s = ResumableDistributedSampler(n, world, r, shuffle=True, seed=5)
+        s.set_epoch(2)
+        idx = list(s)
+        assert len(idx) == math.ceil(n / world)
+        seen += idx
+    assert set(seen) == set(range(n))
+    s = ResumableDistributedSampler(n, world, 1, True, 5)
+    s.set_epoch(2)
+    full = list(s)
+    s.fast_forward(10)
+    assert len(s) == len(full) - 10 and list(s) == full[10:]
+    assert list(s) == full                                     # the offset applies to one epoch only
+
+
+def test_heartbeat_and_watchdog(tmp_path):
+    hb0 = Heartbeat(tmp_path, 0, interval=0.05).start()
+    hb1 = Heartbeat(tmp_path, 1, interval=0.05).start()
+    time.sleep(0.15)
+    assert find_stalled(tmp_path, 2, max_age=1.0) == []
+    assert find_stalled(tmp_path, 3, max_age=1.0) == [2]       # a rank that never joined
+    hb1.stop()                                                  # rank 1 "dies" on the host side
+    time.sleep(0.4)
+    assert find_stalled(tmp_path, 2, max_age=0.3) == [1]
+    with pytest.raises(RankFailure) as e:
+        check_or_raise(tmp_path, 2, 0.3)
+    assert e.value.ranks == [1]
+    hb0.stop()
