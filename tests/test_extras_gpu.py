@@ -1,0 +1,175 @@
+"""GPU kernels of the optional blocks (varlen depthwise conv, mHC mixing), the MoE layer, and the
+student / teacher / distillation step, each against the fp32 CPU restatement."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _close(a, b, tol=3e-2, what=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    ref = max(1.0, b.abs().max().item())
+    err = (a - b).abs().max().item()
+    assert err <= tol * ref, f"{what}: max err {err} (ref max {ref})"
+
+
+def _bounds(lens, device="cuda"):
+    from nanoplm_b200.ops import functional as ops
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=device)
+    return ops.seq_bounds(cu_t, cu[-1]), cu[-1]
+
+
+@pytest.mark.parametrize("ks,bias", [(7, False), (7, True), (3, False)])
+def test_dwconv_fwd_bwd(ks, bias, cuda_status):
+    from nanoplm_b200.models.conv import dwconv_reference, dwconv_varlen
+    (ss, se), T = _bounds([5, 130, 1, 64, 300, 77])
+    C = 768
+    x = (torch.randn(T, C, device="cuda")).to(BF).requires_grad_(True)
+    w = (torch.randn(C, ks, device="cuda") * 0.3).to(BF).requires_grad_(True)
+    b = (torch.randn(C, device="cuda") * 0.1).to(BF).requires_grad_(True) if bias else None
+    dy = torch.randn(T, C, device="cuda").to(BF)
+    y = dwconv_varlen(x, w, b, ss, se)
+    y.backward(dy)
+    xr = x.detach().float().cpu().requires_grad_(True)
+    wr = w.detach().float().cpu().requires_grad_(True)
+    br = b.detach().float().cpu().requires_grad_(True) if bias else None
+    yr = dwconv_reference(xr, wr, br, ss.cpu(), se.cpu())
+    yr.backward(dy.float().cpu())
+    _close(y, yr, what="conv fwd")
+    _close(x.grad, xr.grad, what="conv dx")
+    _close(w.grad, wr.grad, what="conv dw")
+    if bias:
+        _close(b.grad, br.grad, what="conv dbias")
+
+
+def test_mhc_read_write_fwd_bwd(cuda_status):
+    from nanoplm_b200.models import mhc
+    T, n, C = 1000, 4, 768
+    X = torch.randn(T, n, C, device="cuda").to(BF).requires_grad_(True)
+    y = torch.randn(T, C, device="cuda").to(BF).requires_grad_(True)
+    alpha = torch.softmax(torch.randn(T, n, device="cuda"), -1).requires_grad_(True)
+    beta = torch.rand(T, n, device="cuda").requires_grad_(True)
+    R = torch.softmax(torch.randn(T, n, n, device="cuda"), -1).requires_grad_(True)
+    h = mhc.mhc_read(X, alpha)
+    Xn = mhc.mhc_write(X, y, R, beta)
+    gh, gX = torch.randn_like(h), torch.randn_like(Xn)
+    (h * gh).sum().backward(retain_graph=True)
+    g_read = (X.grad.clone(), alpha.grad.clone())
+    X.grad = None
+    (Xn * gX).sum().backward()
+    ref = [t.detach().float().cpu().requires_grad_(True) for t in (X, y, alpha, beta, R)]
+    Xc, yc, ac, bc, Rc = ref
+    hc = torch.einsum("ti,tic->tc", ac, Xc)
+    Xnc = torch.einsum("tij,tjc->tic", Rc, Xc) + bc[:, :, None] * yc[:, None, :]
+    _close(h, hc, what="mhc read")
+    _close(Xn, Xnc, what="mhc write")
+    (hc * gh.float().cpu()).sum().backward(retain_graph=True)
+    _close(g_read[0], Xc.grad, what="read dX")
+    _close(g_read[1], ac.grad, what="read dalpha")
+    Xc.grad = None
+    (Xnc * gX.float().cpu()).sum().backward()
+    _close(X.grad, Xc.grad, what="write dX")
+    _close(y.grad, yc.grad, what="write dy")
+    _close(beta.grad, bc.grad, what="write dbeta")
+    _close(R.grad, Rc.grad, what="write dR")
+
+
+def _hybrid_cfg(**kw):
+    from nanoplm_b200.config.schema import ModelConfig, MoEConfig
+    base = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=4, num_attention_heads=4,
+                max_position_embeddings=256)
+    base.update(kw)
+    return ModelConfig(**base)
+
+
+def _batch(tok, seed=1):
+    from nanoplm_b200.data.collators import PackingCollator
+    from nanoplm_b200.data.synthetic import synthetic_token_sequences
+    seqs = synthetic_token_sequences(24, 20, 200, seed=seed)
+    coll = PackingCollator(tok, 256, 0.3, target_rows=12, batch_size=24, seed=seed)
+    b = coll([{"input_ids": torch.from_numpy(s)} for s in seqs])
+    return {k: b[k] for k in ("input_ids", "cu_seqlens", "position_ids", "masked_idx", "masked_labels", "max_seqlen")}
+
+
+@pytest.mark.parametrize("variant", ["conv_mhc", "moe"])
+def test_hybrid_encoder_matches_cpu(variant, cuda_status):
+    from nanoplm_b200.config.schema import MoEConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    torch.manual_seed(0)
+    tok = ProtTokenizer()
+    if variant == "conv_mhc":
+        cfg = _hybrid_cfg(conv_kernel_size=7, mhc_streams=4)
+    else:
+        cfg = _hybrid_cfg(moe=MoEConfig(num_experts=8, top_k=2, expert_intermediate_size=128, every_n_layers=2))
+    cpu = ProtEncoderMLM(cfg, tok)
+    with torch.no_grad():
+        for layer in cpu.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.03)
+            if hasattr(layer.mlp, "Wo"):
+                layer.mlp.Wo.weight.normal_(0, 0.03)
+            else:
+                layer.mlp.experts_Wo.normal_(0, 0.03)
+    gpu = copy.deepcopy(cpu)
+    eng = ShardedEngine(gpu, AdamWHyper(), torch.device("cuda:0"))
+    b = _batch(tok)
+    oc = cpu(**b)
+    oc["loss"].backward()
+    og = gpu(**{k: (v.cuda() if torch.is_tensor(v) else v) for k, v in b.items()})
+    og["loss"].backward()
+    eng.collect_autograd_grads()
+    torch.cuda.synchronize()
+    assert abs(oc["loss"].item() - og["loss"].item()) < 4e-2, (oc["loss"].item(), og["loss"].item())
+    by_name = dict(cpu.named_parameters())
+    bad = []
+    for s in eng.slots:
+        if "router" in s.name:            # top-k ties may flip between precisions
+            continue
+        if "static_alpha" in s.name:      # softmax over near-identical streams: the gradient is a
+            continue                      # cancellation residue, dominated by bf16 rounding
+        g_ref = by_name[s.name].grad
+        if g_ref is None:
+            continue
+        g = eng.main_grad[s.offset:s.offset + s.numel].view(s.shape).cpu()
+        rel = (g - g_ref).abs().max().item() / (g_ref.abs().max().item() + 1e-6)
+        if rel > 0.12:
+            bad.append((s.name, rel))
+    assert not bad, bad
+
+
+def test_distillation_step_gpu(cuda_status):
+    from nanoplm_b200.config.schema import StudentConfig, TeacherConfig
+    from nanoplm_b200.models.student import ProtX
+    from nanoplm_b200.models.teacher import T5EncoderTeacher
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime.distill import DistillDataCollator, distillation_loss
+    from nanoplm_b200.data.synthetic import synthetic_sequences
+    torch.manual_seed(0)
+    dev = torch.device("cuda:0")
+    teacher = T5EncoderTeacher(TeacherConfig(d_model=1024, d_kv=64, d_ff=512, num_layers=2, num_heads=4), seed=1)
+    t_cpu = copy.deepcopy(teacher)
+    teacher.to(dev).to(BF)
+    scfg = StudentConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                         conv_kernel_size=7, mhc_streams=4)
+    student = ProtX(scfg)
+    s_cpu = copy.deepcopy(student)
+    eng = ShardedEngine(student, AdamWHyper(lr=1e-3), dev)
+    coll = DistillDataCollator(True, 96)
+    batch = coll([{"raw_sequence": s} for s in synthetic_sequences(6, 20, 90, seed=4)])
+    loss_c = distillation_loss(s_cpu, batch, t_cpu)
+    loss_g = distillation_loss(student, {k: v.to(dev) for k, v in batch.items()}, teacher)
+    assert abs(loss_c.item() - loss_g.item()) / loss_c.item() < 0.05, (loss_c.item(), loss_g.item())
+    losses = []
+    for _ in range(8):
+        l = distillation_loss(student, {k: v.to(dev) for k, v in batch.items()}, teacher)
+        l.backward()
+        eng.step(2e-3, 1)
+        losses.append(l.item())
+    assert losses[-1] < losses[0], losses
