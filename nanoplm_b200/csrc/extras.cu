@@ -331,3 +331,56 @@ extern "C" int nplm_mhc_bwd(const void* X, const void* y, const float* R, const 
       reinterpret_cast<__nv_bfloat16*>(dX), reinterpret_cast<__nv_bfloat16*>(dy), dR, dalpha, dbeta, T, n, C);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------- device-side MLM masking
+// Counter-based (Philox4x32-10) masking of packed token ids, the semantics of the host collator
+// (src/nanoplm/pretraining/collator.py:333-382): a position is selected with probability p_sel
+// unless its id is special (bit set in special_mask) or it lies at / beyond n_real; selected
+// positions keep their id as label and become <mask> with probability p_mask, a random id from
+// pool[0..pool_n) with probability p_rand, or stay unchanged. The stream depends only on
+// (seed, step, position), so a batch is reproducible whatever the launch geometry.
+#include <curand_kernel.h>
+
+namespace nplm {
+
+__global__ void __launch_bounds__(256)
+mlm_mask_kernel(const long long* __restrict__ ids_in, long long* __restrict__ ids_out,
+                long long* __restrict__ labels, int n, int n_real, unsigned long long special_mask,
+                int mask_id, const int* __restrict__ pool, int pool_n, float p_sel, float p_mask,
+                float p_rand, unsigned long long seed, unsigned long long step) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    curandStatePhilox4_32_10_t st;
+    curand_init(seed, static_cast<unsigned long long>(i), step * 4ULL, &st);
+    const float4 u = curand_uniform4(&st);
+    const long long id = ids_in[i];
+    const bool special = id < 0 || id >= 64 || ((special_mask >> id) & 1ULL) || i >= n_real;
+    long long out = id, lab = -100;
+    if (!special && u.x <= p_sel) {        // curand_uniform is (0, 1]
+      lab = id;
+      if (u.y <= p_mask) {
+        out = mask_id;
+      } else if (u.y <= p_mask + p_rand) {
+        int k = static_cast<int>(u.z * pool_n);
+        if (k >= pool_n) k = pool_n - 1;
+        out = pool[k];
+      }
+    }
+    ids_out[i] = out;
+    labels[i] = lab;
+  }
+}
+
+}  // namespace nplm
+
+extern "C" int nplm_mlm_mask(const long long* ids_in, long long* ids_out, long long* labels, int n, int n_real,
+                             unsigned long long special_mask, int mask_id, const int* pool, int pool_n,
+                             float p_sel, float p_mask, float p_rand, unsigned long long seed,
+                             unsigned long long step, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (pool_n <= 0) return -3;
+  int blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  nplm::mlm_mask_kernel<<<blocks, 256, 0, st>>>(ids_in, ids_out, labels, n, n_real, special_mask, mask_id, pool,
+                                                pool_n, p_sel, p_mask, p_rand, seed, step);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -385,3 +385,23 @@ def mhc_bwd(X, y, R, alpha, beta, dXn, dh):
     check_rc(rc, "mhc_bwd")
     count_launch()
     return dX, dy, dR, dalpha, dbeta
+
+
+# --------------------------------------------------------------------------- device-side MLM masking
+def mlm_mask(ids: torch.Tensor, n_real: int, special_ids, mask_id: int, pool: torch.Tensor, p_sel: float,
+             p_mask: float, p_rand: float, seed: int, step: int):
+    """Philox masking of flat int64 ids on the device. Returns (corrupted ids, labels)."""
+    from ctypes import c_ulonglong
+    _chk(ids, torch.int64, "ids")
+    _chk(pool, torch.int32, "pool")
+    bits = 0
+    for s in special_ids:
+        bits |= 1 << int(s)
+    out, labels = torch.empty_like(ids), torch.empty_like(ids)
+    rc = lib("extras").nplm_mlm_mask(ptr(ids), ptr(out), ptr(labels), c_int(ids.numel()), c_int(int(n_real)),
+                                     c_ulonglong(bits), c_int(mask_id), ptr(pool), c_int(pool.numel()),
+                                     c_float(p_sel), c_float(p_mask), c_float(p_rand), c_ulonglong(seed),
+                                     c_ulonglong(step), stream_ptr())
+    check_rc(rc, "mlm_mask")
+    count_launch()
+    return out, labels

@@ -221,6 +221,14 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
     train_collator, eval_collator = build_collators(tokenizer, cfg, pt, manifest.max_seq_len,
                                                     cfg.seed + 1000 * rank)
     static_packing = pt.use_packing and pt.target_packed_rows is not None
+    # optional: corrupt the batch on the GPU (Philox, keyed by seed / rank / micro-step) instead of
+    # in the collator workers; the collator then only packs
+    device_masking = bool(cfg.device_masking) and device.type == "cuda" and static_packing
+    if device_masking:
+        train_collator.masker.mlm_probability = 0.0
+        mask_pool = torch.tensor(train_collator.masker.allowed_random_token_ids.tolist(), dtype=torch.int32,
+                                 device=device)
+        mask_micro = 0
     train_sampler = ResumableDistributedSampler(len(train_ds), world, rank, True, cfg.seed)
     eval_sampler = ResumableDistributedSampler(len(val_ds), world, rank, False, cfg.seed)
     workers = get_num_workers(cfg.num_workers, world)
@@ -290,6 +298,16 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
             tok += a
             raw_tok += b
             dev_batch = move_batch(host_batch, device)
+            if device_masking:
+                from nanoplm_b200.ops import kernels as K
+                mk = train_collator.masker
+                ids_m, lab_m = K.mlm_mask(dev_batch["input_ids"], a, tokenizer.all_special_ids, mk.mask_token_id,
+                                          mask_pool, float(cfg.mlm_probability), mk.p_mask, mk.p_rand,
+                                          cfg.seed * 1000003 + rank, mask_micro)
+                mask_micro += 1
+                dev_batch.update(input_ids=ids_m, labels=lab_m)
+                dev_batch.pop("masked_idx", None)
+                dev_batch.pop("masked_labels", None)
             out = model(**model_inputs(dev_batch))
             loss = out["loss"]
             loss.backward()

@@ -173,3 +173,28 @@ def test_distillation_step_gpu(cuda_status):
         eng.step(2e-3, 1)
         losses.append(l.item())
     assert losses[-1] < losses[0], losses
+
+
+def test_device_mlm_masking_statistics_and_determinism(cuda_status):
+    from nanoplm_b200.ops import kernels as K
+    n, n_real = 400_000, 390_000
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(4, 24, (n,), generator=g)
+    ids[::50] = 1                                           # </s> every 50 tokens
+    ids = ids.cuda()
+    pool = torch.arange(4, 32, dtype=torch.int32, device="cuda")
+    out, lab = K.mlm_mask(ids, n_real, [0, 1, 2, 3], 3, pool, 0.3, 0.8, 0.1, seed=7, step=5)
+    out2, lab2 = K.mlm_mask(ids, n_real, [0, 1, 2, 3], 3, pool, 0.3, 0.8, 0.1, seed=7, step=5)
+    assert torch.equal(out, out2) and torch.equal(lab, lab2)                 # counter-based: reproducible
+    out3, _ = K.mlm_mask(ids, n_real, [0, 1, 2, 3], 3, pool, 0.3, 0.8, 0.1, seed=7, step=6)
+    assert not torch.equal(out, out3)
+    sel = lab != -100
+    assert (lab[sel] == ids[sel]).all() and (out[~sel] == ids[~sel]).all()
+    assert not sel[ids == 1].any() and not sel[n_real:].any()               # specials and padding untouched
+    eligible = ((ids != 1) & (torch.arange(n, device="cuda") < n_real)).sum().item()
+    frac = sel.sum().item() / eligible
+    assert abs(frac - 0.3) < 0.01
+    masked = (out[sel] == 3).float().mean().item()
+    changed = ((out[sel] != 3) & (out[sel] != ids[sel])).float().mean().item()
+    assert abs(masked - 0.8) < 0.01 and 0.08 < changed < 0.11
+    assert out[sel].min().item() >= 3
