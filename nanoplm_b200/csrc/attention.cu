@@ -20,6 +20,8 @@
 // All operand tiles are [128 rows][64 bf16] = [128][128 B] with the 128-byte swizzle, loaded by
 // one TMA box each; the same tile serves as a K-major operand (contraction over head_dim) and
 // as an MN-major operand (contraction over tokens).
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace nplm {
@@ -190,17 +192,30 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaFwdArgs args) {
     tc_fence_after();
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
 
-    // pass 1: row maximum over the valid keys of this tile
+    // pass 1: row maximum over the valid keys of this tile. A 32-column chunk that no row of this
+    // warp can see is skipped by the whole warp (tcgen05.ld is warp-aligned, so the decision is
+    // taken with a warp vote); a chunk that lies completely inside the row's key range takes the
+    // compare-free path.
     float tmax = -1e30f;
 #pragma unroll 1
     for (int c = 0; c < FA_T; c += 32) {
+      const int c_lo = kv0 + c, c_hi = c_lo + 32;
+      const bool none = c_hi <= lo || c_lo >= hi;
+      if (__all_sync(0xffffffffu, none)) continue;
       uint32_t r[32];
       tmem_ld32(tS + lane_addr + c, r);
       tmem_ld_wait();
+      if (!none) {
+        if (c_lo >= lo && c_hi <= hi) {
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const int col = kv0 + c + e;
-        if (col >= lo && col < hi) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+          for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int col = c_lo + e;
+            if (col >= lo && col < hi) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+          }
+        }
       }
     }
     const float m_new = fmaxf(m_run, tmax);
@@ -210,18 +225,39 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaFwdArgs args) {
     // pass 2: probabilities -> bf16 -> swizzled shared memory (A operand of P V)
 #pragma unroll 1
     for (int c = 0; c < FA_T; c += 32) {
-      uint32_t r[32];
-      tmem_ld32(tS + lane_addr + c, r);
-      tmem_ld_wait();
+      const int c_lo = kv0 + c, c_hi = c_lo + 32;
+      const bool none = c_hi <= lo || c_lo >= hi;
+      const bool skip = __all_sync(0xffffffffu, none);
       uint32_t packed[16];
+      if (!skip) {
+        uint32_t r[32];
+        tmem_ld32(tS + lane_addr + c, r);
+        tmem_ld_wait();
+        if (none) {
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        const int col = kv0 + c + e;
-        float p0 = 0.f, p1 = 0.f;
-        if (col >= lo && col < hi) p0 = exp2f(fmaf(__uint_as_float(r[e]), sl2, -moff));
-        if (col + 1 >= lo && col + 1 < hi) p1 = exp2f(fmaf(__uint_as_float(r[e + 1]), sl2, -moff));
-        psum += p0 + p1;
-        packed[e >> 1] = pack_bf16x2(p0, p1);
+          for (int e = 0; e < 16; ++e) packed[e] = 0u;
+        } else if (c_lo >= lo && c_hi <= hi) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(r[e]), sl2, -moff));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[e + 1]), sl2, -moff));
+            psum += p0 + p1;
+            packed[e >> 1] = pack_bf16x2(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const int col = c_lo + e;
+            float p0 = 0.f, p1 = 0.f;
+            if (col >= lo && col < hi) p0 = exp2f(fmaf(__uint_as_float(r[e]), sl2, -moff));
+            if (col + 1 >= lo && col + 1 < hi) p1 = exp2f(fmaf(__uint_as_float(r[e + 1]), sl2, -moff));
+            psum += p0 + p1;
+            packed[e >> 1] = pack_bf16x2(p0, p1);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) packed[e] = 0u;
       }
       uint8_t* blk = sP + (c >> 6) * FA_TILE_BYTES;
       const int chunk0 = ((c >> 5) & 1) * 4;
@@ -344,6 +380,12 @@ struct FaBwdArgs {
   int T, H, window;
   float scale;
   int* status;
+  // optional: q / k were rotated (RoPE) before the forward pass; when set, dQ and dK are
+  // rotated back so the caller receives gradients of the un-rotated projections
+  const int* rope_pos;
+  const float* rope_cos;   // [max_pos][32]
+  const float* rope_sin;
+  int chunk_skip;          // 1: warp-voted skipping of 32-column chunks nobody attends to
 };
 
 // smem: K, V, Q[2], dO[2] (16 KB each) + P^T (32 KB) + dS^T (32 KB) + lse/delta (2*2*128 fp32)
@@ -500,30 +542,46 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     }
     tc_fence_after();
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    // this thread: key row krow_local, query columns [half*64, half*64+64)
+    // this thread: key row krow_local, query columns [half*64, half*64+64). Chunks of 32 query
+    // columns that no key row of the warp attends to are skipped by a warp vote (zeros are written
+    // so the MMAs see an empty block); chunks fully inside the row's range skip the compares.
 #pragma unroll 1
     for (int c = 0; c < 64; c += 32) {
       const int cbase = half * 64 + c;
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tS + lane_addr + cbase, rs);
-      tmem_ld32(tdP + lane_addr + cbase, rp);
-      tmem_ld_wait();
+      const int c_lo = q0 + cbase, c_hi = c_lo + 32;
+      const bool none = c_hi <= lo || c_lo >= hi;
+      const bool skip = args.chunk_skip && __all_sync(0xffffffffu, none);
       uint32_t pk[16], dk[16];
+      if (!skip) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + lane_addr + cbase, rs);
+        tmem_ld32(tdP + lane_addr + cbase, rp);
+        tmem_ld_wait();
+        if (none) {
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float p[2], ds[2];
+          for (int e = 0; e < 16; ++e) pk[e] = dk[e] = 0u;
+        } else {
+          const bool all_in = c_lo >= lo && c_hi <= hi;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int qc = cbase + e + u;
-          const int q = q0 + qc;
-          float pv = 0.f;
-          if (q >= lo && q < hi)
-            pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -s_lse[buf * 128 + qc]));
-          p[u] = pv;
-          ds[u] = pv * (__uint_as_float(rp[e + u]) - s_delta[buf * 128 + qc]);
+          for (int e = 0; e < 32; e += 2) {
+            float p[2], ds[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int qc = cbase + e + u;
+              const int q = q0 + qc;
+              float pv = 0.f;
+              if (all_in || (q >= lo && q < hi))
+                pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -s_lse[buf * 128 + qc]));
+              p[u] = pv;
+              ds[u] = pv * (__uint_as_float(rp[e + u]) - s_delta[buf * 128 + qc]);
+            }
+            pk[e >> 1] = pack_bf16x2(p[0], p[1]);
+            dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
+          }
         }
-        pk[e >> 1] = pack_bf16x2(p[0], p[1]);
-        dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) pk[e] = dk[e] = 0u;
       }
       const int chunk0 = (c >> 5) * 4;
 #pragma unroll
@@ -600,33 +658,48 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
 
   if (alive) {
     // tcgen05.ld is warp-aligned: every lane of the warp executes it, rows past T only skip the
-    // global stores.
+    // global stores. Warps 0-3 (half 0) write dK, warps 4-7 (half 1) write dV; each thread owns
+    // all 64 channels of its key row, which is what the inverse rotation of dK needs.
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    uint32_t rk[32], rv[32];
+    float g[FA_D];
     if (n_q > 0) {
-      tmem_ld32(tdK + lane_addr + half * 32, rk);
-      tmem_ld32(tdV + lane_addr + half * 32, rv);
-      tmem_ld_wait();
+      const uint32_t src = (half == 0 ? tdK : tdV) + lane_addr;
+#pragma unroll
+      for (int c = 0; c < FA_D; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(src + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) g[c + e] = __uint_as_float(r[e]);
+      }
     } else {
 #pragma unroll
-      for (int e = 0; e < 32; ++e) rk[e] = rv[e] = 0u;
+      for (int e = 0; e < FA_D; ++e) g[e] = 0.f;
     }
     if (krow_ok) {
-      __nv_bfloat16* dk_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 1) * HD + h * FA_D + half * 32;
-      __nv_bfloat16* dv_dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 2) * HD + h * FA_D + half * 32;
+      if (half == 0) {
 #pragma unroll
-      for (int e = 0; e < 32; e += 8) {
-        uint4 uk, uv;
-        uint32_t* pk = reinterpret_cast<uint32_t*>(&uk);
-        uint32_t* pv = reinterpret_cast<uint32_t*>(&uv);
+        for (int e = 0; e < FA_D; ++e) g[e] *= args.scale;
+        if (args.rope_pos != nullptr) {
+          const int pos = args.rope_pos[krow];
+          const float* cp = args.rope_cos + static_cast<size_t>(pos) * 32;
+          const float* sp = args.rope_sin + static_cast<size_t>(pos) * 32;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          pk[q] = pack_bf16x2(__uint_as_float(rk[e + 2 * q]) * args.scale,
-                              __uint_as_float(rk[e + 2 * q + 1]) * args.scale);
-          pv[q] = pack_bf16x2(__uint_as_float(rv[e + 2 * q]), __uint_as_float(rv[e + 2 * q + 1]));
+          for (int e = 0; e < 32; ++e) {
+            const float c = cp[e], sn = sp[e], a = g[e], b = g[e + 32];
+            g[e] = a * c + b * sn;
+            g[e + 32] = b * c - a * sn;
+          }
         }
-        *reinterpret_cast<uint4*>(dk_dst + e) = uk;
-        *reinterpret_cast<uint4*>(dv_dst + e) = uv;
+      }
+      __nv_bfloat16* dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 1 + half) * HD + h * FA_D;
+#pragma unroll
+      for (int e = 0; e < FA_D; e += 8) {
+        uint4 u;
+        uint32_t* pk = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) pk[q] = pack_bf16x2(g[e + 2 * q], g[e + 2 * q + 1]);
+        *reinterpret_cast<uint4*>(dst + e) = u;
       }
     }
   }
@@ -640,21 +713,42 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
   }
 }
 
-// dq (fp32 accumulator) -> bf16 into the q part of dqkv[T][3][H][64]
+// dq (fp32 accumulator) -> bf16 into the q part of dqkv[T][3][H][64]; with rope_pos the gradient is
+// rotated back first. One thread handles channels [8v, 8v+8) and [32+8v, 32+8v+8) of one head.
 __global__ void __launch_bounds__(256)
-fa_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int T,
-                   int HD) {
-  const int vec = HD >> 3;
-  const long long total = static_cast<long long>(T) * vec;
+fa_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int T, int H,
+                   const int* __restrict__ rope_pos, const float* __restrict__ rope_cos,
+                   const float* __restrict__ rope_sin) {
+  const int HD = H * FA_D;
+  const long long total = static_cast<long long>(T) * H * 4;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(i / vec);
-    const int c = static_cast<int>(i % vec) * 8;
-    const float4 a = *reinterpret_cast<const float4*>(dq_acc + static_cast<size_t>(t) * HD + c);
-    const float4 b = *reinterpret_cast<const float4*>(dq_acc + static_cast<size_t>(t) * HD + c + 4);
-    uint4 u = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
-                         pack_bf16x2(b.z, b.w));
-    *reinterpret_cast<uint4*>(dqkv + static_cast<size_t>(t) * 3 * HD + c) = u;
+    const int v = static_cast<int>(i & 3);
+    const long long th = i >> 2;
+    const int h = static_cast<int>(th % H);
+    const int t = static_cast<int>(th / H);
+    const float* src = dq_acc + static_cast<size_t>(t) * HD + h * FA_D + v * 8;
+    float a[8], b[8];
+    *reinterpret_cast<float4*>(a) = *reinterpret_cast<const float4*>(src);
+    *reinterpret_cast<float4*>(a + 4) = *reinterpret_cast<const float4*>(src + 4);
+    *reinterpret_cast<float4*>(b) = *reinterpret_cast<const float4*>(src + 32);
+    *reinterpret_cast<float4*>(b + 4) = *reinterpret_cast<const float4*>(src + 36);
+    if (rope_pos != nullptr) {
+      const int pos = rope_pos[t];
+      const float* cp = rope_cos + static_cast<size_t>(pos) * 32 + v * 8;
+      const float* sp = rope_sin + static_cast<size_t>(pos) * 32 + v * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = cp[e], sn = sp[e], x1 = a[e], x2 = b[e];
+        a[e] = x1 * c + x2 * sn;
+        b[e] = x2 * c - x1 * sn;
+      }
+    }
+    __nv_bfloat16* dst = dqkv + static_cast<size_t>(t) * 3 * HD + h * FA_D + v * 8;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]),
+                                                pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+    *reinterpret_cast<uint4*>(dst + 32) = make_uint4(pack_bf16x2(b[0], b[1]), pack_bf16x2(b[2], b[3]),
+                                                     pack_bf16x2(b[4], b[5]), pack_bf16x2(b[6], b[7]));
   }
 }
 
@@ -732,10 +826,27 @@ extern "C" int nplm_fa_fwd(const void* qkv, void* out, float* lse, const int* se
 }
 
 // dq_acc: caller-provided fp32 scratch [T][H*D]; it is cleared here. delta: fp32 scratch [H][T].
+extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* dout, const float* lse,
+                                void* dqkv, float* dq_acc, float* delta, const int* seq_start,
+                                const int* seq_end, int T, int H, int D, int window, float scale,
+                                const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                                int* status, cudaStream_t st);
+
 extern "C" int nplm_fa_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
                            void* dqkv, float* dq_acc, float* delta, const int* seq_start,
                            const int* seq_end, int T, int H, int D, int window, float scale,
                            int* status, cudaStream_t st) {
+  return nplm_fa_bwd_rope(qkv, out, dout, lse, dqkv, dq_acc, delta, seq_start, seq_end, T, H, D, window,
+                          scale, nullptr, nullptr, nullptr, status, st);
+}
+
+// Same, for q / k that were rotated before the forward pass (rope_* may be null): dQ and dK are
+// returned as gradients of the un-rotated projections.
+extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* dout, const float* lse,
+                                void* dqkv, float* dq_acc, float* delta, const int* seq_start,
+                                const int* seq_end, int T, int H, int D, int window, float scale,
+                                const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                                int* status, cudaStream_t st) {
   if (T <= 0) return 0;
   if (D != FA_D) return -3;
   CUtensorMap tmQKV, tmDO;
@@ -771,14 +882,25 @@ extern "C" int nplm_fa_bwd(const void* qkv, const void* out, const void* dout, c
   a.window = window;
   a.scale = scale;
   a.status = status;
+  a.rope_pos = rope_pos;
+  a.rope_cos = rope_cos;
+  a.rope_sin = rope_sin;
+  {
+    static int chunk_skip = -1;
+    if (chunk_skip < 0) {
+      const char* e = getenv("NPLM_FA_BWD_CHUNK_SKIP");
+      chunk_skip = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    a.chunk_skip = chunk_skip;
+  }
   dim3 grid((T + FA_T - 1) / FA_T, H);
   fa_bwd_kernel<<<grid, 256, FA_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   {
-    const long long total = static_cast<long long>(T) * (HD / 8);
+    const long long total = static_cast<long long>(T) * H * 4;
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     fa_dq_store_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
-        dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), T, HD);
+        dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), T, H, rope_pos, rope_cos, rope_sin);
   }
   return static_cast<int>(cudaGetLastError());
 }

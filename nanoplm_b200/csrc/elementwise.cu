@@ -648,7 +648,7 @@ extern "C" int nplm_norm_bwd(const void* dy, const void* x, const int* ids, cons
   if (T <= 0) return 0;
   if (C % 8) return -3;
   int blocks = (T + 7) / 8;
-  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks > 148 * 2) blocks = 148 * 2;   // more blocks only add contention on the dw atomics
 #define CALL(N_)                                                                              \
   norm_bwd_kernel<N_><<<blocks, 256, C * sizeof(float), st>>>(                                \
       reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),  \

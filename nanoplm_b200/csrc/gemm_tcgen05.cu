@@ -32,6 +32,8 @@ enum : int {
   EPI_STORE_F32 = 4,   // C(fp32) = acc
   EPI_SWIGLU = 5,      // B tile = [value rows | gate rows]; C(bf16, N/2 wide) = silu(gate)*value,
                        // pre-activations (bf16, N wide) written to R
+  EPI_ROPE = 6,        // C(bf16) = acc with rotary embedding applied to every 64-wide head whose
+                       // first column is < rope_cols (the q and k parts of a fused QKV projection)
 };
 
 template <int BN>
@@ -54,6 +56,11 @@ struct GemmArgs {
   int splits;
   int swiglu_half;  // EPI_SWIGLU: row offset of the gate half inside B (= N/2)
   int* status;
+  // EPI_ROPE: position of every output row, cos / sin tables [max_pos][32] (head_dim 64)
+  const int* rope_pos;
+  const float* rope_cos;
+  const float* rope_sin;
+  int rope_cols;
 };
 
 // Writes 32 rows x 64 bf16 columns held by one warp (lane = row, packed[0..31] = the 64 values of
@@ -406,6 +413,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             } else {
               if (active) {
+                if constexpr (EPI == EPI_ROPE) {
+                  if (x < args.rope_cols) {
+                    // this thread holds one whole head (64 channels) of its row: rotate-half RoPE
+                    const int rr = y0 + lane;
+                    const int pos = rr < M ? args.rope_pos[rr] : 0;
+                    const float4* cp = reinterpret_cast<const float4*>(args.rope_cos + static_cast<size_t>(pos) * 32);
+                    const float4* sp = reinterpret_cast<const float4*>(args.rope_sin + static_cast<size_t>(pos) * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                      const float4 c4 = cp[q4], s4 = sp[q4];
+                      const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                      for (int u = 0; u < 4; ++u) {
+                        const int e = q4 * 4 + u;
+                        const float a = f[e], b = f[e + 32];
+                        f[e] = a * cc[u] - b * ss[u];
+                        f[e + 32] = b * cc[u] + a * ss[u];
+                      }
+                    }
+                  }
+                }
 #pragma unroll
                 for (int e = 0; e < 32; ++e) packed[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
                 stage_store_bf16(stage, stage_toggle, &tmC, packed, x, y0, lane);
@@ -633,10 +661,14 @@ static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas,
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch(const GemmMaps& maps, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
-  if constexpr (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_GELU || EPI == EPI_SWIGLU) {
-    if (maps.tma_epi) return launch_impl<BN, A_MN, B_MN, EPI, true>(maps, args, max_ctas, stream);
+  if constexpr (EPI == EPI_ROPE) {
+    return launch_impl<BN, A_MN, B_MN, EPI, true>(maps, args, max_ctas, stream);
+  } else {
+    if constexpr (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_GELU || EPI == EPI_SWIGLU) {
+      if (maps.tma_epi) return launch_impl<BN, A_MN, B_MN, EPI, true>(maps, args, max_ctas, stream);
+    }
+    return launch_impl<BN, A_MN, B_MN, EPI, false>(maps, args, max_ctas, stream);
   }
-  return launch_impl<BN, A_MN, B_MN, EPI, false>(maps, args, max_ctas, stream);
 }
 
 }  // namespace nplm
@@ -650,7 +682,8 @@ using namespace nplm;
 extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
                               int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn,
                               int epi, int splits, int bn, int max_ctas, int direct_epilogue,
-                              int* status, cudaStream_t stream) {
+                              const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                              int rope_cols, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))
@@ -661,6 +694,9 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
   if ((epi == EPI_ATOMIC_F32 || epi == EPI_STORE_F32) ? (N % 4 || ldc % 4) : (N % 8 || ldc % 8))
     return -5;
   if (bn != 128 && bn != 256) return -6;
+  if (epi == EPI_ROPE && (a_mn || b_mn || direct_epilogue || rope_pos == nullptr || rope_cos == nullptr ||
+                          rope_sin == nullptr || (rope_cols % 64) || (N % 64)))
+    return -7;
   const int num_kb = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;
   if (splits > num_kb) splits = num_kb;
@@ -684,7 +720,7 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
   if (rc) return rc;
   // staged (TMA store) epilogue for the bf16 outputs; maps C / R describe [32 rows][64 cols] boxes
   maps.tma_epi = !direct_epilogue &&
-                 (epi == EPI_STORE || epi == EPI_ADD || epi == EPI_GELU || epi == EPI_SWIGLU) &&
+                 (epi == EPI_STORE || epi == EPI_ADD || epi == EPI_GELU || epi == EPI_SWIGLU || epi == EPI_ROPE) &&
                  !(epi == EPI_ADD && (R == nullptr || (reinterpret_cast<uintptr_t>(R) & 15) || (ldr % 8)));
   maps.C = tmA;
   maps.R = tmA;
@@ -710,6 +746,10 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
   args.splits = splits;
   args.swiglu_half = N / 2;
   args.status = status;
+  args.rope_pos = rope_pos;
+  args.rope_cos = rope_cos;
+  args.rope_sin = rope_sin;
+  args.rope_cols = rope_cols;
 
 #define NPLM_DISPATCH_EPI(BN_, AMN_, BMN_)                                                   \
   switch (epi) {                                                                             \
@@ -731,6 +771,10 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
     if (a_mn || b_mn) return -7;
     if (bn == 256) return launch<256, false, false, EPI_SWIGLU>(maps, args, max_ctas, stream);
     return launch<128, false, false, EPI_SWIGLU>(maps, args, max_ctas, stream);
+  }
+  if (epi == EPI_ROPE) {
+    if (bn == 256) return launch<256, false, false, EPI_ROPE>(maps, args, max_ctas, stream);
+    return launch<128, false, false, EPI_ROPE>(maps, args, max_ctas, stream);
   }
   if (bn == 256) {
     if (!a_mn && !b_mn) { NPLM_DISPATCH_EPI(256, false, false) }

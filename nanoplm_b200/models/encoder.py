@@ -45,6 +45,10 @@ class Norm(nn.Module):
     def forward(self, x):
         return ops.norm(x, self.weight, self.eps, self.rms)
 
+    def with_residual(self, x):
+        """(norm(x), x): the second value is the skip connection of a pre-norm block."""
+        return ops.norm_residual(x, self.weight, self.eps, self.rms)
+
 
 class Embeddings(nn.Module):
     def __init__(self, cfg: ModelConfig):
@@ -65,10 +69,17 @@ class Attention(nn.Module):
         self.Wo = Linear(cfg.hidden_size, cfg.hidden_size, cfg.attention_bias)
 
     def forward(self, x, ctx: "BatchContext", window: int, rope: tuple, residual=None):
-        qkv = self.Wqkv(x)
-        qkv = ops.rope_qkv(qkv, ctx.position_ids, rope[0], rope[1], self.num_heads, self.head_dim)
-        y = ops.attention_varlen(qkv, ctx.seq_start, ctx.seq_end, self.num_heads, self.head_dim,
-                                 window, self.scale)
+        H, D = self.num_heads, self.head_dim
+        fused = (x.is_cuda and x.dtype == torch.bfloat16 and D == 64 and self.Wqkv.bias is None
+                 and x.dim() == 2 and self.Wqkv.in_features % 8 == 0)
+        if fused:   # RoPE in the QKV GEMM epilogue, its transpose inside the attention backward
+            qkv = ops.linear_rope(x, self.Wqkv.weight, ctx.position_ids, rope[0], rope[1], 2 * H * D)
+            y = ops.attention_varlen(qkv, ctx.seq_start, ctx.seq_end, H, D, window, self.scale,
+                                     rope=(ctx.position_ids, rope[0], rope[1]))
+        else:
+            qkv = self.Wqkv(x)
+            qkv = ops.rope_qkv(qkv, ctx.position_ids, rope[0], rope[1], H, D)
+            y = ops.attention_varlen(qkv, ctx.seq_start, ctx.seq_end, H, D, window, self.scale)
         return self.Wo(y, residual=residual)
 
 
@@ -125,8 +136,9 @@ class EncoderLayer(nn.Module):
             self.mhc_attn = HyperConnection(cfg.hidden_size, cfg.mhc_streams, cfg.mhc_sinkhorn_iters, cfg.norm_eps)
             self.mhc_mlp = HyperConnection(cfg.hidden_size, cfg.mhc_streams, cfg.mhc_sinkhorn_iters, cfg.norm_eps)
 
-    def _attn_branch(self, h, ctx, window, rope, residual):
-        h = self.attn_norm(h)
+    def _attn_branch(self, h, ctx, window, rope, residual, normed: bool = False):
+        if not normed:
+            h = self.attn_norm(h)
         if self.conv is not None:
             h = h + self.conv(h, ctx)
         return self.attn(h, ctx, window, rope, residual=residual)
@@ -134,12 +146,17 @@ class EncoderLayer(nn.Module):
     def forward(self, x, ctx: BatchContext, window: int, rope: tuple):
         aux = None
         if self.mhc_attn is None:
-            x = self._attn_branch(x, ctx, window, rope, residual=x)
+            if isinstance(self.attn_norm, Norm):
+                h, skip = self.attn_norm.with_residual(x)
+                x = self._attn_branch(h, ctx, window, rope, residual=skip, normed=True)
+            else:
+                x = self._attn_branch(x, ctx, window, rope, residual=x)
             if self.is_moe:
                 y, aux = self.mlp(self.mlp_norm(x))
                 x = x + y
             else:
-                x = self.mlp(self.mlp_norm(x), residual=x)
+                h, skip = self.mlp_norm.with_residual(x)
+                x = self.mlp(h, residual=skip)
             return x, aux
         # hyper-connections: x is (T, n, C)
         h, state = self.mhc_attn.read(x)

@@ -65,12 +65,14 @@ def _param_grad(p, g32: torch.Tensor):
 # ------------------------------------------------------------------------------------- linear
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias, residual, act):
+    def forward(ctx, x, w, bias, residual, act, rope=None):
         x2 = x.reshape(-1, x.shape[-1])
         if not (x2.stride(1) == 1 and x2.stride(0) % 8 == 0):
             x2 = x2.contiguous()
         pre = None
-        if act == "gelu":
+        if rope is not None:
+            y = K.gemm(x2, w, epi=K.EPI_ROPE, rope=rope)
+        elif act == "gelu":
             pre = torch.empty((x2.shape[0], w.shape[0]), dtype=BF, device=x.device)
             y = K.gemm(x2, w, epi=K.EPI_GELU, aux=pre)
         elif act == "swiglu":
@@ -110,7 +112,14 @@ class _LinearFn(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _param_grad(ctx.bias_ref, dpre.float().sum(0))
         dres = dy if ctx.has_res else None
-        return dx, dw, db, dres, None
+        return dx, dw, db, dres, None, None
+
+
+def linear_rope(x, w, pos, cos, sin, rope_cols: int):
+    """QKV projection with the rotary embedding of q and k applied in the GEMM epilogue (CUDA,
+    head_dim 64). The result equals rope_qkv(linear(x, w)); its gradient w.r.t. the un-rotated
+    projection is obtained by passing rope=(pos, cos, sin) to attention_varlen."""
+    return _LinearFn.apply(x, w, None, None, None, (pos, cos, sin, rope_cols))
 
 
 def linear(x, w, bias=None, residual=None, act: str | None = None):
@@ -200,6 +209,42 @@ class _NormFn(torch.autograd.Function):
         return _as_shape(dx, ctx.shape), dw, None, None
 
 
+class _NormResFn(torch.autograd.Function):
+    """norm(x) plus x itself as a second output. In a pre-norm residual block both the branch and
+    the skip connection start at x; routing the skip through this function lets the backward add
+    the skip gradient inside the norm-backward kernel instead of a separate elementwise pass."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps, rms):
+        x2 = x if x.is_contiguous() else x.contiguous()
+        y, mean, rstd = K.norm_fwd(x2, w, eps, rms=rms)
+        ctx.save_for_backward(x2, w, mean, rstd)
+        ctx.rms = rms
+        return y, x2.view_as(x2)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x2, w, mean, rstd = ctx.saved_tensors
+        dw = None
+        if w is not None and ctx.needs_input_grad[1]:
+            dw = w.main_grad if _has_main_grad(w) else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        if dy is None:
+            return dres, None, None, None
+        if dres is not None and not dres.is_contiguous():
+            dres = dres.contiguous()
+        dx = K.norm_bwd(dy, x2, w, mean, rstd, rms=ctx.rms, dres=dres, dw=dw)
+        if dw is not None:
+            dw = None if _has_main_grad(w) else dw.to(w.dtype)
+        return dx, dw, None, None
+
+
+def norm_residual(x, w, eps: float = 1e-5, rms: bool = False):
+    """Returns (norm(x), x) — see _NormResFn. x is a flat [T, C] activation."""
+    if x.is_cuda and x.dtype == BF and x.dim() == 2 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096:
+        return _NormResFn.apply(x, w, eps, rms)
+    return norm(x, w, eps, rms), x
+
+
 def norm(x, w, eps: float = 1e-5, rms: bool = False):
     """LayerNorm without bias (reference encoder norms) or RMSNorm (T5LayerNorm) over the last dim."""
     if x.is_cuda and x.dtype == BF and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096:
@@ -287,18 +332,19 @@ def rope_qkv(qkv, pos, cos, sin, H: int, D: int):
 # ------------------------------------------------------------------------------------- attention
 class _AttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, seq_start, seq_end, H, D, window, scale):
+    def forward(ctx, qkv, seq_start, seq_end, H, D, window, scale, rope):
         out, lse = K.fa_fwd(qkv, seq_start, seq_end, H, D, window, scale)
         ctx.save_for_backward(qkv, out, lse, seq_start, seq_end)
         ctx.cfg = (H, D, window, scale)
+        ctx.rope = rope
         return out
 
     @staticmethod
     def backward(ctx, dout):
         qkv, out, lse, ss, se = ctx.saved_tensors
         H, D, window, scale = ctx.cfg
-        dqkv = K.fa_bwd(qkv, out, dout.contiguous(), lse, ss, se, H, D, window, scale)
-        return dqkv, None, None, None, None, None, None
+        dqkv = K.fa_bwd(qkv, out, dout.contiguous(), lse, ss, se, H, D, window, scale, rope=ctx.rope)
+        return dqkv, None, None, None, None, None, None, None
 
 
 def seq_bounds(cu_seqlens: torch.Tensor, T: int):
@@ -316,10 +362,14 @@ def seq_bounds(cu_seqlens: torch.Tensor, T: int):
     return a.to(torch.int32), b.to(torch.int32)
 
 
-def attention_varlen(qkv, seq_start, seq_end, H: int, D: int, window: int, scale: float):
-    """Non-causal attention inside each packed sequence; window >= 0 limits |q - k| <= window."""
+def attention_varlen(qkv, seq_start, seq_end, H: int, D: int, window: int, scale: float, rope=None):
+    """Non-causal attention inside each packed sequence; window >= 0 limits |q - k| <= window.
+    rope=(pos, cos, sin) (CUDA only) declares that q / k were rotated by linear_rope: the backward
+    then returns the gradient of the un-rotated projection."""
     if qkv.is_cuda and qkv.dtype == BF and D == 64:
-        return _AttnFn.apply(qkv, seq_start, seq_end, H, D, window, scale)
+        return _AttnFn.apply(qkv, seq_start, seq_end, H, D, window, scale, rope)
+    if rope is not None:
+        raise ValueError("fused rope backward is only available on the CUDA kernels")
     T = qkv.shape[0]
     q, k, v = qkv.view(T, 3, H, D).unbind(1)
     pos = torch.arange(T, device=qkv.device)

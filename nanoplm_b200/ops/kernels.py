@@ -12,7 +12,7 @@ import torch
 from . import _lib
 from ._lib import check_rc, count_launch, lib, ptr, status_word, stream_ptr
 
-EPI_STORE, EPI_ADD, EPI_ATOMIC_F32, EPI_GELU, EPI_STORE_F32, EPI_SWIGLU = 0, 1, 2, 3, 4, 5
+EPI_STORE, EPI_ADD, EPI_ATOMIC_F32, EPI_GELU, EPI_STORE_F32, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4, 5, 6
 
 _BF16 = torch.bfloat16
 
@@ -35,7 +35,7 @@ def _rowmajor(t: torch.Tensor, name: str) -> int:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          epi: int = EPI_STORE, out: torch.Tensor | None = None, aux: torch.Tensor | None = None,
          splits: int = 1, bn: int | None = None, max_ctas: int = 0,
-         direct_epilogue: bool = False) -> torch.Tensor:
+         direct_epilogue: bool = False, rope: tuple | None = None) -> torch.Tensor:
     """C[M,N] (+)= op(A) op(B)^T on tcgen05 tensor cores.
 
     a: [M,K] (a_mn=False) or [K,M] (a_mn=True); b: [N,K] (b_mn=False) or [K,N] (b_mn=True).
@@ -43,6 +43,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     EPI_GELU (aux = optional pre-activation output) / EPI_STORE_F32 / EPI_SWIGLU (out is N/2 wide,
     aux = optional [M,N] pre-activation output). bf16 outputs leave through shared memory and
     TMA stores; direct_epilogue=True selects per-thread global stores instead.
+    EPI_ROPE: rope = (pos int32 [M], cos fp32 [P,32], sin fp32 [P,32], rope_cols): rotary embedding
+    (head_dim 64) on every 64-wide head that starts below column rope_cols.
     """
     _chk(a, _BF16, "a")
     _chk(b, _BF16, "b")
@@ -77,11 +79,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise ValueError("EPI_ADD needs the residual passed as aux")
     if bn is None:
         bn = 256 if (N >= 256 or epi == EPI_SWIGLU) else 128
+    r_pos = r_cos = r_sin = None
+    r_cols = 0
+    if epi == EPI_ROPE:
+        if rope is None:
+            raise ValueError("EPI_ROPE needs rope=(pos, cos, sin, rope_cols)")
+        r_pos, r_cos, r_sin, r_cols = rope
+        _chk(r_pos, torch.int32, "rope pos")
+        _chk(r_cos, torch.float32, "rope cos")
+        if r_pos.numel() != M or r_cos.shape[-1] != 32:
+            raise ValueError("rope tables must be [P, 32] and pos must have one entry per row")
     rc = lib("gemm_tcgen05").nplm_gemm_bf16(
         ptr(a), ptr(b), ptr(out), ptr(aux), c_int(M), c_int(N), c_int(K), c_int(lda), c_int(ldb),
         c_int(ldc), c_int(ldr), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi), c_int(splits),
-        c_int(bn), c_int(max_ctas), c_int(int(direct_epilogue)), ptr(status_word(a.device)),
-        stream_ptr())
+        c_int(bn), c_int(max_ctas), c_int(int(direct_epilogue)), ptr(r_pos), ptr(r_cos), ptr(r_sin),
+        c_int(int(r_cols)), ptr(status_word(a.device)), stream_ptr())
     check_rc(rc, "gemm_bf16")
     count_launch()
     return out
@@ -308,7 +320,10 @@ def fa_fwd(qkv, seq_start, seq_end, H, D, window, scale):
     return out, lse
 
 
-def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=None, delta=None):
+def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=None, delta=None,
+           rope: tuple | None = None):
+    """rope = (pos, cos, sin): q / k in qkv were rotated before the forward pass; dQ / dK are rotated
+    back inside the kernels."""
     T = qkv.shape[0]
     dqkv = torch.empty_like(qkv)
     if dq_acc is None:
@@ -317,10 +332,12 @@ def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=
         delta = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
     if not dout.is_contiguous():
         dout = dout.contiguous()
-    rc = lib("attention").nplm_fa_bwd(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
-                                      ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
-                                      c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
-                                      ptr(status_word(qkv.device)), stream_ptr())
+    r_pos, r_cos, r_sin = rope if rope is not None else (None, None, None)
+    rc = lib("attention").nplm_fa_bwd_rope(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
+                                           ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
+                                           c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                           ptr(r_pos), ptr(r_cos), ptr(r_sin),
+                                           ptr(status_word(qkv.device)), stream_ptr())
     check_rc(rc, "fa_bwd")
     count_launch(4)
     return dqkv

@@ -348,3 +348,32 @@ def test_attention_determinism_and_big(cuda_status):
     sub = qkv.view(T, 3, H, D)[:, :, :2].reshape(T, 3 * 2 * D).contiguous()
     ref = _attn_ref(sub.float(), cu, 2, D, -1, 0.125)
     _close(o1.view(T, H, D)[:, :2].reshape(T, 2 * D), ref, what="attn big")
+
+
+def test_gemm_rope_epilogue_and_attention_rope_backward(cuda_status):
+    """RoPE fused into the QKV GEMM epilogue and un-done inside the attention backward must equal
+    the separate rope kernel around the plain GEMM / attention."""
+    k = _k()
+    H, D, C = 4, 64, 256
+    lens = [50, 200, 6, 300, 77]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    pos = torch.cat([torch.arange(n) for n in lens]).to(torch.int32).cuda()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    fr = torch.outer(torch.arange(512, device="cuda").float(), inv)
+    cos, sin = fr.cos().contiguous(), fr.sin().contiguous()
+    x, w = _randn(T, C), _randn(3 * H * D, C, scale=0.1)
+    fused = k.gemm(x, w, epi=k.EPI_ROPE, rope=(pos, cos, sin, 2 * H * D))
+    ref = k.gemm(x, w)
+    k.rope_(ref, pos, cos, sin, H, D)
+    _close(fused, ref, what="gemm rope epilogue")
+    ss, se = k.seq_bounds(cu_t, T)
+    out, lse = k.fa_fwd(ref, ss, se, H, D, -1, 0.125)
+    dout = _randn(T, H * D)
+    d_plain = k.fa_bwd(ref, out, dout, lse, ss, se, H, D, -1, 0.125)
+    k.rope_(d_plain, pos, cos, sin, H, D, backward=True)
+    d_fused = k.fa_bwd(ref, out, dout, lse, ss, se, H, D, -1, 0.125, rope=(pos, cos, sin))
+    _close(d_fused, d_plain, rtol=3e-2, atol=3e-2, what="attention backward with fused inverse rope")
