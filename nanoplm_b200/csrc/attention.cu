@@ -20,8 +20,6 @@
 // All operand tiles are [128 rows][64 bf16] = [128][128 B] with the 128-byte swizzle, loaded by
 // one TMA box each; the same tile serves as a K-major operand (contraction over head_dim) and
 // as an MN-major operand (contraction over tokens).
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace nplm {
@@ -385,7 +383,6 @@ struct FaBwdArgs {
   const int* rope_pos;
   const float* rope_cos;   // [max_pos][32]
   const float* rope_sin;
-  int chunk_skip;          // 1: warp-voted skipping of 32-column chunks nobody attends to
 };
 
 // smem: K, V, Q[2], dO[2] (16 KB each) + P^T (32 KB) + dS^T (32 KB) + lse/delta (2*2*128 fp32)
@@ -542,46 +539,30 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     }
     tc_fence_after();
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    // this thread: key row krow_local, query columns [half*64, half*64+64). Chunks of 32 query
-    // columns that no key row of the warp attends to are skipped by a warp vote (zeros are written
-    // so the MMAs see an empty block); chunks fully inside the row's range skip the compares.
+    // this thread: key row krow_local, query columns [half*64, half*64+64)
 #pragma unroll 1
     for (int c = 0; c < 64; c += 32) {
       const int cbase = half * 64 + c;
-      const int c_lo = q0 + cbase, c_hi = c_lo + 32;
-      const bool none = c_hi <= lo || c_lo >= hi;
-      const bool skip = args.chunk_skip && __all_sync(0xffffffffu, none);
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS + lane_addr + cbase, rs);
+      tmem_ld32(tdP + lane_addr + cbase, rp);
+      tmem_ld_wait();
       uint32_t pk[16], dk[16];
-      if (!skip) {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tS + lane_addr + cbase, rs);
-        tmem_ld32(tdP + lane_addr + cbase, rp);
-        tmem_ld_wait();
-        if (none) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) pk[e] = dk[e] = 0u;
-        } else {
-          const bool all_in = c_lo >= lo && c_hi <= hi;
+      for (int e = 0; e < 32; e += 2) {
+        float p[2], ds[2];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float p[2], ds[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int qc = cbase + e + u;
-              const int q = q0 + qc;
-              float pv = 0.f;
-              if (all_in || (q >= lo && q < hi))
-                pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -s_lse[buf * 128 + qc]));
-              p[u] = pv;
-              ds[u] = pv * (__uint_as_float(rp[e + u]) - s_delta[buf * 128 + qc]);
-            }
-            pk[e >> 1] = pack_bf16x2(p[0], p[1]);
-            dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
-          }
+        for (int u = 0; u < 2; ++u) {
+          const int qc = cbase + e + u;
+          const int q = q0 + qc;
+          float pv = 0.f;
+          if (q >= lo && q < hi)
+            pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -s_lse[buf * 128 + qc]));
+          p[u] = pv;
+          ds[u] = pv * (__uint_as_float(rp[e + u]) - s_delta[buf * 128 + qc]);
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) pk[e] = dk[e] = 0u;
+        pk[e >> 1] = pack_bf16x2(p[0], p[1]);
+        dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
       }
       const int chunk0 = (c >> 5) * 4;
 #pragma unroll
@@ -682,13 +663,25 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
         for (int e = 0; e < FA_D; ++e) g[e] *= args.scale;
         if (args.rope_pos != nullptr) {
           const int pos = args.rope_pos[krow];
-          const float* cp = args.rope_cos + static_cast<size_t>(pos) * 32;
-          const float* sp = args.rope_sin + static_cast<size_t>(pos) * 32;
+          const float4* cp = reinterpret_cast<const float4*>(args.rope_cos + static_cast<size_t>(pos) * 32);
+          const float4* sp = reinterpret_cast<const float4*>(args.rope_sin + static_cast<size_t>(pos) * 32);
+          float4 c4[8], s4[8];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float c = cp[e], sn = sp[e], a = g[e], b = g[e + 32];
-            g[e] = a * c + b * sn;
-            g[e + 32] = b * c - a * sn;
+          for (int q = 0; q < 8; ++q) {   // 16 independent 16-byte loads, issued back to back
+            c4[q] = __ldg(cp + q);
+            s4[q] = __ldg(sp + q);
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float cc[4] = {c4[q].x, c4[q].y, c4[q].z, c4[q].w};
+            const float ss[4] = {s4[q].x, s4[q].y, s4[q].z, s4[q].w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int e = q * 4 + u;
+              const float a = g[e], b = g[e + 32];
+              g[e] = a * cc[u] + b * ss[u];
+              g[e + 32] = b * cc[u] - a * ss[u];
+            }
           }
         }
       }
@@ -885,14 +878,6 @@ extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* do
   a.rope_pos = rope_pos;
   a.rope_cos = rope_cos;
   a.rope_sin = rope_sin;
-  {
-    static int chunk_skip = -1;
-    if (chunk_skip < 0) {
-      const char* e = getenv("NPLM_FA_BWD_CHUNK_SKIP");
-      chunk_skip = (e != nullptr && e[0] == '0') ? 0 : 1;
-    }
-    a.chunk_skip = chunk_skip;
-  }
   dim3 grid((T + FA_T - 1) / FA_T, H);
   fa_bwd_kernel<<<grid, 256, FA_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   {

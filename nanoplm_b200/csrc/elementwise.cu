@@ -9,6 +9,8 @@
 //
 // Activations are bf16, statistics and gradients of parameters are fp32. All kernels are
 // plain grid-stride / warp-per-row kernels: none of them waits on anything.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace nplm {
@@ -191,6 +193,118 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     }
     __syncthreads();
     for (int i = threadIdx.x; i < C; i += blockDim.x) atomicAdd(&dw[i], sm_dw[i]);
+  }
+}
+
+// Norm backward with a thread block per group of ROWS rows (C/8 threads, each owning 8 channels
+// of every row of the group). All loads of a group are issued before the first reduction, so a
+// block keeps ROWS * 3 * C * 2 bytes in flight; the row reductions of the whole group share one
+// __syncthreads. Registers per thread stay low enough for several blocks per SM.
+//   ids == nullptr : dx[row] = [dres[row] +] norm-backward(dy[row]),  dw += sum dy * xhat
+//   ids != nullptr : embedding mode. x rows are table[ids[row]]; the row gradients are summed per
+//                    vocabulary entry in shared memory (each thread owns its channels, so no
+//                    atomics inside the block) and flushed to dtable with one atomic per element.
+template <int ROWS>
+__global__ void __launch_bounds__(256)
+norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
+                     const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                     const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                     float* __restrict__ dw, float* __restrict__ dtable, int T, int C, int V, int rms) {
+  extern __shared__ float s_table[];   // [V][C] in embedding mode
+  __shared__ float red[2][ROWS][8][2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int i = tid * 8;
+  const bool on = i < C;
+  if (ids != nullptr) {
+    for (int k = tid; k < V * C; k += blockDim.x) s_table[k] = 0.f;
+    __syncthreads();
+  }
+  float wv[8], acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    wv[e] = 1.f;
+    acc[e] = 0.f;
+  }
+  if (on && w) load8(w + i, wv);
+  int buf = 0;
+  for (int row0 = blockIdx.x * ROWS; row0 < T; row0 += gridDim.x * ROWS, buf ^= 1) {
+    float xh[ROWS][8], g[ROWS][8];
+    float rstd[ROWS];
+    int id[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int row = row0 + r;
+      float sg = 0.f, sgx = 0.f;
+      rstd[r] = 0.f;
+      id[r] = 0;
+      if (row < T) {
+        const float mean = rms ? 0.f : mean_in[row];
+        rstd[r] = rstd_in[row];
+        if (ids != nullptr) id[r] = ids[row];
+        if (on) {
+          float xv[8], dv[8];
+          const __nv_bfloat16* src = ids ? x + static_cast<size_t>(id[r]) * C : x + static_cast<size_t>(row) * C;
+          load8(src + i, xv);
+          load8(dy + static_cast<size_t>(row) * C + i, dv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            xh[r][e] = (xv[e] - mean) * rstd[r];
+            g[r][e] = dv[e] * wv[e];
+            sg += g[r][e];
+            sgx += g[r][e] * xh[r][e];
+            acc[e] += dv[e] * xh[r][e];
+          }
+        }
+      }
+      sg = warp_sum(sg);
+      sgx = warp_sum(sgx);
+      if (lane == 0) {
+        red[buf][r][warp][0] = sg;
+        red[buf][r][warp][1] = sgx;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int row = row0 + r;
+      if (row < T && on) {
+        float tg = 0.f, tgx = 0.f;
+        for (int k = 0; k < nwarps; ++k) {
+          tg += red[buf][r][k][0];
+          tgx += red[buf][r][k][1];
+        }
+        tg = rms ? 0.f : tg / C;
+        tgx /= C;
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rstd[r] * (g[r][e] - tg - xh[r][e] * tgx);
+        if (ids != nullptr) {
+          float* dst = s_table + static_cast<size_t>(id[r]) * C + i;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dst[e] += o[e];
+        } else {
+          if (dres) {
+            float rr[8];
+            load8(dres + static_cast<size_t>(row) * C + i, rr);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] += rr[e];
+          }
+          store8(dx + static_cast<size_t>(row) * C + i, o);
+        }
+      }
+    }
+  }
+  if (dw && on) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&dw[i + e], acc[e]);
+  }
+  if (ids != nullptr) {
+    __syncthreads();
+    for (int k = tid; k < V * C; k += blockDim.x) {
+      const float v = s_table[k];
+      if (v != 0.f) atomicAdd(&dtable[k], v);
+    }
   }
 }
 
@@ -644,9 +758,33 @@ extern "C" int nplm_norm_fwd(const void* x, const int* ids, const void* w, void*
 
 extern "C" int nplm_norm_bwd(const void* dy, const void* x, const int* ids, const void* w,
                              const float* mean, const float* rstd, const void* dres, void* dx,
-                             float* dw, float* dtable, int T, int C, int rms, cudaStream_t st) {
+                             float* dw, float* dtable, int T, int C, int V, int rms, cudaStream_t st) {
   if (T <= 0) return 0;
   if (C % 8) return -3;
+  static int use_rows = -1;   // NPLM_NORM_BWD_ROWS=1 routes the dx path through the row-group kernel too
+  if (use_rows < 0) {
+    const char* e = getenv("NPLM_NORM_BWD_ROWS");
+    use_rows = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  if (C >= 256 && C <= 2048 && (ids == nullptr ? (use_rows && dx != nullptr) : (dtable != nullptr && V > 0))) {
+    // block-per-row-group variant: C/8 threads (rounded up to whole warps)
+    constexpr int ROWS = 4;
+    const int threads = ((C / 8) + 31) / 32 * 32;
+    const size_t smem = ids != nullptr ? static_cast<size_t>(V) * C * sizeof(float) : 0;
+    if (smem <= 200 * 1024) {
+      const int groups = (T + ROWS - 1) / ROWS;
+      int blocks = ids != nullptr ? 148 : 148 * 6;
+      if (blocks > groups) blocks = groups;
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(norm_bwd_rows_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+      norm_bwd_rows_kernel<ROWS><<<blocks, threads, smem, st>>>(
+          reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), ids,
+          reinterpret_cast<const __nv_bfloat16*>(w), mean, rstd, reinterpret_cast<const __nv_bfloat16*>(dres),
+          reinterpret_cast<__nv_bfloat16*>(dx), dw, dtable, T, C, V, rms);
+      return static_cast<int>(cudaGetLastError());
+    }
+  }
   int blocks = (T + 7) / 8;
   if (blocks > 148 * 2) blocks = 148 * 2;   // more blocks only add contention on the dw atomics
 #define CALL(N_)                                                                              \

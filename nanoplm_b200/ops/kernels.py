@@ -153,9 +153,10 @@ def norm_bwd(dy, x, w, mean, rstd, *, rms=False, dres=None, dw=None, ids=None, d
     if not dy2.is_contiguous():
         dy2 = dy2.contiguous()
     dx = None if ids is not None else torch.empty((T, C), dtype=_BF16, device=dy.device)
+    V = x.shape[0] if ids is not None else 0
     rc = lib("elementwise").nplm_norm_bwd(
         ptr(dy2), ptr(x), ptr(ids), ptr(w), ptr(mean), ptr(rstd), ptr(dres), ptr(dx), ptr(dw),
-        ptr(dtable), c_int(T), c_int(C), c_int(int(rms)), stream_ptr())
+        ptr(dtable), c_int(T), c_int(C), c_int(V), c_int(int(rms)), stream_ptr())
     check_rc(rc, "norm_bwd")
     count_launch()
     return dx
