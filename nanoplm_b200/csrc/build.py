@@ -25,8 +25,8 @@ SOURCES = [
     "attention.cu",
     "extras.cu",
     "comm.cu",
+    "moe.cu",
     "fp8.cu",
-    "noalloc.cu",
 ]
 
 NVCC_FLAGS = [

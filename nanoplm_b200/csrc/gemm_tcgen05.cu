@@ -61,6 +61,24 @@ struct GemmArgs {
   const float* rope_cos;
   const float* rope_sin;
   int rope_cols;
+  // Grouped (mixture-of-experts) forms, one launch for all groups:
+  //   group_mode 1: rows of A / C are partitioned into groups in units of 128-row tiles
+  //                 (tile_group[m_tile] = group, or -1 for an unused tile); group g multiplies by
+  //                 its own B, found b_group_rows * g rows further down the B tensor map.
+  //   group_mode 2: weight gradients. A and B are MN-major over a common row axis; group g
+  //                 contracts rows [group_off[g], group_off[g+1]) (multiples of 128) and adds the
+  //                 M x N result into C + g * c_group_stride.
+  int group_mode;
+  int groups;
+  const int* tile_group;
+  const int* group_off;
+  int b_group_rows;
+  long long c_group_stride;
+};
+
+struct WorkItem {
+  int m0, n0, kb0, kb1, b_row;
+  long long c_off;
 };
 
 // Writes 32 rows x 64 bf16 columns held by one warp (lane = row, packed[0..31] = the 64 values of
@@ -118,7 +136,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_kb = (K + BK - 1) / BK;
   const int splits = args.splits;
   const int kb_per = (num_kb + splits - 1) / splits;
-  const int total_work = num_m * num_n * splits;
+  const int total_work = (args.group_mode == 2 ? args.groups : splits) * num_m * num_n;
+
+  // work item -> tile coordinates and contraction range; false = nothing to do for this item
+  auto decode = [&](int w, WorkItem& it) -> bool {
+    it.b_row = 0;
+    it.c_off = 0;
+    if (args.group_mode == 2) {
+      const int per = num_m * num_n;
+      const int g = w / per, tile = w % per;
+      it.m0 = (tile / num_n) * BM;
+      it.n0 = (tile % num_n) * TILE_N;
+      it.kb0 = args.group_off[g] / BK;
+      it.kb1 = args.group_off[g + 1] / BK;
+      it.c_off = static_cast<long long>(g) * args.c_group_stride;
+      return it.kb0 < it.kb1;
+    }
+    const int split = w % splits, tile = w / splits;
+    it.m0 = (tile / num_n) * BM;
+    it.n0 = (tile % num_n) * TILE_N;
+    it.kb0 = split * kb_per;
+    it.kb1 = min(num_kb, it.kb0 + kb_per);
+    if (args.group_mode == 1) {
+      const int g = args.tile_group[it.m0 / BM];
+      if (g < 0) return false;
+      it.b_row = g * args.b_group_rows;
+    }
+    return it.kb0 < it.kb1;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -158,12 +203,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int split = w % splits;
-        const int tile = w / splits;
-        const int m0 = (tile / num_n) * BM;
-        const int n0 = (tile % num_n) * TILE_N;
-        const int kb0 = split * kb_per;
-        const int kb1 = min(num_kb, kb0 + kb_per);
+        WorkItem it;
+        if (!decode(w, it)) continue;
+        const int m0 = it.m0, n0 = it.n0, kb0 = it.kb0, kb1 = it.kb1;
+        const int brow = it.b_row;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicExch(args.status, ST_TIMEOUT_EMPTY);
@@ -184,14 +227,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if constexpr (EPI == EPI_SWIGLU) {
             // value rows then gate rows, both K-major
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
-            tma_load_2d(sb + (BN / 2) * 128, &tmB, &full_bar[stage], k0, args.swiglu_half + n0);
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, brow + n0);
+            tma_load_2d(sb + (BN / 2) * 128, &tmB, &full_bar[stage], k0, brow + args.swiglu_half + n0);
           } else if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, brow + n0);
           } else {
 #pragma unroll
             for (int g = 0; g < BN / 64; ++g)
-              tma_load_2d(sb + g * (BK * 128), &tmB, &full_bar[stage], n0 + g * 64, k0);
+              tma_load_2d(sb + g * (BK * 128), &tmB, &full_bar[stage], n0 + g * 64, brow + k0);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -210,10 +253,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int split = w % splits;
-        const int kb0 = split * kb_per;
-        const int kb1 = min(num_kb, kb0 + kb_per);
-        if (kb0 >= kb1) continue;
+        WorkItem it;
+        if (!decode(w, it)) continue;
+        const int kb0 = it.kb0, kb1 = it.kb1;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) {
           atomicExch(args.status, ST_TIMEOUT_TMEM_EMPTY);
           *abort_flag = 1;
@@ -261,13 +303,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int stage_toggle = 0;       // which of this warp's two staging buffers is next
     uint32_t res_phase = 0;     // parity bits of this warp's two residual barriers
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const int split = w % splits;
-      const int tile = w / splits;
-      const int m0 = (tile / num_n) * BM;
-      const int n0 = (tile % num_n) * TILE_N;
-      const int kb0 = split * kb_per;
-      const int kb1 = min(num_kb, kb0 + kb_per);
-      if (kb0 >= kb1) continue;
+      WorkItem it;
+      if (!decode(w, it)) continue;
+      const int m0 = it.m0, n0 = it.n0;
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
         if (lane == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
@@ -503,7 +541,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int col = n0 + c;
           if (row_ok) {
             if constexpr (EPI == EPI_ATOMIC_F32 || EPI == EPI_STORE_F32) {
-              float* Cf = reinterpret_cast<float*>(args.C) + static_cast<size_t>(row) * args.ldc;
+              float* Cf = reinterpret_cast<float*>(args.C) + it.c_off + static_cast<size_t>(row) * args.ldc;
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 if (col + j < N) {
@@ -651,7 +689,7 @@ static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas,
   const int n_extent = (EPI == EPI_SWIGLU) ? args.swiglu_half : args.N;
   const int num_m = (args.M + BM - 1) / BM;
   const int num_n = (n_extent + TILE_N - 1) / TILE_N;
-  const int total = num_m * num_n * args.splits;
+  const int total = num_m * num_n * (args.group_mode == 2 ? args.groups : args.splits);
   int grid = total < num_sms() ? total : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
@@ -679,12 +717,26 @@ using namespace nplm;
 // arguments. `status` is a device int the kernel writes a non-zero code to if a bounded wait
 // ran out. `max_ctas` (0 = all SMs) caps the grid so a concurrent communication kernel keeps
 // some SMs.
-extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
-                              int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn,
-                              int epi, int splits, int bn, int max_ctas, int direct_epilogue,
-                              const int* rope_pos, const float* rope_cos, const float* rope_sin,
-                              int rope_cols, int* status, cudaStream_t stream) {
+struct GroupSpec {
+  int mode = 0;
+  int groups = 1;
+  const int* tile_group = nullptr;
+  const int* group_off = nullptr;
+  int b_group_rows = 0;
+  long long c_group_stride = 0;
+};
+
+static int gemm_entry(const void* A, const void* B, void* C, const void* R, int M, int N,
+                      int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn,
+                      int epi, int splits, int bn, int max_ctas, int direct_epilogue,
+                      const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                      int rope_cols, int* status, cudaStream_t stream, const GroupSpec& grp) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (grp.mode == 1 && (grp.tile_group == nullptr || grp.groups < 1 || (K % BK) || epi == EPI_ATOMIC_F32))
+    return -9;
+  if (grp.mode == 2 && (grp.group_off == nullptr || grp.groups < 1 || !a_mn || !b_mn ||
+                        (epi != EPI_ATOMIC_F32 && epi != EPI_STORE_F32)))
+    return -9;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))
     return -3;
@@ -700,7 +752,10 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
   const int num_kb = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;
   if (splits > num_kb) splits = num_kb;
-  if (epi != EPI_ATOMIC_F32) splits = 1;
+  if (epi != EPI_ATOMIC_F32 || grp.mode != 0) splits = 1;
+  // outer (row) extent of the B tensor map: all groups' operands stacked
+  const uint64_t b_rows_kmajor = grp.mode == 1 ? static_cast<uint64_t>(grp.b_group_rows) * grp.groups : N;
+  const uint64_t b_rows_mnmajor = grp.mode == 1 ? static_cast<uint64_t>(grp.b_group_rows) * grp.groups : K;
 
   GemmMaps maps;
   CUtensorMap& tmA = maps.A;
@@ -712,11 +767,11 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
     rc = make_map_2d(&tmA, A, M, K, lda, 64, BK, 2);
   if (rc) return rc;
   if (epi == EPI_SWIGLU)
-    rc = make_map_2d(&tmB, B, K, N, ldb, BK, bn / 2, 2);
+    rc = make_map_2d(&tmB, B, K, b_rows_kmajor, ldb, BK, bn / 2, 2);
   else if (!b_mn)
-    rc = make_map_2d(&tmB, B, K, N, ldb, BK, bn, 2);
+    rc = make_map_2d(&tmB, B, K, b_rows_kmajor, ldb, BK, bn, 2);
   else
-    rc = make_map_2d(&tmB, B, N, K, ldb, 64, BK, 2);
+    rc = make_map_2d(&tmB, B, N, b_rows_mnmajor, ldb, 64, BK, 2);
   if (rc) return rc;
   // staged (TMA store) epilogue for the bf16 outputs; maps C / R describe [32 rows][64 cols] boxes
   maps.tma_epi = !direct_epilogue &&
@@ -750,6 +805,12 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
   args.rope_cos = rope_cos;
   args.rope_sin = rope_sin;
   args.rope_cols = rope_cols;
+  args.group_mode = grp.mode;
+  args.groups = grp.groups;
+  args.tile_group = grp.tile_group;
+  args.group_off = grp.group_off;
+  args.b_group_rows = grp.b_group_rows;
+  args.c_group_stride = grp.c_group_stride;
 
 #define NPLM_DISPATCH_EPI(BN_, AMN_, BMN_)                                                   \
   switch (epi) {                                                                             \
@@ -788,4 +849,48 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
     else { NPLM_DISPATCH_EPI(128, true, false) }
   }
   return -8;
+}
+
+extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
+                              int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn,
+                              int epi, int splits, int bn, int max_ctas, int direct_epilogue,
+                              const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                              int rope_cols, int* status, cudaStream_t stream) {
+  return gemm_entry(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, splits, bn, max_ctas,
+                    direct_epilogue, rope_pos, rope_cos, rope_sin, rope_cols, status, stream, GroupSpec());
+}
+
+// Grouped GEMM over row groups (mixture-of-experts forward and data gradient).
+//   A [M][K] (rows of all groups, every group padded to whole 128-row tiles), C [M][N] likewise;
+//   B holds `groups` operands stacked along its row axis, b_group_rows apart (N rows per group
+//   for a K-major B, K rows per group for an MN-major B); tile_group[M / 128] names the group of
+//   every row tile (-1 = tile not in use, skipped). K must be a multiple of 64.
+extern "C" int nplm_gemm_bf16_grouped(const void* A, const void* B, void* C, const void* R, int M,
+                                      int N, int K, int lda, int ldb, int ldc, int ldr, int b_mn,
+                                      int epi, int bn, int groups, const int* tile_group,
+                                      int b_group_rows, int* status, cudaStream_t stream) {
+  GroupSpec g;
+  g.mode = 1;
+  g.groups = groups;
+  g.tile_group = tile_group;
+  g.b_group_rows = b_group_rows;
+  return gemm_entry(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, 0, b_mn, epi, 1, bn, 0, 0, nullptr,
+                    nullptr, nullptr, 0, status, stream, g);
+}
+
+// Grouped weight gradient: C_g[M][N] (fp32, += or =) = A[rows_g][M]^T * B[rows_g][N] with
+// rows_g = [group_off[g], group_off[g+1]), offsets multiples of 128, `rows` rows in total.
+extern "C" int nplm_gemm_bf16_grouped_wgrad(const void* A, const void* B, float* C, int M, int N,
+                                            int rows, int lda, int ldb, int ldc, int accumulate,
+                                            int bn, int groups, const int* group_off,
+                                            long long c_group_stride, int* status,
+                                            cudaStream_t stream) {
+  GroupSpec g;
+  g.mode = 2;
+  g.groups = groups;
+  g.group_off = group_off;
+  g.c_group_stride = c_group_stride;
+  return gemm_entry(A, B, C, nullptr, M, N, rows, lda, ldb, ldc, 0, 1, 1,
+                    accumulate ? EPI_ATOMIC_F32 : EPI_STORE_F32, 1, bn, 0, 0, nullptr, nullptr,
+                    nullptr, 0, status, stream, g);
 }

@@ -2,11 +2,14 @@
 experts, Switch-style load-balancing loss  aux = E * sum_e f_e * P_e  (f_e: share of assignments
 routed to expert e, P_e: mean router probability of e).
 
-Tokens are sorted by expert once per layer (a permutation of T*k rows), every expert runs its two
-GEMMs on a contiguous row slice with the tcgen05 GEMM (SwiGLU fused into the up-projection
-epilogue), and the outputs are combined with the gate weights. With expert parallelism
-(`ep_group`) the experts are split over the ranks of the group and the permuted rows travel through
-an all-to-all before and after the expert GEMMs (nanoplm_b200.parallel.expert).
+On a GPU the whole layer runs through nanoplm_b200.ops.moe without a host synchronisation: router
+top-k kernel, device-side plan (expert segments padded to 128-row tiles), token rows pushed into an
+expert-major buffer, two grouped tcgen05 GEMMs over all experts in one launch each (SwiGLU fused
+into the up-projection epilogue), and a gate-weighted pull. With expert parallelism (`ep_group`)
+the experts are split over the ranks of the group and the rows travel over NVLink peer memory
+inside the same push / pull kernels. Set `device_path=False` (or run on the CPU) for the plain
+PyTorch restatement, which with `ep_group` uses an all-to-all (nanoplm_b200.parallel.expert) and
+serves as the oracle and the collective-library baseline.
 
 The reference has no MoE layers.
 """
@@ -44,8 +47,10 @@ def _expert_weight(param: torch.Tensor, e: int) -> torch.Tensor:
 
 
 class MoEMLP(nn.Module):
-    def __init__(self, cfg: ModelConfig, ep_group=None):
+    def __init__(self, cfg: ModelConfig, ep_group=None, device_path: bool = True):
         super().__init__()
+        self.device_path = device_path
+        self._comm = None
         m = cfg.moe
         self.num_experts, self.top_k = m.num_experts, m.top_k
         self.inter = m.expert_intermediate_size
@@ -79,8 +84,18 @@ class MoEMLP(nn.Module):
             return out.zero_() + 0.0 * (self.experts_Wi.sum() + self.experts_Wo.sum()).to(out.dtype)
         return torch.cat(pieces, dim=0)
 
+    def _use_device_path(self, x: torch.Tensor) -> bool:
+        return (self.device_path and x.is_cuda and x.dtype == torch.bfloat16 and self.hidden % 64 == 0
+                and self.inter % 64 == 0 and self.num_experts <= 256 and self.top_k <= 8)
+
     def forward(self, x: torch.Tensor):
         T, C = x.shape
+        if self._use_device_path(x):
+            from nanoplm_b200.ops import moe as M
+            if self._comm is None:
+                self._comm = M.MoEComm(self.hidden, self.num_experts, self.top_k, group=self.ep_group)
+            logits = ops.linear(x, self.router.weight)
+            return M.moe_mlp(x, logits, self.experts_Wi, self.experts_Wo, self.top_k, self._comm)
         logits = F.linear(x, self.router.weight)
         gates, experts, aux = route_topk(logits, self.top_k)
         flat_e = experts.reshape(-1)
