@@ -138,10 +138,20 @@ class MoEComm:
         return (rows + 127) // 128 * 128
 
     def _ensure_symmetric(self, cap: int, device):
-        if self._sym is not None and self._cap >= cap:
+        """Allocates the symmetric buffers on first use. Symmetric allocations must have the same
+        size on every rank, so the capacity is the maximum over the ranks of the first request
+        (one host-synchronising all-reduce, once); later requests must fit."""
+        if self._sym is not None:
+            if cap > self._cap:
+                raise ValueError(f"MoE layer received {cap} expert rows but its symmetric buffers hold "
+                                 f"{self._cap}; keep the token count per micro-batch constant")
             return
+        import torch.distributed as dist
         from nanoplm_b200.comm.fused_optimizer import SymmetricBuffer
         g = self.group
+        agreed = torch.tensor([cap], dtype=torch.int64, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX, group=g)
+        cap = int(agreed.item())
         self._cap = cap
         self._sym = {
             "xs": SymmetricBuffer(cap * self.C, _BF16, device, g),

@@ -124,3 +124,75 @@ def test_peer_barrier_times_out_without_hanging():
     x = torch.ones(4, device="cuda") * 2
     assert x.sum().item() == 8
     _lib.check_status()
+
+
+def _ep_worker(rank, world, port, out_path):
+    """Expert parallelism over peer memory: every rank routes its own tokens to experts that are
+    split over the ranks; outputs and gradients must match an fp32 run of all experts on all tokens."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from nanoplm_b200.ops import _lib
+    from nanoplm_b200.ops import moe as M
+    from test_moe_gpu import _moe_oracle
+    BF = torch.bfloat16
+    T, E, k, C, I = 700 + 37 * rank, 8, 2, 128, 128
+    El = E // world
+    g = torch.Generator(device="cpu").manual_seed(7)
+    Wi_all = (torch.randn(E, 2 * I, C, generator=g) * 0.06).to(BF).to(dev)
+    Wo_all = (torch.randn(E, C, I, generator=g) * 0.06).to(BF).to(dev)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(T, C, device=dev).to(BF).requires_grad_(True)
+    logits = (torch.randn(T, E, device=dev) * 1.5).to(BF).requires_grad_(True)
+    gy = torch.randn(T, C, device=dev).to(BF)
+    Wi = Wi_all[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    Wo = Wo_all[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    comm = M.MoEComm(C, E, k, group=dist.group.WORLD, capacity_factor=float(world))
+    worst = {}
+    for it in range(2):                       # second pass reuses the symmetric buffers
+        for t in (x, logits, Wi, Wo):
+            t.grad = None
+        y, aux = M.moe_mlp(x, logits, Wi, Wo, k, comm)
+        ((y.float() * gy.float()).sum() + 0.5 * aux).backward()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        # oracle: all experts, this rank's tokens (outputs, dx, dlogits)
+        x32 = x.detach().float().requires_grad_(True)
+        l32 = logits.detach().float().requires_grad_(True)
+        Wi32 = Wi_all.float().requires_grad_(True)
+        Wo32 = Wo_all.float().requires_grad_(True)
+        experts = M.router_topk(logits.detach(), k)[2]
+        y_ref, aux_ref = _moe_oracle(x32, l32, Wi32, Wo32, k, experts)
+        ((y_ref * gy.float()).sum() + 0.5 * aux_ref).backward()
+        # weight gradients are sums over the tokens of every rank
+        gWi, gWo = Wi32.grad.clone(), Wo32.grad.clone()
+        dist.all_reduce(gWi)
+        dist.all_reduce(gWo)
+
+        def rel(a, b):
+            return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+        worst = {"y": rel(y, y_ref), "dx": rel(x.grad, x32.grad), "dlogits": rel(logits.grad, l32.grad),
+                 "dWi": rel(Wi.grad, gWi[rank * El:(rank + 1) * El]),
+                 "dWo": rel(Wo.grad, gWo[rank * El:(rank + 1) * El])}
+        for name, v in worst.items():
+            assert v < 0.06, (it, rank, name, v)
+    if rank == 0:
+        torch.save(worst, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+def test_expert_parallel_peer_memory(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    out = str(tmp_path / "ep.pt")
+    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    assert os.path.exists(out)
