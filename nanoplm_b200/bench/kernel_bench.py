@@ -183,6 +183,73 @@ def bench_elementwise(T, peaks):
     k.check_status()
 
 
+def bench_fp8(T, peaks):
+    """e4m3 block-scaled GEMM (per-K-block promotion) next to the bf16 tcgen05 GEMM, and the
+    quantisation kernels."""
+    from nanoplm_b200.ops import fp8
+    from nanoplm_b200.ops import kernels as k
+    flush = _flush_buf()
+    for name, N, K in [("qkv_fwd", 3072, 1024), ("mlp_up_fwd", 4096, 1024), ("mlp_down_fwd", 1024, 2048)]:
+        x = torch.randn(T, K, device="cuda").to(BF)
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(BF)
+        qx, qw = fp8.quant_rows(x), fp8.quant_tile(w, transpose=False, block=True)
+        out = torch.empty(T, N, dtype=BF, device="cuda")
+        ms8 = time_fn(lambda: fp8.gemm_fp8(qx, qw, out=out), flush=flush)
+        ms16 = time_fn(lambda: k.gemm(x, w, out=out), flush=flush)
+        msq = time_fn(lambda: fp8.quant_rows(x), flush=flush)
+        fl = 2.0 * T * N * K
+        print(json.dumps({"kernel": "gemm_fp8_block128", "shape": name, "M": T, "N": N, "K": K,
+                          "ms_fp8": round(ms8, 4), "tflops_fp8": round(fl / ms8 / 1e9, 1),
+                          "ms_bf16": round(ms16, 4), "tflops_bf16": round(fl / ms16 / 1e9, 1),
+                          "ms_quant_rows": round(msq, 4),
+                          "quant_gbs": round(T * K * 3 / msq / 1e6, 1)}), flush=True)
+
+
+def bench_moe(T, peaks):
+    """Grouped tcgen05 GEMM over 64 experts (I = 512, top-2) next to a loop of per-expert GEMMs, and
+    the whole device-side MoE layer forward + backward."""
+    from nanoplm_b200.ops import kernels as k
+    from nanoplm_b200.ops import moe as M
+    flush = _flush_buf()
+    E, top_k, C, I = 64, 2, 1024, 512
+    torch.manual_seed(0)
+    experts = torch.randint(0, E, (T, top_k), device="cuda", dtype=torch.int32)
+    comm = M.MoEComm(C, E, top_k)
+    plan = M.make_plan(comm, experts)
+    xs = torch.randn(plan.cap, C, device="cuda").to(BF)
+    Wi = (torch.randn(E, 2 * I, C, device="cuda") * 0.03).to(BF)
+    Wo = (torch.randn(E, C, I, device="cuda") * 0.03).to(BF)
+    pre = torch.empty(plan.cap, 2 * I, dtype=BF, device="cuda")
+    ms_up = time_fn(lambda: M.gemm_grouped(xs, Wi, plan.tile_group, epi=k.EPI_SWIGLU, aux=pre), flush=flush)
+    off = plan.group_off.cpu().tolist()
+    rows = off[-1]
+
+    def loop():
+        for e in range(E):
+            if off[e + 1] > off[e]:
+                k.gemm(xs[off[e]:off[e + 1]], Wi[e], epi=k.EPI_SWIGLU, aux=pre[off[e]:off[e + 1]])
+
+    ms_loop = time_fn(loop, flush=flush)
+    fl = 2.0 * rows * 2 * I * C
+    print(json.dumps({"kernel": "gemm_grouped_swiglu", "experts": E, "rows": rows, "N": 2 * I, "K": C,
+                      "ms_grouped": round(ms_up, 4), "tflops_grouped": round(fl / ms_up / 1e9, 1),
+                      "ms_per_expert_loop": round(ms_loop, 4)}), flush=True)
+    x = torch.randn(T, C, device="cuda").to(BF).requires_grad_(True)
+    logits = torch.randn(T, E, device="cuda").to(BF).requires_grad_(True)
+    Wi.requires_grad_(True)
+    Wo.requires_grad_(True)
+    gy = torch.randn(T, C, device="cuda").to(BF)
+
+    def layer():
+        y, aux = M.moe_mlp(x, logits, Wi, Wo, top_k, comm)
+        (y.float() * gy.float()).sum().add(aux).backward()
+
+    ms_layer = time_fn(layer, iters=5, flush=flush)
+    flops = 3 * 2.0 * T * top_k * (2 * I * C + C * I)
+    print(json.dumps({"kernel": "moe_layer_fwd_bwd", "tokens": T, "experts": E, "top_k": top_k,
+                      "ms": round(ms_layer, 3), "expert_tflops": round(flops / ms_layer / 1e9, 1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=65536)
@@ -191,7 +258,8 @@ def main():
     from nanoplm_b200.utils.peaks import measured_peaks
     peaks = measured_peaks()
     for what in args.what.split(","):
-        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise}[what](args.tokens, peaks)
+        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "fp8": bench_fp8,
+         "moe": bench_moe}[what](args.tokens, peaks)
 
 
 if __name__ == "__main__":

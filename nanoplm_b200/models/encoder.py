@@ -71,7 +71,7 @@ class Attention(nn.Module):
     def forward(self, x, ctx: "BatchContext", window: int, rope: tuple, residual=None):
         H, D = self.num_heads, self.head_dim
         fused = (x.is_cuda and x.dtype == torch.bfloat16 and D == 64 and self.Wqkv.bias is None
-                 and x.dim() == 2 and self.Wqkv.in_features % 8 == 0)
+                 and x.dim() == 2 and self.Wqkv.in_features % 8 == 0 and not ops.fp8_enabled())
         if fused:   # RoPE in the QKV GEMM epilogue, its transpose inside the attention backward
             qkv = ops.linear_rope(x, self.Wqkv.weight, ctx.position_ids, rope[0], rope[1], 2 * H * D)
             y = ops.attention_varlen(qkv, ctx.seq_start, ctx.seq_end, H, D, window, self.scale,

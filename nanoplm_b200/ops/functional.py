@@ -122,9 +122,34 @@ def linear_rope(x, w, pos, cos, sin, rope_cols: int):
     return _LinearFn.apply(x, w, None, None, None, (pos, cos, sin, rope_cols))
 
 
+_FP8_STATE = {"enabled": False}
+
+
+def set_fp8(enabled: bool) -> None:
+    """Routes every bias-free linear layer whose weight dims are multiples of 128 through the
+    e4m3 block-scaled GEMM (forward, data gradient and weight gradient); see nanoplm_b200.ops.fp8.
+    The reference has no FP8 mode."""
+    _FP8_STATE["enabled"] = bool(enabled)
+
+
+def fp8_enabled() -> bool:
+    return _FP8_STATE["enabled"]
+
+
 def linear(x, w, bias=None, residual=None, act: str | None = None):
     """y = act(x w^T + bias) + residual.  act: None | "gelu" | "swiglu" (w rows = [value | gate],
     output is half as wide). residual and act are mutually exclusive."""
+    if x.is_cuda and _FP8_STATE["enabled"] and bias is None:
+        from . import fp8
+        if fp8.supported(x, w):
+            y = fp8.fp8_linear(x, w)
+            if act == "swiglu":
+                y = swiglu(y)
+            elif act == "gelu":
+                y = activation(y, "gelu")
+            if residual is not None:
+                y = y + residual
+            return y
     if x.is_cuda:
         if w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.dtype == BF:
             if act == "swiglu" and bias is not None:

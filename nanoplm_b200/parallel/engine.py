@@ -62,6 +62,14 @@ class AdamWHyper:
     max_grad_norm: float = 1.0
 
 
+def _invalidate_fp8_weights() -> None:
+    """Quantised copies of the weights are valid for one optimizer step only."""
+    import sys
+    mod = sys.modules.get("nanoplm_b200.ops.fp8")
+    if mod is not None:
+        mod.invalidate_weight_cache()
+
+
 class ShardedEngine:
     def __init__(self, model: nn.Module, hyper: AdamWHyper, device: torch.device,
                  process_group=None, compute_dtype: torch.dtype = torch.bfloat16,
@@ -185,6 +193,7 @@ class ShardedEngine:
         """One optimizer step. Returns the global gradient norm (a device scalar; no host sync)."""
         self.collect_autograd_grads()
         self.step_count += 1
+        _invalidate_fp8_weights()
         grad_scale = 1.0 / (grad_accum * self.world)
         self._fill_hyper(lr, grad_scale)
         if self.fused is not None:

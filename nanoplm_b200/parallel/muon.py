@@ -101,6 +101,8 @@ class MuonEngine(ShardedEngine):
     def step(self, lr: float, grad_accum: int = 1) -> torch.Tensor:
         self.collect_autograd_grads()
         self.step_count += 1
+        from nanoplm_b200.parallel.engine import _invalidate_fp8_weights
+        _invalidate_fp8_weights()
         if self.distributed:
             dist.all_reduce(self.main_grad, group=self.pg)
         scale = 1.0 / (grad_accum * self.world)

@@ -217,6 +217,12 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
     else:
         raise ValueError(f"Invalid optimizer: {cfg.optimizer}. Supported: [adamw, stable_adamw, muon, normuon]")
     model.train()
+    if getattr(cfg, "fp8", False):
+        if str(getattr(cfg, "fp8_recipe", "block128")) != "block128":
+            raise ValueError(f"Unknown fp8_recipe {cfg.fp8_recipe!r}; supported: block128")
+        from nanoplm_b200.ops import functional as _ops
+        _ops.set_fp8(device.type == "cuda" and use_bf16)
+        logger.info("FP8 (e4m3, block128) linear layers enabled")
 
     train_collator, eval_collator = build_collators(tokenizer, cfg, pt, manifest.max_seq_len,
                                                     cfg.seed + 1000 * rank)
