@@ -74,6 +74,17 @@ struct GemmArgs {
   const int* group_off;
   int b_group_rows;
   long long c_group_stride;
+  // All-gather mode (ag_world > 1): B [N][K] is row-sharded over ag_world ranks, ag_rows rows each.
+  // The local B buffer holds this rank's rows only; at kernel start the epilogue warps of all CTAs
+  // copy the other shards out of the peers' memory (plain P2P loads, each byte crosses NVLink
+  // once), bump ag_flags[shard] when their slice of a shard has landed, and the TMA producer waits
+  // (bounded) for a shard's flag before it loads the first tile of that shard. Tiles are visited
+  // shard by shard, the local shard first, so the copies overlap the first waves of MMAs.
+  int ag_world, ag_rank, ag_rows;
+  const void* ag_src[8];   // peer r's shard: ag_rows x K, row stride ag_ld elements
+  void* ag_dst;            // local full B (row stride ag_ld)
+  int ag_ld;
+  unsigned* ag_flags;      // [ag_world], zeroed before the launch
 };
 
 struct WorkItem {
@@ -153,8 +164,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       return it.kb0 < it.kb1;
     }
     const int split = w % splits, tile = w / splits;
-    it.m0 = (tile / num_n) * BM;
-    it.n0 = (tile % num_n) * TILE_N;
+    if (args.ag_world > 1) {
+      // shard by shard starting with the local one; inside a shard n runs fastest
+      const int n_per = args.ag_rows / TILE_N;
+      const int per_shard = num_m * n_per;
+      const int shard = (args.ag_rank + tile / per_shard) % args.ag_world;
+      const int rem = tile % per_shard;
+      it.m0 = (rem / n_per) * BM;
+      it.n0 = shard * args.ag_rows + (rem % n_per) * TILE_N;
+    } else {
+      it.m0 = (tile / num_n) * BM;
+      it.n0 = (tile % num_n) * TILE_N;
+    }
     it.kb0 = split * kb_per;
     it.kb1 = min(num_kb, it.kb0 + kb_per);
     if (args.group_mode == 1) {
@@ -202,11 +223,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t ag_seen = 0;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         WorkItem it;
         if (!decode(w, it)) continue;
         const int m0 = it.m0, n0 = it.n0, kb0 = it.kb0, kb1 = it.kb1;
         const int brow = it.b_row;
+        if (args.ag_world > 1) {
+          const int shard = n0 / args.ag_rows;
+          if (shard != args.ag_rank && !((ag_seen >> shard) & 1u)) {
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(args.ag_flags + shard) < gridDim.x) {
+              if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                atomicExch(args.status, ST_TIMEOUT_PEER);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+            if (!ok) break;
+            ag_seen |= 1u << shard;
+            fence_proxy_async_global();  // the shard was written with generic stores, TMA reads it
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicExch(args.status, ST_TIMEOUT_EMPTY);
@@ -298,6 +338,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;
+    if (args.ag_world > 1) {
+      // all-gather: this CTA's slice of every remote shard, nearest shard (in visiting order) first
+      const int et = threadIdx.x - 64;                       // 0..127 over the four epilogue warps
+      const long long row_vecs = args.K / 8;                 // 16-byte vectors per row
+      const long long shard_vecs = static_cast<long long>(args.ag_rows) * row_vecs;
+      const long long per_cta = (shard_vecs + gridDim.x - 1) / gridDim.x;
+      const long long v0 = per_cta * blockIdx.x;
+      const long long v1 = min(shard_vecs, v0 + per_cta);
+      for (int d = 1; d < args.ag_world; ++d) {
+        const int shard = (args.ag_rank + d) % args.ag_world;
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(args.ag_src[shard]);
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.ag_dst) +
+                             static_cast<size_t>(shard) * args.ag_rows * args.ag_ld;
+        for (long long v = v0 + et; v < v1; v += 128) {
+          const long long r = v / row_vecs, c = (v % row_vecs) * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(src + r * args.ag_ld + c);
+          *reinterpret_cast<uint4*>(dst + r * args.ag_ld + c) = val;
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps only
+        if (et == 0) red_release_gpu_add(args.ag_flags + shard, 1u);
+      }
+    }
     int acc = 0;
     uint32_t acc_phase = 0;
     int stage_toggle = 0;       // which of this warp's two staging buffers is next
@@ -693,6 +756,16 @@ static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas,
   int grid = total < num_sms() ? total : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
+  if (args.ag_world > 1) {
+    // CTAs wait on one another's copies: they must all be resident, which a cooperative launch
+    // guarantees (it fails instead of running a grid that does not fit)
+    if (grid > num_sms()) grid = num_sms();
+    void* params[] = {const_cast<CUtensorMap*>(&tmA), const_cast<CUtensorMap*>(&tmB),
+                      const_cast<CUtensorMap*>(&maps.C), const_cast<CUtensorMap*>(&maps.R),
+                      const_cast<GemmArgs*>(&args)};
+    return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), dim3(grid),
+                                                        dim3(GEMM_THREADS), params, S::TOTAL, stream));
+  }
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, maps.C, maps.R, args);
   return static_cast<int>(cudaGetLastError());
 }
@@ -724,6 +797,10 @@ struct GroupSpec {
   const int* group_off = nullptr;
   int b_group_rows = 0;
   long long c_group_stride = 0;
+  // all-gather mode
+  int ag_world = 0, ag_rank = 0;
+  void* const* ag_ptrs = nullptr;  // every rank's full B buffer (this rank's one is B itself)
+  unsigned* ag_flags = nullptr;
 };
 
 static int gemm_entry(const void* A, const void* B, void* C, const void* R, int M, int N,
@@ -811,6 +888,24 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   args.group_off = grp.group_off;
   args.b_group_rows = grp.b_group_rows;
   args.c_group_stride = grp.c_group_stride;
+  args.ag_world = grp.ag_world;
+  args.ag_rank = grp.ag_rank;
+  args.ag_rows = 0;
+  args.ag_dst = const_cast<void*>(B);
+  args.ag_ld = ldb;
+  args.ag_flags = grp.ag_flags;
+  for (int r = 0; r < 8; ++r) args.ag_src[r] = nullptr;
+  if (grp.ag_world > 1) {
+    if (grp.ag_world > 8 || a_mn || b_mn || grp.mode != 0 || epi == EPI_ATOMIC_F32 || epi == EPI_SWIGLU ||
+        grp.ag_ptrs == nullptr || grp.ag_flags == nullptr || (N % grp.ag_world) || (K % 8))
+      return -10;
+    args.ag_rows = N / grp.ag_world;
+    if (args.ag_rows % bn) return -10;   // a tile must not straddle two shards
+    for (int r = 0; r < grp.ag_world; ++r)
+      args.ag_src[r] = reinterpret_cast<const __nv_bfloat16*>(grp.ag_ptrs[r]) +
+                       static_cast<size_t>(r) * args.ag_rows * ldb;
+    NPLM_CUDA_CHECK(cudaMemsetAsync(grp.ag_flags, 0, 8 * sizeof(unsigned), stream));
+  }
 
 #define NPLM_DISPATCH_EPI(BN_, AMN_, BMN_)                                                   \
   switch (epi) {                                                                             \
@@ -893,4 +988,23 @@ extern "C" int nplm_gemm_bf16_grouped_wgrad(const void* A, const void* B, float*
   return gemm_entry(A, B, C, nullptr, M, N, rows, lda, ldb, ldc, 0, 1, 1,
                     accumulate ? EPI_ATOMIC_F32 : EPI_STORE_F32, 1, bn, 0, 0, nullptr, nullptr,
                     nullptr, 0, status, stream, g);
+}
+
+// All-gather fused into the GEMM: C[M][N] = A[M][K] * B[N][K]^T where B is row-sharded over
+// `world` ranks. b_ptrs[r] is rank r's full-size B buffer (peer-mapped); on entry only rows
+// [r * N/world, (r+1) * N/world) of buffer r are valid. On return this rank's buffer holds all of
+// B (the all-gather result, reusable by later GEMMs) and C is complete. flags: 8 device words.
+// The caller orders this launch after the peers' writes of their shards (a barrier) and keeps the
+// shards unchanged until every rank's launch has finished.
+extern "C" int nplm_gemm_bf16_ag(const void* A, void* const* b_ptrs, void* C, const void* R, int M, int N,
+                                 int K, int lda, int ldb, int ldc, int ldr, int epi, int bn, int rank,
+                                 int world, unsigned* flags, int* status, cudaStream_t stream) {
+  GroupSpec g;
+  g.ag_world = world;
+  g.ag_rank = rank;
+  g.ag_ptrs = b_ptrs;
+  g.ag_flags = flags;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return -10;
+  return gemm_entry(A, b_ptrs[rank], C, R, M, N, K, lda, ldb, ldc, ldr, 0, 0, epi, 1, bn, 0, 0, nullptr,
+                    nullptr, nullptr, 0, status, stream, g);
 }

@@ -99,6 +99,44 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def gemm_ag(a: torch.Tensor, b_full: torch.Tensor, b_ptrs, rank: int, world: int, flags: torch.Tensor, *,
+            epi: int = EPI_STORE, out: torch.Tensor | None = None, aux: torch.Tensor | None = None,
+            bn: int | None = None) -> torch.Tensor:
+    """All-gather fused into the GEMM: C = A B^T with B [N,K] row-sharded over `world` ranks.
+
+    b_full is this rank's full-size weight buffer in peer-mapped (symmetric) memory, of which only
+    rows [rank*N/world, (rank+1)*N/world) are valid on entry; b_ptrs is the ctypes array of all ranks'
+    buffer addresses. The kernel pulls the other shards over NVLink while the tensor cores work on
+    the local shard's tiles; afterwards b_full holds the whole matrix. flags: uint32/int32 [8].
+    The caller orders the call after the peers' shard writes and before their next update.
+    """
+    _chk(a, _BF16, "a")
+    _chk(b_full, _BF16, "b")
+    M, K = a.shape
+    N, Kb = b_full.shape
+    if K != Kb:
+        raise ValueError(f"inner dims differ: {K} vs {Kb}")
+    if N % world:
+        raise ValueError("rows of B must divide evenly over the ranks")
+    rows = N // world
+    if bn is None:
+        bn = 256 if rows % 256 == 0 else 128
+    if rows % bn:
+        raise ValueError(f"shard height {rows} must be a multiple of the {bn}-wide tile")
+    if out is None:
+        out = torch.empty((M, N), dtype=_BF16, device=a.device)
+    ldr = 0
+    if aux is not None:
+        ldr = _rowmajor(aux, "aux")
+    rc = lib("gemm_tcgen05").nplm_gemm_bf16_ag(
+        ptr(a), b_ptrs, ptr(out), ptr(aux), c_int(M), c_int(N), c_int(K), c_int(_rowmajor(a, "a")),
+        c_int(_rowmajor(b_full, "b")), c_int(_rowmajor(out, "out")), c_int(ldr), c_int(epi), c_int(bn),
+        c_int(rank), c_int(world), ptr(flags), ptr(status_word(a.device)), stream_ptr())
+    check_rc(rc, "gemm_bf16_ag")
+    count_launch()
+    return out
+
+
 def wgrad_splits(n_out: int, k_in: int, tokens: int, bn: int = 256, sms: int = 148) -> int:
     """Split-K factor for a weight-gradient GEMM [n_out, k_in] reduced over `tokens`: the smallest
     factor (<= 4) whose work items fill the last wave of `sms` CTAs best."""

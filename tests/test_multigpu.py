@@ -196,3 +196,62 @@ def test_expert_parallel_peer_memory(tmp_path):
         p.join(240)
         assert p.exitcode == 0, f"rank exited with {p.exitcode}"
     assert os.path.exists(out)
+
+
+def _ag_worker(rank, world, port, out_path):
+    """All-gather fused into the GEMM: the weight is row-sharded over the ranks in symmetric memory;
+    every rank multiplies its own activations by the whole weight."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from nanoplm_b200.comm.fused_optimizer import SymmetricBuffer
+    from nanoplm_b200.ops import _lib
+    from nanoplm_b200.ops import kernels as K
+    BF = torch.bfloat16
+    results = {}
+    for (M, N, Kd, epi) in [(1000, 512, 256, K.EPI_STORE), (4096, 3072, 1024, K.EPI_STORE),
+                            (2048, 1024, 512, K.EPI_ADD)]:
+        g = torch.Generator(device="cpu").manual_seed(11)
+        W = (torch.randn(N, Kd, generator=g) * 0.05).to(BF).to(dev)
+        torch.manual_seed(200 + rank)
+        x = torch.randn(M, Kd, device=dev).to(BF)
+        res = torch.randn(M, N, device=dev).to(BF) if epi == K.EPI_ADD else None
+        sb = SymmetricBuffer(N * Kd, BF, dev, dist.group.WORLD)
+        full = sb.tensor.view(N, Kd)
+        rows = N // world
+        for it in range(2):                      # second pass: buffers already hold the gathered matrix
+            full.fill_(float("nan"))
+            full[rank * rows:(rank + 1) * rows] = W[rank * rows:(rank + 1) * rows]
+            flags = torch.zeros(8, dtype=torch.int32, device=dev)
+            torch.cuda.synchronize()
+            dist.barrier()                       # every rank's shard is in place
+            y = K.gemm_ag(x, full, sb.ptr_array, rank, world, flags, epi=epi, aux=res)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            dist.barrier()                       # peers are done reading before the next fill
+            ref = x.float() @ W.float().t()
+            if res is not None:
+                ref = ref + res.float()
+            err = (y.float() - ref).abs().max().item() / ref.abs().max().item()
+            assert err < 0.02, (M, N, Kd, it, err)
+            assert torch.equal(full, W), "the local buffer must hold the gathered weight"
+            results[(M, N, Kd)] = err
+    if rank == 0:
+        torch.save(results, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+def test_all_gather_gemm(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    out = str(tmp_path / "ag.pt")
+    procs = [ctx.Process(target=_ag_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    assert os.path.exists(out)
