@@ -28,6 +28,16 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
   }
 }
 
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 t = unpack_bf16x2(w[e]);
+    f[2 * e] = t.x;
+    f[2 * e + 1] = t.y;
+  }
+}
+
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   uint4 u;
   uint32_t* w = reinterpret_cast<uint32_t*>(&u);
@@ -108,7 +118,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids
 // ids != nullptr (embedding): x rows are gathered from the table, dx is not written, and the
 // row gradient is accumulated into dtable[ids[row]] (fp32) instead.
 template <int CHUNKS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
@@ -130,17 +140,29 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
        row += gridDim.x * warps_per_block) {
     const __nv_bfloat16* src =
         ids ? x + static_cast<size_t>(ids[row]) * C : x + static_cast<size_t>(row) * C;
+    // Every global load of the row (x, dy and the skip gradient) is issued before the first use and
+    // kept packed (bf16) in registers, so a warp has 6 KB in flight; the second pass unpacks again.
+    uint4 xr[CHUNKS], dr[CHUNKS], rr[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int i = c * 256 + lane * 8;
+      xr[c] = dr[c] = rr[c] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < C) {
+        xr[c] = __ldg(reinterpret_cast<const uint4*>(src + i));
+        dr[c] = __ldg(reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * C + i));
+        if (dres) rr[c] = __ldg(reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * C + i));
+      }
+    }
     const float mean = rms ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
-    float xh[CHUNKS][8], g[CHUNKS][8];
     float sg = 0.f, sgx = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int i = c * 256 + lane * 8;
       if (i < C) {
         float xv[8], dv[8], wv[8];
-        load8(src + i, xv);
-        load8(dy + static_cast<size_t>(row) * C + i, dv);
+        unpack8(xr[c], xv);
+        unpack8(dr[c], dv);
         if (w) {
           load8(w + i, wv);
         } else {
@@ -149,11 +171,11 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          xh[c][e] = (xv[e] - mean) * rstd;
-          g[c][e] = dv[e] * wv[e];
-          sg += g[c][e];
-          sgx += g[c][e] * xh[c][e];
-          acc[c][e] += dv[e] * xh[c][e];
+          const float xh = (xv[e] - mean) * rstd;
+          const float g = dv[e] * wv[e];
+          sg += g;
+          sgx += g * xh;
+          acc[c][e] += dv[e] * xh;
         }
       }
     }
@@ -163,9 +185,20 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     for (int c = 0; c < CHUNKS; ++c) {
       const int i = c * 256 + lane * 8;
       if (i < C) {
-        float o[8];
+        float xv[8], dv[8], wv[8], o[8];
+        unpack8(xr[c], xv);
+        unpack8(dr[c], dv);
+        if (w) {
+          load8(w + i, wv);
+        } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[c][e] - sg - xh[c][e] * sgx);
+          for (int e = 0; e < 8; ++e) wv[e] = 1.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = (xv[e] - mean) * rstd;
+          o[e] = rstd * (dv[e] * wv[e] - sg - xh * sgx);
+        }
         if (ids) {
           float* dst = dtable + static_cast<size_t>(ids[row]) * C + i;
 #pragma unroll
@@ -173,7 +206,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
         } else {
           if (dres) {
             float r[8];
-            load8(dres + static_cast<size_t>(row) * C + i, r);
+            unpack8(rr[c], r);
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[e] += r[e];
           }

@@ -49,6 +49,15 @@ def _mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return a @ b.t()
 
 
+def _mm_nn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a @ b for bf16 2-D operands; on CUDA b is consumed as an MN-major operand, no transpose."""
+    if (a.is_cuda and a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] % 8 == 0
+            and b.shape[1] % 64 == 0 and b.is_contiguous()):
+        from nanoplm_b200.ops import kernels as K
+        return K.gemm(a.contiguous(), b, b_mn=True)
+    return a @ b
+
+
 def orthogonalize(G: torch.Tensor, coeffs=NS_QUINTIC, eps: float = 1e-7) -> torch.Tensor:
     """Approximate polar factor of G by quintic iterations X <- aX + (bA + cA^2)X, A = X X^T."""
     dt = torch.bfloat16 if G.is_cuda else torch.float32
@@ -60,7 +69,7 @@ def orthogonalize(G: torch.Tensor, coeffs=NS_QUINTIC, eps: float = 1e-7) -> torc
     for a, b, c in coeffs:
         A = _mm(X, X)                                   # X X^T          [m, m], symmetric
         B = b * A + c * _mm(A, A)                       # A A^T = A^2
-        X = a * X + _mm(B, X.t().contiguous())          # B X
+        X = a * X + _mm_nn(B, X)                        # B X
     if transposed:
         X = X.t().contiguous()
     return X
