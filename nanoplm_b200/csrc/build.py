@@ -23,6 +23,7 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "elementwise.cu",
     "attention.cu",
+    "attention_bias.cu",
     "extras.cu",
     "comm.cu",
     "moe.cu",

@@ -73,7 +73,34 @@ class SelfAttention(nn.Module):
                                            self.cfg.relative_attention_max_distance)
         return self.relative_attention_bias(buckets).permute(2, 0, 1)[None]     # [1, H, S, S]
 
+    def compute_bias_table(self, S: int, device) -> torch.Tensor:
+        """fp32 [H, 2S-1]: bias of relative position (key - query) = index - (S - 1)."""
+        rel = torch.arange(-(S - 1), S, device=device)
+        buckets = relative_position_bucket(rel, self.cfg.relative_attention_num_buckets,
+                                           self.cfg.relative_attention_max_distance)
+        return self.relative_attention_bias(buckets).float().t().contiguous()
+
+    def _fused_qkv_weight(self) -> torch.Tensor:
+        """[3*H*dk, d_model] = [Wq; Wk; Wv] (the teacher is frozen, so the copy is built once)."""
+        w = getattr(self, "_wqkv", None)
+        if w is None or w.device != self.q.weight.device or w.dtype != self.q.weight.dtype:
+            w = torch.cat([self.q.weight, self.k.weight, self.v.weight], dim=0).detach().contiguous()
+            self._wqkv = w
+        return w
+
+    def forward_native(self, x, fast, residual):
+        """tcgen05 path: one fused QKV GEMM, attention with the relative-position bias table in the
+        kernel (nanoplm_b200/csrc/attention_bias.cu), output projection with the residual add."""
+        from nanoplm_b200.ops import kernels as K
+        B, S, _ = x.shape
+        x2 = x.reshape(B * S, -1)
+        qkv = ops.linear(x2, self._fused_qkv_weight())
+        y = K.fa_bias_fwd(qkv, fast["seq_start"], fast["seq_end"], fast["table"], self.h, self.dk, 1.0)
+        return self.o(y, residual=residual.reshape(B * S, -1)).view(B, S, -1)
+
     def forward(self, x, bias, residual):
+        if isinstance(bias, dict):
+            return self.forward_native(x, bias, residual)
         B, S, _ = x.shape
         x2 = x.reshape(B * S, -1)
         q = self.q(x2).view(B, S, self.h, self.dk).transpose(1, 2)
@@ -145,6 +172,7 @@ class T5EncoderTeacher(nn.Module):
                         p.copy_(torch.randn(p.shape, generator=g) * (p.shape[-1] ** -0.5))
         for p in self.parameters():
             p.requires_grad_(False)
+        self.native_attention = True   # False: PyTorch SDPA with a dense bias (the restatement)
         self.eval()
 
     @classmethod
@@ -172,7 +200,27 @@ class T5EncoderTeacher(nn.Module):
         """(B, S) token ids -> (B, S, d_model) last hidden state."""
         B, S = input_ids.shape
         x = self.shared(input_ids)
-        bias = self.encoder.block[0].layer[0].SelfAttention.compute_bias(S, input_ids.device)
+        attn0 = self.encoder.block[0].layer[0].SelfAttention
+        if (x.is_cuda and x.dtype == torch.bfloat16 and self.cfg.d_kv in (64, 128) and S <= 2048
+                and self.native_attention):
+            # key range of every token of the padded batch: its sequence's valid prefix; padding
+            # tokens see themselves only (their outputs are never used)
+            dev = x.device
+            if attention_mask is None:
+                lengths = torch.full((B,), S, device=dev, dtype=torch.int32)
+            else:
+                lengths = attention_mask.sum(dim=1).to(torch.int32)
+            pos = torch.arange(S, device=dev, dtype=torch.int32)[None, :]
+            base = (torch.arange(B, device=dev, dtype=torch.int32) * S)[:, None]
+            valid = pos < lengths[:, None]
+            start = torch.where(valid, base.expand(B, S), base + pos)
+            end = torch.where(valid, (base + lengths[:, None]).expand(B, S), base + pos + 1)
+            fast = {"seq_start": start.reshape(-1).contiguous(), "seq_end": end.reshape(-1).contiguous(),
+                    "table": attn0.compute_bias_table(S, dev)}
+            for blk in self.encoder.block:
+                x = blk(x, fast)
+            return self.encoder.final_layer_norm(x)
+        bias = attn0.compute_bias(S, input_ids.device)
         if attention_mask is not None:
             neg = torch.finfo(torch.float32).min
             bias = bias.float() + (1.0 - attention_mask[:, None, None, :].float()) * neg

@@ -382,6 +382,27 @@ def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=
     return dqkv
 
 
+def fa_bias_fwd(qkv: torch.Tensor, seq_start: torch.Tensor, seq_end: torch.Tensor, bias: torch.Tensor,
+                H: int, D: int, scale: float = 1.0) -> torch.Tensor:
+    """Inference attention with a relative-position bias (T5-style teacher).
+
+    qkv bf16 [T, 3*H*D] (q | k | v, head-major), seq_start / seq_end int32 [T] (key range of every
+    token), bias fp32 [H, 2*S-1] indexed by key - query + S - 1. Returns bf16 [T, H*D]."""
+    _chk(qkv, _BF16, "qkv")
+    _chk(seq_start, torch.int32, "seq_start")
+    _chk(seq_end, torch.int32, "seq_end")
+    _chk(bias, torch.float32, "bias")
+    T = qkv.shape[0]
+    S = (bias.shape[1] + 1) // 2
+    out = torch.empty((T, H * D), dtype=_BF16, device=qkv.device)
+    rc = lib("attention_bias").nplm_fa_bias_fwd(ptr(qkv), ptr(out), ptr(seq_start), ptr(seq_end),
+                                                ptr(bias.contiguous()), c_int(T), c_int(H), c_int(D), c_int(S),
+                                                c_float(scale), ptr(status_word(qkv.device)), stream_ptr())
+    check_rc(rc, "fa_bias_fwd")
+    count_launch()
+    return out
+
+
 def check_status() -> None:
     _lib.check_status()
 

@@ -198,3 +198,52 @@ def test_device_mlm_masking_statistics_and_determinism(cuda_status):
     changed = ((out[sel] != 3) & (out[sel] != ids[sel])).float().mean().item()
     assert abs(masked - 0.8) < 0.01 and 0.08 < changed < 0.11
     assert out[sel].min().item() >= 3
+
+
+@pytest.mark.parametrize("D,H,S,lens", [(64, 4, 160, [160, 37, 101]), (128, 2, 300, [300, 129, 5, 256])])
+def test_bias_attention_matches_dense_softmax(D, H, S, lens, cuda_status):
+    """Relative-position-bias attention (teacher) against a dense fp32 softmax with the same bias and
+    key-padding mask."""
+    from nanoplm_b200.ops import kernels as K
+    torch.manual_seed(0)
+    dev = torch.device("cuda:0")
+    B = len(lens)
+    qkv = (torch.randn(B * S, 3 * H * D, device=dev) * 0.5).to(BF)
+    table = torch.randn(H, 2 * S - 1, device=dev) * 2.0
+    lengths = torch.tensor(lens, device=dev, dtype=torch.int32)
+    pos = torch.arange(S, device=dev, dtype=torch.int32)[None, :]
+    base = (torch.arange(B, device=dev, dtype=torch.int32) * S)[:, None]
+    valid = pos < lengths[:, None]
+    start = torch.where(valid, base.expand(B, S), base + pos).reshape(-1).contiguous()
+    end = torch.where(valid, (base + lengths[:, None]).expand(B, S), base + pos + 1).reshape(-1).contiguous()
+    scale = 0.7
+    out = K.fa_bias_fwd(qkv, start, end, table, H, D, scale).float().view(B, S, H, D)
+    q, k, v = qkv.float().view(B, S, 3, H, D).unbind(2)
+    idx = (torch.arange(S, device=dev)[None, :] - torch.arange(S, device=dev)[:, None]) + S - 1   # [q, k]
+    bias = table[:, idx]                                                                          # [H, S, S]
+    s = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale + bias[None]
+    s = s.masked_fill(~valid[:, None, None, :], float("-inf"))
+    ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v)
+    for b, n in enumerate(lens):
+        err = (out[b, :n] - ref[b, :n]).abs().max().item()
+        assert err < 0.03, (b, err)
+
+
+def test_teacher_native_attention_matches_sdpa(cuda_status):
+    from nanoplm_b200.config.schema import TeacherConfig
+    from nanoplm_b200.models.teacher import T5EncoderTeacher
+    dev = torch.device("cuda:0")
+    for d_kv in (64, 128):
+        teacher = T5EncoderTeacher(TeacherConfig(d_model=256, d_kv=d_kv, d_ff=512, num_layers=2, num_heads=4),
+                                   seed=3).to(dev).to(BF)
+        ids = torch.randint(3, 20, (3, 200), device=dev)
+        mask = torch.ones(3, 200, dtype=torch.long, device=dev)
+        mask[1, 150:] = 0
+        mask[2, 31:] = 0
+        teacher.native_attention = True
+        a = teacher(ids, mask).float()
+        teacher.native_attention = False
+        b = teacher(ids, mask).float()
+        m = mask.bool()
+        err = (a[m] - b[m]).abs().max().item()
+        assert err < 0.08 * b[m].abs().max().item() + 0.02, (d_kv, err)
