@@ -149,7 +149,16 @@ def run_own(args) -> dict:
     K, W = args.steps, args.warmup
     set_seed(42)
     tok = ProtTokenizer()
-    model = ProtEncoderMLM(ModelConfig(**MODEL), tok)
+    model_kw = dict(MODEL)
+    if args.variant == "moe":        # every 2nd MLP -> 64 SwiGLU experts (I = 512), top-2
+        from nanoplm_b200.config.schema import MoEConfig
+        model_kw["moe"] = MoEConfig(num_experts=64, top_k=2, expert_intermediate_size=512, every_n_layers=2)
+    elif args.variant == "conv_mhc":  # varlen depthwise conv (k = 7) + 4 hyper-connection streams
+        model_kw.update(conv_kernel_size=7, mhc_streams=4)
+    elif args.variant == "fp8":
+        from nanoplm_b200.ops import functional as _ops
+        _ops.set_fp8(True)
+    model = ProtEncoderMLM(ModelConfig(**model_kw), tok)
     engine = ShardedEngine(model, AdamWHyper(lr=1e-3, max_grad_norm=1.0), device,
                            compute_dtype=torch.bfloat16, fused_comm=not args.no_fused_comm)
     model.train()
@@ -232,6 +241,14 @@ def run_own(args) -> dict:
            "gpu_launches": launches, "final_loss": last_loss,
            "raw_tokens_per_sec": K * MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN / (ms / 1e3),
            "fused_comm": engine.fused is not None, "loaded_libs": [Path(p).name for p in _lib.loaded_libraries()]}
+    if args.variant != "default":
+        res["variant"] = args.variant
+        res["config"]["model"] += {"moe": " + MoE (64 experts, top-2, I 512) on every 2nd layer",
+                                   "conv_mhc": " + varlen depthwise conv (k 7) + 4 mHC streams",
+                                   "fp8": " with e4m3 block128 linear layers (not the headline precision)"}[args.variant]
+        res["parameters"] = engine.num_parameters()
+        if args.variant == "fp8":
+            res["dtype"] = "fp8-e4m3 linears, bf16 elsewhere"
     if world > 1:
         dist.destroy_process_group()
     return res if rank == 0 else {}
@@ -364,6 +381,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("own", "reference"), default="own")
     ap.add_argument("--no-fused-comm", action="store_true", help="use NCCL collectives in the optimizer step")
+    ap.add_argument("--variant", choices=("default", "moe", "conv_mhc", "fp8"), default="default",
+                    help="own arm only: optional model extensions (the headline number is 'default')")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     res = run_reference(args) if args.impl == "reference" else run_own(args)

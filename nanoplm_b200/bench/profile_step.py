@@ -20,6 +20,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--optimizer-step", action="store_true")
+    ap.add_argument("--variant", choices=("default", "moe", "conv_mhc"), default="default")
     args = ap.parse_args()
 
     from nanoplm_b200.config.schema import ModelConfig
@@ -34,12 +35,21 @@ def main() -> None:
     dev = torch.device("cuda:0")
     torch.manual_seed(0)
     tok = ProtTokenizer()
+    extra = {}
+    if args.variant == "moe":
+        from nanoplm_b200.config.schema import MoEConfig
+        extra["moe"] = MoEConfig(num_experts=64, top_k=2, expert_intermediate_size=512, every_n_layers=2)
+    elif args.variant == "conv_mhc":
+        extra.update(conv_kernel_size=7, mhc_streams=4)
     model = ProtEncoderMLM(ModelConfig(hidden_size=1024, intermediate_size=2048, num_hidden_layers=args.layers,
-                                       num_attention_heads=16, max_position_embeddings=1024), tok)
+                                       num_attention_heads=16, max_position_embeddings=1024, **extra), tok)
     with torch.no_grad():
         for layer in model.model.layers:
             layer.attn.Wo.weight.normal_(0, 0.02)
-            layer.mlp.Wo.weight.normal_(0, 0.02)
+            if hasattr(layer.mlp, "Wo"):
+                layer.mlp.Wo.weight.normal_(0, 0.02)
+            else:
+                layer.mlp.experts_Wo.normal_(0, 0.02)
     engine = ShardedEngine(model, AdamWHyper(lr=1e-4), dev)
     model.train()
     seqs = synthetic_token_sequences(args.seqs, 19, 511, seed=7)
