@@ -27,6 +27,16 @@ __device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
   }
 }
 
+__device__ __forceinline__ void unpack8x(const uint4& u, float (&f)[8]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 t = unpack_bf16x2(w[e]);
+    f[2 * e] = t.x;
+    f[2 * e + 1] = t.y;
+  }
+}
+
 __device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
   uint4 u;
   uint32_t* w = reinterpret_cast<uint32_t*>(&u);
@@ -139,32 +149,64 @@ mhc_read_kernel(const __nv_bfloat16* __restrict__ X, const float* __restrict__ a
 }
 
 // Xn[t][i][:] = sum_j R[t][i][j] X[t][j][:] + beta[t][i] y[t][:]
+// N = number of streams (compile-time, so every per-stream array stays in registers).
+template <int N>
 __global__ void __launch_bounds__(256)
 mhc_write_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ y,
                  const float* __restrict__ R, const float* __restrict__ beta,
-                 __nv_bfloat16* __restrict__ Xn, int T, int n, int C) {
+                 __nv_bfloat16* __restrict__ Xn, int T, int C) {
   const int vec = C >> 3;
   const long long total = static_cast<long long>(T) * vec;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int t = static_cast<int>(idx / vec);
     const int c = static_cast<int>(idx % vec) * 8;
-    float xv[MAX_STREAMS][8], yv[8];
-    for (int j = 0; j < n; ++j) ld8(X + (static_cast<size_t>(t) * n + j) * C + c, xv[j]);
+    uint4 xr[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      xr[j] = __ldg(reinterpret_cast<const uint4*>(X + (static_cast<size_t>(t) * N + j) * C + c));
+    float yv[8];
     ld8(y + static_cast<size_t>(t) * C + c, yv);
-    for (int i = 0; i < n; ++i) {
-      float acc[8];
-      const float b = beta[t * n + i];
+    float acc[N][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = b * yv[e];
-      for (int j = 0; j < n; ++j) {
-        const float rr = R[(t * n + i) * n + j];
+    for (int i = 0; i < N; ++i) {
+      const float bt = beta[t * N + i];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += rr * xv[j][e];
+      for (int e = 0; e < 8; ++e) acc[i][e] = bt * yv[e];
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      float xv[8];
+      unpack8x(xr[j], xv);
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const float rr = R[(t * N + i) * N + j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] += rr * xv[e];
       }
-      st8(Xn + (static_cast<size_t>(t) * n + i) * C + c, acc);
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) st8(Xn + (static_cast<size_t>(t) * N + i) * C + c, acc[i]);
+  }
+}
+
+// Sum of V <= 32 per-lane values over the warp: lane l (l < 32) returns the total of value l.
+// Five exchange rounds that halve the number of live values (31 shuffles instead of 5 per value).
+template <int V>
+__device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {
+#pragma unroll
+  for (int i = V; i < 32; ++i) v[i] = 0.f;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < off; ++i) {
+      const float keep = upper ? v[i + off] : v[i];
+      const float send = upper ? v[i] : v[i + off];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
     }
   }
+  return v[0];
 }
 
 // Backward of read and / or write, one warp per token (dXn == null: read part only, dh == null:
@@ -173,95 +215,91 @@ mhc_write_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __res
 //   dX[t][j][:]  = sum_i R[t][i][j] dXn[t][i][:] + alpha[t][j] dh[t][:]
 //   dy[t][:]     = sum_i beta[t][i] dXn[t][i][:]
 //   dR[t][i][j]  = <dXn[t][i], X[t][j]>,  dbeta[t][i] = <dXn[t][i], y[t]>,  dalpha[t][j] = <dh[t], X[t][j]>
-__global__ void __launch_bounds__(256)
+// All loads of a 256-channel slice are issued before the first use and kept packed in registers.
+template <int N>
+__global__ void __launch_bounds__(256, 2)
 mhc_bwd_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ y,
                const float* __restrict__ R, const float* __restrict__ alpha, const float* __restrict__ beta,
                const __nv_bfloat16* __restrict__ dXn, const __nv_bfloat16* __restrict__ dh,
                __nv_bfloat16* __restrict__ dX, __nv_bfloat16* __restrict__ dy, float* __restrict__ dR,
-               float* __restrict__ dalpha, float* __restrict__ dbeta, int T, int n, int C) {
+               float* __restrict__ dalpha, float* __restrict__ dbeta, int T, int C) {
+  static_assert(N * N + 2 * N <= 32, "too many streams for the warp-transpose reduction");
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const bool has_w = dXn != nullptr, has_r = dh != nullptr;
   for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
-    float sR[MAX_STREAMS][MAX_STREAMS], sB[MAX_STREAMS], sA[MAX_STREAMS];
+    // sums[i * N + j] = dR[i][j], sums[N*N + i] = dbeta[i], sums[N*N + N + j] = dalpha[j]
+    float sums[32];
 #pragma unroll
-    for (int i = 0; i < MAX_STREAMS; ++i) {
-      sB[i] = sA[i] = 0.f;
+    for (int i = 0; i < 32; ++i) sums[i] = 0.f;
+    float rc[N][N], bt[N], al[N];
 #pragma unroll
-      for (int j = 0; j < MAX_STREAMS; ++j) sR[i][j] = 0.f;
+    for (int i = 0; i < N; ++i) {
+      bt[i] = has_w ? beta[t * N + i] : 0.f;
+      al[i] = has_r ? alpha[t * N + i] : 0.f;
+#pragma unroll
+      for (int j = 0; j < N; ++j) rc[i][j] = has_w ? R[(t * N + i) * N + j] : 0.f;
     }
+#pragma unroll 1
     for (int c = lane * 8; c < C; c += 256) {
-      float xv[MAX_STREAMS][8], gv[MAX_STREAMS][8], yv[8], hv[8];
+      uint4 xr[N], gr[N], yr = make_uint4(0u, 0u, 0u, 0u), hr = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int j = 0; j < MAX_STREAMS; ++j) {
-        if (j < n) {
-          ld8(X + (static_cast<size_t>(t) * n + j) * C + c, xv[j]);
-          if (has_w) {
-            ld8(dXn + (static_cast<size_t>(t) * n + j) * C + c, gv[j]);
-          } else {
+      for (int j = 0; j < N; ++j) {
+        xr[j] = __ldg(reinterpret_cast<const uint4*>(X + (static_cast<size_t>(t) * N + j) * C + c));
+        gr[j] = has_w ? __ldg(reinterpret_cast<const uint4*>(dXn + (static_cast<size_t>(t) * N + j) * C + c))
+                      : make_uint4(0u, 0u, 0u, 0u);
+      }
+      if (has_w) yr = __ldg(reinterpret_cast<const uint4*>(y + static_cast<size_t>(t) * C + c));
+      if (has_r) hr = __ldg(reinterpret_cast<const uint4*>(dh + static_cast<size_t>(t) * C + c));
+      float yv[8], hv[8];
+      unpack8x(yr, yv);
+      unpack8x(hr, hv);
+      float dyv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float o[N][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) gv[j][e] = 0.f;
-          }
+      for (int j = 0; j < N; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[j][e] = al[j] * hv[e];
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        float xv[8];
+        unpack8x(xr[j], xv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sums[N * N + N + j] += hv[e] * xv[e];
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          float gv[8];
+          unpack8x(gr[i], gv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sums[i * N + j] += gv[e] * xv[e];
         }
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) yv[e] = hv[e] = 0.f;
-      if (has_w) ld8(y + static_cast<size_t>(t) * C + c, yv);
-      if (has_r) ld8(dh + static_cast<size_t>(t) * C + c, hv);
-      float dyv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int i = 0; i < N; ++i) {
+        float gv[8];
+        unpack8x(gr[i], gv);
 #pragma unroll
-      for (int i = 0; i < MAX_STREAMS; ++i) {
-        if (i < n) {
-          const float b = has_w ? beta[t * n + i] : 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            dyv[e] += b * gv[i][e];
-            sB[i] += gv[i][e] * yv[e];
-            sA[i] += hv[e] * xv[i][e];
-          }
-#pragma unroll
-          for (int j = 0; j < MAX_STREAMS; ++j) {
-            if (j < n) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) sR[i][j] += gv[i][e] * xv[j][e];
-            }
-          }
+        for (int e = 0; e < 8; ++e) {
+          dyv[e] += bt[i] * gv[e];
+          sums[N * N + i] += gv[e] * yv[e];
         }
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[j][e] += rc[i][j] * gv[e];
       }
       if (has_w) st8(dy + static_cast<size_t>(t) * C + c, dyv);
 #pragma unroll
-      for (int j = 0; j < MAX_STREAMS; ++j) {
-        if (j < n) {
-          float o[8];
-          const float a = has_r ? alpha[t * n + j] : 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] = a * hv[e];
-#pragma unroll
-          for (int i = 0; i < MAX_STREAMS; ++i) {
-            if (i < n) {
-              const float rr = has_w ? R[(t * n + i) * n + j] : 0.f;
-#pragma unroll
-              for (int e = 0; e < 8; ++e) o[e] += rr * gv[i][e];
-            }
-          }
-          st8(dX + (static_cast<size_t>(t) * n + j) * C + c, o);
-        }
-      }
+      for (int j = 0; j < N; ++j) st8(dX + (static_cast<size_t>(t) * N + j) * C + c, o[j]);
     }
-    // warp reductions happen on every lane, outside any lane-dependent branch
-#pragma unroll
-    for (int i = 0; i < MAX_STREAMS; ++i) {
-      const float b = warp_sum(sB[i]);
-      const float a = warp_sum(sA[i]);
-      if (lane == 0 && i < n) {
-        if (has_w) dbeta[t * n + i] = b;
-        if (has_r) dalpha[t * n + i] = a;
-      }
-#pragma unroll
-      for (int j = 0; j < MAX_STREAMS; ++j) {
-        const float v = warp_sum(sR[i][j]);
-        if (lane == 0 && i < n && j < n && has_w) dR[(t * n + i) * n + j] = v;
-      }
+    // every lane takes part in the reduction; lane l ends up with the total of sums[l]
+    const float total = warp_transpose_sum<N * N + 2 * N>(sums, lane);
+    if (lane < N * N) {
+      if (has_w) dR[t * N * N + lane] = total;
+    } else if (lane < N * N + N) {
+      if (has_w) dbeta[t * N + (lane - N * N)] = total;
+    } else if (lane < N * N + 2 * N) {
+      if (has_r) dalpha[t * N + (lane - N * N - N)] = total;
     }
   }
 }
@@ -311,10 +349,19 @@ extern "C" int nplm_mhc_read(const void* X, const float* alpha, void* h, int T, 
 extern "C" int nplm_mhc_write(const void* X, const void* y, const float* R, const float* beta, void* Xn,
                               int T, int n, int C, cudaStream_t st) {
   if (T <= 0) return 0;
-  if ((C % 8) || n < 1 || n > MAX_STREAMS) return -3;
-  mhc_write_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(X), reinterpret_cast<const __nv_bfloat16*>(y), R, beta,
-      reinterpret_cast<__nv_bfloat16*>(Xn), T, n, C);
+  if ((C % 8) || n < 1 || n > 4) return -3;
+  const int grid = grid_for(static_cast<long long>(T) * (C / 8), 256);
+#define NPLM_MHC_WRITE(N_)                                                                              \
+  mhc_write_kernel<N_><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(X),                  \
+                                             reinterpret_cast<const __nv_bfloat16*>(y), R, beta,         \
+                                             reinterpret_cast<__nv_bfloat16*>(Xn), T, C)
+  switch (n) {
+    case 1: NPLM_MHC_WRITE(1); break;
+    case 2: NPLM_MHC_WRITE(2); break;
+    case 3: NPLM_MHC_WRITE(3); break;
+    default: NPLM_MHC_WRITE(4); break;
+  }
+#undef NPLM_MHC_WRITE
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -322,13 +369,21 @@ extern "C" int nplm_mhc_bwd(const void* X, const void* y, const float* R, const 
                             const float* beta, const void* dXn, const void* dh, void* dX, void* dy,
                             float* dR, float* dalpha, float* dbeta, int T, int n, int C, cudaStream_t st) {
   if (T <= 0) return 0;
-  if ((C % 8) || n < 1 || n > MAX_STREAMS) return -3;
+  if ((C % 8) || n < 1 || n > 4) return -3;
   int blocks = (T + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  mhc_bwd_kernel<<<blocks, 256, 0, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(X), reinterpret_cast<const __nv_bfloat16*>(y), R, alpha, beta,
-      reinterpret_cast<const __nv_bfloat16*>(dXn), reinterpret_cast<const __nv_bfloat16*>(dh),
-      reinterpret_cast<__nv_bfloat16*>(dX), reinterpret_cast<__nv_bfloat16*>(dy), dR, dalpha, dbeta, T, n, C);
+#define NPLM_MHC_BWD(N_)                                                                                  \
+  mhc_bwd_kernel<N_><<<blocks, 256, 0, st>>>(                                                              \
+      reinterpret_cast<const __nv_bfloat16*>(X), reinterpret_cast<const __nv_bfloat16*>(y), R, alpha, beta, \
+      reinterpret_cast<const __nv_bfloat16*>(dXn), reinterpret_cast<const __nv_bfloat16*>(dh),              \
+      reinterpret_cast<__nv_bfloat16*>(dX), reinterpret_cast<__nv_bfloat16*>(dy), dR, dalpha, dbeta, T, C)
+  switch (n) {
+    case 1: NPLM_MHC_BWD(1); break;
+    case 2: NPLM_MHC_BWD(2); break;
+    case 3: NPLM_MHC_BWD(3); break;
+    default: NPLM_MHC_BWD(4); break;
+  }
+#undef NPLM_MHC_BWD
   return static_cast<int>(cudaGetLastError());
 }
 

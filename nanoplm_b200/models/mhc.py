@@ -63,13 +63,13 @@ class _WriteFn(torch.autograd.Function):
 
 
 def mhc_read(X, alpha):
-    if X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 8:
+    if X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 4:
         return _ReadFn.apply(X, alpha)
     return torch.einsum("ti,tic->tc", alpha.to(X.dtype), X)
 
 
 def mhc_write(X, y, R, beta):
-    if X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 8:
+    if X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 4:
         return _WriteFn.apply(X, y, R, beta)
     return torch.einsum("tij,tjc->tic", R.to(X.dtype), X) + beta.to(X.dtype)[:, :, None] * y[:, None, :]
 
@@ -88,9 +88,15 @@ class HyperConnection(nn.Module):
 
     def coefficients(self, X):
         n = self.n
-        z = X.float().mean(dim=1)
-        z = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + self.eps) * self.coef_norm_weight.float()
-        d = torch.tanh(F.linear(z, self.coef_proj.weight.float()))
+        if X.is_cuda and X.dtype == torch.bfloat16 and self.coef_proj.weight.shape[0] % 8 == 0:
+            # stream mean without an fp32 copy of X, then the RMSNorm and GEMM kernels of this package
+            from nanoplm_b200.ops import functional as ops
+            zn = ops.norm(X.mean(dim=1), self.coef_norm_weight, self.eps, rms=True)
+            d = torch.tanh(ops.linear(zn, self.coef_proj.weight).float())
+        else:
+            z = X.float().mean(dim=1)
+            z = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + self.eps) * self.coef_norm_weight.float()
+            d = torch.tanh(F.linear(z, self.coef_proj.weight.float()))
         s = self.dyn_scale.float()
         alpha = torch.softmax(self.static_alpha.float() + s[0] * d[:, :n], dim=-1)
         beta = 2.0 * torch.sigmoid(self.static_beta.float() + s[1] * d[:, n:2 * n])
