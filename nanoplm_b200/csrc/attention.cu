@@ -790,18 +790,22 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
                 idesc_s, k > 0 ? 1u : 0u);
     umma_commit(bar_s);
   };
-  auto load_stats = [&](int buf, int q0) {
-    if (tid < 128) {
-      const int q = q0 + tid;
-      s_lse[buf * 128 + tid] = q < T ? args.lse[static_cast<size_t>(h) * T + q] * LOG2E : 0.f;
-    } else {
-      const int q = q0 + tid - 128;
-      s_delta[buf * 128 + tid - 128] = q < T ? args.delta[static_cast<size_t>(h) * T + q] : 0.f;
-    }
+  // Row statistics of a query tile: threads 0-127 fetch lse (scaled to log2), 128-255 delta. The
+  // global load and the shared-memory store are separate steps, so the value can travel while
+  // the thread works on the current tile.
+  auto fetch_stat = [&](int q0) -> float {
+    const bool first = tid < 128;
+    const int q = q0 + (first ? tid : tid - 128);
+    if (q >= T) return 0.f;
+    return first ? __ldg(args.lse + static_cast<size_t>(h) * T + q) * LOG2E
+                 : __ldg(args.delta + static_cast<size_t>(h) * T + q);
   };
-
+  auto store_stat = [&](int buf, float v) {
+    if (tid < 128) s_lse[buf * 128 + tid] = v;
+    else s_delta[buf * 128 + tid - 128] = v;
+  };
   if (n_q > 0) {
-    load_stats(0, q_lo);
+    store_stat(0, fetch_stat(q_lo));
     if (tid == 0) {
       mbar_arrive_expect_tx(bar_kv, 2 * FA_TILE_BYTES);
       tma_load_2d(sK, &tmQKV, bar_kv, colK, kv0);
@@ -821,8 +825,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
   for (int j = 0; j < n_q; ++j) {
     const int buf = j & 1;
     const int q0 = q_lo + j * FA_T;
+    float next_stat = 0.f;
     if (j + 1 < n_q) {
-      load_stats(buf ^ 1, q0 + FA_T);
+      next_stat = fetch_stat(q0 + FA_T);   // stored to shared memory after this tile's softmax
       if (tid == 0) load_q_tile(buf ^ 1, q0 + FA_T);
     }
     __syncthreads();  // stats of tile j visible (written one iteration ahead, or before the loop)
@@ -844,21 +849,25 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       tmem_ld32(tdP + lane_addr + cbase, rp);
       tmem_ld_wait();
       uint32_t pk[16], dk[16];
+      const float4* lse4 = reinterpret_cast<const float4*>(s_lse + buf * 128 + cbase);
+      const float4* del4 = reinterpret_cast<const float4*>(s_delta + buf * 128 + cbase);
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float p[2], ds[2];
+      for (int e = 0; e < 32; e += 4) {
+        const float4 l4 = lse4[e >> 2], d4 = del4[e >> 2];   // broadcast reads, 4 columns each
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+        float p[4], ds[4];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int qc = cbase + e + u;
-          const int q = q0 + qc;
+        for (int u = 0; u < 4; ++u) {
+          const int q = q0 + cbase + e + u;
           float pv = 0.f;
-          if (q >= lo && q < hi)
-            pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -s_lse[buf * 128 + qc]));
+          if (q >= lo && q < hi) pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -ls[u]));
           p[u] = pv;
-          ds[u] = pv * (__uint_as_float(rp[e + u]) - s_delta[buf * 128 + qc]);
+          ds[u] = pv * (__uint_as_float(rp[e + u]) - dl[u]);
         }
         pk[e >> 1] = pack_bf16x2(p[0], p[1]);
+        pk[(e >> 1) + 1] = pack_bf16x2(p[2], p[3]);
         dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
+        dk[(e >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
       }
       const int chunk0 = (c >> 5) * 4;
 #pragma unroll
@@ -870,6 +879,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
             make_uint4(dk[4 * q4], dk[4 * q4 + 1], dk[4 * q4 + 2], dk[4 * q4 + 3]);
       }
     }
+    if (j + 1 < n_q) store_stat(buf ^ 1, next_stat);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();

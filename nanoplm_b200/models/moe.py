@@ -70,6 +70,23 @@ class MoEMLP(nn.Module):
         self.experts_Wi = nn.Parameter(torch.empty(self.local_experts, 2 * self.inter, cfg.hidden_size).uniform_(-bound, bound))
         self.experts_Wo = nn.Parameter(torch.zeros(self.local_experts, cfg.hidden_size, self.inter))
 
+    def shard_experts(self, group) -> None:
+        """Keeps only this rank's experts (num_experts / world of them, a contiguous block) and routes
+        the others' rows to their owners. Every rank must call this with identically initialised
+        weights; the optimizer must treat the expert weights as rank-local
+        (nanoplm_b200.parallel.expert_engine)."""
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.num_experts % world:
+            raise ValueError("num_experts must be divisible by the expert-parallel size")
+        if self.ep_world != 1:
+            raise RuntimeError("experts are already sharded")
+        L = self.num_experts // world
+        self.ep_group, self.ep_world, self.ep_rank, self.local_experts = group, world, rank, L
+        self.experts_Wi = nn.Parameter(self.experts_Wi.data[rank * L:(rank + 1) * L].clone())
+        self.experts_Wo = nn.Parameter(self.experts_Wo.data[rank * L:(rank + 1) * L].clone())
+        self._comm = None
+
     def _run_experts(self, rows: torch.Tensor, counts: list[int]) -> torch.Tensor:
         """rows sorted by local expert; counts[e] rows belong to local expert e."""
         out = torch.empty((rows.shape[0], self.hidden), dtype=rows.dtype, device=rows.device)

@@ -189,14 +189,18 @@ class ShardedEngine:
                 [lr, h.beta1, h.beta2, h.eps, wd, bc1, bc2, grad_scale, h.max_grad_norm])
         self._hyper_dev.copy_(self._hyper_host, non_blocking=True)
 
-    def step(self, lr: float, grad_accum: int = 1) -> torch.Tensor:
-        """One optimizer step. Returns the global gradient norm (a device scalar; no host sync)."""
+    def step(self, lr: float, grad_accum: int = 1, extra_sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One optimizer step. Returns the global gradient norm (a device scalar; no host sync).
+        extra_sumsq: sum of squares of gradients held outside this engine's flat buffer (already
+        summed over ranks, same scaling); it enters the clipping norm."""
         self.collect_autograd_grads()
         self.step_count += 1
         _invalidate_fp8_weights()
         grad_scale = 1.0 / (grad_accum * self.world)
         self._fill_hyper(lr, grad_scale)
         if self.fused is not None:
+            if extra_sumsq is not None:
+                raise ValueError("extra_sumsq is not supported by the fused communication step")
             return self.fused.step(lr, grad_scale)
         # 1. reduce-scatter: the owned slice of main_grad becomes the sum over ranks
         if self.distributed:
@@ -217,6 +221,8 @@ class ShardedEngine:
             self._sumsq += shard_grad.double().pow(2).sum().float()
         if self.distributed:
             dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=self.pg)
+        if extra_sumsq is not None:
+            self._sumsq += extra_sumsq.to(self._sumsq.dtype).reshape(1)
         grad_norm = self._sumsq.sqrt() * grad_scale
         # 3. clip + AdamW on the owned slice, decay part then no-decay part
         new_shard = self.flat_params[self.lo:self.hi]
@@ -238,14 +244,19 @@ class ShardedEngine:
         return grad_norm
 
     def _adamw_reference(self, sl, grad, out, group, lr, grad_scale) -> None:
+        self._adamw_cpu(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], grad[sl], out[sl], group, lr,
+                        grad_scale)
+
+    def _adamw_cpu(self, p, m, v, grad, out, group, lr, grad_scale) -> None:
+        """fp32 PyTorch restatement of the AdamW kernel (clip by the global norm in self._sumsq)."""
         h = self.hyper
         wd = h.weight_decay if group == 0 else 0.0
         norm = float(self._sumsq.sqrt()) * grad_scale
         scale = grad_scale
         if h.max_grad_norm > 0:
             scale *= min(1.0, h.max_grad_norm / (norm + 1e-6))
-        g = grad[sl] * scale
-        p, m, v = self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl]
+        g = grad * scale
+        sl = slice(None)
         t = self.step_count
         p.mul_(1.0 - lr * wd)
         m.mul_(h.beta1).add_(g, alpha=1 - h.beta1)

@@ -1,0 +1,181 @@
+"""Optimizer engine for models whose MoE experts are split over the data-parallel ranks
+(`pretraining.expert_parallel_size` = number of ranks).
+
+Dense parameters (attention, dense MLPs, routers, norms, embeddings) go through the sharded
+data-parallel engine unchanged: gradients are summed over ranks, AdamW runs on the owned slice,
+the bf16 copy is all-gathered. Expert weights are rank-local: every rank owns
+num_experts / world experts, their gradients already contain the contributions of ALL ranks'
+tokens (the rows travelled to the owner in the forward pass and their gradients came back in the
+backward pass), so they are neither reduced nor gathered; they only share the scaling
+1 / (grad_accum * world) and the global clipping norm with the dense part.
+
+The reference has neither MoE layers nor expert parallelism.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from nanoplm_b200.parallel.engine import ALIGN, AdamWHyper, ParamSlot, ShardedEngine, _round_up
+
+EXPERT_PARAM_MARKERS = ("experts_Wi", "experts_Wo")
+
+
+def is_expert_param(name: str) -> bool:
+    return any(name.endswith(m) for m in EXPERT_PARAM_MARKERS)
+
+
+def shard_model_experts(model: torch.nn.Module, group) -> int:
+    """Splits the experts of every MoE layer of `model` over the ranks of `group` (in place).
+    Returns the number of MoE layers touched."""
+    from nanoplm_b200.models.moe import MoEMLP
+    n = 0
+    for m in model.modules():
+        if isinstance(m, MoEMLP):
+            m.shard_experts(group)
+            n += 1
+    return n
+
+
+class ExpertParallelEngine(ShardedEngine):
+    def __init__(self, model, hyper: AdamWHyper, device, process_group=None,
+                 compute_dtype: torch.dtype = torch.bfloat16):
+        expert_names = [n for n, _ in model.named_parameters() if is_expert_param(n)]
+        if not expert_names:
+            raise ValueError("the model has no expert parameters (model.moe is not configured)")
+        super().__init__(model, hyper, device, process_group, compute_dtype=compute_dtype, fused_comm=False,
+                         exclude=expert_names)
+        named = dict(model.named_parameters())
+        self.x_slots: list[ParamSlot] = []
+        off = 0
+        for n in expert_names:
+            p = named[n]
+            self.x_slots.append(ParamSlot(n, p, off, p.numel(), p.shape, True))
+            off = _round_up(off + p.numel(), ALIGN)
+        self.x_total = max(off, ALIGN)
+        dev = self.device
+        self.x_params = torch.zeros(self.x_total, dtype=self.compute_dtype, device=dev)
+        self.x_grad = torch.zeros(self.x_total, dtype=torch.float32, device=dev)
+        self.x_master = torch.zeros(self.x_total, dtype=torch.float32, device=dev)
+        self.x_exp_avg = torch.zeros(self.x_total, dtype=torch.float32, device=dev)
+        self.x_exp_avg_sq = torch.zeros(self.x_total, dtype=torch.float32, device=dev)
+        self._x_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        for s in self.x_slots:
+            self.x_master[s.offset:s.offset + s.numel] = s.param.detach().to(dev, torch.float32).reshape(-1)
+        self.x_params.copy_(self.x_master.to(self.compute_dtype))
+        self._rebind_experts()
+
+    def _rebind_experts(self) -> None:
+        for s in self.x_slots:
+            s.param.data = self.x_params[s.offset:s.offset + s.numel].view(s.shape)
+            s.param.grad = None
+            if self.on_cuda:
+                s.param.main_grad = self.x_grad[s.offset:s.offset + s.numel].view(s.shape)
+
+    def num_parameters(self) -> int:
+        return super().num_parameters() + self.world * sum(s.numel for s in self.x_slots)
+
+    def collect_autograd_grads(self) -> None:
+        super().collect_autograd_grads()
+        for s in self.x_slots:
+            g = s.param.grad
+            if g is not None:
+                self.x_grad[s.offset:s.offset + s.numel].add_(g.reshape(-1).float())
+                s.param.grad = None
+
+    def zero_grad(self) -> None:
+        super().zero_grad()
+        self.x_grad.zero_()
+        for s in self.x_slots:
+            s.param.grad = None
+
+    def step(self, lr: float, grad_accum: int = 1, extra_sumsq=None) -> torch.Tensor:
+        self.collect_autograd_grads()
+        # squared norm of all experts' gradients: every rank holds different experts
+        self._x_sumsq.zero_()
+        if self.on_cuda:
+            from nanoplm_b200.ops import kernels as K
+            K.sumsq_(self.x_grad, self._x_sumsq)
+        else:
+            self._x_sumsq += self.x_grad.double().pow(2).sum().float()
+        if self.distributed:
+            dist.all_reduce(self._x_sumsq, op=dist.ReduceOp.SUM, group=self.pg)
+        norm = super().step(lr, grad_accum, extra_sumsq=self._x_sumsq)   # leaves the global norm in _sumsq
+        grad_scale = 1.0 / (grad_accum * self.world)
+        if self.on_cuda:
+            from nanoplm_b200.ops import kernels as K
+            K.adamw_(self.x_master, self.x_exp_avg, self.x_exp_avg_sq, self.x_grad, self.x_params,
+                     self._hyper_dev[0], self._sumsq, zero_grad=False)
+        else:
+            self._adamw_cpu(self.x_master, self.x_exp_avg, self.x_exp_avg_sq, self.x_grad, self.x_params, 0, lr,
+                            grad_scale)
+        self.x_grad.zero_()
+        return norm
+
+    # ---- checkpoint: experts are gathered along their first axis ---------------------------------
+    def _gather_experts(self, flat: torch.Tensor) -> dict:
+        """name -> full tensor [num_experts, ...] (fp32, CPU); collective on every rank."""
+        out = {}
+        for s in self.x_slots:
+            local = flat[s.offset:s.offset + s.numel].view(s.shape).contiguous()
+            if self.distributed:
+                parts = [torch.empty_like(local) for _ in range(self.world)]
+                dist.all_gather(parts, local, group=self.pg)
+                local = torch.cat(parts, dim=0)
+            out[s.name] = local.float().cpu()
+        return out
+
+    def _scatter_experts(self, flat: torch.Tensor, tensors: dict, strict: bool) -> None:
+        for s in self.x_slots:
+            t = tensors.get(s.name)
+            if t is None:
+                if strict:
+                    raise KeyError(f"missing expert tensor in checkpoint: {s.name}")
+                continue
+            L = s.shape[0]
+            mine = t[self.rank * L:(self.rank + 1) * L]
+            if tuple(mine.shape) != tuple(s.shape):
+                raise ValueError(f"{s.name}: checkpoint holds {tuple(t.shape)}, this rank needs {tuple(s.shape)} "
+                                 f"x {self.world} ranks")
+            flat[s.offset:s.offset + s.numel] = mine.to(flat.device, torch.float32).reshape(-1)
+
+    def full_state_dict_model(self, extra_tied=None) -> dict:
+        sd = super().full_state_dict_model(extra_tied)
+        sd.update(self._gather_experts(self.x_master))
+        return sd
+
+    def load_model_state_dict(self, sd: dict, strict: bool = True) -> None:
+        sd = {k[len("_orig_mod."):] if k.startswith("_orig_mod.") else k: v for k, v in sd.items()}
+        expert = {k: v for k, v in sd.items() if is_expert_param(k)}
+        super().load_model_state_dict({k: v for k, v in sd.items() if k not in expert}, strict)
+        self._scatter_experts(self.x_master, expert, strict)
+        self.x_params.copy_(self.x_master.to(self.compute_dtype))
+        self._rebind_experts()
+
+    def optimizer_state_dict(self) -> dict:
+        sd = super().optimizer_state_dict()
+        sd["expert_parallel"] = {"exp_avg": self._gather_experts(self.x_exp_avg),
+                                 "exp_avg_sq": self._gather_experts(self.x_exp_avg_sq)}
+        return sd
+
+    def load_optimizer_state_dict(self, sd: dict) -> None:
+        super().load_optimizer_state_dict(sd)
+        extra = sd.get("expert_parallel")
+        if extra:
+            self._scatter_experts(self.x_exp_avg, extra["exp_avg"], strict=False)
+            self._scatter_experts(self.x_exp_avg_sq, extra["exp_avg_sq"], strict=False)
+
+    def shard_state(self) -> dict:
+        st = super().shard_state()
+        st["experts"] = {"master": self.x_master.cpu(), "exp_avg": self.x_exp_avg.cpu(),
+                         "exp_avg_sq": self.x_exp_avg_sq.cpu()}
+        return st
+
+    def load_shard_state(self, st: dict) -> None:
+        super().load_shard_state(st)
+        ex = st.get("experts")
+        if ex:
+            self.x_master.copy_(ex["master"])
+            self.x_exp_avg.copy_(ex["exp_avg"])
+            self.x_exp_avg_sq.copy_(ex["exp_avg_sq"])
+            self.x_params.copy_(self.x_master.to(self.compute_dtype))

@@ -207,7 +207,20 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                        beta2=float(cfg.adam_beta2), eps=float(cfg.adam_epsilon),
                        weight_decay=float(cfg.adam_weight_decay), max_grad_norm=float(cfg.max_grad_norm))
     opt_name = str(cfg.optimizer).lower()
-    if opt_name in ("muon", "normuon"):
+    ep_size = int(getattr(cfg, "expert_parallel_size", 1) or 1)
+    if ep_size > 1:
+        # experts split over the data-parallel ranks (peer-memory dispatch / combine on CUDA)
+        if ep_size != world:
+            raise ValueError(f"expert_parallel_size ({ep_size}) must equal the number of ranks ({world}): "
+                             "experts are split over all data-parallel ranks")
+        if opt_name not in ("adamw", "stable_adamw"):
+            raise ValueError("expert parallelism is implemented for the AdamW engine only")
+        from nanoplm_b200.parallel.expert_engine import ExpertParallelEngine, shard_model_experts
+        if shard_model_experts(model, dist.group.WORLD) == 0:
+            raise ValueError("expert_parallel_size > 1 needs a model with model.moe configured")
+        engine = ExpertParallelEngine(model, hyper, device,
+                                      compute_dtype=torch.bfloat16 if use_bf16 else torch.float32)
+    elif opt_name in ("muon", "normuon"):
         from nanoplm_b200.parallel.muon import MuonEngine
         engine = MuonEngine(model, hyper, cfg, device)
     elif opt_name in ("adamw", "stable_adamw"):

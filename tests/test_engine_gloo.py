@@ -121,3 +121,88 @@ def test_two_rank_training_matches_single_rank(tmp_path):
     assert len(opt["param_groups"]) == 2 and opt["param_groups"][1]["weight_decay"] == 0.0
     n_params = sum(len(g["params"]) for g in opt["param_groups"])
     assert n_params == len(eng.slots) and len(opt["state"]) == n_params
+
+
+def _make_moe_model():
+    from nanoplm_b200.config.schema import ModelConfig, MoEConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    torch.manual_seed(0)
+    cfg = ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+                      max_position_embeddings=128,
+                      moe=MoEConfig(num_experts=4, top_k=2, expert_intermediate_size=32, every_n_layers=2))
+    m = ProtEncoderMLM(cfg, ProtTokenizer())
+    with torch.no_grad():
+        for layer in m.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.05)
+            if hasattr(layer.mlp, "Wo"):
+                layer.mlp.Wo.weight.normal_(0, 0.05)
+            else:
+                layer.mlp.experts_Wo.normal_(0, 0.05)
+    return m
+
+
+def _train_moe(rank, world, port, tmp, expert_parallel):
+    """world == 1: replicated experts, gradient accumulation over both micro-batches.
+    world == 2 + expert_parallel: every rank takes one micro-batch and owns half of the experts."""
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.parallel.expert_engine import ExpertParallelEngine, shard_model_experts
+    from nanoplm_b200.runtime.pretrain import TrainStep
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    if world > 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    model = _make_moe_model()
+    hyper = AdamWHyper(lr=5e-3, weight_decay=0.01, max_grad_norm=0.5)
+    if expert_parallel:
+        assert shard_model_experts(model, dist.group.WORLD) == 1
+        eng = ExpertParallelEngine(model, hyper, torch.device("cpu"))
+    else:
+        eng = ShardedEngine(model, hyper, torch.device("cpu"))
+    st = TrainStep(model, eng, WarmupLinearSchedule(5e-3, 2, 100), "cpu")
+    batches = _batches(8)
+    losses = []
+    for step in range(3):
+        losses.append(st.step_from_host(batches[2 * step:2 * step + 2][rank::world]))
+    if world > 1:
+        t = torch.tensor(losses)
+        dist.all_reduce(t)
+        losses = (t / world).tolist()
+    sd = eng.full_state_dict_model()
+    opt = eng.optimizer_state_dict()
+    if rank == 0:
+        torch.save((losses, {k: v.clone() for k, v in sd.items()}, opt.get("expert_parallel")),
+                   os.path.join(tmp, "result.pt"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _run_moe(world, tmp, expert_parallel):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_train_moe, args=(r, world, port, tmp, expert_parallel)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    return torch.load(os.path.join(tmp, "result.pt"))
+
+
+def test_expert_parallel_training_matches_replicated_experts(tmp_path):
+    """Experts split over 2 ranks (rank-local AdamW, shared clipping norm, rows exchanged between
+    ranks) must follow the single-process trajectory with all experts in one place."""
+    d1, d2 = str(tmp_path / "one"), str(tmp_path / "ep")
+    os.makedirs(d1)
+    os.makedirs(d2)
+    l1, sd1, _ = _run_moe(1, d1, False)
+    l2, sd2, extra = _run_moe(2, d2, True)
+    for a, b in zip(l1, l2):
+        assert abs(a - b) < 2e-4, (l1, l2)
+    assert set(sd1) == set(sd2)
+    for k in sd1:
+        assert sd1[k].shape == sd2[k].shape, k            # gathered experts have the full first axis
+        assert torch.allclose(sd1[k], sd2[k], atol=5e-5), k
+    assert extra is not None and all(v.shape[0] == 4 for v in extra["exp_avg"].values())

@@ -255,3 +255,77 @@ def test_all_gather_gemm(tmp_path):
         p.join(240)
         assert p.exitcode == 0, f"rank exited with {p.exitcode}"
     assert os.path.exists(out)
+
+
+def _moe_train_worker(rank, world, port, out_path):
+    """MoE encoder trained for a few steps: world 1 = replicated experts on one GPU; world 2 = experts
+    split over the GPUs through ExpertParallelEngine and the peer-memory dispatch."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from nanoplm_b200.config.schema import ModelConfig, MoEConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.ops import _lib
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.parallel.expert_engine import ExpertParallelEngine, shard_model_experts
+    from nanoplm_b200.runtime.pretrain import TrainStep
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    torch.manual_seed(0)
+    cfg = ModelConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      max_position_embeddings=256,
+                      moe=MoEConfig(num_experts=8, top_k=2, expert_intermediate_size=128, every_n_layers=2))
+    model = ProtEncoderMLM(cfg, ProtTokenizer())
+    with torch.no_grad():
+        for layer in model.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.03)
+            if hasattr(layer.mlp, "Wo"):
+                layer.mlp.Wo.weight.normal_(0, 0.03)
+            else:
+                layer.mlp.experts_Wo.normal_(0, 0.03)
+    hyper = AdamWHyper(lr=2e-3, weight_decay=0.01)
+    if world > 1:
+        assert shard_model_experts(model, dist.group.WORLD) == 1
+        eng = ExpertParallelEngine(model, hyper, dev)
+    else:
+        eng = ShardedEngine(model, hyper, dev)
+    model.train()
+    st = TrainStep(model, eng, WarmupLinearSchedule(2e-3, 2, 100), dev)
+    batches = _batches(8)
+    losses = []
+    for step in range(4):
+        losses.append(st.step_from_host(batches[2 * step:2 * step + 2][rank::world]))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    t = torch.tensor(losses, device=dev)
+    if world > 1:
+        dist.all_reduce(t)
+        t /= world
+    sd = eng.full_state_dict_model()
+    if rank == 0:
+        torch.save({"losses": t.cpu(), "sd": sd}, out_path)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+def test_expert_parallel_training_on_two_gpus(tmp_path):
+    ctx = mp.get_context("spawn")
+    res = {}
+    for world in (1, 2):
+        port = _free_port()
+        out = str(tmp_path / f"moe{world}.pt")
+        procs = [ctx.Process(target=_moe_train_worker, args=(r, world, port, out)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(240)
+            assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+        res[world] = torch.load(out)
+    assert torch.allclose(res[1]["losses"], res[2]["losses"], atol=4e-2), (res[1]["losses"], res[2]["losses"])
+    assert res[2]["losses"][-1] < res[2]["losses"][0]
+    for k, v in res[1]["sd"].items():
+        assert res[2]["sd"][k].shape == v.shape, k
