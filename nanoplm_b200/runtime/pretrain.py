@@ -431,13 +431,33 @@ class TrainStep:
         self._acc = torch.zeros((), dtype=torch.float32, device=self.device)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # host->device copies run on their own stream, one micro-batch ahead of the compute stream
+        self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+
+    def _prefetch(self, b: dict):
+        """Starts the host->device copy of one micro-batch; returns (device batch, ready event)."""
+        self.h2d_bytes += sum(v.numel() * v.element_size() for v in b.values() if torch.is_tensor(v))
+        if self._copy_stream is None:
+            return move_batch(b, self.device), None
+        with torch.cuda.stream(self._copy_stream):
+            moved = move_batch(b, self.device)
+            ready = torch.cuda.Event()
+            ready.record(self._copy_stream)
+        return moved, ready
 
     def _run(self, batches, from_host: bool) -> torch.Tensor:
         self._acc.zero_()
-        for b in batches:
+        pending = self._prefetch(batches[0]) if (from_host and batches) else None
+        for i, b in enumerate(batches):
             if from_host:
-                self.h2d_bytes += sum(v.numel() * v.element_size() for v in b.values() if torch.is_tensor(v))
-                b = move_batch(b, self.device)
+                b, ready = pending
+                pending = self._prefetch(batches[i + 1]) if i + 1 < len(batches) else None
+                if ready is not None:
+                    cur = torch.cuda.current_stream(self.device)
+                    cur.wait_event(ready)
+                    for v in b.values():
+                        if torch.is_tensor(v):
+                            v.record_stream(cur)     # allocated on the copy stream, used on this one
             out = self.model(**model_inputs(b))
             out["loss"].backward()
             self._acc += out["loss"].detach().float()
