@@ -181,7 +181,27 @@ struct Fp8Args {
   int b_block;
   int out_mode;      // 0: bf16 store, 1: fp32 store, 2: fp32 atomic add
   int* status;
+  // All-gather mode (ag_world > 1, block-scaled B only): B's rows and the matching scale columns
+  // are sharded over the ranks. The epilogue warps of all CTAs first copy the other ranks' e4m3
+  // rows (half the bytes of a bf16 gather) and scales out of peer memory into the local full-size
+  // buffers, bump ag_flags[shard], and both the TMA producer and the epilogue wait (bounded) on a
+  // shard's flag before touching it. Tiles are visited shard by shard, the local shard first.
+  int ag_world, ag_rank, ag_rows;
+  const uint8_t* ag_src[8];   // peer r's shard rows (ag_rows x K bytes)
+  const float* ag_ssrc[8];    // peer r's full-size scale buffer [KB][N/128]
+  uint8_t* ag_dst;            // local full B
+  float* ag_sdst;             // local full scale buffer
+  unsigned* ag_flags;         // [ag_world], zeroed before the launch
 };
+
+__device__ __forceinline__ bool f8_wait_shard(const Fp8Args& args, int shard, unsigned target) {
+  const long long t0 = clock64();
+  while (ld_acquire_gpu(args.ag_flags + shard) < target) {
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    __nanosleep(100);
+  }
+  return true;
+}
 
 __global__ void __launch_bounds__(F8_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -201,6 +221,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int num_m = (M + F8_BM - 1) / F8_BM, num_n = (N + F8_BN - 1) / F8_BN;
   const int KB = args.K / F8_BK;
   const int total = num_m * num_n;
+  // work item -> tile origin (all-gather mode: shard by shard, the local one first)
+  auto tile_of = [&](int w, int& m0, int& n0) {
+    if (args.ag_world > 1) {
+      const int n_per = args.ag_rows / F8_BN;
+      const int per_shard = num_m * n_per;
+      const int shard = (args.ag_rank + w / per_shard) % args.ag_world;
+      const int rem = w % per_shard;
+      m0 = (rem / n_per) * F8_BM;
+      n0 = shard * args.ag_rows + (rem % n_per) * F8_BN;
+    } else {
+      m0 = (w / num_n) * F8_BM;
+      n0 = (w % num_n) * F8_BN;
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < F8_STAGES; ++s) {
@@ -230,8 +264,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t ag_seen = 0;
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-        const int m0 = (w / num_n) * F8_BM, n0 = (w % num_n) * F8_BN;
+        int m0, n0;
+        tile_of(w, m0, n0);
+        if (args.ag_world > 1) {
+          const int shard = n0 / args.ag_rows;
+          if (shard != args.ag_rank && !((ag_seen >> shard) & 1u)) {
+            if (!f8_wait_shard(args, shard, gridDim.x)) {
+              atomicExch(args.status, ST_TIMEOUT_PEER);
+              ok = false;
+              break;
+            }
+            ag_seen |= 1u << shard;
+            fence_proxy_async_global();
+          }
+        }
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicExch(args.status, ST_TIMEOUT_EMPTY);
@@ -296,11 +344,47 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     constexpr int HC = F8_BN / 2;  // 64 columns per thread
+    uint32_t ag_seen = 0;
+    if (args.ag_world > 1) {
+      const int et = threadIdx.x - 64;  // 0..255 over the eight epilogue warps
+      const long long shard_vecs = static_cast<long long>(args.ag_rows) * args.K / 16;
+      const long long per_cta = (shard_vecs + gridDim.x - 1) / gridDim.x;
+      const long long v0 = per_cta * blockIdx.x, v1 = min(shard_vecs, v0 + per_cta);
+      const int nb_all = num_n, nb_shard = args.ag_rows / F8_BN;
+      for (int d = 1; d < args.ag_world; ++d) {
+        const int shard = (args.ag_rank + d) % args.ag_world;
+        const uint4* src = reinterpret_cast<const uint4*>(args.ag_src[shard]);
+        uint4* dst = reinterpret_cast<uint4*>(args.ag_dst + static_cast<size_t>(shard) * args.ag_rows * args.K);
+        for (long long v = v0 + et; v < v1; v += 256) dst[v] = src[v];
+        if (blockIdx.x == 0) {   // the scale columns of this shard, every K block
+          for (int i = et; i < KB * nb_shard; i += 256) {
+            const int idx = (i / nb_shard) * nb_all + shard * nb_shard + (i % nb_shard);
+            args.ag_sdst[idx] = args.ag_ssrc[shard][idx];
+          }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (et == 0) red_release_gpu_add(args.ag_flags + shard, 1u);
+      }
+    }
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-      const int m0 = (w / num_n) * F8_BM, n0 = (w % num_n) * F8_BN + half * HC;
+      int m0, n0;
+      tile_of(w, m0, n0);
+      if (args.ag_world > 1) {
+        const int shard = n0 / args.ag_rows;
+        if (shard != args.ag_rank && !((ag_seen >> shard) & 1u)) {
+          if (!f8_wait_shard(args, shard, gridDim.x)) {   // scales of this shard must have landed
+            if (lane == 0) atomicExch(args.status, ST_TIMEOUT_PEER);
+            ok = false;
+            break;
+          }
+          ag_seen |= 1u << shard;
+        }
+      }
+      n0 += half * HC;
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < M;
       float c[HC];
@@ -308,13 +392,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int j = 0; j < HC; ++j) c[j] = 0.f;
       // scales of K block 0; those of block kb + 1 are fetched while block kb is being awaited
       float sa_n = row_ok ? args.sa[row] : 0.f;
-      float sb_n = args.b_block ? args.sb[(n0 >> 7)] : 0.f;
+      float sb_n = args.b_block ? __ldcg(args.sb + (n0 >> 7)) : 0.f;
       for (int kb = 0; kb < KB; ++kb) {
         const float sa = sa_n;
         const float sblk = sb_n * sa;
         if (kb + 1 < KB) {
           sa_n = row_ok ? args.sa[static_cast<size_t>(kb + 1) * M + row] : 0.f;
-          if (args.b_block) sb_n = args.sb[static_cast<size_t>(kb + 1) * num_n + (n0 >> 7)];
+          if (args.b_block) sb_n = __ldcg(args.sb + static_cast<size_t>(kb + 1) * num_n + (n0 >> 7));
         }
         if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
           if (lane == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
@@ -499,6 +583,16 @@ extern "C" int nplm_gemm_fp8(const void* A, const void* B, void* C, const float*
   args.b_block = b_block;
   args.out_mode = out_mode;
   args.status = status;
+  args.ag_world = 0;
+  args.ag_rank = 0;
+  args.ag_rows = 0;
+  args.ag_dst = nullptr;
+  args.ag_sdst = nullptr;
+  args.ag_flags = nullptr;
+  for (int r = 0; r < 8; ++r) {
+    args.ag_src[r] = nullptr;
+    args.ag_ssrc[r] = nullptr;
+  }
   const int total = ((M + F8_BM - 1) / F8_BM) * ((N + F8_BN - 1) / F8_BN);
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -506,4 +600,59 @@ extern "C" int nplm_gemm_fp8(const void* A, const void* B, void* C, const float*
   const int grid = total < sms ? total : sms;
   gemm_fp8_kernel<<<grid, F8_THREADS, F8_SMEM, stream>>>(tmA, tmB, args);
   return static_cast<int>(cudaGetLastError());
+}
+
+// All-gather fused into the fp8 GEMM. b_ptrs[r] / sb_ptrs[r]: rank r's full-size e4m3 weight buffer
+// [N][K] and block-scale buffer [K/128][N/128] in peer-mapped memory; on entry only the rows (and
+// scale columns) of shard r are valid in buffer r. N / world must be a multiple of 128. On return
+// this rank's buffers hold the whole quantised weight. flags: 8 device words.
+extern "C" int nplm_gemm_fp8_ag(const void* A, void* const* b_ptrs, void* C, const float* sa,
+                                void* const* sb_ptrs, int M, int N, int K, int ldc, int out_mode,
+                                int rank, int world, unsigned* flags, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || (N % world) || ((N / world) % F8_BN) ||
+      (K % 128) || flags == nullptr)
+    return -10;
+  if (out_mode == 0 ? ((N % 8) || (ldc % 8)) : ((N % 4) || (ldc % 4))) return -5;
+  CUtensorMap tmA, tmB;
+  int rc = f8_make_map(&tmA, A, K, M);
+  if (rc) return rc;
+  rc = f8_make_map(&tmB, b_ptrs[rank], K, N);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM));
+    configured = true;
+  }
+  Fp8Args args;
+  args.C = C;
+  args.sa = sa;
+  args.sb = reinterpret_cast<const float*>(sb_ptrs[rank]);
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.b_block = 1;
+  args.out_mode = out_mode;
+  args.status = status;
+  args.ag_world = world;
+  args.ag_rank = rank;
+  args.ag_rows = N / world;
+  args.ag_dst = reinterpret_cast<uint8_t*>(b_ptrs[rank]);
+  args.ag_sdst = reinterpret_cast<float*>(sb_ptrs[rank]);
+  args.ag_flags = flags;
+  for (int r = 0; r < 8; ++r) {
+    args.ag_src[r] = r < world ? reinterpret_cast<const uint8_t*>(b_ptrs[r]) + static_cast<size_t>(r) * args.ag_rows * K
+                               : nullptr;
+    args.ag_ssrc[r] = r < world ? reinterpret_cast<const float*>(sb_ptrs[r]) : nullptr;
+  }
+  NPLM_CUDA_CHECK(cudaMemsetAsync(flags, 0, 8 * sizeof(unsigned), stream));
+  const int total = ((M + F8_BM - 1) / F8_BM) * (N / F8_BN);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = total < sms ? total : sms;
+  void* params[] = {&tmA, &tmB, &args};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(gemm_fp8_kernel), dim3(grid),
+                                                      dim3(F8_THREADS), params, F8_SMEM, stream));
 }

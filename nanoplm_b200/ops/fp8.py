@@ -103,6 +103,26 @@ def gemm_fp8(a: Quantized, b: Quantized, *, out: torch.Tensor | None = None, out
     return out
 
 
+def gemm_fp8_ag(a: Quantized, b_payload: torch.Tensor, b_payload_ptrs, b_scale: torch.Tensor, b_scale_ptrs,
+                rank: int, world: int, flags: torch.Tensor, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gather fused into the fp8 GEMM: C = deq(a) deq(B)^T with B's rows (e4m3 payload [N,K] and
+    block scales [K/128, N/128]) sharded over `world` ranks in peer-mapped memory. b_payload /
+    b_scale are this rank's full-size buffers (only its shard valid on entry, everything valid on
+    return); *_ptrs are the ctypes arrays of every rank's buffer addresses. The fp8 payload moves
+    half the bytes of a bf16 gather. flags: int32 [8]."""
+    M, K = a.q.shape
+    N = b_payload.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=_BF16, device=a.q.device)
+    mode = 0 if out.dtype == _BF16 else 1
+    rc = lib("fp8").nplm_gemm_fp8_ag(ptr(a.q), b_payload_ptrs, ptr(out), ptr(a.scale), b_scale_ptrs, c_int(M),
+                                     c_int(N), c_int(K), c_int(out.stride(0)), c_int(mode), c_int(rank),
+                                     c_int(world), ptr(flags), ptr(status_word(a.q.device)), stream_ptr())
+    check_rc(rc, "gemm_fp8_ag")
+    count_launch()
+    return out
+
+
 # ------------------------------------------------------------------------------ weight cache
 _weight_cache: dict[int, tuple] = {}
 

@@ -329,3 +329,57 @@ def test_expert_parallel_training_on_two_gpus(tmp_path):
     assert res[2]["losses"][-1] < res[2]["losses"][0]
     for k, v in res[1]["sd"].items():
         assert res[2]["sd"][k].shape == v.shape, k
+
+
+def _ag_fp8_worker(rank, world, port, out_path):
+    """fp8 all-gather GEMM: e4m3 weight rows and their block scales are sharded over the ranks."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from nanoplm_b200.comm.fused_optimizer import SymmetricBuffer
+    from nanoplm_b200.ops import _lib, fp8
+    BF = torch.bfloat16
+    for (M, N, Kd) in [(1000, 512, 256), (4096, 3072, 1024)]:
+        g = torch.Generator(device="cpu").manual_seed(11)
+        W = (torch.randn(N, Kd, generator=g) * 0.05).to(BF).to(dev)
+        torch.manual_seed(300 + rank)
+        x = torch.randn(M, Kd, device=dev).to(BF)
+        qx = fp8.quant_rows(x)
+        qw = fp8.quant_tile(W, transpose=False, block=True)       # every rank quantises the same W
+        rows, nb = N // world, N // 128 // world
+        pay = SymmetricBuffer(N * Kd, torch.uint8, dev, dist.group.WORLD)
+        sc = SymmetricBuffer((Kd // 128) * (N // 128), torch.float32, dev, dist.group.WORLD)
+        payload, scales = pay.tensor.view(N, Kd), sc.tensor.view(Kd // 128, N // 128)
+        payload.fill_(0x7f)                                         # NaN pattern in e4m3
+        scales.fill_(float("nan"))
+        payload[rank * rows:(rank + 1) * rows] = qw.q[rank * rows:(rank + 1) * rows]
+        scales[:, rank * nb:(rank + 1) * nb] = qw.scale[:, rank * nb:(rank + 1) * nb]
+        flags = torch.zeros(8, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        dist.barrier()
+        y = fp8.gemm_fp8_ag(qx, payload, pay.ptr_array, scales, sc.ptr_array, rank, world, flags)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        dist.barrier()
+        ref = fp8.gemm_fp8(qx, qw)
+        assert torch.equal(payload, qw.q) and torch.equal(scales, qw.scale)
+        assert torch.equal(y, ref), (M, N, Kd, (y.float() - ref.float()).abs().max().item())
+    if rank == 0:
+        torch.save({"ok": True}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+def test_all_gather_gemm_fp8(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    out = str(tmp_path / "agf8.pt")
+    procs = [ctx.Process(target=_ag_fp8_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    assert os.path.exists(out)
