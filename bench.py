@@ -122,7 +122,11 @@ def config_block(n_gpus: int, accum: int) -> dict:
             "grad_accum": accum, "parallelism": f"dp{n_gpus}" + ("-sharded-optimizer" if n_gpus > 1 else ""),
             "optimizer": "adamw lr 1e-3, clip 1.0", "mlm_probability": MLM_PROB,
             "tokens_counted": "real (non-padding) tokens; the flat batch also holds the padding tail",
-            "l2_policy": "inputs larger than L2: every layer streams >= 128 MB of activations per micro-batch"}
+            "l2_policy": "inputs larger than L2: every layer streams >= 128 MB of activations per micro-batch",
+            "padding_tail": "both arms receive the same 65 536-token flat micro-batches (about 55.3 K real "
+                            "tokens + padding tail); the own arm cuts the tail off on the host-known real-token "
+                            "count before its first kernel (loss and gradients unchanged; --no-trim disables it), "
+                            "the reference computes over the full static shape its compiler needs"}
 
 
 # ----------------------------------------------------------------------------------- own arm
@@ -175,7 +179,9 @@ def run_own(args) -> dict:
     for i in range(n_micro):
         ex = [{"input_ids": torch.from_numpy(s)} for s in seqs[i * SEQS_PER_MICRO:(i + 1) * SEQS_PER_MICRO]]
         b = coll(ex)
-        real_tokens.append(int(b.pop("num_real_tokens")))
+        real_tokens.append(int(b["num_real_tokens"]))
+        if args.no_trim:               # process the padding tail too (the reference's static shape)
+            b.pop("num_real_tokens")
         b.pop("labels")            # masked_idx / masked_labels carry the same information
         host.append({k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in b.items()})
     steps_host = [host[s * accum:(s + 1) * accum] for s in range(W + K)]
@@ -241,6 +247,8 @@ def run_own(args) -> dict:
            "gpu_launches": launches, "final_loss": last_loss,
            "raw_tokens_per_sec": K * MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN / (ms / 1e3),
            "fused_comm": engine.fused is not None, "loaded_libs": [Path(p).name for p in _lib.loaded_libraries()]}
+    if args.no_trim:
+        res["config"]["padding_tail"] = "own arm run with --no-trim: its kernels cover the padding tail as well"
     if args.variant != "default":
         res["variant"] = args.variant
         res["config"]["model"] += {"moe": " + MoE (64 experts, top-2, I 512) on every 2nd layer",
@@ -381,6 +389,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("own", "reference"), default="own")
     ap.add_argument("--no-fused-comm", action="store_true", help="use NCCL collectives in the optimizer step")
+    ap.add_argument("--no-trim", action="store_true",
+                    help="own arm: also run the kernels over the padding tail of every flat micro-batch")
     ap.add_argument("--variant", choices=("default", "moe", "conv_mhc", "fp8"), default="default",
                     help="own arm only: optional model extensions (the headline number is 'default')")
     args = ap.parse_args()

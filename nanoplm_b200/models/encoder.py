@@ -311,11 +311,25 @@ class ProtEncoderMLM(nn.Module):
         return flat_ids, flat_labels, cu_seqlens, position_ids, (indices, B, S)
 
     def forward(self, input_ids, attention_mask=None, labels=None, cu_seqlens=None, max_seqlen=None,
-                position_ids=None, masked_idx=None, masked_labels=None, return_logits=None):
+                position_ids=None, masked_idx=None, masked_labels=None, return_logits=None,
+                num_real_tokens: Optional[int] = None):
+        """num_real_tokens (a host integer, as the packing collator reports it): flat batches of the
+        static format end in a padding tail that carries no label and attends to nothing real. With
+        the count known on the host the tail is cut off before the first kernel (the kernels take
+        the token count at run time, there is no compiled static shape to keep), rounded up to a
+        whole 128-token tile. Loss and gradients are unchanged."""
         cfg = self.config
         ids, flat_labels, cu, pos, pad_info = self._flatten_inputs(
             input_ids, attention_mask, labels, cu_seqlens, position_ids)
         T = ids.shape[0]
+        if num_real_tokens is not None and pad_info is None and return_logits is None:
+            keep = min(T, (int(num_real_tokens) + 127) // 128 * 128)
+            if 0 < keep < T:
+                ids, pos = ids[:keep], pos[:keep]
+                if flat_labels is not None:
+                    flat_labels = flat_labels[:keep]
+                cu = torch.clamp(cu, max=keep)
+                T = keep
         if int(max_seqlen or 0) > cfg.max_position_embeddings:
             raise ValueError(f"Sequence length {max_seqlen} exceeds max_position_embeddings="
                              f"{cfg.max_position_embeddings}")

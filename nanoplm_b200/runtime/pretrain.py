@@ -120,7 +120,7 @@ def move_batch(batch: dict, device: torch.device) -> dict:
 
 def model_inputs(batch: dict) -> dict:
     keys = ("input_ids", "attention_mask", "labels", "cu_seqlens", "max_seqlen", "position_ids",
-            "masked_idx", "masked_labels")
+            "masked_idx", "masked_labels", "num_real_tokens")
     return {k: batch[k] for k in keys if k in batch}
 
 

@@ -116,3 +116,44 @@ def test_checkpoint_roundtrip_gpu(tmp_path, cuda_status):
     sd = torch.load(tmp_path / "checkpoint-3" / "pytorch_model.bin")
     assert "decoder.weight" in sd and "model.layers.1.mlp.Wi.weight" in sd
     assert sd["model.layers.1.mlp.Wi.weight"].dtype == torch.float32
+
+
+def test_padding_tail_trim_leaves_loss_and_grads_unchanged(cuda_status):
+    """Cutting the padding tail off a static flat batch (host-known real-token count) must not
+    change the loss or any gradient: the tail carries no label and attends to nothing real."""
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.collators import PackingCollator
+    from nanoplm_b200.data.synthetic import synthetic_token_sequences
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    torch.manual_seed(0)
+    tok = ProtTokenizer()
+    cfg = ModelConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      max_position_embeddings=256)
+    model = ProtEncoderMLM(cfg, tok)
+    with torch.no_grad():
+        for layer in model.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.03)
+            layer.mlp.Wo.weight.normal_(0, 0.03)
+    engine = ShardedEngine(model, AdamWHyper(lr=1e-3), torch.device("cuda:0"))
+    seqs = synthetic_token_sequences(16, 20, 120, seed=5)
+    coll = PackingCollator(tok, 256, 0.3, target_rows=12, batch_size=16, seed=5)     # 3072 slots, ~1100 real
+    b = coll([{"input_ids": torch.from_numpy(s)} for s in seqs])
+    n_real = int(b["num_real_tokens"])
+    assert n_real + 256 < b["input_ids"].numel()
+    keys = ("input_ids", "cu_seqlens", "position_ids", "masked_idx", "masked_labels", "max_seqlen")
+    inputs = {k: (b[k].cuda() if torch.is_tensor(b[k]) else b[k]) for k in keys}
+    grads, losses = [], []
+    for trim in (None, n_real):
+        engine.zero_grad()
+        out = model(**inputs, num_real_tokens=trim)
+        out["loss"].backward()
+        engine.collect_autograd_grads()
+        torch.cuda.synchronize()
+        losses.append(out["loss"].item())
+        grads.append(engine.main_grad.clone())
+    assert abs(losses[0] - losses[1]) < 1e-5, losses
+    scale = grads[0].abs().max().item()
+    # weight gradients are fp32 atomic sums, so only the summation order may differ
+    assert (grads[0] - grads[1]).abs().max().item() < 2e-3 * scale
