@@ -21,6 +21,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--optimizer-step", action="store_true")
     ap.add_argument("--variant", choices=("default", "moe", "conv_mhc"), default="default")
+    ap.add_argument("--no-trim", action="store_true", help="run the kernels over the padding tail as well")
     args = ap.parse_args()
 
     from nanoplm_b200.config.schema import ModelConfig
@@ -55,9 +56,11 @@ def main() -> None:
     seqs = synthetic_token_sequences(args.seqs, 19, 511, seed=7)
     coll = PackingCollator(tok, 512, 0.15, target_rows=args.tokens_rows, batch_size=args.seqs, seed=3)
     b = coll([{"input_ids": torch.from_numpy(s)} for s in seqs])
-    b.pop("num_real_tokens")
+    n_real = b.pop("num_real_tokens")
     b.pop("labels")
     batch = model_inputs(move_batch(b, dev))
+    if not args.no_trim:
+        batch["num_real_tokens"] = int(n_real)   # the padding tail is cut off before the first kernel
 
     def micro():
         out = model(**batch)

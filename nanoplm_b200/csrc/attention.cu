@@ -679,11 +679,13 @@ struct FaBwdArgs {
   const int* rope_pos;
   const float* rope_cos;   // [max_pos][32]
   const float* rope_sin;
+  int heads_per_cta;       // consecutive heads handled by one CTA (grid.y = ceil(H / heads_per_cta))
 };
 
 // smem: K, V, Q[2], dO[2] (16 KB each) + P^T (32 KB) + dS^T (32 KB) + lse/delta (2*2*128 fp32)
 constexpr int FA_BWD_SMEM = 6 * FA_TILE_BYTES + 4 * FA_TILE_BYTES + 2048 + 256;
 
+template <bool MULTI_HEAD>
 __global__ void __launch_bounds__(256, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
               const FaBwdArgs args) {
@@ -705,7 +707,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
   uint64_t* bar_q = bars + 1;  // [2]
   uint64_t* bar_s = bars + 3;
   uint64_t* bar_g = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bar_dq = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
@@ -715,7 +718,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
   const int half = warp >> 2;
   const int T = args.T, H = args.H, w = args.window;
   const int kv0 = blockIdx.x * FA_T;
-  const int h = blockIdx.y;
+  // One CTA handles a 128-key tile for heads_per_cta consecutive heads: barriers, TMEM and the
+  // key / query ranges are set up once, and the operand loads of head h+1 are in flight while the
+  // dK / dV tiles of head h leave TMEM.
+  // (MULTI_HEAD = false: exactly one head per CTA, which lets the compiler drop the hand-over code.)
+  const int h_first = MULTI_HEAD ? blockIdx.y * args.heads_per_cta : blockIdx.y;
+  const int h_last = MULTI_HEAD ? min(H, h_first + args.heads_per_cta) : h_first + 1;
   const int HD = H * FA_D;
 
   if (tid == 0) {
@@ -724,6 +732,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     mbar_init(&bar_q[1], 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_g, 1);
+    mbar_init(bar_dq, 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -769,12 +778,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
   constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
   constexpr uint32_t idesc_kv = make_idesc_bf16(128, 64, 0, 1);  // A K-major, B MN-major
   constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, 1, 1);  // A MN-major, B MN-major
-  const int colQ = h * FA_D, colK = HD + h * FA_D, colV = 2 * HD + h * FA_D;
   const float sl2 = args.scale * LOG2E;
 
-  auto load_q_tile = [&](int buf, int q0) {
+  auto load_kv = [&](int h) {
+    mbar_arrive_expect_tx(bar_kv, 2 * FA_TILE_BYTES);
+    tma_load_2d(sK, &tmQKV, bar_kv, HD + h * FA_D, kv0);
+    tma_load_2d(sV, &tmQKV, bar_kv, 2 * HD + h * FA_D, kv0);
+  };
+  auto load_q_tile = [&](int buf, int q0, int h) {
     mbar_arrive_expect_tx(&bar_q[buf], 2 * FA_TILE_BYTES);
-    tma_load_2d(sQ + buf * FA_TILE_BYTES, &tmQKV, &bar_q[buf], colQ, q0);
+    tma_load_2d(sQ + buf * FA_TILE_BYTES, &tmQKV, &bar_q[buf], h * FA_D, q0);
     tma_load_2d(sdO + buf * FA_TILE_BYTES, &tmDO, &bar_q[buf], h * FA_D, q0);
   };
   auto issue_s = [&](int buf) {
@@ -793,7 +806,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
   // Row statistics of a query tile: threads 0-127 fetch lse (scaled to log2), 128-255 delta. The
   // global load and the shared-memory store are separate steps, so the value can travel while
   // the thread works on the current tile.
-  auto fetch_stat = [&](int q0) -> float {
+  auto fetch_stat = [&](int q0, int h) -> float {
     const bool first = tid < 128;
     const int q = q0 + (first ? tid : tid - 128);
     if (q >= T) return 0.f;
@@ -804,14 +817,23 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     if (tid < 128) s_lse[buf * 128 + tid] = v;
     else s_delta[buf * 128 + tid - 128] = v;
   };
-  if (n_q > 0) {
-    store_stat(0, fetch_stat(q_lo));
+
+  // completions consumed so far on each barrier (the wait parity is the low bit)
+  uint32_t c_kv = 0, c_q0 = 0, c_q1 = 0, c_s = 0, c_g = 0, c_dq = 0;
+  auto wait_q = [&](int buf) -> bool {
+    const bool r = buf == 0 ? mbar_wait(&bar_q[0], c_q0 & 1u) : mbar_wait(&bar_q[1], c_q1 & 1u);
+    if (buf == 0) ++c_q0; else ++c_q1;
+    return r;
+  };
+
+  if (n_q > 0 && h_first < h_last) {
+    store_stat(0, fetch_stat(q_lo, h_first));
     if (tid == 0) {
-      mbar_arrive_expect_tx(bar_kv, 2 * FA_TILE_BYTES);
-      tma_load_2d(sK, &tmQKV, bar_kv, colK, kv0);
-      tma_load_2d(sV, &tmQKV, bar_kv, colV, kv0);
-      load_q_tile(0, q_lo);
-      if (mbar_wait(bar_kv, 0) && mbar_wait(&bar_q[0], 0)) {
+      load_kv(h_first);
+      load_q_tile(0, q_lo, h_first);
+      const bool got_kv = mbar_wait(bar_kv, c_kv & 1u);
+      const bool got_q = wait_q(0);
+      if (got_kv && got_q) {
         tc_fence_after();
         issue_s(0);
       } else {
@@ -819,135 +841,154 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
         *abort_flag = 1;
       }
     }
+    ++c_kv;
   }
 
   bool alive = true;
-  for (int j = 0; j < n_q; ++j) {
-    const int buf = j & 1;
-    const int q0 = q_lo + j * FA_T;
-    float next_stat = 0.f;
-    if (j + 1 < n_q) {
-      next_stat = fetch_stat(q0 + FA_T);   // stored to shared memory after this tile's softmax
-      if (tid == 0) load_q_tile(buf ^ 1, q0 + FA_T);
-    }
-    __syncthreads();  // stats of tile j visible (written one iteration ahead, or before the loop)
-    bool ok = mbar_wait(bar_s, j & 1);
-    ok = __syncthreads_and(ok);
-    if (!ok) {
-      if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
-      alive = false;
-      break;
-    }
-    tc_fence_after();
-    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    // this thread: key row krow_local, query columns [half*64, half*64+64)
-#pragma unroll 1
-    for (int c = 0; c < 64; c += 32) {
-      const int cbase = half * 64 + c;
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tS + lane_addr + cbase, rs);
-      tmem_ld32(tdP + lane_addr + cbase, rp);
-      tmem_ld_wait();
-      uint32_t pk[16], dk[16];
-      const float4* lse4 = reinterpret_cast<const float4*>(s_lse + buf * 128 + cbase);
-      const float4* del4 = reinterpret_cast<const float4*>(s_delta + buf * 128 + cbase);
-#pragma unroll
-      for (int e = 0; e < 32; e += 4) {
-        const float4 l4 = lse4[e >> 2], d4 = del4[e >> 2];   // broadcast reads, 4 columns each
-        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
-        float p[4], ds[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int q = q0 + cbase + e + u;
-          float pv = 0.f;
-          if (q >= lo && q < hi) pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -ls[u]));
-          p[u] = pv;
-          ds[u] = pv * (__uint_as_float(rp[e + u]) - dl[u]);
-        }
-        pk[e >> 1] = pack_bf16x2(p[0], p[1]);
-        pk[(e >> 1) + 1] = pack_bf16x2(p[2], p[3]);
-        dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
-        dk[(e >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
-      }
-      const int chunk0 = (c >> 5) * 4;
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        const uint32_t off = half * FA_TILE_BYTES + swz(krow_local, chunk0 + q4);
-        *reinterpret_cast<uint4*>(sPT + off) =
-            make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-        *reinterpret_cast<uint4*>(sdST + off) =
-            make_uint4(dk[4 * q4], dk[4 * q4 + 1], dk[4 * q4 + 2], dk[4 * q4 + 3]);
-      }
-    }
-    if (j + 1 < n_q) store_stat(buf ^ 1, next_stat);
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t pa = smem_u32(sPT), sa = smem_u32(sdST);
-      const uint32_t qa = smem_u32(sQ + buf * FA_TILE_BYTES), da = smem_u32(sdO + buf * FA_TILE_BYTES);
-      const uint32_t ka = smem_u32(sK);
-#pragma unroll
-      for (int k = 0; k < FA_T / 16; ++k) {  // dV[kv][d] += P^T[kv][q] dO[q][d]
-        umma_bf16(tdV, make_smem_desc(pa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
-                  make_smem_desc(da + k * 2048, 8192, 1024), idesc_kv, (j > 0 || k > 0) ? 1u : 0u);
-      }
-#pragma unroll
-      for (int k = 0; k < FA_T / 16; ++k) {  // dK[kv][d] += dS^T[kv][q] Q[q][d]
-        umma_bf16(tdK, make_smem_desc(sa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
-                  make_smem_desc(qa + k * 2048, 8192, 1024), idesc_kv, (j > 0 || k > 0) ? 1u : 0u);
-      }
-#pragma unroll
-      for (int k = 0; k < FA_T / 16; ++k) {  // dQ[q][d] = dS[q][kv] K[kv][d]
-        umma_bf16(tdQ, make_smem_desc(sa + k * 2048, FA_TILE_BYTES, 1024),
-                  make_smem_desc(ka + k * 2048, 8192, 1024), idesc_dq, k > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_g);
+  const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+  for (int h = h_first; h < h_last && alive; ++h) {
+    for (int j = 0; j < n_q; ++j) {
+      const int buf = j & 1;
+      const int q0 = q_lo + j * FA_T;
+      float next_stat = 0.f;
       if (j + 1 < n_q) {
-        if (mbar_wait(&bar_q[buf ^ 1], ((j + 1) >> 1) & 1)) {
-          tc_fence_after();
-          issue_s(buf ^ 1);
-        } else {
-          atomicExch(args.status, ST_TIMEOUT_FULL);
-          *abort_flag = 1;
-        }
+        next_stat = fetch_stat(q0 + FA_T, h);   // stored to shared memory after this tile's softmax
+        if (tid == 0) load_q_tile(buf ^ 1, q0 + FA_T, h);
       }
-    }
-    ok = mbar_wait(bar_g, j & 1);
-    ok = __syncthreads_and(ok);
-    if (!ok) {
-      if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
-      alive = false;
-      break;
-    }
-    tc_fence_after();
-    {
-      // dQ tile: lane = query row, this thread adds channels [half*32, half*32+32)
-      uint32_t r[32];
-      tmem_ld32(tdQ + lane_addr + half * 32, r);
-      tmem_ld_wait();
-      const int q = q0 + krow_local;
-      if (q < T && q < q_hi) {
-        float* dst = args.dq_acc + static_cast<size_t>(q) * HD + h * FA_D + half * 32;
+      __syncthreads();  // stats of tile j visible (written one iteration ahead, or before the loop)
+      bool ok = mbar_wait(bar_s, c_s & 1u);
+      ++c_s;
+      ok = __syncthreads_and(ok && *abort_flag == 0);
+      if (!ok) {
+        if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      // this thread: key row krow_local, query columns [half*64, half*64+64)
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 32) {
+        const int cbase = half * 64 + c;
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + lane_addr + cbase, rs);
+        tmem_ld32(tdP + lane_addr + cbase, rp);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+        const float4* lse4 = reinterpret_cast<const float4*>(s_lse + buf * 128 + cbase);
+        const float4* del4 = reinterpret_cast<const float4*>(s_delta + buf * 128 + cbase);
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
-          atomicAdd(reinterpret_cast<float4*>(dst + e),
-                    make_float4(__uint_as_float(r[e]) * args.scale, __uint_as_float(r[e + 1]) * args.scale,
-                                __uint_as_float(r[e + 2]) * args.scale,
-                                __uint_as_float(r[e + 3]) * args.scale));
+          const float4 l4 = lse4[e >> 2], d4 = del4[e >> 2];   // broadcast reads, 4 columns each
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float p[4], ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int q = q0 + cbase + e + u;
+            float pv = 0.f;
+            if (q >= lo && q < hi) pv = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -ls[u]));
+            p[u] = pv;
+            ds[u] = pv * (__uint_as_float(rp[e + u]) - dl[u]);
+          }
+          pk[e >> 1] = pack_bf16x2(p[0], p[1]);
+          pk[(e >> 1) + 1] = pack_bf16x2(p[2], p[3]);
+          dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
+          dk[(e >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
+        }
+        const int chunk0 = (c >> 5) * 4;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t off = half * FA_TILE_BYTES + swz(krow_local, chunk0 + q4);
+          *reinterpret_cast<uint4*>(sPT + off) =
+              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(sdST + off) =
+              make_uint4(dk[4 * q4], dk[4 * q4 + 1], dk[4 * q4 + 2], dk[4 * q4 + 3]);
         }
       }
+      if (j + 1 < n_q) store_stat(buf ^ 1, next_stat);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sPT), sa = smem_u32(sdST);
+        const uint32_t qa = smem_u32(sQ + buf * FA_TILE_BYTES), da = smem_u32(sdO + buf * FA_TILE_BYTES);
+        const uint32_t ka = smem_u32(sK);
+        // dQ first, with its own barrier: its read-out (TMEM -> fp32 atomics) then overlaps the
+        // dV / dK MMAs that follow in the tensor pipe
+#pragma unroll
+        for (int k = 0; k < FA_T / 16; ++k) {  // dQ[q][d] = dS[q][kv] K[kv][d]
+          umma_bf16(tdQ, make_smem_desc(sa + k * 2048, FA_TILE_BYTES, 1024),
+                    make_smem_desc(ka + k * 2048, 8192, 1024), idesc_dq, k > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_dq);
+#pragma unroll
+        for (int k = 0; k < FA_T / 16; ++k) {  // dV[kv][d] += P^T[kv][q] dO[q][d]
+          umma_bf16(tdV, make_smem_desc(pa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(da + k * 2048, 8192, 1024), idesc_kv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < FA_T / 16; ++k) {  // dK[kv][d] += dS^T[kv][q] Q[q][d]
+          umma_bf16(tdK, make_smem_desc(sa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(qa + k * 2048, 8192, 1024), idesc_kv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(bar_g);
+        if (j + 1 < n_q) {
+          if (wait_q(buf ^ 1)) {
+            tc_fence_after();
+            issue_s(buf ^ 1);
+          } else {
+            atomicExch(args.status, ST_TIMEOUT_FULL);
+            *abort_flag = 1;
+          }
+        }
+      }
+      ok = mbar_wait(bar_dq, c_dq & 1u);
+      ++c_dq;
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+      if (ok) {
+        // dQ tile: lane = query row, this thread adds channels [half*32, half*32+32)
+        uint32_t r[32];
+        tmem_ld32(tdQ + lane_addr + half * 32, r);
+        tmem_ld_wait();
+        const int q = q0 + krow_local;
+        if (q < T && q < q_hi) {
+          float* dst = args.dq_acc + static_cast<size_t>(q) * HD + h * FA_D + half * 32;
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            atomicAdd(reinterpret_cast<float4*>(dst + e),
+                      make_float4(__uint_as_float(r[e]) * args.scale, __uint_as_float(r[e + 1]) * args.scale,
+                                  __uint_as_float(r[e + 2]) * args.scale,
+                                  __uint_as_float(r[e + 3]) * args.scale));
+          }
+        }
+      }
+      ok = mbar_wait(bar_g, c_g & 1u) && ok;   // dV / dK of this tile done: operand buffers are free
+      ++c_g;
+      tc_fence_before();   // the dQ columns may be overwritten by the next tile's MMA after this barrier
+      ok = __syncthreads_and(ok && *abort_flag == 0);
+      if (!ok) {
+        if (tid == 0) atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+        alive = false;
+        break;
+      }
     }
-    tc_fence_before();
-    __syncthreads();  // dQ columns and the P^T / dS^T buffers may be overwritten from here on
-  }
+    if (!alive) break;
+    tc_fence_after();
+    // Every MMA of this head has finished (bar_g of its last tile): K, V, Q and dO buffers are free.
+    // Start the next head's loads before the dK / dV tiles are read out.
+    const bool more = MULTI_HEAD && h + 1 < h_last && n_q > 0;
+    if (more) {
+      store_stat(0, fetch_stat(q_lo, h + 1));
+      if (tid == 0) {
+        load_kv(h + 1);
+        load_q_tile(0, q_lo, h + 1);
+      }
+    }
 
-  if (alive) {
     // tcgen05.ld is warp-aligned: every lane of the warp executes it, rows past T only skip the
     // global stores. Warps 0-3 (half 0) write dK, warps 4-7 (half 1) write dV; each thread owns
     // all 64 channels of its key row, which is what the inverse rotation of dK needs.
-    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float g[FA_D];
     if (n_q > 0) {
       const uint32_t src = (half == 0 ? tdK : tdV) + lane_addr;
@@ -962,6 +1003,23 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     } else {
 #pragma unroll
       for (int e = 0; e < FA_D; ++e) g[e] = 0.f;
+    }
+    if (more) {
+      // all warps hold their dK / dV values: the accumulators may be overwritten by the next head
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        const bool got_kv = mbar_wait(bar_kv, c_kv & 1u);
+        const bool got_q = wait_q(0);
+        if (got_kv && got_q) {
+          tc_fence_after();
+          issue_s(0);
+        } else {
+          atomicExch(args.status, ST_TIMEOUT_FULL);
+          *abort_flag = 1;
+        }
+      }
+      ++c_kv;
     }
     if (krow_ok) {
       if (half == 0) {
@@ -1166,7 +1224,9 @@ extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* do
   if (rc) return rc;
   static bool configured = false;
   if (!configured) {
-    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FA_BWD_SMEM));
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FA_BWD_SMEM));
     configured = true;
   }
@@ -1195,8 +1255,26 @@ extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* do
   a.rope_pos = rope_pos;
   a.rope_cos = rope_cos;
   a.rope_sin = rope_sin;
-  dim3 grid((T + FA_T - 1) / FA_T, H);
-  fa_bwd_kernel<<<grid, 256, FA_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  // several heads per CTA amortise the per-CTA set-up and overlap the next head's loads with the
+  // dK / dV read-out, as long as the grid still fills the GPU a few times over
+  static int hpc_env = -1;
+  if (hpc_env < 0) {
+    const char* e = getenv("NPLM_FA_BWD_HEADS_PER_CTA");
+    hpc_env = (e != nullptr && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 0;
+  }
+  // measured on 65 536 packed tokens, 16 heads: 4 heads per CTA help the +-64 window (few query
+  // tiles per key tile, so the set-up weighs more): 0.818 vs 0.892 ms; unlimited attention is best
+  // with one head per CTA (1.357 ms)
+  const int n_tiles = (T + FA_T - 1) / FA_T;
+  int hpc = hpc_env > 0 ? hpc_env : (window >= 0 ? 4 : 1);
+  while (hpc > 1 && (static_cast<long long>(n_tiles) * ((H + hpc - 1) / hpc) < 148LL * 4)) hpc >>= 1;
+  if (hpc > H) hpc = H;
+  a.heads_per_cta = hpc;
+  dim3 grid(n_tiles, (H + hpc - 1) / hpc);
+  if (hpc > 1)
+    fa_bwd_kernel<true><<<grid, 256, FA_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  else
+    fa_bwd_kernel<false><<<grid, 256, FA_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   {
     const long long total = static_cast<long long>(T) * H * 4;
     long long blocks = (total + 255) / 256;

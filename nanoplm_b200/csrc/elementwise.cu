@@ -794,13 +794,9 @@ extern "C" int nplm_norm_bwd(const void* dy, const void* x, const int* ids, cons
                              float* dw, float* dtable, int T, int C, int V, int rms, cudaStream_t st) {
   if (T <= 0) return 0;
   if (C % 8) return -3;
-  static int use_rows = -1;   // NPLM_NORM_BWD_ROWS=1 routes the dx path through the row-group kernel too
-  if (use_rows < 0) {
-    const char* e = getenv("NPLM_NORM_BWD_ROWS");
-    use_rows = (e != nullptr && e[0] == '1') ? 1 : 0;
-  }
-  if (C >= 256 && C <= 2048 && (ids == nullptr ? (use_rows && dx != nullptr) : (dtable != nullptr && V > 0))) {
-    // block-per-row-group variant: C/8 threads (rounded up to whole warps)
+  if (C >= 256 && C <= 2048 && ids != nullptr && dtable != nullptr && V > 0) {
+    // embedding gradient: row-group kernel, per-vocabulary-entry sums in shared memory
+    // (C/8 threads, rounded up to whole warps)
     constexpr int ROWS = 4;
     const int threads = ((C / 8) + 31) / 32 * 32;
     const size_t smem = ids != nullptr ? static_cast<size_t>(V) * C * sizeof(float) : 0;
