@@ -200,19 +200,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaFwdArgs args) {
       const int c_lo = kv0 + c, c_hi = c_lo + 32;
       const bool none = c_hi <= lo || c_lo >= hi;
       if (__all_sync(0xffffffffu, none)) continue;
+      // the fast path is taken by the whole warp or not at all: a per-lane split would run both
+      const bool w_in = __all_sync(0xffffffffu, c_lo >= lo && c_hi <= hi);
       uint32_t r[32];
       tmem_ld32(tS + lane_addr + c, r);
       tmem_ld_wait();
-      if (!none) {
-        if (c_lo >= lo && c_hi <= hi) {
+      if (w_in) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
-        } else {
+        for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+      } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = c_lo + e;
-            if (col >= lo && col < hi) tmax = fmaxf(tmax, __uint_as_float(r[e]));
-          }
+        for (int e = 0; e < 32; ++e) {
+          const int col = c_lo + e;
+          if (col >= lo && col < hi) tmax = fmaxf(tmax, __uint_as_float(r[e]));
         }
       }
     }
@@ -231,10 +231,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaFwdArgs args) {
         uint32_t r[32];
         tmem_ld32(tS + lane_addr + c, r);
         tmem_ld_wait();
-        if (none) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) packed[e] = 0u;
-        } else if (c_lo >= lo && c_hi <= hi) {
+        if (__all_sync(0xffffffffu, c_lo >= lo && c_hi <= hi)) {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
             const float p0 = exp2f(fmaf(__uint_as_float(r[e]), sl2, -moff));
