@@ -131,3 +131,54 @@ def inspect_checkpoint_architecture(path: str | Path) -> dict:
     if layers:
         info["intermediate_size"] = sd[f"layers.{layers[0]}.mlp.Wo.weight"].shape[1]
     return info
+
+
+def calculate_model_parameters(model: torch.nn.Module) -> dict:
+    """Total and trainable parameter counts (reference: student/model.py, parameter utilities)."""
+    total = sum(p.numel() for p in model.parameters())
+    trainable = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    return {"total": total, "trainable": trainable, "frozen": total - trainable}
+
+
+def print_parameter_breakdown(model: "ProtX") -> dict:
+    """Logs the per-group parameter counts of a student and returns them."""
+    from nanoplm_b200.utils.logging import logger
+    groups = model.parameter_breakdown()
+    total = max(1, groups["total"])
+    for name, n in groups.items():
+        if name != "total":
+            logger.info(f"{name:>12s}: {n:>12,d}  ({100.0 * n / total:5.1f} %)")
+    logger.info(f"{'total':>12s}: {groups['total']:>12,d}")
+    return groups
+
+
+def load_and_generate_embeddings(checkpoint: str | Path, sequences: list[str], cfg: Optional[StudentConfig] = None,
+                                 batch_size: int = 16, per_token: bool = False,
+                                 device: Optional[torch.device] = None) -> list[torch.Tensor]:
+    """Loads a saved student (safetensors or torch state dict) and embeds raw sequences: mean-pooled
+    over the residues (the trailing </s> excluded) or one vector per residue
+    (reference: student/model.py:111-248). Without `cfg` the architecture is inferred from the file;
+    the head count defaults to hidden_size / 64."""
+    p = Path(checkpoint)
+    if p.is_dir():
+        p = p / ("model.safetensors" if (p / "model.safetensors").exists() else "pytorch_model.bin")
+    if p.suffix == ".safetensors":
+        from safetensors.torch import load_file
+        sd = load_file(str(p))
+    else:
+        sd = torch.load(p, map_location="cpu", weights_only=True)
+    if cfg is None:
+        info = inspect_checkpoint_architecture(p)
+        cfg = StudentConfig(hidden_size=info["hidden_size"], intermediate_size=info.get("intermediate_size", 2 * info["hidden_size"]),
+                            num_hidden_layers=info["num_hidden_layers"],
+                            num_attention_heads=max(1, info["hidden_size"] // 64),
+                            projection_layer=info["projection_layer"])
+    model = ProtX(cfg)
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    if unexpected:
+        raise KeyError(f"unexpected keys in student checkpoint: {sorted(unexpected)[:5]}")
+    device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    model = model.to(device)
+    if device.type == "cuda":
+        model = model.to(torch.bfloat16)
+    return model.embed_sequences(sequences, batch_size=batch_size, per_token=per_token, device=device)

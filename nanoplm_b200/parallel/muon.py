@@ -152,3 +152,9 @@ class MuonEngine(ShardedEngine):
             self.flat_params[sl] = p.to(self.flat_params.dtype)
         self.main_grad.zero_()
         return norm
+
+
+def is_muon_optimizer(engine) -> bool:
+    """True for the Muon / NorMuon engine (used to decide which learning rates to log;
+    reference: pretraining/optim.py:10-17)."""
+    return isinstance(engine, MuonEngine)
