@@ -45,7 +45,7 @@ def main():
     engine = ShardedEngine(student, AdamWHyper(lr=1e-3), dev)
     coll = DistillDataCollator(True, args.max_len)
     seqs = synthetic_sequences(args.batch, 20, args.max_len - 1, seed=4)
-    batch = {k: v.to(dev) for k, v in coll([{"raw_sequence": s} for s in seqs]).items()}
+    batch = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in coll([{"raw_sequence": s} for s in seqs]).items()}
     tokens = int(batch["attention_mask"].sum().item())
 
     def step():
@@ -56,7 +56,7 @@ def main():
 
     def teacher_only():
         with torch.no_grad():
-            teacher(batch["teacher_input_ids"], batch["teacher_attention_mask"])
+            teacher(batch["teacher_input_ids"], batch["teacher_attention_mask"], lengths=batch.get("teacher_lengths"))
 
     def timed(fn, n):
         for _ in range(args.warmup):

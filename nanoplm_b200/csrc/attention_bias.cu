@@ -12,6 +12,11 @@
 // length) is cut into 128-token tiles; operands are [128 rows][64 bf16] swizzled tiles loaded by
 // TMA (two per operand for head_dim 128), S = Q K^T and O_part = P V run on tcgen05 with fp32
 // accumulators in TMEM, the online softmax runs one thread per query row.
+//
+// Keys are consumed KC at a time: 128 for head_dim 64; 64 for head_dim 128, which keeps a CTA at
+// 112 KB of shared memory and 192 TMEM columns so that two CTAs share an SM (the kernel is bound
+// by the latency of its MMA -> softmax -> MMA chain, so the second CTA nearly doubles throughput).
+// The bias table is read through the read-only cache instead of shared memory for the same reason.
 #include "common.cuh"
 
 namespace nplm {
@@ -34,33 +39,38 @@ struct AbArgs {
   int* status;
 };
 
-template <int D>
-constexpr int ab_smem_bytes(int S) {
-  return (D / 64) * AB_TILE * 5 + 2 * AB_TILE + 256 + (2 * S) * 4;
+template <int D, int KC>
+constexpr int ab_smem_bytes() {
+  // Q + 2 K + 2 V + P + barriers
+  return (D / 64) * AB_TILE + 4 * (D / 64) * (KC * 128) + AB_T * KC * 2 + 256;
 }
 
-template <int D>
-__global__ void __launch_bounds__(128)
-fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args) {
+template <int D, int KC>
+__global__ void __launch_bounds__(128, 2)
+fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmKV,
+                   const AbArgs args) {
   constexpr int NA = D / 64;              // 64-column atoms per operand tile
-  constexpr int OP = NA * AB_TILE;        // bytes of one operand tile
+  constexpr int QB = NA * AB_TILE;        // bytes of the Q tile (128 rows)
+  constexpr int KA = KC * 128;            // bytes of one K / V atom (KC rows x 64 columns)
+  constexpr int OP = NA * KA;             // bytes of one K / V tile
+  constexpr int PB = AB_T * KC * 2;       // bytes of the P tile (KC / 64 atoms of [128][128 B])
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {
     if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
     return;
   }
   uint8_t* sQ = smem;
-  uint8_t* sK = smem + OP;        // 2 buffers
-  uint8_t* sV = smem + 3 * OP;    // 2 buffers
-  uint8_t* sP = smem + 5 * OP;    // [2 key blocks][128 rows][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 5 * OP + 2 * AB_TILE);
+  uint8_t* sK = smem + QB;            // 2 buffers
+  uint8_t* sV = smem + QB + 2 * OP;   // 2 buffers
+  uint8_t* sP = smem + QB + 4 * OP;   // [KC / 64 key blocks][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + QB + 4 * OP + PB);
   uint64_t* bar_q = bars;
   uint64_t* bar_kv = bars + 1;  // [2]
   uint64_t* bar_s = bars + 3;
   uint64_t* bar_o = bars + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_bias = reinterpret_cast<float*>(smem + 5 * OP + 2 * AB_TILE + 256);
+  const float* g_bias = args.bias + static_cast<size_t>(blockIdx.y) * (2 * args.S - 1);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -80,7 +90,6 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmQKV);
   }
-  for (int i = tid; i < 2 * S - 1; i += 128) s_bias[i] = args.bias[static_cast<size_t>(h) * (2 * S - 1) + i];
   if (warp == 1) {
     __syncwarp();
     tmem_alloc(tmem_slot, 256);
@@ -90,7 +99,7 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base;        // 128 columns
+  const uint32_t tS = tmem_base;        // KC columns
   const uint32_t tO = tmem_base + 128;  // D columns
 
   const int row = t0 + tid;
@@ -119,28 +128,32 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
     kv_lo = s_rng[0];
     kv_hi = s_rng[1];
   }
-  const int n_kv = kv_hi > kv_lo ? (kv_hi - kv_lo + AB_T - 1) / AB_T : 0;
+  const int n_kv = kv_hi > kv_lo ? (kv_hi - kv_lo + KC - 1) / KC : 0;
 
-  constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_s = make_idesc_bf16(128, KC, 0, 0);
   constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
   const int colQ = h * D, colK = HD + h * D, colV = 2 * HD + h * D;
 
-  auto load_tile = [&](uint8_t* dst, uint64_t* bar, int col, int r0) {
+  auto load_q = [&](uint8_t* dst, uint64_t* bar, int col, int r0) {
 #pragma unroll
     for (int a = 0; a < NA; ++a) tma_load_2d(dst + a * AB_TILE, &tmQKV, bar, col + a * 64, r0);
+  };
+  auto load_tile = [&](uint8_t* dst, uint64_t* bar, int col, int r0) {   // KC rows
+#pragma unroll
+    for (int a = 0; a < NA; ++a) tma_load_2d(dst + a * KA, &tmKV, bar, col + a * 64, r0);
   };
   auto issue_s = [&](int buf) {
     const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + buf * OP);
 #pragma unroll
     for (int k = 0; k < D / 16; ++k)
       umma_bf16(tS, make_smem_desc(qa + (k >> 2) * AB_TILE + (k & 3) * 32, 16, 1024),
-                make_smem_desc(ka + (k >> 2) * AB_TILE + (k & 3) * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+                make_smem_desc(ka + (k >> 2) * KA + (k & 3) * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
     umma_commit(bar_s);
   };
 
   if (tid == 0 && n_kv > 0) {
-    mbar_arrive_expect_tx(bar_q, OP);
-    load_tile(sQ, bar_q, colQ, t0);
+    mbar_arrive_expect_tx(bar_q, QB);
+    load_q(sQ, bar_q, colQ, t0);
     mbar_arrive_expect_tx(&bar_kv[0], 2 * OP);
     load_tile(sK, &bar_kv[0], colK, kv_lo);
     load_tile(sV, &bar_kv[0], colV, kv_lo);
@@ -165,11 +178,11 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
   bool alive = true;
   for (int j = 0; j < n_kv && alive; ++j) {
     const int buf = j & 1;
-    const int kv0 = kv_lo + j * AB_T;
+    const int kv0 = kv_lo + j * KC;
     if (tid == 0 && j + 1 < n_kv) {
       mbar_arrive_expect_tx(&bar_kv[buf ^ 1], 2 * OP);
-      load_tile(sK + (buf ^ 1) * OP, &bar_kv[buf ^ 1], colK, kv0 + AB_T);
-      load_tile(sV + (buf ^ 1) * OP, &bar_kv[buf ^ 1], colV, kv0 + AB_T);
+      load_tile(sK + (buf ^ 1) * OP, &bar_kv[buf ^ 1], colK, kv0 + KC);
+      load_tile(sV + (buf ^ 1) * OP, &bar_kv[buf ^ 1], colV, kv0 + KC);
     }
     __syncwarp();
     bool ok = mbar_wait(bar_s, j & 1);
@@ -184,7 +197,7 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
     // pass 1: row maximum of scale * s + bias over the valid keys (log2 domain)
     float tmax = -1e30f;
 #pragma unroll 1
-    for (int c = 0; c < AB_T; c += 32) {
+    for (int c = 0; c < KC; c += 32) {
       uint32_t r[32];
       tmem_ld32(tS + lane_addr + c, r);
       tmem_ld_wait();
@@ -192,7 +205,7 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
       for (int e = 0; e < 32; ++e) {
         const int col = kv0 + c + e;
         if (col >= lo && col < hi)
-          tmax = fmaxf(tmax, fmaf(__uint_as_float(r[e]), sl2, s_bias[col + boff] * AB_LOG2E));
+          tmax = fmaxf(tmax, fmaf(__uint_as_float(r[e]), sl2, __ldg(g_bias + col + boff) * AB_LOG2E));
       }
     }
     const float m_new = fmaxf(m_run, tmax);
@@ -200,7 +213,7 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
     float psum = 0.f;
     // pass 2: probabilities -> bf16 -> swizzled shared memory
 #pragma unroll 1
-    for (int c = 0; c < AB_T; c += 32) {
+    for (int c = 0; c < KC; c += 32) {
       uint32_t r[32];
       tmem_ld32(tS + lane_addr + c, r);
       tmem_ld_wait();
@@ -213,7 +226,7 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
           const int col = kv0 + c + e + u;
           p[u] = 0.f;
           if (col >= lo && col < hi)
-            p[u] = exp2f(fmaf(__uint_as_float(r[e + u]), sl2, s_bias[col + boff] * AB_LOG2E) - m_new);
+            p[u] = exp2f(fmaf(__uint_as_float(r[e + u]), sl2, __ldg(g_bias + col + boff) * AB_LOG2E) - m_new);
         }
         psum += p[0] + p[1];
         packed[e >> 1] = pack_bf16x2(p[0], p[1]);
@@ -237,9 +250,9 @@ fa_bias_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AbArgs args)
       tc_fence_after();
       const uint32_t pa = smem_u32(sP), va = smem_u32(sV + buf * OP);
 #pragma unroll
-      for (int k = 0; k < AB_T / 16; ++k)
+      for (int k = 0; k < KC / 16; ++k)
         umma_bf16(tO, make_smem_desc(pa + (k >> 2) * AB_TILE + (k & 3) * 32, 16, 1024),
-                  make_smem_desc(va + k * 2048, AB_TILE, 1024), idesc_o, k > 0 ? 1u : 0u);
+                  make_smem_desc(va + k * 2048, KA, 1024), idesc_o, k > 0 ? 1u : 0u);
       umma_commit(bar_o);
       if (j + 1 < n_kv) {
         if (mbar_wait(&bar_kv[buf ^ 1], ((j + 1) >> 1) & 1)) {
@@ -310,17 +323,16 @@ static AbEncodeFn ab_encode_fn() {
   return fn;
 }
 
-template <int D>
-static int ab_launch(const CUtensorMap& tm, const AbArgs& a, cudaStream_t st) {
-  const int smem = ab_smem_bytes<D>(a.S);
-  if (smem > 227 * 1024) return -4;
-  static int configured = 0;
-  if (configured < smem) {
-    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bias_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = smem;
+template <int D, int KC>
+static int ab_launch(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const AbArgs& a, cudaStream_t st) {
+  constexpr int smem = ab_smem_bytes<D, KC>();
+  static bool configured = false;
+  if (!configured) {
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bias_fwd_kernel<D, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
   }
   dim3 grid((a.T + AB_T - 1) / AB_T, a.H);
-  fa_bias_fwd_kernel<D><<<grid, 128, smem, st>>>(tm, a);
+  fa_bias_fwd_kernel<D, KC><<<grid, 128, smem, st>>>(tmQ, tmKV, a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -336,12 +348,18 @@ extern "C" int nplm_fa_bias_fwd(const void* qkv, void* out, const int* seq_start
   if ((D != 64 && D != 128) || S < 1 || (reinterpret_cast<uintptr_t>(qkv) & 15)) return -3;
   AbEncodeFn fn = ab_encode_fn();
   if (fn == nullptr) return -1;
-  CUtensorMap tm;
+  CUtensorMap tmQ, tmKV;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(3) * H * D, static_cast<cuuint64_t>(T)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(3) * H * D * 2};
-  cuuint32_t box[2] = {64, AB_T};
   cuuint32_t estr[2] = {1, 1};
-  if (fn(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides, box, estr,
+  const cuuint32_t kc = D == 64 ? 128 : 64;     // key rows per K / V box
+  cuuint32_t box_q[2] = {64, AB_T};
+  cuuint32_t box_kv[2] = {64, kc};
+  if (fn(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides, box_q, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return -2;
+  if (fn(&tmKV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides, box_kv, estr,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return -2;
@@ -355,5 +373,5 @@ extern "C" int nplm_fa_bias_fwd(const void* qkv, void* out, const int* seq_start
   a.S = S;
   a.scale = scale;
   a.status = status;
-  return D == 64 ? ab_launch<64>(tm, a, st) : ab_launch<128>(tm, a, st);
+  return D == 64 ? ab_launch<64, 128>(tmQ, tmKV, a, st) : ab_launch<128, 64>(tmQ, tmKV, a, st);
 }

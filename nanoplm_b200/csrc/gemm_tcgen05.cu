@@ -28,10 +28,12 @@ enum : int {
   EPI_STORE = 0,       // C(bf16) = acc
   EPI_ADD = 1,         // C(bf16) = acc + R(bf16)
   EPI_ATOMIC_F32 = 2,  // C(fp32) += acc   (split-K capable; used for weight gradients)
-  EPI_GELU = 3,        // C(bf16) = gelu(acc), also writes the pre-activation to R when R != null
+  EPI_GELU = 3,        // C(bf16) = act(acc), act = GELU (erf) or ReLU (GemmArgs::act_relu); also writes
+                       // the pre-activation to R when R != null
   EPI_STORE_F32 = 4,   // C(fp32) = acc
   EPI_SWIGLU = 5,      // B tile = [value rows | gate rows]; C(bf16, N/2 wide) = silu(gate)*value,
                        // pre-activations (bf16, N wide) written to R
+  EPI_RELU = 7,        // host-side alias: EPI_GELU with act_relu = 1
   EPI_ROPE = 6,        // C(bf16) = acc with rotary embedding applied to every 64-wide head whose
                        // first column is < rope_cols (the q and k parts of a fused QKV projection)
 };
@@ -61,6 +63,7 @@ struct GemmArgs {
   const float* rope_cos;
   const float* rope_sin;
   int rope_cols;
+  int act_relu;        // EPI_GELU: 0 = GELU, 1 = ReLU
   // Grouped (mixture-of-experts) forms, one launch for all groups:
   //   group_mode 1: rows of A / C are partitioned into groups in units of 128-row tiles
   //                 (tile_group[m_tile] = group, or -1 for an unused tile); group g multiplies by
@@ -507,7 +510,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int e = 0; e < 32; ++e) {
                   pre[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
                   const float2 t = unpack_bf16x2(pre[e]);
-                  packed[e] = pack_bf16x2(gelu_erf(t.x), gelu_erf(t.y));
+                  packed[e] = args.act_relu ? pack_bf16x2(fmaxf(t.x, 0.f), fmaxf(t.y, 0.f))
+                                            : pack_bf16x2(gelu_erf(t.x), gelu_erf(t.y));
                 }
                 stage_store_bf16(stage, stage_toggle, &tmC, packed, x, y0, lane);
                 if (args.R != nullptr) stage_store_bf16(stage, stage_toggle, &tmR, pre, x, y0, lane);
@@ -643,7 +647,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                       p[e] = pack_bf16x2(__uint_as_float(r[j + 2 * e]),
                                          __uint_as_float(r[j + 2 * e + 1]));
                       const float2 f = unpack_bf16x2(p[e]);
-                      o[e] = pack_bf16x2(gelu_erf(f.x), gelu_erf(f.y));
+                      o[e] = args.act_relu ? pack_bf16x2(fmaxf(f.x, 0.f), fmaxf(f.y, 0.f))
+                                           : pack_bf16x2(gelu_erf(f.x), gelu_erf(f.y));
                     }
                     if (args.R != nullptr) {
                       *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(args.R) +
@@ -809,6 +814,11 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
                       const int* rope_pos, const float* rope_cos, const float* rope_sin,
                       int rope_cols, int* status, cudaStream_t stream, const GroupSpec& grp) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  int act_relu = 0;
+  if (epi == EPI_RELU) {
+    epi = EPI_GELU;
+    act_relu = 1;
+  }
   if (grp.mode == 1 && (grp.tile_group == nullptr || grp.groups < 1 || (K % BK) || epi == EPI_ATOMIC_F32))
     return -9;
   if (grp.mode == 2 && (grp.group_off == nullptr || grp.groups < 1 || !a_mn || !b_mn ||
@@ -882,6 +892,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   args.rope_cos = rope_cos;
   args.rope_sin = rope_sin;
   args.rope_cols = rope_cols;
+  args.act_relu = act_relu;
   args.group_mode = grp.mode;
   args.groups = grp.groups;
   args.tile_group = grp.tile_group;

@@ -127,7 +127,7 @@ class _DenseReluDense(nn.Module):
         self.wi, self.wo = _Lin(cfg.d_model, cfg.d_ff), _Lin(cfg.d_ff, cfg.d_model)
 
     def forward(self, x2, residual):
-        return self.wo(ops.activation(self.wi(x2), "relu"), residual=residual)
+        return self.wo(ops.linear(x2, self.wi.weight, act="relu"), residual=residual)   # ReLU in the GEMM epilogue
 
 
 class _FFLayer(nn.Module):
@@ -196,25 +196,51 @@ class T5EncoderTeacher(nn.Module):
         return TeacherTokenizer.preprocess(seq)
 
     @torch.no_grad()
-    def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """(B, S) token ids -> (B, S, d_model) last hidden state."""
+    def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                lengths: Optional[list] = None) -> torch.Tensor:
+        """(B, S) token ids -> (B, S, d_model) last hidden state.
+
+        lengths: number of real (left-aligned) tokens of every row as host integers. When given on
+        the native path, the padding is removed before the first layer (the whole encoder then
+        runs on the real tokens only, like the student's varlen path) and the output is scattered
+        back into the padded layout with zeros at the padding positions. Without it the padded
+        batch is processed as is, padding tokens attending to themselves."""
         B, S = input_ids.shape
-        x = self.shared(input_ids)
         attn0 = self.encoder.block[0].layer[0].SelfAttention
-        if (x.is_cuda and x.dtype == torch.bfloat16 and self.cfg.d_kv in (64, 128) and S <= 2048
-                and self.native_attention):
+        native = (input_ids.is_cuda and self.shared.weight.dtype == torch.bfloat16 and self.cfg.d_kv in (64, 128)
+                  and S <= 2048 and self.native_attention)
+        if native and lengths is not None:
+            dev = input_ids.device
+            lens = [int(min(max(n, 0), S)) for n in lengths]
+            idx_host = torch.cat([torch.arange(n, dtype=torch.int64) + b * S for b, n in enumerate(lens)])
+            cu_host = torch.zeros(B + 1, dtype=torch.int32)
+            cu_host[1:] = torch.cumsum(torch.tensor(lens, dtype=torch.int32), 0)
+            idx = idx_host.pin_memory().to(dev, non_blocking=True)
+            cu = cu_host.pin_memory().to(dev, non_blocking=True)
+            T = int(idx_host.numel())
+            x = self.shared(input_ids.reshape(-1)[idx]).unsqueeze(0)                  # [1, T, d]
+            start, end = ops.seq_bounds(cu, T)
+            fast = {"seq_start": start, "seq_end": end, "table": attn0.compute_bias_table(max(lens + [1]), dev)}
+            for blk in self.encoder.block:
+                x = blk(x, fast)
+            y = self.encoder.final_layer_norm(x)[0]
+            out = torch.zeros((B * S, y.shape[-1]), dtype=y.dtype, device=dev)
+            out.index_copy_(0, idx, y)
+            return out.view(B, S, -1)
+        x = self.shared(input_ids)
+        if native:
             # key range of every token of the padded batch: its sequence's valid prefix; padding
             # tokens see themselves only (their outputs are never used)
             dev = x.device
             if attention_mask is None:
-                lengths = torch.full((B,), S, device=dev, dtype=torch.int32)
+                lengths_t = torch.full((B,), S, device=dev, dtype=torch.int32)
             else:
-                lengths = attention_mask.sum(dim=1).to(torch.int32)
+                lengths_t = attention_mask.sum(dim=1).to(torch.int32)
             pos = torch.arange(S, device=dev, dtype=torch.int32)[None, :]
             base = (torch.arange(B, device=dev, dtype=torch.int32) * S)[:, None]
-            valid = pos < lengths[:, None]
+            valid = pos < lengths_t[:, None]
             start = torch.where(valid, base.expand(B, S), base + pos)
-            end = torch.where(valid, (base + lengths[:, None]).expand(B, S), base + pos + 1)
+            end = torch.where(valid, (base + lengths_t[:, None]).expand(B, S), base + pos + 1)
             fast = {"seq_start": start.reshape(-1).contiguous(), "seq_end": end.reshape(-1).contiguous(),
                     "table": attn0.compute_bias_table(S, dev)}
             for blk in self.encoder.block:

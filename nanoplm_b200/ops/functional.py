@@ -72,9 +72,11 @@ class _LinearFn(torch.autograd.Function):
         pre = None
         if rope is not None:
             y = K.gemm(x2, w, epi=K.EPI_ROPE, rope=rope)
-        elif act == "gelu":
-            pre = torch.empty((x2.shape[0], w.shape[0]), dtype=BF, device=x.device)
-            y = K.gemm(x2, w, epi=K.EPI_GELU, aux=pre)
+        elif act in ("gelu", "relu"):
+            # the pre-activation is only kept when a backward pass will need it
+            need_pre = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+            pre = torch.empty((x2.shape[0], w.shape[0]), dtype=BF, device=x.device) if need_pre else None
+            y = K.gemm(x2, w, epi=K.EPI_GELU if act == "gelu" else K.EPI_RELU, aux=pre)
         elif act == "swiglu":
             pre = torch.empty((x2.shape[0], w.shape[0]), dtype=BF, device=x.device)
             y = K.gemm(x2, w, epi=K.EPI_SWIGLU, aux=pre)
@@ -98,8 +100,8 @@ class _LinearFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        if ctx.act == "gelu":
-            dpre = K.act_bwd(pre, dy2, "gelu")
+        if ctx.act in ("gelu", "relu"):
+            dpre = K.act_bwd(pre, dy2, ctx.act)
         elif ctx.act == "swiglu":
             dpre = K.swiglu_bwd(pre, dy2)
         else:
@@ -137,7 +139,7 @@ def fp8_enabled() -> bool:
 
 
 def linear(x, w, bias=None, residual=None, act: str | None = None):
-    """y = act(x w^T + bias) + residual.  act: None | "gelu" | "swiglu" (w rows = [value | gate],
+    """y = act(x w^T + bias) + residual.  act: None | "gelu" | "relu" | "swiglu" (w rows = [value | gate],
     output is half as wide). residual and act are mutually exclusive."""
     if x.is_cuda and _FP8_STATE["enabled"] and bias is None:
         from . import fp8
@@ -145,8 +147,8 @@ def linear(x, w, bias=None, residual=None, act: str | None = None):
             y = fp8.fp8_linear(x, w)
             if act == "swiglu":
                 y = swiglu(y)
-            elif act == "gelu":
-                y = activation(y, "gelu")
+            elif act in ("gelu", "relu"):
+                y = activation(y, act)
             if residual is not None:
                 y = y + residual
             return y
@@ -159,6 +161,8 @@ def linear(x, w, bias=None, residual=None, act: str | None = None):
     y = F.linear(x, w, bias)
     if act == "gelu":
         y = F.gelu(y)
+    elif act == "relu":
+        y = F.relu(y)
     elif act == "swiglu":
         v, g = y.chunk(2, dim=-1)
         y = F.silu(g) * v

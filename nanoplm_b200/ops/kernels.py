@@ -12,7 +12,7 @@ import torch
 from . import _lib
 from ._lib import check_rc, count_launch, lib, ptr, status_word, stream_ptr
 
-EPI_STORE, EPI_ADD, EPI_ATOMIC_F32, EPI_GELU, EPI_STORE_F32, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4, 5, 6
+EPI_STORE, EPI_ADD, EPI_ATOMIC_F32, EPI_GELU, EPI_STORE_F32, EPI_SWIGLU, EPI_ROPE, EPI_RELU = 0, 1, 2, 3, 4, 5, 6, 7
 
 _BF16 = torch.bfloat16
 
@@ -40,7 +40,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
     a: [M,K] (a_mn=False) or [K,M] (a_mn=True); b: [N,K] (b_mn=False) or [K,N] (b_mn=True).
     epi: EPI_STORE / EPI_ADD (aux = residual) / EPI_ATOMIC_F32 (out fp32, accumulated in place) /
-    EPI_GELU (aux = optional pre-activation output) / EPI_STORE_F32 / EPI_SWIGLU (out is N/2 wide,
+    EPI_GELU / EPI_RELU (aux = optional pre-activation output) / EPI_STORE_F32 / EPI_SWIGLU (out is N/2 wide,
     aux = optional [M,N] pre-activation output). bf16 outputs leave through shared memory and
     TMA stores; direct_epilogue=True selects per-thread global stores instead.
     EPI_ROPE: rope = (pos int32 [M], cos fp32 [P,32], sin fp32 [P,32], rope_cols): rotary embedding

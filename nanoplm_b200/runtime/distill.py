@@ -55,7 +55,9 @@ class DistillDataCollator:
         tt = self.teacher_tok([TeacherTokenizer.preprocess(s) for s in seqs], padding="max_length", max_length=L,
                               truncation=True, return_tensors="pt")
         return {"input_ids": st["input_ids"], "attention_mask": st["attention_mask"],
-                "teacher_input_ids": tt["input_ids"], "teacher_attention_mask": tt["attention_mask"]}
+                "teacher_input_ids": tt["input_ids"], "teacher_attention_mask": tt["attention_mask"],
+                # host-side row lengths: the teacher drops the padding before its first layer
+                "teacher_lengths": tt["attention_mask"].sum(dim=1).tolist()}
 
 
 def distillation_loss(student: ProtX, batch: dict, teacher=None) -> torch.Tensor:
@@ -65,7 +67,8 @@ def distillation_loss(student: ProtX, batch: dict, teacher=None) -> torch.Tensor
         target = batch["teacher_embeddings"]
     else:
         with torch.no_grad():
-            target = teacher(batch["teacher_input_ids"], batch["teacher_attention_mask"])
+            target = teacher(batch["teacher_input_ids"], batch["teacher_attention_mask"],
+                             lengths=batch.get("teacher_lengths"))
     out = student(ids, mask, training_mode=True)["last_hidden_state"]
     B, S, D = out.shape
     return ops.masked_mse(out.reshape(B * S, D), target.reshape(B * S, D).to(out.dtype), mask.reshape(-1))
@@ -176,7 +179,7 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
     sink = MetricsSink(str(out_dir), cfg.project_name, plan.wandb_run_name, as_plain_dict(cfg), is_main)
 
     def to_dev(b):
-        return {k: v.to(device, non_blocking=True) for k, v in b.items()}
+        return {k: (v.to(device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in b.items()}
 
     @torch.no_grad()
     def evaluate() -> float:

@@ -164,11 +164,11 @@ def test_distillation_step_gpu(cuda_status):
     coll = DistillDataCollator(True, 96)
     batch = coll([{"raw_sequence": s} for s in synthetic_sequences(6, 20, 90, seed=4)])
     loss_c = distillation_loss(s_cpu, batch, t_cpu)
-    loss_g = distillation_loss(student, {k: v.to(dev) for k, v in batch.items()}, teacher)
+    loss_g = distillation_loss(student, {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in batch.items()}, teacher)
     assert abs(loss_c.item() - loss_g.item()) / loss_c.item() < 0.05, (loss_c.item(), loss_g.item())
     losses = []
     for _ in range(8):
-        l = distillation_loss(student, {k: v.to(dev) for k, v in batch.items()}, teacher)
+        l = distillation_loss(student, {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in batch.items()}, teacher)
         l.backward()
         eng.step(2e-3, 1)
         losses.append(l.item())
@@ -247,3 +247,9 @@ def test_teacher_native_attention_matches_sdpa(cuda_status):
         m = mask.bool()
         err = (a[m] - b[m]).abs().max().item()
         assert err < 0.08 * b[m].abs().max().item() + 0.02, (d_kv, err)
+        # host-known lengths: the encoder runs on the real tokens only
+        teacher.native_attention = True
+        c = teacher(ids, mask, lengths=[200, 150, 31]).float()
+        err = (c[m] - b[m]).abs().max().item()
+        assert err < 0.08 * b[m].abs().max().item() + 0.02, (d_kv, err)
+        assert c[~m].abs().max().item() == 0.0

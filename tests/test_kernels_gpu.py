@@ -377,3 +377,22 @@ def test_gemm_rope_epilogue_and_attention_rope_backward(cuda_status):
     k.rope_(d_plain, pos, cos, sin, H, D, backward=True)
     d_fused = k.fa_bwd(ref, out, dout, lse, ss, se, H, D, -1, 0.125, rope=(pos, cos, sin))
     _close(d_fused, d_plain, rtol=3e-2, atol=3e-2, what="attention backward with fused inverse rope")
+
+
+def test_linear_relu_epilogue(cuda_status):
+    """ReLU in the GEMM epilogue (teacher feed-forward): forward under no_grad and forward + backward."""
+    from nanoplm_b200.ops import functional as ops
+    torch.manual_seed(0)
+    x = torch.randn(777, 256, device="cuda").to(BF)
+    w = (torch.randn(512, 256, device="cuda") * 0.1).to(BF)
+    ref = torch.relu(x.float() @ w.float().t())
+    with torch.no_grad():
+        y = ops.linear(x, w, act="relu")
+    assert (y.float() - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 0.02
+    xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    gy = torch.randn(777, 512, device="cuda").to(BF)
+    ops.linear(xg, wg, act="relu").backward(gy)
+    x32, w32 = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    torch.relu(x32 @ w32.t()).backward(gy.float())
+    assert (xg.grad.float() - x32.grad).abs().max().item() < 0.05 * x32.grad.abs().max().item()
+    assert (wg.grad.float() - w32.grad).abs().max().item() < 0.05 * w32.grad.abs().max().item()
