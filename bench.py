@@ -30,6 +30,8 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
+# both arms: same allocator policy as the reference's own pipeline sets for itself
+os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
 
 MODEL = dict(hidden_size=1024, intermediate_size=2048, num_hidden_layers=16, num_attention_heads=16,
              vocab_size=32, max_position_embeddings=1024)
