@@ -123,3 +123,38 @@ def test_heartbeat_and_watchdog(tmp_path):
         check_or_raise(tmp_path, 2, 0.3)
     assert e.value.ranks == [1]
     hb0.stop()
+
+
+def test_padding_tail_trim_is_exact_on_cpu():
+    """forward(num_real_tokens=...) cuts the padding tail of a static flat batch; loss and gradients of
+    the fp32 CPU model must not change."""
+    import torch
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.collators import PackingCollator
+    from nanoplm_b200.data.synthetic import synthetic_token_sequences
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    torch.manual_seed(0)
+    tok = ProtTokenizer()
+    model = ProtEncoderMLM(ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                       num_attention_heads=2, max_position_embeddings=128), tok)
+    with torch.no_grad():
+        for layer in model.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.05)
+            layer.mlp.Wo.weight.normal_(0, 0.05)
+    seqs = synthetic_token_sequences(6, 10, 60, seed=3)
+    coll = PackingCollator(tok, 64, 0.3, target_rows=10, batch_size=6, seed=3)     # 640 slots, ~200 real
+    b = coll([{"input_ids": torch.from_numpy(s)} for s in seqs])
+    n_real = int(b["num_real_tokens"])
+    assert n_real + 128 < b["input_ids"].numel()
+    keys = ("input_ids", "cu_seqlens", "position_ids", "masked_idx", "masked_labels", "max_seqlen")
+    inputs = {k: b[k] for k in keys}
+    results = []
+    for trim in (None, n_real):
+        model.zero_grad()
+        out = model(**inputs, num_real_tokens=trim)
+        out["loss"].backward()
+        results.append((out["loss"].item(), [p.grad.clone() for p in model.parameters() if p.grad is not None]))
+    assert abs(results[0][0] - results[1][0]) < 1e-6
+    for g0, g1 in zip(results[0][1], results[1][1]):
+        assert torch.allclose(g0, g1, atol=1e-6)
