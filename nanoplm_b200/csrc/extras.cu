@@ -439,3 +439,226 @@ extern "C" int nplm_mlm_mask(const long long* ids_in, long long* ids_out, long l
                                                 pool_n, p_sel, p_mask, p_rand, seed, step);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------- mHC coefficients
+// One thread per token turns the raw outputs of the coefficient projection (before tanh) into the
+// mixing coefficients of one hyper-connection site:
+//   d      = tanh(pre[t, :])                                   [2N + N*N]
+//   alpha  = softmax(a + s0 * d[0:N])
+//   beta   = 2 * sigmoid(b + s1 * d[N:2N])
+//   R      = exp(sinkhorn_log(r + s2 * d[2N:], iters))         (rows, then columns, `iters` times)
+// The backward kernel recomputes the forward, keeps the value after every Sinkhorn half-step
+// (for y = x - logsumexp(x): dx = dy - exp(y) * sum(dy)), and returns the gradient w.r.t. pre
+// (bf16) plus block-reduced atomics for the static parameters a, b, r and the three scales.
+// The reference has no hyper-connections.
+namespace nplm {
+
+constexpr int MHC_MAX_ITERS = 8;
+
+template <int N>
+__device__ __forceinline__ void mhc_coef_forward(const float (&d)[2 * N + N * N], const float* a, const float* b,
+                                                 const float* r, const float* s, int iters,
+                                                 float (&alpha)[N], float (&beta)[N], float (&x)[N * N],
+                                                 float* hist) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    alpha[i] = a[i] + s[0] * d[i];
+    mx = fmaxf(mx, alpha[i]);
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    alpha[i] = __expf(alpha[i] - mx);
+    sum += alpha[i];
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) alpha[i] /= sum;
+#pragma unroll
+  for (int i = 0; i < N; ++i) beta[i] = 2.f / (1.f + __expf(-(b[i] + s[1] * d[N + i])));
+#pragma unroll
+  for (int i = 0; i < N * N; ++i) x[i] = r[i] + s[2] * d[2 * N + i];
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {   // rows
+      float m = -INFINITY, se = 0.f;
+#pragma unroll
+      for (int j = 0; j < N; ++j) m = fmaxf(m, x[i * N + j]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) se += __expf(x[i * N + j] - m);
+      const float lse = m + __logf(se);
+#pragma unroll
+      for (int j = 0; j < N; ++j) x[i * N + j] -= lse;
+    }
+    if (hist != nullptr) {
+#pragma unroll
+      for (int i = 0; i < N * N; ++i) hist[(2 * it) * N * N + i] = x[i];
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) {   // columns
+      float m = -INFINITY, se = 0.f;
+#pragma unroll
+      for (int i = 0; i < N; ++i) m = fmaxf(m, x[i * N + j]);
+#pragma unroll
+      for (int i = 0; i < N; ++i) se += __expf(x[i * N + j] - m);
+      const float lse = m + __logf(se);
+#pragma unroll
+      for (int i = 0; i < N; ++i) x[i * N + j] -= lse;
+    }
+    if (hist != nullptr) {
+#pragma unroll
+      for (int i = 0; i < N * N; ++i) hist[(2 * it + 1) * N * N + i] = x[i];
+    }
+  }
+}
+
+template <int N>
+__global__ void __launch_bounds__(128)
+mhc_coef_fwd_kernel(const __nv_bfloat16* __restrict__ pre, const float* __restrict__ a,
+                    const float* __restrict__ b, const float* __restrict__ r, const float* __restrict__ s,
+                    int iters, int T, float* __restrict__ alpha_out, float* __restrict__ beta_out,
+                    float* __restrict__ R_out) {
+  constexpr int M = 2 * N + N * N;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x) {
+    float d[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) d[i] = tanhf(__bfloat162float(pre[static_cast<size_t>(t) * M + i]));
+    float alpha[N], beta[N], x[N * N];
+    mhc_coef_forward<N>(d, a, b, r, s, iters, alpha, beta, x, nullptr);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      alpha_out[t * N + i] = alpha[i];
+      beta_out[t * N + i] = beta[i];
+    }
+#pragma unroll
+    for (int i = 0; i < N * N; ++i) R_out[static_cast<size_t>(t) * N * N + i] = __expf(x[i]);
+  }
+}
+
+template <int N>
+__global__ void __launch_bounds__(128)
+mhc_coef_bwd_kernel(const __nv_bfloat16* __restrict__ pre, const float* __restrict__ a,
+                    const float* __restrict__ b, const float* __restrict__ r, const float* __restrict__ s,
+                    int iters, int T, const float* __restrict__ dalpha, const float* __restrict__ dbeta,
+                    const float* __restrict__ dR, __nv_bfloat16* __restrict__ dpre,
+                    float* __restrict__ da, float* __restrict__ db, float* __restrict__ dr,
+                    float* __restrict__ ds) {
+  constexpr int M = 2 * N + N * N;
+  static_assert(M + 3 <= 32, "parameter gradients are reduced with one value per lane");
+  // per-thread sums of the parameter gradients: [da (N) | db (N) | dr (N*N) | ds (3)]
+  float acc[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+  const int lane = threadIdx.x & 31;
+  // every warp runs the same number of iterations (the reduction below is warp-wide)
+  const int per_pass = gridDim.x * blockDim.x;
+  for (int base = blockIdx.x * blockDim.x; base < T; base += per_pass) {
+    const int t = base + threadIdx.x;
+    if (t < T) {
+      float d[M];
+#pragma unroll
+      for (int i = 0; i < M; ++i) d[i] = tanhf(__bfloat162float(pre[static_cast<size_t>(t) * M + i]));
+      float alpha[N], beta[N], x[N * N];
+      float hist[2 * MHC_MAX_ITERS * N * N];
+      mhc_coef_forward<N>(d, a, b, r, s, iters, alpha, beta, x, hist);
+      float gd[M];   // gradient w.r.t. d (tanh output)
+      // alpha = softmax(u): du = alpha * (dalpha - sum alpha * dalpha)
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < N; ++i) dot += alpha[i] * dalpha[t * N + i];
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const float du = alpha[i] * (dalpha[t * N + i] - dot);
+        acc[i] += du;
+        acc[2 * N + N * N] += du * d[i];
+        gd[i] = du * s[0];
+      }
+      // beta = 2 sigmoid(v): dv = dbeta * beta * (1 - beta / 2)
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const float dv = dbeta[t * N + i] * beta[i] * (1.f - 0.5f * beta[i]);
+        acc[N + i] += dv;
+        acc[2 * N + N * N + 1] += dv * d[N + i];
+        gd[N + i] = dv * s[1];
+      }
+      // R = exp(x_final): dx = dR * R, then back through the half-steps
+      float g[N * N];
+#pragma unroll
+      for (int i = 0; i < N * N; ++i) g[i] = dR[static_cast<size_t>(t) * N * N + i] * __expf(x[i]);
+      for (int it = iters - 1; it >= 0; --it) {
+        const float* yc = hist + (2 * it + 1) * N * N;   // after the column step
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          float sg = 0.f;
+#pragma unroll
+          for (int i = 0; i < N; ++i) sg += g[i * N + j];
+#pragma unroll
+          for (int i = 0; i < N; ++i) g[i * N + j] -= __expf(yc[i * N + j]) * sg;
+        }
+        const float* yr = hist + (2 * it) * N * N;       // after the row step
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          float sg = 0.f;
+#pragma unroll
+          for (int j = 0; j < N; ++j) sg += g[i * N + j];
+#pragma unroll
+          for (int j = 0; j < N; ++j) g[i * N + j] -= __expf(yr[i * N + j]) * sg;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < N * N; ++i) {
+        acc[2 * N + i] += g[i];
+        acc[2 * N + N * N + 2] += g[i] * d[2 * N + i];
+        gd[2 * N + i] = g[i] * s[2];
+      }
+#pragma unroll
+      for (int i = 0; i < M; ++i)
+        dpre[static_cast<size_t>(t) * M + i] = __float2bfloat16(gd[i] * (1.f - d[i] * d[i]));
+    }
+  }
+  // warp-wide sums (lane l receives the total of acc[l]), one atomic per value and warp
+  const float total = warp_transpose_sum<M + 3>(acc, lane);
+  if (lane < N) atomicAdd(&da[lane], total);
+  else if (lane < 2 * N) atomicAdd(&db[lane - N], total);
+  else if (lane < 2 * N + N * N) atomicAdd(&dr[lane - 2 * N], total);
+  else if (lane < M + 3) atomicAdd(&ds[lane - M], total);
+}
+
+}  // namespace nplm
+
+extern "C" int nplm_mhc_coef_fwd(const void* pre, const float* a, const float* b, const float* r,
+                                 const float* s, int iters, int T, int n, float* alpha, float* beta,
+                                 float* R, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (n != 4 && n != 2) return -3;
+  if (iters < 1 || iters > nplm::MHC_MAX_ITERS) return -3;
+  int blocks = (T + 127) / 128;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(pre);
+  if (n == 4)
+    nplm::mhc_coef_fwd_kernel<4><<<blocks, 128, 0, st>>>(p, a, b, r, s, iters, T, alpha, beta, R);
+  else
+    nplm::mhc_coef_fwd_kernel<2><<<blocks, 128, 0, st>>>(p, a, b, r, s, iters, T, alpha, beta, R);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// da / db / dr / ds are accumulated (callers pass zeroed or running fp32 buffers)
+extern "C" int nplm_mhc_coef_bwd(const void* pre, const float* a, const float* b, const float* r,
+                                 const float* s, int iters, int T, int n, const float* dalpha,
+                                 const float* dbeta, const float* dR, void* dpre, float* da, float* db,
+                                 float* dr, float* ds, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (n != 4 && n != 2) return -3;
+  if (iters < 1 || iters > nplm::MHC_MAX_ITERS) return -3;
+  int blocks = (T + 127) / 128;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(pre);
+  __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(dpre);
+  if (n == 4)
+    nplm::mhc_coef_bwd_kernel<4><<<blocks, 128, 0, st>>>(p, a, b, r, s, iters, T, dalpha, dbeta, dR, dp, da, db,
+                                                         dr, ds);
+  else
+    nplm::mhc_coef_bwd_kernel<2><<<blocks, 128, 0, st>>>(p, a, b, r, s, iters, T, dalpha, dbeta, dR, dp, da, db,
+                                                         dr, ds);
+  return static_cast<int>(cudaGetLastError());
+}

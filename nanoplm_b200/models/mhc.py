@@ -74,6 +74,36 @@ def mhc_write(X, y, R, beta):
     return torch.einsum("tij,tjc->tic", R.to(X.dtype), X) + beta.to(X.dtype)[:, :, None] * y[:, None, :]
 
 
+class _CoefFn(torch.autograd.Function):
+    """(raw projections, static parts, scales) -> (alpha, beta, R) in one kernel each way
+    (tanh, softmax, sigmoid and the log-domain Sinkhorn iterations; nanoplm_b200/csrc/extras.cu)."""
+
+    @staticmethod
+    def forward(ctx, pre, a, b, r, s, iters, n):
+        pre = pre.contiguous()
+        a32, b32, r32, s32 = (t.detach().float().contiguous() for t in (a, b, r, s))
+        alpha, beta, R = K.mhc_coef_fwd(pre, a32, b32, r32, s32, iters, n)
+        ctx.save_for_backward(pre, a32, b32, r32, s32)
+        ctx.iters, ctx.n = iters, n
+        ctx.refs = (a, b, r, s)
+        return alpha, beta, R
+
+    @staticmethod
+    def backward(ctx, dalpha, dbeta, dR):
+        from nanoplm_b200.ops.functional import _param_grad
+        pre, a32, b32, r32, s32 = ctx.saved_tensors
+        n, dev = ctx.n, pre.device
+        T = pre.shape[0]
+        zeros = lambda *shape: torch.zeros(shape, dtype=torch.float32, device=dev)
+        dalpha = dalpha.float().contiguous() if dalpha is not None else zeros(T, n)
+        dbeta = dbeta.float().contiguous() if dbeta is not None else zeros(T, n)
+        dR = dR.float().contiguous() if dR is not None else zeros(T, n, n)
+        da, db, dr, ds = zeros(n), zeros(n), zeros(n, n), zeros(3)
+        dpre = K.mhc_coef_bwd(pre, a32, b32, r32, s32, ctx.iters, n, dalpha, dbeta, dR, da, db, dr, ds)
+        a, b, r, s = ctx.refs
+        return dpre, _param_grad(a, da), _param_grad(b, db), _param_grad(r, dr), _param_grad(s, ds), None, None
+
+
 class HyperConnection(nn.Module):
     def __init__(self, dim: int, n: int, sinkhorn_iters: int = 5, eps: float = 1e-5):
         super().__init__()
@@ -92,7 +122,11 @@ class HyperConnection(nn.Module):
             # stream mean without an fp32 copy of X, then the RMSNorm and GEMM kernels of this package
             from nanoplm_b200.ops import functional as ops
             zn = ops.norm(X.mean(dim=1), self.coef_norm_weight, self.eps, rms=True)
-            d = torch.tanh(ops.linear(zn, self.coef_proj.weight).float())
+            pre = ops.linear(zn, self.coef_proj.weight)
+            if n in (2, 4) and 1 <= self.iters <= 8:
+                return _CoefFn.apply(pre, self.static_alpha, self.static_beta, self.static_res, self.dyn_scale,
+                                     max(1, self.iters), n)
+            d = torch.tanh(pre.float())
         else:
             z = X.float().mean(dim=1)
             z = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + self.eps) * self.coef_norm_weight.float()

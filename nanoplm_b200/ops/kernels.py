@@ -465,6 +465,34 @@ def mhc_bwd(X, y, R, alpha, beta, dXn, dh):
 
 
 # --------------------------------------------------------------------------- device-side MLM masking
+def mhc_coef_fwd(pre, a, b, r, s, iters: int, n: int):
+    """Raw coefficient projections pre bf16 [T, 2n+n*n] -> (alpha [T,n], beta [T,n], R [T,n,n]) fp32.
+    a, b [n], r [n,n], s [3]: fp32 static parts and dynamic scales."""
+    _chk(pre, _BF16, "pre")
+    T = pre.shape[0]
+    dev = pre.device
+    alpha = torch.empty((T, n), dtype=torch.float32, device=dev)
+    beta = torch.empty((T, n), dtype=torch.float32, device=dev)
+    R = torch.empty((T, n, n), dtype=torch.float32, device=dev)
+    rc = lib("extras").nplm_mhc_coef_fwd(ptr(pre), ptr(a), ptr(b), ptr(r), ptr(s), c_int(iters), c_int(T),
+                                         c_int(n), ptr(alpha), ptr(beta), ptr(R), stream_ptr())
+    check_rc(rc, "mhc_coef_fwd")
+    count_launch()
+    return alpha, beta, R
+
+
+def mhc_coef_bwd(pre, a, b, r, s, iters: int, n: int, dalpha, dbeta, dR, da, db, dr, ds):
+    """Backward of mhc_coef_fwd. Returns dpre (bf16); da, db, dr, ds (fp32) are accumulated in place."""
+    T = pre.shape[0]
+    dpre = torch.empty_like(pre)
+    rc = lib("extras").nplm_mhc_coef_bwd(ptr(pre), ptr(a), ptr(b), ptr(r), ptr(s), c_int(iters), c_int(T),
+                                         c_int(n), ptr(dalpha), ptr(dbeta), ptr(dR), ptr(dpre), ptr(da), ptr(db),
+                                         ptr(dr), ptr(ds), stream_ptr())
+    check_rc(rc, "mhc_coef_bwd")
+    count_launch()
+    return dpre
+
+
 def mlm_mask(ids: torch.Tensor, n_real: int, special_ids, mask_id: int, pool: torch.Tensor, p_sel: float,
              p_mask: float, p_rand: float, seed: int, step: int):
     """Philox masking of flat int64 ids on the device. Returns (corrupted ids, labels)."""

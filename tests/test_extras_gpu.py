@@ -134,6 +134,10 @@ def test_hybrid_encoder_matches_cpu(variant, cuda_status):
             continue
         if "static_alpha" in s.name:      # softmax over near-identical streams: the gradient is a
             continue                      # cancellation residue, dominated by bf16 rounding
+        if "static_res" in s.name:        # R starts within e^-6 of the identity: the Sinkhorn backward
+            continue                      # leaves a residue of that size times dR, i.e. of the size of
+                                          # dR's bf16 rounding; the kernel itself is checked against fp32
+                                          # in test_mhc_coefficient_kernel_matches_torch (sharp case)
         g_ref = by_name[s.name].grad
         if g_ref is None:
             continue
@@ -253,3 +257,46 @@ def test_teacher_native_attention_matches_sdpa(cuda_status):
         err = (c[m] - b[m]).abs().max().item()
         assert err < 0.08 * b[m].abs().max().item() + 0.02, (d_kv, err)
         assert c[~m].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("n,iters,sharp", [(4, 5, False), (2, 3, False), (4, 5, True)])
+def test_mhc_coefficient_kernel_matches_torch(n, iters, sharp, cuda_status):
+    """Fused tanh / softmax / sigmoid / Sinkhorn coefficient kernel against the PyTorch restatement,
+    forward values and every gradient."""
+    from nanoplm_b200.models.mhc import _CoefFn, sinkhorn
+    torch.manual_seed(0)
+    dev = torch.device("cuda:0")
+    T, M = 777, 2 * n + n * n
+    pre = (torch.randn(T, M, device=dev) * 1.5).to(BF)
+    a = (torch.randn(n, device=dev) * 0.3).requires_grad_(True)
+    b = (torch.randn(n, device=dev) * 0.3).requires_grad_(True)
+    if sharp:   # the initial state of a model: R within e^-6 of the identity, tiny dynamic part
+        r = (torch.eye(n, device=dev) * 6.0 - 3.0).requires_grad_(True)
+        s = torch.tensor([0.01, 0.01, 0.01], device=dev, requires_grad=True)
+    else:
+        r = (torch.eye(n, device=dev) * 3.0 - 1.5 + 0.2 * torch.randn(n, n, device=dev)).requires_grad_(True)
+        s = torch.tensor([0.4, 0.3, 0.5], device=dev, requires_grad=True)
+    ga, gb, gR = torch.randn(T, n, device=dev), torch.randn(T, n, device=dev), torch.randn(T, n, n, device=dev)
+
+    p1 = pre.clone().requires_grad_(True)
+    alpha, beta, R = _CoefFn.apply(p1, a, b, r, s, iters, n)
+    ((alpha * ga).sum() + (beta * gb).sum() + (R * gR).sum()).backward()
+    got = [t.grad.clone() for t in (p1, a, b, r, s)]
+    for t in (a, b, r, s):
+        t.grad = None
+
+    p2 = pre.float().requires_grad_(True)
+    d = torch.tanh(p2)
+    alpha_r = torch.softmax(a + s[0] * d[:, :n], dim=-1)
+    beta_r = 2.0 * torch.sigmoid(b + s[1] * d[:, n:2 * n])
+    R_r = sinkhorn(r + s[2] * d[:, 2 * n:].reshape(-1, n, n), iters)
+    ((alpha_r * ga).sum() + (beta_r * gb).sum() + (R_r * gR).sum()).backward()
+    want = [t.grad for t in (p2, a, b, r, s)]
+
+    assert torch.allclose(alpha, alpha_r.detach(), atol=2e-5)
+    assert torch.allclose(beta, beta_r.detach(), atol=2e-5)
+    assert torch.allclose(R, R_r.detach(), atol=2e-5)
+    for name, g, w in zip(("dpre", "da", "db", "dr", "ds"), got, want):
+        tol = 0.02 if name == "dpre" else 2e-3           # dpre is stored in bf16
+        err = (g.float() - w.float()).abs().max().item()
+        assert err <= tol * (w.abs().max().item() + 1e-3), (name, err, w.abs().max().item())
