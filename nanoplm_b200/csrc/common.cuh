@@ -28,6 +28,9 @@ enum : int {
 
 // ~1 s at 2 GHz. Long enough for any legitimate wait in these kernels.
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+#ifndef NPLM_TRY_WAIT_BURST
+#define NPLM_TRY_WAIT_BURST 64   // blocking try_wait attempts before the polling loop
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -111,14 +114,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // the clock every few polls, so the bound holds whatever the hardware's try_wait time-out is.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 #pragma unroll 1
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < NPLM_TRY_WAIT_BURST; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_test_wait(bar, parity)) {
     if ((++spins & 0xf) == 0) {
       if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
-      __nanosleep(64);
+      if (spins > 4096) __nanosleep(64);   // back off only on waits that are already long
     }
   }
   return true;
