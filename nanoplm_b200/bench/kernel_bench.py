@@ -39,7 +39,7 @@ def time_fn(fn, iters=10, warmup=3, flush=None):
     return times[len(times) // 2]
 
 
-def bench_gemm(T, peaks):
+def bench_gemm(T, peaks, sweep_splits=False):
     from nanoplm_b200.ops import kernels as k
     flush = _flush_buf()
     shapes = [  # (name, M, N, K, a_mn, b_mn, epi)
@@ -74,6 +74,24 @@ def bench_gemm(T, peaks):
             print(json.dumps({"kernel": "gemm_bf16_tcgen05", "case": name, "bn": bn, "splits": splits,
                               "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
                               "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 3)}))
+        if not (a_mn and not b_mn):
+            sp = k.wgrad_splits(M, N, K, 256) if epi == k.EPI_ATOMIC_F32 else 1
+            ms = time_fn(lambda: k.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=epi, out=out, aux=aux,
+                                        splits=sp, bn=256, pair=True), flush=flush)
+            tf = 2.0 * M * N * K / ms / 1e9
+            print(json.dumps({"kernel": "gemm_bf16_tcgen05_cta_pair", "case": name, "bn": 256, "splits": sp,
+                              "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
+                              "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 3)}))
+        if epi == k.EPI_ATOMIC_F32 and sweep_splits:
+            for pr in (False, True):
+                for sp in (0, 1, 2, 3, 4, 6, 8, 12, 16):
+                    ms = time_fn(lambda: k.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=epi, out=out, splits=sp, bn=256,
+                                                pair=pr), flush=flush)
+                    tf = 2.0 * M * N * K / ms / 1e9
+                    print(json.dumps({"kernel": "gemm_bf16_tcgen05" + ("_cta_pair" if pr else ""), "case": name,
+                                      "bn": 256, "splits": sp if sp else "stream-k", "M": M, "N": N, "K": K,
+                                      "ms": round(ms, 4), "tflops": round(tf, 1),
+                                      "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 3)}))
         af = a.t() if a_mn else a
         bf_ = b if b_mn else b.t()
         ms = time_fn(lambda: torch.matmul(af, bf_), flush=flush)
@@ -254,10 +272,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--what", default="gemm,attn,elementwise")
+    ap.add_argument("--sweep-splits", action="store_true",
+                    help="gemm: time every weight-gradient shape at split-K factors 1..16 and stream-K")
     args = ap.parse_args()
     from nanoplm_b200.utils.peaks import measured_peaks
     peaks = measured_peaks()
     for what in args.what.split(","):
+        if what == "gemm":
+            bench_gemm(args.tokens, peaks, args.sweep_splits)
+            continue
         {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "fp8": bench_fp8,
          "moe": bench_moe}[what](args.tokens, peaks)
 

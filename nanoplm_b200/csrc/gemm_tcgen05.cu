@@ -38,15 +38,19 @@ enum : int {
                        // first column is < rope_cols (the q and k parts of a fused QKV projection)
 };
 
-template <int BN>
+// PAIR: two CTAs of a cluster (cta_group::2) share one 256 x BN tile; each holds its own 128 rows
+// of A and half of B, which cuts the L2 -> shared-memory traffic per FLOP by a third.
+// STAGED: the epilogue goes through shared memory (TMA stores); kernels that write straight from
+// registers (fp32 outputs, the direct epilogue) spend that room on one more pipeline stage.
+template <int BN, bool PAIR = false, bool STAGED = true>
 struct GemmSmem {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = PAIR ? (STAGED ? 6 : 7) : ((BN == 256) ? 4 : (STAGED ? 6 : 7));
   static constexpr int BAR_BYTES = 256;
   // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B), written swizzled, read by TMA stores
-  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int EPI_BYTES = STAGED ? 4 * 2 * 4096 : 0;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
@@ -118,12 +122,17 @@ __device__ __forceinline__ void stage_store_bf16(uint8_t* stage, int& toggle, co
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI, bool TMA_EPI>
+template <int BN, bool A_MN, bool B_MN, int EPI, bool TMA_EPI, bool PAIR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  const GemmArgs args) {
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, PAIR, TMA_EPI>;
+  // CTA pair: rank 0 issues the MMAs, both CTAs load operands and run their own epilogue
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int work_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int work_stride = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  constexpr int MT = PAIR ? 2 * BM : BM;   // rows of one work item
   constexpr int STAGES = S::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -145,12 +154,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // For EPI_SWIGLU the logical tile covers BN/2 value columns and BN/2 gate columns.
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int n_extent = (EPI == EPI_SWIGLU) ? args.swiglu_half : N;
-  const int num_m = (M + BM - 1) / BM;
+  const int num_m = (M + MT - 1) / MT;
   const int num_n = (n_extent + TILE_N - 1) / TILE_N;
   const int num_kb = (K + BK - 1) / BK;
-  const int splits = args.splits;
+  // splits == 0: stream-K. The tiles x k-blocks units are cut into one contiguous, equally long
+  // range per worker (CTA or CTA pair); a worker's range covers the tail of one tile, whole tiles
+  // and the head of another, and every piece is added to C atomically (EPI_ATOMIC_F32 only).
+  const bool stream_k = args.splits == 0;
+  const int splits = stream_k ? 1 : args.splits;
   const int kb_per = (num_kb + splits - 1) / splits;
-  const int total_work = (args.group_mode == 2 ? args.groups : splits) * num_m * num_n;
+  const long long sk_units = static_cast<long long>(num_m) * num_n * num_kb;
+  const long long sk_lo = sk_units * work_first / work_stride;
+  const long long sk_hi = sk_units * (work_first + 1) / work_stride;
+  const int w_begin = stream_k ? 0 : work_first;
+  const int w_step = stream_k ? 1 : work_stride;
+  const int total_work = stream_k ? static_cast<int>((sk_hi + num_kb - 1) / num_kb - sk_lo / num_kb)
+                                  : (args.group_mode == 2 ? args.groups : splits) * num_m * num_n;
 
   // work item -> tile coordinates and contraction range; false = nothing to do for this item
   auto decode = [&](int w, WorkItem& it) -> bool {
@@ -159,14 +178,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (args.group_mode == 2) {
       const int per = num_m * num_n;
       const int g = w / per, tile = w % per;
-      it.m0 = (tile / num_n) * BM;
+      it.m0 = (tile / num_n) * MT + static_cast<int>(rank) * BM;
       it.n0 = (tile % num_n) * TILE_N;
       it.kb0 = args.group_off[g] / BK;
       it.kb1 = args.group_off[g + 1] / BK;
       it.c_off = static_cast<long long>(g) * args.c_group_stride;
       return it.kb0 < it.kb1;
     }
-    const int split = w % splits, tile = w / splits;
+    if (stream_k) {
+      const long long tile = sk_lo / num_kb + w;
+      const long long first = tile * num_kb;
+      it.m0 = static_cast<int>(tile / num_n) * MT + static_cast<int>(rank) * BM;
+      it.n0 = static_cast<int>(tile % num_n) * TILE_N;
+      it.kb0 = w == 0 ? static_cast<int>(sk_lo - first) : 0;
+      it.kb1 = static_cast<int>(min(sk_hi - first, static_cast<long long>(num_kb)));
+      return it.kb0 < it.kb1;
+    }
+    // tiles run fastest: the CTAs of one wave then walk the same contraction range of different
+    // tiles, so an operand panel fetched for one of them serves its whole tile row / column from L2
+    const int num_tiles = num_m * num_n;
+    const int split = w / num_tiles, tile = w % num_tiles;
     if (args.ag_world > 1) {
       // shard by shard starting with the local one; inside a shard n runs fastest
       const int n_per = args.ag_rows / TILE_N;
@@ -176,7 +207,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       it.m0 = (rem / n_per) * BM;
       it.n0 = shard * args.ag_rows + (rem % n_per) * TILE_N;
     } else {
-      it.m0 = (tile / num_n) * BM;
+      it.m0 = (tile / num_n) * MT + static_cast<int>(rank) * BM;
       it.n0 = (tile % num_n) * TILE_N;
     }
     it.kb0 = split * kb_per;
@@ -196,7 +227,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], PAIR ? 8 : 4);   // epilogue warps of both CTAs release rank 0's accumulator
     }
     for (int i = 0; i < 8; ++i) mbar_init(&res_bar[i], 1);
     *abort_flag = 0;
@@ -212,13 +243,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, 2 * BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // hands accumulator `a` back to the MMA thread (of rank 0)
+  auto release_acc = [&](int a) {
+    if constexpr (PAIR) {
+      if (rank == 0) mbar_arrive(&tempty_bar[a]);
+      else mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[a]), 0));
+    } else {
+      mbar_arrive(&tempty_bar[a]);
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -227,7 +273,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       uint32_t ag_seen = 0;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      for (int w = w_begin; w < total_work && ok; w += w_step) {
         WorkItem it;
         if (!decode(w, it)) continue;
         const int m0 = it.m0, n0 = it.n0, kb0 = it.kb0, kb1 = it.kb1;
@@ -259,8 +305,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], S::STAGE_BYTES);
           const int k0 = kb * BK;
+          if constexpr (PAIR) {
+            // rank 0's barrier counts the bytes of both CTAs; every CTA loads its own 128 rows of A
+            // (m0 already carries the rank offset) and its half of B
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+            if constexpr (!A_MN) {
+              tma_load_2d_pair(sa, &tmA, &full_bar[stage], k0, m0);
+            } else {
+#pragma unroll
+              for (int g = 0; g < BM / 64; ++g)
+                tma_load_2d_pair(sa + g * (BK * 128), &tmA, &full_bar[stage], m0 + g * 64, k0);
+            }
+            if constexpr (EPI == EPI_SWIGLU) {
+              // rank 0 holds the value rows, rank 1 the gate rows of this tile
+              tma_load_2d_pair(sb, &tmB, &full_bar[stage], k0,
+                               (rank == 0 ? 0 : args.swiglu_half) + n0);
+            } else if constexpr (!B_MN) {
+              tma_load_2d_pair(sb, &tmB, &full_bar[stage], k0, n0 + static_cast<int>(rank) * (BN / 2));
+            } else {
+#pragma unroll
+              for (int g = 0; g < BN / 128; ++g)
+                tma_load_2d_pair(sb + g * (BK * 128), &tmB, &full_bar[stage],
+                                 n0 + (static_cast<int>(rank) * (BN / 128) + g) * 64, k0);
+            }
+          } else {
+          mbar_arrive_expect_tx(&full_bar[stage], S::STAGE_BYTES);
           if constexpr (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
           } else {
@@ -279,6 +349,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int g = 0; g < BN / 64; ++g)
               tma_load_2d(sb + g * (BK * 128), &tmB, &full_bar[stage], n0 + g * 64, brow + k0);
           }
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -288,14 +359,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    if (lane == 0 && (!PAIR || rank == 0)) {
+      constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 2 * BM : BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // arrive-on-completion of everything issued so far; in a pair both CTAs are notified
+      auto commit = [&](uint64_t* bar) {
+        if constexpr (PAIR) {
+          const uint32_t a = smem_u32(bar);
+          umma_commit_pair(a);
+          umma_commit_pair(mapa_shared(a, 1));
+        } else {
+          umma_commit(bar);
+        }
+      };
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      for (int w = w_begin; w < total_work && ok; w += w_step) {
         WorkItem it;
         if (!decode(w, it)) continue;
         const int kb0 = it.kb0, kb1 = it.kb1;
@@ -322,16 +403,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * (UMMA_K * 128), BK * 128, 1024)
                                      : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024);
-            umma_bf16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if constexpr (PAIR)
+              umma_bf16_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else
+              umma_bf16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
+          commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&tfull_bar[acc]);
+        commit(&tfull_bar[acc]);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
@@ -368,7 +452,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     int stage_toggle = 0;       // which of this warp's two staging buffers is next
     uint32_t res_phase = 0;     // parity bits of this warp's two residual barriers
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+    for (int w = w_begin; w < total_work; w += w_step) {
       WorkItem it;
       if (!decode(w, it)) continue;
       const int m0 = it.m0, n0 = it.n0;
@@ -413,7 +497,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (c == NCH - 1) {
               tc_fence_before();
               __syncwarp();
-              if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+              if (lane == 0) release_acc(acc);
             }
             const int x = n0 + c * 64;
             if (rows_in && x < n_extent) {
@@ -454,7 +538,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (c == NCH - 1) {
               tc_fence_before();
               __syncwarp();
-              if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+              if (lane == 0) release_acc(acc);
             }
             const int x = n0 + c * 64;
             const bool active = rows_in && x < N;
@@ -559,7 +643,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // last read of this accumulator: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+            if (lane == 0) release_acc(acc);
           }
           const int col = n0 + c;
           if (row_ok) {
@@ -603,7 +687,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (c + 32 >= BN) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+            if (lane == 0) release_acc(acc);
           }
           const int col = n0 + c;
           if (row_ok) {
@@ -681,9 +765,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // nobody leaves while the peer may still signal or use this CTA
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
@@ -746,7 +832,7 @@ template <int BN, bool A_MN, bool B_MN, int EPI, bool TMA_EPI>
 static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
   const CUtensorMap& tmA = maps.A;
   const CUtensorMap& tmB = maps.B;
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, false, TMA_EPI>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, TMA_EPI>;
   static bool configured = false;
   if (!configured) {
@@ -757,8 +843,11 @@ static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas,
   const int n_extent = (EPI == EPI_SWIGLU) ? args.swiglu_half : args.N;
   const int num_m = (args.M + BM - 1) / BM;
   const int num_n = (n_extent + TILE_N - 1) / TILE_N;
-  const int total = num_m * num_n * (args.group_mode == 2 ? args.groups : args.splits);
-  int grid = total < num_sms() ? total : num_sms();
+  const long long total = args.splits == 0
+                              ? static_cast<long long>(num_m) * num_n * ((args.K + BK - 1) / BK)
+                              : static_cast<long long>(num_m) * num_n *
+                                    (args.group_mode == 2 ? args.groups : args.splits);
+  int grid = total < num_sms() ? static_cast<int>(total) : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
   if (args.ag_world > 1) {
@@ -773,6 +862,52 @@ static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas,
   }
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, maps.C, maps.R, args);
   return static_cast<int>(cudaGetLastError());
+}
+
+// CTA-pair form (BN = 256 only): clusters of two CTAs, one 256 x 256 work item per cluster and step.
+template <bool A_MN, bool B_MN, int EPI, bool TMA_EPI>
+static int launch_pair_impl(const GemmMaps& maps, const GemmArgs& args, cudaStream_t stream) {
+  using S = GemmSmem<256, true, TMA_EPI>;
+  auto kern = gemm_bf16_kernel<256, A_MN, B_MN, EPI, TMA_EPI, true>;
+  static bool configured = false;
+  if (!configured) {
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured = true;
+  }
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? 128 : 256;
+  const int n_extent = (EPI == EPI_SWIGLU) ? args.swiglu_half : args.N;
+  const int num_m = (args.M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (n_extent + TILE_N - 1) / TILE_N;
+  const long long total = static_cast<long long>(num_m) * num_n *
+                          (args.splits == 0 ? (args.K + BK - 1) / BK : args.splits);
+  int pairs = num_sms() / 2;
+  if (pairs > total) pairs = static_cast<int>(total);
+  if (pairs <= 0) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = S::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, maps.A, maps.B, maps.C, maps.R, args));
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_pair(const GemmMaps& maps, const GemmArgs& args, cudaStream_t stream) {
+  if constexpr (EPI == EPI_ROPE) {
+    return launch_pair_impl<A_MN, B_MN, EPI, true>(maps, args, stream);
+  } else {
+    if constexpr (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_GELU || EPI == EPI_SWIGLU) {
+      if (maps.tma_epi) return launch_pair_impl<A_MN, B_MN, EPI, true>(maps, args, stream);
+    }
+    return launch_pair_impl<A_MN, B_MN, EPI, false>(maps, args, stream);
+  }
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
@@ -802,6 +937,8 @@ struct GroupSpec {
   const int* group_off = nullptr;
   int b_group_rows = 0;
   long long c_group_stride = 0;
+  // CTA-pair (cta_group::2) kernel, BN = 256, plain (not grouped / all-gather) GEMMs only
+  bool pair = false;
   // all-gather mode
   int ag_world = 0, ag_rank = 0;
   void* const* ag_ptrs = nullptr;  // every rank's full B buffer (this rank's one is B itself)
@@ -837,13 +974,16 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
                           rope_sin == nullptr || (rope_cols % 64) || (N % 64)))
     return -7;
   const int num_kb = (K + BK - 1) / BK;
-  if (splits < 1) splits = 1;
+  if (splits < 0) splits = 1;
   if (splits > num_kb) splits = num_kb;
-  if (epi != EPI_ATOMIC_F32 || grp.mode != 0) splits = 1;
+  if (epi != EPI_ATOMIC_F32 || grp.mode != 0) splits = 1;   // splits == 0 (stream-K) adds atomically too
+  if (splits == 0 && grp.ag_world > 1) splits = 1;
   // outer (row) extent of the B tensor map: all groups' operands stacked
   const uint64_t b_rows_kmajor = grp.mode == 1 ? static_cast<uint64_t>(grp.b_group_rows) * grp.groups : N;
   const uint64_t b_rows_mnmajor = grp.mode == 1 ? static_cast<uint64_t>(grp.b_group_rows) * grp.groups : K;
 
+  const bool pair = grp.pair && bn == 256 && grp.mode == 0 && grp.ag_world <= 1 && max_ctas == 0 &&
+                    !(a_mn && !b_mn);
   GemmMaps maps;
   CUtensorMap& tmA = maps.A;
   CUtensorMap& tmB = maps.B;
@@ -856,7 +996,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   if (epi == EPI_SWIGLU)
     rc = make_map_2d(&tmB, B, K, b_rows_kmajor, ldb, BK, bn / 2, 2);
   else if (!b_mn)
-    rc = make_map_2d(&tmB, B, K, b_rows_kmajor, ldb, BK, bn, 2);
+    rc = make_map_2d(&tmB, B, K, b_rows_kmajor, ldb, BK, pair ? bn / 2 : bn, 2);   // a pair CTA loads half of the rows
   else
     rc = make_map_2d(&tmB, B, N, b_rows_mnmajor, ldb, 64, BK, 2);
   if (rc) return rc;
@@ -929,6 +1069,27 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
     default: break;                                                                          \
   }
 
+  if (pair) {
+#define NPLM_DISPATCH_PAIR(AMN_, BMN_)                                                     \
+  switch (epi) {                                                                           \
+    case EPI_STORE: return launch_pair<AMN_, BMN_, EPI_STORE>(maps, args, stream);         \
+    case EPI_ADD: return launch_pair<AMN_, BMN_, EPI_ADD>(maps, args, stream);             \
+    case EPI_ATOMIC_F32: return launch_pair<AMN_, BMN_, EPI_ATOMIC_F32>(maps, args, stream); \
+    case EPI_STORE_F32: return launch_pair<AMN_, BMN_, EPI_STORE_F32>(maps, args, stream); \
+    default: break;                                                                        \
+  }
+    if (epi == EPI_GELU || epi == EPI_SWIGLU || epi == EPI_ROPE) {
+      if (a_mn || b_mn) return -7;
+      if (epi == EPI_GELU) return launch_pair<false, false, EPI_GELU>(maps, args, stream);
+      if (epi == EPI_SWIGLU) return launch_pair<false, false, EPI_SWIGLU>(maps, args, stream);
+      return launch_pair<false, false, EPI_ROPE>(maps, args, stream);
+    }
+    if (!a_mn && !b_mn) { NPLM_DISPATCH_PAIR(false, false) }
+    else if (!a_mn && b_mn) { NPLM_DISPATCH_PAIR(false, true) }
+    else { NPLM_DISPATCH_PAIR(true, true) }
+#undef NPLM_DISPATCH_PAIR
+    return -8;
+  }
   if (epi == EPI_GELU) {
     if (a_mn || b_mn) return -7;
     if (bn == 256) return launch<256, false, false, EPI_GELU>(maps, args, max_ctas, stream);
@@ -964,6 +1125,19 @@ extern "C" int nplm_gemm_bf16(const void* A, const void* B, void* C, const void*
                               int rope_cols, int* status, cudaStream_t stream) {
   return gemm_entry(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, splits, bn, max_ctas,
                     direct_epilogue, rope_pos, rope_cos, rope_sin, rope_cols, status, stream, GroupSpec());
+}
+
+// Same GEMM on CTA pairs (tcgen05 cta_group::2): two SMs share every 256 x 256 tile, each loading
+// its own rows of A and half of B. bn is 256; unsupported forms fall back to the single-CTA kernel.
+extern "C" int nplm_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N,
+                                   int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn,
+                                   int epi, int splits, int direct_epilogue, const int* rope_pos,
+                                   const float* rope_cos, const float* rope_sin, int rope_cols,
+                                   int* status, cudaStream_t stream) {
+  GroupSpec g;
+  g.pair = true;
+  return gemm_entry(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, splits, 256, 0,
+                    direct_epilogue, rope_pos, rope_cos, rope_sin, rope_cols, status, stream, g);
 }
 
 // Grouped GEMM over row groups (mixture-of-experts forward and data gradient).

@@ -32,10 +32,20 @@ def _rowmajor(t: torch.Tensor, name: str) -> int:
 
 
 # --------------------------------------------------------------------------- GEMM
+import os as _os
+
+_GEMM_PAIR_DEFAULT = [_os.environ.get("NPLM_GEMM_PAIR", "0") == "1"]
+
+
+def set_gemm_pair_default(enabled: bool) -> None:
+    """Default of gemm(pair=None): run qualifying GEMMs on CTA pairs (cta_group::2)."""
+    _GEMM_PAIR_DEFAULT[0] = bool(enabled)
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          epi: int = EPI_STORE, out: torch.Tensor | None = None, aux: torch.Tensor | None = None,
          splits: int = 1, bn: int | None = None, max_ctas: int = 0,
-         direct_epilogue: bool = False, rope: tuple | None = None) -> torch.Tensor:
+         direct_epilogue: bool = False, rope: tuple | None = None, pair: bool | None = None) -> torch.Tensor:
     """C[M,N] (+)= op(A) op(B)^T on tcgen05 tensor cores.
 
     a: [M,K] (a_mn=False) or [K,M] (a_mn=True); b: [N,K] (b_mn=False) or [K,N] (b_mn=True).
@@ -45,6 +55,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     TMA stores; direct_epilogue=True selects per-thread global stores instead.
     EPI_ROPE: rope = (pos int32 [M], cos fp32 [P,32], sin fp32 [P,32], rope_cols): rotary embedding
     (head_dim 64) on every 64-wide head that starts below column rope_cols.
+    pair: run on CTA pairs (tcgen05 cta_group::2, two SMs per 256 x 256 tile). None = the package
+    default (`set_gemm_pair_default`); only 256-wide tiles without max_ctas qualify.
     """
     _chk(a, _BF16, "a")
     _chk(b, _BF16, "b")
@@ -89,6 +101,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         _chk(r_cos, torch.float32, "rope cos")
         if r_pos.numel() != M or r_cos.shape[-1] != 32:
             raise ValueError("rope tables must be [P, 32] and pos must have one entry per row")
+    if pair is None:
+        pair = _GEMM_PAIR_DEFAULT[0]
+    if pair and bn == 256 and max_ctas == 0 and not (a_mn and not b_mn):
+        rc = lib("gemm_tcgen05").nplm_gemm_bf16_pair(
+            ptr(a), ptr(b), ptr(out), ptr(aux), c_int(M), c_int(N), c_int(K), c_int(lda), c_int(ldb),
+            c_int(ldc), c_int(ldr), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi), c_int(splits),
+            c_int(int(direct_epilogue)), ptr(r_pos), ptr(r_cos), ptr(r_sin),
+            c_int(int(r_cols)), ptr(status_word(a.device)), stream_ptr())
+        check_rc(rc, "gemm_bf16_pair")
+        count_launch()
+        return out
     rc = lib("gemm_tcgen05").nplm_gemm_bf16(
         ptr(a), ptr(b), ptr(out), ptr(aux), c_int(M), c_int(N), c_int(K), c_int(lda), c_int(ldb),
         c_int(ldc), c_int(ldr), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi), c_int(splits),

@@ -396,3 +396,73 @@ def test_linear_relu_epilogue(cuda_status):
     torch.relu(x32 @ w32.t()).backward(gy.float())
     assert (xg.grad.float() - x32.grad).abs().max().item() < 0.05 * x32.grad.abs().max().item()
     assert (wg.grad.float() - w32.grad).abs().max().item() < 0.05 * w32.grad.abs().max().item()
+
+
+@pytest.mark.parametrize("form", ["store", "add", "swiglu", "rope", "dgrad", "wgrad"])
+def test_gemm_cta_pair_matches_fp32(form, cuda_status):
+    """The cta_group::2 GEMM (two SMs per 256 x 256 tile) against fp32 matmul, in every form the
+    training step uses; shapes with partial tiles in M and N."""
+    from nanoplm_b200.ops import kernels as K
+    torch.manual_seed(0)
+    dev = "cuda"
+    M, N, Kd = 1000, 768, 320
+    x = torch.randn(M, Kd, device=dev).to(BF)
+    w = (torch.randn(N, Kd, device=dev) * 0.1).to(BF)
+    ref = x.float() @ w.float().t()
+    tol = lambda r: 0.02 * r.abs().max().item() + 0.02
+    if form == "store":
+        y = K.gemm(x, w, bn=256, pair=True)
+        assert (y.float() - ref).abs().max().item() < tol(ref)
+    elif form == "add":
+        res = torch.randn(M, N, device=dev).to(BF)
+        y = K.gemm(x, w, epi=K.EPI_ADD, aux=res, bn=256, pair=True)
+        assert (y.float() - (ref + res.float())).abs().max().item() < tol(ref)
+    elif form == "swiglu":
+        pre = torch.empty(M, N, dtype=BF, device=dev)
+        y = K.gemm(x, w, epi=K.EPI_SWIGLU, aux=pre, bn=256, pair=True)
+        z = ref.to(BF).float()
+        want = torch.nn.functional.silu(z[:, N // 2:]) * z[:, :N // 2]
+        assert (pre.float() - z).abs().max().item() < tol(z)
+        assert (y.float() - want).abs().max().item() < tol(want)
+    elif form == "rope":
+        H, D = N // 64 // 3, 64                      # q and k parts rotated, v untouched
+        pos = torch.randint(0, 100, (M,), device=dev, dtype=torch.int32)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, 32, device=dev).float() / 32))
+        ang = torch.arange(128, device=dev).float()[:, None] * inv[None, :]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        y = K.gemm(x, w, epi=K.EPI_ROPE, rope=(pos, cos, sin, 2 * H * D), bn=256, pair=True).float()
+        want = ref.clone().view(M, N // 64, 64)
+        c, s_ = cos[pos.long()][:, None, :], sin[pos.long()][:, None, :]
+        a, b = want[:, :2 * H, :32].clone(), want[:, :2 * H, 32:].clone()
+        want[:, :2 * H, :32] = a * c - b * s_
+        want[:, :2 * H, 32:] = b * c + a * s_
+        assert (y - want.view(M, N)).abs().max().item() < tol(ref)
+    elif form == "dgrad":
+        dy = torch.randn(M, N, device=dev).to(BF)
+        dx = K.gemm(dy, w[:, :256].contiguous(), b_mn=True, bn=256, pair=True)      # [M, 256]
+        want = dy.float() @ w[:, :256].float()
+        assert (dx.float() - want).abs().max().item() < tol(want)
+    else:
+        T = 4096 + 64
+        dy = torch.randn(T, 512, device=dev).to(BF)
+        xx = torch.randn(T, 256, device=dev).to(BF)
+        acc = torch.ones(512, 256, dtype=torch.float32, device=dev)
+        K.gemm(dy, xx, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=acc, splits=3, bn=256, pair=True)
+        want = 1.0 + dy.float().t() @ xx.float()
+        assert (acc - want).abs().max().item() < 0.01 * want.abs().max().item() + 0.05
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("shape", [(512, 256, 4096 + 64), (960, 768, 20000), (3072, 1024, 8192)])
+def test_gemm_stream_k_wgrad_matches_fp32(shape, pair, cuda_status):
+    """splits=0 cuts tiles x k-blocks into one contiguous range per CTA (or CTA pair): every piece
+    is added atomically, so the sum equals the plain product whatever the cut points are."""
+    from nanoplm_b200.ops import kernels as K
+    torch.manual_seed(1)
+    n_out, k_in, T = shape
+    dy = torch.randn(T, n_out, device="cuda").to(BF)
+    xx = torch.randn(T, k_in, device="cuda").to(BF)
+    acc = torch.ones(n_out, k_in, dtype=torch.float32, device="cuda")
+    K.gemm(dy, xx, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=acc, splits=0, bn=256, pair=pair)
+    want = 1.0 + dy.float().t() @ xx.float()
+    assert (acc - want).abs().max().item() < 0.01 * want.abs().max().item() + 0.05
