@@ -6,10 +6,19 @@ hidden matrix by Muon (momentum, optional Nesterov, orthogonalisation of the upd
 Newton-Schulz iteration or the Polar-Express coefficient schedule, decoupled and optionally
 "cautious" weight decay); NorMuon additionally normalises each output row of the orthogonalised
 update by a running second moment (beta2 0.95) and rescales so the update has unit RMS times a
-shape factor. The reference delegates this to the external `dion` package (Triton Newton-Schulz,
-sharded all-to-all); here the iterations are plain matrix products on this package's GEMM kernel,
-gradients are all-reduced and every rank applies the same (replicated) update: at 169 M parameters
-the full orthogonalisation costs a few milliseconds per optimizer step.
+shape factor.
+
+The reference delegates this to the external `dion` package: Triton Newton-Schulz kernels and, on
+several ranks, an all-to-all that hands one whole matrix of every batch of `world` same-shape
+matrices to each rank. Here:
+* matrices of one shape (one per layer: all QKV projections, all MLP up-projections, ...) are
+  stacked and orthogonalised together; every one of the three products of an iteration is ONE
+  launch of this package's row-grouped tcgen05 GEMM over the whole stack, so a stack of 16 matrices
+  of 1024 x 1024 fills the GPU where a single one would occupy 32 of 148 SMs;
+* on several ranks every stack is cut into `world` contiguous runs of matrices: a rank keeps the
+  momentum of its run, orthogonalises only that run and the orthogonal factors (bf16) are
+  all-gathered; gradients are all-reduced and parameters stay replicated, so what follows the
+  gather is elementwise and identical on every rank.
 
 The engine shares storage layout, checkpoint format and API with `ShardedEngine`.
 """
@@ -41,45 +50,92 @@ def is_embedding_or_unembedding(name: str) -> bool:
     return any(k in n for k in ("tok_embeddings", "embed_tokens", "word_embeddings", "decoder", "lm_head", "shared"))
 
 
-def _mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """a @ b^T for bf16 2-D operands: tcgen05 GEMM on CUDA (both K-major), torch elsewhere."""
-    if a.is_cuda and a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] % 8 == 0 and b.shape[0] % 8 == 0:
-        from nanoplm_b200.ops import kernels as K
-        return K.gemm(a.contiguous(), b.contiguous())
-    return a @ b.t()
+_TILE_GROUPS: dict = {}
 
 
-def _mm_nn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """a @ b for bf16 2-D operands; on CUDA b is consumed as an MN-major operand, no transpose."""
-    if (a.is_cuda and a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] % 8 == 0
-            and b.shape[1] % 64 == 0 and b.is_contiguous()):
-        from nanoplm_b200.ops import kernels as K
-        return K.gemm(a.contiguous(), b, b_mn=True)
-    return a @ b
+def _tile_groups(batch: int, rows: int, device) -> torch.Tensor:
+    """int32 [batch * rows / 128]: which matrix of the stack every 128-row tile belongs to."""
+    key = (batch, rows, str(device))
+    t = _TILE_GROUPS.get(key)
+    if t is None:
+        t = torch.arange(batch, dtype=torch.int32, device=device).repeat_interleave(rows // 128).contiguous()
+        _TILE_GROUPS[key] = t
+    return t
+
+
+def _grouped_ok(X: torch.Tensor) -> bool:
+    """Stack [B, m, n] whose three Newton-Schulz products fit the row-grouped GEMM kernel."""
+    return X.is_cuda and X.dtype == torch.bfloat16 and X.shape[1] % 128 == 0 and X.shape[2] % 64 == 0
+
+
+def _bmm_nt(a: torch.Tensor, b: torch.Tensor, grouped: bool) -> torch.Tensor:
+    """a[i] @ b[i]^T for stacks a [B, m, k], b [B, n, k]."""
+    if grouped:
+        from nanoplm_b200.ops.moe import gemm_grouped
+        B, m, k = a.shape
+        return gemm_grouped(a.reshape(B * m, k), b, _tile_groups(B, m, a.device)).view(B, m, b.shape[1])
+    return torch.bmm(a, b.transpose(1, 2))
+
+
+def _bmm_nn(a: torch.Tensor, b: torch.Tensor, grouped: bool) -> torch.Tensor:
+    """a[i] @ b[i] for stacks a [B, m, k], b [B, k, n]; b is read as an MN-major operand."""
+    if grouped:
+        from nanoplm_b200.ops.moe import gemm_grouped
+        B, m, k = a.shape
+        return gemm_grouped(a.reshape(B * m, k), b, _tile_groups(B, m, a.device), b_mn=True).view(B, m, b.shape[2])
+    return torch.bmm(a, b)
+
+
+def orthogonalize_batched(G: torch.Tensor, coeffs=NS_QUINTIC, eps: float = 1e-7) -> torch.Tensor:
+    """Approximate polar factor of every matrix of the stack G [B, r, c] by quintic iterations
+    X <- aX + (bA + cA^2)X, A = X X^T (bf16 on CUDA, fp32 elsewhere)."""
+    dt = torch.bfloat16 if G.is_cuda else torch.float32
+    X = G.to(dt)
+    transposed = X.shape[1] > X.shape[2]
+    if transposed:
+        X = X.transpose(1, 2).contiguous()
+    nrm = X.float().flatten(1).norm(dim=1)
+    X = (X / (nrm * 1.01 + eps).to(dt)[:, None, None]).contiguous()
+    grouped = _grouped_ok(X)
+    for a, b, c in coeffs:
+        A = _bmm_nt(X, X, grouped)                              # X X^T, symmetric [B, m, m]
+        Bm = torch.add(A * b, _bmm_nt(A, A, grouped), alpha=c)  # A A^T = A^2
+        X = torch.add(_bmm_nn(Bm, X, grouped), X, alpha=a)      # B X
+    if transposed:
+        X = X.transpose(1, 2).contiguous()
+    return X
 
 
 def orthogonalize(G: torch.Tensor, coeffs=NS_QUINTIC, eps: float = 1e-7) -> torch.Tensor:
-    """Approximate polar factor of G by quintic iterations X <- aX + (bA + cA^2)X, A = X X^T."""
-    dt = torch.bfloat16 if G.is_cuda else torch.float32
-    X = G.to(dt)
-    transposed = X.shape[0] > X.shape[1]
-    if transposed:
-        X = X.t().contiguous()
-    X = X / (X.float().norm() * 1.01 + eps).to(dt)
-    for a, b, c in coeffs:
-        A = _mm(X, X)                                   # X X^T          [m, m], symmetric
-        B = b * A + c * _mm(A, A)                       # A A^T = A^2
-        X = a * X + _mm_nn(B, X)                        # B X
-    if transposed:
-        X = X.t().contiguous()
-    return X
+    """Approximate polar factor of one matrix (see `orthogonalize_batched`)."""
+    return orthogonalize_batched(G[None], coeffs, eps)[0]
+
+
+class _Stack:
+    """Muon matrices of one shape; `lo:hi` is the run this rank orthogonalises."""
+
+    def __init__(self, slots, rank: int, world: int):
+        self.slots = slots
+        self.shape = tuple(slots[0].shape)
+        n = len(slots)
+        self.even = world > 1 and n % world == 0
+        if world == 1:
+            self.lo, self.hi = 0, n
+        elif self.even:
+            self.lo, self.hi = rank * (n // world), (rank + 1) * (n // world)
+        else:                                   # uneven: near-equal contiguous runs, exchanged by all-reduce
+            self.lo, self.hi = rank * n // world, (rank + 1) * n // world
+
+    def views(self, flat: torch.Tensor, lo: int = 0, hi: int | None = None):
+        return [flat[s.offset:s.offset + s.numel].view(s.shape) for s in self.slots[lo:hi]]
 
 
 class MuonEngine(ShardedEngine):
     def __init__(self, model, hyper: AdamWHyper, cfg, device, process_group=None):
         compute = torch.bfloat16 if (getattr(cfg, "bf16", True) and torch.device(device).type == "cuda") else torch.float32
         super().__init__(model, hyper, device, process_group, compute_dtype=compute, fused_comm=False)
-        # replicated optimizer state: full-size buffers on every rank
+        # replicated parameters and AdamW state: full-size buffers on every rank; the Muon momentum
+        # lives in the same flat buffer but only the entries of matrices this rank owns are used
         dev = self.device
         self.master = self._gather_full(self.master).clone()
         self.exp_avg = torch.zeros(self.total, dtype=torch.float32, device=dev)
@@ -96,15 +152,113 @@ class MuonEngine(ShardedEngine):
         self.muon_slots = [s for s in self.slots if len(s.shape) == 2 and not is_embedding_or_unembedding(s.name)]
         if not self.muon_slots:
             raise ValueError("No eligible matrix parameters found for Muon (expected 2D hidden-layer weights).")
-        self._muon_ids = {id(s) for s in self.slots if s in self.muon_slots}
+        muon_ids = {id(s) for s in self.muon_slots}
+        self.adam_slots = [s for s in self.slots if id(s) not in muon_ids]
+        by_shape: dict = {}
+        for s in self.muon_slots:
+            by_shape.setdefault(tuple(s.shape), []).append(s)
+        self.stacks = [_Stack(v, self.rank, self.world) for v in by_shape.values()]
         self.row_second_moment = {s.name: torch.zeros(s.shape[0], dtype=torch.float32, device=dev)
                                   for s in self.muon_slots} if self.normuon else {}
         self.muon_lr = self.muon_lr0
 
-    def _gather_full(self, t):                       # state is already complete on every rank
-        if t.numel() == self.total:
-            return t
-        return super()._gather_full(t)
+    # ---- checkpoint helpers ------------------------------------------------------------------
+    def _owned(self):
+        return [s for st in self.stacks for s in st.slots[st.lo:st.hi]]
+
+    def _gather_full(self, t):
+        if t.numel() != self.total:
+            return super()._gather_full(t)
+        if t is not getattr(self, "exp_avg", None) or not self.distributed:
+            return t                                  # replicated: already complete on every rank
+        # Muon momentum: every matrix from the rank that owns it, AdamW entries from this rank
+        full = torch.zeros_like(t)
+        for s in self._owned():
+            full[s.offset:s.offset + s.numel] = t[s.offset:s.offset + s.numel]
+        dist.all_reduce(full, group=self.pg)
+        for s in self.adam_slots:
+            full[s.offset:s.offset + s.numel] = t[s.offset:s.offset + s.numel]
+        return full
+
+    def _drop_unowned_momentum(self) -> None:
+        owned = {id(s) for s in self._owned()}
+        for s in self.muon_slots:
+            if id(s) not in owned:
+                self.exp_avg[s.offset:s.offset + s.numel].zero_()
+
+    def optimizer_state_dict(self) -> dict:
+        sd = super().optimizer_state_dict()
+        if self.normuon:
+            rows = {}
+            owned = {id(s) for s in self._owned()}
+            for s in self.muon_slots:
+                v = self.row_second_moment[s.name]
+                v = v.clone() if id(s) in owned else torch.zeros_like(v)
+                if self.distributed:
+                    dist.all_reduce(v, group=self.pg)
+                rows[s.name] = v.cpu()
+            sd["normuon_row_second_moment"] = rows
+        return sd
+
+    def load_optimizer_state_dict(self, sd: dict) -> None:
+        super().load_optimizer_state_dict(sd)
+        self._drop_unowned_momentum()
+        for name, v in (sd.get("normuon_row_second_moment") or {}).items():
+            if name in self.row_second_moment:
+                self.row_second_moment[name].copy_(v)
+
+    # ---- the step ----------------------------------------------------------------------------
+    def _adamw_group(self, slots, g_all, lr: float, wd: float, bc1: float, bc2: float) -> None:
+        if not slots:
+            return
+        h = self.hyper
+        view = lambda flat: [flat[s.offset:s.offset + s.numel] for s in slots]
+        p, m, v, g = view(self.master), view(self.exp_avg), view(self.exp_avg_sq), view(g_all)
+        if wd:
+            torch._foreach_mul_(p, 1 - lr * wd)
+        torch._foreach_mul_(m, h.beta1)
+        torch._foreach_add_(m, g, alpha=1 - h.beta1)
+        torch._foreach_mul_(v, h.beta2)
+        torch._foreach_addcmul_(v, g, g, value=1 - h.beta2)
+        den = torch._foreach_sqrt(v)
+        torch._foreach_div_(den, math.sqrt(bc2))
+        torch._foreach_add_(den, h.eps)
+        torch._foreach_addcdiv_(p, m, den, value=-lr / bc1)
+
+    def _orthogonal_updates(self, st: _Stack, g_all: torch.Tensor) -> torch.Tensor:
+        """Orthogonalised (and, for NorMuon, row-normalised) updates of the whole stack
+        [n, r, c]; this rank computes its run, the others arrive by all-gather."""
+        n = len(st.slots)
+        dt = torch.bfloat16 if self.on_cuda else torch.float32
+        O = torch.zeros((n,) + st.shape, dtype=dt, device=self.device) if not st.even and self.distributed \
+            else torch.empty((n,) + st.shape, dtype=dt, device=self.device)
+        if st.hi > st.lo:
+            g = st.views(g_all, st.lo, st.hi)
+            m = st.views(self.exp_avg, st.lo, st.hi)
+            torch._foreach_mul_(m, self.mu)
+            torch._foreach_add_(m, g)
+            upd = torch.stack(torch._foreach_add(g, m, alpha=self.mu) if self.nesterov else m)
+            mine = orthogonalize_batched(upd, self.coeffs, self.muon_eps)
+            if self.normuon:
+                mine = mine.float()
+                v = torch.stack([self.row_second_moment[s.name] for s in st.slots[st.lo:st.hi]])
+                v.mul_(0.95).add_(mine.pow(2).mean(dim=2), alpha=0.05)
+                for s, row in zip(st.slots[st.lo:st.hi], v):
+                    self.row_second_moment[s.name].copy_(row)
+                mine = mine / (v.sqrt()[:, :, None] + self.muon_eps)
+                scale = 0.2 * math.sqrt(mine[0].numel()) / (mine.flatten(1).norm(dim=1) + self.muon_eps)
+                mine = mine * scale[:, None, None]                                        # rms_norm scaling
+            O[st.lo:st.hi] = mine.to(dt)
+        if self.distributed:
+            if st.even and self.on_cuda:
+                dist.all_gather_into_tensor(O, O[st.lo:st.hi].clone(), group=self.pg)
+            elif st.even:
+                parts = [torch.empty_like(O[st.lo:st.hi]) for _ in range(self.world)]
+                dist.all_gather(parts, O[st.lo:st.hi].contiguous(), group=self.pg)
+                O = torch.cat(parts)
+            else:
+                dist.all_reduce(O, group=self.pg)
+        return O
 
     @torch.no_grad()
     def step(self, lr: float, grad_accum: int = 1) -> torch.Tensor:
@@ -122,34 +276,20 @@ class MuonEngine(ShardedEngine):
         h, t = self.hyper, self.step_count
         self.muon_lr = self.muon_lr0 * (lr / self.adam_lr0 if self.adam_lr0 > 0 else 1.0)   # same schedule shape
         bc1, bc2 = 1 - h.beta1 ** t, 1 - h.beta2 ** t
-        for s in self.slots:
-            sl = slice(s.offset, s.offset + s.numel)
-            g, p = g_all[sl], self.master[sl]
-            if id(s) in self._muon_ids:
-                m = self.exp_avg[sl]
-                m.mul_(self.mu).add_(g)
-                upd = (g + self.mu * m) if self.nesterov else m
-                O = orthogonalize(upd.view(s.shape), self.coeffs, self.muon_eps).float()
-                if self.normuon:
-                    v = self.row_second_moment[s.name]
-                    v.mul_(0.95).add_(O.pow(2).mean(dim=1), alpha=0.05)
-                    O = O / (v.sqrt()[:, None] + self.muon_eps)
-                    O = O * (0.2 * math.sqrt(O.numel()) / (O.norm() + self.muon_eps))      # rms_norm scaling
-                O = O.reshape(-1)
-                if self.muon_wd > 0:
-                    if self.cautious:
-                        p.sub_(self.muon_lr * self.muon_wd * p * ((O * p) > 0))
-                    else:
-                        p.mul_(1 - self.muon_lr * self.muon_wd)
-                p.sub_(self.muon_lr * O)
-            else:
-                m, v = self.exp_avg[sl], self.exp_avg_sq[sl]
-                wd = h.weight_decay if s.decay else 0.0
-                p.mul_(1 - lr * wd)
-                m.mul_(h.beta1).add_(g, alpha=1 - h.beta1)
-                v.mul_(h.beta2).addcmul_(g, g, value=1 - h.beta2)
-                p.addcdiv_(m, (v.sqrt() / math.sqrt(bc2)).add_(h.eps), value=-lr / bc1)
-            self.flat_params[sl] = p.to(self.flat_params.dtype)
+        for st in self.stacks:
+            O = self._orthogonal_updates(st, g_all).float()
+            p_views = st.views(self.master)
+            p = torch.stack(p_views)
+            if self.muon_wd > 0:
+                if self.cautious:
+                    p.sub_(self.muon_lr * self.muon_wd * p * ((O * p) > 0))
+                else:
+                    p.mul_(1 - self.muon_lr * self.muon_wd)
+            p.sub_(self.muon_lr * O)
+            torch._foreach_copy_(p_views, list(p.unbind(0)))
+        self._adamw_group([s for s in self.adam_slots if s.decay], g_all, lr, h.weight_decay, bc1, bc2)
+        self._adamw_group([s for s in self.adam_slots if not s.decay], g_all, lr, 0.0, bc1, bc2)
+        self.flat_params.copy_(self.master)
         self.main_grad.zero_()
         return norm
 

@@ -206,3 +206,60 @@ def test_expert_parallel_training_matches_replicated_experts(tmp_path):
         assert sd1[k].shape == sd2[k].shape, k            # gathered experts have the full first axis
         assert torch.allclose(sd1[k], sd2[k], atol=5e-5), k
     assert extra is not None and all(v.shape[0] == 4 for v in extra["exp_avg"].values())
+
+
+def _train_muon(rank, world, port, tmp, optimizer):
+    from nanoplm_b200.config.schema import PretrainingConfig
+    from nanoplm_b200.parallel.engine import AdamWHyper
+    from nanoplm_b200.parallel.muon import MuonEngine
+    from nanoplm_b200.runtime.pretrain import TrainStep
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    if world > 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    model = _make_model()
+    cfg = PretrainingConfig(dataset_dir="x", optimizer=optimizer, bf16=False)
+    eng = MuonEngine(model, AdamWHyper(lr=1e-3, weight_decay=0.01), cfg, torch.device("cpu"))
+    sch = WarmupLinearSchedule(1e-3, 2, 100)
+    st = TrainStep(model, eng, sch, "cpu")
+    batches = _batches(8)
+    for step in range(3):
+        st.step_from_host(batches[2 * step:2 * step + 2][rank::world])
+    opt_sd = eng.optimizer_state_dict()          # collective: momentum comes from the owning rank
+    sd = eng.full_state_dict_model()
+    # a 2-layer model has 2 matrices per shape: with 2 ranks every rank owns one of each
+    owned = sum(st_.hi - st_.lo for st_ in eng.stacks)
+    if rank == 0:
+        torch.save((sd, opt_sd, owned, len(eng.muon_slots)), os.path.join(tmp, "muon.pt"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("optimizer", ["muon", "normuon"])
+def test_matrix_parallel_muon_matches_single_rank(tmp_path, optimizer):
+    """Two ranks each orthogonalise half of every stack of same-shape matrices and exchange the
+    orthogonal factors; parameters, momentum and NorMuon row moments must equal the 1-rank run."""
+    out = []
+    for world in (1, 2):
+        d = str(tmp_path / f"w{world}")
+        os.makedirs(d)
+        ctx = mp.get_context("spawn")
+        port = _free_port()
+        procs = [ctx.Process(target=_train_muon, args=(r, world, port, d, optimizer)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(180)
+            assert p.exitcode == 0
+        out.append(torch.load(os.path.join(d, "muon.pt")))
+    (sd1, opt1, owned1, n1), (sd2, opt2, owned2, n2) = out
+    assert owned1 == n1 and owned2 < n2
+    for k in sd1:
+        assert torch.allclose(sd1[k], sd2[k], atol=3e-5), k
+    for i in opt1["state"]:
+        assert torch.allclose(opt1["state"][i]["exp_avg"], opt2["state"][i]["exp_avg"], atol=3e-5), i
+    if optimizer == "normuon":
+        for k, v in opt1["normuon_row_second_moment"].items():
+            assert torch.allclose(v, opt2["normuon_row_second_moment"][k], atol=1e-5), k

@@ -157,3 +157,54 @@ def test_padding_tail_trim_leaves_loss_and_grads_unchanged(cuda_status):
     scale = grads[0].abs().max().item()
     # weight gradients are fp32 atomic sums, so only the summation order may differ
     assert (grads[0] - grads[1]).abs().max().item() < 2e-3 * scale
+
+
+@pytest.mark.parametrize("shape", [(4, 256, 512), (3, 512, 256), (2, 1024, 1024)])
+def test_newton_schulz_on_grouped_gemm_matches_fp32(shape, cuda_status):
+    """All matrices of a stack are orthogonalised by three row-grouped tcgen05 GEMM launches per
+    iteration; the fp32 restatement runs the same iterations with torch.bmm on the CPU."""
+    from nanoplm_b200.parallel import muon
+    torch.manual_seed(3)
+    G = torch.randn(*shape) * torch.tensor([0.1, 1.0, 7.0, 30.0])[:shape[0], None, None]   # norms differ
+    ref = muon.orthogonalize_batched(G, muon.POLAR_EXPRESS)
+    X = G.cuda().to(torch.bfloat16)
+    assert muon._grouped_ok(X if shape[1] <= shape[2] else X.transpose(1, 2).contiguous())
+    from nanoplm_b200.ops import _lib
+    n0 = _lib.launches()
+    out = muon.orthogonalize_batched(G.cuda(), muon.POLAR_EXPRESS).float().cpu()
+    assert _lib.launches() - n0 == 3 * len(muon.POLAR_EXPRESS)
+    assert out.shape == ref.shape
+    for o, r in zip(out, ref):
+        assert (o - r).norm().item() < 0.06 * r.norm().item(), ((o - r).norm().item(), r.norm().item())
+        sv = torch.linalg.svdvals(o)
+        assert 0.9 < sv.min().item() and sv.max().item() < 1.1
+
+
+@pytest.mark.parametrize("optimizer", ["muon", "normuon"])
+def test_muon_engine_trains_on_gpu_like_cpu(optimizer, cuda_status):
+    from nanoplm_b200.config.schema import ModelConfig, PretrainingConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.parallel.engine import AdamWHyper
+    from nanoplm_b200.parallel.muon import MuonEngine
+    from nanoplm_b200.runtime.pretrain import TrainStep
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+
+    torch.manual_seed(0)
+    tok = ProtTokenizer()
+    cfg = ModelConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      max_position_embeddings=256)
+    base = ProtEncoderMLM(cfg, tok)
+    losses = {}
+    for dev in ("cpu", "cuda:0"):
+        m = copy.deepcopy(base)
+        pc = PretrainingConfig(dataset_dir="x", optimizer=optimizer, bf16=dev != "cpu", muon_learning_rate=5e-3)
+        eng = MuonEngine(m, AdamWHyper(lr=1e-3), pc, torch.device(dev))
+        m.train()
+        st = TrainStep(m, eng, WarmupLinearSchedule(1e-3, 2, 1000), torch.device(dev))
+        batches = [_batch(tok, seed=s) for s in range(3)]
+        losses[dev] = [st.step_from_host([batches[i % 3]]) for i in range(10)]
+    c, g = losses["cpu"], losses["cuda:0"]
+    assert g[-1] < g[0] - 0.1, g
+    for a, b in zip(c, g):
+        assert abs(a - b) < 0.12, (c, g)
