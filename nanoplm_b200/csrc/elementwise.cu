@@ -700,6 +700,117 @@ adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v
   }
 }
 
+// ---- Muon (matrices of one shape, addressed through a table of flat offsets) -----------------
+// gradient scale shared by the optimizer kernels: grad_scale and clip_grad_norm_ by the global norm
+__device__ __forceinline__ float clip_scale(const float* sumsq, float gs, float max_norm) {
+  if (sumsq == nullptr || max_norm <= 0.f) return gs;
+  return gs * fminf(1.f, max_norm / (sqrtf(*sumsq) * gs + 1e-6f));
+}
+
+// Momentum of matrix blockIdx.y (numel elements at flat offset off[y]) and the bf16 update that
+// enters the Newton-Schulz iterations:  m <- mu m + g,  u = nesterov ? g + mu m : m,
+// upd[y] = bf16(u),  usq[y] += sum of the rounded u^2 (its Frobenius norm normalises the iteration).
+__global__ void __launch_bounds__(256)
+muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ m,
+                     const long long* __restrict__ off, long long numel,
+                     __nv_bfloat16* __restrict__ upd, float* __restrict__ usq,
+                     const float* __restrict__ sumsq, float gs, float max_norm, float mu, int nesterov) {
+  const float scale = clip_scale(sumsq, gs, max_norm);
+  const long long base = off[blockIdx.y];
+  const float4* g4 = reinterpret_cast<const float4*>(g + base);
+  float4* m4 = reinterpret_cast<float4*>(m + base);
+  uint2* u4 = reinterpret_cast<uint2*>(upd + static_cast<long long>(blockIdx.y) * numel);
+  float acc = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < (numel >> 2);
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 gv = g4[i];
+    float4 mv = m4[i];
+    gv.x *= scale; gv.y *= scale; gv.z *= scale; gv.w *= scale;
+    mv.x = mu * mv.x + gv.x; mv.y = mu * mv.y + gv.y; mv.z = mu * mv.z + gv.z; mv.w = mu * mv.w + gv.w;
+    m4[i] = mv;
+    float4 u = mv;
+    if (nesterov) { u.x = gv.x + mu * mv.x; u.y = gv.y + mu * mv.y; u.z = gv.z + mu * mv.z; u.w = gv.w + mu * mv.w; }
+    uint2 pk;
+    pk.x = pack_bf16x2(u.x, u.y);
+    pk.y = pack_bf16x2(u.z, u.w);
+    u4[i] = pk;
+    const float2 a = unpack_bf16x2(pk.x), b = unpack_bf16x2(pk.y);
+    acc += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+  }
+  acc = warp_sum(acc);
+  __shared__ float ws[8];
+  if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += ws[i];
+    atomicAdd(&usq[blockIdx.y], t);
+  }
+}
+
+// Applies the orthogonalised update O[y] (bf16) to matrix y: decoupled weight decay (cautious:
+// only where the update and the weight agree in sign), p <- p - lr O, and the bf16 compute copy.
+__global__ void __launch_bounds__(256)
+muon_apply_kernel(float* __restrict__ p, __nv_bfloat16* __restrict__ p16,
+                  const long long* __restrict__ off, long long numel,
+                  const __nv_bfloat16* __restrict__ O, float lr, float wd, int cautious) {
+  const long long base = off[blockIdx.y];
+  float4* p4 = reinterpret_cast<float4*>(p + base);
+  uint2* q4 = p16 ? reinterpret_cast<uint2*>(p16 + base) : nullptr;
+  const uint2* o4 = reinterpret_cast<const uint2*>(O + static_cast<long long>(blockIdx.y) * numel);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < (numel >> 2);
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 pv = p4[i];
+    const uint2 ov = o4[i];
+    const float2 oa = unpack_bf16x2(ov.x), ob = unpack_bf16x2(ov.y);
+    const float o[4] = {oa.x, oa.y, ob.x, ob.y};
+    float* pe = reinterpret_cast<float*>(&pv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float x = pe[e];
+      if (wd > 0.f) {
+        if (cautious) x -= (o[e] * x > 0.f) ? lr * wd * x : 0.f;
+        else x *= (1.f - lr * wd);
+      }
+      pe[e] = x - lr * o[e];
+    }
+    p4[i] = pv;
+    if (q4) {
+      uint2 pk;
+      pk.x = pack_bf16x2(pv.x, pv.y);
+      pk.y = pack_bf16x2(pv.z, pv.w);
+      q4[i] = pk;
+    }
+  }
+}
+
+// AdamW over a table of parameter tensors of one flat buffer (tensor y: numel[y] elements at
+// offset off[y], weight decay only where decay[y] != 0); same update as adamw_kernel.
+__global__ void __launch_bounds__(256)
+adamw_slots_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                   const float* __restrict__ g, __nv_bfloat16* __restrict__ p16,
+                   const long long* __restrict__ off, const long long* __restrict__ numel,
+                   const int* __restrict__ decay, const float* __restrict__ sumsq, float gs, float max_norm,
+                   float lr, float b1, float b2, float eps, float wd, float bc1, float bc2) {
+  const float scale = clip_scale(sumsq, gs, max_norm);
+  const long long base = off[blockIdx.y], n = numel[blockIdx.y];
+  const float decay_mul = decay[blockIdx.y] ? (1.f - lr * wd) : 1.f;
+  const float step_size = lr / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long j = base + i;
+    const float gr = g[j] * scale;
+    float pv = p[j] * decay_mul;
+    const float mv = b1 * m[j] + (1.f - b1) * gr;
+    const float vv = b2 * v[j] + (1.f - b2) * gr * gr;
+    pv -= step_size * mv / (sqrtf(vv) * inv_sqrt_bc2 + eps);
+    p[j] = pv;
+    m[j] = mv;
+    v[j] = vv;
+    if (p16) p16[j] = __float2bfloat16(pv);
+  }
+}
+
 __global__ void __launch_bounds__(256)
 cast_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                         long long n) {
@@ -948,6 +1059,42 @@ extern "C" int nplm_adamw(float* p, float* m, float* v, float* g, void* p_bf16, 
   if (n <= 0) return 0;
   adamw_kernel<<<grid_for(n, 256), 256, 0, st>>>(p, m, v, g, reinterpret_cast<__nv_bfloat16*>(p_bf16),
                                                  hyper, sumsq, n, zero_grad);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_muon_momentum(const float* g, float* m, const long long* off, int n_mat, long long numel,
+                                  void* upd, float* usq, const float* sumsq, float gs, float max_norm,
+                                  float mu, int nesterov, cudaStream_t st) {
+  if (n_mat <= 0 || numel <= 0) return 0;
+  if (numel & 3) return -3;
+  int bx = grid_for(numel / 4, 256);
+  if (bx > 592) bx = 592;
+  muon_momentum_kernel<<<dim3(bx, n_mat), 256, 0, st>>>(g, m, off, numel, reinterpret_cast<__nv_bfloat16*>(upd),
+                                                        usq, sumsq, gs, max_norm, mu, nesterov);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_muon_apply(float* p, void* p16, const long long* off, int n_mat, long long numel,
+                               const void* O, float lr, float wd, int cautious, cudaStream_t st) {
+  if (n_mat <= 0 || numel <= 0) return 0;
+  if (numel & 3) return -3;
+  int bx = grid_for(numel / 4, 256);
+  if (bx > 592) bx = 592;
+  muon_apply_kernel<<<dim3(bx, n_mat), 256, 0, st>>>(p, reinterpret_cast<__nv_bfloat16*>(p16), off, numel,
+                                                     reinterpret_cast<const __nv_bfloat16*>(O), lr, wd, cautious);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_adamw_slots(float* p, float* m, float* v, const float* g, void* p16, const long long* off,
+                                const long long* numel, const int* decay, int n_slots, long long max_numel,
+                                const float* sumsq, float gs, float max_norm, float lr, float b1, float b2,
+                                float eps, float wd, float bc1, float bc2, cudaStream_t st) {
+  if (n_slots <= 0 || max_numel <= 0) return 0;
+  int bx = grid_for(max_numel, 256);
+  if (bx > 64) bx = 64;
+  adamw_slots_kernel<<<dim3(bx, n_slots), 256, 0, st>>>(p, m, v, g, reinterpret_cast<__nv_bfloat16*>(p16), off,
+                                                        numel, decay, sumsq, gs, max_norm, lr, b1, b2, eps, wd,
+                                                        bc1, bc2);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -339,6 +339,41 @@ def adamw_(p, m, v, g, p_bf16, hyper, sumsq, zero_grad=True) -> None:
     count_launch()
 
 
+def muon_momentum_(g, m, offsets, numel: int, upd, usq, sumsq, grad_scale: float, max_norm: float,
+                   mu: float, nesterov: bool) -> None:
+    """Momentum update of the matrices at flat `offsets` (int64, device) of g / m (fp32 flat
+    buffers); writes the bf16 Newton-Schulz input `upd` [n, numel] and adds its squared Frobenius
+    norms to `usq` [n]."""
+    rc = lib("elementwise").nplm_muon_momentum(
+        ptr(g), ptr(m), ptr(offsets), c_int(offsets.numel()), c_longlong(numel), ptr(upd), ptr(usq),
+        ptr(sumsq), c_float(grad_scale), c_float(max_norm), c_float(mu), c_int(int(nesterov)), stream_ptr())
+    check_rc(rc, "muon_momentum")
+    count_launch()
+
+
+def muon_apply_(p, p_bf16, offsets, numel: int, O, lr: float, wd: float, cautious: bool) -> None:
+    """p[offsets[i] : +numel] -= lr * (wd-term + O[i]) for the bf16 stack O [n, numel]; also
+    writes the bf16 copy of the parameters."""
+    rc = lib("elementwise").nplm_muon_apply(
+        ptr(p), ptr(p_bf16), ptr(offsets), c_int(offsets.numel()), c_longlong(numel), ptr(O),
+        c_float(lr), c_float(wd), c_int(int(cautious)), stream_ptr())
+    check_rc(rc, "muon_apply")
+    count_launch()
+
+
+def adamw_slots_(p, m, v, g, p_bf16, offsets, numels, decay, max_numel: int, sumsq, grad_scale: float,
+                 max_norm: float, lr: float, beta1: float, beta2: float, eps: float, wd: float,
+                 bc1: float, bc2: float) -> None:
+    """AdamW on the tensors listed in (offsets, numels, decay) of one flat buffer, one launch."""
+    rc = lib("elementwise").nplm_adamw_slots(
+        ptr(p), ptr(m), ptr(v), ptr(g), ptr(p_bf16), ptr(offsets), ptr(numels), ptr(decay),
+        c_int(offsets.numel()), c_longlong(max_numel), ptr(sumsq), c_float(grad_scale), c_float(max_norm),
+        c_float(lr), c_float(beta1), c_float(beta2), c_float(eps), c_float(wd), c_float(bc1), c_float(bc2),
+        stream_ptr())
+    check_rc(rc, "adamw_slots")
+    count_launch()
+
+
 def cast_f32_bf16_(src: torch.Tensor, dst: torch.Tensor) -> None:
     rc = lib("elementwise").nplm_cast_f32_bf16(ptr(src), ptr(dst), c_longlong(src.numel()),
                                                stream_ptr())

@@ -86,21 +86,38 @@ def _bmm_nn(a: torch.Tensor, b: torch.Tensor, grouped: bool) -> torch.Tensor:
     return torch.bmm(a, b)
 
 
-def orthogonalize_batched(G: torch.Tensor, coeffs=NS_QUINTIC, eps: float = 1e-7) -> torch.Tensor:
+def orthogonalize_batched(G: torch.Tensor, coeffs=NS_QUINTIC, eps: float = 1e-7,
+                          sumsq: torch.Tensor | None = None) -> torch.Tensor:
     """Approximate polar factor of every matrix of the stack G [B, r, c] by quintic iterations
-    X <- aX + (bA + cA^2)X, A = X X^T (bf16 on CUDA, fp32 elsewhere)."""
+    X <- aX + (bA + cA^2)X, A = X X^T (bf16 on CUDA, fp32 elsewhere). `sumsq` [B]: squared
+    Frobenius norms of the matrices when the caller already has them.
+
+    On the grouped-GEMM path the polynomial is applied through the products only:
+    bA + cA^2 = (cA + bI) A and aX + BX = (B + aI) X, so an iteration is three GEMM launches plus
+    three small operations on the [B, m, m] Gram stack and never touches X elementwise."""
     dt = torch.bfloat16 if G.is_cuda else torch.float32
     X = G.to(dt)
     transposed = X.shape[1] > X.shape[2]
     if transposed:
         X = X.transpose(1, 2).contiguous()
-    nrm = X.float().flatten(1).norm(dim=1)
-    X = (X / (nrm * 1.01 + eps).to(dt)[:, None, None]).contiguous()
+    nrm = X.float().flatten(1).norm(dim=1) if sumsq is None else sumsq.float().sqrt()
+    inv = (1.0 / (nrm * 1.01 + eps)).to(dt)[:, None, None]
     grouped = _grouped_ok(X)
-    for a, b, c in coeffs:
-        A = _bmm_nt(X, X, grouped)                              # X X^T, symmetric [B, m, m]
-        Bm = torch.add(A * b, _bmm_nt(A, A, grouped), alpha=c)  # A A^T = A^2
-        X = torch.add(_bmm_nn(Bm, X, grouped), X, alpha=a)      # B X
+    if grouped:
+        X = X.mul_(inv) if (X.data_ptr() != G.data_ptr() or sumsq is not None) else X * inv
+        for a, b, c in coeffs:
+            A = _bmm_nt(X, X, grouped)                          # X X^T, symmetric [B, m, m]
+            Ac = A * c
+            Ac.diagonal(dim1=1, dim2=2).add_(b)                 # cA + bI
+            Bm = _bmm_nt(Ac, A, grouped)                        # (cA + bI) A^T = bA + cA^2
+            Bm.diagonal(dim1=1, dim2=2).add_(a)                 # + aI
+            X = _bmm_nn(Bm, X, grouped)                         # aX + (bA + cA^2) X
+    else:
+        X = X * inv
+        for a, b, c in coeffs:
+            A = _bmm_nt(X, X, grouped)
+            Bm = torch.add(A * b, _bmm_nt(A, A, grouped), alpha=c)
+            X = torch.add(_bmm_nn(Bm, X, grouped), X, alpha=a)
     if transposed:
         X = X.transpose(1, 2).contiguous()
     return X
@@ -125,6 +142,16 @@ class _Stack:
             self.lo, self.hi = rank * (n // world), (rank + 1) * (n // world)
         else:                                   # uneven: near-equal contiguous runs, exchanged by all-reduce
             self.lo, self.hi = rank * n // world, (rank + 1) * n // world
+
+    def offsets(self, device, own: bool) -> torch.Tensor:
+        """int64 flat offsets of this rank's run (own) or of all matrices of the stack."""
+        key = "_off_own" if own else "_off_all"
+        t = getattr(self, key, None)
+        if t is None:
+            sl = self.slots[self.lo:self.hi] if own else self.slots
+            t = torch.tensor([s.offset for s in sl], dtype=torch.int64, device=device)
+            setattr(self, key, t)
+        return t
 
     def views(self, flat: torch.Tensor, lo: int = 0, hi: int | None = None):
         return [flat[s.offset:s.offset + s.numel].view(s.shape) for s in self.slots[lo:hi]]
@@ -161,6 +188,11 @@ class MuonEngine(ShardedEngine):
         self.row_second_moment = {s.name: torch.zeros(s.shape[0], dtype=torch.float32, device=dev)
                                   for s in self.muon_slots} if self.normuon else {}
         self.muon_lr = self.muon_lr0
+        # CUDA kernels for the elementwise parts: matrices are whole float4 runs at aligned offsets
+        self._kernels = self.on_cuda and all(s.numel % 4 == 0 and s.offset % 4 == 0 for s in self.muon_slots)
+        self._gsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._gscale = 1.0
+        self._adam_table = None
 
     # ---- checkpoint helpers ------------------------------------------------------------------
     def _owned(self):
@@ -233,12 +265,21 @@ class MuonEngine(ShardedEngine):
         O = torch.zeros((n,) + st.shape, dtype=dt, device=self.device) if not st.even and self.distributed \
             else torch.empty((n,) + st.shape, dtype=dt, device=self.device)
         if st.hi > st.lo:
-            g = st.views(g_all, st.lo, st.hi)
-            m = st.views(self.exp_avg, st.lo, st.hi)
-            torch._foreach_mul_(m, self.mu)
-            torch._foreach_add_(m, g)
-            upd = torch.stack(torch._foreach_add(g, m, alpha=self.mu) if self.nesterov else m)
-            mine = orthogonalize_batched(upd, self.coeffs, self.muon_eps)
+            if self._kernels:
+                from nanoplm_b200.ops import kernels as K
+                k, numel = st.hi - st.lo, st.slots[0].numel
+                upd = torch.empty((k,) + st.shape, dtype=torch.bfloat16, device=self.device)
+                usq = torch.zeros(k, dtype=torch.float32, device=self.device)
+                K.muon_momentum_(g_all, self.exp_avg, st.offsets(self.device, True), numel, upd, usq, self._gsq,
+                                 self._gscale, self.hyper.max_grad_norm, self.mu, self.nesterov)
+                mine = orthogonalize_batched(upd, self.coeffs, self.muon_eps, sumsq=usq)
+            else:
+                g = st.views(g_all, st.lo, st.hi)
+                m = st.views(self.exp_avg, st.lo, st.hi)
+                torch._foreach_mul_(m, self.mu)
+                torch._foreach_add_(m, g)
+                upd = torch.stack(torch._foreach_add(g, m, alpha=self.mu) if self.nesterov else m)
+                mine = orthogonalize_batched(upd, self.coeffs, self.muon_eps)
             if self.normuon:
                 mine = mine.float()
                 v = torch.stack([self.row_second_moment[s.name] for s in st.slots[st.lo:st.hi]])
@@ -269,13 +310,15 @@ class MuonEngine(ShardedEngine):
         if self.distributed:
             dist.all_reduce(self.main_grad, group=self.pg)
         scale = 1.0 / (grad_accum * self.world)
+        h, t = self.hyper, self.step_count
+        self.muon_lr = self.muon_lr0 * (lr / self.adam_lr0 if self.adam_lr0 > 0 else 1.0)   # same schedule shape
+        bc1, bc2 = 1 - h.beta1 ** t, 1 - h.beta2 ** t
+        if self._kernels:
+            return self._step_kernels(lr, scale, bc1, bc2)
         g_all = self.main_grad.mul_(scale)
         norm = g_all.norm()
         if self.hyper.max_grad_norm > 0:
             g_all.mul_(torch.clamp(self.hyper.max_grad_norm / (norm + 1e-6), max=1.0))
-        h, t = self.hyper, self.step_count
-        self.muon_lr = self.muon_lr0 * (lr / self.adam_lr0 if self.adam_lr0 > 0 else 1.0)   # same schedule shape
-        bc1, bc2 = 1 - h.beta1 ** t, 1 - h.beta2 ** t
         for st in self.stacks:
             O = self._orthogonal_updates(st, g_all).float()
             p_views = st.views(self.master)
@@ -290,6 +333,37 @@ class MuonEngine(ShardedEngine):
         self._adamw_group([s for s in self.adam_slots if s.decay], g_all, lr, h.weight_decay, bc1, bc2)
         self._adamw_group([s for s in self.adam_slots if not s.decay], g_all, lr, 0.0, bc1, bc2)
         self.flat_params.copy_(self.master)
+        self.main_grad.zero_()
+        return norm
+
+    def _step_kernels(self, lr: float, scale: float, bc1: float, bc2: float) -> torch.Tensor:
+        """CUDA path: gradient scaling and clipping are folded into the kernels that read the
+        gradient (global norm read on the device), one kernel each for the momentum and the
+        parameter update of a stack, one for all AdamW tensors."""
+        from nanoplm_b200.ops import kernels as K
+        h = self.hyper
+        self._gsq.zero_()
+        K.sumsq_(self.main_grad, self._gsq)
+        self._gscale = scale
+        norm = self._gsq.sqrt() * scale
+        p16 = self.flat_params if self.flat_params.dtype == torch.bfloat16 else None
+        for st in self.stacks:
+            O = self._orthogonal_updates(st, self.main_grad)
+            K.muon_apply_(self.master, p16, st.offsets(self.device, False), st.slots[0].numel, O.contiguous(),
+                          self.muon_lr, self.muon_wd, self.cautious)
+        if self.adam_slots:
+            if self._adam_table is None:
+                dev = self.device
+                self._adam_table = (
+                    torch.tensor([s.offset for s in self.adam_slots], dtype=torch.int64, device=dev),
+                    torch.tensor([s.numel for s in self.adam_slots], dtype=torch.int64, device=dev),
+                    torch.tensor([int(s.decay) for s in self.adam_slots], dtype=torch.int32, device=dev),
+                    max(s.numel for s in self.adam_slots))
+            off, num, dec, mx = self._adam_table
+            K.adamw_slots_(self.master, self.exp_avg, self.exp_avg_sq, self.main_grad, p16, off, num, dec, mx,
+                           self._gsq, scale, h.max_grad_norm, lr, h.beta1, h.beta2, h.eps, h.weight_decay, bc1, bc2)
+        if p16 is None:
+            self.flat_params.copy_(self.master)
         self.main_grad.zero_()
         return norm
 

@@ -159,7 +159,7 @@ def test_padding_tail_trim_leaves_loss_and_grads_unchanged(cuda_status):
     assert (grads[0] - grads[1]).abs().max().item() < 2e-3 * scale
 
 
-@pytest.mark.parametrize("shape", [(4, 256, 512), (3, 512, 256), (2, 1024, 1024)])
+@pytest.mark.parametrize("shape", [(4, 256, 512), (3, 512, 256), (2, 1024, 2048)])
 def test_newton_schulz_on_grouped_gemm_matches_fp32(shape, cuda_status):
     """All matrices of a stack are orthogonalised by three row-grouped tcgen05 GEMM launches per
     iteration; the fp32 restatement runs the same iterations with torch.bmm on the CPU."""

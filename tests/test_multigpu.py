@@ -53,8 +53,17 @@ def _worker(rank, world, port, fused, out_path):
     from nanoplm_b200.runtime.pretrain import TrainStep
     from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
     model = _model()
-    eng = ShardedEngine(model, AdamWHyper(lr=2e-3, weight_decay=0.01), dev, fused_comm=fused)
-    if fused and world > 1:
+    if fused == "muon":
+        from nanoplm_b200.config.schema import PretrainingConfig
+        from nanoplm_b200.parallel.muon import MuonEngine
+        eng = MuonEngine(model, AdamWHyper(lr=2e-3, weight_decay=0.01),
+                         PretrainingConfig(dataset_dir="x", optimizer="normuon", muon_learning_rate=5e-3), dev)
+        assert eng._kernels
+        if world > 1:       # even stacks (all-gather) and an uneven one (3 matrices of 256 x 256: all-reduce)
+            assert {st.even for st in eng.stacks} == {True, False}
+    else:
+        eng = ShardedEngine(model, AdamWHyper(lr=2e-3, weight_decay=0.01), dev, fused_comm=fused)
+    if fused is True and world > 1:
         assert eng.fused is not None, "symmetric memory path was expected on this machine"
     model.train()
     st = TrainStep(model, eng, WarmupLinearSchedule(2e-3, 2, 100), dev)
@@ -70,7 +79,7 @@ def _worker(rank, world, port, fused, out_path):
         t /= world
     sd = eng.full_state_dict_model()
     if rank == 0:
-        torch.save({"losses": t.cpu(), "sd": sd, "fused": eng.fused is not None}, out_path)
+        torch.save({"losses": t.cpu(), "sd": sd, "fused": getattr(eng, "fused", None) is not None}, out_path)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -102,6 +111,19 @@ def test_two_gpu_steps_match_single_gpu(tmp_path):
         a, b = nccl["sd"][k].float(), fused["sd"][k].float()
         worst = max(worst, (a - b).abs().max().item())
     assert worst < 5e-3, worst
+
+
+@pytest.mark.multigpu
+def test_matrix_parallel_muon_on_two_gpus_matches_single_gpu(tmp_path):
+    """NorMuon with every stack of same-shape matrices split over two GPUs (momentum kernel and
+    grouped Newton-Schulz on the owner, all-gather of the bf16 orthogonal factors) against the
+    same training on one GPU."""
+    one = _run(1, "muon", str(tmp_path / "one.pt"))
+    two = _run(2, "muon", str(tmp_path / "two.pt"))
+    assert one["losses"][-1] < one["losses"][0] - 0.1, one["losses"]
+    assert torch.allclose(one["losses"], two["losses"], atol=3e-2), (one["losses"], two["losses"])
+    worst = max((one["sd"][k].float() - two["sd"][k].float()).abs().max().item() for k in one["sd"])
+    assert worst < 2e-2, worst
 
 
 def test_peer_barrier_times_out_without_hanging():
