@@ -237,20 +237,24 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
 //   ids != nullptr : embedding mode. x rows are table[ids[row]]; the row gradients are summed per
 //                    vocabulary entry in shared memory (each thread owns its channels, so no
 //                    atomics inside the block) and flushed to dtable with one atomic per element.
-template <int ROWS>
-__global__ void __launch_bounds__(256)
+template <int ROWS, int SUB>
+__global__ void __launch_bounds__(512)
 norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                      const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                      float* __restrict__ dw, float* __restrict__ dtable, int T, int C, int V, int rms) {
   extern __shared__ float s_table[];   // [V][C] in embedding mode
-  __shared__ float red[2][ROWS][8][2];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  // SUB row groups run side by side in one block (blockDim.x / SUB threads each): they share the
+  // table sums, which therefore take shared-memory atomics (two groups may hold the same token)
+  __shared__ float red[2][SUB][ROWS][8][2];
+  const int cthreads = blockDim.x / SUB;
+  const int sub = threadIdx.x / cthreads, tid = threadIdx.x % cthreads;
+  const int lane = tid & 31, warp = tid >> 5, nwarps = cthreads >> 5;
   const int i = tid * 8;
   const bool on = i < C;
   if (ids != nullptr) {
-    for (int k = tid; k < V * C; k += blockDim.x) s_table[k] = 0.f;
+    for (int k = threadIdx.x; k < V * C; k += blockDim.x) s_table[k] = 0.f;
     __syncthreads();
   }
   float wv[8], acc[8];
@@ -261,7 +265,9 @@ norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
   if (on && w) load8(w + i, wv);
   int buf = 0;
-  for (int row0 = blockIdx.x * ROWS; row0 < T; row0 += gridDim.x * ROWS, buf ^= 1) {
+  // every thread of the block runs the same number of iterations (the barrier below is block-wide)
+  for (int base = blockIdx.x * ROWS * SUB; base < T; base += gridDim.x * ROWS * SUB, buf ^= 1) {
+    const int row0 = base + sub * ROWS;
     float xh[ROWS][8], g[ROWS][8];
     float rstd[ROWS];
     int id[ROWS];
@@ -293,8 +299,8 @@ norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       sg = warp_sum(sg);
       sgx = warp_sum(sgx);
       if (lane == 0) {
-        red[buf][r][warp][0] = sg;
-        red[buf][r][warp][1] = sgx;
+        red[buf][sub][r][warp][0] = sg;
+        red[buf][sub][r][warp][1] = sgx;
       }
     }
     __syncthreads();
@@ -304,8 +310,8 @@ norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       if (row < T && on) {
         float tg = 0.f, tgx = 0.f;
         for (int k = 0; k < nwarps; ++k) {
-          tg += red[buf][r][k][0];
-          tgx += red[buf][r][k][1];
+          tg += red[buf][sub][r][k][0];
+          tgx += red[buf][sub][r][k][1];
         }
         tg = rms ? 0.f : tg / C;
         tgx /= C;
@@ -315,7 +321,10 @@ norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
         if (ids != nullptr) {
           float* dst = s_table + static_cast<size_t>(id[r]) * C + i;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dst[e] += o[e];
+          for (int e = 0; e < 8; ++e) {
+            if (SUB > 1) atomicAdd(&dst[e], o[e]);
+            else dst[e] += o[e];
+          }
         } else {
           if (dres) {
             float rr[8];
@@ -334,7 +343,7 @@ norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
   if (ids != nullptr) {
     __syncthreads();
-    for (int k = tid; k < V * C; k += blockDim.x) {
+    for (int k = threadIdx.x; k < V * C; k += blockDim.x) {
       const float v = s_table[k];
       if (v != 0.f) atomicAdd(&dtable[k], v);
     }
@@ -640,6 +649,88 @@ ce_bwd_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restri
   if (dbias && threadIdx.x < V) atomicAdd(&dbias[threadIdx.x], sdb[threadIdx.x]);
 }
 
+// Same backward for C <= 1024 (C % 4 == 0) as a tiled product: a block stages 32 rows of h (bf16)
+// and their dlogits in shared memory next to W; thread t owns channels 4t .. 4t+3 and keeps
+// dW[v][4t..4t+3] for all v in registers (4 V accumulators), so a row costs 8 V FMAs per thread and
+// no atomics; the block's dW is flushed once at the end.
+constexpr int CE_TILE_ROWS = 32;
+
+__global__ void __launch_bounds__(256)
+ce_bwd_tiled_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ W,
+                    const float* __restrict__ dlogits, const float* __restrict__ gscale,
+                    __nv_bfloat16* __restrict__ dh, float* __restrict__ dW, float* __restrict__ dbias,
+                    int n, int C, int V) {
+  extern __shared__ __align__(16) uint8_t ce_smem[];
+  __nv_bfloat16* sW = reinterpret_cast<__nv_bfloat16*>(ce_smem);            // [V][C]
+  __nv_bfloat16* sH = sW + static_cast<size_t>(V) * C;                       // [32][C]
+  float* sD = reinterpret_cast<float*>(sH + static_cast<size_t>(CE_TILE_ROWS) * C);  // [32][32]
+  const int t = threadIdx.x;
+  for (int i = t * 8; i < V * C; i += 256 * 8)
+    *reinterpret_cast<uint4*>(sW + i) = *reinterpret_cast<const uint4*>(W + i);
+  const float g = *gscale;
+  const int ch = t * 4;
+  const bool own = ch < C;
+  float acc[32][4];
+#pragma unroll
+  for (int v = 0; v < 32; ++v)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[v][e] = 0.f;
+  float db = 0.f;
+  const int tiles = (n + CE_TILE_ROWS - 1) / CE_TILE_ROWS;
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int r0 = tile * CE_TILE_ROWS;
+    __syncthreads();   // previous tile fully consumed (and sW written, first time round)
+    for (int i = t * 8; i < CE_TILE_ROWS * C; i += 256 * 8) {
+      const int r = i / C;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r0 + r < n) val = *reinterpret_cast<const uint4*>(h + static_cast<size_t>(r0) * C + i);
+      *reinterpret_cast<uint4*>(sH + i) = val;
+    }
+    for (int i = t; i < CE_TILE_ROWS * 32; i += 256) {
+      const int r = i >> 5;
+      sD[i] = (r0 + r < n) ? dlogits[static_cast<size_t>(r0) * 32 + i] * g : 0.f;
+    }
+    __syncthreads();
+    if (t < V) {
+#pragma unroll 8
+      for (int r = 0; r < CE_TILE_ROWS; ++r) db += sD[r * 32 + t];
+    }
+    if (own) {
+      const int rows = min(CE_TILE_ROWS, n - r0);
+      for (int r = 0; r < rows; ++r) {
+        const uint2 hp = *reinterpret_cast<const uint2*>(sH + static_cast<size_t>(r) * C + ch);
+        const float2 h01 = unpack_bf16x2(hp.x), h23 = unpack_bf16x2(hp.y);
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int v = 0; v < 32; ++v) {
+          if (v < V) {
+            const float d = sD[r * 32 + v];
+            const uint2 wp = *reinterpret_cast<const uint2*>(sW + static_cast<size_t>(v) * C + ch);
+            const float2 w01 = unpack_bf16x2(wp.x), w23 = unpack_bf16x2(wp.y);
+            o0 += d * w01.x; o1 += d * w01.y; o2 += d * w23.x; o3 += d * w23.y;
+            acc[v][0] += d * h01.x; acc[v][1] += d * h01.y; acc[v][2] += d * h23.x; acc[v][3] += d * h23.y;
+          }
+        }
+        uint2 op;
+        op.x = pack_bf16x2(o0, o1);
+        op.y = pack_bf16x2(o2, o3);
+        *reinterpret_cast<uint2*>(dh + static_cast<size_t>(r0 + r) * C + ch) = op;
+      }
+    }
+  }
+  if (own) {
+#pragma unroll
+    for (int v = 0; v < 32; ++v) {
+      if (v < V) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (acc[v][e] != 0.f) atomicAdd(&dW[static_cast<size_t>(v) * C + ch + e], acc[v][e]);
+      }
+    }
+  }
+  if (dbias && t < V && db != 0.f) atomicAdd(&dbias[t], db);
+}
+
 // ------------------------------------------------------------------ optimizer
 // sum of squares of an fp32 buffer, accumulated into out[0]
 __global__ void __launch_bounds__(256)
@@ -908,20 +999,29 @@ extern "C" int nplm_norm_bwd(const void* dy, const void* x, const int* ids, cons
   if (C >= 256 && C <= 2048 && ids != nullptr && dtable != nullptr && V > 0) {
     // embedding gradient: row-group kernel, per-vocabulary-entry sums in shared memory
     // (C/8 threads, rounded up to whole warps)
+    // the table sums fill the SM's shared memory (one block per SM), so the block itself keeps
+    // ROWS * SUB rows in flight: 4 groups of C/8 threads up to C = 1024, 2 beyond (512 threads)
     constexpr int ROWS = 4;
-    const int threads = ((C / 8) + 31) / 32 * 32;
-    const size_t smem = ids != nullptr ? static_cast<size_t>(V) * C * sizeof(float) : 0;
+    const int sub = C <= 1024 ? 4 : 2;
+    const int threads = ((C / 8) + 31) / 32 * 32 * sub;
+    const size_t smem = static_cast<size_t>(V) * C * sizeof(float);
     if (smem <= 200 * 1024) {
-      const int groups = (T + ROWS - 1) / ROWS;
-      int blocks = ids != nullptr ? 148 : 148 * 6;
+      const int groups = (T + ROWS * sub - 1) / (ROWS * sub);
+      int blocks = 148;
       if (blocks > groups) blocks = groups;
-      if (smem > 48 * 1024)
-        cudaFuncSetAttribute(norm_bwd_rows_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
-      norm_bwd_rows_kernel<ROWS><<<blocks, threads, smem, st>>>(
-          reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), ids,
-          reinterpret_cast<const __nv_bfloat16*>(w), mean, rstd, reinterpret_cast<const __nv_bfloat16*>(dres),
-          reinterpret_cast<__nv_bfloat16*>(dx), dw, dtable, T, C, V, rms);
+#define CALL_ROWS(SUB_)                                                                                   \
+  do {                                                                                                    \
+    if (smem > 48 * 1024)                                                                                 \
+      cudaFuncSetAttribute(norm_bwd_rows_kernel<ROWS, SUB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           static_cast<int>(smem));                                                       \
+    norm_bwd_rows_kernel<ROWS, SUB_><<<blocks, threads, smem, st>>>(                                      \
+        reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), ids,       \
+        reinterpret_cast<const __nv_bfloat16*>(w), mean, rstd, reinterpret_cast<const __nv_bfloat16*>(dres), \
+        reinterpret_cast<__nv_bfloat16*>(dx), dw, dtable, T, C, V, rms);                                  \
+  } while (0)
+      if (sub == 4) CALL_ROWS(4);
+      else CALL_ROWS(2);
+#undef CALL_ROWS
       return static_cast<int>(cudaGetLastError());
     }
   }
@@ -1030,6 +1130,21 @@ extern "C" int nplm_ce_bwd(const void* h, const void* W, const float* dlogits, c
                            cudaStream_t st) {
   if (n <= 0) return 0;
   if (V > 32 || V < 1 || (C % 8)) return -3;
+  if (C <= 1024) {
+    const size_t tsm = (static_cast<size_t>(V) * C + static_cast<size_t>(CE_TILE_ROWS) * C) * 2 +
+                       CE_TILE_ROWS * 32 * 4;
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(ce_bwd_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      configured = true;
+    }
+    int tb = (n + CE_TILE_ROWS - 1) / CE_TILE_ROWS;
+    if (tb > 148) tb = 148;
+    ce_bwd_tiled_kernel<<<tb, 256, tsm, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(h), reinterpret_cast<const __nv_bfloat16*>(W), dlogits, gscale,
+        reinterpret_cast<__nv_bfloat16*>(dh), dW, dbias, n, C, V);
+    return static_cast<int>(cudaGetLastError());
+  }
   const size_t smem = (static_cast<size_t>(V) * C + 32) * 4;
   if (smem > 220 * 1024) return -4;
   int blocks = (n + CE_WARPS - 1) / CE_WARPS;
