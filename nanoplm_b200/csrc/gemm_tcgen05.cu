@@ -36,6 +36,9 @@ enum : int {
   EPI_RELU = 7,        // host-side alias: EPI_GELU with act_relu = 1
   EPI_ROPE = 6,        // C(bf16) = acc with rotary embedding applied to every 64-wide head whose
                        // first column is < rope_cols (the q and k parts of a fused QKV projection)
+  EPI_SWIGLU_BWD = 8,  // acc = gradient of the SwiGLU output h = silu(gate) * value, N wide;
+                       // R = the pre-activations [value | gate] (bf16, 2N wide); C (bf16, 2N wide) =
+                       // [acc * silu(gate) | acc * value * silu'(gate)], the gradient of R
 };
 
 // PAIR: two CTAs of a cluster (cta_group::2) share one 256 x BN tile; each holds its own 128 rows
@@ -508,6 +511,56 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           }
+        } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+          constexpr int NCH = BN / 64;
+          const __nv_bfloat16* prow = args.R + static_cast<size_t>(row_ok ? row : 0) * args.ldr;
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            const int x = n0 + c * 64;
+            const bool active = rows_in && x < N;
+            // this lane's 64 value and 64 gate pre-activations: in flight while the accumulator loads
+            uint4 vv[8], gg[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              vv[j] = make_uint4(0, 0, 0, 0);
+              gg[j] = make_uint4(0, 0, 0, 0);
+            }
+            if (active && row_ok) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                vv[j] = __ldg(reinterpret_cast<const uint4*>(prow + x) + j);
+                gg[j] = __ldg(reinterpret_cast<const uint4*>(prow + N + x) + j);
+              }
+            }
+            uint32_t dvp[32], dgp[32];
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              uint32_t d[32];
+              tmem_ld32(taddr + c * 64 + hlf * 32, d);
+              tmem_ld_wait();
+              if (c == NCH - 1 && hlf == 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) release_acc(acc);
+              }
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const int q = hlf * 16 + e;   // bf16 pair index inside the 64-column chunk
+                const uint32_t vraw = reinterpret_cast<const uint32_t*>(&vv[q >> 2])[q & 3];
+                const uint32_t graw = reinterpret_cast<const uint32_t*>(&gg[q >> 2])[q & 3];
+                const float2 v2 = unpack_bf16x2(vraw), g2 = unpack_bf16x2(graw);
+                const float d0 = __uint_as_float(d[2 * e]), d1 = __uint_as_float(d[2 * e + 1]);
+                const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+                dvp[q] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
+                dgp[q] = pack_bf16x2(d0 * v2.x * s0 * (1.f + g2.x * (1.f - s0)),
+                                     d1 * v2.y * s1 * (1.f + g2.y * (1.f - s1)));
+              }
+            }
+            if (active) {
+              stage_store_bf16(stage, stage_toggle, &tmC, dvp, x, y0, lane);
+              stage_store_bf16(stage, stage_toggle, &tmC, dgp, N + x, y0, lane);
+            }
+          }
         } else {
           constexpr int NCH = BN / 64;
           if constexpr (EPI == EPI_ADD) {
@@ -912,7 +965,7 @@ static int launch_pair(const GemmMaps& maps, const GemmArgs& args, cudaStream_t 
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch(const GemmMaps& maps, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
-  if constexpr (EPI == EPI_ROPE) {
+  if constexpr (EPI == EPI_ROPE || EPI == EPI_SWIGLU_BWD) {
     return launch_impl<BN, A_MN, B_MN, EPI, true>(maps, args, max_ctas, stream);
   } else {
     if constexpr (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_GELU || EPI == EPI_SWIGLU) {
@@ -973,6 +1026,9 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   if (epi == EPI_ROPE && (a_mn || b_mn || direct_epilogue || rope_pos == nullptr || rope_cos == nullptr ||
                           rope_sin == nullptr || (rope_cols % 64) || (N % 64)))
     return -7;
+  if (epi == EPI_SWIGLU_BWD && (a_mn || direct_epilogue || R == nullptr || (N % 64) || (ldr % 8) || (ldc % 8) ||
+                                (reinterpret_cast<uintptr_t>(R) & 15) || grp.mode != 0 || grp.ag_world > 1))
+    return -7;
   const int num_kb = (K + BK - 1) / BK;
   if (splits < 0) splits = 1;
   if (splits > num_kb) splits = num_kb;
@@ -983,7 +1039,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   const uint64_t b_rows_mnmajor = grp.mode == 1 ? static_cast<uint64_t>(grp.b_group_rows) * grp.groups : K;
 
   const bool pair = grp.pair && bn == 256 && grp.mode == 0 && grp.ag_world <= 1 && max_ctas == 0 &&
-                    !(a_mn && !b_mn);
+                    !(a_mn && !b_mn) && epi != EPI_SWIGLU_BWD;
   GemmMaps maps;
   CUtensorMap& tmA = maps.A;
   CUtensorMap& tmB = maps.B;
@@ -1002,15 +1058,16 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   if (rc) return rc;
   // staged (TMA store) epilogue for the bf16 outputs; maps C / R describe [32 rows][64 cols] boxes
   maps.tma_epi = !direct_epilogue &&
-                 (epi == EPI_STORE || epi == EPI_ADD || epi == EPI_GELU || epi == EPI_SWIGLU || epi == EPI_ROPE) &&
+                 (epi == EPI_STORE || epi == EPI_ADD || epi == EPI_GELU || epi == EPI_SWIGLU || epi == EPI_ROPE ||
+                  epi == EPI_SWIGLU_BWD) &&
                  !(epi == EPI_ADD && (R == nullptr || (reinterpret_cast<uintptr_t>(R) & 15) || (ldr % 8)));
   maps.C = tmA;
   maps.R = tmA;
   if (maps.tma_epi) {
-    const int out_cols = epi == EPI_SWIGLU ? N / 2 : N;
+    const int out_cols = epi == EPI_SWIGLU ? N / 2 : (epi == EPI_SWIGLU_BWD ? 2 * N : N);
     rc = make_map_2d(&maps.C, C, out_cols, M, ldc, 64, 32, 2);
     if (rc) return rc;
-    if (R != nullptr) {
+    if (R != nullptr && epi != EPI_SWIGLU_BWD) {
       if ((reinterpret_cast<uintptr_t>(R) & 15) || (ldr % 8)) return -3;
       rc = make_map_2d(&maps.R, R, N, M, ldr, 64, 32, 2);
       if (rc) return rc;
@@ -1103,6 +1160,11 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   if (epi == EPI_ROPE) {
     if (bn == 256) return launch<256, false, false, EPI_ROPE>(maps, args, max_ctas, stream);
     return launch<128, false, false, EPI_ROPE>(maps, args, max_ctas, stream);
+  }
+  if (epi == EPI_SWIGLU_BWD) {
+    if (bn != 256) return -6;
+    if (b_mn) return launch<256, false, true, EPI_SWIGLU_BWD>(maps, args, max_ctas, stream);
+    return launch<256, false, false, EPI_SWIGLU_BWD>(maps, args, max_ctas, stream);
   }
   if (bn == 256) {
     if (!a_mn && !b_mn) { NPLM_DISPATCH_EPI(256, false, false) }

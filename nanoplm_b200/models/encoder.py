@@ -93,6 +93,8 @@ class MLP(nn.Module):
         self.Wo = Linear(inter, cfg.hidden_size, cfg.mlp_bias)
 
     def forward(self, x, residual=None):
+        if self.swiglu and self.Wi.bias is None and self.Wo.bias is None:
+            return ops.mlp_swiglu(x, self.Wi.weight, self.Wo.weight, residual)
         if self.swiglu:
             h = self.Wi(x, act="swiglu")
         else:  # GLU variant: act(value) * gate (reference: modeling.py:281-282)

@@ -121,6 +121,50 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db, dres, None, None
 
 
+class _SwiGLUMLPFn(torch.autograd.Function):
+    """out = (silu(gate) * value) w_out^T + residual with [value | gate] = x w_in^T, as one autograd
+    node so that the backward pass can compute the gradient of the pre-activations in the epilogue
+    of the GEMM that produces dL/dh (no separate SwiGLU-backward pass over [T, 3I] elements)."""
+
+    @staticmethod
+    def forward(ctx, x, w_in, w_out, residual):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not (x2.stride(1) == 1 and x2.stride(0) % 8 == 0):
+            x2 = x2.contiguous()
+        pre = torch.empty((x2.shape[0], w_in.shape[0]), dtype=BF, device=x.device)
+        h = K.gemm(x2, w_in, epi=K.EPI_SWIGLU, aux=pre, pair=True)
+        if residual is not None:
+            y = K.gemm(h, w_out, epi=K.EPI_ADD, aux=residual.reshape(-1, w_out.shape[0]))
+        else:
+            y = K.gemm(h, w_out)
+        ctx.save_for_backward(x2, w_in, w_out, pre, h)
+        ctx.has_res = residual is not None
+        ctx.x_shape = x.shape
+        return _as_shape(y, (*x.shape[:-1], y.shape[1]))
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_in, w_out, pre, h = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dpre = K.gemm(dy2, w_out, b_mn=True, epi=K.EPI_SWIGLU_BWD, aux=pre)
+        dw_out = _wgrad(dy2, h, w_out) if ctx.needs_input_grad[2] else None
+        dw_in = _wgrad(dpre, x2, w_in) if ctx.needs_input_grad[1] else None
+        dx = _as_shape(K.gemm(dpre, w_in, b_mn=True), ctx.x_shape) if ctx.needs_input_grad[0] else None
+        return dx, dw_in, dw_out, (dy if ctx.has_res else None)
+
+
+def mlp_swiglu(x, w_in, w_out, residual=None):
+    """SwiGLU MLP block (w_in rows = [value | gate]) + residual. CUDA bf16 with 64-aligned widths:
+    one autograd node with the fused backward epilogue; otherwise two `linear` calls."""
+    inter = w_out.shape[1]
+    if (x.is_cuda and x.dtype == BF and not _FP8_STATE["enabled"] and inter % 64 == 0 and w_in.shape[0] == 2 * inter
+            and w_in.shape[1] % 64 == 0 and w_out.shape[0] % 64 == 0):
+        return _SwiGLUMLPFn.apply(x, w_in, w_out, residual)
+    return linear(linear(x, w_in, act="swiglu"), w_out, residual=residual)
+
+
 def linear_rope(x, w, pos, cos, sin, rope_cols: int):
     """QKV projection with the rotary embedding of q and k applied in the GEMM epilogue (CUDA,
     head_dim 64). The result equals rope_qkv(linear(x, w)); its gradient w.r.t. the un-rotated

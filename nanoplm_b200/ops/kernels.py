@@ -13,6 +13,9 @@ from . import _lib
 from ._lib import check_rc, count_launch, lib, ptr, status_word, stream_ptr
 
 EPI_STORE, EPI_ADD, EPI_ATOMIC_F32, EPI_GELU, EPI_STORE_F32, EPI_SWIGLU, EPI_ROPE, EPI_RELU = 0, 1, 2, 3, 4, 5, 6, 7
+# acc = dL/dh of h = silu(gate) * value; aux = the [value | gate] pre-activations (2N wide);
+# out = their gradient (2N wide)
+EPI_SWIGLU_BWD = 8
 
 _BF16 = torch.bfloat16
 
@@ -71,7 +74,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         N, Kb = b.shape
     if K != Kb:
         raise ValueError(f"inner dims differ: {K} vs {Kb}")
-    out_cols = N // 2 if epi == EPI_SWIGLU else N
+    out_cols = N // 2 if epi == EPI_SWIGLU else (2 * N if epi == EPI_SWIGLU_BWD else N)
     f32_out = epi in (EPI_ATOMIC_F32, EPI_STORE_F32)
     if out is None:
         if epi == EPI_ATOMIC_F32:
@@ -85,12 +88,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if aux is not None:
         _chk(aux, _BF16, "aux")
         ldr = _rowmajor(aux, "aux")
-        if tuple(aux.shape) != (M, N):
-            raise ValueError(f"aux has shape {tuple(aux.shape)}, expected {(M, N)}")
+        aux_cols = 2 * N if epi == EPI_SWIGLU_BWD else N
+        if tuple(aux.shape) != (M, aux_cols):
+            raise ValueError(f"aux has shape {tuple(aux.shape)}, expected {(M, aux_cols)}")
     elif epi == EPI_ADD:
         raise ValueError("EPI_ADD needs the residual passed as aux")
+    elif epi == EPI_SWIGLU_BWD:
+        raise ValueError("EPI_SWIGLU_BWD needs the pre-activations passed as aux")
     if bn is None:
-        bn = 256 if (N >= 256 or epi == EPI_SWIGLU) else 128
+        bn = 256 if (N >= 256 or epi in (EPI_SWIGLU, EPI_SWIGLU_BWD)) else 128
     r_pos = r_cos = r_sin = None
     r_cols = 0
     if epi == EPI_ROPE:

@@ -466,3 +466,38 @@ def test_gemm_stream_k_wgrad_matches_fp32(shape, pair, cuda_status):
     K.gemm(dy, xx, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=acc, splits=0, bn=256, pair=pair)
     want = 1.0 + dy.float().t() @ xx.float()
     assert (acc - want).abs().max().item() < 0.01 * want.abs().max().item() + 0.05
+
+
+@pytest.mark.parametrize("T,C,I", [(1000, 256, 512), (333, 128, 192), (4096, 1024, 2048)])
+def test_swiglu_backward_epilogue_and_fused_mlp(T, C, I, cuda_status):
+    """The gradient of the SwiGLU pre-activations computed in the epilogue of the dL/dh GEMM
+    against fp32 autograd, and the fused MLP node against the two-linear composition."""
+    from nanoplm_b200.ops import functional as ops
+    from nanoplm_b200.ops import kernels as K
+    torch.manual_seed(5)
+    x = _randn(T, C)
+    w_in = _randn(2 * I, C, scale=C ** -0.5)
+    w_out = _randn(C, I, scale=I ** -0.5)
+    res = _randn(T, C)
+    dy = _randn(T, C)
+    # epilogue alone
+    pre = (x.float() @ w_in.float().t()).to(BF)
+    dpre = K.gemm(dy, w_out, b_mn=True, epi=K.EPI_SWIGLU_BWD, aux=pre)
+    assert dpre.shape == (T, 2 * I)
+    p32 = pre.float().requires_grad_(True)
+    v, g = p32.chunk(2, dim=-1)
+    (F.silu(g) * v).backward(dy.float() @ w_out.float())
+    _close(dpre, p32.grad, what="swiglu bwd epilogue")
+    # fused node, forward and all four gradients
+    xs, wi, wo, rs = (t.clone().requires_grad_(True) for t in (x, w_in, w_out, res))
+    out = ops.mlp_swiglu(xs, wi, wo, rs)
+    out.backward(dy)
+    x32, wi32, wo32, r32 = (t.float().requires_grad_(True) for t in (x, w_in, w_out, res))
+    v, g = (x32 @ wi32.t()).chunk(2, dim=-1)
+    ref = (F.silu(g) * v) @ wo32.t() + r32
+    ref.backward(dy.float())
+    _close(out, ref, what="fused mlp out")
+    _close(xs.grad, x32.grad, rtol=3e-2, atol=3e-2, what="fused mlp dx")
+    _close(wi.grad, wi32.grad, rtol=3e-2, atol=3e-2, what="fused mlp dw_in")
+    _close(wo.grad, wo32.grad, rtol=3e-2, atol=3e-2, what="fused mlp dw_out")
+    _close(rs.grad, r32.grad, what="fused mlp dres")
