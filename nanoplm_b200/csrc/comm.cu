@@ -101,6 +101,61 @@ __global__ void publish_kernel(PeerPtrs slots, int rank, int world, const float*
   }
 }
 
+// Packed statistics all-reduce (tokens, raw tokens, elapsed time, ... of a logging window): every
+// rank stores its <= 16 doubles into its row of every peer's table, raises a flag there, waits
+// (bounded) for the flags of all peers in its own table and reduces the rows in rank order:
+// value i is summed, or maximised when bit i of max_mask is set. One launch of one block replaces
+// the 2-3 small library all-reduces of the reference's logging path
+// (src/nanoplm/pretraining/pure_pipeline.py:775-800). Per-rank area behind buf.p[r]:
+//   double rows[2][MAX_PEERS][16]; uint32 flags[2][MAX_PEERS]     (2 = parity of the call counter:
+// a rank can run at most one call ahead of a peer, so two alternating tables never collide).
+constexpr int STATS_MAX = 16;
+constexpr int STATS_FLAG_OFFSET = 2 * MAX_PEERS * STATS_MAX * 8;   // bytes
+
+__global__ void __launch_bounds__(128)
+stats_allreduce_kernel(PeerPtrs buf, int rank, int world, uint32_t epoch, const double* __restrict__ in,
+                       double* __restrict__ out, int n, uint32_t max_mask, long long limit_cycles,
+                       int* status) {
+  __shared__ int failed;
+  const int t = threadIdx.x;
+  const int par = static_cast<int>(epoch & 1u);
+  if (t == 0) failed = 0;
+  {
+    const int p = t / STATS_MAX, i = t % STATS_MAX;
+    if (p < world && i < n) {
+      volatile double* rows = reinterpret_cast<volatile double*>(buf.p[p]);
+      rows[(par * MAX_PEERS + rank) * STATS_MAX + i] = in[i];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (t < world) {
+    uint32_t* peer_flags = reinterpret_cast<uint32_t*>(static_cast<char*>(buf.p[t]) + STATS_FLAG_OFFSET);
+    st_release_sys(peer_flags + par * MAX_PEERS + rank, epoch);
+    const uint32_t* mine =
+        reinterpret_cast<const uint32_t*>(static_cast<char*>(buf.p[rank]) + STATS_FLAG_OFFSET) + par * MAX_PEERS + t;
+    const long long t0 = clock64();
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - t0 > limit_cycles) {
+        atomicExch(status, ST_TIMEOUT_PEER);
+        failed = 1;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  if (t < n && !failed) {
+    const volatile double* rows = reinterpret_cast<const volatile double*>(buf.p[rank]);
+    double acc = rows[(par * MAX_PEERS + 0) * STATS_MAX + t];
+    for (int p = 1; p < world; ++p) {
+      const double v = rows[(par * MAX_PEERS + p) * STATS_MAX + t];
+      acc = ((max_mask >> t) & 1u) ? fmax(acc, v) : acc + v;
+    }
+    out[t] = acc;
+  }
+}
+
 // AdamW on the owned slice [lo, lo+n) + push of the bf16 result to every rank's parameter buffer.
 // hyper: [lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale, max_norm].
 // Elements with global index < decay_end use weight_decay, the rest none. n is a multiple of 8.
@@ -185,6 +240,19 @@ extern "C" int nplm_rs_sumsq(void* const* grad_ptrs, int world, long long lo, lo
   long long blocks = (n / 4 + 511) / 512;
   if (blocks > 148 * 4) blocks = 148 * 4;
   rs_sumsq_kernel<<<static_cast<int>(blocks), 512, 0, st>>>(to_peers(grad_ptrs, world), world, lo, n, shard, sumsq);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// buffer bytes per rank that nplm_stats_allreduce needs (zero-initialised symmetric memory)
+extern "C" int nplm_stats_buffer_bytes() { return STATS_FLAG_OFFSET + 2 * MAX_PEERS * 4; }
+
+extern "C" int nplm_stats_allreduce(void* const* buf_ptrs, int rank, int world, unsigned epoch, const double* in,
+                                    double* out, int n, unsigned max_mask, double timeout_s, int* status,
+                                    cudaStream_t st) {
+  if (world < 1 || world > MAX_PEERS || n < 1 || n > STATS_MAX || epoch == 0) return -3;
+  const long long limit = static_cast<long long>(timeout_s * 1.8e9);
+  stats_allreduce_kernel<<<1, 128, 0, st>>>(to_peers(buf_ptrs, world), rank, world, epoch, in, out, n, max_mask,
+                                            limit, status);
   return static_cast<int>(cudaGetLastError());
 }
 

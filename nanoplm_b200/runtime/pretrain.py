@@ -230,6 +230,12 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
     else:
         raise ValueError(f"Invalid optimizer: {cfg.optimizer}. Supported: [adamw, stable_adamw, muon, normuon]")
     model.train()
+    # logging statistics: one kernel over peer memory instead of library all-reduces, where the
+    # ranks can map each other's memory (same switch as the fused optimizer step)
+    peer_stats = None
+    if distributed and device.type == "cuda" and bool(cfg.fused_comm):
+        from nanoplm_b200.comm.peer_stats import PeerStats
+        peer_stats = PeerStats.try_create(device)
     if getattr(cfg, "fp8", False):
         if str(getattr(cfg, "fp8_recipe", "block128")) != "block128":
             raise ValueError(f"Unknown fp8_recipe {cfg.fp8_recipe!r}; supported: block128")
@@ -350,7 +356,10 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                     torch.cuda.synchronize()
                 elapsed = time.perf_counter() - t0
                 stats = torch.tensor([tok, raw_tok, elapsed], dtype=torch.float64, device=device)
-                if distributed:
+                if peer_stats is not None:
+                    stats = torch.tensor(peer_stats.all_reduce([tok, raw_tok, elapsed], max_mask=0b100),
+                                         dtype=torch.float64)
+                elif distributed:
                     mx = stats[2:].clone()
                     dist.all_reduce(stats[:2])
                     dist.all_reduce(mx, op=dist.ReduceOp.MAX)

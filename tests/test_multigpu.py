@@ -405,3 +405,49 @@ def test_all_gather_gemm_fp8(tmp_path):
         p.join(240)
         assert p.exitcode == 0, f"rank exited with {p.exitcode}"
     assert os.path.exists(out)
+
+
+def _stats_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from nanoplm_b200.comm.peer_stats import PeerStats
+    ps = PeerStats.try_create(dev)
+    assert ps is not None and ps.world == world
+    got = []
+    for call in range(5):      # alternating tables, a different number of values every call
+        vals = [float(rank + 1) * (call + 1), 1000.0 + rank, 0.25 * (rank + 1) + call][: 1 + call % 3]
+        got.append(ps.all_reduce(vals, max_mask=0b100))
+    if rank == 0:
+        torch.save(got, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+def test_peer_stats_all_reduce_two_gpus(tmp_path):
+    out = str(tmp_path / "stats.pt")
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_stats_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    got = torch.load(out)
+    for call, res in enumerate(got):
+        want = [3.0 * (call + 1), 2001.0, 0.5 + call][: 1 + call % 3]      # sum, sum, max over ranks 0 and 1
+        assert res == pytest.approx(want), (call, res, want)
+
+
+def test_peer_stats_single_process():
+    """One process: the table lives in ordinary device memory and the kernel talks to itself."""
+    from nanoplm_b200.comm.peer_stats import PeerStats
+    ps = PeerStats.try_create(torch.device("cuda:0"))
+    for call in range(3):
+        vals = [1.5 + call, 7.0, -2.0]
+        assert ps.all_reduce(vals, max_mask=0b010) == pytest.approx(vals)
+    with pytest.raises(ValueError):
+        ps.all_reduce([0.0] * 17)
