@@ -481,3 +481,9 @@ class TrainStep:
         loss = self._run(host_batches, True)
         self.d2h_bytes += loss.element_size()
         return float(loss.item())
+
+
+# The reference has two entry points, the HF-Trainer pipeline `run_pretraining`
+# (src/nanoplm/pretraining/pipeline.py:107-295) and `run_pure_pretraining`
+# (src/nanoplm/pretraining/pure_pipeline.py:334-927); both names lead to the one native pipeline.
+run_pure_pretraining = run_pretraining
