@@ -1190,7 +1190,8 @@ extern "C" int nplm_fa_fwd(const void* qkv, void* out, float* lse, const int* se
   return static_cast<int>(cudaGetLastError());
 }
 
-// dq_acc: caller-provided fp32 scratch [T][H*D]; it is cleared here. delta: fp32 scratch [H][T].
+// dq_acc: caller-provided fp32 scratch [T][H*D]; it is cleared here. delta: fp32 scratch [H][T],
+// computed here from out and dout unless out is null (then it must hold rowsum(dO * O) already).
 extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* dout, const float* lse,
                                 void* dqkv, float* dq_acc, float* delta, const int* seq_start,
                                 const int* seq_end, int T, int H, int D, int window, float scale,
@@ -1229,7 +1230,7 @@ extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* do
   }
   const int HD = H * D;
   NPLM_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * HD * sizeof(float), st));
-  {
+  if (out != nullptr) {   // out == nullptr: the caller has filled delta already
     const long long total = static_cast<long long>(T) * H * 8;
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
@@ -1305,7 +1306,7 @@ extern "C" int nplm_fa_bwd_noalloc(const void* qkv, const void* out, const void*
                                    void* dqkv, const int* seq_start, const int* seq_end, int T, int H,
                                    int D, int window, float scale, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (H <= 0 || D <= 0) return -3;
+  if (H <= 0 || D <= 0 || out == nullptr) return -3;   // this entry always computes delta itself
   const size_t need_dq = static_cast<size_t>(T) * H * D;
   const size_t need_stat = static_cast<size_t>(T) * H;
   if (need_dq > NPLM_NOALLOC_MAX_DQ_FLOATS || need_stat > NPLM_NOALLOC_MAX_STAT_FLOATS)

@@ -36,6 +36,8 @@ enum : int {
   EPI_RELU = 7,        // host-side alias: EPI_GELU with act_relu = 1
   EPI_ROPE = 6,        // C(bf16) = acc with rotary embedding applied to every 64-wide head whose
                        // first column is < rope_cols (the q and k parts of a fused QKV projection)
+  EPI_STORE_DELTA = 9, // C(bf16) = acc, and delta[col / 64][row] = sum over each 64-column head of
+                       // bf16(acc) * R (the attention backward's rowsum(dO * O), R = O)
   EPI_SWIGLU_BWD = 8,  // acc = gradient of the SwiGLU output h = silu(gate) * value, N wide;
                        // R = the pre-activations [value | gate] (bf16, 2N wide); C (bf16, 2N wide) =
                        // [acc * silu(gate) | acc * value * silu'(gate)], the gradient of R
@@ -63,6 +65,7 @@ struct GemmArgs {
   int M, N, K;
   int ldc, ldr;
   int splits;
+  float* delta;     // EPI_STORE_DELTA: fp32 [N / 64][M]
   int swiglu_half;  // EPI_SWIGLU: row offset of the gate half inside B (= N/2)
   int* status;
   // EPI_ROPE: position of every output row, cos / sin tables [max_pos][32] (head_dim 64)
@@ -509,6 +512,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 stage_store_bf16(stage, stage_toggle, &tmR, pv, x, y0, lane);
                 stage_store_bf16(stage, stage_toggle, &tmR, pg, args.swiglu_half + x, y0, lane);
               }
+            }
+          }
+        } else if constexpr (EPI == EPI_STORE_DELTA) {
+          constexpr int NCH = BN / 64;
+          const __nv_bfloat16* orow = args.R + static_cast<size_t>(row_ok ? row : 0) * args.ldr;
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            const int x = n0 + c * 64;
+            const bool active = rows_in && x < N;
+            uint4 ov[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ov[j] = make_uint4(0, 0, 0, 0);
+            if (active && row_ok) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) ov[j] = __ldg(reinterpret_cast<const uint4*>(orow + x) + j);
+            }
+            uint32_t packed[32];
+            float dot = 0.f;
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              uint32_t d[32];
+              tmem_ld32(taddr + c * 64 + hlf * 32, d);
+              tmem_ld_wait();
+              if (c == NCH - 1 && hlf == 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) release_acc(acc);
+              }
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const int q = hlf * 16 + e;
+                const uint32_t pk = pack_bf16x2(__uint_as_float(d[2 * e]), __uint_as_float(d[2 * e + 1]));
+                packed[q] = pk;
+                const float2 g2 = unpack_bf16x2(pk);
+                const float2 o2 = unpack_bf16x2(reinterpret_cast<const uint32_t*>(&ov[q >> 2])[q & 3]);
+                dot += g2.x * o2.x + g2.y * o2.y;
+              }
+            }
+            if (active) {
+              stage_store_bf16(stage, stage_toggle, &tmC, packed, x, y0, lane);
+              if (row_ok) args.delta[static_cast<size_t>(x >> 6) * M + row] = dot;
             }
           }
         } else if constexpr (EPI == EPI_SWIGLU_BWD) {
@@ -965,7 +1009,7 @@ static int launch_pair(const GemmMaps& maps, const GemmArgs& args, cudaStream_t 
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch(const GemmMaps& maps, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
-  if constexpr (EPI == EPI_ROPE || EPI == EPI_SWIGLU_BWD) {
+  if constexpr (EPI == EPI_ROPE || EPI == EPI_SWIGLU_BWD || EPI == EPI_STORE_DELTA) {
     return launch_impl<BN, A_MN, B_MN, EPI, true>(maps, args, max_ctas, stream);
   } else {
     if constexpr (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_GELU || EPI == EPI_SWIGLU) {
@@ -996,6 +1040,7 @@ struct GroupSpec {
   int ag_world = 0, ag_rank = 0;
   void* const* ag_ptrs = nullptr;  // every rank's full B buffer (this rank's one is B itself)
   unsigned* ag_flags = nullptr;
+  float* delta = nullptr;          // EPI_STORE_DELTA side output
 };
 
 static int gemm_entry(const void* A, const void* B, void* C, const void* R, int M, int N,
@@ -1026,6 +1071,10 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   if (epi == EPI_ROPE && (a_mn || b_mn || direct_epilogue || rope_pos == nullptr || rope_cos == nullptr ||
                           rope_sin == nullptr || (rope_cols % 64) || (N % 64)))
     return -7;
+  if (epi == EPI_STORE_DELTA && (a_mn || direct_epilogue || R == nullptr || grp.delta == nullptr || (N % 64) ||
+                                 (ldr % 8) || (reinterpret_cast<uintptr_t>(R) & 15) || grp.mode != 0 ||
+                                 grp.ag_world > 1 || bn != 256))
+    return -7;
   if (epi == EPI_SWIGLU_BWD && (a_mn || direct_epilogue || R == nullptr || (N % 64) || (ldr % 8) || (ldc % 8) ||
                                 (reinterpret_cast<uintptr_t>(R) & 15) || grp.mode != 0 || grp.ag_world > 1))
     return -7;
@@ -1039,7 +1088,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   const uint64_t b_rows_mnmajor = grp.mode == 1 ? static_cast<uint64_t>(grp.b_group_rows) * grp.groups : K;
 
   const bool pair = grp.pair && bn == 256 && grp.mode == 0 && grp.ag_world <= 1 && max_ctas == 0 &&
-                    !(a_mn && !b_mn) && epi != EPI_SWIGLU_BWD;
+                    !(a_mn && !b_mn) && epi != EPI_SWIGLU_BWD && epi != EPI_STORE_DELTA;
   GemmMaps maps;
   CUtensorMap& tmA = maps.A;
   CUtensorMap& tmB = maps.B;
@@ -1059,7 +1108,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   // staged (TMA store) epilogue for the bf16 outputs; maps C / R describe [32 rows][64 cols] boxes
   maps.tma_epi = !direct_epilogue &&
                  (epi == EPI_STORE || epi == EPI_ADD || epi == EPI_GELU || epi == EPI_SWIGLU || epi == EPI_ROPE ||
-                  epi == EPI_SWIGLU_BWD) &&
+                  epi == EPI_SWIGLU_BWD || epi == EPI_STORE_DELTA) &&
                  !(epi == EPI_ADD && (R == nullptr || (reinterpret_cast<uintptr_t>(R) & 15) || (ldr % 8)));
   maps.C = tmA;
   maps.R = tmA;
@@ -1067,7 +1116,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
     const int out_cols = epi == EPI_SWIGLU ? N / 2 : (epi == EPI_SWIGLU_BWD ? 2 * N : N);
     rc = make_map_2d(&maps.C, C, out_cols, M, ldc, 64, 32, 2);
     if (rc) return rc;
-    if (R != nullptr && epi != EPI_SWIGLU_BWD) {
+    if (R != nullptr && epi != EPI_SWIGLU_BWD && epi != EPI_STORE_DELTA) {
       if ((reinterpret_cast<uintptr_t>(R) & 15) || (ldr % 8)) return -3;
       rc = make_map_2d(&maps.R, R, N, M, ldr, 64, 32, 2);
       if (rc) return rc;
@@ -1083,6 +1132,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   args.ldc = ldc;
   args.ldr = ldr;
   args.splits = splits;
+  args.delta = grp.delta;
   args.swiglu_half = N / 2;
   args.status = status;
   args.rope_pos = rope_pos;
@@ -1161,6 +1211,10 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
     if (bn == 256) return launch<256, false, false, EPI_ROPE>(maps, args, max_ctas, stream);
     return launch<128, false, false, EPI_ROPE>(maps, args, max_ctas, stream);
   }
+  if (epi == EPI_STORE_DELTA) {
+    if (b_mn) return launch<256, false, true, EPI_STORE_DELTA>(maps, args, max_ctas, stream);
+    return launch<256, false, false, EPI_STORE_DELTA>(maps, args, max_ctas, stream);
+  }
   if (epi == EPI_SWIGLU_BWD) {
     if (bn != 256) return -6;
     if (b_mn) return launch<256, false, true, EPI_SWIGLU_BWD>(maps, args, max_ctas, stream);
@@ -1200,6 +1254,18 @@ extern "C" int nplm_gemm_bf16_pair(const void* A, const void* B, void* C, const 
   g.pair = true;
   return gemm_entry(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, splits, 256, 0,
                     direct_epilogue, rope_pos, rope_cos, rope_sin, rope_cols, status, stream, g);
+}
+
+// C = A B^T (b_mn = 0) or A B (b_mn = 1) in bf16, plus delta[h][row] = sum_{64 columns of head h}
+// C[row] * R[row] (fp32 [N / 64][M]): the data gradient of the attention output projection and the
+// rowsum(dO * O) term of the attention backward in one pass (R = the attention output O).
+extern "C" int nplm_gemm_bf16_delta(const void* A, const void* B, void* C, const void* R, float* delta, int M,
+                                    int N, int K, int lda, int ldb, int ldc, int ldr, int b_mn, int* status,
+                                    cudaStream_t stream) {
+  GroupSpec g;
+  g.delta = delta;
+  return gemm_entry(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, 0, b_mn, EPI_STORE_DELTA, 1, 256, 0, 0, nullptr,
+                    nullptr, nullptr, 0, status, stream, g);
 }
 
 // Grouped GEMM over row groups (mixture-of-experts forward and data gradient).

@@ -74,6 +74,9 @@ class Attention(nn.Module):
                  and x.dim() == 2 and self.Wqkv.in_features % 8 == 0 and not ops.fp8_enabled())
         if fused:   # RoPE in the QKV GEMM epilogue, its transpose inside the attention backward
             qkv = ops.linear_rope(x, self.Wqkv.weight, ctx.position_ids, rope[0], rope[1], 2 * H * D)
+            if self.Wo.bias is None:
+                return ops.attention_out_proj(qkv, self.Wo.weight, residual, ctx.seq_start, ctx.seq_end, H, D,
+                                              window, self.scale, rope=(ctx.position_ids, rope[0], rope[1]))
             y = ops.attention_varlen(qkv, ctx.seq_start, ctx.seq_end, H, D, window, self.scale,
                                      rope=(ctx.position_ids, rope[0], rope[1]))
         else:

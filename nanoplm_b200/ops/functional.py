@@ -424,6 +424,48 @@ class _AttnFn(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None, None
 
 
+class _AttnOutFn(torch.autograd.Function):
+    """Attention followed by its output projection (+ residual) as one autograd node: the GEMM that
+    turns dy into dO also emits rowsum(dO * O) from its epilogue, so the attention backward does
+    not read O and dO once more for it."""
+
+    @staticmethod
+    def forward(ctx, qkv, w_out, residual, seq_start, seq_end, H, D, window, scale, rope):
+        out, lse = K.fa_fwd(qkv, seq_start, seq_end, H, D, window, scale)
+        if residual is not None:
+            y = K.gemm(out, w_out, epi=K.EPI_ADD, aux=residual.reshape(-1, w_out.shape[0]))
+        else:
+            y = K.gemm(out, w_out)
+        ctx.save_for_backward(qkv, out, lse, seq_start, seq_end, w_out)
+        ctx.cfg = (H, D, window, scale)
+        ctx.rope = rope
+        ctx.has_res = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        qkv, out, lse, ss, se, w_out = ctx.saved_tensors
+        H, D, window, scale = ctx.cfg
+        dy2 = dy if dy.is_contiguous() else dy.contiguous()
+        delta = torch.empty((H, qkv.shape[0]), dtype=torch.float32, device=qkv.device)
+        dout = K.gemm_dgrad_delta(dy2, w_out, out, delta)
+        dw = _wgrad(dy2, out, w_out) if ctx.needs_input_grad[1] else None
+        dqkv = K.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, scale, delta=delta, rope=ctx.rope,
+                        delta_ready=True)
+        return dqkv, dw, (dy if ctx.has_res else None), None, None, None, None, None, None, None
+
+
+def attention_out_proj(qkv, w_out, residual, seq_start, seq_end, H: int, D: int, window: int, scale: float,
+                       rope=None):
+    """attention_varlen(qkv, ...) @ w_out^T + residual. CUDA bf16, head_dim 64, 2-D activations and a
+    bias-free projection run as one autograd node (fused backward); otherwise the two separate ops."""
+    if (qkv.is_cuda and qkv.dtype == BF and D == 64 and qkv.dim() == 2 and not _FP8_STATE["enabled"]
+            and w_out.shape[1] == H * D and w_out.shape[0] % 8 == 0):
+        return _AttnOutFn.apply(qkv, w_out, residual, seq_start, seq_end, H, D, window, scale, rope)
+    return linear(attention_varlen(qkv, seq_start, seq_end, H, D, window, scale, rope=rope), w_out,
+                  residual=residual)
+
+
 def seq_bounds(cu_seqlens: torch.Tensor, T: int):
     """Per-token [start, end) of the sequence each flat token belongs to."""
     if cu_seqlens.is_cuda:

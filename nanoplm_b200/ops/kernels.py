@@ -423,10 +423,34 @@ def fa_fwd(qkv, seq_start, seq_end, H, D, window, scale):
     return out, lse
 
 
+def gemm_dgrad_delta(dy: torch.Tensor, w: torch.Tensor, o: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """dO = dy @ w (w [K, N] read MN-major) in bf16 and, from the same epilogue,
+    delta[h, t] = sum over head h's 64 columns of dO[t] * o[t] (fp32 [N / 64, T])."""
+    _chk(dy, _BF16, "dy")
+    _chk(w, _BF16, "w")
+    _chk(o, _BF16, "o")
+    _chk(delta, torch.float32, "delta")
+    M, Kd = dy.shape
+    if w.shape[0] != Kd:
+        raise ValueError("inner dims differ")
+    N = w.shape[1]
+    if N % 64 or tuple(o.shape) != (M, N) or tuple(delta.shape) != (N // 64, M) or not delta.is_contiguous():
+        raise ValueError("o must be [M, N], delta [N / 64, M] contiguous, N a multiple of 64")
+    out = torch.empty((M, N), dtype=_BF16, device=dy.device)
+    rc = lib("gemm_tcgen05").nplm_gemm_bf16_delta(
+        ptr(dy), ptr(w), ptr(out), ptr(o), ptr(delta), c_int(M), c_int(N), c_int(Kd), c_int(_rowmajor(dy, "dy")),
+        c_int(_rowmajor(w, "w")), c_int(N), c_int(_rowmajor(o, "o")), c_int(1), ptr(status_word(dy.device)),
+        stream_ptr())
+    check_rc(rc, "gemm_bf16_delta")
+    count_launch()
+    return out
+
+
 def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=None, delta=None,
-           rope: tuple | None = None):
+           rope: tuple | None = None, delta_ready: bool = False):
     """rope = (pos, cos, sin): q / k in qkv were rotated before the forward pass; dQ / dK are rotated
-    back inside the kernels."""
+    back inside the kernels. delta_ready: `delta` [H, T] already holds rowsum(dO * O) (see
+    gemm_dgrad_delta); the kernel that computes it from out and dout is skipped."""
     T = qkv.shape[0]
     dqkv = torch.empty_like(qkv)
     if dq_acc is None:
@@ -436,13 +460,15 @@ def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=
     if not dout.is_contiguous():
         dout = dout.contiguous()
     r_pos, r_cos, r_sin = rope if rope is not None else (None, None, None)
+    if delta_ready:
+        out = None
     rc = lib("attention").nplm_fa_bwd_rope(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
                                            ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
                                            c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
                                            ptr(r_pos), ptr(r_cos), ptr(r_sin),
                                            ptr(status_word(qkv.device)), stream_ptr())
     check_rc(rc, "fa_bwd")
-    count_launch(4)
+    count_launch(3 if delta_ready else 4)
     return dqkv
 
 

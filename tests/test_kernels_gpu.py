@@ -501,3 +501,43 @@ def test_swiglu_backward_epilogue_and_fused_mlp(T, C, I, cuda_status):
     _close(wi.grad, wi32.grad, rtol=3e-2, atol=3e-2, what="fused mlp dw_in")
     _close(wo.grad, wo32.grad, rtol=3e-2, atol=3e-2, what="fused mlp dw_out")
     _close(rs.grad, r32.grad, what="fused mlp dres")
+
+
+@pytest.mark.parametrize("T,H", [(1000, 4), (333, 2), (4096, 16)])
+def test_dgrad_with_delta_epilogue_and_fused_attention_node(T, H, cuda_status):
+    """dO = dy @ W with rowsum(dO * O) per head from the same epilogue against fp32, and the fused
+    attention + output projection node against the two separate ops (same kernels otherwise)."""
+    from nanoplm_b200.ops import functional as ops
+    from nanoplm_b200.ops import kernels as K
+    torch.manual_seed(7)
+    D, C = 64, H * 64
+    dy = _randn(T, C)
+    w = _randn(C, C, scale=C ** -0.5)
+    o = _randn(T, C)
+    delta = torch.full((H, T), 7.0, dtype=torch.float32, device="cuda")
+    dout = K.gemm_dgrad_delta(dy, w, o, delta)
+    ref = dy.float() @ w.float()
+    _close(dout, ref, what="dgrad")
+    want = (dout.float() * o.float()).view(T, H, D).sum(-1).t()
+    assert (delta - want).abs().max().item() < 2e-3 * max(1.0, want.abs().max().item())
+    # fused node vs attention_varlen + linear
+    lens = [T // 3, T // 5, T - T // 3 - T // 5]
+    cu = torch.tensor([0, lens[0], lens[0] + lens[1], T], dtype=torch.int32, device="cuda")
+    ss, se = ops.seq_bounds(cu, T)
+    qkv = _randn(T, 3 * C, scale=0.5)
+    res = _randn(T, C)
+    for window in (-1, 64):
+        grads = []
+        outs = []
+        for fused in (True, False):
+            q, ww, r = (t.clone().requires_grad_(True) for t in (qkv, w, res))
+            if fused:
+                y = ops.attention_out_proj(q, ww, r, ss, se, H, D, window, D ** -0.5)
+            else:
+                y = ops.linear(ops.attention_varlen(q, ss, se, H, D, window, D ** -0.5), ww, residual=r)
+            y.backward(dy)
+            outs.append(y)
+            grads.append((q.grad, ww.grad, r.grad))
+        assert torch.equal(outs[0], outs[1])
+        for a, b, name in zip(grads[0], grads[1], ("dqkv", "dw", "dres")):
+            _close(a, b, rtol=2e-2, atol=2e-2, what=f"fused attention node {name} window={window}")
