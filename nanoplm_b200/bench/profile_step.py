@@ -22,6 +22,8 @@ def main() -> None:
     ap.add_argument("--optimizer-step", action="store_true")
     ap.add_argument("--variant", choices=("default", "moe", "conv_mhc"), default="default")
     ap.add_argument("--no-trim", action="store_true", help="run the kernels over the padding tail as well")
+    ap.add_argument("--gaps", action="store_true",
+                    help="trace the step with torch.profiler and report the GPU idle time between kernels")
     args = ap.parse_args()
 
     from nanoplm_b200.config.schema import ModelConfig
@@ -72,15 +74,49 @@ def main() -> None:
         micro()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    prof = None
+    if args.gaps:
+        from torch.profiler import ProfilerActivity, profile
+        prof = profile(activities=[ProfilerActivity.CUDA])
+        prof.__enter__()
     torch.cuda.profiler.start()
     e0.record()
     micro()
     e1.record()
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
+    if prof is not None:
+        prof.__exit__(None, None, None)
+        _report_gaps(prof)
     _lib.check_status()
     print(f"profiled micro-step: {e0.elapsed_time(e1):.3f} ms, {args.tokens_rows * 512} flat tokens, "
           f"{args.layers} layers, kernels launched by this package so far: {_lib.launches()}")
+
+
+def _report_gaps(prof) -> None:
+    """Union of the kernel intervals of the trace against its span: what is left is launch latency
+    and dependencies between consecutive kernels."""
+    ev = sorted((e.time_range.start, e.time_range.end) for e in prof.events()
+                if e.device_type == torch.autograd.DeviceType.CUDA)
+    if not ev:
+        print("gaps: the trace holds no device events")
+        return
+    busy, gaps = 0.0, []
+    cur_s, cur_e = ev[0]
+    for s, e in ev[1:]:
+        if s > cur_e:
+            gaps.append(s - cur_e)
+            busy += cur_e - cur_s
+            cur_s, cur_e = s, e
+        else:
+            cur_e = max(cur_e, e)
+    busy += cur_e - cur_s
+    span = ev[-1][1] - ev[0][0]
+    gaps.sort()
+    med = gaps[len(gaps) // 2] if gaps else 0.0
+    print(f"gaps: {len(ev)} device activities, span {span / 1e3:.2f} ms, busy {busy / 1e3:.2f} ms, "
+          f"idle {(span - busy) / 1e3:.2f} ms in {len(gaps)} gaps (median {med:.1f} us, "
+          f"max {gaps[-1] if gaps else 0.0:.1f} us)")
 
 
 if __name__ == "__main__":
