@@ -290,7 +290,10 @@ mhc_bwd_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restr
       }
       if (has_w) st8(dy + static_cast<size_t>(t) * C + c, dyv);
 #pragma unroll
-      for (int j = 0; j < N; ++j) st8(dX + (static_cast<size_t>(t) * N + j) * C + c, o[j]);
+      if (dX != nullptr) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) st8(dX + (static_cast<size_t>(t) * N + j) * C + c, o[j]);
+      }
     }
     // every lane takes part in the reduction; lane l ends up with the total of sums[l]
     const float total = warp_transpose_sum<N * N + 2 * N>(sums, lane);
@@ -300,6 +303,61 @@ mhc_bwd_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restr
       if (has_w) dbeta[t * N + (lane - N * N)] = total;
     } else if (lane < N * N + 2 * N) {
       if (has_r) dalpha[t * N + (lane - N * N - N)] = total;
+    }
+  }
+}
+
+// z[t][:] = (1/n) sum_i X[t][i][:]   (what the coefficient network of a site sees)
+__global__ void __launch_bounds__(256)
+mhc_mean_kernel(const __nv_bfloat16* __restrict__ X, __nv_bfloat16* __restrict__ z, int T, int n, int C) {
+  const int vec = C >> 3;
+  const long long total = static_cast<long long>(T) * vec;
+  const float inv = 1.f / static_cast<float>(n);
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / vec);
+    const int c = static_cast<int>(idx % vec) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < n; ++i) {
+      float xv[8];
+      ld8(X + (static_cast<size_t>(t) * n + i) * C + c, xv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += xv[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] *= inv;
+    st8(z + static_cast<size_t>(t) * C + c, acc);
+  }
+}
+
+// Gradient of the streams entering a site, all three consumers in one pass:
+//   dX[t][j][:] = g[t][j][:] (from the write, may be null) + alpha[t][j] dh[t][:] (read, may be null)
+//                 + dz[t][:] / n (stream mean, may be null)
+__global__ void __launch_bounds__(256)
+mhc_dx_combine_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ alpha,
+                      const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ dz,
+                      __nv_bfloat16* __restrict__ dX, int T, int n, int C) {
+  const int vec = C >> 3;
+  const long long total = static_cast<long long>(T) * vec;
+  const float inv = 1.f / static_cast<float>(n);
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / vec);
+    const int c = static_cast<int>(idx % vec) * 8;
+    float hv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, zv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (dh != nullptr) ld8(dh + static_cast<size_t>(t) * C + c, hv);
+    if (dz != nullptr) {
+      ld8(dz + static_cast<size_t>(t) * C + c, zv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) zv[e] *= inv;
+    }
+    for (int j = 0; j < n; ++j) {
+      float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (g != nullptr) ld8(g + (static_cast<size_t>(t) * n + j) * C + c, o);
+      const float a = (dh != nullptr) ? alpha[t * n + j] : 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] += a * hv[e] + zv[e];
+      st8(dX + (static_cast<size_t>(t) * n + j) * C + c, o);
     }
   }
 }
@@ -343,6 +401,24 @@ extern "C" int nplm_mhc_read(const void* X, const float* alpha, void* h, int T, 
   if ((C % 8) || n < 1 || n > MAX_STREAMS) return -3;
   mhc_read_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(X), alpha, reinterpret_cast<__nv_bfloat16*>(h), T, n, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_mhc_mean(const void* X, void* z, int T, int n, int C, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if ((C % 8) || n < 1 || n > MAX_STREAMS) return -3;
+  mhc_mean_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(X), reinterpret_cast<__nv_bfloat16*>(z), T, n, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_mhc_dx_combine(const void* g, const float* alpha, const void* dh, const void* dz, void* dX,
+                                   int T, int n, int C, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if ((C % 8) || n < 1 || n > MAX_STREAMS || (dh != nullptr && alpha == nullptr)) return -3;
+  mhc_dx_combine_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(g), alpha, reinterpret_cast<const __nv_bfloat16*>(dh),
+      reinterpret_cast<const __nv_bfloat16*>(dz), reinterpret_cast<__nv_bfloat16*>(dX), T, n, C);
   return static_cast<int>(cudaGetLastError());
 }
 

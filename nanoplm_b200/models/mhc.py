@@ -62,6 +62,63 @@ class _WriteFn(torch.autograd.Function):
         return dX, dy, dR, dbeta
 
 
+class _SiteGrad:
+    """Hand-over between the two backward nodes of one site (see _MeanFn)."""
+    __slots__ = ("alpha", "dh")
+
+    def __init__(self):
+        self.alpha = self.dh = None
+
+
+class _MeanFn(torch.autograd.Function):
+    """z = stream mean of X, and X itself handed on as X1 for the read and the write of the site.
+
+    The streams entering a site have three consumers (the mean for the coefficient network, the
+    read and the write); left to autograd that is three [T, n, C] gradients and two sums. Here X is
+    threaded through the site instead (X -> X1 -> read -> X2 -> write), the read's backward only
+    computes d alpha and leaves (alpha, dh) in `site`, and this node, which runs last, forms
+    dX = dX2 + alpha dh + dz / n in one pass."""
+
+    @staticmethod
+    def forward(ctx, X, site):
+        ctx.site = site
+        ctx.shape = tuple(X.shape)
+        return K.mhc_mean(X), X.view_as(X)
+
+    @staticmethod
+    def backward(ctx, dz, g):
+        site = ctx.site
+        alpha, dh = site.alpha, site.dh
+        site.alpha = site.dh = None
+        dz = dz.contiguous() if dz is not None else None
+        g = g.contiguous() if g is not None else None
+        if g is None and dh is None and dz is None:
+            return None, None
+        return K.mhc_dx_combine(g, alpha, dh, dz, ctx.shape), None
+
+
+class _ReadThreadFn(torch.autograd.Function):
+    """h = sum_i alpha_i X1_i, and X1 handed on as X2 for the write. Backward: d alpha only; the
+    gradient arriving for X2 goes back unchanged and _MeanFn adds the read's share to it."""
+
+    @staticmethod
+    def forward(ctx, X1, alpha, site):
+        alpha = alpha.float().contiguous()
+        ctx.save_for_backward(X1, alpha)
+        ctx.site = site
+        return K.mhc_read(X1, alpha), X1.view_as(X1)
+
+    @staticmethod
+    def backward(ctx, dh, g):
+        X1, alpha = ctx.saved_tensors
+        dalpha = None
+        if dh is not None:
+            dh = dh.contiguous()
+            _, _, _, dalpha, _ = K.mhc_bwd(X1, None, None, alpha, None, None, dh, want_dx=False)
+            ctx.site.alpha, ctx.site.dh = alpha, dh
+        return g, dalpha, None
+
+
 def mhc_read(X, alpha):
     if X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 4:
         return _ReadFn.apply(X, alpha)
@@ -116,12 +173,13 @@ class HyperConnection(nn.Module):
         self.static_res = nn.Parameter(torch.eye(n) * 6.0 - 3.0)   # sinkhorn(exp(.)) ~ identity
         self.dyn_scale = nn.Parameter(torch.full((3,), 0.01))
 
-    def coefficients(self, X):
+    def coefficients(self, X, z=None):
+        """z: the stream mean of X when the caller has it already (bf16 [T, C])."""
         n = self.n
         if X.is_cuda and X.dtype == torch.bfloat16 and self.coef_proj.weight.shape[0] % 8 == 0:
             # stream mean without an fp32 copy of X, then the RMSNorm and GEMM kernels of this package
             from nanoplm_b200.ops import functional as ops
-            zn = ops.norm(X.mean(dim=1), self.coef_norm_weight, self.eps, rms=True)
+            zn = ops.norm(X.mean(dim=1) if z is None else z, self.coef_norm_weight, self.eps, rms=True)
             pre = ops.linear(zn, self.coef_proj.weight)
             if n in (2, 4) and 1 <= self.iters <= 8:
                 return _CoefFn.apply(pre, self.static_alpha, self.static_beta, self.static_res, self.dyn_scale,
@@ -137,10 +195,21 @@ class HyperConnection(nn.Module):
         R = sinkhorn(self.static_res.float() + s[2] * d[:, 2 * n:].reshape(-1, n, n), self.iters)
         return alpha, beta, R
 
+    def _threaded(self, X) -> bool:
+        return (X.is_cuda and X.dtype == torch.bfloat16 and X.shape[-1] % 8 == 0 and X.shape[1] <= 4
+                and self.coef_proj.weight.shape[0] % 8 == 0 and torch.is_grad_enabled() and X.requires_grad)
+
     def read(self, X):
+        """Returns (h, state); `state` goes to `write` together with the same X."""
+        if self._threaded(X):
+            site = _SiteGrad()
+            z, X1 = _MeanFn.apply(X.contiguous(), site)
+            alpha, beta, R = self.coefficients(X1, z)
+            h, X2 = _ReadThreadFn.apply(X1, alpha, site)
+            return h, (beta, R, X2)
         alpha, beta, R = self.coefficients(X)
-        return mhc_read(X, alpha), (beta, R)
+        return mhc_read(X, alpha), (beta, R, None)
 
     def write(self, X, y, state):
-        beta, R = state
-        return mhc_write(X, y, R, beta)
+        beta, R, threaded = state
+        return mhc_write(X if threaded is None else threaded, y, R, beta)

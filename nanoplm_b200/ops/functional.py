@@ -51,7 +51,18 @@ def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
         K.gemm(dy2, x2, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=acc,
                splits=K.wgrad_splits(N, Kd, T), pair=pair)
         return acc.to(w.dtype)
-    g = dy2.float().t() @ x2.float()
+    if Kd % 64 == 0 and N < 256 and dy2.is_cuda and dy2.dtype == BF and x2.dtype == BF:
+        # narrow outputs (the 2n + n^2 coefficient projection of a hyper-connection site, a router):
+        # pad the output columns to a whole 64 so the tensor-core kernel applies instead of an fp32
+        # library GEMM over fp32 copies of both operands
+        Np = (N + 63) // 64 * 64
+        dyp = torch.zeros((T, Np), dtype=BF, device=dy2.device)
+        dyp[:, :N] = dy2
+        acc = torch.zeros((Np, Kd), dtype=torch.float32, device=w.device)
+        K.gemm(dyp, x2, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=acc, splits=K.wgrad_splits(Np, Kd, T))
+        g = acc[:N]
+    else:
+        g = dy2.float().t() @ x2.float()
     if _has_main_grad(w):
         w.main_grad.add_(g)
         return None

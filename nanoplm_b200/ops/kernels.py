@@ -537,11 +537,35 @@ def mhc_write(X, y, R, beta):
     return Xn
 
 
-def mhc_bwd(X, y, R, alpha, beta, dXn, dh):
-    """Backward of write (dXn given) and / or read (dh given). Returns (dX, dy, dR, dalpha, dbeta)."""
+def mhc_mean(X):
+    """Mean over the streams: X [T, n, C] bf16 -> [T, C]."""
+    T, n, C = X.shape
+    z = torch.empty((T, C), dtype=_BF16, device=X.device)
+    rc = lib("extras").nplm_mhc_mean(ptr(X), ptr(z), c_int(T), c_int(n), c_int(C), stream_ptr())
+    check_rc(rc, "mhc_mean")
+    count_launch()
+    return z
+
+
+def mhc_dx_combine(g, alpha, dh, dz, shape):
+    """dX = g + alpha[:, :, None] * dh[:, None, :] + dz[:, None, :] / n in one pass (any of the three
+    terms may be None); shape = (T, n, C)."""
+    T, n, C = shape
+    ref = next(t for t in (g, dh, dz) if t is not None)
+    dX = torch.empty((T, n, C), dtype=_BF16, device=ref.device)
+    rc = lib("extras").nplm_mhc_dx_combine(ptr(g), ptr(alpha), ptr(dh), ptr(dz), ptr(dX), c_int(T), c_int(n),
+                                           c_int(C), stream_ptr())
+    check_rc(rc, "mhc_dx_combine")
+    count_launch()
+    return dX
+
+
+def mhc_bwd(X, y, R, alpha, beta, dXn, dh, want_dx: bool = True):
+    """Backward of write (dXn given) and / or read (dh given). Returns (dX, dy, dR, dalpha, dbeta);
+    want_dx=False skips the dX output (only the coefficient gradients are computed)."""
     T, n, C = X.shape
     dev = X.device
-    dX = torch.empty_like(X)
+    dX = torch.empty_like(X) if want_dx else None
     dy = torch.empty((T, C), dtype=_BF16, device=dev) if dXn is not None else None
     dR = torch.empty((T, n, n), dtype=torch.float32, device=dev) if dXn is not None else None
     dbeta = torch.empty((T, n), dtype=torch.float32, device=dev) if dXn is not None else None

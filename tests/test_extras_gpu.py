@@ -300,3 +300,49 @@ def test_mhc_coefficient_kernel_matches_torch(n, iters, sharp, cuda_status):
         tol = 0.02 if name == "dpre" else 2e-3           # dpre is stored in bf16
         err = (g.float() - w.float()).abs().max().item()
         assert err <= tol * (w.abs().max().item() + 1e-3), (name, err, w.abs().max().item())
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_mhc_site_threaded_backward_matches_unthreaded(n, cuda_status):
+    """X threaded through a site (mean -> read -> write, one combined dX pass) against the same
+    site with the three consumers of X left to autograd, and against the fp32 CPU restatement."""
+    from nanoplm_b200.models.mhc import HyperConnection
+    torch.manual_seed(11)
+    T, C = 777, 256
+    hc = HyperConnection(C, n).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        hc.dyn_scale.fill_(0.3)
+    w = (torch.randn(C, C, device="cuda") * C ** -0.5).to(torch.bfloat16)
+    X0 = torch.randn(T, n, C, device="cuda").to(torch.bfloat16)
+    gout = torch.randn(T, n, C, device="cuda").to(torch.bfloat16)
+
+    def run(threaded):
+        X = X0.clone().requires_grad_(True)
+        hc.zero_grad()
+        if not threaded:
+            hc._threaded = lambda _x: False
+        else:
+            hc.__dict__.pop("_threaded", None)
+        h, state = hc.read(X)
+        assert (state[2] is not None) == threaded
+        out = hc.write(X, torch.tanh(h @ w.t()), state)
+        out.backward(gout)
+        grads = {k: p.grad.float().clone() for k, p in hc.named_parameters()}
+        return out.detach().float(), X.grad.float(), grads
+
+    out_t, dx_t, g_t = run(True)
+    out_u, dx_u, g_u = run(False)
+    hc.__dict__.pop("_threaded", None)
+    assert torch.equal(out_t, out_u)
+    assert (dx_t - dx_u).abs().max().item() < 0.03 * dx_u.abs().max().item() + 1e-3
+    for k in g_u:
+        assert (g_t[k] - g_u[k]).abs().max().item() < 0.03 * g_u[k].abs().max().item() + 2e-3, k
+    # fp32 restatement on the CPU
+    ref = HyperConnection(C, n)
+    ref.load_state_dict({k: v.float().cpu() for k, v in hc.state_dict().items()})
+    Xc = X0.float().cpu().requires_grad_(True)
+    hcpu, st = ref.read(Xc)
+    outc = ref.write(Xc, torch.tanh(hcpu @ w.float().cpu().t()), st)
+    outc.backward(gout.float().cpu())
+    assert (out_t.cpu() - outc.detach()).abs().max().item() < 0.05 * outc.abs().max().item()
+    assert (dx_t.cpu() - Xc.grad).abs().max().item() < 0.05 * Xc.grad.abs().max().item()
