@@ -79,6 +79,67 @@ dwconv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   }
 }
 
+// Same convolution with the kernel size known at compile time: a thread owns 8 channels of
+// DW_TT consecutive tokens, keeps its 8 x KS weights in registers and walks the DW_TT + KS - 1 input
+// rows once (the general kernel above re-reads KS rows and 8 x KS scalar weights per output row).
+constexpr int DW_TT = 8;
+
+template <int KS>
+__global__ void __launch_bounds__(256)
+dwconv_tile_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   const __nv_bfloat16* __restrict__ bias, const int* __restrict__ s_start,
+                   const int* __restrict__ s_end, __nv_bfloat16* __restrict__ y, int T, int C, int flip) {
+  constexpr int R = KS / 2;
+  const int vec = C >> 3;
+  const int n_tb = (T + DW_TT - 1) / DW_TT;
+  const long long total = static_cast<long long>(n_tb) * vec;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t0 = static_cast<int>(idx / vec) * DW_TT;
+    const int c = static_cast<int>(idx % vec) * 8;
+    float wt[KS][8];   // wt[k][e]: weight of tap k (already flipped for the input gradient)
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int k = 0; k < KS; ++k)
+        wt[flip ? KS - 1 - k : k][e] = __bfloat162float(w[(c + e) * KS + k]);
+    float acc[DW_TT][8];
+    int lo[DW_TT], hi[DW_TT];
+    float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (bias != nullptr && !flip) ld8(bias + c, b8);
+#pragma unroll
+    for (int i = 0; i < DW_TT; ++i) {
+      const int t = t0 + i;
+      lo[i] = t < T ? s_start[t] : 0;
+      hi[i] = t < T ? s_end[t] : 0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[i][e] = b8[e];
+    }
+    // output t0 + i takes input row src with tap k = src - (t0 + i) + R (after the flip both
+    // directions read "tap k at offset k - R")
+#pragma unroll
+    for (int j = 0; j < DW_TT + KS - 1; ++j) {
+      const int src = t0 - R + j;
+      if (src < 0 || src >= T) continue;
+      float xv[8];
+      ld8(x + static_cast<size_t>(src) * C + c, xv);
+#pragma unroll
+      for (int i = 0; i < DW_TT; ++i) {
+        const int k = j - i;   // = src - (t0 + i) + R
+        if (k >= 0 && k < KS) {
+          if (src >= lo[i] && src < hi[i]) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[i][e] += xv[e] * wt[k][e];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < DW_TT; ++i)
+      if (t0 + i < T) st8(y + static_cast<size_t>(t0 + i) * C + c, acc[i]);
+  }
+}
+
 // dw[c][k] += sum_t dy[t][c] x[t+k-r][c];  dbias[c] += sum_t dy[t][c]. One block handles a slab of
 // tokens for 32 channels x 8 token lanes and reduces through shared memory before the atomics.
 __global__ void __launch_bounds__(256)
@@ -119,6 +180,63 @@ dwconv_bwd_w_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
       for (int j = 0; j < 8; ++j) s += red[j][cl][k];
       if (k < KS) atomicAdd(&dw[c * KS + k], s);
       else if (k == MAX_KS && dbias != nullptr) atomicAdd(&dbias[c], s);
+    }
+  }
+}
+
+// Weight gradient with the kernel size known at compile time: same block shape, but a token lane
+// walks one contiguous run of the slab and keeps the KS input values around the current token in
+// registers, so a token costs one x and one dy load instead of KS + 1.
+template <int KS>
+__global__ void __launch_bounds__(256)
+dwconv_bwd_w_tile_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                         const int* __restrict__ s_start, const int* __restrict__ s_end,
+                         float* __restrict__ dw, float* __restrict__ dbias, int T, int C,
+                         int tokens_per_block) {
+  constexpr int R = KS / 2;
+  __shared__ float red[8][32][KS + 1];
+  const int cl = threadIdx.x & 31;       // channel lane
+  const int tl = threadIdx.x >> 5;       // token lane
+  const int c = blockIdx.y * 32 + cl;
+  float acc[KS + 1];
+#pragma unroll
+  for (int k = 0; k <= KS; ++k) acc[k] = 0.f;
+  const int run = (tokens_per_block + 7) / 8;
+  const int ts = blockIdx.x * tokens_per_block + tl * run;
+  const int te = min(min(T, ts + run), (static_cast<int>(blockIdx.x) + 1) * tokens_per_block);
+  if (c < C && ts < te) {
+    float win[KS];   // x[t - R .. t + R] of channel c
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+      const int src = ts - R + k;
+      win[k] = (src >= 0 && src < T) ? __bfloat162float(x[static_cast<size_t>(src) * C + c]) : 0.f;
+    }
+    for (int t = ts; t < te; ++t) {
+      const float g = __bfloat162float(dy[static_cast<size_t>(t) * C + c]);
+      const int a = s_start[t], b = s_end[t];
+      const int nsrc = t + 1 + R;
+      const float nx = nsrc < T ? __bfloat162float(x[static_cast<size_t>(nsrc) * C + c]) : 0.f;
+      acc[KS] += g;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        const int src = t + k - R;
+        if (src >= a && src < b) acc[k] += g * win[k];
+      }
+#pragma unroll
+      for (int k = 0; k + 1 < KS; ++k) win[k] = win[k + 1];
+      win[KS - 1] = nx;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k <= KS; ++k) red[tl][cl][k] = acc[k];
+  __syncthreads();
+  if (tl == 0 && c < C) {
+#pragma unroll
+    for (int k = 0; k <= KS; ++k) {
+      float sum = 0.f;
+      for (int j = 0; j < 8; ++j) sum += red[j][cl][k];
+      if (k < KS) atomicAdd(&dw[c * KS + k], sum);
+      else if (dbias != nullptr) atomicAdd(&dbias[c], sum);
     }
   }
 }
@@ -377,6 +495,21 @@ extern "C" int nplm_dwconv(const void* x, const void* w, const void* bias, const
                            const int* s_end, void* y, int T, int C, int KS, int flip, cudaStream_t st) {
   if (T <= 0) return 0;
   if ((C % 8) || KS < 1 || KS > MAX_KS || !(KS & 1)) return -3;
+  if (KS == 3 || KS == 5 || KS == 7 || KS == 9) {
+    const int grid = grid_for(static_cast<long long>((T + DW_TT - 1) / DW_TT) * (C / 8), 256);
+#define NPLM_DWCONV(KS_)                                                                                   \
+  dwconv_tile_kernel<KS_><<<grid, 256, 0, st>>>(                                                           \
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),                \
+      reinterpret_cast<const __nv_bfloat16*>(bias), s_start, s_end, reinterpret_cast<__nv_bfloat16*>(y), T, C, flip)
+    switch (KS) {
+      case 3: NPLM_DWCONV(3); break;
+      case 5: NPLM_DWCONV(5); break;
+      case 7: NPLM_DWCONV(7); break;
+      default: NPLM_DWCONV(9); break;
+    }
+#undef NPLM_DWCONV
+    return static_cast<int>(cudaGetLastError());
+  }
   dwconv_kernel<<<grid_for(static_cast<long long>(T) * (C / 8), 256), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
       reinterpret_cast<const __nv_bfloat16*>(bias), s_start, s_end, reinterpret_cast<__nv_bfloat16*>(y), T, C,
@@ -390,6 +523,20 @@ extern "C" int nplm_dwconv_bwd_w(const void* x, const void* dy, const int* s_sta
   if (KS < 1 || KS > MAX_KS || !(KS & 1)) return -3;
   const int tokens_per_block = 512;
   dim3 grid((T + tokens_per_block - 1) / tokens_per_block, (C + 31) / 32);
+  if (KS == 3 || KS == 5 || KS == 7 || KS == 9) {
+#define NPLM_DWCONV_W(KS_)                                                                              \
+  dwconv_bwd_w_tile_kernel<KS_><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x),          \
+                                                      reinterpret_cast<const __nv_bfloat16*>(dy), s_start, \
+                                                      s_end, dw, dbias, T, C, tokens_per_block)
+    switch (KS) {
+      case 3: NPLM_DWCONV_W(3); break;
+      case 5: NPLM_DWCONV_W(5); break;
+      case 7: NPLM_DWCONV_W(7); break;
+      default: NPLM_DWCONV_W(9); break;
+    }
+#undef NPLM_DWCONV_W
+    return static_cast<int>(cudaGetLastError());
+  }
   dwconv_bwd_w_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x),
                                             reinterpret_cast<const __nv_bfloat16*>(dy), s_start, s_end, dw,
                                             dbias, T, C, KS, tokens_per_block);
