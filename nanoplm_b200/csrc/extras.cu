@@ -97,12 +97,26 @@ dwconv_tile_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int t0 = static_cast<int>(idx / vec) * DW_TT;
     const int c = static_cast<int>(idx % vec) * 8;
+    // all loads of the thread are issued before the first use: DW_TT + KS - 1 input rows (16 bytes
+    // each, zero outside the tensor) and the 8 x KS weights, which are contiguous in w[C][KS]
+    uint4 xr[DW_TT + KS - 1];
+#pragma unroll
+    for (int j = 0; j < DW_TT + KS - 1; ++j) {
+      const int src = t0 - R + j;
+      xr[j] = (src >= 0 && src < T) ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(src) * C + c))
+                                    : make_uint4(0u, 0u, 0u, 0u);
+    }
+    uint4 wr[KS];      // 8 channels x KS taps = 8 * KS bf16 = KS 16-byte words (c is a multiple of 8)
+#pragma unroll
+    for (int q = 0; q < KS; ++q) wr[q] = __ldg(reinterpret_cast<const uint4*>(w + static_cast<size_t>(c) * KS) + q);
     float wt[KS][8];   // wt[k][e]: weight of tap k (already flipped for the input gradient)
+    {
+      const __nv_bfloat16* wl = reinterpret_cast<const __nv_bfloat16*>(wr);
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
+      for (int e = 0; e < 8; ++e)
 #pragma unroll
-      for (int k = 0; k < KS; ++k)
-        wt[flip ? KS - 1 - k : k][e] = __bfloat162float(w[(c + e) * KS + k]);
+        for (int k = 0; k < KS; ++k) wt[k][e] = __bfloat162float(wl[e * KS + (flip ? KS - 1 - k : k)]);
+    }
     float acc[DW_TT][8];
     int lo[DW_TT], hi[DW_TT];
     float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -116,21 +130,19 @@ dwconv_tile_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       for (int e = 0; e < 8; ++e) acc[i][e] = b8[e];
     }
     // output t0 + i takes input row src with tap k = src - (t0 + i) + R (after the flip both
-    // directions read "tap k at offset k - R")
+    // directions read "tap k at offset k - R"); rows outside [lo, hi) belong to another sequence
 #pragma unroll
     for (int j = 0; j < DW_TT + KS - 1; ++j) {
       const int src = t0 - R + j;
-      if (src < 0 || src >= T) continue;
       float xv[8];
-      ld8(x + static_cast<size_t>(src) * C + c, xv);
+      unpack8x(xr[j], xv);
 #pragma unroll
       for (int i = 0; i < DW_TT; ++i) {
         const int k = j - i;   // = src - (t0 + i) + R
         if (k >= 0 && k < KS) {
-          if (src >= lo[i] && src < hi[i]) {
+          const float m = (src >= lo[i] && src < hi[i]) ? 1.f : 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[i][e] += xv[e] * wt[k][e];
-          }
+          for (int e = 0; e < 8; ++e) acc[i][e] += m * xv[e] * wt[k][e];
         }
       }
     }
@@ -495,7 +507,8 @@ extern "C" int nplm_dwconv(const void* x, const void* w, const void* bias, const
                            const int* s_end, void* y, int T, int C, int KS, int flip, cudaStream_t st) {
   if (T <= 0) return 0;
   if ((C % 8) || KS < 1 || KS > MAX_KS || !(KS & 1)) return -3;
-  if (KS == 3 || KS == 5 || KS == 7 || KS == 9) {
+  const bool aligned = ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
+  if ((KS == 3 || KS == 5 || KS == 7 || KS == 9) && aligned) {   // the tile kernel loads 16-byte words of w
     const int grid = grid_for(static_cast<long long>((T + DW_TT - 1) / DW_TT) * (C / 8), 256);
 #define NPLM_DWCONV(KS_)                                                                                   \
   dwconv_tile_kernel<KS_><<<grid, 256, 0, st>>>(                                                           \
