@@ -131,13 +131,15 @@ def bench_attn(T, peaks):
         flash_attn_varlen_func = None
     for window in (-1, 64):
         fwd_flops = 4.0 * flops_pairs[window] * D * H
-        ms = time_fn(lambda: k.fa_fwd(qkv, ss, se, H, D, window, 0.125), flush=flush)
-        print(json.dumps({"kernel": "fa_varlen_fwd", "window": window, "T": T, "ms": round(ms, 4),
-                          "tflops": round(fwd_flops / ms / 1e9, 1)}))
+        for impl in ("ws", "single"):
+            ms = time_fn(lambda: k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl=impl), flush=flush)
+            print(json.dumps({"kernel": "fa_varlen_fwd", "impl": impl, "window": window, "T": T,
+                              "ms": round(ms, 4), "tflops": round(fwd_flops / ms / 1e9, 1)}), flush=True)
         out, lse = k.fa_fwd(qkv, ss, se, H, D, window, 0.125)
-        ms = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125), flush=flush)
-        print(json.dumps({"kernel": "fa_varlen_bwd", "window": window, "T": T, "ms": round(ms, 4),
-                          "tflops": round(2.5 * fwd_flops / ms / 1e9, 1)}))
+        for impl in ("ws", "single"):
+            ms = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl=impl), flush=flush)
+            print(json.dumps({"kernel": "fa_varlen_bwd", "impl": impl, "window": window, "T": T,
+                              "ms": round(ms, 4), "tflops": round(2.5 * fwd_flops / ms / 1e9, 1)}), flush=True)
         if flash_attn_varlen_func is not None:
             q, kk, v = qkv.view(T, 3, H, D).unbind(1)
             q = q.contiguous().requires_grad_(True)

@@ -265,6 +265,7 @@ class DistillationConfig:
     teacher: TeacherConfig = field(default_factory=TeacherConfig)
     teacher_random_init: bool = False    # benchmarks: random-init frozen teacher instead of HF weights
     max_grad_norm: float = 1.0
+    fused_comm: bool = True              # P2P-fused optimizer step on multi-GPU NVLink nodes
 
     def __post_init__(self) -> None:
         if isinstance(self.teacher, dict):

@@ -1138,6 +1138,18 @@ static int fa_make_map(CUtensorMap* map, const void* base, uint64_t cols, uint64
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// cudaFuncSetAttribute applies to the current device only: one flag per device ordinal. Returns the
+// slot of the current device (or a negative / CUDA error code).
+constexpr int FA_MAX_DEVICES = 64;
+static bool fa_fwd_configured[FA_MAX_DEVICES];
+static bool fa_bwd_configured[FA_MAX_DEVICES];
+
+static int fa_current_device(int* dev) {
+  NPLM_CUDA_CHECK(cudaGetDevice(dev));
+  if (*dev < 0 || *dev >= FA_MAX_DEVICES) return -4;
+  return 0;
+}
+
 }  // namespace nplm
 
 using namespace nplm;
@@ -1158,16 +1170,18 @@ extern "C" int nplm_fa_fwd(const void* qkv, void* out, float* lse, const int* se
   CUtensorMap tm;
   int rc = fa_make_map(&tm, qkv, static_cast<uint64_t>(3) * H * D, T);
   if (rc) return rc;
-  static bool configured = false;
+  int dev = 0;
+  rc = fa_current_device(&dev);
+  if (rc) return rc;
   static int force = 0;  // NPLM_FA_FWD_KERNEL=1 / 2 pins one generation (benchmarks)
-  if (!configured) {
+  if (!fa_fwd_configured[dev]) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FA_FWD_SMEM));
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FA_FWD_SMEM));
     const char* env = getenv("NPLM_FA_FWD_KERNEL");
     if (env != nullptr && (env[0] == '1' || env[0] == '2')) force = env[0] - '0';
-    configured = true;
+    fa_fwd_configured[dev] = true;
   }
   FaFwdArgs a;
   a.out = reinterpret_cast<__nv_bfloat16*>(out);
@@ -1220,13 +1234,15 @@ extern "C" int nplm_fa_bwd_rope(const void* qkv, const void* out, const void* do
   if (rc) return rc;
   rc = fa_make_map(&tmDO, dout, static_cast<uint64_t>(H) * D, T);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
+  int dev = 0;
+  rc = fa_current_device(&dev);
+  if (rc) return rc;
+  if (!fa_bwd_configured[dev]) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FA_BWD_SMEM));
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FA_BWD_SMEM));
-    configured = true;
+    fa_bwd_configured[dev] = true;
   }
   const int HD = H * D;
   NPLM_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * HD * sizeof(float), st));

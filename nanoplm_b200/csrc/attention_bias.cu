@@ -326,7 +326,10 @@ static AbEncodeFn ab_encode_fn() {
 template <int D, int KC>
 static int ab_launch(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const AbArgs& a, cudaStream_t st) {
   constexpr int smem = ab_smem_bytes<D, KC>();
-  static bool configured = false;
+  static bool configured_on[nplm::MAX_DEVICES];
+  const int dev_slot = nplm::current_device_slot();
+  if (dev_slot < 0) return -4;
+  bool& configured = configured_on[dev_slot];
   if (!configured) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bias_fwd_kernel<D, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;

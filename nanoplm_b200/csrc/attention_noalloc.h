@@ -18,7 +18,10 @@
 //
 // The first call on a device looks up the device address of the array (cudaGetSymbolAddress) for
 // that device; make that first call before starting any stream capture. The call itself performs
-// no cudaMalloc / cudaFree and uses no allocating library routine.
+// no cudaMalloc / cudaFree and uses no allocating library routine. The device is taken from
+// cudaGetDevice(), not from the stream: the current device must be the one that owns `stream` and
+// the tensors. The per-device address cache is filled without a lock; two host threads that make the
+// first call on one device at the same time both store the same value, which is harmless.
 //
 // All calls on a device share the one array and it keeps whatever the previous call left in it.
 // The function clears the part that must start at zero on the caller's stream before using it.

@@ -1,0 +1,1074 @@
+// Warp-specialised varlen (cu_seqlens) flash attention for sm_100a, head_dim 64, non-causal,
+// optional symmetric sliding window, on packed activations qkv[T][3][H][64] (bf16).
+//
+// Same interface, tiling of the FLAT token axis and mask semantics as attention.cu (the kernels
+// there stay available as the single-role form); what differs is how an SM is kept busy:
+//
+//   * persistent: one CTA per SM walks a static list of work items (256 query tokens x 1 head),
+//     so barrier / TMEM set-up happens once and the loads of item i+1 are in flight while item i
+//     is still in its softmax;
+//   * roles: two softmax warpgroups own one 128-row query tile each; in a third warpgroup one warp
+//     issues every TMA load and one every tcgen05.mma (that warpgroup gives most of its registers
+//     to the softmax warpgroups with setmaxnreg). The two tiles share the K / V tiles of the
+//     item, and their score / output accumulators (S0, S1, O0, O1) are all resident in TMEM, so
+//     the tensor pipe works on one tile's QK^T or PV while the other tile is in its exponentials;
+//   * a softmax warpgroup copies its score tile to registers, hands the TMEM tile straight back
+//     (the next QK^T runs under this tile's exponentials), and only rescales its output
+//     accumulator when the running maximum grew by more than 2^8.
+//
+// Replaces flash_attn_varlen_func as called by the reference
+// (src/nanoplm/pretraining/models/modern_bert/modeling.py:331-366) with window (-1,-1) or (64,64).
+#include "common.cuh"
+
+namespace nplm {
+
+constexpr int FA_T = 128;                       // tile of tokens (queries and keys)
+constexpr int FA_D = 64;                        // head dim
+constexpr int FA_TILE_BYTES = FA_T * FA_D * 2;  // 16 KB
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t swz(int r, int chunk) {
+  return static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4));
+}
+
+struct FaWsArgs {
+  __nv_bfloat16* out;   // [T][H*64]
+  float* lse;           // [H][T] natural-log LSE of the scaled scores
+  const int* seq_start;
+  const int* seq_end;
+  int T, H, window;     // window < 0: unlimited
+  float scale;
+  int* status;
+};
+
+constexpr int WS_KV_STAGES = 3;
+constexpr int WS_THREADS = 384;   // 2 softmax warpgroups (warps 0-7), then loader warp 8, MMA warp 9, 2 idle warps
+constexpr int WS_LOADER_WARP = 8, WS_MMA_WARP = 9;
+// setmaxnreg: the loader / MMA warpgroup drops to WS_REGS_LIGHT registers per thread, the two
+// compute warpgroups grow to WS_REGS_HEAVY. The increase BLOCKS until the CTA's register pool holds
+// enough, and the pool is what the launch allocated (168 per thread at 384 threads, the most three
+// warps per scheduler can get), not the whole register file: the sum must fit or the kernel hangs.
+constexpr int WS_REGS_LAUNCH = 168, WS_REGS_LIGHT = 72, WS_REGS_HEAVY = 216;
+static_assert(128 * WS_REGS_LIGHT + 256 * WS_REGS_HEAVY <= WS_THREADS * WS_REGS_LAUNCH,
+              "setmaxnreg.inc would wait forever for registers the CTA does not own");
+static_assert(WS_REGS_LIGHT % 8 == 0 && WS_REGS_HEAVY % 8 == 0, "setmaxnreg takes multiples of 8");
+// Q: 2 buffers x 2 tiles; K, V: WS_KV_STAGES tiles each; P: 2 tiles x 2 column blocks
+constexpr int WS_OFF_Q = 0;
+constexpr int WS_OFF_K = WS_OFF_Q + 4 * FA_TILE_BYTES;
+constexpr int WS_OFF_V = WS_OFF_K + WS_KV_STAGES * FA_TILE_BYTES;
+constexpr int WS_OFF_P = WS_OFF_V + WS_KV_STAGES * FA_TILE_BYTES;
+constexpr int WS_OFF_BAR = WS_OFF_P + 4 * FA_TILE_BYTES;
+constexpr int WS_FWD_SMEM = WS_OFF_BAR + 512;
+
+// Key-tile geometry of one work item: query tiles i = 0, 1 cover tokens [t0 + 128 i, +128); the
+// item walks key tiles j = 0 .. n-1 starting at kv_lo, and tile i takes part in j in [a[i], b[i]).
+struct WsGeo {
+  int t0, kv_lo, n;
+  int a[2], b[2];
+};
+
+__device__ __forceinline__ WsGeo ws_geometry(const FaWsArgs& args, int pair) {
+  WsGeo g;
+  const int T = args.T, w = args.window;
+  g.t0 = pair * 2 * FA_T;
+  int lo[2] = {0, 0}, hi[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int first = g.t0 + i * FA_T;
+    if (first < T) {
+      const int last = min(first + FA_T - 1, T - 1);
+      lo[i] = __ldg(args.seq_start + first);
+      hi[i] = __ldg(args.seq_end + last);
+      if (w >= 0) {
+        lo[i] = max(lo[i], first - w);
+        hi[i] = min(hi[i], last + w + 1);
+      }
+    }
+  }
+  g.kv_lo = lo[0];
+  const int kv_hi = max(hi[0], hi[1]);
+  g.n = kv_hi > g.kv_lo ? (kv_hi - g.kv_lo + FA_T - 1) / FA_T : 0;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (hi[i] > lo[i]) {
+      g.a[i] = (lo[i] - g.kv_lo) / FA_T;
+      g.b[i] = (hi[i] - g.kv_lo + FA_T - 1) / FA_T;
+    } else {
+      g.a[i] = g.b[i] = 0;
+    }
+  }
+  return g;
+}
+
+__global__ void __launch_bounds__(WS_THREADS, 1)
+fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
+    return;
+  }
+  uint8_t* sQ = smem + WS_OFF_Q;   // [buf][tile]
+  uint8_t* sK = smem + WS_OFF_K;
+  uint8_t* sV = smem + WS_OFF_V;
+  uint8_t* sP = smem + WS_OFF_P;   // [tile][column block][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WS_OFF_BAR);
+  uint64_t* q_full = bars;                       // [2]
+  uint64_t* q_empty = bars + 2;                  // [2]
+  uint64_t* k_full = bars + 4;                   // [WS_KV_STAGES]
+  uint64_t* k_empty = k_full + WS_KV_STAGES;
+  uint64_t* v_full = k_empty + WS_KV_STAGES;
+  uint64_t* v_empty = v_full + WS_KV_STAGES;
+  uint64_t* s_full = v_empty + WS_KV_STAGES;     // [2] per query tile
+  uint64_t* s_free = s_full + 2;
+  uint64_t* p_ready = s_free + 2;
+  uint64_t* pv_done = p_ready + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int T = args.T, H = args.H;
+  const int HD = H * FA_D;
+  const int n_items = ((T + 2 * FA_T - 1) / (2 * FA_T)) * H;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);      // one lane of each softmax warp
+      mbar_init(&p_ready[i], 128);   // every thread of the warpgroup, after its own proxy fence
+      mbar_init(&pv_done[i], 1);
+    }
+    for (int i = 0; i < WS_KV_STAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmQKV);
+  }
+  if (warp == WS_MMA_WARP) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // columns: S0 [0,128), S1 [128,256), O0 [256,320), O1 [320,384)
+
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_REGS_LIGHT));
+  if (warp == WS_LOADER_WARP) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0) {
+      uint32_t qc = 0, kc = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const int h = item % H;
+        const WsGeo g = ws_geometry(args, item / H);
+        const int colQ = h * FA_D, colK = HD + h * FA_D, colV = 2 * HD + h * FA_D;
+        const uint32_t qb = qc & 1u;
+        if (!mbar_wait(&q_empty[qb], ((qc >> 1) & 1u) ^ 1u)) { ok = false; break; }
+        const int nq = (g.b[0] > g.a[0] ? 1 : 0) + (g.b[1] > g.a[1] ? 1 : 0);
+        mbar_arrive_expect_tx(&q_full[qb], nq * FA_TILE_BYTES);
+        if (g.b[0] > g.a[0]) tma_load_2d(sQ + (qb * 2 + 0) * FA_TILE_BYTES, &tmQKV, &q_full[qb], colQ, g.t0);
+        if (g.b[1] > g.a[1]) tma_load_2d(sQ + (qb * 2 + 1) * FA_TILE_BYTES, &tmQKV, &q_full[qb], colQ, g.t0 + FA_T);
+        for (int j = 0; j < g.n; ++j, ++kc) {
+          const uint32_t st = kc % WS_KV_STAGES, ph = (kc / WS_KV_STAGES) & 1u;
+          const int kv0 = g.kv_lo + j * FA_T;
+          if (!mbar_wait(&k_empty[st], ph ^ 1u)) { ok = false; break; }
+          mbar_arrive_expect_tx(&k_full[st], FA_TILE_BYTES);
+          tma_load_2d(sK + st * FA_TILE_BYTES, &tmQKV, &k_full[st], colK, kv0);
+          if (!mbar_wait(&v_empty[st], ph ^ 1u)) { ok = false; break; }
+          mbar_arrive_expect_tx(&v_full[st], FA_TILE_BYTES);
+          tma_load_2d(sV + st * FA_TILE_BYTES, &tmQKV, &v_full[st], colV, kv0);
+        }
+        ++qc;
+        if (*abort_flag) ok = false;
+      }
+      if (!ok && *abort_flag == 0) {
+        atomicExch(args.status, ST_TIMEOUT_EMPTY);
+        *abort_flag = 1;
+      }
+    }
+  } else if (warp == WS_MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
+      uint32_t qc = 0, kc = 0;
+      uint32_t s_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
+      bool ok = true;
+      int why = ST_TIMEOUT_FULL;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const WsGeo g = ws_geometry(args, item / H);
+        const uint32_t qb = qc & 1u;
+        if (!mbar_wait(&q_full[qb], (qc >> 1) & 1u)) { ok = false; break; }
+        for (int j = 0; j <= g.n && ok; ++j) {
+          if (j < g.n) {   // scores of key tile j
+            const uint32_t st = (kc + j) % WS_KV_STAGES, ph = ((kc + j) / WS_KV_STAGES) & 1u;
+            if (!mbar_wait(&k_full[st], ph)) { ok = false; break; }
+            const uint32_t ka = smem_u32(sK + st * FA_TILE_BYTES);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              if (j < g.a[i] || j >= g.b[i]) continue;
+              // the warpgroup holds the previous score tile in registers
+              if (!mbar_wait(&s_free[i], (s_cnt[i] & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
+              tc_fence_after();
+              const uint32_t qa = smem_u32(sQ + (qb * 2 + i) * FA_TILE_BYTES);
+              const uint32_t tS = tmem_base + i * 128;
+#pragma unroll
+              for (int k = 0; k < FA_D / 16; ++k)
+                umma_bf16(tS, make_smem_desc(qa + k * 32, 16, 1024), make_smem_desc(ka + k * 32, 16, 1024),
+                          idesc_s, k > 0 ? 1u : 0u);
+              umma_commit(&s_full[i]);
+              ++s_cnt[i];
+            }
+            if (!ok) break;
+            umma_commit(&k_empty[st]);
+            if (j == g.n - 1) umma_commit(&q_empty[qb]);
+          }
+          if (j >= 1) {    // output update with key tile j - 1
+            const int jj = j - 1;
+            const uint32_t st = (kc + jj) % WS_KV_STAGES, ph = ((kc + jj) / WS_KV_STAGES) & 1u;
+            if (!mbar_wait(&v_full[st], ph)) { ok = false; break; }
+            const uint32_t va = smem_u32(sV + st * FA_TILE_BYTES);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              if (jj < g.a[i] || jj >= g.b[i]) continue;
+              if (!mbar_wait(&p_ready[i], p_cnt[i] & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
+              tc_fence_after();
+              const uint32_t pa = smem_u32(sP + i * 2 * FA_TILE_BYTES);
+              const uint32_t tO = tmem_base + 256 + i * 64;
+#pragma unroll
+              for (int k = 0; k < FA_T / 16; ++k)
+                umma_bf16(tO, make_smem_desc(pa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                          make_smem_desc(va + k * 2048, 8192, 1024), idesc_o, (jj > g.a[i] || k > 0) ? 1u : 0u);
+              umma_commit(&pv_done[i]);
+              ++p_cnt[i];
+            }
+            if (!ok) break;
+            umma_commit(&v_empty[st]);
+          }
+        }
+        kc += g.n;
+        ++qc;
+        if (*abort_flag) ok = false;
+      }
+      if (!ok && *abort_flag == 0) {
+        atomicExch(args.status, why);
+        *abort_flag = 1;
+      }
+    }
+  }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WS_REGS_HEAVY));
+    const int i = warp >> 2;                // query tile of this warpgroup
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may access
+    const int row_local = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + i * 128 + lane_addr;
+    const uint32_t tO = tmem_base + 256 + i * 64 + lane_addr;
+    uint8_t* sPi = sP + i * 2 * FA_TILE_BYTES;
+    const float sl2 = args.scale * LOG2E;
+    const uint32_t NEG_INF = 0xff800000u;
+    const int w = args.window;
+    uint32_t s_cnt = 0, pv_cnt = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int h = item % H;
+      const WsGeo g = ws_geometry(args, item / H);
+      if (g.b[i] <= g.a[i]) continue;
+      const int row = g.t0 + i * FA_T + row_local;
+      const bool row_ok = row < T;
+      int lo = 0, hi = 0;  // this row attends to keys [lo, hi)
+      if (row_ok) {
+        lo = __ldg(args.seq_start + row);
+        hi = __ldg(args.seq_end + row);
+        if (w >= 0) {
+          lo = max(lo, row - w);
+          hi = min(hi, row + w + 1);
+        }
+      }
+      float m_used = -1e30f, l_run = 0.f;
+      for (int j = g.a[i]; j < g.b[i]; ++j) {
+        const int kv0 = g.kv_lo + j * FA_T;
+        ok = mbar_wait(&s_full[i], s_cnt & 1u);
+        ++s_cnt;
+        ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+        if (!ok) break;
+        tc_fence_after();
+        const bool none = (kv0 + FA_T <= lo) || (kv0 >= hi);
+        const bool warp_none = __all_sync(0xffffffffu, none);
+        uint32_t r[FA_T];
+        if (!warp_none) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+          tmem_ld_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[i]);   // the score tile may be overwritten
+
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (!warp_none) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int c_lo = kv0 + c * 32, c_hi = c_lo + 32;
+            if (!(c_lo >= lo && c_hi <= hi)) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int col = c_lo + e;
+                if (!(col >= lo && col < hi)) r[c * 32 + e] = NEG_INF;
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(r[c * 32 + e]));
+          }
+        }
+        const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        const float m_new = fmaxf(m_used, tmax);
+        const bool warp_need = __any_sync(0xffffffffu, (m_new - m_used) * sl2 > 8.f);
+        float alpha = 1.f;
+        if (warp_need) {
+          alpha = exp2f((m_used - m_new) * sl2);
+          m_used = m_new;
+        }
+        if (j > g.a[i]) {
+          // the previous output update has finished: the P tile is free and O may be rescaled
+          ok = mbar_wait(&pv_done[i], pv_cnt & 1u);
+          ++pv_cnt;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          if (warp_need) {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              uint32_t o[32];
+              tmem_ld32(tO + hlf * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(tO + hlf * 32, o);
+            }
+            tmem_st_wait();
+          }
+        }
+        l_run *= alpha;
+
+        const float moff = m_used * sl2;
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!warp_none) {
+#pragma unroll
+          for (int c8 = 0; c8 < 16; ++c8) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float p0 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q]), sl2, -moff));
+              const float p1 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q + 1]), sl2, -moff));
+              ps[q] += p0 + p1;
+              pk[q] = pack_bf16x2(p0, p1);
+            }
+            *reinterpret_cast<uint4*>(sPi + (c8 >> 3) * FA_TILE_BYTES + swz(row_local, c8 & 7)) =
+                make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+        } else {
+#pragma unroll
+          for (int c8 = 0; c8 < 16; ++c8)
+            *reinterpret_cast<uint4*>(sPi + (c8 >> 3) * FA_TILE_BYTES + swz(row_local, c8 & 7)) =
+                make_uint4(0u, 0u, 0u, 0u);
+        }
+        l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&p_ready[i]);
+      }
+      if (!ok) break;
+      // last output update of this item
+      ok = mbar_wait(&pv_done[i], pv_cnt & 1u);
+      ++pv_cnt;
+      ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = args.out + static_cast<size_t>(row) * HD + h * FA_D;
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        uint32_t o[32];
+        tmem_ld32(tO + hlf * 32, o);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 u;
+            uint32_t* p = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              p[q] = pack_bf16x2(__uint_as_float(o[e + 2 * q]) * inv, __uint_as_float(o[e + 2 * q + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + hlf * 32 + e) = u;
+          }
+        }
+      }
+      tc_fence_before();
+      if (row_ok)
+        args.lse[static_cast<size_t>(h) * T + row] = l_run > 0.f ? m_used * args.scale + __logf(l_run) : 0.f;
+    }
+    if (!ok && lane == 0 && *abort_flag == 0) {
+      atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WS_MMA_WARP) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------- backward
+// One work item = one 128-key tile of one head; the item streams the query tiles that can see it.
+// Every thread of the two compute warpgroups owns one query row of the current tile (row
+// statistics lse / delta and the row's key range are plain registers); warpgroup g handles key
+// columns [64 g, 64 g + 64) of S = Q K^T and dP = dO V^T (TMEM, [query lanes][key columns]).
+//   P = exp2(S * scale * log2e - lse * log2e) inside the row's key range, dS = P (dP - delta)
+//   -> bf16 tiles [query rows][key columns] in shared memory ->
+//   dV += P^T dO, dK += dS^T Q (TMEM-resident across the item), dQ = dS K (read back by the
+//   compute warpgroups one step later and added to the fp32 dq accumulator with vector atomics).
+// The loader runs ahead by up to three query tiles and one key tile; S / dP of step j + 1 are
+// issued as soon as the warpgroups hold step j in registers.
+struct FaWsBwdArgs {
+  __nv_bfloat16* dqkv;   // [T][3][H][64]: the kernel writes the dK and dV parts
+  float* dq_acc;         // [T][H*64] fp32, zero-initialised by the caller
+  const float* lse;      // [H][T]
+  const float* delta;    // [H][T]
+  const int* seq_start;
+  const int* seq_end;
+  int T, H, window;
+  float scale;
+  int* status;
+  const int* rope_pos;   // optional: q / k were rotated before the forward pass
+  const float* rope_cos; // [max_pos][32]
+  const float* rope_sin;
+};
+
+constexpr int WSB_Q_STAGES = 3;
+constexpr int WSB_OFF_K = 0;                                   // [2]
+constexpr int WSB_OFF_V = WSB_OFF_K + 2 * FA_TILE_BYTES;       // [2]
+constexpr int WSB_OFF_Q = WSB_OFF_V + 2 * FA_TILE_BYTES;       // [WSB_Q_STAGES]
+constexpr int WSB_OFF_DO = WSB_OFF_Q + WSB_Q_STAGES * FA_TILE_BYTES;
+constexpr int WSB_OFF_P = WSB_OFF_DO + WSB_Q_STAGES * FA_TILE_BYTES;   // [2 key blocks][128 q rows][128 B]
+constexpr int WSB_OFF_DS = WSB_OFF_P + 2 * FA_TILE_BYTES;
+constexpr int WSB_OFF_BAR = WSB_OFF_DS + 2 * FA_TILE_BYTES;
+constexpr int WS_BWD_SMEM = WSB_OFF_BAR + 512;
+
+struct WsBwdGeo {
+  int kv0, q_lo, q_hi, n_q;
+};
+
+__device__ __forceinline__ WsBwdGeo ws_bwd_geometry(const FaWsBwdArgs& args, int kt) {
+  WsBwdGeo g;
+  const int T = args.T, w = args.window;
+  g.kv0 = kt * FA_T;
+  const int last = min(g.kv0 + FA_T - 1, T - 1);
+  g.q_lo = __ldg(args.seq_start + g.kv0);
+  g.q_hi = __ldg(args.seq_end + last);
+  if (w >= 0) {
+    g.q_lo = max(g.q_lo, g.kv0 - w);
+    g.q_hi = min(g.q_hi, last + w + 1);
+  }
+  g.n_q = g.q_hi > g.q_lo ? (g.q_hi - g.q_lo + FA_T - 1) / FA_T : 0;
+  return g;
+}
+
+__global__ void __launch_bounds__(WS_THREADS, 1)
+fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                 const FaWsBwdArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
+    return;
+  }
+  uint8_t* sK = smem + WSB_OFF_K;
+  uint8_t* sV = smem + WSB_OFF_V;
+  uint8_t* sQ = smem + WSB_OFF_Q;
+  uint8_t* sdO = smem + WSB_OFF_DO;
+  uint8_t* sP = smem + WSB_OFF_P;
+  uint8_t* sdS = smem + WSB_OFF_DS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WSB_OFF_BAR);
+  uint64_t* kv_full = bars;                        // [2]
+  uint64_t* kv_empty = bars + 2;                   // [2]
+  uint64_t* qdo_full = bars + 4;                   // [WSB_Q_STAGES]
+  uint64_t* qdo_empty = qdo_full + WSB_Q_STAGES;
+  uint64_t* sdp_full = qdo_empty + WSB_Q_STAGES;   // S and dP of a step are in TMEM
+  uint64_t* sdp_free = sdp_full + 1;               // the warpgroups hold them in registers
+  uint64_t* pds_ready = sdp_free + 1;              // P and dS of a step are in shared memory
+  uint64_t* g_done = pds_ready + 1;                // dV, dK, dQ of a step have finished
+  uint64_t* dq_free = g_done + 1;                  // the dQ tile has been read back
+  uint64_t* acc_free = dq_free + 1;                // dK / dV of the previous item have been read back
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int T = args.T, H = args.H;
+  const int HD = H * FA_D;
+  const int n_items = ((T + FA_T - 1) / FA_T) * H;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < WSB_Q_STAGES; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, 8);       // one lane of each compute warp
+    mbar_init(pds_ready, 256);    // every compute thread, after its own proxy fence
+    mbar_init(g_done, 1);
+    mbar_init(dq_free, 8);
+    mbar_init(acc_free, 8);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmQKV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == WS_MMA_WARP) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;          // S   [q][kv] 128 columns
+  const uint32_t tdP = tmem_base + 128;   // dP  [q][kv] 128 columns
+  const uint32_t tdQ = tmem_base + 256;   // dQ  [q][d]   64 columns
+  const uint32_t tdK = tmem_base + 320;   // dK  [kv][d]  64 columns
+  const uint32_t tdV = tmem_base + 384;   // dV  [kv][d]  64 columns
+
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_REGS_LIGHT));
+  if (warp == WS_LOADER_WARP) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0) {
+      uint32_t ic = 0, qc = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
+        const int h = item % H;
+        const WsBwdGeo g = ws_bwd_geometry(args, item / H);
+        const uint32_t kb = ic & 1u;
+        if (!mbar_wait(&kv_empty[kb], ((ic >> 1) & 1u) ^ 1u)) { ok = false; break; }
+        mbar_arrive_expect_tx(&kv_full[kb], 2 * FA_TILE_BYTES);
+        tma_load_2d(sK + kb * FA_TILE_BYTES, &tmQKV, &kv_full[kb], HD + h * FA_D, g.kv0);
+        tma_load_2d(sV + kb * FA_TILE_BYTES, &tmQKV, &kv_full[kb], 2 * HD + h * FA_D, g.kv0);
+        for (int j = 0; j < g.n_q; ++j, ++qc) {
+          const uint32_t st = qc % WSB_Q_STAGES, ph = (qc / WSB_Q_STAGES) & 1u;
+          if (!mbar_wait(&qdo_empty[st], ph ^ 1u)) { ok = false; break; }
+          mbar_arrive_expect_tx(&qdo_full[st], 2 * FA_TILE_BYTES);
+          tma_load_2d(sQ + st * FA_TILE_BYTES, &tmQKV, &qdo_full[st], h * FA_D, g.q_lo + j * FA_T);
+          tma_load_2d(sdO + st * FA_TILE_BYTES, &tmDO, &qdo_full[st], h * FA_D, g.q_lo + j * FA_T);
+        }
+        if (*abort_flag) ok = false;
+      }
+      if (!ok && *abort_flag == 0) {
+        atomicExch(args.status, ST_TIMEOUT_EMPTY);
+        *abort_flag = 1;
+      }
+    }
+  } else if (warp == WS_MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, 1, 1);   // A MN-major, B MN-major
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, 0, 1);  // A K-major, B MN-major
+      uint32_t ic = 0, qc = 0;       // items, query steps started so far
+      uint32_t c_sdp = 0, c_pds = 0, c_dq = 0;
+      bool ok = true;
+      int why = ST_TIMEOUT_FULL;
+      const uint32_t pa = smem_u32(sP), sa = smem_u32(sdS);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
+        const WsBwdGeo g = ws_bwd_geometry(args, item / H);
+        const uint32_t kb = ic & 1u;
+        if (!mbar_wait(&kv_full[kb], (ic >> 1) & 1u)) { ok = false; break; }
+        const uint32_t ka = smem_u32(sK + kb * FA_TILE_BYTES), va = smem_u32(sV + kb * FA_TILE_BYTES);
+        auto issue_sdp = [&](uint32_t step) -> bool {
+          const uint32_t st = step % WSB_Q_STAGES, ph = (step / WSB_Q_STAGES) & 1u;
+          if (!mbar_wait(&qdo_full[st], ph)) return false;
+          if (!mbar_wait(sdp_free, (c_sdp & 1u) ^ 1u)) { why = ST_TIMEOUT_TMEM_EMPTY; return false; }
+          tc_fence_after();
+          const uint32_t qa = smem_u32(sQ + st * FA_TILE_BYTES), da = smem_u32(sdO + st * FA_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < FA_D / 16; ++k)
+            umma_bf16(tS, make_smem_desc(qa + k * 32, 16, 1024), make_smem_desc(ka + k * 32, 16, 1024),
+                      idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < FA_D / 16; ++k)
+            umma_bf16(tdP, make_smem_desc(da + k * 32, 16, 1024), make_smem_desc(va + k * 32, 16, 1024),
+                      idesc_s, k > 0 ? 1u : 0u);
+          umma_commit(sdp_full);
+          ++c_sdp;
+          return true;
+        };
+        if (g.n_q > 0 && !issue_sdp(qc)) { ok = false; break; }
+        for (int j = 0; j < g.n_q; ++j) {
+          const uint32_t step = qc + j;
+          const uint32_t st = step % WSB_Q_STAGES;
+          if (j + 1 < g.n_q && !issue_sdp(step + 1)) { ok = false; break; }
+          if (!mbar_wait(pds_ready, c_pds & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
+          ++c_pds;
+          if (j == 0 && !mbar_wait(acc_free, (ic & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
+          tc_fence_after();
+          const uint32_t qa = smem_u32(sQ + st * FA_TILE_BYTES), da = smem_u32(sdO + st * FA_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < FA_T / 16; ++k)   // dV[kv][d] += P^T[kv][q] dO[q][d]
+            umma_bf16(tdV, make_smem_desc(pa + k * 2048, FA_TILE_BYTES, 1024),
+                      make_smem_desc(da + k * 2048, 8192, 1024), idesc_g, (j > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < FA_T / 16; ++k)   // dK[kv][d] += dS^T[kv][q] Q[q][d]
+            umma_bf16(tdK, make_smem_desc(sa + k * 2048, FA_TILE_BYTES, 1024),
+                      make_smem_desc(qa + k * 2048, 8192, 1024), idesc_g, (j > 0 || k > 0) ? 1u : 0u);
+          if (!mbar_wait(dq_free, (c_dq & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < FA_T / 16; ++k)   // dQ[q][d] = dS[q][kv] K[kv][d]
+            umma_bf16(tdQ, make_smem_desc(sa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                      make_smem_desc(ka + k * 2048, 8192, 1024), idesc_dq, k > 0 ? 1u : 0u);
+          ++c_dq;
+          umma_commit(g_done);
+          umma_commit(&qdo_empty[st]);
+        }
+        if (!ok) break;
+        umma_commit(&kv_empty[kb]);
+        qc += g.n_q;
+        if (*abort_flag) ok = false;
+      }
+      if (!ok && *abort_flag == 0) {
+        atomicExch(args.status, why);
+        *abort_flag = 1;
+      }
+    }
+  }
+  } else {
+    // ------------------------------------------------------------------ compute warpgroups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WS_REGS_HEAVY));
+    const int gh = warp >> 2;               // key-column half of this warpgroup
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;      // query row inside the tile (= key row for dK / dV)
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = args.scale * LOG2E;
+    const int w = args.window;
+    uint32_t c_sdp = 0, c_g = 0;
+    bool ok = true;
+
+    // row statistics and key range of query row q of head h (zeros / empty range past T)
+    struct RowInfo { float lse2, delta; int klo, khi; };
+    auto fetch_row = [&](int q, int h) -> RowInfo {
+      RowInfo ri{0.f, 0.f, 0, 0};
+      if (q < T) {
+        ri.lse2 = __ldg(args.lse + static_cast<size_t>(h) * T + q) * LOG2E;
+        ri.delta = __ldg(args.delta + static_cast<size_t>(h) * T + q);
+        ri.klo = __ldg(args.seq_start + q);
+        ri.khi = __ldg(args.seq_end + q);
+        if (w >= 0) {
+          ri.klo = max(ri.klo, q - w);
+          ri.khi = min(ri.khi, q + w + 1);
+        }
+      }
+      return ri;
+    };
+    // dQ tile of the step whose query rows start at q0: this thread adds channels [32 gh, +32) of row q0 + r
+    auto drain_dq = [&](int q0, int q_hi, int h) {
+      uint32_t v[32];
+      tmem_ld32(tdQ + lane_addr + gh * 32, v);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+      const int q = q0 + r;
+      if (q < T && q < q_hi) {
+        float* dst = args.dq_acc + static_cast<size_t>(q) * HD + h * FA_D + gh * 32;
+#pragma unroll
+        for (int e = 0; e < 32; e += 4)
+          atomicAdd(reinterpret_cast<float4*>(dst + e),
+                    make_float4(__uint_as_float(v[e]) * args.scale, __uint_as_float(v[e + 1]) * args.scale,
+                                __uint_as_float(v[e + 2]) * args.scale, __uint_as_float(v[e + 3]) * args.scale));
+      }
+    };
+
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int h = item % H;
+      const WsBwdGeo g = ws_bwd_geometry(args, item / H);
+      RowInfo nxt = fetch_row(g.q_lo + r, h);
+      for (int j = 0; j < g.n_q; ++j) {
+        const int q0 = g.q_lo + j * FA_T;
+        const RowInfo ri = nxt;
+        if (j + 1 < g.n_q) nxt = fetch_row(q0 + FA_T + r, h);
+        ok = mbar_wait(sdp_full, c_sdp & 1u);
+        ++c_sdp;
+        ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t rs[64], rp[64];
+        tmem_ld32(tS + lane_addr + gh * 64, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
+        tmem_ld32(tS + lane_addr + gh * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
+        tmem_ld32(tdP + lane_addr + gh * 64, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
+        tmem_ld32(tdP + lane_addr + gh * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sdp_free);
+        if (j > 0) {
+          // the previous step's dV / dK / dQ have finished: P / dS tiles are free, dQ can be read
+          ok = mbar_wait(g_done, c_g & 1u);
+          ++c_g;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          drain_dq(q0 - FA_T, g.q_hi, h);
+        }
+        // keys of this thread's columns: [c0, c0 + 64)
+        const int c0 = g.kv0 + gh * 64;
+        const bool inside = __all_sync(0xffffffffu, c0 >= ri.klo && c0 + 64 <= ri.khi);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          uint32_t pk[4], dk[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = c8 * 8 + 2 * u;
+            float p0 = exp2f(fmaf(__uint_as_float(rs[e]), sl2, -ri.lse2));
+            float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), sl2, -ri.lse2));
+            if (!inside) {
+              const int key = c0 + e;
+              if (!(key >= ri.klo && key < ri.khi)) p0 = 0.f;
+              if (!(key + 1 >= ri.klo && key + 1 < ri.khi)) p1 = 0.f;
+            }
+            const float d0 = p0 * (__uint_as_float(rp[e]) - ri.delta);
+            const float d1 = p1 * (__uint_as_float(rp[e + 1]) - ri.delta);
+            pk[u] = pack_bf16x2(p0, p1);
+            dk[u] = pack_bf16x2(d0, d1);
+          }
+          const uint32_t off = gh * FA_TILE_BYTES + swz(r, c8);
+          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(sdS + off) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(pds_ready);
+      }
+      if (!ok) break;
+      if (g.n_q > 0) {
+        ok = mbar_wait(g_done, c_g & 1u);
+        ++c_g;
+        ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+        if (!ok) break;
+        tc_fence_after();
+        drain_dq(g.q_lo + (g.n_q - 1) * FA_T, g.q_hi, h);
+      }
+      // dK (warpgroup 0) / dV (warpgroup 1): every thread owns the 64 channels of key row kv0 + r
+      float acc[FA_D];
+      if (g.n_q > 0) {
+        const uint32_t src = (gh == 0 ? tdK : tdV) + lane_addr;
+#pragma unroll
+        for (int c = 0; c < FA_D; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(src + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[c + e] = __uint_as_float(v[e]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_free);
+      } else {
+#pragma unroll
+        for (int e = 0; e < FA_D; ++e) acc[e] = 0.f;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_free);   // keeps the per-item phase count in step with the MMA warp
+      }
+      const int krow = g.kv0 + r;
+      if (krow < T) {
+        if (gh == 0) {
+#pragma unroll
+          for (int e = 0; e < FA_D; ++e) acc[e] *= args.scale;
+          if (args.rope_pos != nullptr) {
+            const int pos = __ldg(args.rope_pos + krow);
+            const float4* cp = reinterpret_cast<const float4*>(args.rope_cos + static_cast<size_t>(pos) * 32);
+            const float4* sp = reinterpret_cast<const float4*>(args.rope_sin + static_cast<size_t>(pos) * 32);
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              const float4 c4 = __ldg(cp + q4), s4 = __ldg(sp + q4);
+              const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+              const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int e = q4 * 4 + u;
+                const float a = acc[e], b = acc[e + 32];
+                acc[e] = a * cc[u] + b * ss[u];
+                acc[e + 32] = b * cc[u] - a * ss[u];
+              }
+            }
+          }
+        }
+        __nv_bfloat16* dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 1 + gh) * HD + h * FA_D;
+#pragma unroll
+        for (int e = 0; e < FA_D; e += 8) {
+          uint4 u4;
+          uint32_t* pk = reinterpret_cast<uint32_t*>(&u4);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) pk[q4] = pack_bf16x2(acc[e + 2 * q4], acc[e + 2 * q4 + 1]);
+          *reinterpret_cast<uint4*>(dst + e) = u4;
+        }
+      }
+    }
+    if (!ok && lane == 0 && *abort_flag == 0) {
+      atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WS_MMA_WARP) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[h][t] = sum_d dO[t,h,d] * O[t,h,d]
+__global__ void __launch_bounds__(256)
+ws_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                float* __restrict__ delta, int T, int H) {
+  const long long total = static_cast<long long>(T) * H * 8;   // 8 threads per (t, h)
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int sub = static_cast<int>(idx & 7);
+    const long long th = idx >> 3;
+    const int h = static_cast<int>(th % H);
+    const int t = static_cast<int>(th / H);
+    const size_t off = (static_cast<size_t>(t) * H + h) * FA_D + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + off);
+    const uint4 b = *reinterpret_cast<const uint4*>(dout + off);
+    const uint32_t* pa = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* pb = reinterpret_cast<const uint32_t*>(&b);
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 x = unpack_bf16x2(pa[q]);
+      const float2 y = unpack_bf16x2(pb[q]);
+      s += x.x * y.x + x.y * y.y;
+    }
+    const uint32_t gmask = 0xffu << (threadIdx.x & 24);
+    s += __shfl_xor_sync(gmask, s, 1);
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 4);
+    if (sub == 0) delta[static_cast<size_t>(h) * T + t] = s;
+  }
+}
+
+// dq (fp32 accumulator) -> bf16 into the q part of dqkv[T][3][H][64]; with rope_pos the gradient is
+// rotated back first. One thread handles channels [8v, 8v+8) and [32+8v, 32+8v+8) of one head.
+__global__ void __launch_bounds__(256)
+ws_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int T, int H,
+                   const int* __restrict__ rope_pos, const float* __restrict__ rope_cos,
+                   const float* __restrict__ rope_sin) {
+  const int HD = H * FA_D;
+  const long long total = static_cast<long long>(T) * H * 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i & 3);
+    const long long th = i >> 2;
+    const int h = static_cast<int>(th % H);
+    const int t = static_cast<int>(th / H);
+    const float* src = dq_acc + static_cast<size_t>(t) * HD + h * FA_D + v * 8;
+    float a[8], b[8];
+    *reinterpret_cast<float4*>(a) = *reinterpret_cast<const float4*>(src);
+    *reinterpret_cast<float4*>(a + 4) = *reinterpret_cast<const float4*>(src + 4);
+    *reinterpret_cast<float4*>(b) = *reinterpret_cast<const float4*>(src + 32);
+    *reinterpret_cast<float4*>(b + 4) = *reinterpret_cast<const float4*>(src + 36);
+    if (rope_pos != nullptr) {
+      const int pos = rope_pos[t];
+      const float* cp = rope_cos + static_cast<size_t>(pos) * 32 + v * 8;
+      const float* sp = rope_sin + static_cast<size_t>(pos) * 32 + v * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = cp[e], sn = sp[e], x1 = a[e], x2 = b[e];
+        a[e] = x1 * c + x2 * sn;
+        b[e] = x2 * c - x1 * sn;
+      }
+    }
+    __nv_bfloat16* dst = dqkv + static_cast<size_t>(t) * 3 * HD + h * FA_D + v * 8;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]),
+                                                pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+    *reinterpret_cast<uint4*>(dst + 32) = make_uint4(pack_bf16x2(b[0], b[1]), pack_bf16x2(b[2], b[3]),
+                                                     pack_bf16x2(b[4], b[5]), pack_bf16x2(b[6], b[7]));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn ws_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows = T, cols contiguous; box = [128 rows][64 cols]
+static int ws_make_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows) {
+  EncodeTiledFn fn = ws_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {FA_D, FA_T};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+// cudaFuncSetAttribute and the SM count are per device: one slot per device ordinal
+constexpr int WS_MAX_DEVICES = 64;
+struct WsDeviceInfo {
+  bool configured;
+  int sms;
+};
+static WsDeviceInfo ws_device[WS_MAX_DEVICES];
+
+static int ws_configure(int* sms) {
+  int dev = 0;
+  NPLM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= WS_MAX_DEVICES) return -4;
+  if (!ws_device[dev].configured) {
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         WS_FWD_SMEM));
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         WS_BWD_SMEM));
+    int n = 0;
+    NPLM_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    ws_device[dev].sms = n;
+    ws_device[dev].configured = true;
+  }
+  *sms = ws_device[dev].sms;
+  return 0;
+}
+
+}  // namespace nplm
+
+using namespace nplm;
+
+// Forward. The current device must be the one that owns `st` and the tensors.
+extern "C" int nplm_fa_fwd_ws(const void* qkv, void* out, float* lse, const int* seq_start,
+                              const int* seq_end, int T, int H, int D, int window, float scale,
+                              int max_ctas, int* status, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D != FA_D || H <= 0) return -3;
+  if (reinterpret_cast<uintptr_t>(qkv) & 15) return -3;
+  CUtensorMap tm;
+  int rc = ws_make_map(&tm, qkv, static_cast<uint64_t>(3) * H * D, T);
+  if (rc) return rc;
+  int sms = 0;
+  rc = ws_configure(&sms);
+  if (rc) return rc;
+  FaWsArgs a;
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.lse = lse;
+  a.seq_start = seq_start;
+  a.seq_end = seq_end;
+  a.T = T;
+  a.H = H;
+  a.window = window;
+  a.scale = scale;
+  a.status = status;
+  const int n_items = ((T + 2 * FA_T - 1) / (2 * FA_T)) * H;
+  int grid = sms;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (grid > n_items) grid = n_items;
+  fa_fwd_ws_kernel<<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Backward. dq_acc: caller-provided fp32 scratch [T][H*D], cleared here. delta: fp32 scratch [H][T],
+// computed here from out and dout unless out is null (then it must hold rowsum(dO * O) already).
+// rope_* (may be null): q / k were rotated before the forward pass; dQ and dK are returned as
+// gradients of the un-rotated projections.
+extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout, const float* lse,
+                              void* dqkv, float* dq_acc, float* delta, const int* seq_start,
+                              const int* seq_end, int T, int H, int D, int window, float scale,
+                              const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                              int max_ctas, int* status, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D != FA_D || H <= 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15)) return -3;
+  CUtensorMap tmQKV, tmDO;
+  int rc = ws_make_map(&tmQKV, qkv, static_cast<uint64_t>(3) * H * D, T);
+  if (rc) return rc;
+  rc = ws_make_map(&tmDO, dout, static_cast<uint64_t>(H) * D, T);
+  if (rc) return rc;
+  int sms = 0;
+  rc = ws_configure(&sms);
+  if (rc) return rc;
+  const int HD = H * D;
+  NPLM_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * HD * sizeof(float), st));
+  if (out != nullptr) {
+    const long long total = static_cast<long long>(T) * H * 8;
+    long long blocks = (total + 255) / 256;
+    if (blocks > sms * 16) blocks = sms * 16;
+    ws_delta_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, T, H);
+  }
+  FaWsBwdArgs a;
+  a.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  a.dq_acc = dq_acc;
+  a.lse = lse;
+  a.delta = delta;
+  a.seq_start = seq_start;
+  a.seq_end = seq_end;
+  a.T = T;
+  a.H = H;
+  a.window = window;
+  a.scale = scale;
+  a.status = status;
+  a.rope_pos = rope_pos;
+  a.rope_cos = rope_cos;
+  a.rope_sin = rope_sin;
+  const int n_items = ((T + FA_T - 1) / FA_T) * H;
+  int grid = sms;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (grid > n_items) grid = n_items;
+  fa_bwd_ws_kernel<<<grid, WS_THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  {
+    const long long total = static_cast<long long>(T) * H * 4;
+    long long blocks = (total + 255) / 256;
+    if (blocks > sms * 16) blocks = sms * 16;
+    ws_dq_store_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+        dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), T, H, rope_pos, rope_cos, rope_sin);
+  }
+  return static_cast<int>(cudaGetLastError());
+}

@@ -23,6 +23,7 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "elementwise.cu",
     "attention.cu",
+    "attention_ws.cu",
     "attention_bias.cu",
     "extras.cu",
     "comm.cu",
@@ -59,6 +60,35 @@ def lib_path(name: str) -> Path:
     return LIB_DIR / f"lib{Path(name).stem}.so"
 
 
+def _locked_build(out: Path, digest: str, cmd: list[str], what: str, verbose: bool, force: bool) -> Path:
+    """Runs `cmd` (which writes to the path after its ``-o``) under an inter-process file lock, into a
+    temporary name that is renamed into place; the digest stamp is written last. Concurrent ranks /
+    DataLoader workers that see a stale stamp therefore either build once or wait, and nobody can
+    dlopen a half-written library."""
+    import fcntl
+    stamp = out.with_suffix(".sha")
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    with open(LIB_DIR / f".{out.stem}.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+                return out   # another process built it while we waited
+            tmp = out.with_name(f".{out.name}.{os.getpid()}.tmp")
+            full = [tmp.as_posix() if c == "@OUT@" else c for c in cmd]
+            proc = subprocess.run(full, capture_output=True, text=True)
+            if proc.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise RuntimeError(f"build failed for {what}:\n{proc.stdout}\n{proc.stderr}")
+            if verbose:
+                sys.stderr.write(proc.stderr)
+            stamp.unlink(missing_ok=True)      # never leave a matching stamp beside an old library
+            os.replace(tmp, out)
+            stamp.write_text(digest)
+            return out
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
 def build_one(name: str, verbose: bool = False, force: bool = False) -> Path:
     src = CSRC / name
     out = lib_path(name)
@@ -66,17 +96,10 @@ def build_one(name: str, verbose: bool = False, force: bool = False) -> Path:
     digest = _digest(src)
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
         return out
-    LIB_DIR.mkdir(parents=True, exist_ok=True)
-    cmd = [nvcc_path(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(out), str(src)]
+    cmd = [nvcc_path(), *NVCC_FLAGS, "-I", str(CSRC), "-o", "@OUT@", str(src)]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed for {name}:\n{proc.stdout}\n{proc.stderr}")
-    if verbose:
-        sys.stderr.write(proc.stderr)
-    stamp.write_text(digest)
-    return out
+    return _locked_build(out, digest, cmd, name, verbose, force)
 
 
 HOST_SOURCES = ["packer.cpp"]
@@ -90,14 +113,9 @@ def build_host(name: str, force: bool = False) -> Path:
     digest = hashlib.sha256(src.read_bytes()).hexdigest()
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
         return out
-    LIB_DIR.mkdir(parents=True, exist_ok=True)
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-o", str(out), str(src)]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError(f"g++ failed for {name}:\n{proc.stdout}\n{proc.stderr}")
-    stamp.write_text(digest)
-    return out
+    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-o", "@OUT@", str(src)]
+    return _locked_build(out, digest, cmd, name, False, force)
 
 
 def build_all(verbose: bool = False, force: bool = False) -> list[Path]:

@@ -436,6 +436,17 @@ __device__ __forceinline__ float gelu_erf_grad(float x) {
 }  // namespace nplm
 
 // ---------------------------------------------------------------- host helpers
+namespace nplm {
+// Per-function attributes (cudaFuncSetAttribute) apply to the current device only, so one-time
+// set-up is tracked per device ordinal. Returns the slot of the current device or -1.
+constexpr int MAX_DEVICES = 64;
+inline int current_device_slot() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEVICES) return -1;
+  return d;
+}
+}  // namespace nplm
+
 #define NPLM_CUDA_CHECK(expr)                          \
   do {                                                 \
     cudaError_t _e = (expr);                           \

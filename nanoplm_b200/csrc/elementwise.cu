@@ -1133,7 +1133,10 @@ extern "C" int nplm_ce_bwd(const void* h, const void* W, const float* dlogits, c
   if (C <= 1024) {
     const size_t tsm = (static_cast<size_t>(V) * C + static_cast<size_t>(CE_TILE_ROWS) * C) * 2 +
                        CE_TILE_ROWS * 32 * 4;
-    static bool configured = false;
+    static bool configured_on[nplm::MAX_DEVICES];
+    const int dev_slot = nplm::current_device_slot();
+    if (dev_slot < 0) return -4;
+    bool& configured = configured_on[dev_slot];
     if (!configured) {
       cudaFuncSetAttribute(ce_bwd_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
       configured = true;

@@ -567,7 +567,10 @@ extern "C" int nplm_gemm_fp8(const void* A, const void* B, void* C, const float*
   if (rc) return rc;
   rc = f8_make_map(&tmB, B, K, N);
   if (rc) return rc;
-  static bool configured = false;
+  static bool configured_on[nplm::MAX_DEVICES];
+  const int dev_slot = nplm::current_device_slot();
+  if (dev_slot < 0) return -4;
+  bool& configured = configured_on[dev_slot];
   if (!configured) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM));
     configured = true;
@@ -619,7 +622,10 @@ extern "C" int nplm_gemm_fp8_ag(const void* A, void* const* b_ptrs, void* C, con
   if (rc) return rc;
   rc = f8_make_map(&tmB, b_ptrs[rank], K, N);
   if (rc) return rc;
-  static bool configured = false;
+  static bool configured_on[nplm::MAX_DEVICES];
+  const int dev_slot = nplm::current_device_slot();
+  if (dev_slot < 0) return -4;
+  bool& configured = configured_on[dev_slot];
   if (!configured) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM));
     configured = true;

@@ -931,7 +931,10 @@ static int launch_impl(const GemmMaps& maps, const GemmArgs& args, int max_ctas,
   const CUtensorMap& tmB = maps.B;
   using S = GemmSmem<BN, false, TMA_EPI>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, TMA_EPI>;
-  static bool configured = false;
+  static bool configured_on[nplm::MAX_DEVICES];
+  const int dev_slot = nplm::current_device_slot();
+  if (dev_slot < 0) return -4;
+  bool& configured = configured_on[dev_slot];
   if (!configured) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     configured = true;
@@ -966,7 +969,10 @@ template <bool A_MN, bool B_MN, int EPI, bool TMA_EPI>
 static int launch_pair_impl(const GemmMaps& maps, const GemmArgs& args, cudaStream_t stream) {
   using S = GemmSmem<256, true, TMA_EPI>;
   auto kern = gemm_bf16_kernel<256, A_MN, B_MN, EPI, TMA_EPI, true>;
-  static bool configured = false;
+  static bool configured_on[nplm::MAX_DEVICES];
+  const int dev_slot = nplm::current_device_slot();
+  if (dev_slot < 0) return -4;
+  bool& configured = configured_on[dev_slot];
   if (!configured) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     configured = true;

@@ -35,11 +35,27 @@ def have_h5py() -> bool:
 
 
 class _KdzFile:
-    """Read-only view of a `.kdz` archive with the group-per-sequence interface of the HDF5 layout."""
+    """Read-only view of a `.kdz` archive with the group-per-sequence interface of the HDF5 layout.
+
+    An npz member is decompressed as a whole on every access and the underlying zip handle is not
+    safe for concurrent readers (the prefetch thread and the main thread share one handle), so the
+    three arrays are read once, under a lock, and served from memory afterwards."""
+
+    _KEYS = ("input_ids", "attention_mask", "teacher_embeddings")
 
     def __init__(self, path):
-        self._z = np.load(path, mmap_mode="r", allow_pickle=False)
-        self.n = int(self._z["input_ids"].shape[0])
+        self._path = str(path)
+        self._lock = threading.Lock()
+        self._arrays: Optional[dict] = None
+        with np.load(self._path, allow_pickle=False) as z:
+            self.n = int(z["input_ids"].shape[0])
+
+    def _load(self) -> dict:
+        with self._lock:
+            if self._arrays is None:
+                with np.load(self._path, allow_pickle=False) as z:
+                    self._arrays = {k: np.asarray(z[k]) for k in self._KEYS}
+            return self._arrays
 
     def keys(self):
         return [str(i) for i in range(self.n)]
@@ -49,13 +65,12 @@ class _KdzFile:
 
     def __getitem__(self, key):
         i = int(key)
-        return {k: self._z[k][i] for k in ("input_ids", "attention_mask", "teacher_embeddings")}
+        arrays = self._load()
+        return {k: arrays[k][i] for k in self._KEYS}
 
     def close(self):
-        try:
-            self._z.close()
-        except Exception:
-            pass
+        with self._lock:
+            self._arrays = None
 
 
 def open_kd_file(path):

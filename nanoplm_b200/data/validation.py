@@ -59,13 +59,13 @@ def validate_pretrain_dataset(dataset_dir: str | Path) -> dict:
 
 
 def _h5_files(directory: Path, prefix: str | None) -> list[Path]:
+    """HDF5 shards, or their `.kdz` stand-ins (what `SaveKDDataset` writes when h5py is absent)."""
+    exts = (".h5", ".kdz")
     if prefix is None:
-        return sorted(directory.glob("*.h5"))
+        return sorted(f for e in exts for f in directory.glob(f"*{e}"))
     stem = Path(prefix).stem
-    files = sorted(directory.glob(f"{stem}_shard_*.h5"))
-    single = directory / (stem + ".h5")
-    if single.exists():
-        files.append(single)
+    files = sorted(f for e in exts for f in directory.glob(f"{stem}_shard_*{e}"))
+    files += [directory / (stem + e) for e in exts if (directory / (stem + e)).exists()]
     return files
 
 
@@ -82,6 +82,10 @@ def validate_hdf5_shards(directory: str | Path, prefix: str | None = None) -> di
         return {"num_files": len(files), "num_sequences": None}
     total = 0
     for f in files:
+        if f.suffix == ".kdz":
+            from nanoplm_b200.data.kd_dataset import count_kd_sequences
+            total += count_kd_sequences(f)
+            continue
         try:
             with h5py.File(f, "r") as h:
                 total += len(h.keys())

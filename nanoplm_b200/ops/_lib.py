@@ -44,14 +44,10 @@ def lib(name: str) -> ctypes.CDLL:
             return _LIBS[name]
         host = (_build.CSRC / f"{name}.cpp").exists()
         src = f"{name}.cpp" if host else f"{name}.cu"
-        # build_* is a no-op when the source digest matches the stamp next to the .so, so a stale
-        # library is never loaded silently
-        try:
-            path = _build.build_host(src) if host else _build.build_one(src)
-        except RuntimeError:
-            path = _build.lib_path(src)
-            if not path.exists():
-                raise
+        # build_* is a no-op when the source digest matches the stamp next to the .so and raises
+        # when a rebuild is needed but fails: a library that does not match its source is never
+        # loaded
+        path = _build.build_host(src) if host else _build.build_one(src)
         handle = ctypes.CDLL(str(path))
         _LIBS[name] = handle
         return handle

@@ -410,14 +410,30 @@ def seq_bounds(cu_seqlens: torch.Tensor, T: int):
     return s, e
 
 
-def fa_fwd(qkv, seq_start, seq_end, H, D, window, scale):
+_FA_IMPL = [_os.environ.get("NPLM_FA_IMPL", "ws")]
+
+
+def set_attention_impl(name: str) -> None:
+    """"ws": the persistent warp-specialised kernels (attention_ws.cu, default);
+    "single": the one-role-per-CTA kernels of attention.cu."""
+    if name not in ("ws", "single"):
+        raise ValueError("attention impl must be 'ws' or 'single'")
+    _FA_IMPL[0] = name
+
+
+def fa_fwd(qkv, seq_start, seq_end, H, D, window, scale, impl: str | None = None, max_ctas: int = 0):
     _chk(qkv, _BF16, "qkv")
     T = qkv.shape[0]
     out = torch.empty((T, H * D), dtype=_BF16, device=qkv.device)
     lse = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
-    rc = lib("attention").nplm_fa_fwd(ptr(qkv), ptr(out), ptr(lse), ptr(seq_start), ptr(seq_end),
-                                      c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
-                                      ptr(status_word(qkv.device)), stream_ptr())
+    if (impl or _FA_IMPL[0]) == "ws":
+        rc = lib("attention_ws").nplm_fa_fwd_ws(ptr(qkv), ptr(out), ptr(lse), ptr(seq_start), ptr(seq_end),
+                                                c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                                c_int(max_ctas), ptr(status_word(qkv.device)), stream_ptr())
+    else:
+        rc = lib("attention").nplm_fa_fwd(ptr(qkv), ptr(out), ptr(lse), ptr(seq_start), ptr(seq_end),
+                                          c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                          ptr(status_word(qkv.device)), stream_ptr())
     check_rc(rc, "fa_fwd")
     count_launch()
     return out, lse
@@ -447,7 +463,7 @@ def gemm_dgrad_delta(dy: torch.Tensor, w: torch.Tensor, o: torch.Tensor, delta: 
 
 
 def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=None, delta=None,
-           rope: tuple | None = None, delta_ready: bool = False):
+           rope: tuple | None = None, delta_ready: bool = False, impl: str | None = None, max_ctas: int = 0):
     """rope = (pos, cos, sin): q / k in qkv were rotated before the forward pass; dQ / dK are rotated
     back inside the kernels. delta_ready: `delta` [H, T] already holds rowsum(dO * O) (see
     gemm_dgrad_delta); the kernel that computes it from out and dout is skipped."""
@@ -462,11 +478,18 @@ def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=
     r_pos, r_cos, r_sin = rope if rope is not None else (None, None, None)
     if delta_ready:
         out = None
-    rc = lib("attention").nplm_fa_bwd_rope(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
-                                           ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
-                                           c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
-                                           ptr(r_pos), ptr(r_cos), ptr(r_sin),
-                                           ptr(status_word(qkv.device)), stream_ptr())
+    if (impl or _FA_IMPL[0]) == "ws":
+        rc = lib("attention_ws").nplm_fa_bwd_ws(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
+                                                ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
+                                                c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                                ptr(r_pos), ptr(r_cos), ptr(r_sin), c_int(max_ctas),
+                                                ptr(status_word(qkv.device)), stream_ptr())
+    else:
+        rc = lib("attention").nplm_fa_bwd_rope(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
+                                               ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
+                                               c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                               ptr(r_pos), ptr(r_cos), ptr(r_sin),
+                                               ptr(status_word(qkv.device)), stream_ptr())
     check_rc(rc, "fa_bwd")
     count_launch(3 if delta_ready else 4)
     return dqkv

@@ -89,8 +89,12 @@ def resolve_config_from_manifest(cfg: DistillationConfig) -> DistillationConfig:
     return cfg
 
 
-def _save_student(student: ProtX, engine: ShardedEngine, path: Path) -> None:
+def _save_student(engine: ShardedEngine, path: Path, write: bool) -> None:
+    """Gathers the fp32 student weights (a collective: EVERY rank must call this) and writes them
+    on the rank that passes write=True."""
     sd = {k: v.contiguous() for k, v in engine.full_state_dict_model().items()}
+    if not write:
+        return
     try:
         from safetensors.torch import save_file
         save_file(sd, str(path / "model.safetensors"))
@@ -108,7 +112,8 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
     student = ProtX(model_config)
     use_bf16 = cfg.bf16 and device.type == "cuda"
     hyper = AdamWHyper(lr=float(cfg.learning_rate), weight_decay=0.01, max_grad_norm=float(cfg.max_grad_norm))
-    engine = ShardedEngine(student, hyper, device, compute_dtype=torch.bfloat16 if use_bf16 else torch.float32)
+    engine = ShardedEngine(student, hyper, device, compute_dtype=torch.bfloat16 if use_bf16 else torch.float32,
+                           fused_comm=bool(getattr(cfg, "fused_comm", True)))
     student.train()
     if cfg.on_the_fly and teacher is None:
         from nanoplm_b200.models.teacher import T5EncoderTeacher
@@ -127,13 +132,20 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
         val_ds = KDDatasetOnTheFly(cfg.val_fasta, None, rank, world)
         train_loader = DataLoader(train_ds, batch_size=cfg.batch_size, collate_fn=collator, num_workers=0)
         val_loader = DataLoader(val_ds, batch_size=cfg.batch_size, collate_fn=collator, num_workers=0)
-        per_rank = math.ceil(cfg.train_sequences / world)
+        # sequences are dealt round-robin, so ranks hold n // world or n // world + 1 of them: every
+        # rank runs the same number of micro-batches (the surplus sequence of some ranks is dropped),
+        # otherwise the ranks would disagree on the number of collective optimizer steps
+        n_train = cfg.train_sequences if cfg.max_seqs_num is None else min(cfg.train_sequences, cfg.max_seqs_num)
+        per_rank = n_train // world
+        if per_rank == 0:
+            raise ValueError(f"{n_train} training sequences cannot feed {world} ranks")
         sampler = None
     else:
         train_ds = LoadKDDataset(cfg.train_h5_prefix, cfg.max_open_files, cfg.chunk_size, cfg.prefetch_batches,
                                  cfg.use_threading, seed=cfg.seed)
         val_ds = LoadKDDataset(cfg.val_h5_prefix, cfg.max_open_files, cfg.chunk_size, cfg.prefetch_batches,
                                cfg.use_threading)
+        # pads by wrapping around so every rank sees exactly ceil(n / world) samples
         sampler = ResumableDistributedSampler(len(train_ds), world, rank, True, cfg.seed)
         train_loader = DataLoader(train_ds, batch_size=cfg.batch_size, sampler=sampler, collate_fn=collator,
                                   num_workers=0, drop_last=False)
@@ -194,16 +206,20 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
         student.train()
         return float(tot[0] / tot[1].clamp(min=1))
 
+    def check_device_status() -> None:
+        if device.type == "cuda":
+            from nanoplm_b200.ops import _lib
+            _lib.check_status()
+
     def save(step: int) -> None:
-        sd_opt = engine.optimizer_state_dict()
+        check_device_status()                      # never persist state after a failed kernel
+        sd_opt = engine.optimizer_state_dict()     # collective
+        d = out_dir / f"checkpoint-{step}"
+        tmp = out_dir / f".tmp-checkpoint-{step}"
         if is_main:
-            d = out_dir / f"checkpoint-{step}"
-            tmp = out_dir / f".tmp-checkpoint-{step}"
             tmp.mkdir(parents=True, exist_ok=True)
-        if distributed:
-            dist.barrier()
+        _save_student(engine, tmp, write=is_main)  # collective
         if is_main:
-            _save_student(student, engine, tmp)
             torch.save(sd_opt, tmp / "optimizer.pt")
             torch.save(sched.state_dict(), tmp / "scheduler.pt")
             (tmp / "trainer_state.json").write_text(json.dumps({"global_step": step}), encoding="utf-8")
@@ -211,19 +227,29 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
                 import shutil
                 shutil.rmtree(d)
             os.replace(tmp, d)
-        else:
-            engine.full_state_dict_model()
+        if distributed:
+            dist.barrier()
 
     losses, evals = [], []
     acc = torch.zeros((), device=device)
     win, win_n, t0, seen = torch.zeros((), device=device), 0, time.perf_counter(), 0
     start_epoch = global_step // steps_per_epoch
+    # a checkpoint taken inside an epoch: skip the micro-batches that epoch already consumed
+    skip_micro = (global_step % steps_per_epoch) * accum
     done = False
     for epoch in range(start_epoch, plan.num_epochs):
         if sampler is not None:
             sampler.set_epoch(epoch)
-        micro = 0
+            if skip_micro:
+                sampler.fast_forward(skip_micro * cfg.batch_size)   # O(1): the loader starts past them
+        micro = skip_micro if sampler is not None else 0
+        to_skip = 0 if sampler is not None else skip_micro          # iterable dataset: read and drop
+        skip_micro = 0
         for b in train_loader:
+            if to_skip:
+                to_skip -= 1
+                micro += 1
+                continue
             b = to_dev(b)
             loss = distillation_loss(student, b, teacher)
             loss.backward()
@@ -242,6 +268,7 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
             win_n += 1
             if global_step % plan.logging_steps == 0:
                 lv = float(win / max(1, win_n))
+                check_device_status()
                 dt = time.perf_counter() - t0
                 losses.append((global_step, lv))
                 sink.log({"train/global_step": global_step, "train/loss": lv, "train/grad_norm": float(gn),
@@ -261,17 +288,16 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
             if max_steps is not None and global_step >= max_steps:
                 done = True
                 break
+            if micro >= micro_per_epoch:
+                break     # every rank stops after the same number of micro-batches
         if done:
             break
     save(global_step)
-    if is_main:
-        _save_student(student, engine, out_dir)
+    _save_student(engine, out_dir, write=is_main)   # collective: every rank takes part
     ev = evaluate()
     sink.log({"train/global_step": global_step, "eval/loss": ev})
     sink.finish(str(out_dir))
-    if device.type == "cuda":
-        from nanoplm_b200.ops import _lib
-        _lib.check_status()
+    check_device_status()
     logger.info("Distillation complete.")
     return {"output_dir": str(out_dir), "losses": losses, "eval_losses": evals + [(global_step, ev)],
             "global_step": global_step, "student": student, "engine": engine}
