@@ -159,6 +159,25 @@ def bench_attn(T, peaks):
     k.check_status()
 
 
+def bench_attn_ws(T, peaks):
+    """Only the warp-specialised attention kernels (a small, library-free target for profilers)."""
+    from nanoplm_b200.ops import kernels as k
+    H, D = 16, 64
+    lens, cu = _packed_batch(T)
+    qkv = torch.randn(T, 3 * H * D, device="cuda").to(BF)
+    dout = torch.randn(T, H * D, device="cuda").to(BF)
+    ss, se = k.seq_bounds(cu, T)
+    flush = _flush_buf()
+    for window in (-1, 64):
+        ms = time_fn(lambda: k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl="ws"), iters=5, flush=flush)
+        out, lse = k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl="ws")
+        ms_b = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws"), iters=5,
+                       flush=flush)
+        print(json.dumps({"kernel": "fa_varlen_ws", "window": window, "T": T, "fwd_ms": round(ms, 4),
+                          "bwd_ms": round(ms_b, 4)}), flush=True)
+    k.check_status()
+
+
 def bench_elementwise(T, peaks):
     from nanoplm_b200.ops import kernels as k
     C, I = 1024, 2048
@@ -283,7 +302,7 @@ def main():
         if what == "gemm":
             bench_gemm(args.tokens, peaks, args.sweep_splits)
             continue
-        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "fp8": bench_fp8,
+        {"gemm": bench_gemm, "attn": bench_attn, "attn_ws": bench_attn_ws, "elementwise": bench_elementwise, "fp8": bench_fp8,
          "moe": bench_moe}[what](args.tokens, peaks)
 
 

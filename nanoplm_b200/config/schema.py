@@ -156,6 +156,7 @@ class PretrainingConfig:
     device_masking: bool = False         # apply MLM masking on the GPU (Philox) instead of the collator
     metrics_jsonl: bool = True           # write metrics.jsonl next to the checkpoints
     heartbeat_seconds: float = 0.0       # > 0 enables the per-rank heartbeat / watchdog
+    heartbeat_stall_seconds: float = 0.0  # > 0: rank 0 ends the job when a rank's step stops advancing this long
 
 
 @dataclass

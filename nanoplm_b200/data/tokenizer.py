@@ -89,13 +89,18 @@ class _LutTokenizer:
         raw = np.frombuffer(self._normalise(text), dtype=np.uint8)
         ids = self._lut[raw]
         if add_special_tokens:
+            n_special = 1 + (self.bos_token_id is not None)
+            if truncation and max_length is not None and len(ids) + n_special > max_length:
+                # residues are cut, the special tokens stay (what the reference's HF tokenizer does:
+                # a truncated sequence still ends in </s>)
+                ids = ids[:max(0, max_length - n_special)]
             parts = []
             if self.bos_token_id is not None:
                 parts.append(np.array([self.bos_token_id], dtype=np.uint8))
             parts.append(ids)
             parts.append(np.array([self.eos_token_id], dtype=np.uint8))
             ids = np.concatenate(parts)
-        if truncation and max_length is not None and len(ids) > max_length:
+        elif truncation and max_length is not None and len(ids) > max_length:
             ids = ids[:max_length]
         return ids
 

@@ -287,10 +287,24 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                        {"pretrain": as_plain_dict(cfg), "total_steps": total_steps, "warmup_steps": warmup_steps},
                        is_main, jsonl=cfg.metrics_jsonl)
     flops_per_token = estimate_flops_per_token(model.config, manifest.max_seq_len)
-    heartbeat = None
+    heartbeat = watchdog = None
     if cfg.heartbeat_seconds and cfg.heartbeat_seconds > 0:
-        from nanoplm_b200.runtime.watchdog import Heartbeat
+        from nanoplm_b200.runtime.watchdog import Heartbeat, Watchdog
         heartbeat = Heartbeat(Path(output_dir) / "heartbeat", rank, cfg.heartbeat_seconds).start()
+        if is_main and distributed:
+            # a rank that died stops beating; a rank stuck in a collective keeps beating but its
+            # step stops advancing: both end the job instead of leaving it hung
+            stall = float(getattr(cfg, "heartbeat_stall_seconds", 0) or 0)
+            watchdog = Watchdog(Path(output_dir) / "heartbeat", world, max_age=6 * cfg.heartbeat_seconds + 30,
+                                max_step_age=stall if stall > 0 else None,
+                                interval=cfg.heartbeat_seconds).start()
+
+    def check_device_status() -> None:
+        """Bounded waits that ran out, peer time-outs and MoE capacity overflow set a device status
+        word; training must not continue (and no checkpoint may be written) after that."""
+        if device.type == "cuda":
+            from nanoplm_b200.ops import _lib
+            _lib.check_status()
 
     logger.info(f"Starting training: epochs={num_epochs}, total_steps={total_steps}, "
                 f"warmup_steps={warmup_steps}, grad_accum={grad_accum}, world={world}, "
@@ -354,6 +368,7 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
             if global_step % plan.logging_steps == 0:
                 if device.type == "cuda":
                     torch.cuda.synchronize()
+                check_device_status()     # the loop synchronises here anyway
                 elapsed = time.perf_counter() - t0
                 stats = torch.tensor([tok, raw_tok, elapsed], dtype=torch.float64, device=device)
                 if peer_stats is not None:
@@ -398,6 +413,7 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                 if is_main:
                     logger.info(f"[step {global_step}] eval_loss={ev:.4f}")
             if global_step % plan.save_steps == 0:
+                check_device_status()     # raises before a corrupted state could be persisted
                 ckpt.save_checkpoint(engine, scheduler, global_step, epoch, output_dir, plan.logging_steps,
                                      plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint)
             if max_steps is not None and global_step - start_step >= max_steps:
@@ -407,16 +423,17 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
             break
 
     gc.enable()
+    check_device_status()
     if distributed:
         dist.barrier()
     ckpt.save_checkpoint(engine, scheduler, global_step, num_epochs, output_dir, plan.logging_steps,
                          plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint)
     sink.finish(output_dir)
+    if watchdog is not None:
+        watchdog.stop()
     if heartbeat is not None:
         heartbeat.stop()
-    if device.type == "cuda":
-        from nanoplm_b200.ops import _lib
-        _lib.check_status()
+    check_device_status()
     logger.info("Pretraining complete.")
     result["global_step"] = global_step
     result["engine"] = engine

@@ -1,0 +1,265 @@
+"""Parity with the reference implementation itself (the `nanoplm` package installed under
+`baseline/_ref`, imported unmodified; every test here is skipped when it is absent).
+
+  * same state dict -> same logits and loss in fp32 on padded input (the reference's SDPA route,
+    modeling.py:631-752), and the same loss through this package's dynamic-packed and static-packed
+    routes on the same sequences;
+  * `pytorch_model.bin` / `optimizer.pt` written by one side load in the other
+    (pure_pipeline.py:224-331);
+  * tokenizer ids (tokenizer.py:20-62) including lower case and the U / Z / O / B residues;
+  * packing-collator layout: cu_seqlens, position ids, flat length, padding sequences, and the MLM
+    invariants of tests/test_packing_collator.py:57-255 checked on both collators.
+"""
+import os
+import sys
+import types
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+REF = ROOT / "baseline" / "_ref"
+
+pytestmark = pytest.mark.skipif(not (REF / "nanoplm").exists(), reason="reference package not installed")
+
+
+@pytest.fixture(scope="module")
+def ref(tmp_path_factory):
+    """The reference's modules, imported from baseline/_ref (it opens a log file under the current
+    directory on import, hence the temporary cwd; optional third-party modules it imports without
+    using on these paths get empty placeholders)."""
+    work = tmp_path_factory.mktemp("refcwd")
+    cwd = os.getcwd()
+    os.chdir(work)
+    added = []
+    for name, attrs in (("IPython", {"get_ipython": lambda: None}), ("h5py", {"File": object}), ("Bio", {}),
+                        ("Bio.SeqIO", {})):
+        try:
+            __import__(name)
+        except Exception:
+            m = types.ModuleType(name)
+            for k, v in attrs.items():
+                setattr(m, k, v)
+            sys.modules[name] = m
+            added.append(name)
+    if "Bio" in added:
+        sys.modules["Bio"].SeqIO = sys.modules["Bio.SeqIO"]
+    sys.path.insert(0, str(REF))
+    try:
+        from nanoplm.pretraining import collator as ref_collator
+        from nanoplm.pretraining import pure_pipeline as ref_pipeline
+        from nanoplm.pretraining.models.modern_bert.model import ProtModernBertMLMConfig
+        from nanoplm.pretraining.models.modern_bert.pure_model import PureProtModernBertMLM
+        from nanoplm.pretraining.models.modern_bert.tokenizer import ProtModernBertTokenizer
+    except Exception as exc:  # pragma: no cover
+        os.chdir(cwd)
+        pytest.skip(f"reference import failed: {type(exc).__name__}: {exc}")
+    ns = types.SimpleNamespace(collator=ref_collator, pipeline=ref_pipeline, Config=ProtModernBertMLMConfig,
+                               Model=PureProtModernBertMLM, Tokenizer=ProtModernBertTokenizer)
+    yield ns
+    os.chdir(cwd)
+    sys.path.remove(str(REF))
+    for name in added:
+        sys.modules.pop(name, None)
+
+
+GEOM = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=2,
+            max_position_embeddings=256)
+
+
+def _pair(ref):
+    """(reference model, this package's model) with the reference's weights copied across."""
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    torch.manual_seed(0)
+    rm = ref.Model(ref.Config(vocab_size=32, **GEOM)).float().eval()
+    with torch.no_grad():   # the reference zero-initialises some projections; make every path matter
+        for p in rm.parameters():
+            if p.ndim >= 2:
+                p.add_(torch.randn_like(p) * 0.05)
+    om = ProtEncoderMLM(ModelConfig(**GEOM), ProtTokenizer()).float().eval()
+    missing, unexpected = om.load_state_dict(rm.state_dict(), strict=True), None
+    return rm, om
+
+
+def _sequences(n, lo, hi, seed):
+    from nanoplm_b200.data.synthetic import synthetic_sequences
+    return synthetic_sequences(n, lo, hi, seed)
+
+
+def test_state_dict_keys_and_shapes_are_identical(ref):
+    rm, om = _pair(ref)
+    a, b = rm.state_dict(), om.state_dict()
+    assert list(a.keys()) == list(b.keys())
+    assert all(a[k].shape == b[k].shape for k in a)
+    assert sum(p.numel() for p in rm.parameters()) == sum(p.numel() for p in om.parameters())
+
+
+def test_same_weights_give_same_logits_and_loss_on_padded_input(ref):
+    rm, om = _pair(ref)
+    tok = ref.Tokenizer()
+    seqs = _sequences(6, 5, 90, seed=3)
+    enc = tok(seqs, padding=True, return_tensors="pt")
+    ids, mask = enc["input_ids"], enc["attention_mask"]
+    labels = torch.full_like(ids, -100)
+    g = torch.Generator().manual_seed(1)
+    pick = (torch.rand(ids.shape, generator=g) < 0.3) & mask.bool()
+    labels[pick] = ids[pick]
+    with torch.no_grad():
+        r = rm(input_ids=ids, attention_mask=mask, labels=labels)
+        o = om(input_ids=ids, attention_mask=mask, labels=labels)
+        r_logits = rm(input_ids=ids, attention_mask=mask)["logits"]
+        o_logits = om(input_ids=ids, attention_mask=mask)["logits"]
+    assert abs(float(r["loss"]) - float(o["loss"])) < 2e-5
+    real = mask.bool()
+    assert (r_logits[real] - o_logits[real]).abs().max().item() < 2e-4
+
+
+def test_packed_routes_reproduce_the_reference_loss(ref):
+    """Dynamic (2-D rows + cu_seqlens) and static (flat, fixed length) packed batches of the same
+    sequences and the same labels give the loss the reference computes on the padded batch."""
+    from nanoplm_b200.data.collators import PackingCollator
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    rm, om = _pair(ref)
+    tok = ProtTokenizer()
+    seqs = _sequences(10, 5, 60, seed=9)
+    examples = [{"input_ids": torch.tensor(tok.encode(s))} for s in seqs]
+    for static in (False, True):
+        coll = PackingCollator(tok, 64, 0.3, target_rows=8 if static else None,
+                               batch_size=len(examples) if static else None, seed=4)
+        b = coll(examples)
+        b.pop("num_real_tokens", None)
+        with torch.no_grad():
+            o = om(**{k: v for k, v in b.items() if k in ("input_ids", "attention_mask", "labels", "cu_seqlens",
+                                                          "max_seqlen", "position_ids")})
+        # rebuild the padded view of the very same (masked) tokens and labels, sequence by sequence
+        flat_ids = b["input_ids"].reshape(-1)
+        flat_lab = b["labels"].reshape(-1)
+        if not static:
+            keep = b["attention_mask"].reshape(-1).bool()
+            flat_ids, flat_lab = flat_ids[keep], flat_lab[keep]
+        cu = b["cu_seqlens"].tolist()
+        rows = [(flat_ids[s:e], flat_lab[s:e]) for s, e in zip(cu[:-1], cu[1:]) if e > s and flat_ids[s] != tok.pad_token_id]
+        L = max(len(r[0]) for r in rows)
+        ids = torch.full((len(rows), L), tok.pad_token_id, dtype=torch.long)
+        lab = torch.full((len(rows), L), -100, dtype=torch.long)
+        msk = torch.zeros((len(rows), L), dtype=torch.long)
+        for i, (a, l) in enumerate(rows):
+            ids[i, :len(a)], lab[i, :len(a)], msk[i, :len(a)] = a, l, 1
+        with torch.no_grad():
+            r = rm(input_ids=ids, attention_mask=msk, labels=lab)
+        assert abs(float(r["loss"]) - float(o["loss"])) < 3e-5, f"static={static}"
+
+
+def test_checkpoints_are_interchangeable(ref, tmp_path):
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    rm, om = _pair(ref)
+    om.train()
+    hyper = AdamWHyper(lr=1e-3, weight_decay=0.01)
+    eng = ShardedEngine(om, hyper, torch.device("cpu"))
+    tok = ref.Tokenizer()
+    enc = tok(_sequences(4, 10, 40, seed=5), padding=True, return_tensors="pt")
+    labels = enc["input_ids"].clone()
+    labels[enc["attention_mask"] == 0] = -100
+    for _ in range(2):
+        om(input_ids=enc["input_ids"], attention_mask=enc["attention_mask"], labels=labels)["loss"].backward()
+        eng.step(1e-3, 1)
+    sched = WarmupLinearSchedule(1e-3, 1, 10)
+    d = ckpt.save_checkpoint(eng, sched, 2, 0, str(tmp_path), 1, 1, 1)
+    # (a) this package's files load through the reference's own loader into its model + AdamW
+    cfg = types.SimpleNamespace(optimizer="adamw", adam_weight_decay=0.01, adam_learning_rate=1e-3,
+                                adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8)
+    r2 = ref.Model(ref.Config(vocab_size=32, **GEOM)).float()
+    opt = ref.pipeline._create_optimizer(r2, cfg)
+    lam = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: 1.0)
+    torch.save(lam.state_dict(), Path(d) / "scheduler.pt")   # the reference's scheduler is a LambdaLR
+    step, epoch = ref.pipeline._load_checkpoint(r2, opt, lam, str(d), torch.device("cpu"))
+    assert (step, epoch) == (2, 0)
+    full = eng.full_state_dict_model()
+    for k, v in r2.state_dict().items():
+        assert torch.equal(v, full[k]), k
+    st = opt.state_dict()["state"]
+    assert len(st) == len(list(r2.parameters())) and all(float(s["step"]) == 2.0 for s in st.values())
+    named = dict(r2.named_parameters())
+    decay = [n for n, p in named.items() if ref.pipeline._use_weight_decay(n, p)]
+    first = opt.state[named[decay[0]]]["exp_avg"]
+    assert first.shape == named[decay[0]].shape and first.abs().sum() > 0
+    # (b) files written by the reference's saver load here
+    out = tmp_path / "refrun"
+    ref.pipeline._save_checkpoint(r2, opt, lam, 7, 1, str(out), 1, 1, 1)
+    om2 = type(om)(om.config, om.tokenizer).float()
+    eng2 = ShardedEngine(om2, hyper, torch.device("cpu"))
+    sched2 = WarmupLinearSchedule(1e-3, 1, 10)
+    torch.save(sched.state_dict(), out / "checkpoint-7" / "scheduler.pt")
+    step, epoch = ckpt.load_checkpoint(eng2, sched2, str(out / "checkpoint-7"))
+    assert (step, epoch) == (7, 1)
+    back = eng2.full_state_dict_model()
+    for k, v in r2.state_dict().items():
+        assert torch.equal(v, back[k]), k
+    a, b = eng.optimizer_state_dict()["state"], eng2.optimizer_state_dict()["state"]
+    assert a.keys() == b.keys() and all(torch.equal(a[i]["exp_avg_sq"], b[i]["exp_avg_sq"]) for i in a)
+
+
+def test_tokenizer_ids_match(ref):
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    rt, ot = ref.Tokenizer(), ProtTokenizer()
+    seqs = ["MKTAYIAKQR", "mktayiakqr", "ACDEFGHIKLMNPQRSTVWY", "UZOBXuzobx", "A", "MKT" * 50]
+    assert rt.get_vocab() == ot.get_vocab()
+    for name in ("pad_token_id", "eos_token_id", "unk_token_id", "mask_token_id"):
+        assert getattr(rt, name) == getattr(ot, name), name
+    assert sorted(rt.all_special_ids) == sorted(ot.all_special_ids)
+    for s in seqs:
+        assert rt.encode(s) == ot.encode(s), s
+    a = rt(seqs, padding=True, return_tensors="pt")
+    b = ot(seqs, padding=True, return_tensors="pt")
+    assert torch.equal(a["input_ids"], b["input_ids"]) and torch.equal(a["attention_mask"], b["attention_mask"])
+    a = rt(seqs, padding="max_length", max_length=32, truncation=True, return_tensors="pt")
+    b = ot(seqs, padding="max_length", max_length=32, truncation=True, return_tensors="pt")
+    assert torch.equal(a["input_ids"], b["input_ids"])
+
+
+@pytest.mark.parametrize("static", [False, True], ids=["dynamic", "static"])
+def test_packing_collator_layout_matches(ref, static):
+    """Both collators pack first-fit-decreasing: with masking off they must emit the same tokens,
+    cu_seqlens and position ids; with masking on, the invariants of the reference's own collator
+    tests hold for both."""
+    from nanoplm_b200.data.collators import PackingCollator
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    rt, ot = ref.Tokenizer(), ProtTokenizer()
+    seqs = _sequences(12, 3, 60, seed=21)
+    ex_r = [{"input_ids": torch.tensor(rt.encode(s))} for s in seqs]
+    ex_o = [{"input_ids": torch.tensor(ot.encode(s))} for s in seqs]
+    kw = dict(target_rows=8, batch_size=len(seqs)) if static else {}
+    rc = ref.collator.PackingCollator(rt, 64, mlm_probability=0.0, **kw)
+    oc = PackingCollator(ot, 64, 0.0, seed=0, **kw)
+    a, b = rc(ex_r), oc(ex_o)
+    assert torch.equal(a["input_ids"], b["input_ids"])
+    assert torch.equal(a["cu_seqlens"].to(torch.int32), b["cu_seqlens"].to(torch.int32))
+    assert int(a["max_seqlen"]) == int(b["max_seqlen"])
+    if static:
+        assert torch.equal(a["position_ids"], b["position_ids"])
+        assert a["input_ids"].shape == (8 * 64,) and a["cu_seqlens"].numel() == len(seqs) + 1 + 8
+    else:
+        assert torch.equal(a["attention_mask"], b["attention_mask"])
+    assert bool((a["labels"] == -100).all()) and bool((b["labels"] == -100).all())
+    # masking on: invariants (labels only on real non-special tokens, the original id as label,
+    # replaced ids inside the amino-acid pool, roughly the requested fraction)
+    rc = ref.collator.PackingCollator(rt, 64, mlm_probability=0.3, **kw)
+    oc = PackingCollator(ot, 64, 0.3, seed=1, **kw)
+    clean = a["input_ids"].reshape(-1)
+    special = torch.tensor(sorted(ot.all_special_ids))
+    for out in (rc(ex_r), oc(ex_o)):
+        ids, lab = out["input_ids"].reshape(-1), out["labels"].reshape(-1)
+        m = lab != -100
+        assert torch.equal(lab[m], clean[m])
+        assert not torch.isin(clean[m], special).any()
+        assert torch.equal(ids[~m], clean[~m])
+        changed = ids[m] != clean[m]
+        pool_or_mask = (ids[m][changed] == ot.mask_token_id) | (ids[m][changed] >= 4)
+        assert bool(pool_or_mask.all())
+        n_real = int((~torch.isin(clean, special)).sum())
+        assert 0.15 < m.sum().item() / n_real < 0.45

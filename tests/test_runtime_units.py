@@ -12,7 +12,7 @@ from nanoplm_b200.runtime.run_dirs import (archive_future_checkpoints, compute_b
                                            prepare_run_and_steps)
 from nanoplm_b200.runtime.schedule import (WarmupLinearSchedule, get_warmup_steps, make_distill_schedule,
                                            num_update_steps_per_epoch)
-from nanoplm_b200.runtime.watchdog import Heartbeat, RankFailure, check_or_raise, find_stalled
+from nanoplm_b200.runtime.watchdog import Heartbeat, RankFailure, Watchdog, check_or_raise, find_stalled
 
 
 def test_warmup_linear_schedule_matches_torch_lambda_lr():
@@ -123,6 +123,22 @@ def test_heartbeat_and_watchdog(tmp_path):
         check_or_raise(tmp_path, 2, 0.3)
     assert e.value.ranks == [1]
     hb0.stop()
+
+
+def test_watchdog_sees_a_rank_that_beats_but_makes_no_progress(tmp_path):
+    """A rank stuck in a collective keeps its beat thread alive; only its step counter stops."""
+    hb0 = Heartbeat(tmp_path, 0, interval=0.05).start()
+    hb1 = Heartbeat(tmp_path, 1, interval=0.05).start()
+    fired = []
+    wd = Watchdog(tmp_path, 2, max_age=5.0, max_step_age=0.4, interval=0.05, on_stall=fired.append).start()
+    for step in range(1, 10):          # rank 0 advances, rank 1 stays at step 0 (but keeps beating)
+        hb0.step = step
+        time.sleep(0.08)
+    wd.stop()
+    assert fired == [[1]] and wd.fired == [1]
+    assert find_stalled(tmp_path, 2, max_age=5.0) == []          # by file age alone nobody is stalled
+    hb0.stop()
+    hb1.stop()
 
 
 def test_padding_tail_trim_is_exact_on_cpu():

@@ -30,7 +30,7 @@ def test_vocabulary_ids_and_text_handling(tok):
     assert tok.encode("UZOB") == [24, 24, 24, 24, 1]                 # rare residues read as X
     assert tok.encode("M*") == [20, 2, 1]                            # unknown character
     assert ProtTokenizer(use_bos_token=True).encode("MK") == [29, 20, 15, 1]
-    assert tok.encode("MKTAY", max_length=3) == [20, 15, 12]
+    assert tok.encode("MKTAY", max_length=3) == [20, 15, 1]             # truncation keeps </s> (as the reference does)
     assert tok.all_special_ids == [0, 1, 2, 3]
     assert tok.decode([20, 15, 12, 1], skip_special_tokens=True) == "MKT"
 
