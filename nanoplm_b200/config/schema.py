@@ -57,6 +57,7 @@ class ModelConfig:
     unk_token_id: int = 2
     mask_token_id: int = 3
     # --- additive keys ----------------------------------------------------------------------------
+    embedding_dropout: float = 0.0       # after the embedding norm (fixed at 0 in the reference's config)
     norm_type: str = "layernorm"         # layernorm | rmsnorm
     conv_kernel_size: int = 0            # 0 = no conv, 7 = varlen depthwise conv before attention
     conv_bias: bool = False
@@ -82,6 +83,18 @@ class ModelConfig:
             raise ValueError("conv_kernel_size must be 0 (off) or an odd size <= 9")
         if self.mhc_streams < 1:
             raise ValueError("mhc_streams must be >= 1")
+        for name in ("mlp_dropout", "attention_dropout", "embedding_dropout"):
+            v = float(getattr(self, name))
+            if not 0.0 <= v < 1.0:
+                raise ValueError(f"{name} must be in [0, 1), got {v}")
+            setattr(self, name, v)
+        if self.attention_dropout > 0.0:
+            # the reference drops attention probabilities inside flash-attn (dropout_p) and the
+            # output projection (modeling.py:310-325, 359); the attention kernels here have no
+            # probability dropout, and silently ignoring the setting would change the training recipe
+            raise ValueError("attention_dropout > 0 is not supported: the varlen attention kernels implement no "
+                             "dropout on attention probabilities; set attention_dropout: 0.0 "
+                             "(mlp_dropout and embedding_dropout are supported)")
 
     @property
     def head_dim(self) -> int:
@@ -157,6 +170,9 @@ class PretrainingConfig:
     metrics_jsonl: bool = True           # write metrics.jsonl next to the checkpoints
     heartbeat_seconds: float = 0.0       # > 0 enables the per-rank heartbeat / watchdog
     heartbeat_stall_seconds: float = 0.0  # > 0: rank 0 ends the job when a rank's step stops advancing this long
+    balance_ranks: bool = True           # deal each optimizer step's sequences to ranks / micro-batches by cost
+    balance_quadratic: float = 1.0 / 2700.0   # cost(len) = len + balance_quadratic * len^2
+    shard_params: bool = False           # keep 1/N of every layer's weights per rank, gather inside the GEMMs
 
 
 @dataclass

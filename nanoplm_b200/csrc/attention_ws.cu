@@ -41,8 +41,27 @@ struct FaWsArgs {
   int* status;
 };
 
+// Optional in-kernel trace for tuning (compiled in with -DNPLM_WS_TRACE only): when a buffer has been
+// registered (nplm_fa_ws_set_trace), CTA 0 records (clock64 << 8 | event) per role: role 0 = MMA
+// issuer, 1 / 2 = lane 0 of one warp of two compute warpgroups, 3 = loader. 1024 slots per role, in
+// order; the host clears the buffer first and reads up to the first zero.
+#ifdef NPLM_WS_TRACE
+__device__ long long* g_ws_trace = nullptr;
+#define WS_TRACE_INIT()                                                       \
+  long long* const tr_base = (blockIdx.x == 0) ? g_ws_trace : nullptr;        \
+  int tr_n = 0
+#define WS_TRACE(cond, role, ev)                                                        \
+  do {                                                                                  \
+    if (tr_base != nullptr && (threadIdx.x & 31) == 0 && (cond) && tr_n < 1024)         \
+      tr_base[(role) * 1024 + tr_n++] = (clock64() << 8) | (ev);                        \
+  } while (0)
+#else
+#define WS_TRACE_INIT() do { } while (0)
+#define WS_TRACE(cond, role, ev) do { } while (0)
+#endif
+
 constexpr int WS_KV_STAGES = 3;
-constexpr int WS_THREADS = 384;   // 2 softmax warpgroups (warps 0-7), then loader warp 8, MMA warp 9, 2 idle warps
+constexpr int WS_THREADS = 384;   // 2 softmax warpgroups (warps 0-7), then loader warp 8, MMA warps 9 / 10, 1 idle warp
 constexpr int WS_LOADER_WARP = 8, WS_MMA_WARP = 9;
 // setmaxnreg: the loader / MMA warpgroup drops to WS_REGS_LIGHT registers per thread, the two
 // compute warpgroups grow to WS_REGS_HEAVY. The increase BLOCKS until the CTA's register pool holds
@@ -135,17 +154,17 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
-      mbar_init(&q_empty[i], 1);
+      mbar_init(&q_empty[i], 2);     // both MMA issuers
       mbar_init(&s_full[i], 1);
       mbar_init(&s_free[i], 4);      // one lane of each softmax warp
-      mbar_init(&p_ready[i], 128);   // every thread of the warpgroup, after its own proxy fence
+      mbar_init(&p_ready[i], 4);     // one lane per softmax warp, after every lane's proxy fence
       mbar_init(&pv_done[i], 1);
     }
     for (int i = 0; i < WS_KV_STAGES; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&k_empty[i], 2);     // both MMA issuers
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&v_empty[i], 2);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -162,6 +181,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // columns: S0 [0,128), S1 [128,256), O0 [256,320), O1 [320,384)
+  WS_TRACE_INIT();
 
   if (warp >= 8) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_REGS_LIGHT));
@@ -186,6 +206,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
           if (!mbar_wait(&k_empty[st], ph ^ 1u)) { ok = false; break; }
           mbar_arrive_expect_tx(&k_full[st], FA_TILE_BYTES);
           tma_load_2d(sK + st * FA_TILE_BYTES, &tmQKV, &k_full[st], colK, kv0);
+          WS_TRACE(true, 3, 1);
           if (!mbar_wait(&v_empty[st], ph ^ 1u)) { ok = false; break; }
           mbar_arrive_expect_tx(&v_full[st], FA_TILE_BYTES);
           tma_load_2d(sV + st * FA_TILE_BYTES, &tmQKV, &v_full[st], colV, kv0);
@@ -198,40 +219,46 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         *abort_flag = 1;
       }
     }
-  } else if (warp == WS_MMA_WARP) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == WS_MMA_WARP || warp == WS_MMA_WARP + 1) {
+    // ------------------------------------------------------------------ MMA issuers
+    // One issuing thread per query tile: the two tiles then advance independently (a tile whose
+    // probabilities are late does not hold back the other tile's next score tile), and the issue
+    // work of a step (12 instructions per tile) is spread over two schedulers. Descriptors of a
+    // tile are formed once; a step inside a tile only adds to the 14-bit address field.
     if (lane == 0) {
+      const int i = warp - WS_MMA_WARP;
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
       uint32_t qc = 0, kc = 0;
-      uint32_t s_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
+      uint32_t s_cnt = 0, p_cnt = 0;
       bool ok = true;
       int why = ST_TIMEOUT_FULL;
+      const uint32_t tS = tmem_base + i * 128;
+      const uint32_t tO = tmem_base + 256 + i * 64;
+      const uint64_t dP0 = make_smem_desc(smem_u32(sP + i * 2 * FA_TILE_BYTES), 16, 1024);
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const WsGeo g = ws_geometry(args, item / H);
         const uint32_t qb = qc & 1u;
         if (!mbar_wait(&q_full[qb], (qc >> 1) & 1u)) { ok = false; break; }
+        const uint64_t dQ0 = make_smem_desc(smem_u32(sQ + (qb * 2 + i) * FA_TILE_BYTES), 16, 1024);
         for (int j = 0; j <= g.n && ok; ++j) {
           if (j < g.n) {   // scores of key tile j
             const uint32_t st = (kc + j) % WS_KV_STAGES, ph = ((kc + j) / WS_KV_STAGES) & 1u;
             if (!mbar_wait(&k_full[st], ph)) { ok = false; break; }
-            const uint32_t ka = smem_u32(sK + st * FA_TILE_BYTES);
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              if (j < g.a[i] || j >= g.b[i]) continue;
+            WS_TRACE(true, 0, 1);
+            if (j >= g.a[i] && j < g.b[i]) {
               // the warpgroup holds the previous score tile in registers
-              if (!mbar_wait(&s_free[i], (s_cnt[i] & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
+              if (!mbar_wait(&s_free[i], (s_cnt & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
               tc_fence_after();
-              const uint32_t qa = smem_u32(sQ + (qb * 2 + i) * FA_TILE_BYTES);
-              const uint32_t tS = tmem_base + i * 128;
+              const uint64_t dK0 = make_smem_desc(smem_u32(sK + st * FA_TILE_BYTES), 16, 1024);
 #pragma unroll
-              for (int k = 0; k < FA_D / 16; ++k)
-                umma_bf16(tS, make_smem_desc(qa + k * 32, 16, 1024), make_smem_desc(ka + k * 32, 16, 1024),
-                          idesc_s, k > 0 ? 1u : 0u);
+              for (int k = 0; k < FA_D / 16; ++k)   // 32 bytes along the row per 16 channels
+                umma_bf16(tS, dQ0 + 2 * k, dK0 + 2 * k, idesc_s, k > 0 ? 1u : 0u);
               umma_commit(&s_full[i]);
-              ++s_cnt[i];
+              ++s_cnt;
+              WS_TRACE(true, 0, 2);
             }
-            if (!ok) break;
+            // both issuers release the stage (a commit with nothing outstanding arrives at once)
             umma_commit(&k_empty[st]);
             if (j == g.n - 1) umma_commit(&q_empty[qb]);
           }
@@ -239,22 +266,20 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
             const int jj = j - 1;
             const uint32_t st = (kc + jj) % WS_KV_STAGES, ph = ((kc + jj) / WS_KV_STAGES) & 1u;
             if (!mbar_wait(&v_full[st], ph)) { ok = false; break; }
-            const uint32_t va = smem_u32(sV + st * FA_TILE_BYTES);
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              if (jj < g.a[i] || jj >= g.b[i]) continue;
-              if (!mbar_wait(&p_ready[i], p_cnt[i] & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
+            if (jj >= g.a[i] && jj < g.b[i]) {
+              if (!mbar_wait(&p_ready[i], p_cnt & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
+              WS_TRACE(true, 0, 3);
               tc_fence_after();
-              const uint32_t pa = smem_u32(sP + i * 2 * FA_TILE_BYTES);
-              const uint32_t tO = tmem_base + 256 + i * 64;
+              const uint64_t dV0 = make_smem_desc(smem_u32(sV + st * FA_TILE_BYTES), 8192, 1024);
 #pragma unroll
-              for (int k = 0; k < FA_T / 16; ++k)
-                umma_bf16(tO, make_smem_desc(pa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
-                          make_smem_desc(va + k * 2048, 8192, 1024), idesc_o, (jj > g.a[i] || k > 0) ? 1u : 0u);
+              for (int k = 0; k < FA_T / 16; ++k)   // P: 32 bytes per 16 keys, next column block after 4;
+                                                    // V: 16 key rows = 2048 bytes
+                umma_bf16(tO, dP0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dV0 + k * (2048 >> 4), idesc_o,
+                          (jj > g.a[i] || k > 0) ? 1u : 0u);
               umma_commit(&pv_done[i]);
-              ++p_cnt[i];
+              ++p_cnt;
+              WS_TRACE(true, 0, 4);
             }
-            if (!ok) break;
             umma_commit(&v_empty[st]);
           }
         }
@@ -305,6 +330,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         ++s_cnt;
         ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
         if (!ok) break;
+        WS_TRACE(quarter == 0, 1 + i, 1);
         tc_fence_after();
         const bool none = (kv0 + FA_T <= lo) || (kv0 >= hi);
         const bool warp_none = __all_sync(0xffffffffu, none);
@@ -318,6 +344,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_free[i]);   // the score tile may be overwritten
+        WS_TRACE(quarter == 0, 1 + i, 2);
 
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (!warp_none) {
@@ -349,6 +376,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
           ++pv_cnt;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          WS_TRACE(quarter == 0, 1 + i, 4);
           tc_fence_after();
           if (warp_need) {
 #pragma unroll
@@ -390,7 +418,9 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(&p_ready[i]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[i]);
+        WS_TRACE(quarter == 0, 1 + i, 3);
       }
       if (!ok) break;
       // last output update of this item
@@ -421,6 +451,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
       tc_fence_before();
       if (row_ok)
         args.lse[static_cast<size_t>(h) * T + row] = l_run > 0.f ? m_used * args.scale + __logf(l_run) : 0.f;
+      WS_TRACE(quarter == 0, 1 + i, 5);
     }
     if (!ok && lane == 0 && *abort_flag == 0) {
       atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
@@ -492,7 +523,27 @@ __device__ __forceinline__ WsBwdGeo ws_bwd_geometry(const FaWsBwdArgs& args, int
   return g;
 }
 
-__global__ void __launch_bounds__(WS_THREADS, 1)
+// NWG compute warpgroups share the key columns of a step: warpgroup g handles columns
+// [g * 128 / NWG, +128 / NWG) of every query row. Four warpgroups put four compute warps on every
+// scheduler (the per-element work has no cross-thread dependency, so the split is free) at 104
+// registers per thread; two warpgroups run at 216.
+// DQ: also form dQ = dS K per step and add it to the fp32 accumulator with vector atomics. Without
+// it the kernel produces dK / dV only and dQ comes from fa_dq_ws_kernel (no atomics, no scratch,
+// bitwise reproducible).
+template <int NWG>
+struct WsBwdCfg {
+  static constexpr int THREADS = (NWG + 1) * 128;
+  static constexpr int LOADER_WARP = NWG * 4, MMA_WARP = NWG * 4 + 1;
+  static constexpr int CPT = FA_T / NWG;              // key columns per thread
+  static constexpr int REGS_LAUNCH = NWG == 2 ? 168 : 96;
+  static constexpr int REGS_LIGHT = NWG == 2 ? 72 : 56;
+  static constexpr int REGS_HEAVY = NWG == 2 ? 216 : 104;
+  static_assert(128 * REGS_LIGHT + NWG * 128 * REGS_HEAVY <= THREADS * REGS_LAUNCH,
+                "setmaxnreg.inc would wait forever for registers the CTA does not own");
+};
+
+template <int NWG, bool DQ>
+__global__ void __launch_bounds__(WsBwdCfg<NWG>::THREADS, 1)
 fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                  const FaWsBwdArgs args) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -520,6 +571,8 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  using Cfg = WsBwdCfg<NWG>;
+  constexpr int CPT = Cfg::CPT;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -530,25 +583,25 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&kv_empty[i], DQ ? 2 : 1);   // issuer A, and C when it runs
     }
     for (int i = 0; i < WSB_Q_STAGES; ++i) {
       mbar_init(&qdo_full[i], 1);
-      mbar_init(&qdo_empty[i], 1);
+      mbar_init(&qdo_empty[i], 2);           // issuers A and B
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_free, 8);       // one lane of each compute warp
-    mbar_init(pds_ready, 256);    // every compute thread, after its own proxy fence
-    mbar_init(g_done, 1);
-    mbar_init(dq_free, 8);
-    mbar_init(acc_free, 8);
+    mbar_init(sdp_free, NWG * 4);   // one lane of each compute warp
+    mbar_init(pds_ready, NWG * 4);     // one lane per compute warp, after every lane's proxy fence
+    mbar_init(g_done, DQ ? 2 : 1);           // issuer B, and C when it runs
+    mbar_init(dq_free, NWG * 4);
+    mbar_init(acc_free, 8);       // the two warpgroups that read dK / dV back
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
   }
-  if (warp == WS_MMA_WARP) {
+  if (warp == Cfg::MMA_WARP) {
     __syncwarp();
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
@@ -562,10 +615,11 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   const uint32_t tdQ = tmem_base + 256;   // dQ  [q][d]   64 columns
   const uint32_t tdK = tmem_base + 320;   // dK  [kv][d]  64 columns
   const uint32_t tdV = tmem_base + 384;   // dV  [kv][d]  64 columns
+  WS_TRACE_INIT();
 
-  if (warp >= 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_REGS_LIGHT));
-  if (warp == WS_LOADER_WARP) {
+  if (warp >= NWG * 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_LIGHT));
+  if (warp == Cfg::LOADER_WARP) {
     // ------------------------------------------------------------------ loader
     if (lane == 0) {
       uint32_t ic = 0, qc = 0;
@@ -592,83 +646,114 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         *abort_flag = 1;
       }
     }
-  } else if (warp == WS_MMA_WARP) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, 1, 1);   // A MN-major, B MN-major
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, 0, 1);  // A K-major, B MN-major
-      uint32_t ic = 0, qc = 0;       // items, query steps started so far
-      uint32_t c_sdp = 0, c_pds = 0, c_dq = 0;
-      bool ok = true;
-      int why = ST_TIMEOUT_FULL;
-      const uint32_t pa = smem_u32(sP), sa = smem_u32(sdS);
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Three issuing threads, one per kind of product, so that a step's 24 - 32 instructions do not
+    // queue behind one thread: A issues S = Q K^T and dP = dO V^T of the NEXT step as soon as the
+    // warpgroups hold the current one in registers; B issues dV += P^T dO and dK += dS^T Q; C issues
+    // dQ = dS K (only with DQ). Descriptors are formed once per buffer; a step adds to the address
+    // field. Buffers read by several issuers are released by all of them (barrier counts).
+    const int role = warp - Cfg::MMA_WARP;            // 0 = A, 1 = B, 2 = C
+    constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+    constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, 1, 1);   // A MN-major, B MN-major
+    constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, 0, 1);  // A K-major, B MN-major
+    uint32_t ic = 0, qc = 0;       // items, query steps started so far
+    uint32_t c_sdp = 0, c_pds = 0, c_dq = 0;
+    bool ok = true;
+    int why = ST_TIMEOUT_FULL;
+    if (role == 0) {
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
         const WsBwdGeo g = ws_bwd_geometry(args, item / H);
         const uint32_t kb = ic & 1u;
         if (!mbar_wait(&kv_full[kb], (ic >> 1) & 1u)) { ok = false; break; }
-        const uint32_t ka = smem_u32(sK + kb * FA_TILE_BYTES), va = smem_u32(sV + kb * FA_TILE_BYTES);
-        auto issue_sdp = [&](uint32_t step) -> bool {
+        const uint64_t dK0 = make_smem_desc(smem_u32(sK + kb * FA_TILE_BYTES), 16, 1024);
+        const uint64_t dV0 = make_smem_desc(smem_u32(sV + kb * FA_TILE_BYTES), 16, 1024);
+        for (int j = 0; j < g.n_q; ++j) {
+          const uint32_t step = qc + j;
           const uint32_t st = step % WSB_Q_STAGES, ph = (step / WSB_Q_STAGES) & 1u;
-          if (!mbar_wait(&qdo_full[st], ph)) return false;
-          if (!mbar_wait(sdp_free, (c_sdp & 1u) ^ 1u)) { why = ST_TIMEOUT_TMEM_EMPTY; return false; }
+          if (!mbar_wait(&qdo_full[st], ph)) { ok = false; break; }
+          if (!mbar_wait(sdp_free, (c_sdp & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
           tc_fence_after();
-          const uint32_t qa = smem_u32(sQ + st * FA_TILE_BYTES), da = smem_u32(sdO + st * FA_TILE_BYTES);
+          const uint64_t dQ0 = make_smem_desc(smem_u32(sQ + st * FA_TILE_BYTES), 16, 1024);
+          const uint64_t dO0 = make_smem_desc(smem_u32(sdO + st * FA_TILE_BYTES), 16, 1024);
 #pragma unroll
           for (int k = 0; k < FA_D / 16; ++k)
-            umma_bf16(tS, make_smem_desc(qa + k * 32, 16, 1024), make_smem_desc(ka + k * 32, 16, 1024),
-                      idesc_s, k > 0 ? 1u : 0u);
+            umma_bf16(tS, dQ0 + 2 * k, dK0 + 2 * k, idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
           for (int k = 0; k < FA_D / 16; ++k)
-            umma_bf16(tdP, make_smem_desc(da + k * 32, 16, 1024), make_smem_desc(va + k * 32, 16, 1024),
-                      idesc_s, k > 0 ? 1u : 0u);
+            umma_bf16(tdP, dO0 + 2 * k, dV0 + 2 * k, idesc_s, k > 0 ? 1u : 0u);
           umma_commit(sdp_full);
           ++c_sdp;
-          return true;
-        };
-        if (g.n_q > 0 && !issue_sdp(qc)) { ok = false; break; }
+          umma_commit(&qdo_empty[st]);     // with issuer B
+          WS_TRACE(true, 0, 1);
+        }
+        if (!ok) break;
+        umma_commit(&kv_empty[kb]);        // with issuer C when dQ is formed here
+        qc += g.n_q;
+        if (*abort_flag) ok = false;
+      }
+    } else if (role == 1) {
+      const uint64_t dPT = make_smem_desc(smem_u32(sP), FA_TILE_BYTES, 1024);    // P^T / dS^T as MN-major A
+      const uint64_t dST = make_smem_desc(smem_u32(sdS), FA_TILE_BYTES, 1024);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
+        const WsBwdGeo g = ws_bwd_geometry(args, item / H);
         for (int j = 0; j < g.n_q; ++j) {
           const uint32_t step = qc + j;
           const uint32_t st = step % WSB_Q_STAGES;
-          if (j + 1 < g.n_q && !issue_sdp(step + 1)) { ok = false; break; }
           if (!mbar_wait(pds_ready, c_pds & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
           ++c_pds;
+          WS_TRACE(true, 3, 2);
           if (j == 0 && !mbar_wait(acc_free, (ic & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
           tc_fence_after();
-          const uint32_t qa = smem_u32(sQ + st * FA_TILE_BYTES), da = smem_u32(sdO + st * FA_TILE_BYTES);
+          const uint64_t dQ0 = make_smem_desc(smem_u32(sQ + st * FA_TILE_BYTES), 8192, 1024);   // MN-major B
+          const uint64_t dO0 = make_smem_desc(smem_u32(sdO + st * FA_TILE_BYTES), 8192, 1024);
 #pragma unroll
-          for (int k = 0; k < FA_T / 16; ++k)   // dV[kv][d] += P^T[kv][q] dO[q][d]
-            umma_bf16(tdV, make_smem_desc(pa + k * 2048, FA_TILE_BYTES, 1024),
-                      make_smem_desc(da + k * 2048, 8192, 1024), idesc_g, (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < FA_T / 16; ++k)   // dV[kv][d] += P^T[kv][q] dO[q][d]; 16 query rows = 2048 bytes
+            umma_bf16(tdV, dPT + k * 128, dO0 + k * 128, idesc_g, (j > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
           for (int k = 0; k < FA_T / 16; ++k)   // dK[kv][d] += dS^T[kv][q] Q[q][d]
-            umma_bf16(tdK, make_smem_desc(sa + k * 2048, FA_TILE_BYTES, 1024),
-                      make_smem_desc(qa + k * 2048, 8192, 1024), idesc_g, (j > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tdK, dST + k * 128, dQ0 + k * 128, idesc_g, (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(g_done);                 // with issuer C when dQ is formed here
+          umma_commit(&qdo_empty[st]);
+          WS_TRACE(true, 3, 3);
+        }
+        if (!ok) break;
+        qc += g.n_q;
+        if (*abort_flag) ok = false;
+      }
+    } else if (role == 2 && DQ) {
+      const uint64_t dS0 = make_smem_desc(smem_u32(sdS), 16, 1024);              // dS as K-major A
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
+        const WsBwdGeo g = ws_bwd_geometry(args, item / H);
+        const uint32_t kb = ic & 1u;
+        if (!mbar_wait(&kv_full[kb], (ic >> 1) & 1u)) { ok = false; break; }
+        const uint64_t dK0 = make_smem_desc(smem_u32(sK + kb * FA_TILE_BYTES), 8192, 1024);     // MN-major B
+        for (int j = 0; j < g.n_q; ++j) {
+          if (!mbar_wait(pds_ready, c_pds & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
+          ++c_pds;
           if (!mbar_wait(dq_free, (c_dq & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < FA_T / 16; ++k)   // dQ[q][d] = dS[q][kv] K[kv][d]
-            umma_bf16(tdQ, make_smem_desc(sa + (k >> 2) * FA_TILE_BYTES + (k & 3) * 32, 16, 1024),
-                      make_smem_desc(ka + k * 2048, 8192, 1024), idesc_dq, k > 0 ? 1u : 0u);
+            umma_bf16(tdQ, dS0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dK0 + k * 128, idesc_dq,
+                      k > 0 ? 1u : 0u);
           ++c_dq;
           umma_commit(g_done);
-          umma_commit(&qdo_empty[st]);
         }
         if (!ok) break;
         umma_commit(&kv_empty[kb]);
-        qc += g.n_q;
         if (*abort_flag) ok = false;
       }
-      if (!ok && *abort_flag == 0) {
-        atomicExch(args.status, why);
-        *abort_flag = 1;
-      }
+    }
+    if (!ok && *abort_flag == 0) {
+      atomicExch(args.status, why);
+      *abort_flag = 1;
     }
   }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WS_REGS_HEAVY));
-    const int gh = warp >> 2;               // key-column half of this warpgroup
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_HEAVY));
+    const int gh = warp >> 2;               // key-column slice of this warpgroup
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;      // query row inside the tile (= key row for dK / dV)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
@@ -693,22 +778,26 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
       }
       return ri;
     };
-    // dQ tile of the step whose query rows start at q0: this thread adds channels [32 gh, +32) of row q0 + r
+    // dQ tile of the step whose query rows start at q0: this thread adds its share of the channels of row q0 + r
     auto drain_dq = [&](int q0, int q_hi, int h) {
-      uint32_t v[32];
-      tmem_ld32(tdQ + lane_addr + gh * 32, v);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_free);
-      const int q = q0 + r;
-      if (q < T && q < q_hi) {
-        float* dst = args.dq_acc + static_cast<size_t>(q) * HD + h * FA_D + gh * 32;
+      if constexpr (DQ) {
+        constexpr int DQC = FA_D / NWG;       // dQ channels per thread
+        uint32_t v[DQC];
+        if constexpr (DQC == 32) tmem_ld32(tdQ + lane_addr + gh * DQC, v);
+        else tmem_ld16(tdQ + lane_addr + gh * DQC, v);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_free);
+        const int q = q0 + r;
+        if (q < T && q < q_hi) {
+          float* dst = args.dq_acc + static_cast<size_t>(q) * HD + h * FA_D + gh * DQC;
 #pragma unroll
-        for (int e = 0; e < 32; e += 4)
-          atomicAdd(reinterpret_cast<float4*>(dst + e),
-                    make_float4(__uint_as_float(v[e]) * args.scale, __uint_as_float(v[e + 1]) * args.scale,
-                                __uint_as_float(v[e + 2]) * args.scale, __uint_as_float(v[e + 3]) * args.scale));
+          for (int e = 0; e < DQC; e += 4)
+            atomicAdd(reinterpret_cast<float4*>(dst + e),
+                      make_float4(__uint_as_float(v[e]) * args.scale, __uint_as_float(v[e + 1]) * args.scale,
+                                  __uint_as_float(v[e + 2]) * args.scale, __uint_as_float(v[e + 3]) * args.scale));
+        }
       }
     };
 
@@ -724,52 +813,75 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         ++c_sdp;
         ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
         if (!ok) break;
+        WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 1);
         tc_fence_after();
-        uint32_t rs[64], rp[64];
-        tmem_ld32(tS + lane_addr + gh * 64, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
-        tmem_ld32(tS + lane_addr + gh * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
-        tmem_ld32(tdP + lane_addr + gh * 64, *reinterpret_cast<uint32_t(*)[32]>(&rp[0]));
-        tmem_ld32(tdP + lane_addr + gh * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&rp[32]));
+        uint32_t rs[CPT], rp[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT; c += 32) {
+          tmem_ld32(tS + lane_addr + gh * CPT + c, *reinterpret_cast<uint32_t(*)[32]>(&rs[c]));
+          tmem_ld32(tdP + lane_addr + gh * CPT + c, *reinterpret_cast<uint32_t(*)[32]>(&rp[c]));
+        }
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(sdp_free);
+        WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 2);
         if (j > 0) {
           // the previous step's dV / dK / dQ have finished: P / dS tiles are free, dQ can be read
           ok = mbar_wait(g_done, c_g & 1u);
           ++c_g;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 4);
           tc_fence_after();
           drain_dq(q0 - FA_T, g.q_hi, h);
         }
-        // keys of this thread's columns: [c0, c0 + 64)
-        const int c0 = g.kv0 + gh * 64;
-        const bool inside = __all_sync(0xffffffffu, c0 >= ri.klo && c0 + 64 <= ri.khi);
+        // keys of this thread's columns: [c0, c0 + CPT)
+        const int c0 = g.kv0 + gh * CPT;
+        const bool inside = __all_sync(0xffffffffu, c0 >= ri.klo && c0 + CPT <= ri.khi);
+        const bool outside = __all_sync(0xffffffffu, c0 >= ri.khi || c0 + CPT <= ri.klo);
+        // first 16-byte chunk of this thread: column block (gh * CPT) / 64, chunk ((gh * CPT) % 64) / 8
+        uint8_t* rowP = sP + ((gh * CPT) >> 6) * FA_TILE_BYTES + r * 128;
+        uint8_t* rowS = sdS + ((gh * CPT) >> 6) * FA_TILE_BYTES + r * 128;
+        const int chunk0 = ((gh * CPT) & 63) >> 3;
+        const int rx = r & 7;
+        if (outside) {
+          // no query row of this warp sees any of these keys (they belong to other sequences):
+          // zero tiles, no exponentials
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          uint32_t pk[4], dk[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int e = c8 * 8 + 2 * u;
-            float p0 = exp2f(fmaf(__uint_as_float(rs[e]), sl2, -ri.lse2));
-            float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), sl2, -ri.lse2));
-            if (!inside) {
-              const int key = c0 + e;
-              if (!(key >= ri.klo && key < ri.khi)) p0 = 0.f;
-              if (!(key + 1 >= ri.klo && key + 1 < ri.khi)) p1 = 0.f;
-            }
-            const float d0 = p0 * (__uint_as_float(rp[e]) - ri.delta);
-            const float d1 = p1 * (__uint_as_float(rp[e + 1]) - ri.delta);
-            pk[u] = pack_bf16x2(p0, p1);
-            dk[u] = pack_bf16x2(d0, d1);
+          for (int c8 = 0; c8 < CPT / 8; ++c8) {
+            const uint32_t off = static_cast<uint32_t>(((chunk0 + c8) ^ rx) << 4);
+            *reinterpret_cast<uint4*>(rowP + off) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(rowS + off) = make_uint4(0u, 0u, 0u, 0u);
           }
-          const uint32_t off = gh * FA_TILE_BYTES + swz(r, c8);
-          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          *reinterpret_cast<uint4*>(sdS + off) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+        } else {
+#pragma unroll
+          for (int c8 = 0; c8 < CPT / 8; ++c8) {
+            uint32_t pk[4], dk[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int e = c8 * 8 + 2 * u;
+              float p0 = exp2f(fmaf(__uint_as_float(rs[e]), sl2, -ri.lse2));
+              float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), sl2, -ri.lse2));
+              if (!inside) {
+                const int key = c0 + e;
+                if (!(key >= ri.klo && key < ri.khi)) p0 = 0.f;
+                if (!(key + 1 >= ri.klo && key + 1 < ri.khi)) p1 = 0.f;
+              }
+              const float d0 = p0 * (__uint_as_float(rp[e]) - ri.delta);
+              const float d1 = p1 * (__uint_as_float(rp[e + 1]) - ri.delta);
+              pk[u] = pack_bf16x2(p0, p1);
+              dk[u] = pack_bf16x2(d0, d1);
+            }
+            const uint32_t off = static_cast<uint32_t>(((chunk0 + c8) ^ rx) << 4);
+            *reinterpret_cast<uint4*>(rowP + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(rowS + off) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+          }
         }
         fence_proxy_async_smem();
-        mbar_arrive(pds_ready);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pds_ready);
+        WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 3);
       }
       if (!ok) break;
       if (g.n_q > 0) {
@@ -780,7 +892,9 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         tc_fence_after();
         drain_dq(g.q_lo + (g.n_q - 1) * FA_T, g.q_hi, h);
       }
+      WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 5);
       // dK (warpgroup 0) / dV (warpgroup 1): every thread owns the 64 channels of key row kv0 + r
+      if (gh >= 2) continue;
       float acc[FA_D];
       if (g.n_q > 0) {
         const uint32_t src = (gh == 0 ? tdK : tdV) + lane_addr;
@@ -844,7 +958,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
-  if (warp == WS_MMA_WARP) {
+  if (warp == Cfg::MMA_WARP) {
     tc_fence_after();
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
@@ -968,7 +1082,11 @@ static int ws_configure(int* sms) {
   if (!ws_device[dev].configured) {
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_FWD_SMEM));
-    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         WS_BWD_SMEM));
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         WS_BWD_SMEM));
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_BWD_SMEM));
     int n = 0;
     NPLM_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
@@ -1062,7 +1180,17 @@ extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout
   int grid = sms;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (grid > n_items) grid = n_items;
-  fa_bwd_ws_kernel<<<grid, WS_THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  static int mode = -1;   // NPLM_FA_BWD_MODE: 2 = two compute warpgroups, 4 = four (default), 0 = four, dK / dV only
+  if (mode < 0) {
+    const char* e = getenv("NPLM_FA_BWD_MODE");
+    mode = (e != nullptr && (e[0] == '2' || e[0] == '0')) ? e[0] - '0' : 4;
+  }
+  if (mode == 2)
+    fa_bwd_ws_kernel<2, true><<<grid, WsBwdCfg<2>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  else if (mode == 0)
+    fa_bwd_ws_kernel<4, false><<<grid, WsBwdCfg<4>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  else
+    fa_bwd_ws_kernel<4, true><<<grid, WsBwdCfg<4>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   {
     const long long total = static_cast<long long>(T) * H * 4;
     long long blocks = (total + 255) / 256;
@@ -1072,3 +1200,11 @@ extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout
   }
   return static_cast<int>(cudaGetLastError());
 }
+
+#ifdef NPLM_WS_TRACE
+// Registers (or clears, with null) the trace buffer of 4 x 1024 int64 for the following launches on
+// the current device; see WS_TRACE.
+extern "C" int nplm_fa_ws_set_trace(long long* buf) {
+  return static_cast<int>(cudaMemcpyToSymbol(g_ws_trace, &buf, sizeof(buf)));
+}
+#endif

@@ -96,4 +96,38 @@ int64_t nplm_pack_flatten(const uint8_t* tokens, const int64_t* offsets, const i
   return t;
 }
 
+// Deals n = n_bins * per_bin sequences into n_bins bins of exactly per_bin sequences each so that
+// the bins' costs are as equal as the greedy rule allows: sequences in order of decreasing cost,
+// each to the cheapest bin that still has room (longest-processing-time rule with a cardinality
+// limit). cost(len) = len + quad * len^2: the linear part stands for the per-token work of a
+// training step, the quadratic part for full attention inside a sequence. Ties go to the lowest
+// bin index, so every rank that runs this on the same lengths gets the same answer.
+//   bin_of[i]  : bin of sequence i
+//   bin_cost[b]: total cost of bin b
+// Returns 0, or -1 when n is not n_bins * per_bin.
+int nplm_balance_bins(const int32_t* lens, int n, int n_bins, int per_bin, double quad, int32_t* bin_of,
+                      double* bin_cost) {
+  if (n_bins <= 0 || per_bin <= 0 || n != n_bins * per_bin) return -1;
+  std::vector<double> cost(n);
+  for (int i = 0; i < n; ++i) cost[i] = lens[i] + quad * static_cast<double>(lens[i]) * lens[i];
+  std::vector<int> idx(n);
+  std::iota(idx.begin(), idx.end(), 0);
+  std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return cost[a] > cost[b]; });
+  std::vector<int> fill(n_bins, 0);
+  for (int b = 0; b < n_bins; ++b) bin_cost[b] = 0.0;
+  // n_bins is small (ranks x micro-batches of one optimizer step): a linear scan per sequence is
+  // cheaper than keeping a heap consistent with the cardinality limit
+  for (int k = 0; k < n; ++k) {
+    int best = -1;
+    for (int b = 0; b < n_bins; ++b) {
+      if (fill[b] >= per_bin) continue;
+      if (best < 0 || bin_cost[b] < bin_cost[best]) best = b;
+    }
+    bin_of[idx[k]] = best;
+    bin_cost[best] += cost[idx[k]];
+    ++fill[best];
+  }
+  return 0;
+}
+
 }  // extern "C"

@@ -55,9 +55,13 @@ class Embeddings(nn.Module):
         super().__init__()
         self.tok_embeddings = nn.Embedding(cfg.vocab_size, cfg.hidden_size, padding_idx=cfg.pad_token_id)
         self.norm = Norm(cfg.hidden_size, cfg.norm_eps, cfg.norm_type == "rmsnorm")
+        self.p_drop = float(cfg.embedding_dropout)
 
     def forward(self, ids):
-        return ops.embed_norm(ids, self.tok_embeddings.weight, self.norm.weight, self.norm.eps, self.norm.rms)
+        x = ops.embed_norm(ids, self.tok_embeddings.weight, self.norm.weight, self.norm.eps, self.norm.rms)
+        if self.p_drop > 0.0 and self.training:     # reference: modeling.py:220-223
+            x = F.dropout(x, self.p_drop, True)
+        return x
 
 
 class Attention(nn.Module):
@@ -94,15 +98,19 @@ class MLP(nn.Module):
         self.hidden_activation = cfg.hidden_activation
         self.Wi = Linear(cfg.hidden_size, 2 * inter, cfg.mlp_bias)
         self.Wo = Linear(inter, cfg.hidden_size, cfg.mlp_bias)
+        self.p_drop = float(cfg.mlp_dropout)
 
     def forward(self, x, residual=None):
-        if self.swiglu and self.Wi.bias is None and self.Wo.bias is None:
+        drop = self.p_drop > 0.0 and self.training
+        if self.swiglu and self.Wi.bias is None and self.Wo.bias is None and not drop:
             return ops.mlp_swiglu(x, self.Wi.weight, self.Wo.weight, residual)
         if self.swiglu:
             h = self.Wi(x, act="swiglu")
         else:  # GLU variant: act(value) * gate (reference: modeling.py:281-282)
             v, g = self.Wi(x).chunk(2, dim=-1)
             h = ops.activation(v.contiguous(), self.hidden_activation) * g
+        if drop:    # between the activation and the down-projection (reference: modeling.py:277, 298)
+            h = F.dropout(h, self.p_drop, True)
         return self.Wo(h, residual=residual)
 
 

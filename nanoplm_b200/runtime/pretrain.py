@@ -254,19 +254,30 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
         mask_pool = torch.tensor(train_collator.masker.allowed_random_token_ids.tolist(), dtype=torch.int32,
                                  device=device)
         mask_micro = 0
-    train_sampler = ResumableDistributedSampler(len(train_ds), world, rank, True, cfg.seed)
     eval_sampler = ResumableDistributedSampler(len(val_ds), world, rank, False, cfg.seed)
     workers = get_num_workers(cfg.num_workers, world)
     loader_kw = dict(num_workers=workers, pin_memory=device.type == "cuda",
                      persistent_workers=workers > 0,
                      prefetch_factor=cfg.prefetch_factor if workers > 0 else None)
-    train_loader = DataLoader(train_ds, sampler=train_sampler, batch_size=cfg.micro_batch_size,
-                              collate_fn=train_collator, drop_last=static_packing, **loader_kw)
+    # several ranks on packed batches: every optimizer step's sequences are dealt to the
+    # (rank, micro-step) bins by cost, so no rank waits for another at the step's collective
+    balanced = (bool(getattr(cfg, "balance_ranks", True)) and distributed and static_packing
+                and len(train_ds) >= cfg.micro_batch_size * grad_accum * world)
+    if balanced:
+        from nanoplm_b200.data.sampler import BalancedBatchSampler
+        train_sampler = BalancedBatchSampler(train_ds.sequence_lengths(), cfg.micro_batch_size, grad_accum, world,
+                                             rank, True, cfg.seed, float(cfg.balance_quadratic),
+                                             max_length=manifest.max_seq_len)
+        train_loader = DataLoader(train_ds, batch_sampler=train_sampler, collate_fn=train_collator, **loader_kw)
+        loader_len = len(train_sampler)
+    else:
+        train_sampler = ResumableDistributedSampler(len(train_ds), world, rank, True, cfg.seed)
+        train_loader = DataLoader(train_ds, sampler=train_sampler, batch_size=cfg.micro_batch_size,
+                                  collate_fn=train_collator, drop_last=static_packing, **loader_kw)
+        loader_len = (len(train_sampler) // cfg.micro_batch_size if static_packing
+                      else math.ceil(len(train_sampler) / cfg.micro_batch_size))
     eval_loader = DataLoader(val_ds, sampler=eval_sampler, batch_size=cfg.micro_batch_size,
                              collate_fn=eval_collator, drop_last=False, **loader_kw)
-
-    loader_len = (len(train_sampler) // cfg.micro_batch_size if static_packing
-                  else math.ceil(len(train_sampler) / cfg.micro_batch_size))
     steps_per_epoch = num_update_steps_per_epoch(loader_len, grad_accum)
     total_steps = num_epochs * steps_per_epoch
     warmup_steps = get_warmup_steps(total_steps, float(cfg.warmup_ratio))
@@ -325,7 +336,7 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
         train_sampler.set_epoch(epoch)
         offset = 0
         if resume_micro > 0 and epoch == start_epoch:
-            train_sampler.fast_forward(resume_micro * cfg.micro_batch_size)
+            train_sampler.fast_forward(resume_micro if balanced else resume_micro * cfg.micro_batch_size)
             offset = resume_micro
             resume_micro = 0
         n_micro = offset + len(train_loader)

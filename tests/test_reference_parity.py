@@ -263,3 +263,31 @@ def test_packing_collator_layout_matches(ref, static):
         assert bool(pool_or_mask.all())
         n_real = int((~torch.isin(clean, special)).sum())
         assert 0.15 < m.sum().item() / n_real < 0.45
+
+
+def test_dropout_settings_are_honoured_or_refused(ref):
+    """mlp_dropout changes the training forward (and only that); a non-zero attention_dropout,
+    which the attention kernels cannot honour, is refused instead of being dropped silently."""
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    with pytest.raises(ValueError, match="attention_dropout"):
+        ModelConfig(attention_dropout=0.1, **GEOM)
+    tok = ProtTokenizer()
+    torch.manual_seed(0)
+    m = ProtEncoderMLM(ModelConfig(mlp_dropout=0.5, embedding_dropout=0.1, **GEOM), tok).float()
+    with torch.no_grad():
+        for layer in m.model.layers:
+            layer.mlp.Wo.weight.normal_(0, 0.05)
+    enc = tok(_sequences(3, 10, 40, seed=2), padding=True, return_tensors="pt")
+    labels = enc["input_ids"].clone()
+    labels[enc["attention_mask"] == 0] = -100
+    kw = dict(input_ids=enc["input_ids"], attention_mask=enc["attention_mask"], labels=labels)
+    m.eval()
+    with torch.no_grad():
+        e1, e2 = float(m(**kw)["loss"]), float(m(**kw)["loss"])
+    assert e1 == e2                                   # no dropout in eval mode
+    m.train()
+    with torch.no_grad():
+        t1, t2 = float(m(**kw)["loss"]), float(m(**kw)["loss"])
+    assert t1 != t2 and abs(t1 - e1) > 1e-6           # active, and random, in training mode

@@ -148,3 +148,37 @@ def test_static_packing_drops_whole_rows_instead_of_failing(tok):
     b = c(_examples(tok, seqs))
     assert b["num_real_tokens"] == 4 * 31 and c.dropped_sequences == 4
     assert b["input_ids"].shape == (128,)
+
+
+def test_balanced_batch_sampler_deals_equal_cost_bins_and_resumes():
+    """Every rank's micro-batches of an optimizer step cost the same, the step's global batch is the
+    shuffled sampler's window, ranks never share a sequence, and fast_forward resumes mid-epoch."""
+    import numpy as np
+    from nanoplm_b200.data.packing import balance_bins, balance_bins_python
+    from nanoplm_b200.data.sampler import BalancedBatchSampler
+    rng = np.random.default_rng(3)
+    lens = rng.integers(20, 513, size=4 * 2 * 26 * 5 + 17).astype(np.int32)    # 5 whole steps + a remainder
+    b, c = balance_bins(lens[:208], 8, 26)
+    b2, c2 = balance_bins_python(lens[:208].tolist(), 8, 26)
+    assert b.tolist() == b2 and np.allclose(c, c2)
+    world, accum, mbs = 4, 2, 26
+    samplers = [BalancedBatchSampler(lens, mbs, accum, world, r, True, seed=7) for r in range(world)]
+    batches = [list(s) for s in samplers]
+    assert all(len(bt) == 5 * accum == len(samplers[0]) for bt in batches)
+    cost = lens + lens.astype(np.float64) ** 2 / 2700.0
+    for step in range(5):
+        per_rank = [sum(cost[i] for a in range(accum) for i in batches[r][step * accum + a]) for r in range(world)]
+        assert max(per_rank) / (sum(per_rank) / world) < 1.002
+        seen = [i for r in range(world) for a in range(accum) for i in batches[r][step * accum + a]]
+        assert len(seen) == len(set(seen)) == world * accum * mbs
+        g = torch.Generator()
+        g.manual_seed(7)
+        window = torch.randperm(len(lens), generator=g)[step * len(seen):(step + 1) * len(seen)].tolist()
+        assert sorted(seen) == sorted(window)
+        assert all(len(batches[r][step * accum + a]) == mbs for r in range(world) for a in range(accum))
+    s = samplers[1]
+    s.fast_forward(3)
+    assert len(s) == 5 * accum - 3 and list(s) == batches[1][3:]
+    assert list(s) == batches[1]                   # the offset applies to one epoch only
+    s.set_epoch(1)
+    assert list(s) != batches[1]
