@@ -7,8 +7,12 @@ step over all GPUs, AdamW + gradient clipping), on synthetic protein data with r
 N > 1 is launched as `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...`.
 Rank 0 prints ONE JSON line. `value` = real (non-padding) tokens per second over all GPUs for K
 optimizer steps, timed on the device with CUDA events between barrier + synchronize pairs, maximum
-over ranks. `e2e` is the same metric through `nanoplm_b200.runtime.pretrain.TrainStep` with every
-micro-batch copied from pinned host memory and the loss read back every step.
+over ranks. `e2e` is the same metric through the user-facing pipeline
+(`nanoplm_b200.runtime.pretrain.run_pretraining` on a shard dataset: DataLoader workers, packing
+collator, every micro-batch copied from pinned host memory, loss read back every step).
+`no_trim_value` repeats the device-timed measurement over the full static shape (padding tail left
+in place), `exposed_comm_ms` is the part of the optimizer step's communication that is not hidden
+under the backward pass, `step_ms` the spread of the timed steps.
 
 `--impl reference` runs the unmodified reference package installed under baseline/_ref through its
 own `run_pure_pretraining` (FSDP2 / torch.compile / flash-attn path) on the same synthetic data and
@@ -132,7 +136,101 @@ def config_block(n_gpus: int, accum: int) -> dict:
 
 
 # ----------------------------------------------------------------------------------- own arm
+def _step_batches(step: int, rank: int, world: int, accum: int, coll, balanced: bool, trim: bool):
+    """Pinned host micro-batches of this rank for optimizer step `step`, their real-token counts and
+    the real-token count of every rank. The step's global batch (MICRO_PER_STEP x SEQS_PER_MICRO
+    sequences) is the same whatever the number of ranks; with `balanced` it is dealt to the
+    (rank, micro-step) bins by cost (nanoplm_b200.data.packing.balance_bins), otherwise in order."""
+    import numpy as np
+    import torch
+    from nanoplm_b200.data.packing import balance_bins
+    seqs = make_sequences(MICRO_PER_STEP * SEQS_PER_MICRO, 1234 + step)
+    lens = np.fromiter((len(x) for x in seqs), np.int32, len(seqs))
+    if balanced:
+        bin_of, _ = balance_bins(lens, MICRO_PER_STEP, SEQS_PER_MICRO)
+    else:
+        bin_of = np.arange(len(seqs), dtype=np.int32) // SEQS_PER_MICRO
+    per_rank_tokens = [int(sum(lens[bin_of == a * world + r].sum() for a in range(accum))) for r in range(world)]
+    host, real = [], []
+    for a in range(accum):
+        idx = np.nonzero(bin_of == a * world + rank)[0]
+        b = coll([{"input_ids": torch.from_numpy(seqs[i])} for i in idx])
+        real.append(int(b["num_real_tokens"]))
+        if not trim:                 # process the padding tail too (the reference's static shape)
+            b.pop("num_real_tokens")
+        b.pop("labels")              # masked_idx / masked_labels carry the same information
+        host.append({k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in b.items()})
+    return host, real, per_rank_tokens
+
+
+def _pipeline_e2e(args, device, rank, world, accum, K, W):
+    """The same metric through the user-facing pipeline: `run_pretraining` on a shard dataset
+    (DataLoader workers, packing collator, pinned host -> device copy of every micro-batch, loss
+    read back at every step). Returns (tokens/s over all ranks, ms per step, h2d bytes per step,
+    d2h bytes per step) or None when --no-pipeline-e2e was given."""
+    import torch
+    import torch.distributed as dist
+    from nanoplm_b200.config.schema import ModelConfig, PretrainingConfig, PureTorchConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.runtime.pretrain import run_pretraining
+    work = Path(tempfile.mkdtemp(prefix=f"nplm_own_r{rank}_"))
+    n_train = (W + K + 1) * MICRO_PER_STEP * SEQS_PER_MICRO      # one spare step: the loader prefetches ahead
+    if rank == 0 or world == 1:
+        write_shard_dataset(work / "data", n_train, SEQS_PER_MICRO * world, seed=4321)
+    if world > 1:
+        paths = [str(work)]
+        dist.broadcast_object_list(paths, src=0)
+        work = Path(paths[0])
+    cfg = PretrainingConfig(
+        dataset_dir=str(work / "data"), ckp_dir=str(work / f"ckpt{rank}"), micro_batch_size=SEQS_PER_MICRO,
+        num_epochs=1, warmup_ratio=0.05, optimizer="adamw", adam_learning_rate=1e-3,
+        global_batch_size=MICRO_PER_STEP * SEQS_PER_MICRO * MAX_SEQ_LEN, bf16=True, tf32=True,
+        mlm_probability=MLM_PROB, logging_steps=1, eval_steps=10 ** 9, save_steps=10 ** 9, seed=42,
+        num_workers="auto", prefetch_factor=2, multi_gpu=world > 1, world_size=world, project_name="bench",
+        fused_comm=not args.no_fused_comm, balance_ranks=not args.no_balance, metrics_jsonl=False)
+    pt = PureTorchConfig(use_compile=False, use_packing=True, target_packed_rows=TARGET_ROWS)
+    torch.manual_seed(42)
+    model = ProtEncoderMLM(ModelConfig(**MODEL), ProtTokenizer())
+    st = {"t0": None, "e0": None, "ms": None, "tok": 0.0, "h2d": 0, "d2h": 0}
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def on_step(info: dict) -> None:
+        n = info["global_step"]
+        if n == W:
+            sync_all()
+            st["e0"] = torch.cuda.Event(enable_timing=True)
+            st["e0"].record()
+            st["t0"] = time.perf_counter()
+        elif W < n <= W + K:
+            st["tok"] += info["tokens"]
+            st["h2d"] += info["h2d_bytes"]
+            st["d2h"] += info["d2h_bytes"]
+            if n == W + K:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                sync_all()
+                st["ms"] = max(st["e0"].elapsed_time(e1), 1e3 * (time.perf_counter() - st["t0"]))
+
+    run_pretraining(model, cfg, pt, None, max_steps=W + K, on_step=on_step, final_checkpoint=False)
+    t = torch.tensor([st["ms"] or 0.0, st["tok"]], dtype=torch.float64, device=device)
+    if world > 1:
+        mx = t[:1].clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t[1:])
+        t[0] = mx[0]
+    ms, tokens = float(t[0]), float(t[1])
+    if ms <= 0:
+        return None
+    return tokens / (ms / 1e3), ms / K, st["h2d"] // K, st["d2h"] // K
+
+
 def run_own(args) -> dict:
+    import statistics
     import torch
     import torch.distributed as dist
     from nanoplm_b200.config.schema import ModelConfig
@@ -153,6 +251,7 @@ def run_own(args) -> dict:
         raise SystemExit("gpus must divide 16")
     accum = MICRO_PER_STEP // world
     K, W = args.steps, args.warmup
+    K_nt = 0 if (args.no_trim or args.variant != "default") else min(K, 2)   # extra steps over the full static shape
     set_seed(42)
     tok = ProtTokenizer()
     model_kw = dict(MODEL)
@@ -168,26 +267,20 @@ def run_own(args) -> dict:
     engine = ShardedEngine(model, AdamWHyper(lr=1e-3, max_grad_norm=1.0), device,
                            compute_dtype=torch.bfloat16, fused_comm=not args.no_fused_comm)
     model.train()
-    total_steps = W + 2 * K
+    total_steps = W + 2 * K + K_nt
     sched = WarmupLinearSchedule(1e-3, max(1, total_steps // 20), total_steps * 50)
     stepper = TrainStep(model, engine, sched, device)
+    balanced = world > 1 and not args.no_balance
 
-    # every rank packs its own micro-batches (pinned host memory)
-    n_micro = (W + K) * accum
-    seqs = make_sequences(n_micro * SEQS_PER_MICRO, 1234 + rank)
     coll = PackingCollator(tok, MAX_SEQ_LEN, MLM_PROB, target_rows=TARGET_ROWS, batch_size=SEQS_PER_MICRO,
                            seed=99 + rank)
-    host, real_tokens = [], []
-    for i in range(n_micro):
-        ex = [{"input_ids": torch.from_numpy(s)} for s in seqs[i * SEQS_PER_MICRO:(i + 1) * SEQS_PER_MICRO]]
-        b = coll(ex)
-        real_tokens.append(int(b["num_real_tokens"]))
-        if args.no_trim:               # process the padding tail too (the reference's static shape)
-            b.pop("num_real_tokens")
-        b.pop("labels")            # masked_idx / masked_labels carry the same information
-        host.append({k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in b.items()})
-    steps_host = [host[s * accum:(s + 1) * accum] for s in range(W + K)]
-    steps_tok = [sum(real_tokens[s * accum:(s + 1) * accum]) for s in range(W + K)]
+    steps_host, steps_tok, rank_tok = [], [], []
+    for s in range(W + K):
+        host, real, per_rank = _step_batches(s, rank, world, accum, coll, balanced, trim=not args.no_trim)
+        steps_host.append(host)
+        steps_tok.append(sum(real))
+        rank_tok.append(per_rank)
+    nt_host = [_step_batches(W + K + s, rank, world, accum, coll, balanced, trim=False) for s in range(K_nt)]
 
     def sync_all():
         if world > 1:
@@ -206,21 +299,45 @@ def run_own(args) -> dict:
 
     # ---- device-timed region ------------------------------------------------------------
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    if engine.fused is not None:
+        engine.fused.timing, engine.fused.tail_events = True, []
     sync_all()
     if sampler:
         sampler.start()
     launches0 = _lib.launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for st in timed_dev:
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
+    marks[0].record()
+    for i, st in enumerate(timed_dev):
         stepper.step_on_device(st)
-    e1.record()
+        marks[i + 1].record()
     sync_all()
-    ms = e0.elapsed_time(e1)
+    ms = marks[0].elapsed_time(marks[-1])
+    step_ms = [marks[i].elapsed_time(marks[i + 1]) for i in range(K)]
     launches = _lib.launches() - launches0
     clocks = sampler.stop() if sampler else None
+    tail_ms = 0.0
+    if engine.fused is not None:
+        engine.fused.timing = False
+        tails = [a.elapsed_time(b) for a, b in engine.fused.tail_events]
+        tail_ms = sum(tails) / max(1, len(tails))
 
-    # ---- end-to-end region (H2D every micro-batch, loss read back every step) -----------------
+    # ---- the optimizer step's own arithmetic (AdamW on this rank's slice, no communication) ------
+    from nanoplm_b200.ops import kernels as Kn
+    g = torch.zeros(engine.shard, dtype=torch.float32, device=device)
+    o = torch.empty(engine.shard, dtype=torch.bfloat16, device=device)
+    ssq = torch.ones(1, dtype=torch.float32, device=device)
+    pm, pv, pp_ = (torch.zeros_like(g) for _ in range(3))
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(4):
+        if it == 1:
+            a0.record()
+        Kn.adamw_(pp_, pm, pv, g, o, engine._hyper_dev[0], ssq, zero_grad=False)
+    a1.record()
+    torch.cuda.synchronize()
+    local_opt_ms = a0.elapsed_time(a1) / 3
+    del g, o, pm, pv, pp_
+
+    # ---- TrainStep from pinned host memory (H2D every micro-batch, loss read back every step) ---
     stepper.h2d_bytes = stepper.d2h_bytes = 0
     sync_all()
     t0 = time.perf_counter()
@@ -231,24 +348,80 @@ def run_own(args) -> dict:
         last_loss = stepper.step_from_host(st)
     g1.record()
     sync_all()
-    e2e_ms = max(g0.elapsed_time(g1), 1e3 * (time.perf_counter() - t0))
-    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    ts_ms = max(g0.elapsed_time(g1), 1e3 * (time.perf_counter() - t0))
+    ts_h2d, ts_d2h = stepper.h2d_bytes // K, stepper.d2h_bytes // K
+
+    # ---- the same steps over the full static shape (padding tail not cut off) -------------------
+    nt_ms, nt_tokens = 0.0, 0.0
+    if K_nt:
+        nt_dev = [[move_batch(b, device) for b in h] for h, _, _ in nt_host]
+        nt_tokens = float(sum(sum(r) for _, r, _ in nt_host))
+        stepper.step_on_device(nt_dev[0])          # shapes change: one untimed step first
+        sync_all()
+        n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0.record()
+        for st in nt_dev:
+            stepper.step_on_device(st)
+        n1.record()
+        sync_all()
+        nt_ms = n0.elapsed_time(n1)
+
+    t = torch.tensor([ms, ts_ms, nt_ms, tail_ms, max(step_ms), -min(step_ms)], dtype=torch.float64, device=device)
+    nt_tok_t = torch.tensor([nt_tokens], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+        dist.all_reduce(nt_tok_t)
+    ms, ts_ms, nt_ms, tail_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
     _lib.check_status()
+    fused_on = engine.fused is not None
+    n_params = engine.num_parameters()
+    loaded = [Path(p).name for p in _lib.loaded_libraries()]
+    overlapped = engine.fused.overlapped_bytes if fused_on else 0
+
+    # ---- end to end through the pipeline ------------------------------------------------------------
+    del stepper, engine, model, timed_dev
+    torch.cuda.empty_cache()
+    pipe = None
+    if not args.no_pipeline_e2e and args.variant == "default" and not args.no_trim:
+        pipe = _pipeline_e2e(args, device, rank, world, accum, K, W)
+
     value = global_tokens / (ms / 1e3)
+    e2e = {"value": global_tokens / (ts_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": ts_h2d,
+           "d2h_bytes_per_step": ts_d2h, "ms_per_step": ts_ms / K,
+           "path": "TrainStep.step_from_host on micro-batches collated ahead of time (pinned host memory)"}
+    if pipe is not None:
+        e2e = {"value": pipe[0], "unit": "tokens/s", "h2d_bytes_per_step": pipe[2], "d2h_bytes_per_step": pipe[3],
+               "ms_per_step": pipe[1],
+               "path": "run_pretraining on a shard dataset: DataLoader workers + packing collator + balanced "
+                       "batch sampler, pinned host -> device copy of every micro-batch, loss and gradient norm "
+                       "read back at every step",
+               "trainstep_from_host": {"value": global_tokens / (ts_ms / 1e3), "ms_per_step": ts_ms / K,
+                                       "h2d_bytes_per_step": ts_h2d, "d2h_bytes_per_step": ts_d2h}}
+    spread = [max(r) / (sum(r) / len(r)) for r in rank_tok[W:]]
     res = {"metric": "mlm_pretrain_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
            "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
            "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
            "data": "synthetic (seeded amino-acid sequences, random-init weights)", "impl": "own",
-           "config": config_block(world, accum), "clocks": clocks,
-           "e2e": {"value": global_tokens / (e2e_ms / 1e3), "unit": "tokens/s",
-                   "h2d_bytes_per_step": stepper.h2d_bytes // K, "d2h_bytes_per_step": stepper.d2h_bytes // K,
-                   "ms_per_step": e2e_ms / K},
+           "config": config_block(world, accum), "clocks": clocks, "e2e": e2e,
            "gpu_launches": launches, "final_loss": last_loss,
+           "step_ms": {"min": -float(t[5]), "median": statistics.median(step_ms), "max": float(t[4]),
+                       "note": "device time of every timed optimizer step; min / max over ranks, median of rank 0"},
+           "exposed_comm_ms": max(0.0, tail_ms - local_opt_ms) if fused_on else (0.0 if world == 1 else None),
+           "exposed_comm": {"optimizer_step_after_backward_ms": tail_ms, "local_adamw_ms": local_opt_ms,
+                            "overlapped_with_backward_bytes_per_rank": overlapped,
+                            "definition": "CUDA-event time from the end of the last backward pass to the end of "
+                                          "the optimizer step (barriers, remaining reduce-scatter, norm exchange, "
+                                          "AdamW + parameter push; max over ranks, mean over the timed steps) minus "
+                                          "the time of the same AdamW arithmetic on this rank's slice alone"},
+           "rank_real_tokens_max_over_mean": {"mean": sum(spread) / len(spread), "max": max(spread),
+                                              "balanced_assignment": balanced},
            "raw_tokens_per_sec": K * MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN / (ms / 1e3),
-           "fused_comm": engine.fused is not None, "loaded_libs": [Path(p).name for p in _lib.loaded_libraries()]}
+           "fused_comm": fused_on, "loaded_libs": loaded}
+    if K_nt and nt_ms > 0:
+        res["no_trim_value"] = float(nt_tok_t.item()) / (nt_ms / 1e3)
+        res["no_trim_ms_per_step"] = nt_ms / K_nt
+        res["no_trim_note"] = (f"{K_nt} further steps with the padding tail left in place (the static shape the "
+                               "reference computes over): like-for-like kernel speed, real tokens counted")
     if args.no_trim:
         res["config"]["padding_tail"] = "own arm run with --no-trim: its kernels cover the padding tail as well"
     if args.variant != "default":
@@ -256,7 +429,7 @@ def run_own(args) -> dict:
         res["config"]["model"] += {"moe": " + MoE (64 experts, top-2, I 512) on every 2nd layer",
                                    "conv_mhc": " + varlen depthwise conv (k 7) + 4 mHC streams",
                                    "fp8": " with e4m3 block128 linear layers (not the headline precision)"}[args.variant]
-        res["parameters"] = engine.num_parameters()
+        res["parameters"] = n_params
         if args.variant == "fp8":
             res["dtype"] = "fp8-e4m3 linears, bf16 elsewhere"
     if world > 1:
@@ -393,6 +566,10 @@ def main() -> None:
     ap.add_argument("--no-fused-comm", action="store_true", help="use NCCL collectives in the optimizer step")
     ap.add_argument("--no-trim", action="store_true",
                     help="own arm: also run the kernels over the padding tail of every flat micro-batch")
+    ap.add_argument("--no-balance", action="store_true",
+                    help="own arm, several GPUs: deal the step's sequences to ranks in order instead of by cost")
+    ap.add_argument("--no-pipeline-e2e", action="store_true",
+                    help="own arm: skip the run_pretraining end-to-end region (e2e then reports TrainStep from host)")
     ap.add_argument("--variant", choices=("default", "moe", "conv_mhc", "fp8"), default="default",
                     help="own arm only: optional model extensions (the headline number is 'default')")
     args = ap.parse_args()

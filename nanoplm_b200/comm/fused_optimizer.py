@@ -1,6 +1,16 @@
 """Optimizer step with the collectives fused into the kernels (reduce-scatter + gradient norm,
 AdamW + all-gather push) over symmetric memory. See nanoplm_b200/csrc/comm.cu.
 
+The reduce-scatter is split by parameter and overlapped with the backward pass of the last
+micro-step, as the reference's FSDP2 does with its per-layer reduce-scatter
+(src/nanoplm/pretraining/pure_pipeline.py:697-702, 736-742): when the weight-gradient GEMM of a
+parameter has been launched (`ops.functional.set_wgrad_ready_callback`), a side stream waits for that
+GEMM, passes a peer barrier of its own (every rank's gradient of this parameter is final) and the
+owner(s) of the parameter's slice pull and sum it while the main stream continues with the next
+layer's backward. After the backward pass only the parameters without such a GEMM (embedding,
+norms, head) and the parameter that finished last remain, then the norm exchange and the
+AdamW + push.
+
 `FusedShardedStep.try_create` allocates the gradient buffer, the parameter buffer and the flag /
 slot words in symmetric memory (torch.distributed._symmetric_memory: CUDA VMM allocations whose
 handles are exchanged once over the bootstrap process group and mapped into every rank). If that
@@ -56,7 +66,19 @@ class FusedShardedStep:
         self.flag_ptrs = _ptr_array(words.ptrs)
         self.slot_ptrs = _ptr_array([p + 8 * 4 for p in words.ptrs])
         self.local_slots = words.tensor.view(torch.float32)[8:16]
+        # [16:24]: flags of the side-stream barriers (one per overlapped parameter, own epoch counter)
+        self.side_flag_ptrs = _ptr_array([p + 16 * 4 for p in words.ptrs])
+        self.side_epoch = 0
+        self.side_stream = torch.cuda.Stream(dev)
         self._lib = lib("comm")
+        # ranges [a, b) of the owned slice that were reduced during the backward pass of this step
+        self.done: list[tuple[int, int]] = []
+        self.armed = False
+        self.overlapped_bytes = 0
+        self._events: list[torch.cuda.Event] = []
+        # CUDA events bracketing the part of step() that runs after the backward pass (not overlapped)
+        self.timing = False
+        self.tail_events: list[tuple[torch.cuda.Event, torch.cuda.Event]] = []
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -68,7 +90,7 @@ class FusedShardedStep:
             g = group if group is not None else dist.group.WORLD
             grads = SymmetricBuffer(total, torch.float32, device, g)
             params = SymmetricBuffer(total, torch.bfloat16, device, g)
-            words = SymmetricBuffer(16, torch.int32, device, g)
+            words = SymmetricBuffer(32, torch.int32, device, g)
             ok = torch.ones(1, device=device)
         except Exception as exc:  # noqa: BLE001
             logger.warning(f"symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL collectives")
@@ -88,13 +110,77 @@ class FusedShardedStep:
         check_rc(rc, "peer_barrier")
         count_launch()
 
+    # ------------------------------------------------------------------ overlap with backward
+    def arm(self) -> None:
+        """Call before the forward pass of the LAST micro-step of an optimizer step (on every rank):
+        from now on a parameter whose weight-gradient kernel has been launched is final."""
+        self.armed = True
+        self.done = []
+        self.partial.zero_()
+        self.overlapped_bytes = 0
+
+    def _rs(self, a: int, b: int) -> None:
+        """Sums [a, b) (global flat indices inside the owned slice) over all ranks on the current stream."""
+        e = self.e
+        rc = self._lib.nplm_rs_sumsq(self.grads.ptr_array, c_int(self.world), c_longlong(a), c_longlong(b - a),
+                                     c_void_p(self.shard_grad.data_ptr() + 4 * (a - e.lo)), ptr(self.partial),
+                                     stream_ptr())
+        check_rc(rc, "rs_sumsq")
+        count_launch()
+
+    def on_wgrad_ready(self, slot_range: tuple[int, int]) -> None:
+        """Side stream: wait for the gradient kernel just launched, barrier with the peers, reduce the
+        part of [offset, offset + numel) this rank owns."""
+        if not self.armed:
+            return
+        e = self.e
+        lo, hi = slot_range
+        if (lo | hi) & 7:                                 # odd-sized tensor: left to the final pass
+            return
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(e.device))
+        self._events.append(ev)
+        with torch.cuda.stream(self.side_stream):
+            self.side_stream.wait_event(ev)
+            self.side_epoch += 1
+            rc = self._lib.nplm_peer_barrier(self.side_flag_ptrs, c_int(self.rank), c_int(self.world),
+                                             c_uint(self.side_epoch & 0xFFFFFFFF), c_double(self.timeout),
+                                             ptr(status_word(e.device)), stream_ptr())
+            check_rc(rc, "peer_barrier")
+            count_launch()
+            a, b = max(lo, e.lo), min(hi, e.hi)
+            if b > a:
+                self._rs(a, b)
+                self.done.append((a, b))
+                self.overlapped_bytes += 4 * (b - a) * self.world
+
+    def _remaining(self) -> list[tuple[int, int]]:
+        e = self.e
+        out, cur = [], e.lo
+        for a, b in sorted(self.done):
+            if a > cur:
+                out.append((cur, a))
+            cur = max(cur, b)
+        if cur < e.hi:
+            out.append((cur, e.hi))
+        return out
+
     def step(self, lr: float, grad_scale: float) -> torch.Tensor:
         e = self.e
+        main = torch.cuda.current_stream(e.device)
+        if self.timing:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(main)
+        if not self.armed:
+            self.done = []
+            self.partial.zero_()
+        else:
+            main.wait_stream(self.side_stream)           # the overlapped reductions have finished
+        self.armed = False
+        self._events = []
         self.barrier()                                   # every rank's gradients are final
-        self.partial.zero_()
-        rc = self._lib.nplm_rs_sumsq(self.grads.ptr_array, c_int(self.world), c_longlong(e.lo),
-                                     c_longlong(e.shard), ptr(self.shard_grad), ptr(self.partial), stream_ptr())
-        check_rc(rc, "rs_sumsq")
+        for a, b in self._remaining():
+            self._rs(a, b)
         rc = self._lib.nplm_publish(self.slot_ptrs, c_int(self.rank), c_int(self.world), ptr(self.partial),
                                     stream_ptr())
         check_rc(rc, "publish")
@@ -105,6 +191,9 @@ class FusedShardedStep:
                                        c_longlong(e.shard), c_longlong(e.decay_end), ptr(e._hyper_dev[0]),
                                        ptr(self.local_slots), ptr(self.norm), stream_ptr())
         check_rc(rc, "adamw_push")
-        count_launch(3)
+        count_launch(2)
         self.barrier()                                   # every rank's parameter buffer is complete
+        if self.timing:
+            t1.record(main)
+            self.tail_events.append((t0, t1))
         return self.norm[0]

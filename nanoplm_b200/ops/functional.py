@@ -34,6 +34,16 @@ def _has_main_grad(p) -> bool:
     return getattr(p, "main_grad", None) is not None
 
 
+# Called with a parameter right after the kernel that adds its weight gradient into `main_grad` has
+# been launched (the engine uses it to start that parameter's reduce-scatter while the rest of the
+# backward pass is still running).
+_WGRAD_READY = [None]
+
+
+def set_wgrad_ready_callback(fn) -> None:
+    _WGRAD_READY[0] = fn
+
+
 def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
     """dW[N,K] = dy2[T,N]^T x2[T,K]; accumulates into w.main_grad or returns a bf16 gradient."""
     T, N = dy2.shape
@@ -46,6 +56,8 @@ def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
         if _has_main_grad(w):
             K.gemm(dy2, x2, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=w.main_grad,
                    splits=K.wgrad_splits(N, Kd, T), pair=pair)
+            if _WGRAD_READY[0] is not None:
+                _WGRAD_READY[0](w)
             return None
         acc = torch.zeros((N, Kd), dtype=torch.float32, device=w.device)
         K.gemm(dy2, x2, a_mn=True, b_mn=True, epi=K.EPI_ATOMIC_F32, out=acc,

@@ -86,6 +86,8 @@ class ShardedEngine:
         self.compute_dtype = compute_dtype if self.on_cuda else torch.float32
         self.step_count = 0
         self.fused = None
+        tied = getattr(model, "_tied_weights_keys", {}) or {}
+        self._shared_names = set(tied.values()) | set(tied.keys())
 
         # ---- flat layout ------------------------------------------------------------------
         seen: dict[int, str] = {}
@@ -144,6 +146,25 @@ class ShardedEngine:
         if sym is not None:
             self.fused = FusedShardedStep(self, *sym)
             dist.barrier(group=self.pg)
+        self._slot_of = {id(s.param): s for s in self.slots}
+
+    # ---- overlap of the gradient reduction with the backward pass --------------------------
+    def begin_last_microstep(self) -> None:
+        """Tells the engine that the micro-batch about to run is the last one of this optimizer
+        step: with the fused communication path, every parameter's reduce-scatter then starts as
+        soon as its weight-gradient kernel has been launched, under the rest of the backward pass.
+        Must be called by every rank (the reductions contain peer barriers). No-op otherwise."""
+        if self.fused is None:
+            return
+        from nanoplm_b200.ops import functional as ops
+        self.fused.arm()
+        ops.set_wgrad_ready_callback(self._on_wgrad_ready)
+
+    def _on_wgrad_ready(self, param) -> None:
+        s = self._slot_of.get(id(param))
+        # tied / shared parameters receive several gradient contributions: they wait for the step
+        if s is not None and s.name not in self._shared_names:
+            self.fused.on_wgrad_ready((s.offset, s.offset + s.numel))
 
     # ---- parameter views ------------------------------------------------------------------
     def _rebind(self) -> None:
@@ -201,6 +222,8 @@ class ShardedEngine:
         if self.fused is not None:
             if extra_sumsq is not None:
                 raise ValueError("extra_sumsq is not supported by the fused communication step")
+            from nanoplm_b200.ops import functional as ops
+            ops.set_wgrad_ready_callback(None)
             return self.fused.step(lr, grad_scale)
         # 1. reduce-scatter: the owned slice of main_grad becomes the sum over ranks
         if self.distributed:

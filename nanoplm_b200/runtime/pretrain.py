@@ -164,7 +164,12 @@ def build_collators(tokenizer, cfg: PretrainingConfig, pt: PureTorchConfig, max_
 
 def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                     pure_torch_config: Optional[PureTorchConfig] = None,
-                    resume_config: Optional[ResumeConfig] = None, max_steps: Optional[int] = None) -> dict:
+                    resume_config: Optional[ResumeConfig] = None, max_steps: Optional[int] = None,
+                    on_step=None, final_checkpoint: bool = True) -> dict:
+    """on_step: optional callable invoked after every optimizer step with a dict (global_step, this
+    rank's real / raw token counts of the step, bytes copied host -> device and read back device ->
+    host during the step); benchmarks time the loop with it. final_checkpoint=False skips the
+    checkpoint at the end of the run."""
     cfg = pretrain_config
     pt = pure_torch_config or PureTorchConfig()
     os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
@@ -331,6 +336,7 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
     first = True
     result = {"output_dir": output_dir, "losses": [], "eval_losses": []}
     done = False
+    step_tok = step_raw = step_h2d = 0
 
     for epoch in range(start_epoch, num_epochs):
         train_sampler.set_epoch(epoch)
@@ -347,6 +353,9 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
             a, b = batch_token_counts(host_batch)
             tok += a
             raw_tok += b
+            step_tok += a
+            step_raw += b
+            step_h2d += sum(v.numel() * v.element_size() for v in host_batch.values() if torch.is_tensor(v))
             dev_batch = move_batch(host_batch, device)
             if device_masking:
                 from nanoplm_b200.ops import kernels as K
@@ -358,11 +367,13 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                 dev_batch.update(input_ids=ids_m, labels=lab_m)
                 dev_batch.pop("masked_idx", None)
                 dev_batch.pop("masked_labels", None)
+            boundary = (micro_step + 1) % grad_accum == 0 or micro_step + 1 == n_micro
+            if boundary and hasattr(engine, "begin_last_microstep"):
+                engine.begin_last_microstep()    # gradient reduction overlaps this backward pass
             out = model(**model_inputs(dev_batch))
             loss = out["loss"]
             loss.backward()
             accum_loss += loss.detach().float()
-            boundary = (micro_step + 1) % grad_accum == 0 or micro_step + 1 == n_micro
             if not boundary:
                 continue
             n_acc = (micro_step % grad_accum) + 1
@@ -408,6 +419,13 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                                 f"h100_mfu={h100:.2%} b200_mfu={b200:.2%}")
                 window_loss.zero_()
                 window_steps, tok, raw_tok, t0 = 0, 0, 0, None
+                step_d2h = 8          # window loss + gradient norm read back as two fp32 scalars
+            else:
+                step_d2h = 0
+            if on_step is not None:
+                on_step({"global_step": global_step, "tokens": step_tok, "raw_tokens": step_raw,
+                         "h2d_bytes": step_h2d, "d2h_bytes": step_d2h})
+            step_tok = step_raw = step_h2d = 0
 
             if first:  # keep the collector away from the step loop (reference: pure_pipeline.py:843-853)
                 first = False
@@ -437,8 +455,9 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
     check_device_status()
     if distributed:
         dist.barrier()
-    ckpt.save_checkpoint(engine, scheduler, global_step, num_epochs, output_dir, plan.logging_steps,
-                         plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint)
+    if final_checkpoint:
+        ckpt.save_checkpoint(engine, scheduler, global_step, num_epochs, output_dir, plan.logging_steps,
+                             plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint)
     sink.finish(output_dir)
     if watchdog is not None:
         watchdog.stop()
@@ -495,6 +514,8 @@ class TrainStep:
                     for v in b.values():
                         if torch.is_tensor(v):
                             v.record_stream(cur)     # allocated on the copy stream, used on this one
+            if i + 1 == len(batches) and hasattr(self.engine, "begin_last_microstep"):
+                self.engine.begin_last_microstep()   # gradient reduction overlaps the last backward pass
             out = self.model(**model_inputs(b))
             out["loss"].backward()
             self._acc += out["loss"].detach().float()
