@@ -188,7 +188,8 @@ def _pipeline_e2e(args, device, rank, world, accum, K, W):
         global_batch_size=MICRO_PER_STEP * SEQS_PER_MICRO * MAX_SEQ_LEN, bf16=True, tf32=True,
         mlm_probability=MLM_PROB, logging_steps=1, eval_steps=10 ** 9, save_steps=10 ** 9, seed=42,
         num_workers="auto", prefetch_factor=2, multi_gpu=world > 1, world_size=world, project_name="bench",
-        fused_comm=not args.no_fused_comm, balance_ranks=not args.no_balance, metrics_jsonl=False)
+        fused_comm=not args.no_fused_comm, balance_ranks=not args.no_balance, metrics_jsonl=False,
+        shard_params=bool(args.shard_params))
     pt = PureTorchConfig(use_compile=False, use_packing=True, target_packed_rows=TARGET_ROWS)
     torch.manual_seed(42)
     model = ProtEncoderMLM(ModelConfig(**MODEL), ProtTokenizer())
@@ -264,8 +265,12 @@ def run_own(args) -> dict:
         from nanoplm_b200.ops import functional as _ops
         _ops.set_fp8(True)
     model = ProtEncoderMLM(ModelConfig(**model_kw), tok)
-    engine = ShardedEngine(model, AdamWHyper(lr=1e-3, max_grad_norm=1.0), device,
-                           compute_dtype=torch.bfloat16, fused_comm=not args.no_fused_comm)
+    engine_cls = ShardedEngine
+    if args.shard_params and world > 1:
+        from nanoplm_b200.parallel.param_sharded import ParamShardedEngine
+        engine_cls = ParamShardedEngine
+    engine = engine_cls(model, AdamWHyper(lr=1e-3, max_grad_norm=1.0), device,
+                        compute_dtype=torch.bfloat16, fused_comm=not args.no_fused_comm)
     model.train()
     total_steps = W + 2 * K + K_nt
     sched = WarmupLinearSchedule(1e-3, max(1, total_steps // 20), total_steps * 50)
@@ -377,6 +382,8 @@ def run_own(args) -> dict:
     n_params = engine.num_parameters()
     loaded = [Path(p).name for p in _lib.loaded_libraries()]
     overlapped = engine.fused.overlapped_bytes if fused_on else 0
+    sharded_params = type(engine).__name__ == "ParamShardedEngine"
+    gathered_bytes = engine.gathered_parameter_bytes() if sharded_params else 0
 
     # ---- end to end through the pipeline ------------------------------------------------------------
     del stepper, engine, model, timed_dev
@@ -417,6 +424,13 @@ def run_own(args) -> dict:
                                               "balanced_assignment": balanced},
            "raw_tokens_per_sec": K * MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN / (ms / 1e3),
            "fused_comm": fused_on, "loaded_libs": loaded}
+    if args.shard_params:
+        res["shard_params"] = {"active": sharded_params,
+                               "bf16_bytes_gathered_inside_gemms_per_rank_per_step": gathered_bytes,
+                               "note": "parameters, their gradient reduction and optimizer state are split by row "
+                                       "blocks over the ranks; the all-gather runs inside the first forward GEMM "
+                                       "that uses a matrix (RoPE / SwiGLU / residual epilogues)"}
+        res["config"]["parallelism"] = f"dp{world}-sharded-parameters"
     if K_nt and nt_ms > 0:
         res["no_trim_value"] = float(nt_tok_t.item()) / (nt_ms / 1e3)
         res["no_trim_ms_per_step"] = nt_ms / K_nt
@@ -566,6 +580,8 @@ def main() -> None:
     ap.add_argument("--no-fused-comm", action="store_true", help="use NCCL collectives in the optimizer step")
     ap.add_argument("--no-trim", action="store_true",
                     help="own arm: also run the kernels over the padding tail of every flat micro-batch")
+    ap.add_argument("--shard-params", action="store_true",
+                    help="own arm, several GPUs: row-sharded parameters with the all-gather inside the GEMMs")
     ap.add_argument("--no-balance", action="store_true",
                     help="own arm, several GPUs: deal the step's sequences to ranks in order instead of by cost")
     ap.add_argument("--no-pipeline-e2e", action="store_true",

@@ -197,3 +197,90 @@ class FusedShardedStep:
             t1.record(main)
             self.tail_events.append((t0, t1))
         return self.norm[0]
+
+
+class ParamShardedStep(FusedShardedStep):
+    """Optimizer step of `ParamShardedEngine`: the same kernels on row-block ownership. Every rank
+    reduces its own row block of a matrix as soon as that matrix's gradient kernel of the last
+    micro-step has been launched (so the reduction work of every parameter is spread over all ranks
+    and hidden under the backward pass), AdamW updates the owned rows in place, and nothing is
+    pushed for matrices the next forward pass gathers inside its GEMMs."""
+
+    def __init__(self, engine, grads, params, words, barrier_timeout_s: float = 20.0):
+        super().__init__(engine, grads, params, words, barrier_timeout_s)
+        self.self_ptr = _ptr_array([params.ptrs[self.rank]])
+        self.by_offset = {p.slot.offset: p for p in engine.mine}
+        self.done_ids: set[int] = set()
+
+    def arm(self) -> None:
+        super().arm()
+        self.done_ids = set()
+
+    def _rs_piece(self, p) -> None:
+        rc = self._lib.nplm_rs_sumsq(self.grads.ptr_array, c_int(self.world), c_longlong(p.a),
+                                     c_longlong(p.b - p.a), c_void_p(self.shard_grad.data_ptr() + 4 * p.local),
+                                     ptr(self.partial), stream_ptr())
+        check_rc(rc, "rs_sumsq")
+        count_launch()
+
+    def on_wgrad_ready(self, slot_range: tuple[int, int]) -> None:
+        if not self.armed:
+            return
+        e = self.e
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(e.device))
+        self._events.append(ev)
+        with torch.cuda.stream(self.side_stream):
+            self.side_stream.wait_event(ev)
+            self.side_epoch += 1
+            rc = self._lib.nplm_peer_barrier(self.side_flag_ptrs, c_int(self.rank), c_int(self.world),
+                                             c_uint(self.side_epoch & 0xFFFFFFFF), c_double(self.timeout),
+                                             ptr(status_word(e.device)), stream_ptr())
+            check_rc(rc, "peer_barrier")
+            count_launch()
+            p = self.by_offset.get(slot_range[0])
+            if p is not None and id(p) not in self.done_ids:
+                self._rs_piece(p)
+                self.done_ids.add(id(p))
+                self.overlapped_bytes += 4 * (p.b - p.a) * self.world
+
+    def step(self, lr: float, grad_scale: float) -> torch.Tensor:
+        e = self.e
+        main = torch.cuda.current_stream(e.device)
+        if self.timing:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(main)
+        if not self.armed:
+            self.done_ids = set()
+            self.partial.zero_()
+        else:
+            main.wait_stream(self.side_stream)
+        self.armed = False
+        self._events = []
+        self.barrier()                                   # every rank's gradients are final
+        for p in e.mine:
+            if id(p) not in self.done_ids:
+                self._rs_piece(p)
+        rc = self._lib.nplm_publish(self.slot_ptrs, c_int(self.rank), c_int(self.world), ptr(self.partial),
+                                    stream_ptr())
+        check_rc(rc, "publish")
+        self.barrier()                                   # partial sums exchanged, peers done reading my gradients
+        e.main_grad.zero_()
+        f4 = 4
+        for p in e.mine:
+            loc = f4 * p.local
+            # gathered row blocks stay local (the consuming GEMM of the next forward pass fetches them);
+            # the small tensors go to every rank
+            ptrs, push_world = (self.self_ptr, 1) if p.gathered else (self.params.ptr_array, self.world)
+            rc = self._lib.nplm_adamw_push_ex(
+                c_void_p(e.master.data_ptr() + loc), c_void_p(e.exp_avg.data_ptr() + loc),
+                c_void_p(e.exp_avg_sq.data_ptr() + loc), c_void_p(self.shard_grad.data_ptr() + loc), ptrs,
+                c_int(push_world), c_longlong(p.a), c_longlong(p.b - p.a), c_longlong(e.decay_end),
+                ptr(e._hyper_dev[0]), ptr(self.local_slots), c_int(self.world), ptr(self.norm), stream_ptr())
+            check_rc(rc, "adamw_push")
+        count_launch(1 + len(e.mine))
+        self.barrier()                                   # every rank's rows are final before anybody gathers them
+        if self.timing:
+            t1.record(main)
+            self.tail_events.append((t0, t1))
+        return self.norm[0]

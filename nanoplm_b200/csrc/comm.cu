@@ -159,15 +159,17 @@ stats_allreduce_kernel(PeerPtrs buf, int rank, int world, uint32_t epoch, const 
 // AdamW on the owned slice [lo, lo+n) + push of the bf16 result to every rank's parameter buffer.
 // hyper: [lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale, max_norm].
 // Elements with global index < decay_end use weight_decay, the rest none. n is a multiple of 8.
+// `world` parameter buffers receive the result (1 = only this rank's own buffer: the other ranks
+// fetch the rows later, inside the GEMM that consumes them); the norm sums n_slots partial sums.
 __global__ void __launch_bounds__(512)
 adamw_push_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                   const float* __restrict__ g, PeerPtrs params, int world, long long lo, long long n,
                   long long decay_end, const float* __restrict__ hyper, const float* __restrict__ slots,
-                  float* __restrict__ norm_out) {
+                  int n_slots, float* __restrict__ norm_out) {
   const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd0 = hyper[4];
   const float bc1 = hyper[5], bc2 = hyper[6], gs = hyper[7], max_norm = hyper[8];
   float total = 0.f;
-  for (int p = 0; p < world; ++p) total += slots[p];
+  for (int p = 0; p < n_slots; ++p) total += slots[p];
   const float norm = sqrtf(total) * gs;
   float scale = gs;
   if (max_norm > 0.f) scale = gs * fminf(1.f, max_norm / (norm + 1e-6f));
@@ -263,14 +265,23 @@ extern "C" int nplm_publish(void* const* slot_ptrs, int rank, int world, const f
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int nplm_adamw_push(float* master, float* m, float* v, const float* g, void* const* param_ptrs,
-                               int world, long long lo, long long n, long long decay_end,
-                               const float* hyper, const float* slots, float* norm_out, cudaStream_t st) {
-  if (world < 1 || world > MAX_PEERS || (n & 7) || (lo & 7)) return -3;
+// Pushes to `world` buffers and sums `n_slots` partial sums of squares for the clipping norm.
+extern "C" int nplm_adamw_push_ex(float* master, float* m, float* v, const float* g, void* const* param_ptrs,
+                                  int world, long long lo, long long n, long long decay_end,
+                                  const float* hyper, const float* slots, int n_slots, float* norm_out,
+                                  cudaStream_t st) {
+  if (world < 1 || world > MAX_PEERS || n_slots < 1 || n_slots > MAX_PEERS || (n & 7) || (lo & 7)) return -3;
   if (n == 0) return 0;
   long long blocks = (n / 8 + 511) / 512;
   if (blocks > 148 * 4) blocks = 148 * 4;
   adamw_push_kernel<<<static_cast<int>(blocks), 512, 0, st>>>(master, m, v, g, to_peers(param_ptrs, world), world,
-                                                              lo, n, decay_end, hyper, slots, norm_out);
+                                                              lo, n, decay_end, hyper, slots, n_slots, norm_out);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_adamw_push(float* master, float* m, float* v, const float* g, void* const* param_ptrs,
+                               int world, long long lo, long long n, long long decay_end,
+                               const float* hyper, const float* slots, float* norm_out, cudaStream_t st) {
+  return nplm_adamw_push_ex(master, m, v, g, param_ptrs, world, lo, n, decay_end, hyper, slots, world, norm_out,
+                            st);
 }

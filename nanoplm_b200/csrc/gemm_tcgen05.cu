@@ -205,10 +205,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int num_tiles = num_m * num_n;
     const int split = w / num_tiles, tile = w % num_tiles;
     if (args.ag_world > 1) {
-      // shard by shard starting with the local one; inside a shard n runs fastest
+      // shard by shard starting with the local one; inside a shard n runs fastest. SwiGLU: output
+      // columns [n0, n0 + TILE_N) read value rows n0.. and gate rows swiglu_half + n0.., which live
+      // in two shards (v and n_shards + v); the tiles walk the value shards
+      const int n_shards = (EPI == EPI_SWIGLU) ? args.swiglu_half / args.ag_rows : args.ag_world;
       const int n_per = args.ag_rows / TILE_N;
       const int per_shard = num_m * n_per;
-      const int shard = (args.ag_rank + tile / per_shard) % args.ag_world;
+      const int shard = (args.ag_rank + tile / per_shard) % n_shards;
       const int rem = tile % per_shard;
       it.m0 = (rem / n_per) * BM;
       it.n0 = shard * args.ag_rows + (rem % n_per) * TILE_N;
@@ -285,22 +288,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = it.m0, n0 = it.n0, kb0 = it.kb0, kb1 = it.kb1;
         const int brow = it.b_row;
         if (args.ag_world > 1) {
-          const int shard = n0 / args.ag_rows;
-          if (shard != args.ag_rank && !((ag_seen >> shard) & 1u)) {
-            const long long t0 = clock64();
-            while (ld_acquire_gpu(args.ag_flags + shard) < gridDim.x) {
-              if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                atomicExch(args.status, ST_TIMEOUT_PEER);
-                *abort_flag = 1;
-                ok = false;
-                break;
+          const int n_need = (EPI == EPI_SWIGLU) ? 2 : 1;
+          for (int q = 0; q < n_need && ok; ++q) {
+            const int shard = (q == 0 ? n0 : args.swiglu_half + n0) / args.ag_rows;
+            if (shard != args.ag_rank && !((ag_seen >> shard) & 1u)) {
+              const long long t0 = clock64();
+              while (ld_acquire_gpu(args.ag_flags + shard) < gridDim.x) {
+                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                  atomicExch(args.status, ST_TIMEOUT_PEER);
+                  *abort_flag = 1;
+                  ok = false;
+                  break;
+                }
+                __nanosleep(100);
               }
-              __nanosleep(100);
+              if (!ok) break;
+              ag_seen |= 1u << shard;
+              fence_proxy_async_global();  // the shard was written with generic stores, TMA reads it
             }
-            if (!ok) break;
-            ag_seen |= 1u << shard;
-            fence_proxy_async_global();  // the shard was written with generic stores, TMA reads it
           }
+          if (!ok) break;
         }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
@@ -1160,11 +1167,17 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   args.ag_flags = grp.ag_flags;
   for (int r = 0; r < 8; ++r) args.ag_src[r] = nullptr;
   if (grp.ag_world > 1) {
-    if (grp.ag_world > 8 || a_mn || b_mn || grp.mode != 0 || epi == EPI_ATOMIC_F32 || epi == EPI_SWIGLU ||
+    if (grp.ag_world > 8 || a_mn || b_mn || grp.mode != 0 || epi == EPI_ATOMIC_F32 ||
         grp.ag_ptrs == nullptr || grp.ag_flags == nullptr || (N % grp.ag_world) || (K % 8))
       return -10;
     args.ag_rows = N / grp.ag_world;
-    if (args.ag_rows % bn) return -10;   // a tile must not straddle two shards
+    if (epi == EPI_SWIGLU) {
+      // value rows and gate rows of a tile come from two different shards: the halves must be
+      // whole numbers of shards, and a half-tile (bn / 2 rows) must not straddle two of them
+      if ((grp.ag_world % 2) || ((N / 2) % args.ag_rows) || (args.ag_rows % (bn / 2))) return -10;
+    } else if (args.ag_rows % bn) {
+      return -10;   // a tile must not straddle two shards
+    }
     for (int r = 0; r < grp.ag_world; ++r)
       args.ag_src[r] = reinterpret_cast<const __nv_bfloat16*>(grp.ag_ptrs[r]) +
                        static_cast<size_t>(r) * args.ag_rows * ldb;
@@ -1315,15 +1328,24 @@ extern "C" int nplm_gemm_bf16_grouped_wgrad(const void* A, const void* B, float*
 // B (the all-gather result, reusable by later GEMMs) and C is complete. flags: 8 device words.
 // The caller orders this launch after the peers' writes of their shards (a barrier) and keeps the
 // shards unchanged until every rank's launch has finished.
-extern "C" int nplm_gemm_bf16_ag(const void* A, void* const* b_ptrs, void* C, const void* R, int M, int N,
-                                 int K, int lda, int ldb, int ldc, int ldr, int epi, int bn, int rank,
-                                 int world, unsigned* flags, int* status, cudaStream_t stream) {
+extern "C" int nplm_gemm_bf16_ag_rope(const void* A, void* const* b_ptrs, void* C, const void* R, int M,
+                                      int N, int K, int lda, int ldb, int ldc, int ldr, int epi, int bn,
+                                      int rank, int world, unsigned* flags, const int* rope_pos,
+                                      const float* rope_cos, const float* rope_sin, int rope_cols,
+                                      int* status, cudaStream_t stream) {
   GroupSpec g;
   g.ag_world = world;
   g.ag_rank = rank;
   g.ag_ptrs = b_ptrs;
   g.ag_flags = flags;
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return -10;
-  return gemm_entry(A, b_ptrs[rank], C, R, M, N, K, lda, ldb, ldc, ldr, 0, 0, epi, 1, bn, 0, 0, nullptr,
-                    nullptr, nullptr, 0, status, stream, g);
+  return gemm_entry(A, b_ptrs[rank], C, R, M, N, K, lda, ldb, ldc, ldr, 0, 0, epi, 1, bn, 0, 0, rope_pos,
+                    rope_cos, rope_sin, rope_cols, status, stream, g);
+}
+
+extern "C" int nplm_gemm_bf16_ag(const void* A, void* const* b_ptrs, void* C, const void* R, int M, int N,
+                                 int K, int lda, int ldb, int ldc, int ldr, int epi, int bn, int rank,
+                                 int world, unsigned* flags, int* status, cudaStream_t stream) {
+  return nplm_gemm_bf16_ag_rope(A, b_ptrs, C, R, M, N, K, lda, ldb, ldc, ldr, epi, bn, rank, world, flags,
+                                nullptr, nullptr, nullptr, 0, status, stream);
 }

@@ -63,6 +63,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     """
     _chk(a, _BF16, "a")
     _chk(b, _BF16, "b")
+    ag = getattr(b, "_ag", None)
+    if ag is not None and ag.stale:
+        # a row-sharded weight whose other row blocks are out of date (parameter-sharded data
+        # parallelism): the first forward GEMM of the step gathers them from the peers inside the
+        # kernel; any other consumer triggers an explicit gather
+        if (not a_mn and not b_mn and splits == 1 and max_ctas == 0 and not direct_epilogue
+                and epi in (EPI_STORE, EPI_ADD, EPI_GELU, EPI_RELU, EPI_SWIGLU, EPI_ROPE)):
+            res = gemm_ag(a, b, ag.ptrs, ag.rank, ag.world, ag.flags, epi=epi, out=out, aux=aux, rope=rope)
+            ag.stale = False
+            return res
+        ag.gather_now(b)
     lda, ldb = _rowmajor(a, "a"), _rowmajor(b, "b")
     if a_mn:
         K, M = a.shape
@@ -130,7 +141,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 def gemm_ag(a: torch.Tensor, b_full: torch.Tensor, b_ptrs, rank: int, world: int, flags: torch.Tensor, *,
             epi: int = EPI_STORE, out: torch.Tensor | None = None, aux: torch.Tensor | None = None,
-            bn: int | None = None) -> torch.Tensor:
+            bn: int | None = None, rope: tuple | None = None) -> torch.Tensor:
     """All-gather fused into the GEMM: C = A B^T with B [N,K] row-sharded over `world` ranks.
 
     b_full is this rank's full-size weight buffer in peer-mapped (symmetric) memory, of which only
@@ -148,19 +159,26 @@ def gemm_ag(a: torch.Tensor, b_full: torch.Tensor, b_ptrs, rank: int, world: int
     if N % world:
         raise ValueError("rows of B must divide evenly over the ranks")
     rows = N // world
+    unit = rows * 2 if epi == EPI_SWIGLU else rows     # a SwiGLU tile reads bn / 2 value rows and bn / 2 gate rows
     if bn is None:
-        bn = 256 if rows % 256 == 0 else 128
-    if rows % bn:
-        raise ValueError(f"shard height {rows} must be a multiple of the {bn}-wide tile")
+        bn = 256 if unit % 256 == 0 else 128
+    if unit % bn:
+        raise ValueError(f"shard height {rows} does not hold whole {bn}-wide tiles")
+    if epi == EPI_SWIGLU and (world % 2 or (N // 2) % rows):
+        raise ValueError("SwiGLU with a row-sharded weight needs an even number of ranks")
     if out is None:
-        out = torch.empty((M, N), dtype=_BF16, device=a.device)
+        out = torch.empty((M, N // 2 if epi == EPI_SWIGLU else N), dtype=_BF16, device=a.device)
     ldr = 0
     if aux is not None:
         ldr = _rowmajor(aux, "aux")
-    rc = lib("gemm_tcgen05").nplm_gemm_bf16_ag(
+    r_pos, r_cos, r_sin, r_cols = rope if rope is not None else (None, None, None, 0)
+    if epi == EPI_ROPE and rope is None:
+        raise ValueError("EPI_ROPE needs rope=(pos, cos, sin, rope_cols)")
+    rc = lib("gemm_tcgen05").nplm_gemm_bf16_ag_rope(
         ptr(a), b_ptrs, ptr(out), ptr(aux), c_int(M), c_int(N), c_int(K), c_int(_rowmajor(a, "a")),
         c_int(_rowmajor(b_full, "b")), c_int(_rowmajor(out, "out")), c_int(ldr), c_int(epi), c_int(bn),
-        c_int(rank), c_int(world), ptr(flags), ptr(status_word(a.device)), stream_ptr())
+        c_int(rank), c_int(world), ptr(flags), ptr(r_pos), ptr(r_cos), ptr(r_sin), c_int(r_cols),
+        ptr(status_word(a.device)), stream_ptr())
     check_rc(rc, "gemm_bf16_ag")
     count_launch()
     return out

@@ -112,8 +112,7 @@ class ShardedEngine:
         if not decay:
             self.decay_end = 0
         self.total = _round_up(max(off, ALIGN), ALIGN * self.world)
-        self.shard = self.total // self.world
-        self.lo, self.hi = self.rank * self.shard, (self.rank + 1) * self.shard
+        self._plan_ownership()
 
         dev = self.device
         sym = None
@@ -139,14 +138,29 @@ class ShardedEngine:
             full_master[s.offset:s.offset + s.numel] = src
         if self.distributed:  # identical start on every rank (rank 0's initialisation wins)
             dist.broadcast(full_master, src=dist.get_global_rank(self.pg, 0) if self.pg else 0, group=self.pg)
-        self.master.copy_(full_master[self.lo:self.hi])
+        self.master.copy_(self._take_local(full_master))
         self.flat_params.copy_(full_master.to(self.compute_dtype))
         del full_master
         self._rebind()
         if sym is not None:
-            self.fused = FusedShardedStep(self, *sym)
+            self.fused = self._make_fused(sym)
             dist.barrier(group=self.pg)
         self._slot_of = {id(s.param): s for s in self.slots}
+
+    # ---- who owns which part of the flat index space (overridden by ParamShardedEngine) ----------
+    def _plan_ownership(self) -> None:
+        """Rank r owns the r-th contiguous slice of the flat space; `shard` = elements of optimizer
+        state this rank stores."""
+        self.shard = self.total // self.world
+        self.lo, self.hi = self.rank * self.shard, (self.rank + 1) * self.shard
+
+    def _take_local(self, full: torch.Tensor) -> torch.Tensor:
+        """This rank's part of a full flat vector, in the layout of its optimizer state."""
+        return full[self.lo:self.hi]
+
+    def _make_fused(self, sym):
+        from nanoplm_b200.comm.fused_optimizer import FusedShardedStep
+        return FusedShardedStep(self, *sym)
 
     # ---- overlap of the gradient reduction with the backward pass --------------------------
     def begin_last_microstep(self) -> None:
@@ -327,8 +341,9 @@ class ShardedEngine:
             full[s.offset:s.offset + s.numel] = t.to(device=full.device, dtype=torch.float32).reshape(-1)
         if strict and missing:
             raise KeyError(f"missing keys in checkpoint: {missing}")
-        self.master.copy_(full[self.lo:self.hi])
+        self.master.copy_(self._take_local(full))
         self.flat_params.copy_(full.to(self.compute_dtype))
+        self._params_replaced()
         # non-flat entries (buffers) go through the module
         rest = {k: v for k, v in sd.items() if k not in names}
         own = self.model.state_dict(keep_vars=True)
@@ -375,8 +390,8 @@ class ShardedEngine:
             m[s.offset:s.offset + s.numel] = st["exp_avg"].to(m.device, torch.float32).reshape(-1)
             v[s.offset:s.offset + s.numel] = st["exp_avg_sq"].to(v.device, torch.float32).reshape(-1)
             step = max(step, int(float(st["step"])))
-        self.exp_avg.copy_(m[self.lo:self.hi])
-        self.exp_avg_sq.copy_(v[self.lo:self.hi])
+        self.exp_avg.copy_(self._take_local(m))
+        self.exp_avg_sq.copy_(self._take_local(v))
         self.step_count = step
 
     def shard_state(self) -> dict:
@@ -394,3 +409,8 @@ class ShardedEngine:
         self.step_count = int(st["step"])
         full = self._gather_full(self.master)
         self.flat_params.copy_(full.to(self.compute_dtype))
+        self._params_replaced()
+
+    def _params_replaced(self) -> None:
+        """Called after the whole compute copy was rewritten from outside the optimizer (checkpoint
+        load): every rank's buffer is complete."""

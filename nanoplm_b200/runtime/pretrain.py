@@ -229,9 +229,15 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
         from nanoplm_b200.parallel.muon import MuonEngine
         engine = MuonEngine(model, hyper, cfg, device)
     elif opt_name in ("adamw", "stable_adamw"):
-        engine = ShardedEngine(model, hyper, device,
-                               compute_dtype=torch.bfloat16 if use_bf16 else torch.float32,
-                               fused_comm=bool(cfg.fused_comm))
+        engine_cls = ShardedEngine
+        if bool(getattr(cfg, "shard_params", False)) and distributed:
+            # parameters, gradients' reduction and optimizer state split by row blocks; the all-gather
+            # of the weights runs inside the forward GEMMs (reference: FSDP2, pure_pipeline.py:479-506)
+            from nanoplm_b200.parallel.param_sharded import ParamShardedEngine
+            engine_cls = ParamShardedEngine
+        engine = engine_cls(model, hyper, device,
+                            compute_dtype=torch.bfloat16 if use_bf16 else torch.float32,
+                            fused_comm=bool(cfg.fused_comm))
     else:
         raise ValueError(f"Invalid optimizer: {cfg.optimizer}. Supported: [adamw, stable_adamw, muon, normuon]")
     model.train()

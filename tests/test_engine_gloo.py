@@ -263,3 +263,92 @@ def test_matrix_parallel_muon_matches_single_rank(tmp_path, optimizer):
     if optimizer == "normuon":
         for k, v in opt1["normuon_row_second_moment"].items():
             assert torch.allclose(v, opt2["normuon_row_second_moment"][k], atol=1e-5), k
+
+
+def _make_wide_model():
+    """256-wide: every layer matrix splits into whole 128-row tiles over two ranks."""
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    torch.manual_seed(0)
+    cfg = ModelConfig(hidden_size=256, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      max_position_embeddings=128)
+    m = ProtEncoderMLM(cfg, ProtTokenizer())
+    with torch.no_grad():
+        for layer in m.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.05)
+            layer.mlp.Wo.weight.normal_(0, 0.05)
+    return m
+
+
+def _train_param_sharded(rank, world, port, tmp, sharded):
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.parallel.param_sharded import ParamShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.pretrain import TrainStep
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    if world > 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    model = _make_wide_model()
+    cls = ParamShardedEngine if sharded else ShardedEngine
+    eng = cls(model, AdamWHyper(lr=3e-3, weight_decay=0.01), torch.device("cpu"))
+    if sharded:
+        n_blocks = sum(1 for p in eng.pieces if p.gathered)
+        assert n_blocks == 2 * 2 * 4 + 2            # 4 matrices per layer + the head's dense, two row blocks each
+        assert all((p.b - p.a) * 2 == p.slot.numel for p in eng.pieces if p.gathered)
+        owned = sum(p.b - p.a for p in eng.mine)
+        assert owned < 0.6 * eng.total              # about half of the parameters live here
+    st = TrainStep(model, eng, WarmupLinearSchedule(3e-3, 2, 100), "cpu")
+    batches = _batches(40)
+    losses = []
+    for step in range(20):
+        losses.append(st.step_from_host(batches[2 * step:2 * step + 2][rank::world]))
+    if world > 1:
+        t = torch.tensor(losses)
+        dist.all_reduce(t)
+        losses = (t / world).tolist()
+    ckpt.save_checkpoint(eng, st.scheduler, 20, 0, tmp, 1, 100, 100, is_main=rank == 0)
+    sd = eng.full_state_dict_model()
+    opt = eng.optimizer_state_dict()
+    if rank == 0:
+        torch.save((losses, {k: v.clone() for k, v in sd.items()}, opt), os.path.join(tmp, "result.pt"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_parameter_sharded_engine_follows_the_single_rank_trajectory(tmp_path):
+    """Row-block ownership of parameters / optimizer state over two ranks: 20 steps give the losses,
+    weights and Adam moments of the single-process run, and its checkpoint loads in a plain engine."""
+    out = []
+    for world, sharded in ((1, False), (2, True)):
+        d = str(tmp_path / f"w{world}")
+        os.makedirs(d)
+        ctx = mp.get_context("spawn")
+        port = _free_port()
+        procs = [ctx.Process(target=_train_param_sharded, args=(r, world, port, d, sharded)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+        out.append(torch.load(os.path.join(d, "result.pt")))
+    (l1, sd1, opt1), (l2, sd2, opt2) = out
+    assert l1[-1] < l1[0] - 0.05
+    for a, b in zip(l1, l2):
+        assert abs(a - b) < 2e-4, (l1, l2)
+    for k in sd1:
+        assert torch.allclose(sd1[k], sd2[k], atol=5e-5), k
+    for i in opt1["state"]:
+        assert torch.allclose(opt1["state"][i]["exp_avg_sq"], opt2["state"][i]["exp_avg_sq"], atol=1e-6), i
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    eng = ShardedEngine(_make_wide_model(), AdamWHyper(lr=3e-3, weight_decay=0.01), torch.device("cpu"))
+    step, _ = ckpt.load_checkpoint(eng, WarmupLinearSchedule(3e-3, 2, 100), str(tmp_path / "w2" / "checkpoint-20"))
+    assert step == 20
+    back = eng.full_state_dict_model()
+    for k in sd2:
+        assert torch.allclose(back[k], sd2[k], atol=1e-7), k

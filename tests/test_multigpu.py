@@ -61,6 +61,10 @@ def _worker(rank, world, port, fused, out_path):
         assert eng._kernels
         if world > 1:       # even stacks (all-gather) and an uneven one (3 matrices of 256 x 256: all-reduce)
             assert {st.even for st in eng.stacks} == {True, False}
+    elif fused == "param_sharded":
+        from nanoplm_b200.parallel.param_sharded import ParamShardedEngine
+        eng = ParamShardedEngine(model, AdamWHyper(lr=2e-3, weight_decay=0.01), dev, fused_comm=True)
+        assert type(eng.fused).__name__ == "ParamShardedStep" and len(eng.gather_states) == 2 * 4 + 1
     else:
         eng = ShardedEngine(model, AdamWHyper(lr=2e-3, weight_decay=0.01), dev, fused_comm=fused)
     if fused is True and world > 1:
@@ -73,6 +77,15 @@ def _worker(rank, world, port, fused, out_path):
         losses.append(st.step_from_host(batches[2 * step:2 * step + 2][rank::world]))
     torch.cuda.synchronize()
     _lib.check_status()
+    if fused == "param_sharded":
+        # after a step every gathered matrix waits for its next forward GEMM; one forward pass clears them
+        assert all(st_.stale for st_ in eng.gather_states)
+        with torch.no_grad():
+            from nanoplm_b200.runtime.pretrain import model_inputs, move_batch
+            model(**model_inputs(move_batch(batches[0], dev)))
+        assert not any(st_.stale for st_ in eng.gather_states)
+        torch.cuda.synchronize()
+        _lib.check_status()
     t = torch.tensor(losses, device=dev)
     if world > 1:
         dist.all_reduce(t)
@@ -110,6 +123,20 @@ def test_two_gpu_steps_match_single_gpu(tmp_path):
     for k in nccl["sd"]:
         a, b = nccl["sd"][k].float(), fused["sd"][k].float()
         worst = max(worst, (a - b).abs().max().item())
+    assert worst < 5e-3, worst
+
+
+@pytest.mark.multigpu
+def test_two_gpu_parameter_sharded_training_matches_single_gpu(tmp_path):
+    """Row-sharded parameters: the weights' all-gather runs inside the first forward GEMMs of a step
+    (RoPE, residual, SwiGLU and GELU epilogues), every rank reduces and updates its own row blocks."""
+    one = _run(1, False, str(tmp_path / "one.pt"))
+    nccl = _run(2, False, str(tmp_path / "nccl.pt"))
+    ps = _run(2, "param_sharded", str(tmp_path / "ps.pt"))
+    assert torch.allclose(one["losses"], ps["losses"], atol=3e-2), (one["losses"], ps["losses"])
+    worst = 0.0
+    for k in nccl["sd"]:
+        worst = max(worst, (nccl["sd"][k].float() - ps["sd"][k].float()).abs().max().item())
     assert worst < 5e-3, worst
 
 
@@ -327,6 +354,15 @@ def _moe_train_worker(rank, world, port, out_path):
         losses.append(st.step_from_host(batches[2 * step:2 * step + 2][rank::world]))
     torch.cuda.synchronize()
     _lib.check_status()
+    if fused == "param_sharded":
+        # after a step every gathered matrix waits for its next forward GEMM; one forward pass clears them
+        assert all(st_.stale for st_ in eng.gather_states)
+        with torch.no_grad():
+            from nanoplm_b200.runtime.pretrain import model_inputs, move_batch
+            model(**model_inputs(move_batch(batches[0], dev)))
+        assert not any(st_.stale for st_ in eng.gather_states)
+        torch.cuda.synchronize()
+        _lib.check_status()
     t = torch.tensor(losses, device=dev)
     if world > 1:
         dist.all_reduce(t)
