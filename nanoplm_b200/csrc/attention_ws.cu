@@ -119,6 +119,12 @@ __device__ __forceinline__ WsGeo ws_geometry(const FaWsArgs& args, int pair) {
   return g;
 }
 
+// PTMEM: the probabilities go back to tensor memory (bf16, 64 columns per tile) and the P V product
+// reads its A operand from there. The tensor core fetches shared-memory operands at about 64 bytes
+// per clock, so a 128 x 64 x 16 instruction with P in shared memory waits 3x longer for operands
+// than it computes; with P in tensor memory only the V rows come from shared memory. Without PTMEM
+// the probabilities go through a swizzled shared-memory tile (the form the single-role kernels use).
+template <bool PTMEM>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -180,7 +186,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // columns: S0 [0,128), S1 [128,256), O0 [256,320), O1 [320,384)
+  // columns: S0 [0,128), S1 [128,256), O0 [256,320), O1 [320,384), P0 [384,448), P1 [448,512)
   WS_TRACE_INIT();
 
   if (warp >= 8) {
@@ -271,11 +277,18 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
               WS_TRACE(true, 0, 3);
               tc_fence_after();
               const uint64_t dV0 = make_smem_desc(smem_u32(sV + st * FA_TILE_BYTES), 8192, 1024);
+              if constexpr (PTMEM) {
 #pragma unroll
-              for (int k = 0; k < FA_T / 16; ++k)   // P: 32 bytes per 16 keys, next column block after 4;
-                                                    // V: 16 key rows = 2048 bytes
-                umma_bf16(tO, dP0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dV0 + k * (2048 >> 4), idesc_o,
-                          (jj > g.a[i] || k > 0) ? 1u : 0u);
+                for (int k = 0; k < FA_T / 16; ++k)   // P: 8 columns per 16 keys; V: 16 key rows = 2048 bytes
+                  umma_bf16_ts(tO, tmem_base + 384 + i * 64 + k * 8, dV0 + k * (2048 >> 4), idesc_o,
+                               (jj > g.a[i] || k > 0) ? 1u : 0u);
+              } else {
+#pragma unroll
+                for (int k = 0; k < FA_T / 16; ++k)   // P: 32 bytes per 16 keys, next column block after 4;
+                                                      // V: 16 key rows = 2048 bytes
+                  umma_bf16(tO, dP0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dV0 + k * (2048 >> 4),
+                            idesc_o, (jj > g.a[i] || k > 0) ? 1u : 0u);
+              }
               umma_commit(&pv_done[i]);
               ++p_cnt;
               WS_TRACE(true, 0, 4);
@@ -395,29 +408,51 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
 
         const float moff = m_used * sl2;
         float ps[4] = {0.f, 0.f, 0.f, 0.f};
-        if (!warp_none) {
+        if constexpr (PTMEM) {
+          // probabilities packed in place: word c of r[] takes keys 2c, 2c + 1 (both already consumed)
+          if (!warp_none) {
 #pragma unroll
-          for (int c8 = 0; c8 < 16; ++c8) {
-            uint32_t pk[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float p0 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q]), sl2, -moff));
-              const float p1 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q + 1]), sl2, -moff));
-              ps[q] += p0 + p1;
-              pk[q] = pack_bf16x2(p0, p1);
+            for (int c = 0; c < 64; ++c) {
+              const float p0 = exp2f(fmaf(__uint_as_float(r[2 * c]), sl2, -moff));
+              const float p1 = exp2f(fmaf(__uint_as_float(r[2 * c + 1]), sl2, -moff));
+              ps[c & 3] += p0 + p1;
+              r[c] = pack_bf16x2(p0, p1);
             }
-            *reinterpret_cast<uint4*>(sPi + (c8 >> 3) * FA_TILE_BYTES + swz(row_local, c8 & 7)) =
-                make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          }
-        } else {
+          } else {
 #pragma unroll
-          for (int c8 = 0; c8 < 16; ++c8)
-            *reinterpret_cast<uint4*>(sPi + (c8 >> 3) * FA_TILE_BYTES + swz(row_local, c8 & 7)) =
-                make_uint4(0u, 0u, 0u, 0u);
+            for (int c = 0; c < 64; ++c) r[c] = 0u;
+          }
+          const uint32_t tP = tmem_base + 384 + i * 64 + lane_addr;
+          tmem_st32(tP, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tmem_st32(tP + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          tmem_st_wait();
+          l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+          tc_fence_before();
+        } else {
+          if (!warp_none) {
+#pragma unroll
+            for (int c8 = 0; c8 < 16; ++c8) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float p0 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q]), sl2, -moff));
+                const float p1 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q + 1]), sl2, -moff));
+                ps[q] += p0 + p1;
+                pk[q] = pack_bf16x2(p0, p1);
+              }
+              *reinterpret_cast<uint4*>(sPi + (c8 >> 3) * FA_TILE_BYTES + swz(row_local, c8 & 7)) =
+                  make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          } else {
+#pragma unroll
+            for (int c8 = 0; c8 < 16; ++c8)
+              *reinterpret_cast<uint4*>(sPi + (c8 >> 3) * FA_TILE_BYTES + swz(row_local, c8 & 7)) =
+                  make_uint4(0u, 0u, 0u, 0u);
+          }
+          l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+          fence_proxy_async_smem();
+          tc_fence_before();
         }
-        l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-        fence_proxy_async_smem();
-        tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_ready[i]);
         WS_TRACE(quarter == 0, 1 + i, 3);
@@ -1080,7 +1115,9 @@ static int ws_configure(int* sms) {
   NPLM_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= WS_MAX_DEVICES) return -4;
   if (!ws_device[dev].configured) {
-    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_ws_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         WS_FWD_SMEM));
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_ws_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_FWD_SMEM));
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_BWD_SMEM));
@@ -1128,7 +1165,15 @@ extern "C" int nplm_fa_fwd_ws(const void* qkv, void* out, float* lse, const int*
   int grid = sms;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (grid > n_items) grid = n_items;
-  fa_fwd_ws_kernel<<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, a);
+  static int p_smem = -1;   // NPLM_FA_FWD_P_SMEM=1: probabilities through shared memory (benchmarks)
+  if (p_smem < 0) {
+    const char* e = getenv("NPLM_FA_FWD_P_SMEM");
+    p_smem = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  if (p_smem)
+    fa_fwd_ws_kernel<false><<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, a);
+  else
+    fa_fwd_ws_kernel<true><<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, a);
   return static_cast<int>(cudaGetLastError());
 }
 

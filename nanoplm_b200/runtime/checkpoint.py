@@ -9,6 +9,13 @@ reference's parameter order. Loading accepts `_orig_mod.`-prefixed keys. Differe
 is written under a temporary name and renamed, so a crash never leaves a half-written checkpoint;
 optionally every rank also writes its own optimizer slice (`shard-<rank>.pt` + `index.json`) for a
 resume that needs no gather/scatter.
+
+`load_checkpoint` also accepts the layout the reference's HF-Trainer pipeline writes
+(src/nanoplm/pretraining/pipeline.py:293-295: `checkpoint-N/{model.safetensors, optimizer.pt,
+scheduler.pt, trainer_state.json}`), so a run started there can continue here: the parameter names
+are the same (the reference maps them one to one, modeling.py:758-764), the Trainer's AdamW groups
+are [decay | no-decay] in `named_parameters` order like this engine's, and the step comes from
+`trainer_state.json`.
 """
 from __future__ import annotations
 
@@ -94,9 +101,15 @@ def load_checkpoint(engine, scheduler, checkpoint_dir: str, restore_rng: bool = 
             used_shards = True
     if not used_shards:
         model_path = ckp / MODEL_FILE
-        if not model_path.exists():
-            raise FileNotFoundError(f"{MODEL_FILE} not found in {ckp}")
-        engine.load_model_state_dict(torch.load(model_path, map_location="cpu", weights_only=True))
+        hf_path = ckp / "model.safetensors"
+        if model_path.exists():
+            engine.load_model_state_dict(torch.load(model_path, map_location="cpu", weights_only=True))
+        elif hf_path.exists():      # HF-Trainer layout; tied tensors are stored once there
+            from safetensors.torch import load_file
+            sd = {k: v for k, v in load_file(str(hf_path)).items() if not k.startswith("_")}
+            engine.load_model_state_dict(sd)
+        else:
+            raise FileNotFoundError(f"neither {MODEL_FILE} nor model.safetensors found in {ckp}")
         opt_path = ckp / OPT_FILE
         if opt_path.exists():
             try:
@@ -105,7 +118,10 @@ def load_checkpoint(engine, scheduler, checkpoint_dir: str, restore_rng: bool = 
                 logger.warning(f"Could not load optimizer state ({exc}); optimizer moments start from zero.")
     sched_path = ckp / SCHED_FILE
     if sched_path.exists():
-        scheduler.load_state_dict(torch.load(sched_path, map_location="cpu", weights_only=False))
+        try:
+            scheduler.load_state_dict(torch.load(sched_path, map_location="cpu", weights_only=False))
+        except Exception as exc:  # a scheduler pickled by another framework version
+            logger.warning(f"Could not load scheduler state ({exc}); the schedule restarts from the loaded step.")
     rng_path = ckp / RNG_FILE
     if restore_rng and rng_path.exists():
         rng = torch.load(rng_path, map_location="cpu", weights_only=False)
@@ -121,6 +137,10 @@ def load_checkpoint(engine, scheduler, checkpoint_dir: str, restore_rng: bool = 
     if state_path.exists():
         st = json.loads(state_path.read_text(encoding="utf-8"))
         return int(st.get("global_step", 0)), int(st.get("epoch", 0))
+    hf_state = ckp / "trainer_state.json"
+    if hf_state.exists():           # HF Trainer: {"global_step": N, "epoch": fractional epochs done, ...}
+        st = json.loads(hf_state.read_text(encoding="utf-8"))
+        return int(st.get("global_step", 0)), int(float(st.get("epoch", 0) or 0))
     return 0, 0
 
 

@@ -151,3 +151,25 @@ def test_ws_backward_full_batch_with_fused_rope_and_limited_grid(cuda_status):
         # dK and dV do not go through atomics: bitwise equal whatever the grid
         HD = H * D
         assert torch.equal(a[:, HD:], c[:, HD:])
+
+
+def test_ws_backward_dk_dv_are_bitwise_reproducible(cuda_status):
+    """dK and dV accumulate in TMEM in a fixed order: two runs give identical bits. (dQ is summed
+    over key tiles with fp32 atomics in the default mode and may differ in the last bits.)"""
+    k = _k()
+    H, D = 8, 64
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(20, 513, (30,), generator=g).tolist()
+    cu = _cu(lens)
+    T = cu[-1]
+    qkv = torch.randn(T, 3 * H * D, device="cuda").to(BF)
+    dout = torch.randn(T, H * D, device="cuda").to(BF)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    ss, se = k.seq_bounds(cu_t, T)
+    HD = H * D
+    for window in (-1, 64):
+        out, lse = k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl="ws")
+        a = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws")
+        b = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws")
+        assert torch.equal(a[:, HD:], b[:, HD:])
+        assert (a[:, :HD].float() - b[:, :HD].float()).abs().max().item() <= 2.0 ** -6 * a[:, :HD].float().abs().max().item()

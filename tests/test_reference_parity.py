@@ -291,3 +291,47 @@ def test_dropout_settings_are_honoured_or_refused(ref):
     with torch.no_grad():
         t1, t2 = float(m(**kw)["loss"]), float(m(**kw)["loss"])
     assert t1 != t2 and abs(t1 - e1) > 1e-6           # active, and random, in training mode
+
+
+def test_hf_trainer_checkpoint_layout_resumes_here(ref, tmp_path):
+    """`checkpoint-N/{model.safetensors, optimizer.pt, scheduler.pt, trainer_state.json}` as the
+    reference's HF-Trainer pipeline leaves it (pipeline.py:293-295) loads into this engine: weights
+    (tied decoder stored once), AdamW moments in [decay | no-decay] order, step from trainer_state."""
+    import json
+    from safetensors.torch import save_file
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    rm, om = _pair(ref)
+    rm.train()
+    cfg = types.SimpleNamespace(optimizer="adamw", adam_weight_decay=0.01, adam_learning_rate=1e-3,
+                                adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8)
+    opt = ref.pipeline._create_optimizer(rm, cfg)     # same grouping rule as the HF Trainer's
+    tok = ref.Tokenizer()
+    enc = tok(_sequences(4, 10, 40, seed=8), padding=True, return_tensors="pt")
+    labels = enc["input_ids"].clone()
+    labels[enc["attention_mask"] == 0] = -100
+    rm(input_ids=enc["input_ids"], attention_mask=enc["attention_mask"], labels=labels)["loss"].backward()
+    opt.step()
+    d = tmp_path / "checkpoint-7"
+    d.mkdir()
+    sd = {k: v.detach().clone().contiguous() for k, v in rm.state_dict().items() if k != "decoder.weight"}
+    save_file(sd, str(d / "model.safetensors"))
+    torch.save(opt.state_dict(), d / "optimizer.pt")
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: 1.0)
+    torch.save(sched.state_dict(), d / "scheduler.pt")
+    (d / "trainer_state.json").write_text(json.dumps({"global_step": 7, "epoch": 1.25, "log_history": []}))
+    eng = ShardedEngine(om, AdamWHyper(lr=1e-3, weight_decay=0.01), torch.device("cpu"))
+    step, epoch = ckpt.load_checkpoint(eng, WarmupLinearSchedule(1e-3, 1, 10), str(d))
+    assert (step, epoch) == (7, 1)
+    full = eng.full_state_dict_model()
+    for k, v in rm.state_dict().items():
+        assert torch.allclose(full[k], v.detach(), atol=1e-7), k
+    assert eng.step_count == 1
+    named = [n for n, p in rm.named_parameters()]
+    decay = [n for n, p in rm.named_parameters() if ref.pipeline._use_weight_decay(n, p)]
+    mine = eng.optimizer_state_dict()["state"]
+    theirs = opt.state_dict()["state"]
+    assert len(mine) == len(theirs) == len(named)
+    assert all(torch.allclose(mine[i]["exp_avg"], theirs[i]["exp_avg"], atol=1e-8) for i in theirs)
+    assert len(decay) == len([s for s in eng.slots if s.decay])
