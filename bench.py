@@ -371,12 +371,13 @@ def run_own(args) -> dict:
         sync_all()
         nt_ms = n0.elapsed_time(n1)
 
-    t = torch.tensor([ms, ts_ms, nt_ms, tail_ms, max(step_ms), -min(step_ms)], dtype=torch.float64, device=device)
+    t = torch.tensor([ms, ts_ms, nt_ms, tail_ms, max(step_ms), -min(step_ms), -tail_ms], dtype=torch.float64,
+                     device=device)
     nt_tok_t = torch.tensor([nt_tokens], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(nt_tok_t)
-    ms, ts_ms, nt_ms, tail_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
+    ms, ts_ms, nt_ms, tail_max_ms, tail_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3]), -float(t[6])
     _lib.check_status()
     fused_on = engine.fused is not None
     n_params = engine.num_parameters()
@@ -414,12 +415,17 @@ def run_own(args) -> dict:
            "step_ms": {"min": -float(t[5]), "median": statistics.median(step_ms), "max": float(t[4]),
                        "note": "device time of every timed optimizer step; min / max over ranks, median of rank 0"},
            "exposed_comm_ms": max(0.0, tail_ms - local_opt_ms) if fused_on else (0.0 if world == 1 else None),
-           "exposed_comm": {"optimizer_step_after_backward_ms": tail_ms, "local_adamw_ms": local_opt_ms,
+           "exposed_comm": {"optimizer_step_after_backward_ms": tail_ms,
+                            "optimizer_step_after_backward_ms_slowest_wait": tail_max_ms,
+                            "local_adamw_ms": local_opt_ms,
                             "overlapped_with_backward_bytes_per_rank": overlapped,
                             "definition": "CUDA-event time from the end of the last backward pass to the end of "
                                           "the optimizer step (barriers, remaining reduce-scatter, norm exchange, "
-                                          "AdamW + parameter push; max over ranks, mean over the timed steps) minus "
-                                          "the time of the same AdamW arithmetic on this rank's slice alone"},
+                                          "AdamW + parameter push), mean over the timed steps, on the rank where "
+                                          "it is SHORTEST: the rank that reaches the step last waits for nobody, so "
+                                          "its tail is the communication on the critical path; minus the time of "
+                                          "the same AdamW arithmetic on this rank's slice alone. The longest tail "
+                                          "over the ranks additionally contains the wait for the slowest rank."},
            "rank_real_tokens_max_over_mean": {"mean": sum(spread) / len(spread), "max": max(spread),
                                               "balanced_assignment": balanced},
            "raw_tokens_per_sec": K * MICRO_PER_STEP * TARGET_ROWS * MAX_SEQ_LEN / (ms / 1e3),

@@ -193,11 +193,14 @@ moe_count_kernel(const int* __restrict__ experts, int n, int E, MoePeers tables,
 //   my_base[e]   row (in the owner's buffer) where this rank's first assignment of e goes
 //   tile_group[] local expert of every 128-row tile of the local buffer, -1 beyond the end
 //   pad_lo/pad_hi[el] the zero-padding rows of local expert el
-//   overflow -> status ST_BAD_ARG when the local rows exceed the buffer capacity
+//   overflow: when the local rows exceed the buffer capacity the rows past it are DROPPED (push,
+//   pull and their backward kernels skip them, so those assignments contribute nothing) and counted
+//   in *dropped; training goes on (a skewed router costs some tokens of the tail experts of a rank,
+//   as with a capacity factor)
 __global__ void __launch_bounds__(256)
 moe_plan_kernel(const int* __restrict__ table, int world, int rank, int E, int capacity_rows,
                 int* __restrict__ group_off, int* __restrict__ my_base, int* __restrict__ tile_group,
-                int max_tiles, int* __restrict__ pad_lo, int* __restrict__ pad_hi, int* status) {
+                int max_tiles, int* __restrict__ pad_lo, int* __restrict__ pad_hi, int* dropped) {
   __shared__ int s_total[MOE_MAX_E];   // assignments of expert e over all ranks
   __shared__ int s_before[MOE_MAX_E];  // ... from ranks below this one
   __shared__ int s_off[MOE_MAX_E + 1]; // padded offset of e inside its owner's buffer
@@ -224,7 +227,14 @@ moe_plan_kernel(const int* __restrict__ table, int world, int rank, int E, int c
     }
     if (o == rank) {
       group_off[El] = off;
-      if (off > capacity_rows) atomicExch(status, ST_BAD_ARG);
+      if (off > capacity_rows && dropped != nullptr) {
+        int lost = 0;     // real (non-padding) rows that fall past the capacity
+        for (int el = 0; el < El; ++el) {
+          const int e = o * El + el;
+          lost += max(0, s_off[e] + s_total[e] - max(capacity_rows, s_off[e]));
+        }
+        atomicAdd(dropped, lost);
+      }
     }
   }
   __syncthreads();
@@ -466,10 +476,10 @@ extern "C" int nplm_moe_count(const int* experts, int n, int E, void* const* tab
 
 extern "C" int nplm_moe_plan(const int* table, int world, int rank, int E, int capacity_rows,
                              int* group_off, int* my_base, int* tile_group, int max_tiles,
-                             int* pad_lo, int* pad_hi, int* status, cudaStream_t stream) {
+                             int* pad_lo, int* pad_hi, int* dropped, cudaStream_t stream) {
   if (E < 1 || E > MOE_MAX_E || world < 1 || world > MOE_MAX_PEERS || (E % world)) return -3;
   moe_plan_kernel<<<1, 256, 0, stream>>>(table, world, rank, E, capacity_rows, group_off, my_base,
-                                         tile_group, max_tiles, pad_lo, pad_hi, status);
+                                         tile_group, max_tiles, pad_lo, pad_hi, dropped);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -105,6 +105,11 @@ class MoEMLP(nn.Module):
         return (self.device_path and x.is_cuda and x.dtype == torch.bfloat16 and self.hidden % 64 == 0
                 and self.inter % 64 == 0 and self.num_experts <= 256 and self.top_k <= 8)
 
+    def dropped_rows(self) -> int:
+        """Expert rows this layer dropped so far because a rank's buffers were full (0 without expert
+        parallelism, where the buffers are sized for the batch)."""
+        return 0 if self._comm is None else self._comm.dropped_rows()
+
     def forward(self, x: torch.Tensor):
         T, C = x.shape
         if self._use_device_path(x):

@@ -129,6 +129,17 @@ class MoEComm:
         self.epoch = 0
         self._sym = None
         self._cap = 0
+        self._dropped = None      # int32 device counter: expert rows dropped for lack of buffer room
+
+    def dropped_counter(self, device) -> torch.Tensor:
+        if self._dropped is None:
+            self._dropped = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._dropped
+
+    def dropped_rows(self) -> int:
+        """Assignments dropped so far because a rank's experts received more rows than its buffer
+        holds (synchronises)."""
+        return 0 if self._dropped is None else int(self._dropped.item())
 
     def capacity(self, n_assign: int) -> int:
         if self.world == 1:
@@ -222,7 +233,7 @@ def make_plan(comm: MoEComm, experts: torch.Tensor) -> MoEPlan:
     p.pad_hi = torch.empty(comm.El, dtype=torch.int32, device=dev)
     rc = L.nplm_moe_plan(ptr(table), c_int(comm.world), c_int(comm.rank), c_int(comm.E), c_int(cap),
                          ptr(p.group_off), ptr(my_base), ptr(p.tile_group), c_int(max_tiles), ptr(p.pad_lo),
-                         ptr(p.pad_hi), ptr(status_word(dev)), stream_ptr())
+                         ptr(p.pad_hi), ptr(comm.dropped_counter(dev)), stream_ptr())
     check_rc(rc, "moe_plan")
     p.pos_of = torch.empty(n, dtype=torch.int32, device=dev)
     rc = L.nplm_moe_assign(ptr(flat), c_int(n), c_int(comm.E), ptr(my_base), ptr(p.pos_of), stream_ptr())

@@ -332,6 +332,7 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                 f"warmup_steps={warmup_steps}, grad_accum={grad_accum}, world={world}, "
                 f"params={engine.num_parameters():,}, bf16={use_bf16}")
 
+    moe_layers = [m for m in model.modules() if hasattr(m, "dropped_rows") and hasattr(m, "experts_Wi")]
     global_step = start_step
     window_loss = torch.zeros((), dtype=torch.float32, device=device)
     accum_loss = torch.zeros((), dtype=torch.float32, device=device)
@@ -418,6 +419,8 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                            "train/tokens_per_sec": tps, "train/raw_tokens_per_sec": raw_tps,
                            "train/h100_mfu": h100, "train/b200_mfu": b200,
                            "train/step_ms_max_rank": 1e3 * float(stats[2]) / max(1, window_steps)}
+                if moe_layers:      # rows dropped by full expert buffers (skewed routing), this rank, so far
+                    payload["train/moe_dropped_rows"] = sum(m.dropped_rows() for m in moe_layers)
                 sink.log(payload)
                 if is_main:
                     logger.info(f"[step {global_step}/{total_steps}] loss={loss_val:.4f} lr={lr:.2e} "

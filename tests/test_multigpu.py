@@ -233,6 +233,20 @@ def _ep_worker(rank, world, port, out_path):
                  "dWo": rel(Wo.grad, gWo[rank * El:(rank + 1) * El])}
         for name, v in worst.items():
             assert v < 0.06, (it, rank, name, v)
+    assert comm.dropped_rows() == 0
+    # buffers too small for a router that sends everything to rank 0's experts: the rows past the
+    # capacity are dropped and counted, nothing aborts, the result stays finite
+    tight = M.MoEComm(C, E, k, group=dist.group.WORLD, capacity_factor=0.5)
+    skew = logits.detach().clone()
+    skew[:, :El] += 8.0
+    skew.requires_grad_(True)
+    y2, aux2 = M.moe_mlp(x.detach().requires_grad_(True), skew, Wi, Wo, k, tight)
+    ((y2.float() * gy.float()).sum() + 0.5 * aux2).backward()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    lost = torch.tensor([tight.dropped_rows()], device=dev)
+    dist.all_reduce(lost)
+    assert int(lost.item()) > 0 and torch.isfinite(y2.float()).all() and torch.isfinite(skew.grad.float()).all()
     if rank == 0:
         torch.save(worst, out_path)
     dist.barrier()
@@ -354,15 +368,6 @@ def _moe_train_worker(rank, world, port, out_path):
         losses.append(st.step_from_host(batches[2 * step:2 * step + 2][rank::world]))
     torch.cuda.synchronize()
     _lib.check_status()
-    if fused == "param_sharded":
-        # after a step every gathered matrix waits for its next forward GEMM; one forward pass clears them
-        assert all(st_.stale for st_ in eng.gather_states)
-        with torch.no_grad():
-            from nanoplm_b200.runtime.pretrain import model_inputs, move_batch
-            model(**model_inputs(move_batch(batches[0], dev)))
-        assert not any(st_.stale for st_ in eng.gather_states)
-        torch.cuda.synchronize()
-        _lib.check_status()
     t = torch.tensor(losses, device=dev)
     if world > 1:
         dist.all_reduce(t)
