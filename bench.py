@@ -269,6 +269,11 @@ def run_own(args) -> dict:
     if args.shard_params and world > 1:
         from nanoplm_b200.parallel.param_sharded import ParamShardedEngine
         engine_cls = ParamShardedEngine
+    if args.variant == "moe" and world > 1:
+        # expert parallelism: every rank keeps 64 / world experts, rows travel over peer memory
+        from nanoplm_b200.parallel.expert_engine import ExpertParallelEngine, shard_model_experts
+        shard_model_experts(model, dist.group.WORLD)
+        engine_cls = ExpertParallelEngine
     engine = engine_cls(model, AdamWHyper(lr=1e-3, max_grad_norm=1.0), device,
                         compute_dtype=torch.bfloat16, fused_comm=not args.no_fused_comm)
     model.train()

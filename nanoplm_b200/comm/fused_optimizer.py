@@ -165,7 +165,10 @@ class FusedShardedStep:
             out.append((cur, e.hi))
         return out
 
-    def step(self, lr: float, grad_scale: float) -> torch.Tensor:
+    def step(self, lr: float, grad_scale: float, extra_sumsq=None) -> torch.Tensor:
+        """extra_sumsq: sum of squares (already summed over the ranks, same scaling) of gradients held
+        outside the flat buffer (expert weights); it enters the clipping norm through rank 0's partial
+        sum, and the engine's `_sumsq` receives the global sum for those parameters' own update."""
         e = self.e
         main = torch.cuda.current_stream(e.device)
         if self.timing:
@@ -181,6 +184,8 @@ class FusedShardedStep:
         self.barrier()                                   # every rank's gradients are final
         for a, b in self._remaining():
             self._rs(a, b)
+        if extra_sumsq is not None and self.rank == 0:
+            self.partial += extra_sumsq.to(torch.float32).reshape(1)
         rc = self._lib.nplm_publish(self.slot_ptrs, c_int(self.rank), c_int(self.world), ptr(self.partial),
                                     stream_ptr())
         check_rc(rc, "publish")
@@ -193,6 +198,8 @@ class FusedShardedStep:
         check_rc(rc, "adamw_push")
         count_launch(2)
         self.barrier()                                   # every rank's parameter buffer is complete
+        if extra_sumsq is not None:
+            e._sumsq.copy_((self.norm / grad_scale) ** 2)
         if self.timing:
             t1.record(main)
             self.tail_events.append((t0, t1))

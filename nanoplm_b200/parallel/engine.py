@@ -234,11 +234,9 @@ class ShardedEngine:
         grad_scale = 1.0 / (grad_accum * self.world)
         self._fill_hyper(lr, grad_scale)
         if self.fused is not None:
-            if extra_sumsq is not None:
-                raise ValueError("extra_sumsq is not supported by the fused communication step")
             from nanoplm_b200.ops import functional as ops
             ops.set_wgrad_ready_callback(None)
-            return self.fused.step(lr, grad_scale)
+            return self.fused.step(lr, grad_scale, extra_sumsq)
         # 1. reduce-scatter: the owned slice of main_grad becomes the sum over ranks
         if self.distributed:
             shard_grad = torch.empty(self.shard, dtype=torch.float32, device=self.device)

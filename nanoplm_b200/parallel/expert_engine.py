@@ -3,7 +3,8 @@
 
 Dense parameters (attention, dense MLPs, routers, norms, embeddings) go through the sharded
 data-parallel engine unchanged: gradients are summed over ranks, AdamW runs on the owned slice,
-the bf16 copy is all-gathered. Expert weights are rank-local: every rank owns
+the bf16 copy is all-gathered (NCCL, or with `fused_comm` the peer-memory kernels with the
+reduce-scatter under the backward pass). Expert weights are rank-local: every rank owns
 num_experts / world experts, their gradients already contain the contributions of ALL ranks'
 tokens (the rows travelled to the owner in the forward pass and their gradients came back in the
 backward pass), so they are neither reduced nor gathered; they only share the scaling
@@ -39,11 +40,12 @@ def shard_model_experts(model: torch.nn.Module, group) -> int:
 
 class ExpertParallelEngine(ShardedEngine):
     def __init__(self, model, hyper: AdamWHyper, device, process_group=None,
-                 compute_dtype: torch.dtype = torch.bfloat16):
+                 compute_dtype: torch.dtype = torch.bfloat16, fused_comm: bool = False):
         expert_names = [n for n, _ in model.named_parameters() if is_expert_param(n)]
         if not expert_names:
             raise ValueError("the model has no expert parameters (model.moe is not configured)")
-        super().__init__(model, hyper, device, process_group, compute_dtype=compute_dtype, fused_comm=False,
+        # dense part: the sharded engine, with the peer-memory optimizer step when asked for
+        super().__init__(model, hyper, device, process_group, compute_dtype=compute_dtype, fused_comm=fused_comm,
                          exclude=expert_names)
         named = dict(model.named_parameters())
         self.x_slots: list[ParamSlot] = []

@@ -224,7 +224,8 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
         if shard_model_experts(model, dist.group.WORLD) == 0:
             raise ValueError("expert_parallel_size > 1 needs a model with model.moe configured")
         engine = ExpertParallelEngine(model, hyper, device,
-                                      compute_dtype=torch.bfloat16 if use_bf16 else torch.float32)
+                                      compute_dtype=torch.bfloat16 if use_bf16 else torch.float32,
+                                      fused_comm=bool(cfg.fused_comm))
     elif opt_name in ("muon", "normuon"):
         from nanoplm_b200.parallel.muon import MuonEngine
         engine = MuonEngine(model, hyper, cfg, device)

@@ -357,7 +357,7 @@ def _moe_train_worker(rank, world, port, out_path):
     hyper = AdamWHyper(lr=2e-3, weight_decay=0.01)
     if world > 1:
         assert shard_model_experts(model, dist.group.WORLD) == 1
-        eng = ExpertParallelEngine(model, hyper, dev)
+        eng = ExpertParallelEngine(model, hyper, dev, fused_comm=True)   # dense part on the peer-memory step
     else:
         eng = ShardedEngine(model, hyper, dev)
     model.train()
