@@ -173,6 +173,7 @@ class PretrainingConfig:
     balance_ranks: bool = True           # deal each optimizer step's sequences to ranks / micro-batches by cost
     balance_quadratic: float = 1.0 / 2700.0   # cost(len) = len + balance_quadratic * len^2
     shard_params: bool = False           # keep 1/N of every layer's weights per rank, gather inside the GEMMs
+    nvtx_ranges: bool = False            # NVTX ranges around data / forward / backward / optimizer (for profilers)
 
 
 @dataclass

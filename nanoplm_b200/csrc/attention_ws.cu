@@ -565,20 +565,26 @@ __device__ __forceinline__ WsBwdGeo ws_bwd_geometry(const FaWsBwdArgs& args, int
 // DQ: also form dQ = dS K per step and add it to the fp32 accumulator with vector atomics. Without
 // it the kernel produces dK / dV only and dQ comes from fa_dq_ws_kernel (no atomics, no scratch,
 // bitwise reproducible).
-template <int NWG>
+// With four compute warpgroups and DQ, a further warpgroup does nothing but read each step's dQ
+// tile out of tensor memory and add it to the accumulator: the vector atomics saturate the L2's
+// atomic rate (about 1 GB of fp32 adds per backward pass), and issued by the compute warps they
+// stalled the exponentials behind the load / store queue.
+template <int NWG, bool DQ>
 struct WsBwdCfg {
-  static constexpr int THREADS = (NWG + 1) * 128;
-  static constexpr int LOADER_WARP = NWG * 4, MMA_WARP = NWG * 4 + 1;
+  static constexpr bool DRAIN_WG = NWG == 4 && DQ;
+  static constexpr int THREADS = (NWG + 1 + (DRAIN_WG ? 1 : 0)) * 128;
+  static constexpr int LOADER_WARP = NWG * 4, MMA_WARP = NWG * 4 + 1, DRAIN_WARP = NWG * 4 + 4;
   static constexpr int CPT = FA_T / NWG;              // key columns per thread
-  static constexpr int REGS_LAUNCH = NWG == 2 ? 168 : 96;
-  static constexpr int REGS_LIGHT = NWG == 2 ? 72 : 56;
-  static constexpr int REGS_HEAVY = NWG == 2 ? 216 : 104;
-  static_assert(128 * REGS_LIGHT + NWG * 128 * REGS_HEAVY <= THREADS * REGS_LAUNCH,
+  // registers per thread the launch allocates: the most a scheduler's share of the warps allows
+  static constexpr int REGS_LAUNCH = NWG == 2 ? 168 : (DRAIN_WG ? 80 : 96);
+  static constexpr int REGS_LIGHT = NWG == 2 ? 72 : (DRAIN_WG ? 48 : 56);   // loader / MMA issuers / dQ drain
+  static constexpr int REGS_HEAVY = NWG == 2 ? 216 : (DRAIN_WG ? 96 : 104);
+  static_assert((THREADS - NWG * 128) * REGS_LIGHT + NWG * 128 * REGS_HEAVY <= THREADS * REGS_LAUNCH,
                 "setmaxnreg.inc would wait forever for registers the CTA does not own");
 };
 
 template <int NWG, bool DQ>
-__global__ void __launch_bounds__(WsBwdCfg<NWG>::THREADS, 1)
+__global__ void __launch_bounds__(WsBwdCfg<NWG, DQ>::THREADS, 1)
 fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                  const FaWsBwdArgs args) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -606,7 +612,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  using Cfg = WsBwdCfg<NWG>;
+  using Cfg = WsBwdCfg<NWG, DQ>;
   constexpr int CPT = Cfg::CPT;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -628,7 +634,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
     mbar_init(sdp_free, NWG * 4);   // one lane of each compute warp
     mbar_init(pds_ready, NWG * 4);     // one lane per compute warp, after every lane's proxy fence
     mbar_init(g_done, DQ ? 2 : 1);           // issuer B, and C when it runs
-    mbar_init(dq_free, NWG * 4);
+    mbar_init(dq_free, Cfg::DRAIN_WG ? 4 : NWG * 4);   // the warps that read dQ back
     mbar_init(acc_free, 8);       // the two warpgroups that read dK / dV back
     *abort_flag = 0;
     fence_barrier_init();
@@ -654,7 +660,52 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
 
   if (warp >= NWG * 4) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_LIGHT));
-  if (warp == Cfg::LOADER_WARP) {
+  if (Cfg::DRAIN_WG && warp >= Cfg::DRAIN_WARP) {
+    // ------------------------------------------------------------------ dQ drain warpgroup
+    // thread = query row of the step's tile; waits for the step's products, copies the row's 64
+    // channels out of tensor memory, hands the tile back and issues 16 vector atomics
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    uint32_t c_g = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int h = item % H;
+      const WsBwdGeo g = ws_bwd_geometry(args, item / H);
+      for (int j = 0; j < g.n_q; ++j) {
+        ok = mbar_wait(g_done, c_g & 1u);
+        ++c_g;
+        ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+        if (!ok) break;
+        tc_fence_after();
+        const int q = g.q_lo + j * FA_T + r;
+        const bool live = q < T && q < g.q_hi;
+        float* dst = args.dq_acc + static_cast<size_t>(live ? q : 0) * HD + h * FA_D;
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {     // 32 channels at a time: this warpgroup runs on few registers
+          uint32_t v[32];
+          tmem_ld32(tdQ + lane_addr + hlf * 32, v);
+          tmem_ld_wait();
+          if (hlf == 1) {                       // both halves are in registers / on their way to memory
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dq_free);
+          }
+          if (live) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              atomicAdd(reinterpret_cast<float4*>(dst + hlf * 32 + e),
+                        make_float4(__uint_as_float(v[e]) * args.scale, __uint_as_float(v[e + 1]) * args.scale,
+                                    __uint_as_float(v[e + 2]) * args.scale, __uint_as_float(v[e + 3]) * args.scale));
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0 && *abort_flag == 0) {
+      atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
+      *abort_flag = 1;
+    }
+  } else if (warp == Cfg::LOADER_WARP) {
     // ------------------------------------------------------------------ loader
     if (lane == 0) {
       uint32_t ic = 0, qc = 0;
@@ -815,7 +866,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
     };
     // dQ tile of the step whose query rows start at q0: this thread adds its share of the channels of row q0 + r
     auto drain_dq = [&](int q0, int q_hi, int h) {
-      if constexpr (DQ) {
+      if constexpr (DQ && !Cfg::DRAIN_WG) {
         constexpr int DQC = FA_D / NWG;       // dQ channels per thread
         uint32_t v[DQC];
         if constexpr (DQC == 32) tmem_ld32(tdQ + lane_addr + gh * DQC, v);
@@ -1231,11 +1282,11 @@ extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout
     mode = (e != nullptr && (e[0] == '2' || e[0] == '0')) ? e[0] - '0' : 4;
   }
   if (mode == 2)
-    fa_bwd_ws_kernel<2, true><<<grid, WsBwdCfg<2>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<2, true><<<grid, WsBwdCfg<2, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   else if (mode == 0)
-    fa_bwd_ws_kernel<4, false><<<grid, WsBwdCfg<4>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<4, false><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   else
-    fa_bwd_ws_kernel<4, true><<<grid, WsBwdCfg<4>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<4, true><<<grid, WsBwdCfg<4, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   {
     const long long total = static_cast<long long>(T) * H * 4;
     long long blocks = (total + 255) / 256;

@@ -17,6 +17,7 @@ import gc
 import math
 import os
 import random
+import contextlib
 import time
 from pathlib import Path
 from typing import Optional
@@ -334,6 +335,13 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                 f"params={engine.num_parameters():,}, bf16={use_bf16}")
 
     moe_layers = [m for m in model.modules() if hasattr(m, "dropped_rows") and hasattr(m, "experts_Wi")]
+    use_nvtx = bool(getattr(cfg, "nvtx_ranges", False)) and device.type == "cuda"
+
+    def _range(name: str):
+        """NVTX range (`pretraining.nvtx_ranges: true`) so that a timeline profiler shows the phases
+        of a step; a no-op context otherwise."""
+        return torch.cuda.nvtx.range(name) if use_nvtx else contextlib.nullcontext()
+
     global_step = start_step
     window_loss = torch.zeros((), dtype=torch.float32, device=device)
     accum_loss = torch.zeros((), dtype=torch.float32, device=device)
@@ -378,15 +386,18 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
             boundary = (micro_step + 1) % grad_accum == 0 or micro_step + 1 == n_micro
             if boundary and hasattr(engine, "begin_last_microstep"):
                 engine.begin_last_microstep()    # gradient reduction overlaps this backward pass
-            out = model(**model_inputs(dev_batch))
-            loss = out["loss"]
-            loss.backward()
+            with _range("forward"):
+                out = model(**model_inputs(dev_batch))
+                loss = out["loss"]
+            with _range("backward"):
+                loss.backward()
             accum_loss += loss.detach().float()
             if not boundary:
                 continue
             n_acc = (micro_step % grad_accum) + 1
             lr = scheduler.get_lr()
-            last_grad_norm = engine.step(lr, n_acc)
+            with _range("optimizer_step"):
+                last_grad_norm = engine.step(lr, n_acc)
             scheduler.step()
             global_step += 1
             if heartbeat is not None:
