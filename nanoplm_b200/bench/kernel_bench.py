@@ -173,8 +173,10 @@ def bench_attn_ws(T, peaks):
         out, lse = k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl="ws")
         ms_b = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws"), iters=5,
                        flush=flush)
+        ms_d = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws",
+                                        deterministic=True), iters=5, flush=flush)
         print(json.dumps({"kernel": "fa_varlen_ws", "window": window, "T": T, "fwd_ms": round(ms, 4),
-                          "bwd_ms": round(ms_b, 4)}), flush=True)
+                          "bwd_ms": round(ms_b, 4), "bwd_deterministic_ms": round(ms_d, 4)}), flush=True)
     k.check_status()
 
 

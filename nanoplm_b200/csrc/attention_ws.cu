@@ -563,8 +563,8 @@ __device__ __forceinline__ WsBwdGeo ws_bwd_geometry(const FaWsBwdArgs& args, int
 // scheduler (the per-element work has no cross-thread dependency, so the split is free) at 104
 // registers per thread; two warpgroups run at 216.
 // DQ: also form dQ = dS K per step and add it to the fp32 accumulator with vector atomics. Without
-// it the kernel produces dK / dV only and dQ comes from fa_dq_ws_kernel (no atomics, no scratch,
-// bitwise reproducible).
+// it the kernel produces dK / dV only and dQ comes from the query-stationary launch (MODE 2 below: no
+// atomics, no scratch, bitwise reproducible).
 // With four compute warpgroups and DQ, a further warpgroup does nothing but read each step's dQ
 // tile out of tensor memory and add it to the accumulator: the vector atomics saturate the L2's
 // atomic rate (about 1 GB of fp32 adds per backward pass), and issued by the compute warps they
@@ -583,8 +583,16 @@ struct WsBwdCfg {
                 "setmaxnreg.inc would wait forever for registers the CTA does not own");
 };
 
-template <int NWG, bool DQ>
-__global__ void __launch_bounds__(WsBwdCfg<NWG, DQ>::THREADS, 1)
+// MODE 0: key-stationary, dK / dV only. MODE 1: key-stationary, dK / dV and dQ through atomics.
+// MODE 2: QUERY-stationary: an item is one 128-query tile, the key tiles that can see it stream by,
+// and dQ accumulates in tensor memory over the whole item; at the end warpgroup 0 scales it, rotates
+// it back and stores bf16 straight into dqkv. Same loads, same S / dP products and the same
+// per-element code with the two sides swapped (the mask is symmetric); no dK / dV, no atomics, no
+// scratch. MODE 0 + MODE 2 together are the bitwise-reproducible backward pass.
+constexpr int BWD_KV = 0, BWD_KV_DQ = 1, BWD_Q = 2;
+
+template <int NWG, int MODE>
+__global__ void __launch_bounds__(WsBwdCfg<NWG, MODE == BWD_KV_DQ>::THREADS, 1)
 fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                  const FaWsBwdArgs args) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -612,6 +620,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  constexpr bool DQ = MODE == BWD_KV_DQ, QST = MODE == BWD_Q;
   using Cfg = WsBwdCfg<NWG, DQ>;
   constexpr int CPT = Cfg::CPT;
   const int tid = threadIdx.x;
@@ -624,17 +633,17 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], DQ ? 2 : 1);   // issuer A, and C when it runs
+      mbar_init(&kv_empty[i], DQ ? 2 : 1);   // issuer A, and C when it reads K from the item's buffer
     }
     for (int i = 0; i < WSB_Q_STAGES; ++i) {
       mbar_init(&qdo_full[i], 1);
-      mbar_init(&qdo_empty[i], 2);           // issuers A and B
+      mbar_init(&qdo_empty[i], 2);           // issuers A and B (query-stationary: A and C)
     }
     mbar_init(sdp_full, 1);
     mbar_init(sdp_free, NWG * 4);   // one lane of each compute warp
     mbar_init(pds_ready, NWG * 4);     // one lane per compute warp, after every lane's proxy fence
-    mbar_init(g_done, DQ ? 2 : 1);           // issuer B, and C when it runs
-    mbar_init(dq_free, Cfg::DRAIN_WG ? 4 : NWG * 4);   // the warps that read dQ back
+    mbar_init(g_done, DQ ? 2 : 1);           // issuer B, and C when both run (query-stationary: C alone)
+    mbar_init(dq_free, (Cfg::DRAIN_WG || QST) ? 4 : NWG * 4);   // the warps that read dQ back
     mbar_init(acc_free, 8);       // the two warpgroups that read dK / dV back
     *abort_flag = 0;
     fence_barrier_init();
@@ -716,14 +725,26 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         const uint32_t kb = ic & 1u;
         if (!mbar_wait(&kv_empty[kb], ((ic >> 1) & 1u) ^ 1u)) { ok = false; break; }
         mbar_arrive_expect_tx(&kv_full[kb], 2 * FA_TILE_BYTES);
-        tma_load_2d(sK + kb * FA_TILE_BYTES, &tmQKV, &kv_full[kb], HD + h * FA_D, g.kv0);
-        tma_load_2d(sV + kb * FA_TILE_BYTES, &tmQKV, &kv_full[kb], 2 * HD + h * FA_D, g.kv0);
+        // item buffer: the stationary pair (K, V of the key tile; query-stationary: Q, dO of the query tile)
+        if constexpr (QST) {
+          tma_load_2d(sK + kb * FA_TILE_BYTES, &tmQKV, &kv_full[kb], h * FA_D, g.kv0);
+          tma_load_2d(sV + kb * FA_TILE_BYTES, &tmDO, &kv_full[kb], h * FA_D, g.kv0);
+        } else {
+          tma_load_2d(sK + kb * FA_TILE_BYTES, &tmQKV, &kv_full[kb], HD + h * FA_D, g.kv0);
+          tma_load_2d(sV + kb * FA_TILE_BYTES, &tmQKV, &kv_full[kb], 2 * HD + h * FA_D, g.kv0);
+        }
         for (int j = 0; j < g.n_q; ++j, ++qc) {
           const uint32_t st = qc % WSB_Q_STAGES, ph = (qc / WSB_Q_STAGES) & 1u;
           if (!mbar_wait(&qdo_empty[st], ph ^ 1u)) { ok = false; break; }
           mbar_arrive_expect_tx(&qdo_full[st], 2 * FA_TILE_BYTES);
-          tma_load_2d(sQ + st * FA_TILE_BYTES, &tmQKV, &qdo_full[st], h * FA_D, g.q_lo + j * FA_T);
-          tma_load_2d(sdO + st * FA_TILE_BYTES, &tmDO, &qdo_full[st], h * FA_D, g.q_lo + j * FA_T);
+          // ring: the streamed pair (Q, dO; query-stationary: K, V)
+          if constexpr (QST) {
+            tma_load_2d(sQ + st * FA_TILE_BYTES, &tmQKV, &qdo_full[st], HD + h * FA_D, g.q_lo + j * FA_T);
+            tma_load_2d(sdO + st * FA_TILE_BYTES, &tmQKV, &qdo_full[st], 2 * HD + h * FA_D, g.q_lo + j * FA_T);
+          } else {
+            tma_load_2d(sQ + st * FA_TILE_BYTES, &tmQKV, &qdo_full[st], h * FA_D, g.q_lo + j * FA_T);
+            tma_load_2d(sdO + st * FA_TILE_BYTES, &tmDO, &qdo_full[st], h * FA_D, g.q_lo + j * FA_T);
+          }
         }
         if (*abort_flag) ok = false;
       }
@@ -762,12 +783,14 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           tc_fence_after();
           const uint64_t dQ0 = make_smem_desc(smem_u32(sQ + st * FA_TILE_BYTES), 16, 1024);
           const uint64_t dO0 = make_smem_desc(smem_u32(sdO + st * FA_TILE_BYTES), 16, 1024);
+          // S[q][kv] = Q K^T, dP[q][kv] = dO V^T: the query side is the A operand. Key-stationary: the
+          // ring holds (Q, dO), the item buffer (K, V); query-stationary: the other way round
 #pragma unroll
           for (int k = 0; k < FA_D / 16; ++k)
-            umma_bf16(tS, dQ0 + 2 * k, dK0 + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+            umma_bf16(tS, (QST ? dK0 : dQ0) + 2 * k, (QST ? dQ0 : dK0) + 2 * k, idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
           for (int k = 0; k < FA_D / 16; ++k)
-            umma_bf16(tdP, dO0 + 2 * k, dV0 + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+            umma_bf16(tdP, (QST ? dV0 : dO0) + 2 * k, (QST ? dO0 : dV0) + 2 * k, idesc_s, k > 0 ? 1u : 0u);
           umma_commit(sdp_full);
           ++c_sdp;
           umma_commit(&qdo_empty[st]);     // with issuer B
@@ -778,7 +801,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         qc += g.n_q;
         if (*abort_flag) ok = false;
       }
-    } else if (role == 1) {
+    } else if (role == 1 && !QST) {
       const uint64_t dPT = make_smem_desc(smem_u32(sP), FA_TILE_BYTES, 1024);    // P^T / dS^T as MN-major A
       const uint64_t dST = make_smem_desc(smem_u32(sdS), FA_TILE_BYTES, 1024);
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
@@ -828,6 +851,33 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         }
         if (!ok) break;
         umma_commit(&kv_empty[kb]);
+        if (*abort_flag) ok = false;
+      }
+    }
+    else if (role == 2 && QST) {
+      // dQ[q][d] += dS[q][kv] K[kv][d] over the item's key tiles (K = ring slot 0, read MN-major)
+      const uint64_t dS0 = make_smem_desc(smem_u32(sdS), 16, 1024);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
+        const WsBwdGeo g = ws_bwd_geometry(args, item / H);
+        for (int j = 0; j < g.n_q; ++j) {
+          const uint32_t step = qc + j;
+          const uint32_t st = step % WSB_Q_STAGES, ph = (step / WSB_Q_STAGES) & 1u;
+          if (!mbar_wait(pds_ready, c_pds & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
+          ++c_pds;
+          if (!mbar_wait(&qdo_full[st], ph)) { ok = false; break; }
+          // the previous item's dQ has been read back before this item's first product overwrites it
+          if (j == 0 && !mbar_wait(dq_free, (ic & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
+          tc_fence_after();
+          const uint64_t dKr = make_smem_desc(smem_u32(sQ + st * FA_TILE_BYTES), 8192, 1024);
+#pragma unroll
+          for (int k = 0; k < FA_T / 16; ++k)
+            umma_bf16(tdQ, dS0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dKr + k * 128, idesc_dq,
+                      (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(g_done);
+          umma_commit(&qdo_empty[st]);     // with issuer A
+        }
+        if (!ok) break;
+        qc += g.n_q;
         if (*abort_flag) ok = false;
       }
     }
@@ -890,11 +940,12 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const int h = item % H;
       const WsBwdGeo g = ws_bwd_geometry(args, item / H);
-      RowInfo nxt = fetch_row(g.q_lo + r, h);
+      // key-stationary: the query row changes with every step; query-stationary: one row per item
+      RowInfo nxt = fetch_row((QST ? g.kv0 : g.q_lo) + r, h);
       for (int j = 0; j < g.n_q; ++j) {
-        const int q0 = g.q_lo + j * FA_T;
+        const int q0 = g.q_lo + j * FA_T;      // first row of the streamed tile (queries, or keys when QST)
         const RowInfo ri = nxt;
-        if (j + 1 < g.n_q) nxt = fetch_row(q0 + FA_T + r, h);
+        if (!QST && j + 1 < g.n_q) nxt = fetch_row(q0 + FA_T + r, h);
         ok = mbar_wait(sdp_full, c_sdp & 1u);
         ++c_sdp;
         ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
@@ -923,7 +974,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           drain_dq(q0 - FA_T, g.q_hi, h);
         }
         // keys of this thread's columns: [c0, c0 + CPT)
-        const int c0 = g.kv0 + gh * CPT;
+        const int c0 = (QST ? q0 : g.kv0) + gh * CPT;
         const bool inside = __all_sync(0xffffffffu, c0 >= ri.klo && c0 + CPT <= ri.khi);
         const bool outside = __all_sync(0xffffffffu, c0 >= ri.khi || c0 + CPT <= ri.klo);
         // first 16-byte chunk of this thread: column block (gh * CPT) / 64, chunk ((gh * CPT) % 64) / 8
@@ -937,7 +988,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
 #pragma unroll
           for (int c8 = 0; c8 < CPT / 8; ++c8) {
             const uint32_t off = static_cast<uint32_t>(((chunk0 + c8) ^ rx) << 4);
-            *reinterpret_cast<uint4*>(rowP + off) = make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (!QST) *reinterpret_cast<uint4*>(rowP + off) = make_uint4(0u, 0u, 0u, 0u);
             *reinterpret_cast<uint4*>(rowS + off) = make_uint4(0u, 0u, 0u, 0u);
           }
         } else {
@@ -960,7 +1011,8 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
               dk[u] = pack_bf16x2(d0, d1);
             }
             const uint32_t off = static_cast<uint32_t>(((chunk0 + c8) ^ rx) << 4);
-            *reinterpret_cast<uint4*>(rowP + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if constexpr (!QST)      // the query-stationary pass forms dQ only: P itself is not needed
+              *reinterpret_cast<uint4*>(rowP + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             *reinterpret_cast<uint4*>(rowS + off) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
           }
         }
@@ -979,11 +1031,13 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         drain_dq(g.q_lo + (g.n_q - 1) * FA_T, g.q_hi, h);
       }
       WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 5);
-      // dK (warpgroup 0) / dV (warpgroup 1): every thread owns the 64 channels of key row kv0 + r
-      if (gh >= 2) continue;
+      // dK (warpgroup 0) / dV (warpgroup 1): every thread owns the 64 channels of key row kv0 + r.
+      // Query-stationary: warpgroup 0 alone reads the item's dQ (row kv0 + r of the query tile).
+      if (gh >= (QST ? 1 : 2)) continue;
+      uint64_t* const read_back = QST ? dq_free : acc_free;
       float acc[FA_D];
       if (g.n_q > 0) {
-        const uint32_t src = (gh == 0 ? tdK : tdV) + lane_addr;
+        const uint32_t src = (QST ? tdQ : (gh == 0 ? tdK : tdV)) + lane_addr;
 #pragma unroll
         for (int c = 0; c < FA_D; c += 32) {
           uint32_t v[32];
@@ -994,12 +1048,12 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_free);
+        if (lane == 0) mbar_arrive(read_back);
       } else {
 #pragma unroll
         for (int e = 0; e < FA_D; ++e) acc[e] = 0.f;
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_free);   // keeps the per-item phase count in step with the MMA warp
+        if (lane == 0) mbar_arrive(read_back);   // keeps the per-item phase count in step with the MMA warp
       }
       const int krow = g.kv0 + r;
       if (krow < T) {
@@ -1025,7 +1079,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             }
           }
         }
-        __nv_bfloat16* dst = args.dqkv + (static_cast<size_t>(krow) * 3 + 1 + gh) * HD + h * FA_D;
+        __nv_bfloat16* dst = args.dqkv + (static_cast<size_t>(krow) * 3 + (QST ? 0 : 1 + gh)) * HD + h * FA_D;
 #pragma unroll
         for (int e = 0; e < FA_D; e += 8) {
           uint4 u4;
@@ -1170,11 +1224,13 @@ static int ws_configure(int* sms) {
                                          WS_FWD_SMEM));
     NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_ws_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_FWD_SMEM));
-    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<2, BWD_KV_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_BWD_SMEM));
-    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<4, BWD_KV_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_BWD_SMEM));
-    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<4, BWD_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         WS_BWD_SMEM));
+    NPLM_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_ws_kernel<4, BWD_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          WS_BWD_SMEM));
     int n = 0;
     NPLM_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
@@ -1232,14 +1288,30 @@ extern "C" int nplm_fa_fwd_ws(const void* qkv, void* out, float* lse, const int*
 // computed here from out and dout unless out is null (then it must hold rowsum(dO * O) already).
 // rope_* (may be null): q / k were rotated before the forward pass; dQ and dK are returned as
 // gradients of the un-rotated projections.
-extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout, const float* lse,
-                              void* dqkv, float* dq_acc, float* delta, const int* seq_start,
-                              const int* seq_end, int T, int H, int D, int window, float scale,
-                              const int* rope_pos, const float* rope_cos, const float* rope_sin,
-                              int max_ctas, int* status, cudaStream_t st) {
+// mode: 4 = four compute warpgroups, dQ through fp32 atomics (fastest); 2 = two compute warpgroups, same
+// scheme; 0 = dK / dV only (timing experiments); 3 = bitwise reproducible: a key-stationary launch for
+// dK / dV and a query-stationary launch for dQ, no atomics, dq_acc unused (may be null); -1 = the value
+// of NPLM_FA_BWD_MODE ("2", "0", "det" / "3"), else 4.
+static int ws_bwd_impl(const void* qkv, const void* out, const void* dout, const float* lse,
+                       void* dqkv, float* dq_acc, float* delta, const int* seq_start,
+                       const int* seq_end, int T, int H, int D, int window, float scale,
+                       const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                       int max_ctas, int mode, int* status, cudaStream_t st) {
   if (T <= 0) return 0;
   if (D != FA_D || H <= 0) return -3;
   if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15)) return -3;
+  if (mode < 0) {
+    static int env_mode = -1;
+    if (env_mode < 0) {
+      const char* e = getenv("NPLM_FA_BWD_MODE");
+      env_mode = 4;
+      if (e != nullptr && (e[0] == '2' || e[0] == '0' || e[0] == '3')) env_mode = e[0] - '0';
+      if (e != nullptr && e[0] == 'd') env_mode = 3;
+    }
+    mode = env_mode;
+  }
+  if (mode != 0 && mode != 2 && mode != 3 && mode != 4) return -3;
+  if (mode != 3 && dq_acc == nullptr) return -3;
   CUtensorMap tmQKV, tmDO;
   int rc = ws_make_map(&tmQKV, qkv, static_cast<uint64_t>(3) * H * D, T);
   if (rc) return rc;
@@ -1249,7 +1321,8 @@ extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout
   rc = ws_configure(&sms);
   if (rc) return rc;
   const int HD = H * D;
-  NPLM_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * HD * sizeof(float), st));
+  if (mode != 3)
+    NPLM_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * HD * sizeof(float), st));
   if (out != nullptr) {
     const long long total = static_cast<long long>(T) * H * 8;
     long long blocks = (total + 255) / 256;
@@ -1276,17 +1349,17 @@ extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout
   int grid = sms;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (grid > n_items) grid = n_items;
-  static int mode = -1;   // NPLM_FA_BWD_MODE: 2 = two compute warpgroups, 4 = four (default), 0 = four, dK / dV only
-  if (mode < 0) {
-    const char* e = getenv("NPLM_FA_BWD_MODE");
-    mode = (e != nullptr && (e[0] == '2' || e[0] == '0')) ? e[0] - '0' : 4;
+  if (mode == 2) {
+    fa_bwd_ws_kernel<2, BWD_KV_DQ><<<grid, WsBwdCfg<2, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  } else if (mode == 0) {
+    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+  } else if (mode == 3) {
+    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<4, BWD_Q><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    return static_cast<int>(cudaGetLastError());
+  } else {
+    fa_bwd_ws_kernel<4, BWD_KV_DQ><<<grid, WsBwdCfg<4, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   }
-  if (mode == 2)
-    fa_bwd_ws_kernel<2, true><<<grid, WsBwdCfg<2, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
-  else if (mode == 0)
-    fa_bwd_ws_kernel<4, false><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
-  else
-    fa_bwd_ws_kernel<4, true><<<grid, WsBwdCfg<4, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
   {
     const long long total = static_cast<long long>(T) * H * 4;
     long long blocks = (total + 255) / 256;
@@ -1295,6 +1368,25 @@ extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout
         dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), T, H, rope_pos, rope_cos, rope_sin);
   }
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nplm_fa_bwd_ws(const void* qkv, const void* out, const void* dout, const float* lse,
+                              void* dqkv, float* dq_acc, float* delta, const int* seq_start,
+                              const int* seq_end, int T, int H, int D, int window, float scale,
+                              const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                              int max_ctas, int* status, cudaStream_t st) {
+  return ws_bwd_impl(qkv, out, dout, lse, dqkv, dq_acc, delta, seq_start, seq_end, T, H, D, window, scale,
+                     rope_pos, rope_cos, rope_sin, max_ctas, -1, status, st);
+}
+
+// Same with the mode given by the caller (see ws_bwd_impl).
+extern "C" int nplm_fa_bwd_ws_mode(const void* qkv, const void* out, const void* dout, const float* lse,
+                                   void* dqkv, float* dq_acc, float* delta, const int* seq_start,
+                                   const int* seq_end, int T, int H, int D, int window, float scale,
+                                   const int* rope_pos, const float* rope_cos, const float* rope_sin,
+                                   int max_ctas, int mode, int* status, cudaStream_t st) {
+  return ws_bwd_impl(qkv, out, dout, lse, dqkv, dq_acc, delta, seq_start, seq_end, T, H, D, window, scale,
+                     rope_pos, rope_cos, rope_sin, max_ctas, mode, status, st);
 }
 
 #ifdef NPLM_WS_TRACE

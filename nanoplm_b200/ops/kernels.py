@@ -480,14 +480,27 @@ def gemm_dgrad_delta(dy: torch.Tensor, w: torch.Tensor, o: torch.Tensor, delta: 
     return out
 
 
+_FA_DETERMINISTIC = [_os.environ.get("NPLM_FA_DETERMINISTIC", "0") not in ("", "0")]
+
+
+def set_attention_deterministic(flag: bool) -> None:
+    """True: the warp-specialised backward pass forms dQ in a second, query-stationary launch instead
+    of fp32 atomics, so two runs on the same inputs give the same bits (about 1.4x the time)."""
+    _FA_DETERMINISTIC[0] = bool(flag)
+
+
 def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=None, delta=None,
-           rope: tuple | None = None, delta_ready: bool = False, impl: str | None = None, max_ctas: int = 0):
+           rope: tuple | None = None, delta_ready: bool = False, impl: str | None = None, max_ctas: int = 0,
+           deterministic: bool | None = None):
     """rope = (pos, cos, sin): q / k in qkv were rotated before the forward pass; dQ / dK are rotated
     back inside the kernels. delta_ready: `delta` [H, T] already holds rowsum(dO * O) (see
-    gemm_dgrad_delta); the kernel that computes it from out and dout is skipped."""
+    gemm_dgrad_delta); the kernel that computes it from out and dout is skipped. deterministic (default:
+    `set_attention_deterministic`): no atomics, bitwise reproducible (warp-specialised kernels only)."""
     T = qkv.shape[0]
     dqkv = torch.empty_like(qkv)
-    if dq_acc is None:
+    use_ws = (impl or _FA_IMPL[0]) == "ws"
+    det = use_ws and (_FA_DETERMINISTIC[0] if deterministic is None else deterministic)
+    if dq_acc is None and not det:
         dq_acc = torch.empty((T, H * D), dtype=torch.float32, device=qkv.device)
     if delta is None:
         delta = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
@@ -496,12 +509,13 @@ def fa_bwd(qkv, out, dout, lse, seq_start, seq_end, H, D, window, scale, dq_acc=
     r_pos, r_cos, r_sin = rope if rope is not None else (None, None, None)
     if delta_ready:
         out = None
-    if (impl or _FA_IMPL[0]) == "ws":
-        rc = lib("attention_ws").nplm_fa_bwd_ws(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
-                                                ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
-                                                c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
-                                                ptr(r_pos), ptr(r_cos), ptr(r_sin), c_int(max_ctas),
-                                                ptr(status_word(qkv.device)), stream_ptr())
+    if use_ws:
+        rc = lib("attention_ws").nplm_fa_bwd_ws_mode(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
+                                                     ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),
+                                                     c_int(T), c_int(H), c_int(D), c_int(window), c_float(scale),
+                                                     ptr(r_pos), ptr(r_cos), ptr(r_sin), c_int(max_ctas),
+                                                     c_int(3 if det else -1),
+                                                     ptr(status_word(qkv.device)), stream_ptr())
     else:
         rc = lib("attention").nplm_fa_bwd_rope(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
                                                ptr(dq_acc), ptr(delta), ptr(seq_start), ptr(seq_end),

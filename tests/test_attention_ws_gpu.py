@@ -173,3 +173,64 @@ def test_ws_backward_dk_dv_are_bitwise_reproducible(cuda_status):
         b = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws")
         assert torch.equal(a[:, HD:], b[:, HD:])
         assert (a[:, :HD].float() - b[:, :HD].float()).abs().max().item() <= 2.0 ** -6 * a[:, :HD].float().abs().max().item()
+
+
+DET_SWEEP = [[77], [128, 128], [300, 45, 512, 3], [512] * 3 + [20] * 7]
+
+
+@pytest.mark.parametrize("lens", DET_SWEEP, ids=lambda l: "-".join(map(str, l))[:40])
+@pytest.mark.parametrize("window", [-1, 64])
+def test_ws_backward_deterministic_mode_matches_autograd_of_the_oracle(lens, window, cuda_status):
+    """The query-stationary dQ launch against fp32 autograd, and dK / dV identical to the default mode."""
+    k = _k()
+    H, D = 4, 64
+    cu = _cu(lens)
+    T = cu[-1]
+    torch.manual_seed(5 * T + window)
+    qkv = torch.randn(T, 3 * H * D, device="cuda").to(BF)
+    dout = torch.randn(T, H * D, device="cuda").to(BF)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    ss, se = k.seq_bounds(cu_t, T)
+    scale = D ** -0.5
+    out, lse = k.fa_fwd(qkv, ss, se, H, D, window, scale, impl="ws")
+    qf = qkv.float().requires_grad_(True)
+    ref, _ = _oracle(qf, cu, H, D, window, scale)
+    ref.backward(dout.float())
+    det = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, scale, impl="ws", deterministic=True)
+    g = qf.grad
+    tol = 2.0 ** -6 * g.abs().max().item() + 2e-2
+    err = (det.float() - g).abs().max().item()
+    assert err <= tol, f"deterministic backward {lens} w={window}: max err {err} (tol {tol})"
+    dflt = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, scale, impl="ws", deterministic=False)
+    HD = H * D
+    assert torch.equal(det[:, HD:], dflt[:, HD:])
+
+
+def test_ws_backward_deterministic_mode_is_bitwise_reproducible_with_rope(cuda_status):
+    k = _k()
+    H, D = 16, 64
+    g = torch.Generator().manual_seed(9)
+    lens = torch.randint(20, 513, (40,), generator=g).tolist()
+    cu = _cu(lens)
+    T = cu[-1]
+    qkv = torch.randn(T, 3 * H * D, device="cuda").to(BF)
+    dout = torch.randn(T, H * D, device="cuda").to(BF)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    pos = torch.cat([torch.arange(n) for n in lens]).to(torch.int32).cuda()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    fr = torch.outer(torch.arange(512, device="cuda").float(), inv)
+    cos, sin = fr.cos().contiguous(), fr.sin().contiguous()
+    ss, se = k.seq_bounds(cu_t, T)
+    for window in (-1, 64):
+        out, lse = k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl="ws")
+        a = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, rope=(pos, cos, sin), impl="ws",
+                     deterministic=True)
+        b = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, rope=(pos, cos, sin), impl="ws",
+                     deterministic=True)
+        c = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, rope=(pos, cos, sin), impl="ws",
+                     deterministic=True, max_ctas=7)
+        assert torch.equal(a, b)
+        assert torch.equal(a, c)      # the grid changes which CTA runs an item, not the order inside it
+        ref = k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, rope=(pos, cos, sin), impl="single")
+        scale_ = ref.float().abs().max().item()
+        assert (a.float() - ref.float()).abs().max().item() <= 2.0 ** -6 * scale_ + 2e-2
