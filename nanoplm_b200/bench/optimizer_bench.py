@@ -24,6 +24,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--no-fused-comm", action="store_true",
+                    help="library collectives instead of the peer-memory kernels (multi-GPU A/B)")
     ap.add_argument("--per-matrix", action="store_true",
                     help="Muon: orthogonalise matrix by matrix on every rank (no stacking, no split over ranks)")
     args = ap.parse_args()
@@ -43,9 +45,11 @@ def main():
                                            num_attention_heads=16, vocab_size=32, max_position_embeddings=1024), ProtTokenizer())
         hyper = AdamWHyper(lr=1e-3, max_grad_norm=1.0)
         if name == "adamw":
-            eng = ShardedEngine(model, hyper, device, compute_dtype=torch.bfloat16, fused_comm=world > 1)
+            eng = ShardedEngine(model, hyper, device, compute_dtype=torch.bfloat16,
+                                fused_comm=world > 1 and not args.no_fused_comm)
         else:
-            eng = MuonEngine(model, hyper, PretrainingConfig(dataset_dir="x", optimizer=name), device)
+            eng = MuonEngine(model, hyper, PretrainingConfig(dataset_dir="x", optimizer=name), device,
+                             fused_comm=world > 1 and not args.no_fused_comm)
             if args.per_matrix:
                 from nanoplm_b200.parallel.muon import _Stack
                 eng.stacks = [_Stack([s], 0, 1) for s in eng.muon_slots]
@@ -73,7 +77,7 @@ def main():
         _lib.check_status()
         if rank == 0:
             print(json.dumps({"bench": "optimizer_step", "optimizer": name + (" (matrix by matrix, replicated)" if args.per_matrix and name != "adamw" else ""),
-                              "n_gpus": world,
+                              "n_gpus": world, "peer_memory_comm": getattr(eng, "fused", None) is not None,
                               "parameters": eng.num_parameters(), "ms_per_step": round(float(t), 3),
                               "own_kernel_launches_per_step": (_lib.launches() - n0) // args.steps,
                               "note": "includes filling the gradient buffer with random numbers"}), flush=True)

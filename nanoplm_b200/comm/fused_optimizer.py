@@ -291,3 +291,99 @@ class ParamShardedStep(FusedShardedStep):
             t1.record(main)
             self.tail_events.append((t0, t1))
         return self.norm[0]
+
+
+class MuonPeerStep:
+    """Peer-memory communication of the Muon / NorMuon step (`parallel.muon.MuonEngine`), replacing the
+    all-reduce of the whole fp32 gradient and the all-gathers of the orthogonalised updates:
+
+    * every matrix has one owner rank (the rank that orthogonalises it): the owner PULLS and sums the
+      matrix's gradient from all ranks (`rs_sumsq_kernel`, rank order), nobody else reads it;
+    * the few tensors AdamW updates on every rank (embedding, norms, head) are summed by every rank in the
+      same fixed order, so the replicas stay bitwise equal;
+    * the squared norm for clipping: per-rank partial sums (rank 0 adds the AdamW tensors' share) are
+      exchanged through the slot words and added in rank order on every rank;
+    * the owner stores its orthogonalised updates straight into every peer's copy of the stack buffer
+      (`push_kernel`); one flag barrier later every rank applies all updates locally.
+    """
+
+    def __init__(self, engine, grads: SymmetricBuffer, params: SymmetricBuffer, words: SymmetricBuffer,
+                 barrier_timeout_s: float = 20.0):
+        self.e = engine
+        self.grads, self.params, self.words = grads, params, words
+        self.world, self.rank = engine.world, engine.rank
+        self.epoch = 0
+        self.timeout = barrier_timeout_s
+        dev = engine.device
+        self.partial = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.adam_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.flag_ptrs = _ptr_array(words.ptrs)
+        self.slot_ptrs = _ptr_array([p + 8 * 4 for p in words.ptrs])
+        self.local_slots = words.tensor.view(torch.float32)[8:16]
+        self._lib = lib("comm")
+        self.reduced = None            # full-size fp32 buffer holding the sums this rank needs
+        self.stack_buffers: list[SymmetricBuffer] = []
+        self.adam_ranges: list[tuple[int, int]] = []
+        self.nvlink_bytes_in = 0
+
+    barrier = FusedShardedStep.barrier
+
+    def arm(self) -> None:             # the reduction is not split over the backward pass here
+        pass
+
+    def setup(self, stacks, adam_slots) -> None:
+        """Collective: allocates one symmetric bf16 buffer per stack of same-shape matrices."""
+        e = self.e
+        g = e.pg if e.pg is not None else dist.group.WORLD
+        for st in stacks:
+            self.stack_buffers.append(SymmetricBuffer(len(st.slots) * st.slots[0].numel, torch.bfloat16, e.device, g))
+        self.reduced = torch.zeros(e.total, dtype=torch.float32, device=e.device)
+        # contiguous runs of AdamW tensors (slot starts are 64-element aligned, the gaps hold zeros)
+        spans = sorted((s.offset, s.offset + ((s.numel + 3) // 4) * 4) for s in adam_slots)
+        for a, b in spans:
+            if self.adam_ranges and a <= self.adam_ranges[-1][1] + 64:
+                self.adam_ranges[-1] = (self.adam_ranges[-1][0], max(b, self.adam_ranges[-1][1]))
+            else:
+                self.adam_ranges.append((a, b))
+
+    def _rs(self, a: int, b: int, sumsq: torch.Tensor) -> None:
+        rc = self._lib.nplm_rs_sumsq(self.grads.ptr_array, c_int(self.world), c_longlong(a), c_longlong(b - a),
+                                     c_void_p(self.reduced.data_ptr() + 4 * a), ptr(sumsq), stream_ptr())
+        check_rc(rc, "rs_sumsq")
+        count_launch()
+
+    def reduce(self, owned_slots, gsq: torch.Tensor) -> torch.Tensor:
+        """Fills `reduced` with the summed gradients of this rank's matrices and of the AdamW tensors,
+        `gsq` with the squared norm of the whole summed gradient; returns `reduced`."""
+        self.barrier()                                   # every rank's gradients are final
+        self.partial.zero_()
+        self.adam_sq.zero_()
+        n = 0
+        for s in owned_slots:
+            self._rs(s.offset, s.offset + s.numel, self.partial)
+            n += s.numel
+        for a, b in self.adam_ranges:
+            self._rs(a, b, self.adam_sq)
+            n += b - a
+        self.nvlink_bytes_in = 4 * n * (self.world - 1)
+        if self.rank == 0:
+            self.partial += self.adam_sq
+        rc = self._lib.nplm_publish(self.slot_ptrs, c_int(self.rank), c_int(self.world), ptr(self.partial),
+                                    stream_ptr())
+        check_rc(rc, "publish")
+        count_launch()
+        self.barrier()                                   # partial sums exchanged
+        gsq.zero_()
+        for r in range(self.world):                      # same order on every rank: identical clip coefficient
+            gsq += self.local_slots[r:r + 1]
+        return self.reduced
+
+    def push_run(self, index: int, first: int, count: int, numel: int) -> None:
+        """Stores matrices [first, first + count) of stack `index` into every peer's stack buffer."""
+        if count <= 0:
+            return
+        buf = self.stack_buffers[index]
+        rc = self._lib.nplm_push(buf.ptr_array, c_int(self.rank), c_int(self.world), c_longlong(2 * first * numel),
+                                 c_longlong(2 * count * numel), stream_ptr())
+        check_rc(rc, "push")
+        count_launch()

@@ -347,6 +347,14 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         tc_fence_after();
         const bool none = (kv0 + FA_T <= lo) || (kv0 >= hi);
         const bool warp_none = __all_sync(0xffffffffu, none);
+        // 32-key chunks that no row of this warp can see (keys of other sequences, or outside the
+        // window of all 32 rows): no mask, maximum or exponential, their probabilities are zero
+        uint32_t dead = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int c_lo = kv0 + c * 32;
+          if (__all_sync(0xffffffffu, c_lo >= hi || c_lo + 32 <= lo)) dead |= 1u << c;
+        }
         uint32_t r[FA_T];
         if (!warp_none) {
 #pragma unroll
@@ -363,6 +371,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         if (!warp_none) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
+            if ((dead >> c) & 1u) continue;
             const int c_lo = kv0 + c * 32, c_hi = c_lo + 32;
             if (!(c_lo >= lo && c_hi <= hi)) {
 #pragma unroll
@@ -412,11 +421,19 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
           // probabilities packed in place: word c of r[] takes keys 2c, 2c + 1 (both already consumed)
           if (!warp_none) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-              const float p0 = exp2f(fmaf(__uint_as_float(r[2 * c]), sl2, -moff));
-              const float p1 = exp2f(fmaf(__uint_as_float(r[2 * c + 1]), sl2, -moff));
-              ps[c & 3] += p0 + p1;
-              r[c] = pack_bf16x2(p0, p1);
+            for (int q = 0; q < 4; ++q) {
+              if ((dead >> q) & 1u) {
+#pragma unroll
+                for (int c = q * 16; c < q * 16 + 16; ++c) r[c] = 0u;
+              } else {
+#pragma unroll
+                for (int c = q * 16; c < q * 16 + 16; ++c) {
+                  const float p0 = exp2f(fmaf(__uint_as_float(r[2 * c]), sl2, -moff));
+                  const float p1 = exp2f(fmaf(__uint_as_float(r[2 * c + 1]), sl2, -moff));
+                  ps[c & 3] += p0 + p1;
+                  r[c] = pack_bf16x2(p0, p1);
+                }
+              }
             }
           } else {
 #pragma unroll
@@ -432,13 +449,15 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
           if (!warp_none) {
 #pragma unroll
             for (int c8 = 0; c8 < 16; ++c8) {
-              uint32_t pk[4];
+              uint32_t pk[4] = {0u, 0u, 0u, 0u};
+              if (!((dead >> (c8 >> 2)) & 1u)) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float p0 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q]), sl2, -moff));
-                const float p1 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q + 1]), sl2, -moff));
-                ps[q] += p0 + p1;
-                pk[q] = pack_bf16x2(p0, p1);
+                for (int q = 0; q < 4; ++q) {
+                  const float p0 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q]), sl2, -moff));
+                  const float p1 = exp2f(fmaf(__uint_as_float(r[c8 * 8 + 2 * q + 1]), sl2, -moff));
+                  ps[q] += p0 + p1;
+                  pk[q] = pack_bf16x2(p0, p1);
+                }
               }
               *reinterpret_cast<uint4*>(sPi + (c8 >> 3) * FA_TILE_BYTES + swz(row_local, c8 & 7)) =
                   make_uint4(pk[0], pk[1], pk[2], pk[3]);

@@ -13,6 +13,8 @@
 //   adamw_push_kernel : global norm from the per-rank partial sums -> clip coefficient -> AdamW
 //                       on the fp32 master slice -> the updated bf16 values are PUSHED into the
 //                       parameter buffer of every rank (sharded update + all-gather in one pass).
+//   push_kernel       : a range this rank computed in place in a symmetric buffer is stored into every
+//                       peer's copy (Muon: the orthogonalised updates of the matrices a rank owns).
 //   peer_barrier_kernel / publish_kernel : flag-based cross-GPU barrier and the exchange of the
 //                       partial sums. Every wait on a peer flag is bounded and reports
 //                       ST_TIMEOUT_PEER through the status word instead of hanging.
@@ -217,6 +219,21 @@ adamw_push_kernel(float* __restrict__ master, float* __restrict__ m, float* __re
   }
 }
 
+// Copies n16 16-byte words at the same offset of a symmetric buffer from this rank's copy into
+// every other rank's copy (the all-gather of a run that this rank has just computed in place).
+__global__ void __launch_bounds__(512)
+push_kernel(PeerPtrs bufs, int rank, int world, long long word0, long long n16) {
+  const uint4* src = reinterpret_cast<const uint4*>(bufs.p[rank]) + word0;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 v = src[i];
+#pragma unroll
+    for (int p = 0; p < MAX_PEERS; ++p) {
+      if (p < world && p != rank) (reinterpret_cast<uint4*>(bufs.p[p]) + word0)[i] = v;
+    }
+  }
+}
+
 }  // namespace nplm
 
 using namespace nplm;
@@ -284,4 +301,17 @@ extern "C" int nplm_adamw_push(float* master, float* m, float* v, const float* g
                                const float* hyper, const float* slots, float* norm_out, cudaStream_t st) {
   return nplm_adamw_push_ex(master, m, v, g, param_ptrs, world, lo, n, decay_end, hyper, slots, world, norm_out,
                             st);
+}
+
+// buf_ptrs[r]: rank r's copy of one symmetric buffer. Bytes [byte_offset, byte_offset + bytes) of this
+// rank's copy are stored into every other rank's copy. Offsets and sizes are multiples of 16.
+extern "C" int nplm_push(void* const* buf_ptrs, int rank, int world, long long byte_offset, long long bytes,
+                         cudaStream_t st) {
+  if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || (byte_offset & 15) || (bytes & 15)) return -3;
+  if (bytes == 0 || world == 1) return 0;
+  const long long n16 = bytes >> 4;
+  long long blocks = (n16 + 511) / 512;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  push_kernel<<<static_cast<int>(blocks), 512, 0, st>>>(to_peers(buf_ptrs, world), rank, world, byte_offset >> 4, n16);
+  return static_cast<int>(cudaGetLastError());
 }

@@ -158,9 +158,11 @@ class _Stack:
 
 
 class MuonEngine(ShardedEngine):
-    def __init__(self, model, hyper: AdamWHyper, cfg, device, process_group=None):
+    def __init__(self, model, hyper: AdamWHyper, cfg, device, process_group=None, fused_comm: bool | None = None):
         compute = torch.bfloat16 if (getattr(cfg, "bf16", True) and torch.device(device).type == "cuda") else torch.float32
-        super().__init__(model, hyper, device, process_group, compute_dtype=compute, fused_comm=False)
+        if fused_comm is None:
+            fused_comm = bool(getattr(cfg, "fused_comm", True))
+        super().__init__(model, hyper, device, process_group, compute_dtype=compute, fused_comm=fused_comm)
         # replicated parameters and AdamW state: full-size buffers on every rank; the Muon momentum
         # lives in the same flat buffer but only the entries of matrices this rank owns are used
         dev = self.device
@@ -193,6 +195,22 @@ class MuonEngine(ShardedEngine):
         self._gsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self._gscale = 1.0
         self._adam_table = None
+        # peer-memory path: gradients pulled by the matrix owners, updates pushed to every rank
+        if self.fused is not None:
+            usable = self._kernels and all(s.numel % 8 == 0 for s in self.muon_slots)
+            ok = torch.tensor([1.0 if usable else 0.0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.pg)
+            if ok.item() < 1:
+                self.fused = None
+            else:
+                self.fused.setup(self.stacks, self.adam_slots)
+
+    def _make_fused(self, sym):
+        from nanoplm_b200.comm.fused_optimizer import MuonPeerStep
+        return MuonPeerStep(self, *sym)
+
+    def begin_last_microstep(self) -> None:
+        """The Muon step reduces whole matrices after the backward pass: nothing to arm."""
 
     # ---- checkpoint helpers ------------------------------------------------------------------
     def _owned(self):
@@ -262,8 +280,14 @@ class MuonEngine(ShardedEngine):
         [n, r, c]; this rank computes its run, the others arrive by all-gather."""
         n = len(st.slots)
         dt = torch.bfloat16 if self.on_cuda else torch.float32
-        O = torch.zeros((n,) + st.shape, dtype=dt, device=self.device) if not st.even and self.distributed \
-            else torch.empty((n,) + st.shape, dtype=dt, device=self.device)
+        peer = self.fused is not None
+        if peer:
+            index = self.stacks.index(st)
+            O = self.fused.stack_buffers[index].tensor.view((n,) + st.shape)
+        elif not st.even and self.distributed:
+            O = torch.zeros((n,) + st.shape, dtype=dt, device=self.device)
+        else:
+            O = torch.empty((n,) + st.shape, dtype=dt, device=self.device)
         if st.hi > st.lo:
             if self._kernels:
                 from nanoplm_b200.ops import kernels as K
@@ -290,7 +314,9 @@ class MuonEngine(ShardedEngine):
                 scale = 0.2 * math.sqrt(mine[0].numel()) / (mine.flatten(1).norm(dim=1) + self.muon_eps)
                 mine = mine * scale[:, None, None]                                        # rms_norm scaling
             O[st.lo:st.hi] = mine.to(dt)
-        if self.distributed:
+        if peer:
+            self.fused.push_run(index, st.lo, st.hi - st.lo, st.slots[0].numel)   # visible after the next barrier
+        elif self.distributed:
             if st.even and self.on_cuda:
                 dist.all_gather_into_tensor(O, O[st.lo:st.hi].clone(), group=self.pg)
             elif st.even:
@@ -307,7 +333,7 @@ class MuonEngine(ShardedEngine):
         self.step_count += 1
         from nanoplm_b200.parallel.engine import _invalidate_fp8_weights
         _invalidate_fp8_weights()
-        if self.distributed:
+        if self.distributed and self.fused is None:
             dist.all_reduce(self.main_grad, group=self.pg)
         scale = 1.0 / (grad_accum * self.world)
         h, t = self.hyper, self.step_count
@@ -342,13 +368,19 @@ class MuonEngine(ShardedEngine):
         parameter update of a stack, one for all AdamW tensors."""
         from nanoplm_b200.ops import kernels as K
         h = self.hyper
-        self._gsq.zero_()
-        K.sumsq_(self.main_grad, self._gsq)
+        if self.fused is not None:
+            grad = self.fused.reduce(self._owned(), self._gsq)
+        else:
+            grad = self.main_grad
+            self._gsq.zero_()
+            K.sumsq_(grad, self._gsq)
         self._gscale = scale
         norm = self._gsq.sqrt() * scale
         p16 = self.flat_params if self.flat_params.dtype == torch.bfloat16 else None
-        for st in self.stacks:
-            O = self._orthogonal_updates(st, self.main_grad)
+        updates = [self._orthogonal_updates(st, grad) for st in self.stacks]
+        if self.fused is not None:
+            self.fused.barrier()     # every owner's updates have landed; peers are done reading my gradients
+        for st, O in zip(self.stacks, updates):
             K.muon_apply_(self.master, p16, st.offsets(self.device, False), st.slots[0].numel, O.contiguous(),
                           self.muon_lr, self.muon_wd, self.cautious)
         if self.adam_slots:
@@ -360,7 +392,7 @@ class MuonEngine(ShardedEngine):
                     torch.tensor([int(s.decay) for s in self.adam_slots], dtype=torch.int32, device=dev),
                     max(s.numel for s in self.adam_slots))
             off, num, dec, mx = self._adam_table
-            K.adamw_slots_(self.master, self.exp_avg, self.exp_avg_sq, self.main_grad, p16, off, num, dec, mx,
+            K.adamw_slots_(self.master, self.exp_avg, self.exp_avg_sq, grad, p16, off, num, dec, mx,
                            self._gsq, scale, h.max_grad_norm, lr, h.beta1, h.beta2, h.eps, h.weight_decay, bc1, bc2)
         if p16 is None:
             self.flat_params.copy_(self.master)
