@@ -20,7 +20,12 @@ def _flush_buf():
     return torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
 
 
+_PROFILE = [False]     # --profile: one warm-up and one timed launch per kernel (a short run for a profiler)
+
+
 def time_fn(fn, iters=10, warmup=3, flush=None):
+    if _PROFILE[0]:
+        iters, warmup = 1, 1
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -291,13 +296,113 @@ def bench_moe(T, peaks):
                       "ms": round(ms_layer, 3), "expert_tflops": round(flops / ms_layer / 1e9, 1)}), flush=True)
 
 
+def bench_misc(T, peaks):
+    """The small kernels around the encoder that the other cases do not launch: fused MLM-head
+    cross-entropy (forward / backward), Philox masking, the teacher's bias attention, masked MSE, the
+    optimizer-step communication kernels on one rank (their local memory traffic) and the Muon
+    momentum / apply kernels."""
+    import ctypes
+    from ctypes import c_int, c_longlong
+    from nanoplm_b200.ops import kernels as k
+    from nanoplm_b200.ops._lib import lib, ptr, stream_ptr
+    hbm = peaks["hbm_gbs"]
+    flush = _flush_buf()
+
+    def report(name, ms, nbytes, **extra):
+        gbs = nbytes / ms / 1e6
+        print(json.dumps({"kernel": name, "ms": round(ms, 4), "GBps": round(gbs, 1),
+                          "frac_of_measured_hbm": round(gbs / hbm, 3), **extra}), flush=True)
+
+    C, V = 1024, 32
+    n = T * 3 // 10                                        # masked positions of a 30 % MLM batch
+    h = torch.randn(n, C, device="cuda").to(BF)
+    W = (torch.randn(V, C, device="cuda") * 0.03).to(BF)
+    bias = torch.zeros(V, device="cuda").to(BF)
+    labels = torch.randint(0, V, (n,), device="cuda")
+    inv = torch.full((1,), 1.0 / n, device="cuda")
+    ms = time_fn(lambda: k.ce_fwd(h, W, bias, labels, inv), flush=flush)
+    report("ce_fwd", ms, n * C * 2 + n * 32 * 4, rows=n)
+    _, dlogits, _ = k.ce_fwd(h, W, bias, labels, inv)
+    dW = torch.zeros(V, C, device="cuda")
+    db = torch.zeros(V, device="cuda")
+    gs = torch.ones(1, device="cuda")
+    ms = time_fn(lambda: k.ce_bwd(h, W, dlogits, gs, dW, db), flush=flush)
+    report("ce_bwd", ms, 2 * n * C * 2 + n * 32 * 4, rows=n)
+
+    ids = torch.randint(4, 24, (T,), device="cuda")
+    pool = torch.arange(4, 24, device="cuda", dtype=torch.int32)
+    ms = time_fn(lambda: k.mlm_mask(ids, T, (0, 1, 2, 3), 3, pool, 0.3, 0.8, 0.1, 1234, 7), flush=flush)
+    report("mlm_mask", ms, 3 * T * 8)
+
+    s_t = torch.randn(T, C, device="cuda").to(BF)
+    t_t = torch.randn(T, C, device="cuda").to(BF)
+    valid = torch.ones(T, dtype=torch.int32, device="cuda")
+    try:
+        ms = time_fn(lambda: k.masked_mse(s_t, t_t, valid, torch.full((1,), 1.0 / (T * C), device="cuda")),
+                     flush=flush)
+        report("masked_mse", ms, 3 * T * C * 2)
+    except Exception as exc:  # noqa: BLE001  (signature differences must not hide the other figures)
+        print(json.dumps({"kernel": "masked_mse", "skipped": f"{type(exc).__name__}: {exc}"}), flush=True)
+
+    # teacher attention: 32 heads of 64 channels, relative-position bias, sequences of 512
+    Tb, H, D, S = min(T, 32768), 32, 64, 512
+    qkv = torch.randn(Tb, 3 * H * D, device="cuda").to(BF)
+    cu = torch.arange(0, Tb + 1, S, device="cuda", dtype=torch.int32)
+    ss, se = k.seq_bounds(cu, Tb)
+    bias_t = torch.randn(H, 2 * S - 1, device="cuda")
+    ms = time_fn(lambda: k.fa_bias_fwd(qkv, ss, se, bias_t, H, D), flush=flush)
+    fl = 4.0 * Tb * S * H * D
+    print(json.dumps({"kernel": "fa_bias_fwd", "tokens": Tb, "heads": H, "ms": round(ms, 4),
+                      "tflops": round(fl / ms / 1e9, 1)}), flush=True)
+
+    # optimizer-step communication kernels on ONE rank: the local side of their memory traffic
+    L = lib("comm")
+    N = 64 * 1024 * 1024
+    g = torch.randn(N, device="cuda")
+    shard = torch.empty(N, device="cuda")
+    sq = torch.zeros(1, device="cuda")
+    one_ptr = ctypes.c_void_p * 1                          # the peer table of a single rank
+    gp = one_ptr(g.data_ptr())
+    ms = time_fn(lambda: L.nplm_rs_sumsq(gp, c_int(1), c_longlong(0), c_longlong(N), ptr(shard), ptr(sq),
+                                         stream_ptr()))
+    report("rs_sumsq (1 rank)", ms, 2 * N * 4)
+    master, m, v = torch.randn(N, device="cuda"), torch.zeros(N, device="cuda"), torch.zeros(N, device="cuda")
+    pb = torch.empty(N, dtype=BF, device="cuda")
+    pp = one_ptr(pb.data_ptr())
+    hyper = torch.tensor([1e-3, 0.9, 0.999, 1e-8, 0.0, 0.1, 0.001, 1.0, 1.0], device="cuda")
+    slots = torch.ones(8, device="cuda")
+    norm = torch.zeros(1, device="cuda")
+    ms = time_fn(lambda: L.nplm_adamw_push(ptr(master), ptr(m), ptr(v), ptr(shard), pp, c_int(1), c_longlong(0),
+                                           c_longlong(N), c_longlong(N), ptr(hyper), ptr(slots), ptr(norm),
+                                           stream_ptr()))
+    report("adamw_push (1 rank)", ms, N * (4 * 4 + 3 * 4 + 2))
+
+    # Muon: momentum + Newton-Schulz input, and the parameter update, on 16 matrices of 1024 x 1024
+    nmat, numel = 16, 1024 * 1024
+    gm, mm = torch.randn(nmat * numel, device="cuda"), torch.zeros(nmat * numel, device="cuda")
+    offs = torch.arange(nmat, device="cuda", dtype=torch.int64) * numel
+    upd = torch.empty(nmat, numel, dtype=BF, device="cuda")
+    usq = torch.zeros(nmat, device="cuda")
+    gsq = torch.ones(1, device="cuda")
+    ms = time_fn(lambda: k.muon_momentum_(gm, mm, offs, numel, upd, usq, gsq, 1.0, 1.0, 0.95, True))
+    report("muon_momentum", ms, nmat * numel * (4 + 4 + 4 + 2))
+    pm = torch.randn(nmat * numel, device="cuda")
+    p16 = torch.empty(nmat * numel, dtype=BF, device="cuda")
+    ms = time_fn(lambda: k.muon_apply_(pm, p16, offs, numel, upd, 1e-3, 0.01, True))
+    report("muon_apply", ms, nmat * numel * (4 + 4 + 2 + 2))
+    k.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--what", default="gemm,attn,elementwise")
     ap.add_argument("--sweep-splits", action="store_true",
                     help="gemm: time every weight-gradient shape at split-K factors 1..16 and stream-K")
+    ap.add_argument("--profile", action="store_true",
+                    help="launch every kernel twice only (for a profiler capture; the printed times are not bench values)")
     args = ap.parse_args()
+    _PROFILE[0] = args.profile
     from nanoplm_b200.utils.peaks import measured_peaks
     peaks = measured_peaks()
     for what in args.what.split(","):
@@ -305,7 +410,7 @@ def main():
             bench_gemm(args.tokens, peaks, args.sweep_splits)
             continue
         {"gemm": bench_gemm, "attn": bench_attn, "attn_ws": bench_attn_ws, "elementwise": bench_elementwise, "fp8": bench_fp8,
-         "moe": bench_moe}[what](args.tokens, peaks)
+         "moe": bench_moe, "misc": bench_misc}[what](args.tokens, peaks)
 
 
 if __name__ == "__main__":

@@ -84,6 +84,10 @@ struct GemmArgs {
   int group_mode;
   int groups;
   const int* tile_group;
+  // group_mode 1, optional: rows of A arrive from other GPUs. The producer loads the rows of tile t only
+  // after row_arrive[t] (bumped once per landed row, system scope) has reached row_expect[t].
+  const uint32_t* row_arrive;
+  const int* row_expect;
   const int* group_off;
   int b_group_rows;
   long long c_group_stride;
@@ -287,6 +291,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!decode(w, it)) continue;
         const int m0 = it.m0, n0 = it.n0, kb0 = it.kb0, kb1 = it.kb1;
         const int brow = it.b_row;
+        if (args.group_mode == 1 && args.row_arrive != nullptr) {
+          const int tile = m0 / BM;
+          const uint32_t need = static_cast<uint32_t>(args.row_expect[tile]);
+          const long long t0 = clock64();
+          while (ld_acquire_sys_u32(args.row_arrive + tile) < need) {
+            // the senders are other ranks' host threads away (their launch may lag): ten times the usual limit
+            if (clock64() - t0 > 10 * WAIT_LIMIT_CYCLES) {
+              atomicExch(args.status, ST_TIMEOUT_PEER);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (!ok) break;
+          fence_proxy_async_global();    // the rows were written with generic stores, TMA reads them
+        }
         if (args.ag_world > 1) {
           const int n_need = (EPI == EPI_SWIGLU) ? 2 : 1;
           for (int q = 0; q < n_need && ok; ++q) {
@@ -1044,6 +1065,8 @@ struct GroupSpec {
   int mode = 0;
   int groups = 1;
   const int* tile_group = nullptr;
+  const uint32_t* row_arrive = nullptr;   // mode 1: per-tile arrival counters and expected rows (optional)
+  const int* row_expect = nullptr;
   const int* group_off = nullptr;
   int b_group_rows = 0;
   long long c_group_stride = 0;
@@ -1156,6 +1179,8 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* R, int 
   args.group_mode = grp.mode;
   args.groups = grp.groups;
   args.tile_group = grp.tile_group;
+  args.row_arrive = grp.row_arrive;
+  args.row_expect = grp.row_expect;
   args.group_off = grp.group_off;
   args.b_group_rows = grp.b_group_rows;
   args.c_group_stride = grp.c_group_stride;
@@ -1292,17 +1317,33 @@ extern "C" int nplm_gemm_bf16_delta(const void* A, const void* B, void* C, const
 //   B holds `groups` operands stacked along its row axis, b_group_rows apart (N rows per group
 //   for a K-major B, K rows per group for an MN-major B); tile_group[M / 128] names the group of
 //   every row tile (-1 = tile not in use, skipped). K must be a multiple of 64.
-extern "C" int nplm_gemm_bf16_grouped(const void* A, const void* B, void* C, const void* R, int M,
-                                      int N, int K, int lda, int ldb, int ldc, int ldr, int b_mn,
-                                      int epi, int bn, int groups, const int* tile_group,
-                                      int b_group_rows, int* status, cudaStream_t stream) {
+// row_arrive / row_expect (both or neither): [M / 128] counters in this GPU's memory that other GPUs
+// bump once per row they have stored into A, and the number of rows each tile waits for; the tiles
+// of a group start as soon as their own rows have landed (no barrier between the dispatch and
+// this GEMM). The wait is bounded (ST_TIMEOUT_PEER).
+extern "C" int nplm_gemm_bf16_grouped_gated(const void* A, const void* B, void* C, const void* R, int M,
+                                            int N, int K, int lda, int ldb, int ldc, int ldr, int b_mn,
+                                            int epi, int bn, int groups, const int* tile_group,
+                                            int b_group_rows, const unsigned* row_arrive,
+                                            const int* row_expect, int* status, cudaStream_t stream) {
+  if ((row_arrive == nullptr) != (row_expect == nullptr)) return -3;
   GroupSpec g;
   g.mode = 1;
   g.groups = groups;
   g.tile_group = tile_group;
   g.b_group_rows = b_group_rows;
+  g.row_arrive = row_arrive;
+  g.row_expect = row_expect;
   return gemm_entry(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, 0, b_mn, epi, 1, bn, 0, 0, nullptr,
                     nullptr, nullptr, 0, status, stream, g);
+}
+
+extern "C" int nplm_gemm_bf16_grouped(const void* A, const void* B, void* C, const void* R, int M,
+                                      int N, int K, int lda, int ldb, int ldc, int ldr, int b_mn,
+                                      int epi, int bn, int groups, const int* tile_group,
+                                      int b_group_rows, int* status, cudaStream_t stream) {
+  return nplm_gemm_bf16_grouped_gated(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, b_mn, epi, bn, groups,
+                                      tile_group, b_group_rows, nullptr, nullptr, status, stream);
 }
 
 // Grouped weight gradient: C_g[M][N] (fp32, += or =) = A[rows_g][M]^T * B[rows_g][N] with

@@ -193,6 +193,7 @@ moe_count_kernel(const int* __restrict__ experts, int n, int E, MoePeers tables,
 //   my_base[e]   row (in the owner's buffer) where this rank's first assignment of e goes
 //   tile_group[] local expert of every 128-row tile of the local buffer, -1 beyond the end
 //   pad_lo/pad_hi[el] the zero-padding rows of local expert el
+//   tile_rows[]  (optional) number of real rows of every tile = the value its arrival counter reaches
 //   overflow: when the local rows exceed the buffer capacity the rows past it are DROPPED (push,
 //   pull and their backward kernels skip them, so those assignments contribute nothing) and counted
 //   in *dropped; training goes on (a skewed router costs some tokens of the tail experts of a rank,
@@ -200,7 +201,8 @@ moe_count_kernel(const int* __restrict__ experts, int n, int E, MoePeers tables,
 __global__ void __launch_bounds__(256)
 moe_plan_kernel(const int* __restrict__ table, int world, int rank, int E, int capacity_rows,
                 int* __restrict__ group_off, int* __restrict__ my_base, int* __restrict__ tile_group,
-                int max_tiles, int* __restrict__ pad_lo, int* __restrict__ pad_hi, int* dropped) {
+                int max_tiles, int* __restrict__ pad_lo, int* __restrict__ pad_hi, int* dropped,
+                int* __restrict__ tile_rows) {
   __shared__ int s_total[MOE_MAX_E];   // assignments of expert e over all ranks
   __shared__ int s_before[MOE_MAX_E];  // ... from ranks below this one
   __shared__ int s_off[MOE_MAX_E + 1]; // padded offset of e inside its owner's buffer
@@ -260,6 +262,9 @@ moe_plan_kernel(const int* __restrict__ table, int world, int rank, int E, int c
       g = lo;
     }
     tile_group[tile] = g;
+    // real (pushed) rows of this tile: what its arrival counter has to reach
+    if (tile_rows != nullptr)
+      tile_rows[tile] = g < 0 ? 0 : min(128, max(0, min(pad_lo[g], capacity_rows) - row));
   }
 }
 
@@ -326,10 +331,12 @@ moe_zero_pad_kernel(__nv_bfloat16* __restrict__ buf, int C, const int* __restric
 
 // ------------------------------------------------------------------------------- rows in / out
 // One warp per assignment i = t*k + s: dst_owner[pos_of[i]] = (scale ? scale[i] : 1) * src[t].
+// With `arrive` (per-rank uint32 counters, one per 128-row tile of the owner's buffer) every landed row is
+// counted, so the consumer can start a tile without a barrier over all ranks.
 __global__ void __launch_bounds__(256)
 moe_push_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ experts,
                      const int* __restrict__ pos_of, const float* __restrict__ scale, int n, int k,
-                     int C, int experts_per_rank, int capacity_rows, MoePeers dst) {
+                     int C, int experts_per_rank, int capacity_rows, MoePeers dst, MoePeers arrive) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < n; i += gridDim.x * wpb) {
@@ -352,6 +359,15 @@ moe_push_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restric
           w[q] = pack_bf16x2(f.x * g, f.y * g);
         }
         d[c] = v;
+      }
+    }
+    if (arrive.p[0] != nullptr) {
+      // the row has landed: bump the arrival counter of its 128-row tile on the owner (release at system
+      // scope after the warp's stores; the owner's grouped GEMM acquires it before loading the tile)
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_system();
+        red_release_sys_add(reinterpret_cast<uint32_t*>(arrive.p[owner]) + (pos >> 7), 1u);
       }
     }
   }
@@ -476,10 +492,10 @@ extern "C" int nplm_moe_count(const int* experts, int n, int E, void* const* tab
 
 extern "C" int nplm_moe_plan(const int* table, int world, int rank, int E, int capacity_rows,
                              int* group_off, int* my_base, int* tile_group, int max_tiles,
-                             int* pad_lo, int* pad_hi, int* dropped, cudaStream_t stream) {
+                             int* pad_lo, int* pad_hi, int* dropped, int* tile_rows, cudaStream_t stream) {
   if (E < 1 || E > MOE_MAX_E || world < 1 || world > MOE_MAX_PEERS || (E % world)) return -3;
   moe_plan_kernel<<<1, 256, 0, stream>>>(table, world, rank, E, capacity_rows, group_off, my_base,
-                                         tile_group, max_tiles, pad_lo, pad_hi, dropped);
+                                         tile_group, max_tiles, pad_lo, pad_hi, dropped, tile_rows);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -500,14 +516,18 @@ extern "C" int nplm_moe_zero_pad(void* buf, int C, const int* pad_lo, const int*
 
 extern "C" int nplm_moe_push_rows(const void* src, const int* experts, const int* pos_of,
                                   const float* scale, int n, int k, int C, int experts_per_rank,
-                                  int capacity_rows, void* const* dst, int world, cudaStream_t stream) {
+                                  int capacity_rows, void* const* dst, void* const* arrive, int world,
+                                  cudaStream_t stream) {
   if (n <= 0) return 0;
   if ((C % 8) || world < 1 || world > MOE_MAX_PEERS) return -3;
-  MoePeers d;
-  for (int p = 0; p < MOE_MAX_PEERS; ++p) d.p[p] = p < world ? dst[p] : nullptr;
+  MoePeers d, a;
+  for (int p = 0; p < MOE_MAX_PEERS; ++p) {
+    d.p[p] = p < world ? dst[p] : nullptr;
+    a.p[p] = (arrive != nullptr && p < world) ? arrive[p] : nullptr;
+  }
   moe_push_rows_kernel<<<grid_for(n, 8), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(src),
                                                            experts, pos_of, scale, n, k, C,
-                                                           experts_per_rank, capacity_rows, d);
+                                                           experts_per_rank, capacity_rows, d, a);
   return static_cast<int>(cudaGetLastError());
 }
 

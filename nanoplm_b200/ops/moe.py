@@ -58,9 +58,12 @@ def router_bwd(probs, gates, experts, d_gates, aux_grad):
     return dlogits
 
 
-def gemm_grouped(a, b, tile_group, *, b_mn=False, epi=K.EPI_STORE, aux=None, bn=None, out=None):
+def gemm_grouped(a, b, tile_group, *, b_mn=False, epi=K.EPI_STORE, aux=None, bn=None, out=None,
+                 arrive=None, expect=None):
     """Row-grouped GEMM. a [P,K] bf16 (P multiple of 128), b [G, N, K] (b_mn False) or [G, K, N]
-    (b_mn True), tile_group int32 [P/128]. Returns [P, N] (N/2 wide for EPI_SWIGLU)."""
+    (b_mn True), tile_group int32 [P/128]. Returns [P, N] (N/2 wide for EPI_SWIGLU).
+    arrive / expect (int32 [P/128] each, both or neither): the rows of `a` are being stored by other GPUs;
+    a tile is loaded once its arrival counter has reached its expected row count."""
     P, Kd = a.shape
     G = b.shape[0]
     if b_mn:
@@ -82,10 +85,16 @@ def gemm_grouped(a, b, tile_group, *, b_mn=False, epi=K.EPI_STORE, aux=None, bn=
     if bn is None:
         bn = 256 if (N >= 256 or epi == K.EPI_SWIGLU) else 128
     ldr = aux.stride(0) if aux is not None else 0
-    rc = lib("gemm_tcgen05").nplm_gemm_bf16_grouped(
+    if (arrive is None) != (expect is None):
+        raise ValueError("arrive and expect go together")
+    if arrive is not None and (arrive.numel() < P // 128 or expect.numel() < P // 128
+                               or arrive.dtype != torch.int32 or expect.dtype != torch.int32):
+        raise ValueError("arrive / expect must be int32 with one entry per 128-row tile")
+    rc = lib("gemm_tcgen05").nplm_gemm_bf16_grouped_gated(
         ptr(a), ptr(b2), ptr(out), ptr(aux), c_int(P), c_int(N), c_int(Kd), c_int(a.stride(0)),
         c_int(b2.stride(0)), c_int(out.stride(0)), c_int(ldr), c_int(int(b_mn)), c_int(epi), c_int(bn),
-        c_int(G), ptr(tile_group), c_int(rows_per_group), ptr(status_word(a.device)), stream_ptr())
+        c_int(G), ptr(tile_group), c_int(rows_per_group), ptr(arrive), ptr(expect),
+        ptr(status_word(a.device)), stream_ptr())
     check_rc(rc, "gemm_bf16_grouped")
     count_launch()
     return out
@@ -130,6 +139,10 @@ class MoEComm:
         self._sym = None
         self._cap = 0
         self._dropped = None      # int32 device counter: expert rows dropped for lack of buffer room
+        # expert parallelism: the up-projection starts tile by tile on arrival counters instead of after a
+        # barrier over all ranks (NPLM_MOE_GATED=0 restores the barrier)
+        import os
+        self.gated_dispatch = os.environ.get("NPLM_MOE_GATED", "1") != "0"
 
     def dropped_counter(self, device) -> torch.Tensor:
         if self._dropped is None:
@@ -150,13 +163,14 @@ class MoEComm:
 
     def _ensure_symmetric(self, cap: int, device):
         """Allocates the symmetric buffers on first use. Symmetric allocations must have the same
-        size on every rank, so the capacity is the maximum over the ranks of the first request
-        (one host-synchronising all-reduce, once); later requests must fit."""
+        size on every rank, so the capacity is the maximum over the ranks of the first request (one
+        host-synchronising all-reduce, once) plus a quarter: micro-batches whose padding tail has been
+        cut off differ in length. A later, larger request keeps the buffers: the capacity is a bound
+        on the rows that may LAND on a rank (capacity_factor times the even share), rows past it are
+        dropped and counted by the plan kernel."""
         if self._sym is not None:
-            if cap > self._cap:
-                raise ValueError(f"MoE layer received {cap} expert rows but its symmetric buffers hold "
-                                 f"{self._cap}; keep the token count per micro-batch constant")
             return
+        cap = (cap + cap // 4 + 127) // 128 * 128
         import torch.distributed as dist
         from nanoplm_b200.comm.fused_optimizer import SymmetricBuffer
         g = self.group
@@ -169,6 +183,8 @@ class MoEComm:
             "ys": SymmetricBuffer(cap * self.C, _BF16, device, g),
             "dys": SymmetricBuffer(cap * self.C, _BF16, device, g),
             "table": SymmetricBuffer(self.world * self.E, torch.int32, device, g),
+            # one counter per 128-row tile of xs: rows landed since the last plan (see make_plan)
+            "arrive": SymmetricBuffer(max(cap // 128, 8), torch.int32, device, g),
             "flags": SymmetricBuffer(16, torch.int32, device, g),
         }
 
@@ -204,7 +220,8 @@ class MoEComm:
 
 class MoEPlan:
     """Routing plan of one forward pass (device tensors only)."""
-    __slots__ = ("comm", "T", "cap", "experts", "pos_of", "group_off", "tile_group", "pad_lo", "pad_hi")
+    __slots__ = ("comm", "T", "cap", "experts", "pos_of", "group_off", "tile_group", "pad_lo", "pad_hi",
+                 "tile_rows")
 
 
 def make_plan(comm: MoEComm, experts: torch.Tensor) -> MoEPlan:
@@ -219,6 +236,11 @@ def make_plan(comm: MoEComm, experts: torch.Tensor) -> MoEPlan:
     L = lib("moe")
     table, table_ptrs = comm.table(dev)
     flat = experts.reshape(-1)
+    if comm.world > 1:
+        # the arrival counters of this layer's dispatch start from zero: peers push only after the
+        # barrier below, which this rank joins after the reset (and after everything that consumed the
+        # previous dispatch) in stream order
+        comm._sym["arrive"].tensor.zero_()
     rc = L.nplm_moe_count(ptr(flat), c_int(n), c_int(comm.E), table_ptrs, c_int(comm.rank), c_int(comm.world),
                           stream_ptr())
     check_rc(rc, "moe_count")
@@ -231,9 +253,10 @@ def make_plan(comm: MoEComm, experts: torch.Tensor) -> MoEPlan:
     p.tile_group = torch.empty(max_tiles, dtype=torch.int32, device=dev)
     p.pad_lo = torch.empty(comm.El, dtype=torch.int32, device=dev)
     p.pad_hi = torch.empty(comm.El, dtype=torch.int32, device=dev)
+    p.tile_rows = torch.empty(max_tiles, dtype=torch.int32, device=dev) if comm.world > 1 else None
     rc = L.nplm_moe_plan(ptr(table), c_int(comm.world), c_int(comm.rank), c_int(comm.E), c_int(cap),
                          ptr(p.group_off), ptr(my_base), ptr(p.tile_group), c_int(max_tiles), ptr(p.pad_lo),
-                         ptr(p.pad_hi), ptr(comm.dropped_counter(dev)), stream_ptr())
+                         ptr(p.pad_hi), ptr(comm.dropped_counter(dev)), ptr(p.tile_rows), stream_ptr())
     check_rc(rc, "moe_plan")
     p.pos_of = torch.empty(n, dtype=torch.int32, device=dev)
     rc = L.nplm_moe_assign(ptr(flat), c_int(n), c_int(comm.E), ptr(my_base), ptr(p.pos_of), stream_ptr())
@@ -250,11 +273,11 @@ def _zero_pad(plan: MoEPlan, buf: torch.Tensor) -> None:
     count_launch()
 
 
-def _push(plan: MoEPlan, src, scale, dst_ptrs) -> None:
+def _push(plan: MoEPlan, src, scale, dst_ptrs, arrive_ptrs=None) -> None:
     c = plan.comm
     rc = lib("moe").nplm_moe_push_rows(ptr(src), ptr(plan.experts), ptr(plan.pos_of), ptr(scale),
                                        c_int(plan.T * c.k), c_int(c.k), c_int(c.C), c_int(c.El), c_int(plan.cap),
-                                       dst_ptrs, c_int(c.world), stream_ptr())
+                                       dst_ptrs, arrive_ptrs, c_int(c.world), stream_ptr())
     check_rc(rc, "moe_push_rows")
     count_launch()
 
@@ -309,10 +332,18 @@ class _ExpertsFn(torch.autograd.Function):
         ep = c.world > 1
         xs, xs_ptrs = c.buffer("xs", plan.cap, dev)
         _zero_pad(plan, xs)
-        _push(plan, x.contiguous(), None, xs_ptrs)
-        c.barrier(dev)                                    # all rows of my experts have arrived
         pre = torch.empty((plan.cap, Wi.shape[1]), dtype=_BF16, device=dev)
-        h = gemm_grouped(xs, Wi, plan.tile_group, epi=K.EPI_SWIGLU, aux=pre)
+        if ep and c.gated_dispatch:
+            # no barrier between dispatch and up-projection: every pushed row bumps the arrival counter of
+            # its tile on the owner, and the grouped GEMM loads a tile once its rows have landed
+            arrive = c._sym["arrive"]
+            _push(plan, x.contiguous(), None, xs_ptrs, arrive.ptr_array)
+            h = gemm_grouped(xs, Wi, plan.tile_group, epi=K.EPI_SWIGLU, aux=pre,
+                             arrive=arrive.tensor, expect=plan.tile_rows)
+        else:
+            _push(plan, x.contiguous(), None, xs_ptrs)
+            c.barrier(dev)                                # all rows of my experts have arrived
+            h = gemm_grouped(xs, Wi, plan.tile_group, epi=K.EPI_SWIGLU, aux=pre)
         ys, ys_ptrs = c.buffer("ys", plan.cap, dev)
         gemm_grouped(h, Wo, plan.tile_group, out=ys)
         c.barrier(dev)                                    # every owner's outputs are complete
