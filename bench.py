@@ -455,6 +455,15 @@ def run_own(args) -> dict:
                                    "conv_mhc": " + varlen depthwise conv (k 7) + 4 mHC streams",
                                    "fp8": " with e4m3 block128 linear layers (not the headline precision)"}[args.variant]
         res["parameters"] = n_params
+        if args.variant == "moe":
+            dropped = sum(m.dropped_rows() for m in model.modules() if hasattr(m, "dropped_rows"))
+            res["moe"] = {"expert_rows_dropped_on_rank0": int(dropped),
+                          "dispatch": ("per-tile arrival counters gate the grouped up-projection"
+                                       if os.environ.get("NPLM_MOE_GATED", "1") != "0" else
+                                       "flag barrier between dispatch and up-projection") if world > 1 else "local"}
+            if world > 1:
+                res["config"]["parallelism"] = (f"ep{world} (64 experts over {world} ranks, rows over peer memory) "
+                                                f"x dp{world}-sharded-optimizer for the dense part")
         if args.variant == "fp8":
             res["dtype"] = "fp8-e4m3 linears, bf16 elsewhere"
     if world > 1:
