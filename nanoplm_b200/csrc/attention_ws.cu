@@ -374,11 +374,13 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
             if ((dead >> c) & 1u) continue;
             const int c_lo = kv0 + c * 32, c_hi = c_lo + 32;
             if (!(c_lo >= lo && c_hi <= hi)) {
+              // bit e of `bits`: key c_lo + e lies inside the row's range [lo, hi). One mask word per
+              // 32 keys instead of two comparisons per key.
+              const int a = max(lo - c_lo, 0), b = min(hi - c_lo, 32);
+              const uint32_t bits = b > a ? (0xffffffffu >> (32 - (b - a))) << a : 0u;
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                const int col = c_lo + e;
-                if (!(col >= lo && col < hi)) r[c * 32 + e] = NEG_INF;
-              }
+              for (int e = 0; e < 32; ++e)
+                if (!(bits & (1u << e))) r[c * 32 + e] = NEG_INF;
             }
 #pragma unroll
             for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(r[c * 32 + e]));
@@ -1011,6 +1013,12 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             *reinterpret_cast<uint4*>(rowS + off) = make_uint4(0u, 0u, 0u, 0u);
           }
         } else {
+          // bit e of kbits: key c0 + e lies inside the row's range (CPT <= 64 keys per thread)
+          uint64_t kbits = ~0ull;
+          if (!inside) {
+            const int a = max(ri.klo - c0, 0), b = min(ri.khi - c0, CPT);
+            kbits = b > a ? (~0ull >> (64 - (b - a))) << a : 0ull;
+          }
 #pragma unroll
           for (int c8 = 0; c8 < CPT / 8; ++c8) {
             uint32_t pk[4], dk[4];
@@ -1020,9 +1028,8 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
               float p0 = exp2f(fmaf(__uint_as_float(rs[e]), sl2, -ri.lse2));
               float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), sl2, -ri.lse2));
               if (!inside) {
-                const int key = c0 + e;
-                if (!(key >= ri.klo && key < ri.khi)) p0 = 0.f;
-                if (!(key + 1 >= ri.klo && key + 1 < ri.khi)) p1 = 0.f;
+                if (!(kbits & (1ull << e))) p0 = 0.f;
+                if (!(kbits & (1ull << (e + 1)))) p1 = 0.f;
               }
               const float d0 = p0 * (__uint_as_float(rp[e]) - ri.delta);
               const float d1 = p1 * (__uint_as_float(rp[e + 1]) - ri.delta);

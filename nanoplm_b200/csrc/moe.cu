@@ -411,12 +411,13 @@ moe_pull_rows_kernel(MoePeers src, const int* __restrict__ experts, const int* _
 }
 
 // Gradient of combine, one warp per assignment: d_gates[i] = <dy[t], ys_owner[pos]> (pulled) and
-// d_ys_owner[pos] = gates[i] * dy[t] (pushed).
+// d_ys_owner[pos] = gates[i] * dy[t] (pushed; counted per tile in `arrive` when given, as in the
+// forward push).
 __global__ void __launch_bounds__(256)
 moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, MoePeers ys, MoePeers d_ys,
                        const int* __restrict__ experts, const int* __restrict__ pos_of,
                        const float* __restrict__ gates, int n, int k, int C, int experts_per_rank,
-                       int capacity_rows, float* __restrict__ d_gates) {
+                       int capacity_rows, float* __restrict__ d_gates, MoePeers arrive) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < n; i += gridDim.x * wpb) {
@@ -444,6 +445,13 @@ moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, MoePeers ys, MoePee
           w[q] = pack_bf16x2(f.x * g, f.y * g);
         }
         d[c] = v;
+      }
+      if (arrive.p[0] != nullptr) {     // the d_ys row has landed: count it for its tile on the owner
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();
+          red_release_sys_add(reinterpret_cast<uint32_t*>(arrive.p[owner]) + (pos >> 7), 1u);
+        }
       }
     }
     dot = warp_sum(dot);
@@ -547,16 +555,17 @@ extern "C" int nplm_moe_pull_rows(void* const* src, const int* experts, const in
 extern "C" int nplm_moe_combine_bwd(const void* dy, void* const* ys, void* const* d_ys,
                                     const int* experts, const int* pos_of, const float* gates, int n,
                                     int k, int C, int experts_per_rank, int capacity_rows,
-                                    float* d_gates, int world, cudaStream_t stream) {
+                                    float* d_gates, void* const* arrive, int world, cudaStream_t stream) {
   if (n <= 0) return 0;
   if ((C % 8) || world < 1 || world > MOE_MAX_PEERS) return -3;
-  MoePeers a, b;
+  MoePeers a, b, cnt;
   for (int p = 0; p < MOE_MAX_PEERS; ++p) {
     a.p[p] = p < world ? ys[p] : nullptr;
     b.p[p] = p < world ? d_ys[p] : nullptr;
+    cnt.p[p] = (arrive != nullptr && p < world) ? arrive[p] : nullptr;
   }
   moe_combine_bwd_kernel<<<grid_for(n, 8), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(dy), a, b, experts, pos_of, gates, n, k, C,
-      experts_per_rank, capacity_rows, d_gates);
+      experts_per_rank, capacity_rows, d_gates, cnt);
   return static_cast<int>(cudaGetLastError());
 }

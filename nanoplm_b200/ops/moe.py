@@ -185,6 +185,11 @@ class MoEComm:
             "table": SymmetricBuffer(self.world * self.E, torch.int32, device, g),
             # one counter per 128-row tile of xs: rows landed since the last plan (see make_plan)
             "arrive": SymmetricBuffer(max(cap // 128, 8), torch.int32, device, g),
+            # the same for the gradient rows pushed into dys, and the buffer the data gradient of the
+            # dispatched rows is written to (kept apart from ys so that no barrier has to wait for the
+            # peers' last reads of ys)
+            "arrive_b": SymmetricBuffer(max(cap // 128, 8), torch.int32, device, g),
+            "dxs": SymmetricBuffer(cap * self.C, _BF16, device, g),
             "flags": SymmetricBuffer(16, torch.int32, device, g),
         }
 
@@ -241,6 +246,7 @@ def make_plan(comm: MoEComm, experts: torch.Tensor) -> MoEPlan:
         # barrier below, which this rank joins after the reset (and after everything that consumed the
         # previous dispatch) in stream order
         comm._sym["arrive"].tensor.zero_()
+        comm._sym["arrive_b"].tensor.zero_()
     rc = L.nplm_moe_count(ptr(flat), c_int(n), c_int(comm.E), table_ptrs, c_int(comm.rank), c_int(comm.world),
                           stream_ptr())
     check_rc(rc, "moe_count")
@@ -377,18 +383,29 @@ class _ExpertsFn(torch.autograd.Function):
         dys, dys_ptrs = c.buffer("dys", plan.cap, dev)
         _zero_pad(plan, dys)
         d_gates = torch.empty((plan.T, c.k), dtype=torch.float32, device=dev)
+        gated = ep and c.gated_dispatch
+        arrive_b = c._sym["arrive_b"] if gated else None
         rc = lib("moe").nplm_moe_combine_bwd(ptr(dy), ys_ptrs, dys_ptrs, ptr(plan.experts), ptr(plan.pos_of),
                                              ptr(gates32), c_int(n), c_int(c.k), c_int(c.C), c_int(c.El),
-                                             c_int(plan.cap), ptr(d_gates), c_int(c.world), stream_ptr())
+                                             c_int(plan.cap), ptr(d_gates),
+                                             arrive_b.ptr_array if gated else None, c_int(c.world), stream_ptr())
         check_rc(rc, "moe_combine_bwd")
         count_launch()
-        c.barrier(dev)                                    # d_ys complete, nobody reads ys any more
-        d_h = gemm_grouped(dys, Wo, plan.tile_group, b_mn=True)
+        if gated:
+            # no barrier: the down-projection's data gradient starts tile by tile as the d_ys rows land,
+            # and the data gradient of the dispatched rows goes to a buffer of its own (peers may still
+            # be reading ys)
+            d_h = gemm_grouped(dys, Wo, plan.tile_group, b_mn=True, arrive=arrive_b.tensor, expect=plan.tile_rows)
+            dxs, dx_ptrs = c.buffer("dxs", plan.cap, dev)
+        else:
+            c.barrier(dev)                                # d_ys complete, nobody reads ys any more
+            d_h = gemm_grouped(dys, Wo, plan.tile_group, b_mn=True)
+            # the data gradient of the dispatched rows lands in the buffer that held ys
+            dxs, dx_ptrs = (ys, ys_ptrs) if ep else (None, None)
         d_pre = K.swiglu_bwd(pre, d_h)
-        # the data gradient of the dispatched rows lands in the buffer that held ys
-        dxs = ys if ep else None
         dxs = gemm_grouped(d_pre, Wi, plan.tile_group, b_mn=True, out=dxs)
-        dx_ptrs = ys_ptrs if ep else _ptr_array([dxs.data_ptr()])
+        if not ep:
+            dx_ptrs = _ptr_array([dxs.data_ptr()])
         Wi_p, Wo_p = ctx.Wi_ref, ctx.Wo_ref
         gWi = gWo = None
         if _has_main_grad(Wo_p):
@@ -403,7 +420,10 @@ class _ExpertsFn(torch.autograd.Function):
             gWi = gemm_grouped_wgrad(d_pre, xs, plan.group_off, acc).to(Wi.dtype)
         c.barrier(dev)                                    # every owner's d_xs is complete
         dx = _pull(plan, dx_ptrs, None)
-        c.barrier(dev)                                    # peers are done reading before buffers are reused
+        if not gated:
+            c.barrier(dev)                                # peers are done reading before buffers are reused
+        # (gated: the next write into any of this layer's buffers by a peer or by this rank comes after
+        # the barrier of the next make_plan, which every rank joins after this pull in stream order)
         return dx, d_gates, gWi, gWo, None
 
 

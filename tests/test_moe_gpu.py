@@ -183,3 +183,26 @@ def test_moe_mlp_forward_backward(T, E, k, C, I, cuda_status):
     close(logits.grad, l32.grad, 0.06, "dlogits")
     close(Wi.grad, Wi32.grad, 0.05, "dWi")
     close(Wo.grad, Wo32.grad, 0.05, "dWo")
+
+
+def test_grouped_gemm_gated_by_arrival_counters_matches_ungated(cuda_status):
+    """The arrival-gated grouped GEMM (counters already at their expected values, as after a finished
+    dispatch) gives the bits of the ungated one; counters ABOVE the expectation also pass."""
+    from nanoplm_b200.ops import moe as M
+    torch.manual_seed(4)
+    dev = torch.device("cuda:0")
+    T, E, k, C, N = 3000, 8, 2, 256, 512
+    plan, _ = _random_plan(T, E, k, C, dev)
+    P = plan.cap
+    a = torch.randn(P, C, device=dev).to(BF)
+    W = (torch.randn(E, N, C, device=dev) * 0.05).to(BF)
+    ref = M.gemm_grouped(a, W, plan.tile_group)
+    tiles = P // 128
+    expect = torch.randint(0, 129, (tiles,), device=dev, dtype=torch.int32)
+    for extra in (0, 5):
+        arrive = (expect + extra).contiguous()
+        out = M.gemm_grouped(a, W, plan.tile_group, arrive=arrive, expect=expect)
+        rows = (plan.tile_group >= 0).repeat_interleave(128)
+        assert torch.equal(out[rows], ref[rows])
+    with pytest.raises(ValueError):
+        M.gemm_grouped(a, W, plan.tile_group, arrive=expect)
