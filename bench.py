@@ -392,6 +392,7 @@ def run_own(args) -> dict:
     gathered_bytes = engine.gathered_parameter_bytes() if sharded_params else 0
 
     # ---- end to end through the pipeline ------------------------------------------------------------
+    moe_dropped = sum(m.dropped_rows() for m in model.modules() if hasattr(m, "dropped_rows"))
     del stepper, engine, model, timed_dev
     torch.cuda.empty_cache()
     pipe = None
@@ -456,8 +457,7 @@ def run_own(args) -> dict:
                                    "fp8": " with e4m3 block128 linear layers (not the headline precision)"}[args.variant]
         res["parameters"] = n_params
         if args.variant == "moe":
-            dropped = sum(m.dropped_rows() for m in model.modules() if hasattr(m, "dropped_rows"))
-            res["moe"] = {"expert_rows_dropped_on_rank0": int(dropped),
+            res["moe"] = {"expert_rows_dropped_on_rank0": int(moe_dropped),
                           "dispatch": ("per-tile arrival counters gate the grouped up-projection"
                                        if os.environ.get("NPLM_MOE_GATED", "1") != "0" else
                                        "flag barrier between dispatch and up-projection") if world > 1 else "local"}

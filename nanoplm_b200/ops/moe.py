@@ -143,6 +143,8 @@ class MoEComm:
         # barrier over all ranks (NPLM_MOE_GATED=0 restores the barrier)
         import os
         self.gated_dispatch = os.environ.get("NPLM_MOE_GATED", "1") != "0"
+        # the same for the gradient rows of the backward pass (NPLM_MOE_GATED_BWD=0: flag barriers there)
+        self.gated_backward = self.gated_dispatch and os.environ.get("NPLM_MOE_GATED_BWD", "1") != "0"
 
     def dropped_counter(self, device) -> torch.Tensor:
         if self._dropped is None:
@@ -383,7 +385,7 @@ class _ExpertsFn(torch.autograd.Function):
         dys, dys_ptrs = c.buffer("dys", plan.cap, dev)
         _zero_pad(plan, dys)
         d_gates = torch.empty((plan.T, c.k), dtype=torch.float32, device=dev)
-        gated = ep and c.gated_dispatch
+        gated = ep and c.gated_backward
         arrive_b = c._sym["arrive_b"] if gated else None
         rc = lib("moe").nplm_moe_combine_bwd(ptr(dy), ys_ptrs, dys_ptrs, ptr(plan.experts), ptr(plan.pos_of),
                                              ptr(gates32), c_int(n), c_int(c.k), c_int(c.C), c_int(c.El),
