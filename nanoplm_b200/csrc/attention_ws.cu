@@ -81,6 +81,29 @@ constexpr int WS_FWD_SMEM = WS_OFF_BAR + 512;
 
 // Key-tile geometry of one work item: query tiles i = 0, 1 cover tokens [t0 + 128 i, +128); the
 // item walks key tiles j = 0 .. n-1 starting at kv_lo, and tile i takes part in j in [a[i], b[i]).
+// three-input maximum and packed two-lane fp32 arithmetic (sm_100): half the instructions of the
+// scalar forms in the softmax loops
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)),
+        "l"(*reinterpret_cast<uint64_t*>(&c)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+
 struct WsGeo {
   int t0, kv_lo, n;
   int a[2], b[2];
@@ -383,7 +406,9 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
                 if (!(bits & (1u << e))) r[c * 32 + e] = NEG_INF;
             }
 #pragma unroll
-            for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(r[c * 32 + e]));
+            for (int e = 0; e < 32; e += 2)
+              mx[(e >> 1) & 3] = fmax3(mx[(e >> 1) & 3], __uint_as_float(r[c * 32 + e]),
+                                       __uint_as_float(r[c * 32 + e + 1]));
           }
         }
         const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
@@ -419,6 +444,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
 
         const float moff = m_used * sl2;
         float ps[4] = {0.f, 0.f, 0.f, 0.f};
+        const float2 sl2v = make_float2(sl2, sl2), noffv = make_float2(-moff, -moff);
+        float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         if constexpr (PTMEM) {
           // probabilities packed in place: word c of r[] takes keys 2c, 2c + 1 (both already consumed)
           if (!warp_none) {
@@ -430,10 +457,11 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
               } else {
 #pragma unroll
                 for (int c = q * 16; c < q * 16 + 16; ++c) {
-                  const float p0 = exp2f(fmaf(__uint_as_float(r[2 * c]), sl2, -moff));
-                  const float p1 = exp2f(fmaf(__uint_as_float(r[2 * c + 1]), sl2, -moff));
-                  ps[c & 3] += p0 + p1;
-                  r[c] = pack_bf16x2(p0, p1);
+                  const float2 x = fma2(make_float2(__uint_as_float(r[2 * c]), __uint_as_float(r[2 * c + 1])),
+                                        sl2v, noffv);
+                  const float2 p = make_float2(exp2f(x.x), exp2f(x.y));
+                  ps2[c & 1] = add2(ps2[c & 1], p);
+                  r[c] = pack_bf16x2(p.x, p.y);
                 }
               }
             }
@@ -445,7 +473,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
           tmem_st32(tP, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
           tmem_st32(tP + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
           tmem_st_wait();
-          l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+          l_run += ((ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y)) + ((ps[0] + ps[1]) + (ps[2] + ps[3]));
           tc_fence_before();
         } else {
           if (!warp_none) {
