@@ -714,6 +714,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   const uint32_t tdQ = tmem_base + 256;   // dQ  [q][d]   64 columns
   const uint32_t tdK = tmem_base + 320;   // dK  [kv][d]  64 columns
   const uint32_t tdV = tmem_base + 384;   // dV  [kv][d]  64 columns
+  const uint32_t tdS = tmem_base + 448;   // dS  [q][kv]  bf16, two keys per column: 64 columns (A operand of dQ)
   WS_TRACE_INIT();
 
   if (warp >= NWG * 4) {
@@ -880,7 +881,6 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         if (*abort_flag) ok = false;
       }
     } else if (role == 2 && DQ) {
-      const uint64_t dS0 = make_smem_desc(smem_u32(sdS), 16, 1024);              // dS as K-major A
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
         const WsBwdGeo g = ws_bwd_geometry(args, item / H);
         const uint32_t kb = ic & 1u;
@@ -892,9 +892,8 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           if (!mbar_wait(dq_free, (c_dq & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < FA_T / 16; ++k)   // dQ[q][d] = dS[q][kv] K[kv][d]
-            umma_bf16(tdQ, dS0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dK0 + k * 128, idesc_dq,
-                      k > 0 ? 1u : 0u);
+          for (int k = 0; k < FA_T / 16; ++k)   // dQ[q][d] = dS[q][kv] K[kv][d], dS read from tensor memory
+            umma_bf16_ts(tdQ, tdS + k * 8, dK0 + k * 128, idesc_dq, k > 0 ? 1u : 0u);
           ++c_dq;
           umma_commit(g_done);
         }
@@ -905,7 +904,6 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
     }
     else if (role == 2 && QST) {
       // dQ[q][d] += dS[q][kv] K[kv][d] over the item's key tiles (K = ring slot 0, read MN-major)
-      const uint64_t dS0 = make_smem_desc(smem_u32(sdS), 16, 1024);
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
         const WsBwdGeo g = ws_bwd_geometry(args, item / H);
         for (int j = 0; j < g.n_q; ++j) {
@@ -920,8 +918,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           const uint64_t dKr = make_smem_desc(smem_u32(sQ + st * FA_TILE_BYTES), 8192, 1024);
 #pragma unroll
           for (int k = 0; k < FA_T / 16; ++k)
-            umma_bf16(tdQ, dS0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dKr + k * 128, idesc_dq,
-                      (j > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_ts(tdQ, tdS + k * 8, dKr + k * 128, idesc_dq, (j > 0 || k > 0) ? 1u : 0u);
           umma_commit(g_done);
           umma_commit(&qdo_empty[st]);     // with issuer A
         }
@@ -1031,14 +1028,21 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         uint8_t* rowS = sdS + ((gh * CPT) >> 6) * FA_TILE_BYTES + r * 128;
         const int chunk0 = ((gh * CPT) & 63) >> 3;
         const int rx = r & 7;
+        uint32_t dsw[CPT / 2];
         if (outside) {
           // no query row of this warp sees any of these keys (they belong to other sequences):
           // zero tiles, no exponentials
 #pragma unroll
           for (int c8 = 0; c8 < CPT / 8; ++c8) {
             const uint32_t off = static_cast<uint32_t>(((chunk0 + c8) ^ rx) << 4);
-            if constexpr (!QST) *reinterpret_cast<uint4*>(rowP + off) = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(rowS + off) = make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (!QST) {
+              *reinterpret_cast<uint4*>(rowP + off) = make_uint4(0u, 0u, 0u, 0u);
+              *reinterpret_cast<uint4*>(rowS + off) = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+          if constexpr (DQ || QST) {
+#pragma unroll
+            for (int c = 0; c < CPT / 2; ++c) dsw[c] = 0u;
           }
         } else {
           // bit e of kbits: key c0 + e lies inside the row's range (CPT <= 64 keys per thread)
@@ -1065,10 +1069,22 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
               dk[u] = pack_bf16x2(d0, d1);
             }
             const uint32_t off = static_cast<uint32_t>(((chunk0 + c8) ^ rx) << 4);
-            if constexpr (!QST)      // the query-stationary pass forms dQ only: P itself is not needed
+            if constexpr (!QST) {    // the query-stationary pass forms dQ only: no P, and dS only in tensor memory
               *reinterpret_cast<uint4*>(rowP + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(rowS + off) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+              *reinterpret_cast<uint4*>(rowS + off) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+            }
+            if constexpr (DQ || QST) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) dsw[c8 * 4 + u] = dk[u];
+            }
           }
+        }
+        if constexpr (DQ || QST) {
+          // dS of this thread's keys as the A operand of the dQ product: two keys per 32-bit column
+          if constexpr (CPT == 64) tmem_st32(tdS + lane_addr + gh * (CPT / 2), dsw);
+          else tmem_st16(tdS + lane_addr + gh * (CPT / 2), dsw);
+          tmem_st_wait();
+          tc_fence_before();
         }
         fence_proxy_async_smem();
         __syncwarp();
