@@ -561,8 +561,12 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
 //   -> bf16 tiles [query rows][key columns] in shared memory ->
 //   dV += P^T dO, dK += dS^T Q (TMEM-resident across the item), dQ = dS K (read back by the
 //   compute warpgroups one step later and added to the fp32 dq accumulator with vector atomics).
-// The loader runs ahead by up to three query tiles and one key tile; S / dP of step j + 1 are
+// The loader runs ahead by up to two query tiles and one key tile; S / dP of step j + 1 are
 // issued as soon as the warpgroups hold step j in registers.
+// With four compute warpgroups a further warpgroup moves every step's dQ tile from tensor memory
+// through a staging tile in shared memory into the fp32 accumulator with TMA reduce-adds: issued as
+// vector atomics from the SM instead, the adds filled the load / store path, and the row data of the
+// next step (four small loads per thread) waited about 3 000 cycles behind them in every step.
 struct FaWsBwdArgs {
   __nv_bfloat16* dqkv;   // [T][3][H][64]: the kernel writes the dK and dV parts
   float* dq_acc;         // [T][H*64] fp32, zero-initialised by the caller
@@ -578,15 +582,32 @@ struct FaWsBwdArgs {
   const float* rope_sin;
 };
 
-constexpr int WSB_Q_STAGES = 3;
+constexpr int WSB_Q_STAGES = 2;
 constexpr int WSB_OFF_K = 0;                                   // [2]
 constexpr int WSB_OFF_V = WSB_OFF_K + 2 * FA_TILE_BYTES;       // [2]
 constexpr int WSB_OFF_Q = WSB_OFF_V + 2 * FA_TILE_BYTES;       // [WSB_Q_STAGES]
 constexpr int WSB_OFF_DO = WSB_OFF_Q + WSB_Q_STAGES * FA_TILE_BYTES;
 constexpr int WSB_OFF_P = WSB_OFF_DO + WSB_Q_STAGES * FA_TILE_BYTES;   // [2 key blocks][128 q rows][128 B]
 constexpr int WSB_OFF_DS = WSB_OFF_P + 2 * FA_TILE_BYTES;
-constexpr int WSB_OFF_BAR = WSB_OFF_DS + 2 * FA_TILE_BYTES;
+constexpr int WSB_OFF_DQ = WSB_OFF_DS + 2 * FA_TILE_BYTES;   // [2 channel halves][128 q rows][32 fp32] staging of a dQ tile
+constexpr int WSB_OFF_BAR = WSB_OFF_DQ + 2 * FA_TILE_BYTES;
 constexpr int WS_BWD_SMEM = WSB_OFF_BAR + 512;
+
+// Named barrier 1 over 128 threads (one warpgroup) with an AND over everybody's predicate.
+__device__ __forceinline__ bool wg_barrier_and(bool p) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q, o;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "bar.red.and.pred o, 1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, o;\n\t"
+      "}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(p))
+      : "memory");
+  return r != 0;
+}
 
 struct WsBwdGeo {
   int kv0, q_lo, q_hi, n_q;
@@ -643,7 +664,7 @@ constexpr int BWD_KV = 0, BWD_KV_DQ = 1, BWD_Q = 2;
 template <int NWG, int MODE>
 __global__ void __launch_bounds__(WsBwdCfg<NWG, MODE == BWD_KV_DQ>::THREADS, 1)
 fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
-                 const FaWsBwdArgs args) {
+                 const __grid_constant__ CUtensorMap tmDQ, const FaWsBwdArgs args) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {
     if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
@@ -655,6 +676,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   uint8_t* sdO = smem + WSB_OFF_DO;
   uint8_t* sP = smem + WSB_OFF_P;
   uint8_t* sdS = smem + WSB_OFF_DS;
+  uint8_t* sDQ = smem + WSB_OFF_DQ;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WSB_OFF_BAR);
   uint64_t* kv_full = bars;                        // [2]
   uint64_t* kv_empty = bars + 2;                   // [2]
@@ -721,11 +743,15 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_LIGHT));
   if (Cfg::DRAIN_WG && warp >= Cfg::DRAIN_WARP) {
     // ------------------------------------------------------------------ dQ drain warpgroup
-    // thread = query row of the step's tile; waits for the step's products, copies the row's 64
-    // channels out of tensor memory, hands the tile back and issues 16 vector atomics
+    // thread = query row of the step's tile: waits for the step's products, copies the row's 64 channels
+    // out of tensor memory (scaled) into the staging tile and hands the tensor-memory tile back; one
+    // thread then adds the staging tile into the fp32 accumulator with two TMA reduce-adds (32 channels
+    // = one 128-byte swizzled row each). Rows the item's queries do not reach hold zeros (their
+    // probabilities are masked), rows past the end of the batch are clipped by the tensor map.
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const bool issuer = warp == Cfg::DRAIN_WARP && lane == 0;
     uint32_t c_g = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -734,32 +760,41 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
       for (int j = 0; j < g.n_q; ++j) {
         ok = mbar_wait(g_done, c_g & 1u);
         ++c_g;
-        ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+        // the previous tile's reduce-adds have finished reading the staging tile
+        if (issuer) tma_store_wait_read<0>();
+        // barrier over the warpgroup that also agrees on going on: all four warps leave together (a warp
+        // that stayed behind would leave the others at the second barrier below for ever)
+        ok = wg_barrier_and(ok && *abort_flag == 0);
         if (!ok) break;
         tc_fence_after();
-        const int q = g.q_lo + j * FA_T + r;
-        const bool live = q < T && q < g.q_hi;
-        float* dst = args.dq_acc + static_cast<size_t>(live ? q : 0) * HD + h * FA_D;
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {     // 32 channels at a time: this warpgroup runs on few registers
           uint32_t v[32];
           tmem_ld32(tdQ + lane_addr + hlf * 32, v);
           tmem_ld_wait();
-          if (hlf == 1) {                       // both halves are in registers / on their way to memory
+          if (hlf == 1) {                       // both halves have left tensor memory
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dq_free);
           }
-          if (live) {
+          uint8_t* row = sDQ + hlf * FA_TILE_BYTES + r * 128;
 #pragma unroll
-            for (int e = 0; e < 32; e += 4)
-              atomicAdd(reinterpret_cast<float4*>(dst + hlf * 32 + e),
-                        make_float4(__uint_as_float(v[e]) * args.scale, __uint_as_float(v[e + 1]) * args.scale,
-                                    __uint_as_float(v[e + 2]) * args.scale, __uint_as_float(v[e + 3]) * args.scale));
-          }
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(row + (((c ^ (r & 7))) << 4)) =
+                make_float4(__uint_as_float(v[4 * c]) * args.scale, __uint_as_float(v[4 * c + 1]) * args.scale,
+                            __uint_as_float(v[4 * c + 2]) * args.scale, __uint_as_float(v[4 * c + 3]) * args.scale);
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) {
+          const int q0 = g.q_lo + j * FA_T;
+          tma_reduce_add_2d(&tmDQ, sDQ, h * FA_D, q0);
+          tma_reduce_add_2d(&tmDQ, sDQ + FA_TILE_BYTES, h * FA_D + 32, q0);
+          tma_store_commit();
         }
       }
     }
+    if (issuer) tma_store_wait<0>();            // the adds are complete before the CTA gives up its shared memory
     if (!ok && lane == 0 && *abort_flag == 0) {
       atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
       *abort_flag = 1;
@@ -1264,6 +1299,20 @@ static EncodeTiledFn ws_encode_fn() {
 }
 
 // rows = T, cols contiguous; box = [128 rows][64 cols]
+// fp32 [rows][cols] accumulator, boxes of 128 rows x 32 columns (one 128-byte swizzled row each)
+static int ws_make_map_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows) {
+  EncodeTiledFn fn = ws_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 4};
+  cuuint32_t box[2] = {32, FA_T};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
 static int ws_make_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows) {
   EncodeTiledFn fn = ws_encode_fn();
   if (fn == nullptr) return -1;
@@ -1387,6 +1436,12 @@ static int ws_bwd_impl(const void* qkv, const void* out, const void* dout, const
   if (rc) return rc;
   rc = ws_make_map(&tmDO, dout, static_cast<uint64_t>(H) * D, T);
   if (rc) return rc;
+  CUtensorMap tmDQ = tmDO;     // only the four-warpgroup atomics mode reads it
+  if (mode == 4) {
+    if (reinterpret_cast<uintptr_t>(dq_acc) & 15) return -3;
+    rc = ws_make_map_f32(&tmDQ, dq_acc, static_cast<uint64_t>(H) * D, T);
+    if (rc) return rc;
+  }
   int sms = 0;
   rc = ws_configure(&sms);
   if (rc) return rc;
@@ -1420,15 +1475,15 @@ static int ws_bwd_impl(const void* qkv, const void* out, const void* dout, const
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (grid > n_items) grid = n_items;
   if (mode == 2) {
-    fa_bwd_ws_kernel<2, BWD_KV_DQ><<<grid, WsBwdCfg<2, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<2, BWD_KV_DQ><<<grid, WsBwdCfg<2, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
   } else if (mode == 0) {
-    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
   } else if (mode == 3) {
-    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
-    fa_bwd_ws_kernel<4, BWD_Q><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
+    fa_bwd_ws_kernel<4, BWD_Q><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
     return static_cast<int>(cudaGetLastError());
   } else {
-    fa_bwd_ws_kernel<4, BWD_KV_DQ><<<grid, WsBwdCfg<4, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, a);
+    fa_bwd_ws_kernel<4, BWD_KV_DQ><<<grid, WsBwdCfg<4, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
   }
   {
     const long long total = static_cast<long long>(T) * H * 4;
