@@ -647,9 +647,10 @@ struct WsBwdCfg {
   static constexpr int CPT = FA_T / NWG;              // key columns per thread
   // registers per thread the launch allocates: the most a scheduler's share of the warps allows
   static constexpr int REGS_LAUNCH = NWG == 2 ? 168 : (DRAIN_WG ? 80 : 96);
-  static constexpr int REGS_LIGHT = NWG == 2 ? 72 : (DRAIN_WG ? 48 : 56);   // loader / MMA issuers / dQ drain
+  static constexpr int REGS_LIGHT = NWG == 2 ? 72 : (DRAIN_WG ? 48 : 56);   // loader / MMA issuers
+  static constexpr int REGS_DRAIN = 48;                                     // dQ / dK / dV drain warpgroup
   static constexpr int REGS_HEAVY = NWG == 2 ? 216 : (DRAIN_WG ? 96 : 104);
-  static_assert((THREADS - NWG * 128) * REGS_LIGHT + NWG * 128 * REGS_HEAVY <= THREADS * REGS_LAUNCH,
+  static_assert(128 * REGS_LIGHT + (DRAIN_WG ? 128 * REGS_DRAIN : 0) + NWG * 128 * REGS_HEAVY <= THREADS * REGS_LAUNCH,
                 "setmaxnreg.inc would wait forever for registers the CTA does not own");
 };
 
@@ -664,7 +665,8 @@ constexpr int BWD_KV = 0, BWD_KV_DQ = 1, BWD_Q = 2;
 template <int NWG, int MODE>
 __global__ void __launch_bounds__(WsBwdCfg<NWG, MODE == BWD_KV_DQ>::THREADS, 1)
 fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
-                 const __grid_constant__ CUtensorMap tmDQ, const FaWsBwdArgs args) {
+                 const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmOUT,
+                 const FaWsBwdArgs args) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {
     if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
@@ -715,7 +717,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
     mbar_init(pds_ready, NWG * 4);     // one lane per compute warp, after every lane's proxy fence
     mbar_init(g_done, DQ ? 2 : 1);           // issuer B, and C when both run (query-stationary: C alone)
     mbar_init(dq_free, (Cfg::DRAIN_WG || QST) ? 4 : NWG * 4);   // the warps that read dQ back
-    mbar_init(acc_free, 8);       // the two warpgroups that read dK / dV back
+    mbar_init(acc_free, Cfg::DRAIN_WG ? 4 : 8);   // the warps that read dK / dV back
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -740,8 +742,8 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
   WS_TRACE_INIT();
 
   if (warp >= NWG * 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_LIGHT));
   if (Cfg::DRAIN_WG && warp >= Cfg::DRAIN_WARP) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_DRAIN));
     // ------------------------------------------------------------------ dQ drain warpgroup
     // thread = query row of the step's tile: waits for the step's products, copies the row's 64 channels
     // out of tensor memory (scaled) into the staging tile and hands the tensor-memory tile back; one
@@ -793,13 +795,94 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           tma_store_commit();
         }
       }
+      if (!ok) break;
+      // ---- the item's dK and dV: the last products have finished (the wait above covered them). This
+      // warpgroup, not the compute warpgroups, moves them out: thread = key row kv0 + r, 16 + 16 channels
+      // at a time (channel e and its rotation partner e + 32), scaled and rotated back (dK), packed to
+      // bf16 into the two halves of the staging area laid out as TMA boxes, then two TMA stores into
+      // dqkv. The compute warpgroups are already working on the next item meanwhile.
+      if (issuer) tma_store_wait_read<0>();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      {
+        const int krow = g.kv0 + r;
+        const bool rot = args.rope_pos != nullptr && krow < T;
+        const int pos = rot ? __ldg(args.rope_pos + krow) : 0;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {          // 0: dK, 1: dV
+          const uint32_t src = (which == 0 ? tdK : tdV) + lane_addr;
+          uint8_t* row = sDQ + which * FA_TILE_BYTES + r * 128;
+#pragma unroll
+          for (int grp = 0; grp < 4; ++grp) {              // channels [8 grp, +8) and their partners + 32
+            uint32_t a[8], b[8];
+            if (g.n_q > 0) {
+              tmem_ld8(src + grp * 8, a);
+              tmem_ld8(src + 32 + grp * 8, b);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) a[e] = b[e] = 0u;
+            }
+            if (which == 1 && grp == 3) {                  // everything has left tensor memory
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(acc_free);
+            }
+            float fa[8], fb[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              fa[e] = __uint_as_float(a[e]);
+              fb[e] = __uint_as_float(b[e]);
+            }
+            if (which == 0) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                fa[e] *= args.scale;
+                fb[e] *= args.scale;
+              }
+              if (rot) {
+                const float4* cp = reinterpret_cast<const float4*>(args.rope_cos + static_cast<size_t>(pos) * 32) + grp * 2;
+                const float4* sp = reinterpret_cast<const float4*>(args.rope_sin + static_cast<size_t>(pos) * 32) + grp * 2;
+#pragma unroll
+                for (int q4 = 0; q4 < 2; ++q4) {
+                  const float4 c4 = __ldg(cp + q4), s4 = __ldg(sp + q4);
+                  const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+                  const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    const int e = q4 * 4 + u;
+                    const float x = fa[e], y = fb[e];
+                    fa[e] = x * cc[u] + y * ss[u];
+                    fb[e] = y * cc[u] - x * ss[u];
+                  }
+                }
+              }
+            }
+            // 8 channels = one 16-byte chunk of the row: chunk grp, and chunk 4 + grp for the partners
+            *reinterpret_cast<uint4*>(row + ((grp ^ (r & 7)) << 4)) =
+                make_uint4(pack_bf16x2(fa[0], fa[1]), pack_bf16x2(fa[2], fa[3]), pack_bf16x2(fa[4], fa[5]),
+                           pack_bf16x2(fa[6], fa[7]));
+            *reinterpret_cast<uint4*>(row + (((4 + grp) ^ (r & 7)) << 4)) =
+                make_uint4(pack_bf16x2(fb[0], fb[1]), pack_bf16x2(fb[2], fb[3]), pack_bf16x2(fb[4], fb[5]),
+                           pack_bf16x2(fb[6], fb[7]));
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (issuer) {
+        tma_store_2d(&tmOUT, sDQ, HD + h * FA_D, g.kv0);
+        tma_store_2d(&tmOUT, sDQ + FA_TILE_BYTES, 2 * HD + h * FA_D, g.kv0);
+        tma_store_commit();
+      }
     }
     if (issuer) tma_store_wait<0>();            // the adds are complete before the CTA gives up its shared memory
     if (!ok && lane == 0 && *abort_flag == 0) {
       atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
       *abort_flag = 1;
     }
-  } else if (warp == Cfg::LOADER_WARP) {
+  } else {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_LIGHT));   // all four warps of the warpgroup
+  if (warp == Cfg::LOADER_WARP) {
     // ------------------------------------------------------------------ loader
     if (lane == 0) {
       uint32_t ic = 0, qc = 0;
@@ -966,6 +1049,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
       atomicExch(args.status, why);
       *abort_flag = 1;
     }
+  }
   }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
@@ -1138,7 +1222,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
       WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 5);
       // dK (warpgroup 0) / dV (warpgroup 1): every thread owns the 64 channels of key row kv0 + r.
       // Query-stationary: warpgroup 0 alone reads the item's dQ (row kv0 + r of the query tile).
-      if (gh >= (QST ? 1 : 2)) continue;
+      if (Cfg::DRAIN_WG || gh >= (QST ? 1 : 2)) continue;   // (the drain warpgroup stores dK / dV when it exists)
       uint64_t* const read_back = QST ? dq_free : acc_free;
       float acc[FA_D];
       if (g.n_q > 0) {
@@ -1436,10 +1520,12 @@ static int ws_bwd_impl(const void* qkv, const void* out, const void* dout, const
   if (rc) return rc;
   rc = ws_make_map(&tmDO, dout, static_cast<uint64_t>(H) * D, T);
   if (rc) return rc;
-  CUtensorMap tmDQ = tmDO;     // only the four-warpgroup atomics mode reads it
+  CUtensorMap tmDQ = tmDO, tmOUT = tmDO;     // only the four-warpgroup mode with the drain warpgroup reads them
   if (mode == 4) {
-    if (reinterpret_cast<uintptr_t>(dq_acc) & 15) return -3;
+    if ((reinterpret_cast<uintptr_t>(dq_acc) & 15) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) return -3;
     rc = ws_make_map_f32(&tmDQ, dq_acc, static_cast<uint64_t>(H) * D, T);
+    if (rc) return rc;
+    rc = ws_make_map(&tmOUT, dqkv, static_cast<uint64_t>(3) * H * D, T);
     if (rc) return rc;
   }
   int sms = 0;
@@ -1475,15 +1561,15 @@ static int ws_bwd_impl(const void* qkv, const void* out, const void* dout, const
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (grid > n_items) grid = n_items;
   if (mode == 2) {
-    fa_bwd_ws_kernel<2, BWD_KV_DQ><<<grid, WsBwdCfg<2, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
+    fa_bwd_ws_kernel<2, BWD_KV_DQ><<<grid, WsBwdCfg<2, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, tmOUT, a);
   } else if (mode == 0) {
-    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
+    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, tmOUT, a);
   } else if (mode == 3) {
-    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
-    fa_bwd_ws_kernel<4, BWD_Q><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
+    fa_bwd_ws_kernel<4, BWD_KV><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, tmOUT, a);
+    fa_bwd_ws_kernel<4, BWD_Q><<<grid, WsBwdCfg<4, false>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, tmOUT, a);
     return static_cast<int>(cudaGetLastError());
   } else {
-    fa_bwd_ws_kernel<4, BWD_KV_DQ><<<grid, WsBwdCfg<4, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, a);
+    fa_bwd_ws_kernel<4, BWD_KV_DQ><<<grid, WsBwdCfg<4, true>::THREADS, WS_BWD_SMEM, st>>>(tmQKV, tmDO, tmDQ, tmOUT, a);
   }
   {
     const long long total = static_cast<long long>(T) * H * 4;
