@@ -613,6 +613,30 @@ struct WsBwdGeo {
   int kv0, q_lo, q_hi, n_q;
 };
 
+// The two loads of an item's geometry, and the arithmetic on them, apart: the compute warpgroups issue
+// the loads of the NEXT item early and use them a few thousand cycles later (a global load on the
+// critical path of an item boundary cost 1 000 - 4 500 cycles inside this kernel).
+__device__ __forceinline__ void ws_bwd_geo_load(const FaWsBwdArgs& args, int kt, int& a, int& b) {
+  const int kv0 = kt * FA_T;
+  a = __ldg(args.seq_start + kv0);
+  b = __ldg(args.seq_end + min(kv0 + FA_T - 1, args.T - 1));
+}
+
+__device__ __forceinline__ WsBwdGeo ws_bwd_geo_make(const FaWsBwdArgs& args, int kt, int a, int b) {
+  WsBwdGeo g;
+  const int T = args.T, w = args.window;
+  g.kv0 = kt * FA_T;
+  const int last = min(g.kv0 + FA_T - 1, T - 1);
+  g.q_lo = a;
+  g.q_hi = b;
+  if (w >= 0) {
+    g.q_lo = max(g.q_lo, g.kv0 - w);
+    g.q_hi = min(g.q_hi, last + w + 1);
+  }
+  g.n_q = g.q_hi > g.q_lo ? (g.q_hi - g.q_lo + FA_T - 1) / FA_T : 0;
+  return g;
+}
+
 __device__ __forceinline__ WsBwdGeo ws_bwd_geometry(const FaWsBwdArgs& args, int kt) {
   WsBwdGeo g;
   const int T = args.T, w = args.window;
@@ -1102,15 +1126,29 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
       }
     };
 
+    // Geometry and first row data of an item are fetched during the item before it.
+    WsBwdGeo g_cur{0, 0, 0, 0};
+    RowInfo first{0.f, 0.f, 0, 0};
+    if (static_cast<int>(blockIdx.x) < n_items) {
+      g_cur = ws_bwd_geometry(args, blockIdx.x / H);
+      first = fetch_row((QST ? g_cur.kv0 : g_cur.q_lo) + r, blockIdx.x % H);
+    }
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const int h = item % H;
-      const WsBwdGeo g = ws_bwd_geometry(args, item / H);
+      const WsBwdGeo g = g_cur;
+      const int item_n = item + gridDim.x;
+      int gn_a = 0, gn_b = 0;
+      if (item_n < n_items) ws_bwd_geo_load(args, item_n / H, gn_a, gn_b);   // used in the item's last step
       // key-stationary: the query row changes with every step; query-stationary: one row per item
-      RowInfo nxt = fetch_row((QST ? g.kv0 : g.q_lo) + r, h);
+      RowInfo nxt = first;
       for (int j = 0; j < g.n_q; ++j) {
         const int q0 = g.q_lo + j * FA_T;      // first row of the streamed tile (queries, or keys when QST)
         const RowInfo ri = nxt;
         if (!QST && j + 1 < g.n_q) nxt = fetch_row(q0 + FA_T + r, h);
+        if (j == g.n_q - 1 && item_n < n_items) {
+          g_cur = ws_bwd_geo_make(args, item_n / H, gn_a, gn_b);
+          first = fetch_row((QST ? g_cur.kv0 : g_cur.q_lo) + r, item_n % H);
+        }
         ok = mbar_wait(sdp_full, c_sdp & 1u);
         ++c_sdp;
         ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
@@ -1211,6 +1249,10 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         WS_TRACE(warp == 0 || warp == NWG * 4 - 1, warp == 0 ? 1 : 2, 3);
       }
       if (!ok) break;
+      if (g.n_q == 0 && item_n < n_items) {    // (an item without steps did not reach the prefetch above)
+        g_cur = ws_bwd_geo_make(args, item_n / H, gn_a, gn_b);
+        first = fetch_row((QST ? g_cur.kv0 : g_cur.q_lo) + r, item_n % H);
+      }
       if (g.n_q > 0) {
         ok = mbar_wait(g_done, c_g & 1u);
         ++c_g;
