@@ -104,12 +104,52 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return *reinterpret_cast<float2*>(&d);
 }
 
+// Named barrier `id` over 128 threads (one warpgroup) with an AND over everybody's predicate: the
+// warps of a warpgroup agree on going on before they meet at plain barriers (a warp that had left
+// after a time-out would leave the others there for ever; a leaving warp calls this with false).
+__device__ __forceinline__ bool wg_barrier_and(int id, bool p) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q, o;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "bar.red.and.pred o, %1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, o;\n\t"
+      "}"
+      : "=r"(r)
+      : "r"(id), "r"(static_cast<uint32_t>(p))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void wg_barrier(int id) {
+  asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
+}
+
 struct WsGeo {
   int t0, kv_lo, n;
   int a[2], b[2];
 };
 
-__device__ __forceinline__ WsGeo ws_geometry(const FaWsArgs& args, int pair) {
+// The four loads of an item's geometry: issued by the softmax warpgroups one item ahead.
+struct WsGeoRaw {
+  int lo[2], hi[2];
+};
+__device__ __forceinline__ WsGeoRaw ws_geo_load(const FaWsArgs& args, int pair) {
+  WsGeoRaw raw;
+  const int T = args.T;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int first = pair * 2 * FA_T + i * FA_T;
+    raw.lo[i] = raw.hi[i] = 0;
+    if (first < T) {
+      raw.lo[i] = __ldg(args.seq_start + first);
+      raw.hi[i] = __ldg(args.seq_end + min(first + FA_T - 1, T - 1));
+    }
+  }
+  return raw;
+}
+
+__device__ __forceinline__ WsGeo ws_geo_make(const FaWsArgs& args, int pair, const WsGeoRaw& raw) {
   WsGeo g;
   const int T = args.T, w = args.window;
   g.t0 = pair * 2 * FA_T;
@@ -119,8 +159,8 @@ __device__ __forceinline__ WsGeo ws_geometry(const FaWsArgs& args, int pair) {
     const int first = g.t0 + i * FA_T;
     if (first < T) {
       const int last = min(first + FA_T - 1, T - 1);
-      lo[i] = __ldg(args.seq_start + first);
-      hi[i] = __ldg(args.seq_end + last);
+      lo[i] = raw.lo[i];
+      hi[i] = raw.hi[i];
       if (w >= 0) {
         lo[i] = max(lo[i], first - w);
         hi[i] = min(hi[i], last + w + 1);
@@ -142,6 +182,10 @@ __device__ __forceinline__ WsGeo ws_geometry(const FaWsArgs& args, int pair) {
   return g;
 }
 
+__device__ __forceinline__ WsGeo ws_geometry(const FaWsArgs& args, int pair) {
+  return ws_geo_make(args, pair, ws_geo_load(args, pair));
+}
+
 // PTMEM: the probabilities go back to tensor memory (bf16, 64 columns per tile) and the P V product
 // reads its A operand from there. The tensor core fetches shared-memory operands at about 64 bytes
 // per clock, so a 128 x 64 x 16 instruction with P in shared memory waits 3x longer for operands
@@ -149,7 +193,8 @@ __device__ __forceinline__ WsGeo ws_geometry(const FaWsArgs& args, int pair) {
 // the probabilities go through a swizzled shared-memory tile (the form the single-role kernels use).
 template <bool PTMEM>
 __global__ void __launch_bounds__(WS_THREADS, 1)
-fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args) {
+fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmO,
+                 const FaWsArgs args) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1024-byte aligned base
     if (threadIdx.x == 0) atomicExch(args.status, ST_BAD_ARG);
@@ -344,21 +389,39 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
     const int w = args.window;
     uint32_t s_cnt = 0, pv_cnt = 0;
     bool ok = true;
+    const bool st_issuer = quarter == 0 && lane == 0;     // issues this warpgroup's output stores
+    // geometry and key range of an item's rows are loaded one item ahead (a global load at an item
+    // boundary cost 1 000 - 4 500 cycles inside this kernel)
+    WsGeoRaw raw_n = ws_geo_load(args, blockIdx.x / H);
+    int lo_n = 0, hi_n = 0;
+    {
+      const int row0 = (static_cast<int>(blockIdx.x) / H) * 2 * FA_T + i * FA_T + row_local;
+      if (row0 < T) {
+        lo_n = __ldg(args.seq_start + row0);
+        hi_n = __ldg(args.seq_end + row0);
+      }
+    }
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const int h = item % H;
-      const WsGeo g = ws_geometry(args, item / H);
-      if (g.b[i] <= g.a[i]) continue;
+      const WsGeo g = ws_geo_make(args, item / H, raw_n);
       const int row = g.t0 + i * FA_T + row_local;
       const bool row_ok = row < T;
-      int lo = 0, hi = 0;  // this row attends to keys [lo, hi)
-      if (row_ok) {
-        lo = __ldg(args.seq_start + row);
-        hi = __ldg(args.seq_end + row);
-        if (w >= 0) {
-          lo = max(lo, row - w);
-          hi = min(hi, row + w + 1);
+      int lo = lo_n, hi = hi_n;  // this row attends to keys [lo, hi)
+      if (row_ok && w >= 0) {
+        lo = max(lo, row - w);
+        hi = min(hi, row + w + 1);
+      }
+      if (item + static_cast<int>(gridDim.x) < n_items) {
+        const int pair_n = (item + gridDim.x) / H;
+        raw_n = ws_geo_load(args, pair_n);
+        const int row_n = pair_n * 2 * FA_T + i * FA_T + row_local;
+        lo_n = hi_n = 0;
+        if (row_n < T) {
+          lo_n = __ldg(args.seq_start + row_n);
+          hi_n = __ldg(args.seq_end + row_n);
         }
       }
+      if (g.b[i] <= g.a[i]) continue;
       float m_used = -1e30f, l_run = 0.f;
       for (int j = g.a[i]; j < g.b[i]; ++j) {
         const int kv0 = g.kv_lo + j * FA_T;
@@ -506,11 +569,47 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         if (lane == 0) mbar_arrive(&p_ready[i]);
         WS_TRACE(quarter == 0, 1 + i, 3);
       }
-      if (!ok) break;
-      // last output update of this item
-      ok = mbar_wait(&pv_done[i], pv_cnt & 1u);
-      ++pv_cnt;
-      ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+      if (ok) {
+        // last output update of this item
+        ok = mbar_wait(&pv_done[i], pv_cnt & 1u);
+        ++pv_cnt;
+        ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+      }
+      if constexpr (PTMEM) {
+        // The output tile leaves through this warpgroup's 16 KB of the (otherwise unused) P area and one
+        // TMA store: the warpgroup goes on to its next item while the copy engine writes the rows.
+        if (st_issuer && ok) tma_store_wait_read<0>();     // the previous item's store has read the tile
+        ok = wg_barrier_and(1 + i, ok);                    // (a warp that gives up says so here)
+        if (!ok) break;
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t o[32];
+          tmem_ld32(tO + hlf * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 u;
+            uint32_t* p = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              p[q] = pack_bf16x2(__uint_as_float(o[e + 2 * q]) * inv, __uint_as_float(o[e + 2 * q + 1]) * inv);
+            *reinterpret_cast<uint4*>(sPi + swz(row_local, hlf * 4 + (e >> 3))) = u;
+          }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        wg_barrier(1 + i);
+        if (st_issuer) {                                   // rows past the end of the batch are clipped
+          tma_store_2d(&tmO, sPi, h * FA_D, g.t0 + i * FA_T);
+          tma_store_commit();
+        }
+        if (row_ok)
+          args.lse[static_cast<size_t>(h) * T + row] = l_run > 0.f ? m_used * args.scale + __logf(l_run) : 0.f;
+        WS_TRACE(quarter == 0, 1 + i, 5);
+        continue;
+      }
       if (!ok) break;
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -537,6 +636,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaWsArgs args)
         args.lse[static_cast<size_t>(h) * T + row] = l_run > 0.f ? m_used * args.scale + __logf(l_run) : 0.f;
       WS_TRACE(quarter == 0, 1 + i, 5);
     }
+    if (PTMEM && st_issuer) tma_store_wait<0>();   // the stores are complete before the CTA gives up its shared memory
     if (!ok && lane == 0 && *abort_flag == 0) {
       atomicExch(args.status, ST_TIMEOUT_TMEM_FULL);
       *abort_flag = 1;
@@ -592,22 +692,6 @@ constexpr int WSB_OFF_DS = WSB_OFF_P + 2 * FA_TILE_BYTES;
 constexpr int WSB_OFF_DQ = WSB_OFF_DS + 2 * FA_TILE_BYTES;   // [2 channel halves][128 q rows][32 fp32] staging of a dQ tile
 constexpr int WSB_OFF_BAR = WSB_OFF_DQ + 2 * FA_TILE_BYTES;
 constexpr int WS_BWD_SMEM = WSB_OFF_BAR + 512;
-
-// Named barrier 1 over 128 threads (one warpgroup) with an AND over everybody's predicate.
-__device__ __forceinline__ bool wg_barrier_and(bool p) {
-  uint32_t r;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred q, o;\n\t"
-      "setp.ne.b32 q, %1, 0;\n\t"
-      "bar.red.and.pred o, 1, 128, q;\n\t"
-      "selp.u32 %0, 1, 0, o;\n\t"
-      "}"
-      : "=r"(r)
-      : "r"(static_cast<uint32_t>(p))
-      : "memory");
-  return r != 0;
-}
 
 struct WsBwdGeo {
   int kv0, q_lo, q_hi, n_q;
@@ -790,7 +874,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         if (issuer) tma_store_wait_read<0>();
         // barrier over the warpgroup that also agrees on going on: all four warps leave together (a warp
         // that stayed behind would leave the others at the second barrier below for ever)
-        ok = wg_barrier_and(ok && *abort_flag == 0);
+        ok = wg_barrier_and(1, ok && *abort_flag == 0);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -1497,8 +1581,11 @@ extern "C" int nplm_fa_fwd_ws(const void* qkv, void* out, float* lse, const int*
   if (T <= 0) return 0;
   if (D != FA_D || H <= 0) return -3;
   if (reinterpret_cast<uintptr_t>(qkv) & 15) return -3;
-  CUtensorMap tm;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return -3;
+  CUtensorMap tm, tmO;
   int rc = ws_make_map(&tm, qkv, static_cast<uint64_t>(3) * H * D, T);
+  if (rc) return rc;
+  rc = ws_make_map(&tmO, out, static_cast<uint64_t>(H) * D, T);
   if (rc) return rc;
   int sms = 0;
   rc = ws_configure(&sms);
@@ -1523,9 +1610,9 @@ extern "C" int nplm_fa_fwd_ws(const void* qkv, void* out, float* lse, const int*
     p_smem = (e != nullptr && e[0] == '1') ? 1 : 0;
   }
   if (p_smem)
-    fa_fwd_ws_kernel<false><<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, a);
+    fa_fwd_ws_kernel<false><<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, tmO, a);
   else
-    fa_fwd_ws_kernel<true><<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, a);
+    fa_fwd_ws_kernel<true><<<grid, WS_THREADS, WS_FWD_SMEM, st>>>(tm, tmO, a);
   return static_cast<int>(cudaGetLastError());
 }
 
