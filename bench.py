@@ -419,6 +419,7 @@ def run_own(args) -> dict:
            "config": config_block(world, accum), "clocks": clocks, "e2e": e2e,
            "gpu_launches": launches, "final_loss": last_loss,
            "step_ms": {"min": -float(t[5]), "median": statistics.median(step_ms), "max": float(t[4]),
+                       "rank0_all": [round(x, 2) for x in step_ms],
                        "note": "device time of every timed optimizer step; min / max over ranks, median of rank 0"},
            "exposed_comm_ms": max(0.0, tail_ms - local_opt_ms) if fused_on else (0.0 if world == 1 else None),
            "exposed_comm": {"optimizer_step_after_backward_ms": tail_ms,
