@@ -55,30 +55,46 @@ class ClockSampler:
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu, self.samples, self._stop, self._t = gpu_index, [], threading.Event(), None
+        self.gpu, self.samples, self._t, self._p = gpu_index, [], None, None
+        self._t0 = self._t1 = None
 
     def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
-                                     timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([c.strip() for c in out.split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.2)
+        for line in self._p.stdout:
+            line = line.strip()
+            if line:
+                self.samples.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
     def start(self):
+        """Starts ONE nvidia-smi process that prints a sample every 200 ms (a new process per sample would
+        initialise NVML, and take the driver's locks, five times a second next to the launch thread).
+        Call before the warm-up steps; only samples between begin() and stop() are used."""
+        try:
+            self._p = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                        "--format=csv,noheader,nounits", "-lms", "200"],
+                                       stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._p = None
+            return
         self._t = threading.Thread(target=self._run, daemon=True)
         self._t.start()
 
+    def begin(self):
+        self._t0 = time.monotonic()
+
     def stop(self) -> dict:
-        self._stop.set()
+        self._t1 = time.monotonic()
+        if self._p is not None:
+            self._p.terminate()          # our own child, by handle
+            try:
+                self._p.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._p.kill()
         if self._t is not None:
             self._t.join(timeout=6)
+        t0 = self._t0 if self._t0 is not None else 0.0
+        rows = [f for (t, f) in self.samples if t0 <= t <= self._t1]
         sm, mx, reasons = [], 0.0, set()
-        for s in self.samples:
+        for s in rows:
             try:
                 sm.append(float(s[0]))
                 mx = max(mx, float(s[1]))
@@ -297,10 +313,15 @@ def run_own(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for s in range(W):
-        stepper.step_from_host(steps_host[s])
+    # the timed steps' batches go to the device BEFORE the warm-up steps: allocating them afterwards took
+    # cached blocks away from the first timed step, which then paid for new device allocations
     timed_host = steps_host[W:]
     timed_dev = [[move_batch(b, device) for b in st] for st in timed_host]
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()              # the process starts during the warm-up, its samples count from begin()
+    for s in range(W):
+        stepper.step_from_host(steps_host[s])
     tokens_timed = sum(steps_tok[W:])
     tok_t = torch.tensor([float(tokens_timed)], dtype=torch.float64, device=device)
     if world > 1:
@@ -308,12 +329,11 @@ def run_own(args) -> dict:
     global_tokens = float(tok_t.item())
 
     # ---- device-timed region ------------------------------------------------------------
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     if engine.fused is not None:
         engine.fused.timing, engine.fused.tail_events = True, []
     sync_all()
     if sampler:
-        sampler.start()
+        sampler.begin()
     launches0 = _lib.launches()
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
     marks[0].record()
@@ -553,6 +573,7 @@ def run_reference(args) -> dict:
             sync_all()
             if sampler:
                 sampler.start()
+                sampler.begin()
             ev0.record()
         elif state["n"] == W + K:
             ev1.record()
