@@ -173,6 +173,11 @@ def bench_attn_ws(T, peaks):
     dout = torch.randn(T, H * D, device="cuda").to(BF)
     ss, se = k.seq_bounds(cu, T)
     flush = _flush_buf()
+    pos = torch.cat([torch.arange(n) for n in lens]).to(torch.int32).cuda()
+    pos = torch.cat([pos, torch.zeros(T - pos.numel(), dtype=torch.int32, device="cuda")])[:T].contiguous()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    fr = torch.outer(torch.arange(1024, device="cuda").float(), inv)
+    rope = (pos, fr.cos().contiguous(), fr.sin().contiguous())
     for window in (-1, 64):
         ms = time_fn(lambda: k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl="ws"), iters=5, flush=flush)
         out, lse = k.fa_fwd(qkv, ss, se, H, D, window, 0.125, impl="ws")
@@ -180,8 +185,14 @@ def bench_attn_ws(T, peaks):
                        flush=flush)
         ms_d = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws",
                                         deterministic=True), iters=5, flush=flush)
+        # as in training: q / k were rotated by the QKV GEMM, dQ / dK are rotated back inside the backward
+        # kernels, rowsum(dO * O) comes from the output projection's data-gradient GEMM
+        delta = torch.zeros(H, T, device="cuda")
+        ms_r = time_fn(lambda: k.fa_bwd(qkv, out, dout, lse, ss, se, H, D, window, 0.125, impl="ws",
+                                        rope=rope, delta=delta, delta_ready=True), iters=5, flush=flush)
         print(json.dumps({"kernel": "fa_varlen_ws", "window": window, "T": T, "fwd_ms": round(ms, 4),
-                          "bwd_ms": round(ms_b, 4), "bwd_deterministic_ms": round(ms_d, 4)}), flush=True)
+                          "bwd_ms": round(ms_b, 4), "bwd_deterministic_ms": round(ms_d, 4),
+                          "bwd_fused_rope_delta_ready_ms": round(ms_r, 4)}), flush=True)
     k.check_status()
 
 
