@@ -320,7 +320,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             const uint32_t st = (kc + j) % WS_KV_STAGES, ph = ((kc + j) / WS_KV_STAGES) & 1u;
             if (!mbar_wait(&k_full[st], ph)) { ok = false; break; }
             WS_TRACE(true, 0, 1);
-            if (j >= g.a[i] && j < g.b[i]) {
+            if (j >= (i ? g.a[1] : g.a[0]) && j < (i ? g.b[1] : g.b[0])) {
               // the warpgroup holds the previous score tile in registers
               if (!mbar_wait(&s_free[i], (s_cnt & 1u) ^ 1u)) { ok = false; why = ST_TIMEOUT_TMEM_EMPTY; break; }
               tc_fence_after();
@@ -340,7 +340,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             const int jj = j - 1;
             const uint32_t st = (kc + jj) % WS_KV_STAGES, ph = ((kc + jj) / WS_KV_STAGES) & 1u;
             if (!mbar_wait(&v_full[st], ph)) { ok = false; break; }
-            if (jj >= g.a[i] && jj < g.b[i]) {
+            if (jj >= (i ? g.a[1] : g.a[0]) && jj < (i ? g.b[1] : g.b[0])) {
               if (!mbar_wait(&p_ready[i], p_cnt & 1u)) { ok = false; why = ST_TIMEOUT_MISC; break; }
               WS_TRACE(true, 0, 3);
               tc_fence_after();
@@ -349,13 +349,13 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
 #pragma unroll
                 for (int k = 0; k < FA_T / 16; ++k)   // P: 8 columns per 16 keys; V: 16 key rows = 2048 bytes
                   umma_bf16_ts(tO, tmem_base + 384 + i * 64 + k * 8, dV0 + k * (2048 >> 4), idesc_o,
-                               (jj > g.a[i] || k > 0) ? 1u : 0u);
+                               (jj > (i ? g.a[1] : g.a[0]) || k > 0) ? 1u : 0u);
               } else {
 #pragma unroll
                 for (int k = 0; k < FA_T / 16; ++k)   // P: 32 bytes per 16 keys, next column block after 4;
                                                       // V: 16 key rows = 2048 bytes
                   umma_bf16(tO, dP0 + ((k >> 2) * (FA_TILE_BYTES >> 4) + (k & 3) * 2), dV0 + k * (2048 >> 4),
-                            idesc_o, (jj > g.a[i] || k > 0) ? 1u : 0u);
+                            idesc_o, (jj > (i ? g.a[1] : g.a[0]) || k > 0) ? 1u : 0u);
               }
               umma_commit(&pv_done[i]);
               ++p_cnt;
@@ -421,9 +421,9 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           hi_n = __ldg(args.seq_end + row_n);
         }
       }
-      if (g.b[i] <= g.a[i]) continue;
+      if ((i ? g.b[1] : g.b[0]) <= (i ? g.a[1] : g.a[0])) continue;
       float m_used = -1e30f, l_run = 0.f;
-      for (int j = g.a[i]; j < g.b[i]; ++j) {
+      for (int j = (i ? g.a[1] : g.a[0]); j < (i ? g.b[1] : g.b[0]); ++j) {
         const int kv0 = g.kv_lo + j * FA_T;
         ok = mbar_wait(&s_full[i], s_cnt & 1u);
         ++s_cnt;
@@ -482,7 +482,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           alpha = exp2f((m_used - m_new) * sl2);
           m_used = m_new;
         }
-        if (j > g.a[i]) {
+        if (j > (i ? g.a[1] : g.a[0])) {
           // the previous output update has finished: the P tile is free and O may be rescaled
           ok = mbar_wait(&pv_done[i], pv_cnt & 1u);
           ++pv_cnt;
