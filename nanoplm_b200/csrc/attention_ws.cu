@@ -749,7 +749,7 @@ __device__ __forceinline__ WsBwdGeo ws_bwd_geometry(const FaWsBwdArgs& args, int
 // stalled the exponentials behind the load / store queue.
 template <int NWG, bool DQ>
 struct WsBwdCfg {
-  static constexpr bool DRAIN_WG = NWG == 4 && DQ;
+  static constexpr bool DRAIN_WG = NWG == 4;
   static constexpr int THREADS = (NWG + 1 + (DRAIN_WG ? 1 : 0)) * 128;
   static constexpr int LOADER_WARP = NWG * 4, MMA_WARP = NWG * 4 + 1, DRAIN_WARP = NWG * 4 + 4;
   static constexpr int CPT = FA_T / NWG;              // key columns per thread
@@ -877,6 +877,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         ok = wg_barrier_and(1, ok && *abort_flag == 0);
         if (!ok) break;
         tc_fence_after();
+        if constexpr (DQ) {
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {     // 32 channels at a time: this warpgroup runs on few registers
           uint32_t v[32];
@@ -902,6 +903,7 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
           tma_reduce_add_2d(&tmDQ, sDQ + FA_TILE_BYTES, h * FA_D + 32, q0);
           tma_store_commit();
         }
+        }
       }
       if (!ok) break;
       // ---- the item's dK and dV: the last products have finished (the wait above covered them). This
@@ -915,9 +917,10 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         const int krow = g.kv0 + r;
         const bool rot = args.rope_pos != nullptr && krow < T;
         const int pos = rot ? __ldg(args.rope_pos + krow) : 0;
+        constexpr int N_OUT = QST ? 1 : 2;                 // query-stationary: the item's dQ instead
 #pragma unroll
-        for (int which = 0; which < 2; ++which) {          // 0: dK, 1: dV
-          const uint32_t src = (which == 0 ? tdK : tdV) + lane_addr;
+        for (int which = 0; which < N_OUT; ++which) {      // 0: dK (dQ when QST), 1: dV
+          const uint32_t src = (QST ? tdQ : (which == 0 ? tdK : tdV)) + lane_addr;
           uint8_t* row = sDQ + which * FA_TILE_BYTES + r * 128;
 #pragma unroll
           for (int grp = 0; grp < 4; ++grp) {              // channels [8 grp, +8) and their partners + 32
@@ -930,10 +933,10 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
 #pragma unroll
               for (int e = 0; e < 8; ++e) a[e] = b[e] = 0u;
             }
-            if (which == 1 && grp == 3) {                  // everything has left tensor memory
+            if (which == N_OUT - 1 && grp == 3) {          // everything has left tensor memory
               tc_fence_before();
               __syncwarp();
-              if (lane == 0) mbar_arrive(acc_free);
+              if (lane == 0) mbar_arrive(QST ? dq_free : acc_free);
             }
             float fa[8], fb[8];
 #pragma unroll
@@ -978,8 +981,12 @@ fa_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (issuer) {
-        tma_store_2d(&tmOUT, sDQ, HD + h * FA_D, g.kv0);
-        tma_store_2d(&tmOUT, sDQ + FA_TILE_BYTES, 2 * HD + h * FA_D, g.kv0);
+        if constexpr (QST) {
+          tma_store_2d(&tmOUT, sDQ, h * FA_D, g.kv0);
+        } else {
+          tma_store_2d(&tmOUT, sDQ, HD + h * FA_D, g.kv0);
+          tma_store_2d(&tmOUT, sDQ + FA_TILE_BYTES, 2 * HD + h * FA_D, g.kv0);
+        }
         tma_store_commit();
       }
     }
@@ -1649,12 +1656,15 @@ static int ws_bwd_impl(const void* qkv, const void* out, const void* dout, const
   if (rc) return rc;
   rc = ws_make_map(&tmDO, dout, static_cast<uint64_t>(H) * D, T);
   if (rc) return rc;
-  CUtensorMap tmDQ = tmDO, tmOUT = tmDO;     // only the four-warpgroup mode with the drain warpgroup reads them
-  if (mode == 4) {
-    if ((reinterpret_cast<uintptr_t>(dq_acc) & 15) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) return -3;
-    rc = ws_make_map_f32(&tmDQ, dq_acc, static_cast<uint64_t>(H) * D, T);
-    if (rc) return rc;
+  CUtensorMap tmDQ = tmDO, tmOUT = tmDO;     // read by the drain warpgroup of the four-warpgroup kernels
+  if (mode != 2) {
+    if (reinterpret_cast<uintptr_t>(dqkv) & 15) return -3;
     rc = ws_make_map(&tmOUT, dqkv, static_cast<uint64_t>(3) * H * D, T);
+    if (rc) return rc;
+  }
+  if (mode == 4) {
+    if (reinterpret_cast<uintptr_t>(dq_acc) & 15) return -3;
+    rc = ws_make_map_f32(&tmDQ, dq_acc, static_cast<uint64_t>(H) * D, T);
     if (rc) return rc;
   }
   int sms = 0;
