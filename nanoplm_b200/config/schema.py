@@ -174,6 +174,7 @@ class PretrainingConfig:
     balance_quadratic: float = 1.0 / 2700.0   # cost(len) = len + balance_quadratic * len^2
     shard_params: bool = False           # keep 1/N of every layer's weights per rank, gather inside the GEMMs
     nvtx_ranges: bool = False            # NVTX ranges around data / forward / backward / optimizer (for profilers)
+    deterministic_attention: bool = False  # attention backward without atomics: bitwise reproducible, ~1.4x its time
 
 
 @dataclass

@@ -336,6 +336,9 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
 
     moe_layers = [m for m in model.modules() if hasattr(m, "dropped_rows") and hasattr(m, "experts_Wi")]
     use_nvtx = bool(getattr(cfg, "nvtx_ranges", False)) and device.type == "cuda"
+    if device.type == "cuda":
+        from nanoplm_b200.ops import kernels as _kernels
+        _kernels.set_attention_deterministic(bool(getattr(cfg, "deterministic_attention", False)))
 
     def _range(name: str):
         """NVTX range (`pretraining.nvtx_ranges: true`) so that a timeline profiler shows the phases

@@ -50,6 +50,9 @@ def test_loader_rules():
     assert cfg.adam_learning_rate == 3e-4 and cfg.adam_weight_decay == 0.01 and cfg.bf16 is False
     with pytest.raises(ConfigError, match="Invalid adam_beta1"):
         load_pretrain_config({**pre, "adam_beta1": "abc"})
+    extra = load_pretrain_config({**pre, "deterministic_attention": True, "shard_params": True, "balance_ranks": False})
+    assert extra.deterministic_attention is True and extra.shard_params is True and extra.balance_ranks is False
+    assert load_pretrain_config(pre).deterministic_attention is False
     assert load_resume_config(None).is_resume is False
     with pytest.raises(ConfigError, match="does not exist"):
         load_resume_config({"is_resume": True, "checkpoint_dir": "/nonexistent/ckpt"})
