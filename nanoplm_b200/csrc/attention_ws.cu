@@ -749,13 +749,12 @@ __device__ __forceinline__ WsBwdGeo ws_bwd_geometry(const FaWsBwdArgs& args, int
 // [g * 128 / NWG, +128 / NWG) of every query row. Four warpgroups put four compute warps on every
 // scheduler (the per-element work has no cross-thread dependency, so the split is free) at 104
 // registers per thread; two warpgroups run at 216.
-// DQ: also form dQ = dS K per step and add it to the fp32 accumulator with vector atomics. Without
-// it the kernel produces dK / dV only and dQ comes from the query-stationary launch (MODE 2 below: no
-// atomics, no scratch, bitwise reproducible).
-// With four compute warpgroups and DQ, a further warpgroup does nothing but read each step's dQ
-// tile out of tensor memory and add it to the accumulator: the vector atomics saturate the L2's
-// atomic rate (about 1 GB of fp32 adds per backward pass), and issued by the compute warps they
-// stalled the exponentials behind the load / store queue.
+// DQ: also form dQ = dS K per step and add it to the fp32 accumulator. Without it the kernel produces
+// dK / dV only and dQ comes from the query-stationary launch (MODE 2 below: no atomics, no scratch,
+// bitwise reproducible).
+// With four compute warpgroups a further (drain) warpgroup does nothing but move results out of tensor
+// memory: staging tiles in shared memory, then TMA reduce-adds (dQ tiles) or TMA stores (dK / dV, the
+// item's dQ in the query-stationary launch) issued by one of its threads.
 template <int NWG, bool DQ>
 struct WsBwdCfg {
   static constexpr bool DRAIN_WG = NWG == 4;
