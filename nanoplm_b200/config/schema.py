@@ -163,7 +163,7 @@ class PretrainingConfig:
     max_grad_norm: float = 1.0
     fp8: bool = False
     fp8_recipe: str = "block128"
-    expert_parallel_size: int = 1
+    expert_parallel_size: int = 1        # ranks per expert-parallel group (divides the world; every group holds all experts)
     fused_comm: bool = True              # P2P-fused reduce-scatter + AdamW + all-gather when possible
     sharded_checkpoint: bool = False     # additionally write shard-<rank>.pt + index.json
     device_masking: bool = False         # apply MLM masking on the GPU (Philox) instead of the collator

@@ -1,5 +1,5 @@
-"""Optimizer engine for models whose MoE experts are split over the data-parallel ranks
-(`pretraining.expert_parallel_size` = number of ranks).
+"""Optimizer engine for models whose MoE experts are split over data-parallel ranks
+(`pretraining.expert_parallel_size` ranks per expert-parallel group; the world may hold several groups).
 
 Dense parameters (attention, dense MLPs, routers, norms, embeddings) go through the sharded
 data-parallel engine unchanged: gradients are summed over ranks, AdamW runs on the owned slice,
@@ -9,6 +9,12 @@ num_experts / world experts, their gradients already contain the contributions o
 tokens (the rows travelled to the owner in the forward pass and their gradients came back in the
 backward pass), so they are neither reduced nor gathered; they only share the scaling
 1 / (grad_accum * world) and the global clipping norm with the dense part.
+
+With `expert_parallel_size` < world the ranks form world / size expert-parallel groups of consecutive
+ranks (rows travel inside a group only); the ranks with the same position in their groups hold the
+same experts, and the gradients of those replicas are summed over that "expert data-parallel" group
+before the update (`make_expert_groups`). Not tested on a GPU with more groups than one (it needs
+four GPUs); the gloo test runs it on four CPU ranks.
 
 The reference has neither MoE layers nor expert parallelism.
 """
@@ -38,9 +44,33 @@ def shard_model_experts(model: torch.nn.Module, group) -> int:
     return n
 
 
+def make_expert_groups(ep_size: int):
+    """(expert-parallel group, expert data-parallel group) of this rank for groups of `ep_size`
+    consecutive ranks; (WORLD, None) when one group spans the world. Collective: every rank creates
+    every group, in the same order."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if ep_size == world:
+        return dist.group.WORLD, None
+    if ep_size < 1 or world % ep_size:
+        raise ValueError(f"expert_parallel_size ({ep_size}) must divide the number of ranks ({world})")
+    ep_group = edp_group = None
+    for g in range(world // ep_size):
+        grp = dist.new_group(list(range(g * ep_size, (g + 1) * ep_size)))
+        if rank // ep_size == g:
+            ep_group = grp
+    for k in range(ep_size):
+        grp = dist.new_group(list(range(k, world, ep_size)))
+        if rank % ep_size == k:
+            edp_group = grp
+    return ep_group, edp_group
+
+
 class ExpertParallelEngine(ShardedEngine):
     def __init__(self, model, hyper: AdamWHyper, device, process_group=None,
-                 compute_dtype: torch.dtype = torch.bfloat16, fused_comm: bool = False):
+                 compute_dtype: torch.dtype = torch.bfloat16, fused_comm: bool = False,
+                 ep_group=None, edp_group=None):
+        """ep_group: the ranks the experts are split over (default: all ranks of process_group);
+        edp_group: the ranks holding the same experts as this one in other expert-parallel groups."""
         expert_names = [n for n, _ in model.named_parameters() if is_expert_param(n)]
         if not expert_names:
             raise ValueError("the model has no expert parameters (model.moe is not configured)")
@@ -62,8 +92,14 @@ class ExpertParallelEngine(ShardedEngine):
         self.x_exp_avg = torch.zeros(self.x_total, dtype=torch.float32, device=dev)
         self.x_exp_avg_sq = torch.zeros(self.x_total, dtype=torch.float32, device=dev)
         self._x_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.ep_group = ep_group if ep_group is not None else self.pg
+        self.edp_group = edp_group
+        self.ep_world = dist.get_world_size(self.ep_group) if self.distributed else 1
+        self.ep_rank = dist.get_rank(self.ep_group) if self.distributed else 0
         for s in self.x_slots:
             self.x_master[s.offset:s.offset + s.numel] = s.param.detach().to(dev, torch.float32).reshape(-1)
+        if self.edp_group is not None:     # the replicas of an expert start from the same values
+            dist.broadcast(self.x_master, src=dist.get_global_rank(self.edp_group, 0), group=self.edp_group)
         self.x_params.copy_(self.x_master.to(self.compute_dtype))
         self._rebind_experts()
 
@@ -75,7 +111,7 @@ class ExpertParallelEngine(ShardedEngine):
                 s.param.main_grad = self.x_grad[s.offset:s.offset + s.numel].view(s.shape)
 
     def num_parameters(self) -> int:
-        return super().num_parameters() + self.world * sum(s.numel for s in self.x_slots)
+        return super().num_parameters() + self.ep_world * sum(s.numel for s in self.x_slots)
 
     def collect_autograd_grads(self) -> None:
         super().collect_autograd_grads()
@@ -93,7 +129,9 @@ class ExpertParallelEngine(ShardedEngine):
 
     def step(self, lr: float, grad_accum: int = 1, extra_sumsq=None) -> torch.Tensor:
         self.collect_autograd_grads()
-        # squared norm of all experts' gradients: every rank holds different experts
+        if self.edp_group is not None:     # the other expert-parallel groups saw other tokens
+            dist.all_reduce(self.x_grad, op=dist.ReduceOp.SUM, group=self.edp_group)
+        # squared norm of all experts' gradients: the ranks of ONE expert-parallel group hold every expert once
         self._x_sumsq.zero_()
         if self.on_cuda:
             from nanoplm_b200.ops import kernels as K
@@ -101,7 +139,7 @@ class ExpertParallelEngine(ShardedEngine):
         else:
             self._x_sumsq += self.x_grad.double().pow(2).sum().float()
         if self.distributed:
-            dist.all_reduce(self._x_sumsq, op=dist.ReduceOp.SUM, group=self.pg)
+            dist.all_reduce(self._x_sumsq, op=dist.ReduceOp.SUM, group=self.ep_group)
         norm = super().step(lr, grad_accum, extra_sumsq=self._x_sumsq)   # leaves the global norm in _sumsq
         grad_scale = 1.0 / (grad_accum * self.world)
         if self.on_cuda:
@@ -121,8 +159,8 @@ class ExpertParallelEngine(ShardedEngine):
         for s in self.x_slots:
             local = flat[s.offset:s.offset + s.numel].view(s.shape).contiguous()
             if self.distributed:
-                parts = [torch.empty_like(local) for _ in range(self.world)]
-                dist.all_gather(parts, local, group=self.pg)
+                parts = [torch.empty_like(local) for _ in range(self.ep_world)]
+                dist.all_gather(parts, local, group=self.ep_group)
                 local = torch.cat(parts, dim=0)
             out[s.name] = local.float().cpu()
         return out
@@ -135,10 +173,10 @@ class ExpertParallelEngine(ShardedEngine):
                     raise KeyError(f"missing expert tensor in checkpoint: {s.name}")
                 continue
             L = s.shape[0]
-            mine = t[self.rank * L:(self.rank + 1) * L]
+            mine = t[self.ep_rank * L:(self.ep_rank + 1) * L]
             if tuple(mine.shape) != tuple(s.shape):
                 raise ValueError(f"{s.name}: checkpoint holds {tuple(t.shape)}, this rank needs {tuple(s.shape)} "
-                                 f"x {self.world} ranks")
+                                 f"x {self.ep_world} ranks")
             flat[s.offset:s.offset + s.numel] = mine.to(flat.device, torch.float32).reshape(-1)
 
     def full_state_dict_model(self, extra_tied=None) -> dict:

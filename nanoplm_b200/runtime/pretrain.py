@@ -216,17 +216,19 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
     ep_size = int(getattr(cfg, "expert_parallel_size", 1) or 1)
     if ep_size > 1:
         # experts split over the data-parallel ranks (peer-memory dispatch / combine on CUDA)
-        if ep_size != world:
-            raise ValueError(f"expert_parallel_size ({ep_size}) must equal the number of ranks ({world}): "
-                             "experts are split over all data-parallel ranks")
+        if ep_size > world or world % ep_size:
+            raise ValueError(f"expert_parallel_size ({ep_size}) must divide the number of ranks ({world}): "
+                             "the ranks form world / size groups, each holding every expert once")
         if opt_name not in ("adamw", "stable_adamw"):
             raise ValueError("expert parallelism is implemented for the AdamW engine only")
-        from nanoplm_b200.parallel.expert_engine import ExpertParallelEngine, shard_model_experts
-        if shard_model_experts(model, dist.group.WORLD) == 0:
+        from nanoplm_b200.parallel.expert_engine import (ExpertParallelEngine, make_expert_groups,
+                                                         shard_model_experts)
+        ep_group, edp_group = make_expert_groups(ep_size)
+        if shard_model_experts(model, ep_group) == 0:
             raise ValueError("expert_parallel_size > 1 needs a model with model.moe configured")
         engine = ExpertParallelEngine(model, hyper, device,
                                       compute_dtype=torch.bfloat16 if use_bf16 else torch.float32,
-                                      fused_comm=bool(cfg.fused_comm))
+                                      fused_comm=bool(cfg.fused_comm), ep_group=ep_group, edp_group=edp_group)
     elif opt_name in ("muon", "normuon"):
         from nanoplm_b200.parallel.muon import MuonEngine
         engine = MuonEngine(model, hyper, cfg, device)

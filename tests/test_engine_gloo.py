@@ -142,11 +142,12 @@ def _make_moe_model():
     return m
 
 
-def _train_moe(rank, world, port, tmp, expert_parallel):
-    """world == 1: replicated experts, gradient accumulation over both micro-batches.
-    world == 2 + expert_parallel: every rank takes one micro-batch and owns half of the experts."""
+def _train_moe(rank, world, port, tmp, expert_parallel, per_step=2, ep_size=None):
+    """world == 1: replicated experts, gradient accumulation over the step's micro-batches.
+    world == 2 + expert_parallel: every rank takes one micro-batch and owns half of the experts.
+    ep_size < world: world / ep_size expert-parallel groups, every group holds every expert once."""
     from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
-    from nanoplm_b200.parallel.expert_engine import ExpertParallelEngine, shard_model_experts
+    from nanoplm_b200.parallel.expert_engine import ExpertParallelEngine, make_expert_groups, shard_model_experts
     from nanoplm_b200.runtime.pretrain import TrainStep
     from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
     if world > 1:
@@ -156,15 +157,16 @@ def _train_moe(rank, world, port, tmp, expert_parallel):
     model = _make_moe_model()
     hyper = AdamWHyper(lr=5e-3, weight_decay=0.01, max_grad_norm=0.5)
     if expert_parallel:
-        assert shard_model_experts(model, dist.group.WORLD) == 1
-        eng = ExpertParallelEngine(model, hyper, torch.device("cpu"))
+        ep_group, edp_group = make_expert_groups(ep_size or world)
+        assert shard_model_experts(model, ep_group) == 1
+        eng = ExpertParallelEngine(model, hyper, torch.device("cpu"), ep_group=ep_group, edp_group=edp_group)
     else:
         eng = ShardedEngine(model, hyper, torch.device("cpu"))
     st = TrainStep(model, eng, WarmupLinearSchedule(5e-3, 2, 100), "cpu")
-    batches = _batches(8)
+    batches = _batches(3 * per_step + 2)
     losses = []
     for step in range(3):
-        losses.append(st.step_from_host(batches[2 * step:2 * step + 2][rank::world]))
+        losses.append(st.step_from_host(batches[per_step * step:per_step * step + per_step][rank::world]))
     if world > 1:
         t = torch.tensor(losses)
         dist.all_reduce(t)
@@ -179,14 +181,15 @@ def _train_moe(rank, world, port, tmp, expert_parallel):
         dist.destroy_process_group()
 
 
-def _run_moe(world, tmp, expert_parallel):
+def _run_moe(world, tmp, expert_parallel, per_step=2, ep_size=None):
     ctx = mp.get_context("spawn")
     port = _free_port()
-    procs = [ctx.Process(target=_train_moe, args=(r, world, port, tmp, expert_parallel)) for r in range(world)]
+    procs = [ctx.Process(target=_train_moe, args=(r, world, port, tmp, expert_parallel, per_step, ep_size))
+             for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
-        p.join(180)
+        p.join(240)
         assert p.exitcode == 0
     return torch.load(os.path.join(tmp, "result.pt"))
 
@@ -204,6 +207,24 @@ def test_expert_parallel_training_matches_replicated_experts(tmp_path):
     assert set(sd1) == set(sd2)
     for k in sd1:
         assert sd1[k].shape == sd2[k].shape, k            # gathered experts have the full first axis
+        assert torch.allclose(sd1[k], sd2[k], atol=5e-5), k
+    assert extra is not None and all(v.shape[0] == 4 for v in extra["exp_avg"].values())
+
+
+def test_two_expert_parallel_groups_of_two_ranks_match_replicated_experts(tmp_path):
+    """Four ranks as two expert-parallel groups (expert_parallel_size 2): rows travel inside a group, the
+    replicas of an expert in the two groups sum their gradients, the clipping norm counts every expert
+    once. Same trajectory as one process with all experts and the four micro-batches of a step."""
+    d1, d2 = str(tmp_path / "one"), str(tmp_path / "ep")
+    os.makedirs(d1)
+    os.makedirs(d2)
+    l1, sd1, _ = _run_moe(1, d1, False, per_step=4)
+    l2, sd2, extra = _run_moe(4, d2, True, per_step=4, ep_size=2)
+    for a, b in zip(l1, l2):
+        assert abs(a - b) < 2e-4, (l1, l2)
+    assert set(sd1) == set(sd2)
+    for k in sd1:
+        assert sd1[k].shape == sd2[k].shape, k
         assert torch.allclose(sd1[k], sd2[k], atol=5e-5), k
     assert extra is not None and all(v.shape[0] == 4 for v in extra["exp_avg"].values())
 
