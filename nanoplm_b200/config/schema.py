@@ -175,6 +175,7 @@ class PretrainingConfig:
     shard_params: bool = False           # keep 1/N of every layer's weights per rank, gather inside the GEMMs
     nvtx_ranges: bool = False            # NVTX ranges around data / forward / backward / optimizer (for profilers)
     deterministic_attention: bool = False  # attention backward without atomics: bitwise reproducible, ~1.4x its time
+    hf_checkpoint_files: bool = False    # also write model.safetensors + trainer_state.json (HF-Trainer layout)
 
 
 @dataclass

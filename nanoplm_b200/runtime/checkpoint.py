@@ -15,7 +15,10 @@ resume that needs no gather/scatter.
 scheduler.pt, trainer_state.json}`), so a run started there can continue here: the parameter names
 are the same (the reference maps them one to one, modeling.py:758-764), the Trainer's AdamW groups
 are [decay | no-decay] in `named_parameters` order like this engine's, and the step comes from
-`trainer_state.json`.
+`trainer_state.json`. With `hf_files=True` (`pretraining.hf_checkpoint_files`) `save_checkpoint` writes
+those two files next to its own, so that the reference's HF-Trainer pipeline (or any safetensors
+reader) can pick the run up: `model.safetensors` holds every tensor once (the tied decoder weight is
+left to the embedding, as `save_pretrained` does).
 """
 from __future__ import annotations
 
@@ -46,7 +49,8 @@ def _barrier():
 
 def save_checkpoint(engine, scheduler, global_step: int, epoch: int, output_dir: str,
                     logging_steps: int, eval_steps: int, save_steps: int, is_main: bool = True,
-                    sharded: bool = False, extra_state: Optional[dict] = None) -> Path:
+                    sharded: bool = False, extra_state: Optional[dict] = None, hf_files: bool = False,
+                    tied_keys: tuple = ("decoder.weight",)) -> Path:
     final = Path(output_dir) / f"checkpoint-{global_step}"
     tmp = Path(output_dir) / f".tmp-checkpoint-{global_step}"
     model_sd = engine.full_state_dict_model()       # collective
@@ -73,6 +77,8 @@ def save_checkpoint(engine, scheduler, global_step: int, epoch: int, output_dir:
         if extra_state:
             state.update(extra_state)
         (tmp / STATE_FILE).write_text(json.dumps(state, indent=2), encoding="utf-8")
+        if hf_files:
+            _write_hf_files(tmp, model_sd, global_step, epoch, logging_steps, eval_steps, save_steps, tied_keys)
         if sharded:
             (tmp / "index.json").write_text(json.dumps(
                 {"world_size": engine.world, "total": engine.total, "shard": engine.shard,
@@ -85,6 +91,20 @@ def save_checkpoint(engine, scheduler, global_step: int, epoch: int, output_dir:
         logger.info(f"Checkpoint saved -> {final}")
     _barrier()
     return final
+
+
+def _write_hf_files(ckp: Path, model_sd: dict, global_step: int, epoch: int, logging_steps: int,
+                    eval_steps: int, save_steps: int, tied_keys: tuple) -> None:
+    """`model.safetensors` + `trainer_state.json` as the HF Trainer leaves them (pipeline.py:293-295)."""
+    from safetensors.torch import save_file
+    tensors = {k: v.detach().to("cpu").contiguous().clone() for k, v in model_sd.items()
+               if k not in tied_keys and isinstance(v, torch.Tensor)}
+    save_file(tensors, str(ckp / "model.safetensors"), metadata={"format": "pt"})
+    trainer_state = {"global_step": int(global_step), "epoch": float(epoch), "max_steps": None,
+                     "logging_steps": int(logging_steps), "eval_steps": int(eval_steps),
+                     "save_steps": int(save_steps), "log_history": [], "best_metric": None,
+                     "best_model_checkpoint": None, "is_world_process_zero": True, "is_local_process_zero": True}
+    (ckp / "trainer_state.json").write_text(json.dumps(trainer_state, indent=2), encoding="utf-8")
 
 
 def load_checkpoint(engine, scheduler, checkpoint_dir: str, restore_rng: bool = True) -> tuple[int, int]:

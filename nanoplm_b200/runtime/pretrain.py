@@ -470,7 +470,8 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
             if global_step % plan.save_steps == 0:
                 check_device_status()     # raises before a corrupted state could be persisted
                 ckpt.save_checkpoint(engine, scheduler, global_step, epoch, output_dir, plan.logging_steps,
-                                     plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint)
+                                     plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint,
+                                     hf_files=bool(getattr(cfg, "hf_checkpoint_files", False)))
             if max_steps is not None and global_step - start_step >= max_steps:
                 done = True
                 break
@@ -483,7 +484,8 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
         dist.barrier()
     if final_checkpoint:
         ckpt.save_checkpoint(engine, scheduler, global_step, num_epochs, output_dir, plan.logging_steps,
-                             plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint)
+                             plan.eval_steps, plan.save_steps, is_main, cfg.sharded_checkpoint,
+                             hf_files=bool(getattr(cfg, "hf_checkpoint_files", False)))
     sink.finish(output_dir)
     if watchdog is not None:
         watchdog.stop()

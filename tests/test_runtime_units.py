@@ -174,3 +174,38 @@ def test_padding_tail_trim_is_exact_on_cpu():
     assert abs(results[0][0] - results[1][0]) < 1e-6
     for g0, g1 in zip(results[0][1], results[1][1]):
         assert torch.allclose(g0, g1, atol=1e-6)
+
+
+def test_checkpoint_with_hf_files_loads_through_the_hf_layout_alone(tmp_path):
+    """`hf_files=True` adds model.safetensors + trainer_state.json; with the native files removed the
+    directory is exactly what the HF-Trainer pipeline leaves, and it still resumes (weights, step)."""
+    import torch
+    from safetensors.torch import load_file
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    cfg = ModelConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                      max_position_embeddings=64)
+    torch.manual_seed(0)
+    eng = ShardedEngine(ProtEncoderMLM(cfg, ProtTokenizer()), AdamWHyper(), torch.device("cpu"))
+    eng.main_grad.normal_()
+    eng.step(1e-3, 1)
+    path = ckpt.save_checkpoint(eng, WarmupLinearSchedule(1e-3, 1, 10), 7, 2, str(tmp_path), 1, 5, 5, hf_files=True)
+    st = load_file(str(path / "model.safetensors"))
+    full = eng.full_state_dict_model()
+    assert "decoder.weight" in full and "decoder.weight" not in st          # tied weight stored once
+    assert set(st) == set(full) - {"decoder.weight"}
+    import json
+    assert json.loads((path / "trainer_state.json").read_text())["global_step"] == 7
+    for name in ("pytorch_model.bin", "training_state.json", "rng_state.pth"):
+        (path / name).unlink()
+    torch.manual_seed(1)
+    eng2 = ShardedEngine(ProtEncoderMLM(cfg, ProtTokenizer()), AdamWHyper(), torch.device("cpu"))
+    step, epoch = ckpt.load_checkpoint(eng2, WarmupLinearSchedule(1e-3, 1, 10), str(path))
+    assert (step, epoch) == (7, 2)
+    other = eng2.full_state_dict_model()
+    for k, v in full.items():
+        assert torch.equal(v, other[k]), k
