@@ -59,8 +59,15 @@ def from_yaml(config: Path) -> None:
     except (ConfigError, ValueError) as exc:
         raise click.ClickException(str(exc)) from exc
     if not pure_enabled:
-        logger.info("pure_torch.enabled is false: the HF-Trainer pipeline of the reference has no "
-                    "counterpart here; running the native pipeline with the same settings.")
+        # The reference then runs its HF-Trainer pipeline (src/nanoplm/pretraining/pipeline.py:107-295):
+        # padded batches from ProtDataCollatorForLM, checkpoints with model.safetensors and
+        # trainer_state.json. The same recipe on the native pipeline: no packing, and every checkpoint
+        # also carries the two HF files (the native files stay, so either pipeline can resume).
+        import dataclasses
+        pt = dataclasses.replace(pt, use_packing=False)
+        cfg.hf_checkpoint_files = True
+        logger.info("pure_torch.enabled is false: running the reference's HF-Trainer recipe on the native "
+                    "pipeline (padded batches, checkpoints also carry model.safetensors and trainer_state.json).")
     _launch(model_cfg, cfg, pt, resume)
 
 

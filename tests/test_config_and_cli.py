@@ -115,6 +115,19 @@ def test_cli_data_pretrain_resume_cycle(tmp_path, monkeypatch):
     assert len(archived) == 1 and sorted(p.name for p in archived[0].iterdir()) == ["checkpoint-12", "checkpoint-9"]
     assert (run / "checkpoint-18").exists()                                            # 3 epochs x 6 steps
 
+    # pure_torch.enabled: false = the reference's HF-Trainer recipe: padded batches, HF files in the checkpoints
+    hf = {k: (dict(v) if isinstance(v, dict) else v) for k, v in cfg.items()}
+    hf["resume"] = {"is_resume": False, "checkpoint_dir": "", "extra_epochs": None}
+    hf["pure_torch"] = {"enabled": False}
+    hf["pretraining"].update(ckp_dir="ckpt_hf", num_epochs=1, save_steps=3)
+    (tmp_path / "hf.yaml").write_text(yaml.safe_dump(hf))
+    r = runner.invoke(cli, ["pretrain", "from-yaml", "hf.yaml"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    hf_run = next((tmp_path / "ckpt_hf").glob("run-*"))
+    some = sorted(hf_run.glob("checkpoint-*"))[0]
+    for f in ("model.safetensors", "trainer_state.json", "pytorch_model.bin", "optimizer.pt"):
+        assert (some / f).exists(), f
+
     bad = dict(cfg)
     bad["pretraining"] = {**cfg["pretraining"], "gradient_accumulation_steps": 2}
     (tmp_path / "bad.yaml").write_text(yaml.safe_dump(bad))
