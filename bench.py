@@ -569,10 +569,11 @@ def run_reference(args) -> dict:
     def timed_step(self, *a, **kw):
         out = orig_step(self, *a, **kw)
         state["n"] += 1
+        if state["n"] == 1 and sampler:
+            sampler.start()      # during the warm-up, as in the own arm: NVML start-up stays out of the timed steps
         if state["n"] == W:
             sync_all()
             if sampler:
-                sampler.start()
                 sampler.begin()
             ev0.record()
         elif state["n"] == W + K:
