@@ -8,7 +8,10 @@
     (pure_pipeline.py:224-331);
   * tokenizer ids (tokenizer.py:20-62) including lower case and the U / Z / O / B residues;
   * packing-collator layout: cu_seqlens, position ids, flat length, padding sequences, and the MLM
-    invariants of tests/test_packing_collator.py:57-255 checked on both collators.
+    invariants of tests/test_packing_collator.py:57-255 checked on both collators;
+  * the ProtX student (distillation/models/student/model.py:50-112): same keys, same raw and projected
+    embeddings with the reference's weights, same tokenizer ids, same masked-MSE loss as the reference's
+    distillation trainer (distillation/trainer.py:30-40).
 """
 import os
 import sys
@@ -335,3 +338,47 @@ def test_hf_trainer_checkpoint_layout_resumes_here(ref, tmp_path):
     assert len(mine) == len(theirs) == len(named)
     assert all(torch.allclose(mine[i]["exp_avg"], theirs[i]["exp_avg"], atol=1e-8) for i in theirs)
     assert len(decay) == len([s for s in eng.slots if s.decay])
+
+
+def test_student_protx_matches_the_reference_student(ref):
+    """The reference's ProtX (its SwiGLU ModernBERT body + 1024-wide projection + T5 norm,
+    distillation/models/student/model.py:50-112) and this package's student share state-dict keys; with
+    the reference's weights copied across they give the same raw and projected embeddings on a padded
+    batch, the two tokenizers give the same ids, and the masked MSE of the distillation trainer
+    (distillation/trainer.py:30-40) agrees with `ops.functional.masked_mse`."""
+    try:
+        from nanoplm.distillation.models.student.model import ProtX as RefProtX, ProtXConfig as RefCfg
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference student import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.config.schema import StudentConfig
+    from nanoplm_b200.models.student import ProtX
+    from nanoplm_b200.ops import functional as ops
+    torch.manual_seed(0)
+    geom = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=2)
+    rm = RefProtX(RefCfg(**geom)).float().eval()
+    with torch.no_grad():
+        for p in rm.parameters():
+            if p.ndim >= 2:
+                p.add_(torch.randn_like(p) * 0.05)
+    om = ProtX(StudentConfig(max_position_embeddings=8192, **geom)).float().eval()
+    assert set(om.state_dict()) == set(rm.state_dict())
+    om.load_state_dict(rm.state_dict(), strict=True)
+    seqs = ["MKTAYIAKQRQISFVKSHFSRQ", "ACDEFGHIKLMNPQRSTVWY" * 8, "MK", "mktay" + "UZOB"]
+    enc = rm.tokenizer(seqs, padding=True, return_tensors="pt")
+    for s in seqs:
+        assert om.tokenizer.encode(s) == rm.tokenizer(s)["input_ids"], s
+    keep = enc["attention_mask"].bool()
+    with torch.no_grad():
+        for training_mode in (False, True):
+            a = rm(enc["input_ids"], enc["attention_mask"], training_mode=training_mode).last_hidden_state
+            b = om(enc["input_ids"], enc["attention_mask"], training_mode=training_mode)
+            b = b["last_hidden_state"] if isinstance(b, dict) else b.last_hidden_state
+            assert a.shape == b.shape
+            assert (a[keep] - b[keep]).abs().max().item() < 2e-5 * max(1.0, a[keep].abs().max().item())
+        # the trainer's loss: sum over features of the squared error, mean over real tokens
+        teacher = torch.randn_like(a)
+        m = enc["attention_mask"].unsqueeze(-1).to(a.dtype)
+        ref_loss = (((a - teacher) ** 2) * m).sum() / m.sum().clamp(min=1.0)
+        own = ops.masked_mse(b.reshape(-1, b.shape[-1]), teacher.reshape(-1, b.shape[-1]),
+                             enc["attention_mask"].reshape(-1))
+        assert abs(own.item() - ref_loss.item()) < 1e-3 * abs(ref_loss.item())
