@@ -11,7 +11,8 @@
     invariants of tests/test_packing_collator.py:57-255 checked on both collators;
   * the ProtX student (distillation/models/student/model.py:50-112): same keys, same raw and projected
     embeddings with the reference's weights, same tokenizer ids, same masked-MSE loss as the reference's
-    distillation trainer (distillation/trainer.py:30-40).
+    distillation trainer (distillation/trainer.py:30-40);
+  * batch arithmetic, worker count and run planning (pretraining/utils.py:28-265) for new and resumed runs.
 """
 import os
 import sys
@@ -382,3 +383,64 @@ def test_student_protx_matches_the_reference_student(ref):
         own = ops.masked_mse(b.reshape(-1, b.shape[-1]), teacher.reshape(-1, b.shape[-1]),
                              enc["attention_mask"].reshape(-1))
         assert abs(own.item() - ref_loss.item()) < 1e-3 * abs(ref_loss.item())
+
+
+def test_batch_setup_worker_count_and_run_planning_match(ref, tmp_path, monkeypatch):
+    """`compute_batch_setup`, `get_num_workers` and `prepare_run_and_steps` of the reference
+    (pretraining/utils.py:28-265) against `runtime/run_dirs.py` on a grid of settings, for a new run
+    and for a resume (run directory, W&B name with the resume counter, archived later checkpoints,
+    epochs and clamped step intervals)."""
+    try:
+        from nanoplm.pretraining import utils as ref_utils
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference utils import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.runtime import run_dirs
+    for gbs in (1, 4096, 2 ** 20, 3 * 10 ** 6):
+        for mbs in (1, 8, 64):
+            for seq in (64, 512, 1024):
+                for world in (1, 2, 8):
+                    cfg = types.SimpleNamespace(global_batch_size=gbs, micro_batch_size=mbs)
+                    a = ref_utils.compute_batch_setup(cfg, seq, world)
+                    b = run_dirs.compute_batch_setup(gbs, mbs, seq, world)
+                    assert (a.grad_accum_steps, a.global_batch_size_samples, a.achieved_global_batch_tokens) == \
+                           (b.grad_accum_steps, b.global_batch_size_samples, b.achieved_global_batch_tokens)
+    for value in ("auto", 0, 3, "5"):
+        for world in (1, 4, 8):
+            assert ref_utils.get_num_workers(value, world) == run_dirs.get_num_workers(value, world)
+    for bad in ("many", -1):
+        with pytest.raises(ValueError):
+            ref_utils.get_num_workers(bad, 1)
+        with pytest.raises(ValueError):
+            run_dirs.get_num_workers(bad, 1)
+
+    def both(kind, resume, extra, epochs, log, ev, save, samples, batch):
+        out = []
+        for side in ("ref", "own"):
+            root = tmp_path / f"{kind}-{side}"
+            ck = root / "run-01010101" / "checkpoint-20"
+            if resume:
+                for step in (10, 20, 30, 40):
+                    (root / "run-01010101" / f"checkpoint-{step}").mkdir(parents=True)
+            if side == "ref":
+                pc = types.SimpleNamespace(ckp_dir=str(root), num_epochs=epochs, logging_steps=log, eval_steps=ev,
+                                           save_steps=save)
+                rc = types.SimpleNamespace(is_resume=resume, checkpoint_dir=str(ck), extra_epochs=extra)
+                name, wb, outdir, n_ep, ls, es, ss, rstep = ref_utils.prepare_run_and_steps(pc, rc, samples, batch)
+            else:
+                p = run_dirs.prepare_run_and_steps(str(root), epochs, log, ev, save, resume, str(ck), extra, samples,
+                                                   batch)
+                name, wb, outdir, n_ep, ls, es, ss, rstep = (p.run_name, p.wandb_run_name, p.output_dir, p.num_epochs,
+                                                             p.logging_steps, p.eval_steps, p.save_steps, p.resume_step)
+            rel = Path(outdir).relative_to(root)
+            listing = sorted(str(q.relative_to(root / rel)).split("/")[0].split("_")[0] + ":" + q.name
+                             for q in (root / rel).rglob("checkpoint-*"))
+            out.append((name.startswith("run-"), wb.replace(name, "RUN"), n_ep, ls, es, ss, rstep, listing,
+                        (root / rel / ".resume_counter").read_text() if resume else None))
+        assert out[0] == out[1], (kind, out)
+        return out[0]
+
+    new = both("new", False, None, 3, 10, 5000, 7, 1000, 64)
+    assert new[2:7] == (3, 10, 48, 7, None)                       # 16 steps per epoch, eval clamped to 48
+    res = both("resume", True, 2, 3, 10, 25, 7, 1000, 64)
+    assert res[1] == "RUN-re1" and res[2] == 5 and res[6] == 20
+    assert [x for x in res[7] if x.startswith("archived")] == ["archived:checkpoint-30", "archived:checkpoint-40"]
