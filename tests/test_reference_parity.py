@@ -12,7 +12,8 @@
   * the ProtX student (distillation/models/student/model.py:50-112): same keys, same raw and projected
     embeddings with the reference's weights, same tokenizer ids, same masked-MSE loss as the reference's
     distillation trainer (distillation/trainer.py:30-40);
-  * batch arithmetic, worker count and run planning (pretraining/utils.py:28-265) for new and resumed runs.
+  * batch arithmetic, worker count and run planning (pretraining/utils.py:28-265) for new and resumed runs;
+  * shards written here are read by the reference's `ShardedDataset`, `.data_manifest` files go both ways.
 """
 import os
 import sys
@@ -444,3 +445,41 @@ def test_batch_setup_worker_count_and_run_planning_match(ref, tmp_path, monkeypa
     res = both("resume", True, 2, 3, 10, 25, 7, 1000, 64)
     assert res[1] == "RUN-re1" and res[2] == 5 and res[6] == 20
     assert [x for x in res[7] if x.startswith("archived")] == ["archived:checkpoint-30", "archived:checkpoint-40"]
+
+
+def test_shards_and_manifests_are_read_by_the_reference_and_back(ref, tmp_path):
+    """Shards written by this package's `ShardWriter` are read by the reference's `ShardedDataset`
+    (pretraining/dataset.py:147-290) with identical examples; a `.data_manifest` written by either side is
+    read by the other (data/manifest.py:129-226) with the same fields and dataset paths."""
+    try:
+        from nanoplm.data import manifest as ref_manifest
+        from nanoplm.pretraining import dataset as ref_dataset
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference data modules import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.data import manifest as own_manifest
+    from nanoplm_b200.data.shards import ShardedDataset, ShardWriter
+    from nanoplm_b200.data.synthetic import write_synthetic_fasta
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    write_synthetic_fasta(tmp_path / "x.fasta", 57, 5, 90, seed=3)
+    ShardWriter(tmp_path / "x.fasta", ProtTokenizer(), 64, tmp_path / "train", samples_per_shard=20,
+                max_workers=1).create_shards()
+    theirs, ours = ref_dataset.ShardedDataset(str(tmp_path / "train")), ShardedDataset(str(tmp_path / "train"))
+    assert len(theirs) == len(ours) == 57
+    for i in range(57):
+        a, b = theirs[i], ours[i]
+        assert set(a) == set(b)
+        for k in a:
+            assert torch.equal(torch.as_tensor(a[k]), torch.as_tensor(b[k])), (i, k)
+    fields = dict(pipeline_mode="pretrain", seqs_num=70, min_seq_len=5, max_seq_len=64, val_ratio=0.2,
+                  train_dir="train", val_dir="val", train_sequences=57, val_sequences=13, sharded=True,
+                  samples_per_shard=20)
+    own_manifest.write_manifest(tmp_path / "a", own_manifest.PretrainManifest(**fields))
+    ref_manifest.write_manifest(tmp_path / "b", ref_manifest.PretrainManifest(**fields))
+    for d in ("a", "b"):
+        x, y = ref_manifest.read_manifest(tmp_path / d), own_manifest.read_manifest(tmp_path / d)
+        for k in fields:
+            assert getattr(x, k) == getattr(y, k) == fields[k], (d, k)
+        ref_manifest.validate_manifest_for_pipeline(x, "pretrain")
+        own_manifest.validate_manifest_for_pipeline(y, "pretrain")
+        theirs_p, ours_p = ref_manifest.get_dataset_paths(tmp_path / d, x), own_manifest.get_dataset_paths(tmp_path / d, y)
+        assert {k: str(v) for k, v in theirs_p.items()} == {k: str(v) for k, v in ours_p.items()}
