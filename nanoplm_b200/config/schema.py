@@ -201,6 +201,9 @@ class StudentConfig:
     intermediate_size: int = 1024
     num_hidden_layers: int = 6
     num_attention_heads: int = 8
+    # accepted for the reference's schema; the embedding table is sized from the student
+    # tokenizer, as the reference does (student/model.py:59)
+    vocab_size: int = 32
     mlp_activation: str = "swiglu"
     mlp_dropout: float = 0.0
     mlp_bias: bool = False

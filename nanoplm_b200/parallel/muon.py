@@ -46,8 +46,12 @@ POLAR_EXPRESS = [(a / 1.01, b / 1.01 ** 3, c / 1.01 ** 5) for a, b, c in _PE[:-1
 
 
 def is_embedding_or_unembedding(name: str) -> bool:
+    """Token-embedding and output-head tensors stay on AdamW (reference: optim.py:187-205; the
+    `embed_tokens` / `shared` names cover T5-style tables)."""
     n = name.lower()
-    return any(k in n for k in ("tok_embeddings", "embed_tokens", "word_embeddings", "decoder", "lm_head", "shared"))
+    if n.endswith("decoder.weight") or n.endswith("decoder.bias"):
+        return True
+    return any(k in n for k in ("embedding", "lm_head", "embed_tokens", "shared"))
 
 
 _TILE_GROUPS: dict = {}

@@ -63,6 +63,9 @@ class WarmupLinearSchedule(LambdaSchedule):
 def make_distill_schedule(name: str, base_lr: float, warmup_steps: int, total_steps: int,
                           **kwargs) -> LambdaSchedule:
     name = name.lower()
+    # an explicit warm-up length among the scheduler arguments wins (reference:
+    # distillation/pipeline.py:415-419)
+    warmup_steps = int(kwargs.get("num_warmup_steps", warmup_steps))
 
     def warm(step: int):
         return step / max(1, warmup_steps) if step < warmup_steps else None

@@ -13,7 +13,10 @@
     embeddings with the reference's weights, same tokenizer ids, same masked-MSE loss as the reference's
     distillation trainer (distillation/trainer.py:30-40);
   * batch arithmetic, worker count and run planning (pretraining/utils.py:28-265) for new and resumed runs;
-  * shards written here are read by the reference's `ShardedDataset`, `.data_manifest` files go both ways.
+  * shards written here are read by the reference's `ShardedDataset`, `.data_manifest` files go both ways;
+  * the YAML templates the reference's `get-yaml` commands write load here with the reference's values, and its
+    `params.yaml` drives this package's data pipeline to a dataset the reference's validators accept;
+  * schedules, weight-decay and Muon routing, the FLOP estimate and the Polar-Express iteration.
 """
 import os
 import sys
@@ -483,3 +486,197 @@ def test_shards_and_manifests_are_read_by_the_reference_and_back(ref, tmp_path):
         own_manifest.validate_manifest_for_pipeline(y, "pretrain")
         theirs_p, ours_p = ref_manifest.get_dataset_paths(tmp_path / d, x), own_manifest.get_dataset_paths(tmp_path / d, y)
         assert {k: str(v) for k, v in theirs_p.items()} == {k: str(v) for k, v in ours_p.items()}
+
+
+def _ref_cli_modules():
+    """The reference's cli sub-modules (the names `pretrain`, `distill`, `data` in `nanoplm.cli` are
+    click groups that shadow the modules, hence the look-up through sys.modules)."""
+    try:
+        from nanoplm.cli import cli as ref_cli
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference cli import failed: {type(exc).__name__}: {exc}")
+    return ref_cli, sys.modules["nanoplm.cli.pretrain"], sys.modules["nanoplm.cli.distill"]
+
+
+def test_reference_yaml_templates_load_here_with_the_reference_values(ref, tmp_path, monkeypatch):
+    """The templates written by the reference's own `get-yaml` commands (cli/pretrain.py:594-695,
+    cli/distill.py:540-619) are the schema contract: this package's loaders accept them unchanged and
+    give, field by field, what the reference's loaders give (cli/pretrain.py:704-924,
+    cli/distill.py:629-743)."""
+    import dataclasses
+
+    import yaml
+    from click.testing import CliRunner
+
+    from nanoplm_b200.config import loaders
+    ref_cli, ref_pre, ref_dis = _ref_cli_modules()
+    monkeypatch.chdir(tmp_path)
+    runner = CliRunner()
+    assert runner.invoke(ref_cli, ["pretrain", "get-yaml", "pretrain.yaml"]).exit_code == 0
+    assert runner.invoke(ref_cli, ["distill", "get-yaml", "distill.yaml"]).exit_code == 0
+
+    raw = yaml.safe_load((tmp_path / "pretrain.yaml").read_text())
+    pairs = [(ref_pre._load_model_config(raw["model"]), loaders.load_model_config(raw["model"]), ()),
+             (ref_pre._load_pretrain_config(raw["pretraining"]), loaders.load_pretrain_config(raw["pretraining"]), ()),
+             (ref_pre._load_resume_config(raw["resume"]), loaders.load_resume_config(raw["resume"]), ())]
+    theirs_on, theirs_pt = ref_pre._resolve_pure_torch_config(raw["pure_torch"])
+    ours_on, ours_pt = loaders.resolve_pure_torch_config(raw["pure_torch"])
+    assert theirs_on == ours_on
+    pairs.append((theirs_pt, ours_pt, ()))
+
+    raw = yaml.safe_load((tmp_path / "distill.yaml").read_text())
+    # `sharded: None` means "take it from the manifest" there; here the manifest always decides
+    pairs += [(ref_dis._load_model_config(raw["model"]), loaders.load_student_config(raw["model"]), ()),
+              (ref_dis._load_distill_config(raw["distillation"]), loaders.load_distill_config(raw["distillation"]),
+               ("sharded",)),
+              (ref_dis._load_resume_config(raw["resume"]), loaders.load_resume_config(raw["resume"]), ())]
+    checked = 0
+    for theirs, ours, skip in pairs:
+        for k, v in dataclasses.asdict(theirs).items():
+            if k in skip:
+                continue
+            assert hasattr(ours, k), (type(theirs).__name__, k)
+            assert getattr(ours, k) == v, (type(theirs).__name__, k, v, getattr(ours, k))
+            checked += 1
+    assert checked > 90
+
+    # the error contract of the loaders: same refusals on both sides
+    pre = yaml.safe_load((tmp_path / "pretrain.yaml").read_text())
+    import click
+    for mutate in (lambda d: d["pretraining"].update(gradient_accumulation_steps=2),
+                   lambda d: d["pretraining"].pop("dataset_dir"),
+                   lambda d: d["pretraining"].update(no_such_key=1),
+                   lambda d: d["model"].update(no_such_key=1),
+                   lambda d: d["model"].pop("vocab_size")):
+        bad = {k: dict(v) for k, v in pre.items()}
+        mutate(bad)
+        with pytest.raises((click.ClickException, ValueError)):
+            ref_pre._load_model_config(bad["model"])
+            ref_pre._load_pretrain_config(bad["pretraining"])
+        with pytest.raises(loaders.ConfigError):
+            loaders.load_model_config(bad["model"])
+            loaders.load_pretrain_config(bad["pretraining"])
+
+
+def test_reference_params_template_drives_the_data_pipeline_here(ref, tmp_path, monkeypatch):
+    """`params.yaml` as written by the reference's `data get-yaml` (cli/data.py:676-725), pointed at a
+    local FASTA, runs through this package's `data from-yaml`; the reference's validators then accept
+    the result (data/validation.py:182-354, data/manifest.py:181-274)."""
+    import yaml
+    from click.testing import CliRunner
+
+    from nanoplm_b200.cli import cli as own_cli
+    from nanoplm_b200.data.synthetic import write_synthetic_fasta
+    ref_cli, _, _ = _ref_cli_modules()
+    try:
+        from nanoplm.data import manifest as ref_manifest
+        from nanoplm.data import validation as ref_validation
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference data modules import failed: {type(exc).__name__}: {exc}")
+    monkeypatch.chdir(tmp_path)
+    runner = CliRunner()
+    assert runner.invoke(ref_cli, ["data", "get-yaml", str(tmp_path)]).exit_code == 0
+    params = yaml.safe_load((tmp_path / "params.yaml").read_text())
+    params["data_params"].update(seqs_num=60, min_seq_len=10, max_seq_len=64, val_ratio=0.2)
+    params["pretrain_config"].update(samples_per_shard=20, max_workers=1)
+    params["data_dirs"].update(url="unused", compressed_fasta="raw/x.fasta.gz", extracted_fasta="raw/x.fasta",
+                               shuffled_fasta="raw/x_shuf.fasta", filtered_fasta="raw/x_filt.fasta",
+                               splitted_fasta_dir="raw/split")
+    (tmp_path / "params.yaml").write_text(yaml.safe_dump(params))
+    write_synthetic_fasta(tmp_path / "raw" / "x.fasta", 120, 5, 80, seed=11)
+    r = runner.invoke(own_cli, ["data", "from-yaml", "params.yaml", "--runner", "builtin"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    out = tmp_path / params["pretrain_config"]["output_dir"]
+    m = ref_manifest.read_manifest(out)
+    ref_manifest.validate_manifest_for_pipeline(m, "pretrain")
+    assert (m.train_sequences, m.val_sequences, m.max_seq_len, m.samples_per_shard) == (48, 12, 64, 20)
+    paths = ref_manifest.get_dataset_paths(out, m)
+    res = ref_validation.validate_pretrain_dataset(out)
+    assert len(res["train_shards"]) == 3 and len(res["val_shards"]) == 1
+    assert Path(paths["train_dir"]).is_dir() and Path(paths["val_dir"]).is_dir()
+
+
+def test_schedules_parameter_routing_flops_and_polar_express_match(ref):
+    """The small rules of the training recipe, evaluated by the reference's own functions and by this
+    package's: the warm-up / linear-decay schedule (pure_pipeline.py:150-172) step by step, the four
+    distillation schedules (distillation/pipeline.py:396-446), weight-decay routing
+    (pure_pipeline.py:68-76), Muon / AdamW routing (optim.py:19-60, 187-205), the FLOP estimate
+    (pure_pipeline.py:86-104) and the Polar-Express orthogonalisation (optim.py:85-118)."""
+    import math
+
+    from nanoplm_b200.models.encoder import estimate_flops_per_token
+    from nanoplm_b200.parallel import muon
+    from nanoplm_b200.parallel.engine import use_weight_decay
+    from nanoplm_b200.runtime import schedule
+    P = ref.pipeline
+    # pretraining schedule
+    for total, ratio in ((100, 0.05), (37, 0.1), (10, 3), (1, 0.5), (50, 0.0)):
+        w = P._get_warmup_steps(total, ratio)
+        assert w == schedule.get_warmup_steps(total, ratio)
+        opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.25)
+        theirs = P._create_scheduler(opt, w, total)
+        ours = schedule.WarmupLinearSchedule(0.25, w, total)
+        for _ in range(total + 2):
+            assert math.isclose(theirs.get_last_lr()[0], ours.get_last_lr()[0], rel_tol=1e-12, abs_tol=1e-15)
+            opt.step(); theirs.step(); ours.step()
+        sd = theirs.state_dict()
+        again = schedule.WarmupLinearSchedule(0.25, w, total)
+        again.load_state_dict(sd)
+        assert again.last_epoch == sd["last_epoch"] and math.isclose(again.get_last_lr()[0], theirs.get_last_lr()[0],
+                                                                      abs_tol=1e-15)
+    for n, accum in ((0, 4), (1, 4), (8, 4), (9, 4), (9, 1)):
+        assert P._num_update_steps_per_epoch(n, accum) == schedule.num_update_steps_per_epoch(n, accum)
+
+    # distillation schedules; an explicit num_warmup_steps among the arguments wins on both sides
+    D = sys.modules.get("nanoplm.distillation.pipeline")
+    if D is None:
+        import importlib
+        D = importlib.import_module("nanoplm.distillation.pipeline")
+    for name in ("cosine", "linear", "polynomial", "constant"):
+        for kwargs in ({}, {"num_warmup_steps": 7}):
+            total = 60
+            opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1e-3)
+            theirs = D._get_scheduler(opt, name, dict(kwargs), total)
+            default_warmup = 0 if name == "constant" else int(total * 0.05)
+            ours = schedule.make_distill_schedule(name, 1e-3, default_warmup, total, **kwargs)
+            for _ in range(total + 1):
+                assert math.isclose(theirs.get_last_lr()[0], ours.get_last_lr()[0], rel_tol=1e-9, abs_tol=1e-15), name
+                opt.step(); theirs.step(); ours.step()
+    with pytest.raises(ValueError):
+        D._get_scheduler(opt, "nope", {}, 10)
+    with pytest.raises(ValueError):
+        schedule.make_distill_schedule("nope", 1e-3, 0, 10)
+
+    # routing on the reference's own model
+    rm, om = _pair(ref)
+    O = sys.modules["nanoplm.pretraining.optim"]
+    for name, p in rm.named_parameters():
+        assert P._use_weight_decay(name, p) == use_weight_decay(name, p), name
+        to_muon = p.ndim == 2 and not O._is_embedding_or_unembedding_param(name)
+        ours_muon = p.ndim == 2 and not muon.is_embedding_or_unembedding(name)
+        assert to_muon == ours_muon, name
+    for name in ("lm_head.weight", "x.Embedding.weight", "decoder.bias", "a.unembedding", "layers.0.mlp.Wi.weight"):
+        assert O._is_embedding_or_unembedding_param(name) == muon.is_embedding_or_unembedding(name), name
+
+    cfg = om.config
+    for s in (64, 512, 1024):
+        assert P._estimate_model_flops_per_token(cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size, s,
+                                                 cfg.vocab_size) == estimate_flops_per_token(cfg, s)
+
+    # Polar Express: same coefficients, and the same polar factor as the reference's (bf16) iteration
+    assert len(O.polar_express_coeffs) == len(muon.POLAR_EXPRESS)
+    for x, y in zip(O.polar_express_coeffs, muon.POLAR_EXPRESS):
+        assert all(math.isclose(a, b, rel_tol=1e-15) for a, b in zip(x, y))
+    plain = getattr(O._polar_express_paper, "_torchdynamo_orig_callable", None) or getattr(
+        O._polar_express_paper, "__wrapped__", None)
+    if plain is not None:                       # the undecorated function: no compiler run on the CPU
+        torch.manual_seed(0)
+        for shape in ((48, 96), (96, 48), (64, 64)):
+            G = torch.randn(*shape)
+            theirs = plain(G).float()
+            ours = muon.orthogonalize(G, muon.POLAR_EXPRESS).float()
+            assert ours.shape == theirs.shape
+            # the reference iterates in bf16, this package in fp32 on the CPU: compare as polar factors
+            assert (ours - theirs).norm() / theirs.norm() < 0.03
+            s = torch.linalg.svdvals(ours)
+            assert s.max() < 1.2 and s.min() > 0.5
