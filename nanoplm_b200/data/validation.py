@@ -18,18 +18,44 @@ class ValidationError(Exception):
     pass
 
 
-def validate_pretrain_shards(shard_dir: str | Path, label: str = "shards") -> dict:
+class ShardInfo(dict):
+    """Result of `validate_pretrain_shards`: counts by key (`num_shards`, `num_sequences`) and, like
+    the reference's return value (data/validation.py:182-295), the sorted `.bin` paths when iterated
+    or measured with `len()` / indexed by position."""
+
+    def __init__(self, bins: list[Path], num_sequences: int):
+        super().__init__(num_shards=len(bins), num_sequences=num_sequences)
+        self.paths = list(bins)
+
+    def __iter__(self):
+        return iter(self.paths)
+
+    def __len__(self):
+        return len(self.paths)
+
+    def __getitem__(self, k):
+        return self.paths[k] if isinstance(k, (int, slice)) else dict.__getitem__(self, k)
+
+
+def validate_pretrain_shards(shard_dir: str | Path, expected_count: int | None = None,
+                             check_contents: bool = True, label: str = "shards") -> ShardInfo:
     d = Path(shard_dir)
     if not d.exists():
         raise ValidationError(f"{label} directory not found: {d}")
+    if not d.is_dir():
+        raise ValidationError(f"{label} path is not a directory: {d}")
     bins = sorted(d.glob("*.bin"))
     if not bins:
         raise ValidationError(f"No binary shard files (*.bin) found in {d}")
+    if expected_count is not None and len(bins) != expected_count:
+        raise ValidationError(f"Expected {expected_count} shard files in {d}, found {len(bins)}")
     total = 0
     for b in bins:
         idx = b.with_name(b.stem + ".idx.npy")
         if not idx.exists():
             raise ValidationError(f"Missing index file for shard {b.name}: expected {idx.name}")
+        if not check_contents:
+            continue
         try:
             sizes = np.load(str(idx))
         except Exception as exc:
@@ -41,7 +67,7 @@ def validate_pretrain_shards(shard_dir: str | Path, label: str = "shards") -> di
                 f"Shard {b.name} is corrupt: index sums to {int(sizes.sum())} tokens but the file "
                 f"holds {b.stat().st_size} bytes")
         total += int(sizes.size)
-    return {"num_shards": len(bins), "num_sequences": total}
+    return ShardInfo(bins, total)
 
 
 def validate_pretrain_dataset(dataset_dir: str | Path) -> dict:
@@ -49,13 +75,14 @@ def validate_pretrain_dataset(dataset_dir: str | Path) -> dict:
     manifest = read_manifest(root)
     validate_manifest_for_pipeline(manifest, "pretrain")
     assert isinstance(manifest, PretrainManifest)
-    train = validate_pretrain_shards(root / manifest.train_dir, "Train shard")
-    val = validate_pretrain_shards(root / manifest.val_dir, "Validation shard")
+    train = validate_pretrain_shards(root / manifest.train_dir, label="Train shard")
+    val = validate_pretrain_shards(root / manifest.val_dir, label="Validation shard")
     if train["num_sequences"] != manifest.train_sequences:
         raise ValidationError(
             f"Manifest says {manifest.train_sequences} training sequences but the shards hold "
             f"{train['num_sequences']}")
-    return {"manifest": manifest, "train": train, "val": val}
+    return {"manifest": manifest, "train": train, "val": val,
+            "train_shards": train.paths, "val_shards": val.paths}
 
 
 def _h5_files(directory: Path, prefix: str | None) -> list[Path]:

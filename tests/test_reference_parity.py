@@ -680,3 +680,93 @@ def test_schedules_parameter_routing_flops_and_polar_express_match(ref):
             assert (ours - theirs).norm() / theirs.norm() < 0.03
             s = torch.linalg.svdvals(ours)
             assert s.max() < 1.2 and s.min() > 0.5
+
+
+def test_padding_collator_matches_the_reference_collator(ref):
+    """The padded MLM collator (pretraining/collator.py:7-147): with masking off both give the same
+    padded batch; with masking on both obey the same rules (targets only on residues, original id as
+    label, untouched positions unchanged) and agree on the replacement pool and, within sampling
+    noise, on the selected fraction and the mask / random / keep split."""
+    from nanoplm_b200.data.collators import ProtDataCollatorForLM
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    rt, ot = ref.Tokenizer(), ProtTokenizer()
+    seqs = _sequences(32, 20, 120, seed=5)
+    ex_r = [{"input_ids": torch.tensor(rt.encode(s)), "attention_mask": torch.ones(len(s) + 1, dtype=torch.long)}
+            for s in seqs]
+    ex_o = [{"input_ids": torch.tensor(ot.encode(s)), "attention_mask": torch.ones(len(s) + 1, dtype=torch.long)}
+            for s in seqs]
+    rc = ref.collator.ProtDataCollatorForLM(rt, mlm_probability=0.3, mask_token_probability=6,
+                                            random_token_probability=3, keep_probability=1)
+    oc = ProtDataCollatorForLM(ot, 0.3, mask_token_probability=6, random_token_probability=3, keep_probability=1, seed=4)
+    assert abs(rc.p_mask - oc.p_mask) < 1e-12 and abs(rc.p_rand - oc.p_rand) < 1e-12 and abs(rc.p_keep - oc.p_keep) < 1e-12
+    assert set(rc.allowed_random_token_ids.tolist()) == set(oc.allowed_random_token_ids.tolist())
+    clean = ot.pad(ex_o)["input_ids"]
+    special = torch.tensor(sorted(ot.all_special_ids))
+    stats = []
+    torch.manual_seed(0)
+    for coll, ex in ((rc, ex_r), (oc, ex_o)):
+        sel = n_mask = n_rand_or_keep = n_changed = n_real = 0
+        for _ in range(12):
+            out = coll(ex)
+            ids, lab, att = out["input_ids"], out["labels"], out["attention_mask"]
+            assert ids.dtype == lab.dtype == torch.long and ids.shape == clean.shape
+            assert torch.equal(att.long(), (clean != 0).long())
+            m = lab != -100
+            assert torch.equal(lab[m], clean[m]) and torch.equal(ids[~m], clean[~m])
+            assert not torch.isin(clean[m], special).any()
+            repl = ids[m]
+            assert bool(((repl == 3) | (repl >= 4)).all())
+            sel += int(m.sum()); n_real += int((~torch.isin(clean, special)).sum())
+            n_mask += int((repl == 3).sum())
+            n_changed += int(((repl != 3) & (repl != clean[m])).sum())
+        stats.append((sel / n_real, n_mask / sel, n_changed / sel))
+    (sr, mr, cr), (so, mo, co) = stats
+    assert abs(sr - 0.3) < 0.02 and abs(so - 0.3) < 0.02
+    assert abs(mr - 0.6) < 0.03 and abs(mo - 0.6) < 0.03
+    # a random draw equals the original id once in 28 times
+    assert abs(cr - 0.3 * 27 / 28) < 0.03 and abs(co - 0.3 * 27 / 28) < 0.03
+    off_r = ref.collator.ProtDataCollatorForLM(rt, mlm_probability=0.0)(ex_r)
+    off_o = ProtDataCollatorForLM(ot, 0.0, seed=0)(ex_o)
+    for k in ("input_ids", "attention_mask", "labels"):
+        assert torch.equal(off_r[k].long(), off_o[k].long()), k
+
+
+def test_shard_validation_accepts_and_refuses_the_same_datasets(ref, tmp_path):
+    """`validate_pretrain_shards` / `validate_pretrain_dataset` (data/validation.py:182-354): same
+    arguments, same shard lists for a good dataset, and a refusal from both for a missing index, an
+    index that does not add up to the file size, a wrong shard count and an empty directory."""
+    try:
+        from nanoplm.data import validation as theirs
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference data modules import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.data import validation as ours
+    from nanoplm_b200.data.synthetic import write_synthetic_dataset
+    root = write_synthetic_dataset(tmp_path / "ds", 30, 6, 10, 40, samples_per_shard=10)
+    a, b = theirs.validate_pretrain_dataset(root), ours.validate_pretrain_dataset(root)
+    assert [p.name for p in a["train_shards"]] == [p.name for p in b["train_shards"]] == [
+        "shard_0000.bin", "shard_0001.bin", "shard_0002.bin"]
+    assert [p.name for p in a["val_shards"]] == [p.name for p in b["val_shards"]]
+    assert a["manifest"].train_sequences == b["manifest"].train_sequences == 30
+    got = ours.validate_pretrain_shards(root / "train", expected_count=3, check_contents=True)
+    assert list(got) == theirs.validate_pretrain_shards(root / "train", expected_count=3, check_contents=True)
+    assert len(got) == 3 and got[0].name == "shard_0000.bin" and got["num_sequences"] == 30
+
+    def both_refuse(*args, **kw):
+        with pytest.raises(theirs.ValidationError):
+            theirs.validate_pretrain_shards(*args, **kw)
+        with pytest.raises(ours.ValidationError):
+            ours.validate_pretrain_shards(*args, **kw)
+
+    both_refuse(root / "train", expected_count=4)
+    both_refuse(root / "nowhere")
+    (tmp_path / "empty").mkdir()
+    both_refuse(tmp_path / "empty")
+    (root / "train" / "shard_0001.idx.npy").rename(root / "train" / "hidden.npy")
+    both_refuse(root / "train")
+    (root / "train" / "hidden.npy").rename(root / "train" / "shard_0001.idx.npy")
+    with open(root / "train" / "shard_0002.bin", "ab") as f:
+        f.write(b"\x05\x05")
+    both_refuse(root / "train")
+    # without the content check only the pairing is looked at, on both sides
+    assert len(theirs.validate_pretrain_shards(root / "train", check_contents=False)) == 3
+    assert len(ours.validate_pretrain_shards(root / "train", check_contents=False)) == 3
