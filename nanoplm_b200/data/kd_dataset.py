@@ -133,6 +133,8 @@ class SaveKDDataset:
             self._teacher.to(self.device)
             if self.device.type == "cuda":
                 self._teacher.to(torch.bfloat16)
+        elif hasattr(self._teacher, "encoder_model"):
+            self._teacher = self._teacher.encoder_model      # a `ProtT5`-style wrapper
         return self._teacher
 
     def _shard_path(self, k: Optional[int]) -> Path:

@@ -253,3 +253,78 @@ class T5EncoderTeacher(nn.Module):
         for blk in self.encoder.block:
             x = blk(x, bias)
         return self.encoder.final_layer_norm(x)
+
+
+class BaseTeacher:
+    """What the distillation code needs from a teacher (reference: teacher/base.py:9-29): a
+    tokenizer, an encoder module whose forward gives the last hidden state, and the text
+    preprocessing that goes before tokenisation."""
+
+    def __init__(self, device: Optional[str] = None) -> None:
+        self.device = str(device) if device is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+
+    @property
+    def tokenizer(self):
+        raise NotImplementedError
+
+    @property
+    def encoder_model(self) -> nn.Module:
+        raise NotImplementedError
+
+    def preprocess(self, sequence: str) -> str:
+        raise NotImplementedError
+
+
+class ProtT5(BaseTeacher):
+    """The ProtT5-XL encoder as a teacher (reference: teacher/prott5.py:14-70). `model_name` is a hub
+    id or a local directory with the HF files; `random_init=True` builds the same architecture with
+    seeded random weights (benchmarks, machines without the weights). The encoder is created on
+    first use and cached; on CUDA it runs in bf16 on this package's kernels, no compiler step."""
+
+    def __init__(self, model_name: str = "Rostlab/prot_t5_xl_uniref50", device: Optional[str] = None,
+                 random_init: bool = False, cfg: Optional[TeacherConfig] = None, seed: int = 0):
+        super().__init__(device)
+        self.model_name, self.random_init, self.cfg, self.seed = model_name, random_init, cfg, seed
+        self._encoder_model: Optional[T5EncoderTeacher] = None
+        self._tokenizer: Optional[TeacherTokenizer] = None
+
+    @property
+    def encoder_model(self) -> T5EncoderTeacher:
+        if self._encoder_model is None:
+            if self.random_init:
+                m = T5EncoderTeacher(self.cfg, random_init=True, seed=self.seed)
+            else:
+                m = T5EncoderTeacher.from_pretrained(self.model_name, self.cfg)
+            m = m.to(self.device)
+            if "cuda" in self.device:
+                m = m.to(torch.bfloat16)
+            self._encoder_model = m.eval()
+        return self._encoder_model
+
+    @property
+    def tokenizer(self) -> TeacherTokenizer:
+        if self._tokenizer is None:
+            self._tokenizer = TeacherTokenizer((self.cfg or TeacherConfig()).vocab_size)
+        return self._tokenizer
+
+    def get_layer_weights(self) -> dict:
+        return {k: v.detach() for k, v in self.encoder_model.state_dict().items()}
+
+    def get_layer_by_name(self, layer_name: str) -> torch.Tensor:
+        sd = self.get_layer_weights()
+        if layer_name not in sd:
+            raise ValueError(f"Layer {layer_name} not found in model.")
+        return sd[layer_name]
+
+    def preprocess(self, sequence: str) -> str:
+        return TeacherTokenizer.preprocess(sequence or "")
+
+    @torch.no_grad()
+    def embed(self, sequences: list[str], max_length: Optional[int] = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """(B, S, d_model) last hidden states and the (B, S) attention mask of raw sequences."""
+        enc = self.tokenizer([self.preprocess(s) for s in sequences],
+                             padding="max_length" if max_length else True, max_length=max_length,
+                             truncation=bool(max_length), return_tensors="pt")
+        ids, mask = enc["input_ids"].to(self.device), enc["attention_mask"].to(self.device)
+        out = self.encoder_model(ids, mask, lengths=mask.sum(dim=1).tolist())
+        return out, mask

@@ -121,6 +121,8 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
             teacher = T5EncoderTeacher(cfg.teacher, random_init=True, seed=cfg.seed)
         else:
             teacher = T5EncoderTeacher.from_pretrained(cfg.teacher.name)
+    if teacher is not None and hasattr(teacher, "encoder_model"):
+        teacher = teacher.encoder_model             # a `ProtT5`-style wrapper (reference: teacher/base.py)
     if teacher is not None:
         teacher.to(device)
         if use_bf16:
