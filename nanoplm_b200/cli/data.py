@@ -31,6 +31,14 @@ def data() -> None:
     pass
 
 
+def _make_dirs(path: Path) -> None:
+    """A path with a file extension names a file (its parent is created), any other a directory
+    (reference: utils/common.py:52-59)."""
+    d = Path(path)
+    d = d.parent if d.suffix else d
+    d.mkdir(parents=True, exist_ok=True)
+
+
 def _resolve(p, cwd: Path) -> Path:
     p = Path(p)
     return p if p.is_absolute() else cwd / p
@@ -39,16 +47,28 @@ def _resolve(p, cwd: Path) -> Path:
 # ----------------------------------------------------------------------------------- simple steps
 @data.command("download", help="Download a dataset by key (see --help for keys) or from --url.")
 @click.argument("dataset", required=False)
-@click.option("--url", default=None, help="Explicit download URL (overrides the dataset key).")
-@click.option("-o", "--output", "output", required=True, type=click.Path(path_type=Path))
+@click.option("--url", default=None, help="Explicit download URL (instead of a dataset key).")
+@click.option("-o", "--output", "output", default="downloaded_dataset", show_default=True,
+              type=click.Path(path_type=Path), help="Target file, or a directory (the file keeps the URL's name).")
 @click.option("-f", "--force", is_flag=True, help="Overwrite an existing file.")
 def download(dataset, url, output: Path, force: bool) -> None:
+    if not dataset and not url:
+        raise click.UsageError("Either a dataset key or --url must be provided.")
+    if dataset and url:
+        raise click.UsageError("Both a dataset key and --url cannot be provided.")
     try:
         src = resolve_dataset_url(dataset, url)
     except KeyError as exc:
         raise click.ClickException(str(exc).strip("'\"")) from exc
-    if output.exists() and not force:
-        raise click.ClickException(f"Output already exists: {output}. Use --force to overwrite.")
+    _make_dirs(output)
+    if output.is_dir():
+        output = output / Path(src).name
+    if output.exists():
+        if not force:
+            # the reference reports and leaves with exit code 0 (cli/data.py:96-105)
+            click.echo(f"File already exists: {output} \nUse --force to overwrite.")
+            return
+        output.unlink()
     try:
         Downloader(src, output).download()
     except DownloadError as exc:
@@ -74,7 +94,7 @@ def extract(input_path: Path, output: Path, force: bool) -> None:
 @click.option("-i", "--input", "input_path", required=True, type=click.Path(path_type=Path))
 @click.option("-o", "--output", "output", required=True, type=click.Path(path_type=Path))
 @click.option("--backend", type=click.Choice(["seqkit", "biopython"]), default="biopython")
-@click.option("--seed", type=int, default=24)
+@click.option("--seed", type=int, default=None, help="Random seed (none: a different order every run).")
 def shuffle(input_path: Path, output: Path, backend: str, seed: int) -> None:
     if input_path.suffix != ".fasta":
         raise click.ClickException("Input file must have a .fasta extension")
@@ -89,7 +109,7 @@ def shuffle(input_path: Path, output: Path, backend: str, seed: int) -> None:
 @click.option("-i", "--input", "input_path", required=True, type=click.Path(path_type=Path))
 @click.option("-o", "--output", "output", required=True, type=click.Path(path_type=Path))
 @click.option("--min-seq-len", type=int, default=20)
-@click.option("--max-seq-len", type=int, default=512)
+@click.option("--max-seq-len", type=int, default=1024)
 @click.option("--seqs-num", type=int, default=-1, help="-1 keeps every matching sequence.")
 @click.option("--skip-n", type=int, default=0)
 def filter_cmd(input_path, output, min_seq_len, max_seq_len, seqs_num, skip_n) -> None:
@@ -102,7 +122,8 @@ def filter_cmd(input_path, output, min_seq_len, max_seq_len, seqs_num, skip_n) -
 
 @data.command("split", help="Split a FASTA file into train.fasta and val.fasta.")
 @click.option("-i", "--input", "input_path", required=True, type=click.Path(path_type=Path))
-@click.option("-o", "--output-dir", "output_dir", required=True, type=click.Path(path_type=Path))
+@click.option("-o", "--output", "--output-dir", "output_dir", required=True, type=click.Path(path_type=Path),
+              help="Directory that receives train.fasta and val.fasta.")
 @click.option("--val-ratio", type=float, default=0.1)
 def split(input_path, output_dir, val_ratio) -> None:
     try:
@@ -114,11 +135,11 @@ def split(input_path, output_dir, val_ratio) -> None:
 
 @data.command("save-pretrain-dataset", help="Tokenise a FASTA file into binary shards (.bin + .idx.npy).")
 @click.option("-i", "--input", "input_path", required=True, type=click.Path(path_type=Path))
-@click.option("-o", "--output-dir", "output_dir", required=True, type=click.Path(path_type=Path))
-@click.option("--max-seq-len", type=int, default=512)
+@click.option("-o", "--output", "--output-dir", "output_dir", required=True, type=click.Path(path_type=Path))
+@click.option("--max-seq-len", type=int, default=1024)
 @click.option("--samples-per-shard", type=int, default=10000)
-@click.option("--max-workers", type=int, default=-1)
-@click.option("--force", is_flag=True)
+@click.option("--max-workers", type=int, default=2, help="-1 uses every CPU.")
+@click.option("-f", "--force", is_flag=True)
 def save_pretrain_dataset(input_path, output_dir, max_seq_len, samples_per_shard, max_workers, force) -> None:
     from nanoplm_b200.data.shards import ShardWriter
     from nanoplm_b200.data.tokenizer import ProtTokenizer
@@ -134,23 +155,37 @@ def save_pretrain_dataset(input_path, output_dir, max_seq_len, samples_per_shard
 @click.option("-i", "--input", "input_path", required=True, type=click.Path(path_type=Path))
 @click.option("-o", "--output", "output", required=True, type=click.Path(path_type=Path))
 @click.option("--teacher-model", default="prott5")
-@click.option("--max-seq-len", type=int, default=512)
+@click.option("--max-seq-len", type=int, default=1024)
 @click.option("--batch-size", type=int, default=4)
-@click.option("--device", default="auto")
+@click.option("--device", default="auto", type=click.Choice(["auto", "cuda", "mps", "cpu"]))
 @click.option("--samples-per-shard", type=int, default=-1, help="-1 writes a single file.")
+@click.option("--skip-n", type=int, default=0, help="Skip the first n sequences of the input.")
 @click.option("--teacher-random-init", is_flag=True, help="Random-init teacher (offline machines, tests).")
-@click.option("--force", is_flag=True)
+@click.option("-f", "--force", is_flag=True)
 def save_kd_dataset(input_path, output, teacher_model, max_seq_len, batch_size, device, samples_per_shard,
-                    teacher_random_init, force) -> None:
+                    skip_n, teacher_random_init, force) -> None:
     if teacher_model.lower() != "prott5":
-        raise click.ClickException(f"Unknown teacher model: {teacher_model}. Supported: prott5")
-    if batch_size <= 0 or max_seq_len <= 0:
-        raise click.ClickException("batch-size and max-seq-len must be positive")
-    from nanoplm_b200.data.kd_dataset import SaveKDDataset
+        raise click.ClickException(f"Teacher model {teacher_model} not supported")
+    if samples_per_shard < -1 or samples_per_shard == 0:
+        raise click.ClickException("samples-per-shard must be -1 (no sharding) or a positive number (not 0)")
+    if batch_size < 1:
+        raise click.ClickException("batch-size must be at least 1")
+    if max_seq_len < 1:
+        raise click.ClickException("max-seq-len must be at least 1")
+    if skip_n < 0:
+        raise click.ClickException("skip-n must be at least 0")
+    from nanoplm_b200.data.kd_dataset import SaveKDDataset, have_h5py
+    output = Path(output)
+    _make_dirs(output)
+    if output.is_dir():
+        ext = ".h5" if have_h5py() else ".kdz"
+        output = output / Path(input_path).name.replace(".fasta", "_kd_dataset" + ext)
+    elif output.suffix not in (".h5", ".kdz"):
+        raise click.ClickException("Output must end with .h5 (.kdz without h5py) or be a directory")
     try:
         saver = SaveKDDataset(input_path, output, max_seq_len=max_seq_len, batch_size=batch_size, device=device,
                               samples_per_shard=samples_per_shard, random_init_teacher=teacher_random_init,
-                              force=force)
+                              force=force, skip_n=skip_n)
         files = saver.run()
     except (FileNotFoundError, FileExistsError, ValueError, RuntimeError) as exc:
         raise click.ClickException(str(exc)) from exc
@@ -158,10 +193,11 @@ def save_kd_dataset(input_path, output, teacher_model, max_seq_len, batch_size, 
 
 
 @data.command("shard", help="Split one large KD dataset file into n shards.")
-@click.option("-i", "--input", "input_path", required=True, type=click.Path(path_type=Path))
-@click.option("-n", "--num-shards", "n", required=True, type=int)
+@click.option("-i", "--input-file", "--input", "input_path", required=True, type=click.Path(path_type=Path))
+@click.option("-n", "--n-shards", "--num-shards", "n", required=True, type=int)
 @click.option("-o", "--output-dir", "output_dir", default=None, type=click.Path(path_type=Path))
-@click.option("-t", "--total", default=None, type=int, help="Total number of sequences (skips counting).")
+@click.option("-t", "--total-sequences", "--total", "total", default=None, type=int,
+              help="Total number of sequences (skips counting).")
 def shard(input_path, n, output_dir, total) -> None:
     from nanoplm_b200.data.kd_dataset import shard_h5_file
     try:

@@ -70,7 +70,8 @@ def _o(name, **kw):
 @_o("max_open_files", default=5, type=int)
 @_o("chunk_size", default=32, type=int)
 @_o("prefetch_batches", default=2, type=int)
-@click.option("--use-threading/--no-use-threading", "use_threading", default=True)
+@click.option("--use-threading/--no-threading", "use_threading", default=True)
+@click.option("--no-use-threading", "use_threading", flag_value=False, hidden=True)
 @_o("num_workers", default=8, type=int)
 @_o("project_name", default="nanoplm-distillation", type=str)
 @_o("logging_steps", default=10, type=int)
@@ -94,7 +95,7 @@ def _o(name, **kw):
 @_o("classifier_activation", default="gelu", type=str)
 @click.option("--projection-layer/--no-projection-layer", "projection_layer", default=True)
 @_o("resume_from", default=None, type=str, help="checkpoint-N directory; dataset_dir may be omitted then")
-@_o("extra_epochs", default=None, type=int)
+@_o("extra_epochs", default=0, type=int)
 def run(**kw) -> None:
     model_keys = ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "mlp_activation",
                   "mlp_dropout", "mlp_bias", "attention_bias", "attention_dropout", "classifier_activation",

@@ -59,16 +59,21 @@ def from_yaml(config: Path) -> None:
     except (ConfigError, ValueError) as exc:
         raise click.ClickException(str(exc)) from exc
     if not pure_enabled:
-        # The reference then runs its HF-Trainer pipeline (src/nanoplm/pretraining/pipeline.py:107-295):
-        # padded batches from ProtDataCollatorForLM, checkpoints with model.safetensors and
-        # trainer_state.json. The same recipe on the native pipeline: no packing, and every checkpoint
-        # also carries the two HF files (the native files stay, so either pipeline can resume).
-        import dataclasses
-        pt = dataclasses.replace(pt, use_packing=False)
-        cfg.hf_checkpoint_files = True
-        logger.info("pure_torch.enabled is false: running the reference's HF-Trainer recipe on the native "
-                    "pipeline (padded batches, checkpoints also carry model.safetensors and trainer_state.json).")
+        pt = _hf_trainer_recipe(cfg, pt)
     _launch(model_cfg, cfg, pt, resume)
+
+
+def _hf_trainer_recipe(cfg, pt: PureTorchConfig) -> PureTorchConfig:
+    """With the pure-torch pipeline switched off the reference runs its HF-Trainer pipeline
+    (src/nanoplm/pretraining/pipeline.py:107-295): padded batches from ProtDataCollatorForLM,
+    checkpoints with model.safetensors and trainer_state.json. The same recipe on the native
+    pipeline: no packing, and every checkpoint also carries the two HF files (the native files stay,
+    so either pipeline can resume)."""
+    import dataclasses
+    cfg.hf_checkpoint_files = True
+    logger.info("pure-torch is off: running the reference's HF-Trainer recipe on the native pipeline "
+                "(padded batches, checkpoints also carry model.safetensors and trainer_state.json).")
+    return dataclasses.replace(pt, use_packing=False)
 
 
 @pretrain.command("get-yaml", help="Write a pretraining YAML template.")
@@ -95,7 +100,8 @@ def _opt(name, **kw):
 @_opt("micro_batch_size", default=32, type=int)
 @_opt("global_batch_size", default=2 ** 20, type=int)
 @_opt("num_epochs", default=10, type=int)
-@_opt("warmup_ratio", default=0.05, type=float)
+@click.option("--warmup-ratio", "--adam-warmup-ratio", "warmup_ratio", default=0.05, type=float,
+              help="Warm-up share of the optimizer steps (a value >= 1 is a step count).")
 @_opt("optimizer", default="adamw", type=click.Choice(["adamw", "stable_adamw", "muon", "normuon"]))
 @_opt("adam_beta1", default=0.9, type=float)
 @_opt("adam_beta2", default=0.999, type=float)
@@ -138,8 +144,12 @@ def _opt(name, **kw):
 @_opt("attention_dropout", default=0.0, type=float)
 @_opt("classifier_activation", default="gelu", type=str)
 @_opt("max_position_embeddings", default=1024, type=int)
-@click.option("--pure-torch/--no-pure-torch", "pure_torch", default=True, help="Accepted for compatibility.")
-@click.option("--use-packing/--no-use-packing", "use_packing", default=False)
+@click.option("--pure-torch/--no-pure-torch", "pure_torch", default=True,
+              help="--no-pure-torch runs the HF-Trainer recipe (padded batches, HF files in the checkpoints).")
+@click.option("--compile/--no-compile", "use_compile", default=True,
+              help="Accepted for compatibility: there is no compiler step here.")
+@click.option("--use-packing/--no-packing", "use_packing", default=False)
+@click.option("--no-use-packing", "use_packing", flag_value=False, hidden=True)
 @_opt("target_packed_rows", default=None, type=int)
 @_opt("resume_from", default=None, type=str, help="checkpoint-N directory to resume from")
 @_opt("extra_epochs", default=None, type=int)
@@ -149,8 +159,9 @@ def run(**kw) -> None:
                   "classifier_activation", "max_position_embeddings")
     try:
         model_cfg = ModelConfig(**{k: kw.pop(k) for k in model_keys})
-        kw.pop("pure_torch")
-        pt = PureTorchConfig(use_packing=kw.pop("use_packing"), target_packed_rows=kw.pop("target_packed_rows"))
+        pure_enabled = kw.pop("pure_torch")
+        pt = PureTorchConfig(use_compile=kw.pop("use_compile"), use_packing=kw.pop("use_packing"),
+                             target_packed_rows=kw.pop("target_packed_rows"))
         resume_from, extra = kw.pop("resume_from"), kw.pop("extra_epochs")
         resume = load_resume_config({"is_resume": bool(resume_from), "checkpoint_dir": resume_from or "",
                                      "extra_epochs": extra})
@@ -161,4 +172,6 @@ def run(**kw) -> None:
         cfg = load_pretrain_config(kw)
     except (ConfigError, ValueError) as exc:
         raise click.ClickException(str(exc)) from exc
+    if not pure_enabled:
+        pt = _hf_trainer_recipe(cfg, pt)
     _launch(model_cfg, cfg, pt, resume)

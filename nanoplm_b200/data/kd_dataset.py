@@ -110,8 +110,9 @@ class KDDatasetOnTheFly(IterableDataset):
 class SaveKDDataset:
     def __init__(self, input_fasta, output_path, max_seq_len: int = 512, batch_size: int = 4,
                  device: str = "auto", samples_per_shard: int = -1, teacher=None,
-                 random_init_teacher: bool = False, force: bool = False):
+                 random_init_teacher: bool = False, force: bool = False, skip_n: int = 0):
         self.input_fasta, self.output_path = Path(input_fasta), Path(output_path)
+        self.skip_n = max(0, int(skip_n))
         if not self.input_fasta.exists():
             raise FileNotFoundError(f"FASTA file not found: {self.input_fasta}")
         self.max_seq_len, self.batch_size = int(max_seq_len), int(batch_size)
@@ -165,7 +166,7 @@ class SaveKDDataset:
             f.unlink()
         teacher = self._get_teacher()
         L = self.max_seq_len
-        seqs = [s for _, s in iter_fasta(self.input_fasta)]
+        seqs = [s for _, s in iter_fasta(self.input_fasta)][self.skip_n:]
         files, ids_buf, mask_buf, emb_buf, shard = [], [], [], [], 0
 
         def flush(final: bool):

@@ -14,6 +14,7 @@ import ssl
 import subprocess
 import urllib.request
 from pathlib import Path
+from typing import Optional
 
 from .fasta import FastaIndex, iter_fasta, write_fasta
 
@@ -85,10 +86,12 @@ class FastaShuffler:
     """Shuffles the records of a FASTA file. backend "biopython" is the in-process path (kept under
     that name for CLI compatibility); "seqkit" shells out to the external binary."""
 
-    def __init__(self, input_path, output_path, backend: str = "biopython", seed: int = 24,
+    def __init__(self, input_path, output_path, backend: str = "biopython", seed: Optional[int] = 24,
                  threads: int = 4):
         self.input_path, self.output_path = Path(input_path), Path(output_path)
-        self.backend, self.seed, self.threads = backend, seed, threads
+        # no seed: one is drawn and kept, as the reference does (data/shuffler.py:40)
+        self.seed = int(seed) if seed else random.randint(1, 1000)
+        self.backend, self.threads = backend, threads
 
     def shuffle(self) -> Path:
         if not self.input_path.exists():

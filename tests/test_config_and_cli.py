@@ -159,3 +159,64 @@ def test_cli_distillation_on_the_fly(tmp_path, monkeypatch):
     lines = [json.loads(l) for l in (run / "metrics.jsonl").read_text().splitlines()]
     train = [l["train/loss"] for l in lines if "train/loss" in l]
     assert train[-1] < train[0]
+
+
+def test_cli_data_single_steps_with_the_reference_option_spellings(tmp_path, monkeypatch):
+    """The single-step `data` commands with the option names, defaults and output conventions of the
+    reference CLI (cli/data.py:34-625): a directory as download target, "already exists" reported
+    with exit code 0, `--output` for split / save-pretrain-dataset, a directory and `--skip-n` for
+    save-kd-dataset, `--input-file / --n-shards / --total-sequences` for shard."""
+    import gzip
+    monkeypatch.chdir(tmp_path)
+    runner = CliRunner()
+    src = write_synthetic_fasta(tmp_path / "src" / "mini.fasta", 40, 12, 60, seed=2)
+    with open(src, "rb") as f, gzip.open(tmp_path / "src" / "mini.fasta.gz", "wb") as g:
+        g.write(f.read())
+    url = (tmp_path / "src" / "mini.fasta.gz").as_uri()
+
+    r = runner.invoke(cli, ["data", "download", "--url", url])                     # default: ./downloaded_dataset/
+    assert r.exit_code == 0, r.output
+    got = tmp_path / "downloaded_dataset" / "mini.fasta.gz"
+    assert got.read_bytes() == (tmp_path / "src" / "mini.fasta.gz").read_bytes()
+    r = runner.invoke(cli, ["data", "download", "--url", url])
+    assert r.exit_code == 0 and "already exists" in r.output
+    assert runner.invoke(cli, ["data", "download", "--url", url, "-f", "-o", "downloaded_dataset"]).exit_code == 0
+    assert runner.invoke(cli, ["data", "download", "swissprot", "--url", url]).exit_code == 2
+    assert runner.invoke(cli, ["data", "download"]).exit_code == 2
+    assert runner.invoke(cli, ["data", "download", "-h"]).exit_code == 0
+
+    assert runner.invoke(cli, ["data", "extract", "-i", str(got), "-o", "raw/mini.fasta"]).exit_code == 0
+    assert runner.invoke(cli, ["data", "shuffle", "-i", "raw/mini.fasta", "-o", "raw/shuf.fasta"]).exit_code == 0
+    r = runner.invoke(cli, ["data", "filter", "-i", "raw/shuf.fasta", "-o", "raw/filt.fasta", "--min-seq-len", "15"])
+    assert r.exit_code == 0, r.output
+    r = runner.invoke(cli, ["data", "split", "-i", "raw/filt.fasta", "--output", "split", "--val-ratio", "0.25"])
+    assert r.exit_code == 0 and (tmp_path / "split" / "train.fasta").exists() and (tmp_path / "split" / "val.fasta").exists()
+    r = runner.invoke(cli, ["data", "save-pretrain-dataset", "-i", "split/train.fasta", "--output", "shards/train",
+                            "--samples-per-shard", "10", "--max-seq-len", "64"])
+    assert r.exit_code == 0, r.output
+    assert len(list((tmp_path / "shards" / "train").glob("*.bin"))) >= 2
+    assert runner.invoke(cli, ["data", "save-pretrain-dataset", "-i", "split/train.fasta", "--output", "shards/train",
+                               "--max-seq-len", "64"]).exit_code != 0          # exists: needs -f
+    assert runner.invoke(cli, ["data", "save-pretrain-dataset", "-i", "split/train.fasta", "--output", "shards/train",
+                               "--max-seq-len", "64", "-f"]).exit_code == 0
+
+    from nanoplm_b200.data.fasta import count_fasta
+    from nanoplm_b200.data.kd_dataset import count_kd_sequences
+    n_val = count_fasta(tmp_path / "split" / "val.fasta")
+    # the tiny random teacher of the tests instead of the 1.2 B parameter default
+    from nanoplm_b200.config.schema import TeacherConfig
+    from nanoplm_b200.models import teacher as teacher_mod
+    small = TeacherConfig(d_model=32, d_kv=8, d_ff=64, num_layers=1, num_heads=4)
+    monkeypatch.setattr(teacher_mod.T5EncoderTeacher.__init__, "__defaults__", (small, True, 0))
+    r = runner.invoke(cli, ["data", "save-kd-dataset", "-i", "split/val.fasta", "-o", "kd", "--max-seq-len", "64",
+                            "--skip-n", "2", "--teacher-random-init", "--device", "cpu"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    files = sorted((tmp_path / "kd").glob("val_kd_dataset.*"))
+    assert len(files) == 1 and count_kd_sequences(files[0]) == n_val - 2
+    assert runner.invoke(cli, ["data", "save-kd-dataset", "-i", "split/val.fasta", "-o", "kd/x.txt"]).exit_code != 0
+    assert runner.invoke(cli, ["data", "save-kd-dataset", "-i", "split/val.fasta", "-o", "kd", "--samples-per-shard",
+                               "0"]).exit_code != 0
+    r = runner.invoke(cli, ["data", "shard", "--input-file", str(files[0]), "--n-shards", "2", "-o", "kd_parts",
+                            "--total-sequences", str(n_val - 2)])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    assert sum(count_kd_sequences(p) for p in (tmp_path / "kd_parts").iterdir()) == n_val - 2
