@@ -280,10 +280,12 @@ class ProtEncoderMLM(nn.Module):
         for layer in self.model.layers:
             nn.init.uniform_(layer.attn.Wqkv.weight, -bound, bound)
             nn.init.zeros_(layer.attn.Wo.weight)
+            lins = [layer.attn.Wqkv, layer.attn.Wo]
             if isinstance(layer.mlp, MLP):
                 nn.init.uniform_(layer.mlp.Wi.weight, -bound, bound)
                 nn.init.zeros_(layer.mlp.Wo.weight)
-            for lin in (layer.attn.Wqkv, layer.attn.Wo):
+                lins += [layer.mlp.Wi, layer.mlp.Wo]
+            for lin in lins:
                 if lin.bias is not None:
                     nn.init.zeros_(lin.bias)
         nn.init.uniform_(self.head.dense.weight, -bound, bound)

@@ -825,3 +825,28 @@ def test_cli_commands_options_and_defaults_cover_the_reference_cli(ref):
             assert a == b or (isinstance(a, float) and abs(a - b) < 1e-12), (path, flag, a, b)
             assert bool(p.required) == bool(q.required), (path, flag)
     assert seen > 150
+
+
+def test_initialisation_follows_the_reference_distributions(ref):
+    """`init_weights` (modeling.py:581-623): N(0, 0.02) embeddings, ones in the norms, U(+-sqrt(3/h))
+    for Wqkv / Wi / head.dense, zeros for both output projections and every bias. Different random
+    streams, so each tensor is compared by its statistics."""
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    geom = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=2,
+                max_position_embeddings=256, mlp_bias=True, attention_bias=True)
+    torch.manual_seed(1)
+    theirs = ref.Model(ref.Config(**geom)).state_dict()
+    torch.manual_seed(2)
+    ours = ProtEncoderMLM(ModelConfig(**geom)).state_dict()
+    assert set(theirs) == set(ours)
+    for k, a in theirs.items():
+        a, b = a.float(), ours[k].float()
+        assert a.shape == b.shape, k
+        if float(a.abs().max()) == 0.0 or float(a.std()) == 0.0:        # zeros / ones: exact
+            assert torch.equal(a, b), k
+            continue
+        assert abs(float(a.std()) - float(b.std())) < 0.08 * float(a.std()) + 1e-4, (k, float(a.std()), float(b.std()))
+        assert abs(float(a.mean()) - float(b.mean())) < 0.2 * float(a.std()), k
+        if "tok_embeddings" not in k and "decoder" not in k:             # uniform tensors: same support
+            assert abs(float(a.abs().max()) - float(b.abs().max())) < 0.02 * float(a.abs().max()), k
