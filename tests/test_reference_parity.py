@@ -16,7 +16,9 @@
   * shards written here are read by the reference's `ShardedDataset`, `.data_manifest` files go both ways;
   * the YAML templates the reference's `get-yaml` commands write load here with the reference's values, and its
     `params.yaml` drives this package's data pipeline to a dataset the reference's validators accept;
-  * schedules, weight-decay and Muon routing, the FLOP estimate and the Polar-Express iteration.
+  * schedules, weight-decay and Muon routing, the FLOP estimate and the Polar-Express iteration;
+  * the padded MLM collator, the shard validators, the initialisation, every command / option / default of
+    the CLI, and ten optimizer steps of the reference's recipe step by step.
 """
 import os
 import sys
@@ -850,3 +852,57 @@ def test_initialisation_follows_the_reference_distributions(ref):
         assert abs(float(a.mean()) - float(b.mean())) < 0.2 * float(a.std()), k
         if "tok_embeddings" not in k and "decoder" not in k:             # uniform tensors: same support
             assert abs(float(a.abs().max()) - float(b.abs().max())) < 0.02 * float(a.abs().max()), k
+
+
+def test_training_trajectory_follows_the_reference_recipe(ref):
+    """Ten optimizer steps of the reference's recipe, its own pieces on one side (model,
+    `_create_optimizer`, `_create_scheduler`, gradient accumulation, clip to 1.0:
+    pure_pipeline.py:107-160, 700-790) and this package's on the other (encoder, sharded AdamW engine,
+    schedule), from the same weights on the same masked batches: the losses and the gradient norms
+    agree step by step and the weights agree at the end."""
+    from nanoplm_b200.config.schema import PretrainingConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import schedule
+    P = ref.pipeline
+    rm, om = _pair(ref)
+    rm.train(); om.train()
+    cfg = PretrainingConfig(dataset_dir="unused", adam_learning_rate=2e-3, adam_weight_decay=0.05, warmup_ratio=0.2)
+    opt = P._create_optimizer(rm, cfg)
+    assert [g["weight_decay"] for g in opt.param_groups] == [0.05, 0.0]
+    steps, accum = 10, 2
+    warm = P._get_warmup_steps(steps, cfg.warmup_ratio)
+    sched_r = P._create_scheduler(opt, warm, steps)
+    sched_o = schedule.WarmupLinearSchedule(cfg.adam_learning_rate, schedule.get_warmup_steps(steps, cfg.warmup_ratio), steps)
+    eng = ShardedEngine(om, AdamWHyper(lr=cfg.adam_learning_rate, beta1=cfg.adam_beta1, beta2=cfg.adam_beta2,
+                                       eps=cfg.adam_epsilon, weight_decay=cfg.adam_weight_decay, max_grad_norm=1.0),
+                        torch.device("cpu"))
+    rt = ref.Tokenizer()
+    coll = ref.collator.ProtDataCollatorForLM(rt, mlm_probability=0.3)
+    torch.manual_seed(3)
+    batches = []
+    for i in range(steps * accum):
+        seqs = _sequences(6, 10, 70, seed=100 + i)
+        batches.append(coll([{"input_ids": torch.tensor(rt.encode(s)),
+                              "attention_mask": torch.ones(len(s) + 1, dtype=torch.long)} for s in seqs]))
+    for step in range(steps):
+        loss_r = loss_o = 0.0
+        for k in range(accum):
+            b = batches[step * accum + k]
+            out = rm(input_ids=b["input_ids"], attention_mask=b["attention_mask"], labels=b["labels"])
+            (out["loss"] / accum).backward()
+            loss_r += float(out["loss"].detach()) / accum
+            out = om(input_ids=b["input_ids"], attention_mask=b["attention_mask"], labels=b["labels"])
+            out["loss"].backward()
+            loss_o += float(out["loss"].detach()) / accum
+        gn_r = float(torch.nn.utils.clip_grad_norm_(rm.parameters(), max_norm=1.0))
+        opt.step(); sched_r.step(); opt.zero_grad(set_to_none=True)
+        lr = sched_o.get_last_lr()[0]
+        gn_o = float(eng.step(lr, grad_accum=accum))
+        sched_o.step()
+        assert abs(loss_r - loss_o) < 2e-4 * max(1.0, abs(loss_r)), (step, loss_r, loss_o)
+        assert abs(gn_r - gn_o) < 1e-3 * gn_r, (step, gn_r, gn_o)
+        assert abs(sched_r.get_last_lr()[0] - sched_o.get_last_lr()[0]) < 1e-12
+    theirs, ours = rm.state_dict(), om.state_dict()
+    worst = max(float((theirs[k].float() - ours[k].float()).abs().max()) for k in theirs)
+    assert worst < 5e-4, worst
