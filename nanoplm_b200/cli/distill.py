@@ -103,18 +103,32 @@ def run(**kw) -> None:
     try:
         model_cfg = load_student_config({k: kw.pop(k) for k in model_keys})
         resume_from, extra = kw.pop("resume_from"), kw.pop("extra_epochs")
+        explicit_paths = False
         if resume_from and not kw.get("dataset_dir"):
-            # recover the dataset location from the run's training_config.json
+            # recover the dataset location from the run's training_config.json: the dataset directory
+            # when the file was written here, else the explicit paths the reference stores
+            # (cli/distill.py:303-337, 406-425)
+            if not Path(resume_from).exists():
+                raise ConfigError(f"Resume checkpoint directory does not exist: {resume_from}")
             tc = Path(resume_from).parent / "training_config.json"
-            if tc.exists():
-                kw["dataset_dir"] = json.loads(tc.read_text()).get("distillation", {}).get("dataset_dir")
+            if not tc.exists():
+                raise ConfigError(f"Cannot resume without --dataset-dir: training_config.json not found in "
+                                  f"{tc.parent}\nPlease provide --dataset-dir explicitly.")
+            saved = json.loads(tc.read_text())
+            kw["dataset_dir"] = (saved.get("distillation") or {}).get("dataset_dir")
+            if not kw["dataset_dir"]:
+                explicit_paths = True
+                for k in ("train_fasta", "val_fasta", "train_h5_prefix", "val_h5_prefix", "max_seq_len",
+                          "max_seqs_num", "val_ratio", "on_the_fly", "sharded", "train_sequences", "val_sequences"):
+                    v = saved.get(k)
+                    kw[k] = None if v in (None, "None", "null") else v
         if kw.get("lr_scheduler_kwargs"):
             kw["lr_scheduler_kwargs"] = json.loads(kw["lr_scheduler_kwargs"])
         else:
             kw.pop("lr_scheduler_kwargs")
         ws = kw["world_size"]
         kw["world_size"] = ws if ws == "auto" else int(ws)
-        cfg = load_distill_config(kw)
+        cfg = load_distill_config(kw, require_dataset_dir=not explicit_paths)
         resume = load_resume_config({"is_resume": bool(resume_from), "checkpoint_dir": resume_from or "",
                                      "extra_epochs": extra})
     except (ConfigError, ValueError, json.JSONDecodeError) as exc:

@@ -187,11 +187,11 @@ def load_student_config(section: Optional[Mapping[str, Any]]) -> StudentConfig:
     return StudentConfig(**_coerce(StudentConfig, kwargs))
 
 
-def load_distill_config(section: Optional[Mapping[str, Any]]) -> DistillationConfig:
+def load_distill_config(section: Optional[Mapping[str, Any]], require_dataset_dir: bool = True) -> DistillationConfig:
     if section is None:
         raise ConfigError("Distillation configuration is required but not found in YAML")
     cfg = dict(section)
-    if not cfg.get("dataset_dir"):
+    if require_dataset_dir and not cfg.get("dataset_dir"):
         raise ConfigError("dataset_dir is required in distillation configuration. Run "
                           "'nanoplm data from-yaml' first to prepare the dataset.")
     known = field_names(DistillationConfig)

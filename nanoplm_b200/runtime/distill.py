@@ -74,7 +74,30 @@ def distillation_loss(student: ProtX, batch: dict, teacher=None) -> torch.Tensor
     return ops.masked_mse(out.reshape(B * S, D), target.reshape(B * S, D).to(out.dtype), mask.reshape(-1))
 
 
+REFERENCE_TRAINING_CONFIG_KEYS = (
+    "train_fasta", "val_fasta", "train_h5_prefix", "val_h5_prefix", "num_epochs", "batch_size", "learning_rate",
+    "gradient_accumulation_steps", "lr_scheduler", "lr_scheduler_kwargs", "max_seq_len", "max_seqs_num",
+    "val_ratio", "on_the_fly", "sharded", "project_name")
+
+
 def resolve_config_from_manifest(cfg: DistillationConfig) -> DistillationConfig:
+    """Dataset location and geometry from `<dataset_dir>/.data_manifest`
+    (reference: distillation/pipeline.py:149-340). Without a dataset directory the explicit paths of
+    the configuration are used, which is how a run resumed through its `training_config.json`
+    arrives (reference: cli/distill.py:406-425)."""
+    if not cfg.dataset_dir:
+        need = ("train_fasta", "val_fasta") if cfg.on_the_fly else ("train_h5_prefix", "val_h5_prefix")
+        missing = [k for k in need if not getattr(cfg, k)]
+        if missing or not cfg.max_seq_len:
+            raise ValueError("dataset_dir is required unless " + ", ".join(need) + " and max_seq_len are given")
+        if not cfg.train_sequences:
+            if cfg.on_the_fly:
+                from nanoplm_b200.data.fasta import count_fasta
+                cfg.train_sequences, cfg.val_sequences = count_fasta(cfg.train_fasta), count_fasta(cfg.val_fasta)
+            else:
+                cfg.train_sequences = len(LoadKDDataset(cfg.train_h5_prefix))
+                cfg.val_sequences = len(LoadKDDataset(cfg.val_h5_prefix))
+        return cfg
     info = validate_distillation_dataset(cfg.dataset_dir)
     m: DistillationManifest = info["manifest"]
     paths = get_dataset_paths(cfg.dataset_dir, m)
@@ -188,7 +211,10 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
         logger.info(f"Resumed distillation at step {global_step}")
     if is_main:
         (out_dir / "training_config.json").write_text(json.dumps(
-            {"model": as_plain_dict(model_config), "distillation": as_plain_dict(cfg),
+            # the reference's flat keys (distillation/pipeline.py:557-576) first, then the full sections
+            {**{k: getattr(cfg, k) for k in REFERENCE_TRAINING_CONFIG_KEYS},
+             "train_sequences": cfg.train_sequences, "val_sequences": cfg.val_sequences,
+             "model": as_plain_dict(model_config), "distillation": as_plain_dict(cfg),
              "total_steps": total_steps, "warmup_steps": warmup}, indent=2, default=str), encoding="utf-8")
     sink = MetricsSink(str(out_dir), cfg.project_name, plan.wandb_run_name, as_plain_dict(cfg), is_main)
 

@@ -160,6 +160,29 @@ def test_cli_distillation_on_the_fly(tmp_path, monkeypatch):
     train = [l["train/loss"] for l in lines if "train/loss" in l]
     assert train[-1] < train[0]
 
+    # `distill run --resume-from` without --dataset-dir: the dataset comes back from the run's
+    # training_config.json, here reduced to the flat keys the reference writes
+    # (distillation/pipeline.py:557-576, cli/distill.py:406-425)
+    from nanoplm_b200.config import schema
+    from nanoplm_b200.runtime.distill import REFERENCE_TRAINING_CONFIG_KEYS
+    saved = json.loads((run / "training_config.json").read_text())
+    assert all(k in saved for k in REFERENCE_TRAINING_CONFIG_KEYS) and saved["on_the_fly"] is True
+    flat = {k: saved[k] for k in REFERENCE_TRAINING_CONFIG_KEYS}
+    flat["train_h5_prefix"] = flat["val_h5_prefix"] = "None"
+    (run / "training_config.json").write_text(json.dumps(flat))
+    monkeypatch.setattr(schema.TeacherConfig.__init__, "__defaults__",
+                        (128, 1024, 16, 64, 1, 4, 32, 128, 1e-6, "tiny-random"))
+    args = ["distill", "run", "--resume-from", str(run / "checkpoint-6"), "--extra-epochs", "1", "--ckp-dir", "dckpt",
+            "--num-epochs", "2", "--batch-size", "8", "--logging-steps", "1", "--eval-steps", "4", "--save-steps", "6",
+            "--no-bf16", "--teacher-random-init", "--hidden-size", "64", "--intermediate-size", "128",
+            "--num-hidden-layers", "2", "--num-attention-heads", "2", "--no-threading"]
+    r = runner.invoke(cli, args)
+    assert r.exit_code == 0, r.output + str(r.exception)
+    assert (run / "checkpoint-18").exists() and (run / ".resume_counter").read_text() == "1"
+    (run / "training_config.json").unlink()
+    r = runner.invoke(cli, args)
+    assert r.exit_code != 0 and "training_config.json not found" in r.output
+
 
 def test_cli_data_single_steps_with_the_reference_option_spellings(tmp_path, monkeypatch):
     """The single-step `data` commands with the option names, defaults and output conventions of the
