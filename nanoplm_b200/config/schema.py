@@ -20,7 +20,10 @@ class MoEConfig:
     expert_intermediate_size: int = 512
     every_n_layers: int = 2              # layers with (index % every_n_layers == every_n_layers-1) use experts
     aux_loss_coef: float = 0.01
-    capacity_factor: float = 0.0         # 0 = no token dropping
+    # expert parallelism: rows a rank's receive buffers hold, as a multiple of its even share.
+    # 0 = automatic: the worst case (nothing dropped) up to 4 ranks, 4 shares beyond; rows that do not
+    # fit are dropped and counted (train/moe_dropped_rows). Without expert parallelism nothing is dropped.
+    capacity_factor: float = 0.0
 
     @property
     def enabled(self) -> bool:

@@ -54,6 +54,7 @@ class MoEMLP(nn.Module):
         m = cfg.moe
         self.num_experts, self.top_k = m.num_experts, m.top_k
         self.inter = m.expert_intermediate_size
+        self.capacity_factor = float(m.capacity_factor or 0.0)
         self.hidden = cfg.hidden_size
         self.ep_group = ep_group
         self.ep_world = 1
@@ -115,7 +116,8 @@ class MoEMLP(nn.Module):
         if self._use_device_path(x):
             from nanoplm_b200.ops import moe as M
             if self._comm is None:
-                self._comm = M.MoEComm(self.hidden, self.num_experts, self.top_k, group=self.ep_group)
+                self._comm = M.MoEComm(self.hidden, self.num_experts, self.top_k, group=self.ep_group,
+                                       capacity_factor=self.capacity_factor)
             logits = ops.linear(x, self.router.weight)
             return M.moe_mlp(x, logits, self.experts_Wi, self.experts_Wo, self.top_k, self._comm)
         logits = F.linear(x, self.router.weight)

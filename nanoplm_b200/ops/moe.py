@@ -122,7 +122,7 @@ class MoEComm:
     buffers of `capacity_rows` rows, the count table and the barrier flags live in symmetric memory
     (allocated once, identical on every rank of `group`)."""
 
-    def __init__(self, hidden: int, num_experts: int, top_k: int, group=None, capacity_factor: float = 2.0,
+    def __init__(self, hidden: int, num_experts: int, top_k: int, group=None, capacity_factor: float = 0.0,
                  barrier_timeout_s: float = 20.0):
         self.C, self.E, self.k = hidden, num_experts, top_k
         self.group = group
@@ -133,7 +133,12 @@ class MoEComm:
         if self.E % self.world:
             raise ValueError("num_experts must be divisible by the expert-parallel size")
         self.El = self.E // self.world
-        self.capacity_factor = capacity_factor
+        # rows a rank's buffers hold, in units of its even share of the assignments. `world` is the
+        # worst case (every row of every rank lands here: nothing can be dropped); 0 picks that up to
+        # four shares, which bounds the buffers at 8 and more ranks, where rows past them are
+        # dropped and counted
+        self.capacity_factor = float(capacity_factor) if capacity_factor and capacity_factor > 0 else float(
+            min(max(self.world, 1), 4))
         self.timeout = barrier_timeout_s
         self.epoch = 0
         self._sym = None
