@@ -1,6 +1,9 @@
 """Host-side data pipeline throughput: shard reading, packing collators, balanced sampler.
 
-    python -m nanoplm_b200.bench.data_bench [--sequences 40000] [--workers 0,4]
+    python -m nanoplm_b200.bench.data_bench [--sequences 40000] [--workers 0,4] [--impl reference]
+
+`--impl reference` times the reference package's own `ShardedDataset`, `PackingCollator` and
+`ProtDataCollatorForLM` (imported unmodified from `baseline/_ref`) on the same shards.
 
 Counterpart of the reference's loading micro-benchmark (tests/shm_loading_benchmark.py:202-271 times how
 fast its HDF5 shards get into shared memory; its shards are memory-mapped `.bin` + `.idx.npy` files here,
@@ -43,6 +46,40 @@ def _write_dataset(root: Path, n: int, lo: int, hi: int, seed: int) -> int:
     return total
 
 
+def _import_reference():
+    """The reference's data classes from baseline/_ref, or the reason they cannot be imported."""
+    import os
+    import sys
+    import types
+    ref_dir = Path(__file__).resolve().parents[2] / "baseline" / "_ref"
+    if not (ref_dir / "nanoplm").exists():
+        return "reference package not installed under baseline/_ref"
+    for name, attrs in (("IPython", {"get_ipython": lambda: None}), ("h5py", {"File": object}), ("Bio", {}),
+                        ("Bio.SeqIO", {})):
+        try:
+            __import__(name)
+        except Exception:
+            m = types.ModuleType(name)
+            for k, v in attrs.items():
+                setattr(m, k, v)
+            sys.modules[name] = m
+    if isinstance(sys.modules.get("Bio"), types.ModuleType) and not hasattr(sys.modules["Bio"], "SeqIO"):
+        sys.modules["Bio"].SeqIO = sys.modules["Bio.SeqIO"]
+    sys.path.insert(0, str(ref_dir))
+    cwd = os.getcwd()
+    os.chdir(tempfile.mkdtemp())           # the reference opens a log file in the current directory on import
+    try:
+        from nanoplm.pretraining.collator import PackingCollator, ProtDataCollatorForLM
+        from nanoplm.pretraining.dataset import ShardedDataset
+        from nanoplm.pretraining.models.modern_bert.tokenizer import ProtModernBertTokenizer
+    except Exception as exc:
+        return f"reference import failed: {type(exc).__name__}: {exc}"
+    finally:
+        os.chdir(cwd)
+    return {"PackingCollator": PackingCollator, "ProtDataCollatorForLM": ProtDataCollatorForLM,
+            "ShardedDataset": ShardedDataset, "Tokenizer": ProtModernBertTokenizer}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--sequences", type=int, default=40000)
@@ -51,14 +88,23 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=208, help="sequences per micro-batch (the benchmark's 208)")
     ap.add_argument("--rows", type=int, default=128, help="packed rows per micro-batch")
     ap.add_argument("--workers", default="0,4", help="DataLoader worker counts to time")
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
     args = ap.parse_args()
 
-    from nanoplm_b200.data.collators import PackingCollator, ProtDataCollatorForLM
     from nanoplm_b200.data.sampler import BalancedBatchSampler
-    from nanoplm_b200.data.shards import ShardedDataset
-    from nanoplm_b200.data.tokenizer import ProtTokenizer
-
-    tok = ProtTokenizer()
+    if args.impl == "reference":
+        ref = _import_reference()
+        if isinstance(ref, str):
+            print(json.dumps({"impl": "reference", "unavailable": ref}))
+            return
+        ShardedDataset, tok = ref["ShardedDataset"], ref["Tokenizer"]()
+        PackingCollator = lambda t, w, p, seed=0, **kw: ref["PackingCollator"](t, w, mlm_probability=p, **kw)  # noqa: E731
+        ProtDataCollatorForLM = lambda t, p, seed=0: ref["ProtDataCollatorForLM"](t, mlm_probability=p)  # noqa: E731
+    else:
+        from nanoplm_b200.data.collators import PackingCollator, ProtDataCollatorForLM
+        from nanoplm_b200.data.shards import ShardedDataset
+        from nanoplm_b200.data.tokenizer import ProtTokenizer
+        tok = ProtTokenizer()
     with tempfile.TemporaryDirectory() as tmp:
         root = Path(tmp)
         t0 = time.perf_counter()
@@ -72,7 +118,7 @@ def main() -> None:
         for i in range(len(ds)):
             n_tok += int(ds[i]["input_ids"].numel())
         dt = time.perf_counter() - t0
-        print(json.dumps({"bench": "read_every_sequence", "sequences": len(ds), "tokens": n_tok,
+        print(json.dumps({"bench": "read_every_sequence", "impl": args.impl, "sequences": len(ds), "tokens": n_tok,
                           "sequences_per_s": round(len(ds) / dt), "tokens_per_s": round(n_tok / dt)}), flush=True)
 
         # a B200 running the default encoder consumes about 760 K real tokens per second
@@ -92,9 +138,14 @@ def main() -> None:
                 nb = real = 0
                 for b in it:
                     nb += 1
-                    real += int(b["num_real_tokens"]) if "num_real_tokens" in b else int(b["attention_mask"].sum())
+                    if "num_real_tokens" in b:
+                        real += int(b["num_real_tokens"])
+                    elif "attention_mask" in b:
+                        real += int(b["attention_mask"].sum())
+                    else:                                   # the reference's static layout: real tokens = non-pad ids
+                        real += int((b["input_ids"] != 0).sum())
                 dt = time.perf_counter() - t0
-                print(json.dumps({"bench": name, "workers": workers, "micro_batches": nb,
+                print(json.dumps({"bench": name, "impl": args.impl, "workers": workers, "micro_batches": nb,
                                   "micro_batches_per_s": round(nb / dt, 1), "real_tokens_per_s": round(real / dt),
                                   "needed_tokens_per_s_per_gpu": needed,
                                   "gpus_one_loader_feeds": round(real / dt / needed, 1)}), flush=True)
