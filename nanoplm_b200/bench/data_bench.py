@@ -121,6 +121,16 @@ def main() -> None:
         print(json.dumps({"bench": "read_every_sequence", "impl": args.impl, "sequences": len(ds), "tokens": n_tok,
                           "sequences_per_s": round(len(ds) / dt), "tokens_per_s": round(n_tok / dt)}), flush=True)
 
+        # text -> ids, the inner loop of shard writing (pretraining/dataset.py:285-322): one call per sequence
+        from nanoplm_b200.data.synthetic import synthetic_sequences
+        texts = synthetic_sequences(min(args.sequences, 5000), args.min_len, args.max_len, 11)
+        t0 = time.perf_counter()
+        n_ids = sum(len(tok(t, add_special_tokens=True, truncation=True, max_length=args.max_len)["input_ids"])
+                    for t in texts)
+        dt = time.perf_counter() - t0
+        print(json.dumps({"bench": "tokenize_one_by_one", "impl": args.impl, "sequences": len(texts),
+                          "sequences_per_s": round(len(texts) / dt), "tokens_per_s": round(n_ids / dt)}), flush=True)
+
         # a B200 running the default encoder consumes about 760 K real tokens per second
         needed = 760_000
         for name, coll in (
