@@ -73,7 +73,7 @@ def _invalidate_fp8_weights() -> None:
 class ShardedEngine:
     def __init__(self, model: nn.Module, hyper: AdamWHyper, device: torch.device,
                  process_group=None, compute_dtype: torch.dtype = torch.bfloat16,
-                 fused_comm: bool = False, exclude: Iterable[str] = ()):
+                 fused_comm: bool = False, exclude: Iterable[str] = (), decay_all: bool = False):
         self.model = model
         self.hyper = hyper
         self.device = torch.device(device)
@@ -98,8 +98,10 @@ class ShardedEngine:
                 continue
             seen[id(p)] = name
             named.append((name, p))
-        decay = [(n, p) for n, p in named if use_weight_decay(n, p)]
-        no_decay = [(n, p) for n, p in named if not use_weight_decay(n, p)]
+        # decay_all: one group with the weight decay on every tensor, norms and biases included, which
+        # is what `AdamW(model.parameters())` does (reference: distillation/pipeline.py:669)
+        decay = [(n, p) for n, p in named if decay_all or use_weight_decay(n, p)]
+        no_decay = [(n, p) for n, p in named if not (decay_all or use_weight_decay(n, p))]
         self.slots: list[ParamSlot] = []
         off = 0
         for group, flag in ((decay, True), (no_decay, False)):
@@ -370,6 +372,8 @@ class ShardedEngine:
                     }
                 ids.append(idx)
                 idx += 1
+            if not ids:
+                continue                            # torch optimizers have no empty groups
             groups.append({"lr": h.lr, "betas": (h.beta1, h.beta2), "eps": h.eps, "weight_decay": wd,
                            "amsgrad": False, "maximize": False, "foreach": None, "capturable": False,
                            "differentiable": False, "fused": None, "decoupled_weight_decay": True,

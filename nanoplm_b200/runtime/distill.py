@@ -136,7 +136,7 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
     use_bf16 = cfg.bf16 and device.type == "cuda"
     hyper = AdamWHyper(lr=float(cfg.learning_rate), weight_decay=0.01, max_grad_norm=float(cfg.max_grad_norm))
     engine = ShardedEngine(student, hyper, device, compute_dtype=torch.bfloat16 if use_bf16 else torch.float32,
-                           fused_comm=bool(getattr(cfg, "fused_comm", True)))
+                           fused_comm=bool(getattr(cfg, "fused_comm", True)), decay_all=True)
     student.train()
     if cfg.on_the_fly and teacher is None:
         from nanoplm_b200.models.teacher import T5EncoderTeacher

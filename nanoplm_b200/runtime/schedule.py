@@ -9,7 +9,7 @@ schedules of the distillation pipeline (distillation/pipeline.py:396-446). State
 from __future__ import annotations
 
 import math
-from typing import Callable
+from typing import Callable, Optional, Sequence
 
 
 def get_warmup_steps(total_steps: int, warmup_value: float) -> int:
@@ -25,38 +25,53 @@ def num_update_steps_per_epoch(loader_len: int, grad_accum: int) -> int:
 
 
 class LambdaSchedule:
-    def __init__(self, base_lr: float, fn: Callable[[int], float]):
-        self.base_lrs = [float(base_lr)]
+    """A learning-rate multiplier over optimizer steps with the state-dict layout of torch's LambdaLR.
+
+    `group_lrs` lists the base rate of every parameter group of the optimizer whose `optimizer.pt`
+    is written next to this schedule (decay / no-decay for AdamW, Muon / AdamW for Muon), because
+    torch's scheduler refuses a state whose lists are shorter than its optimizer's groups;
+    `primary` is the group whose rate `get_lr()` returns."""
+
+    def __init__(self, base_lr: float, fn: Callable[[int], float], group_lrs: Optional[Sequence[float]] = None,
+                 primary: int = 0):
+        self.base_lrs = [float(x) for x in group_lrs] if group_lrs else [float(base_lr), float(base_lr)]
+        self.primary = primary if 0 <= primary < len(self.base_lrs) else 0
+        self.base_lrs[self.primary] = float(base_lr)
         self.fn = fn
         self.last_epoch = 0
 
     def get_lr(self) -> float:
-        return self.base_lrs[0] * self.fn(self.last_epoch)
+        return self.base_lrs[self.primary] * self.fn(self.last_epoch)
 
     def get_last_lr(self) -> list[float]:
-        return [self.get_lr()]
+        m = self.fn(self.last_epoch)
+        return [b * m for b in self.base_lrs]
 
     def step(self) -> None:
         self.last_epoch += 1
 
     def state_dict(self) -> dict:
         return {"base_lrs": list(self.base_lrs), "last_epoch": self.last_epoch,
-                "_step_count": self.last_epoch + 1, "_last_lr": self.get_last_lr(),
-                "lr_lambdas": [None]}
+                "_step_count": self.last_epoch + 1, "_is_initial": False, "_get_lr_called_within_step": False,
+                "_last_lr": self.get_last_lr(), "lr_lambdas": [None] * len(self.base_lrs)}
 
     def load_state_dict(self, sd: dict) -> None:
         self.last_epoch = int(sd.get("last_epoch", 0))
-        if sd.get("base_lrs"):
-            self.base_lrs = [float(sd["base_lrs"][0])]
+        saved = [float(x) for x in (sd.get("base_lrs") or [])]
+        if len(saved) == len(self.base_lrs):
+            self.base_lrs = saved
+        elif saved:                                 # a file with another number of groups: one rate for all
+            self.base_lrs = [saved[0]] * len(self.base_lrs)
 
 
 class WarmupLinearSchedule(LambdaSchedule):
-    def __init__(self, base_lr: float, warmup_steps: int, total_steps: int):
+    def __init__(self, base_lr: float, warmup_steps: int, total_steps: int,
+                 group_lrs: Optional[Sequence[float]] = None, primary: int = 0):
         def fn(step: int) -> float:
             if step < warmup_steps:
                 return step / max(1, warmup_steps)
             return max(0.0, (total_steps - step) / max(1, total_steps - warmup_steps))
-        super().__init__(base_lr, fn)
+        super().__init__(base_lr, fn, group_lrs, primary)
         self.warmup_steps, self.total_steps = warmup_steps, total_steps
 
 
@@ -103,4 +118,5 @@ def make_distill_schedule(name: str, base_lr: float, warmup_steps: int, total_st
             return 1.0 if w is None else w
     else:
         raise ValueError(f"Unknown lr_scheduler: {name}. Supported: cosine, linear, polynomial, constant")
-    return LambdaSchedule(base_lr, fn)
+    # the distillation optimizer has one parameter group (reference: distillation/pipeline.py:669)
+    return LambdaSchedule(base_lr, fn, group_lrs=[base_lr])

@@ -18,7 +18,9 @@
     `params.yaml` drives this package's data pipeline to a dataset the reference's validators accept;
   * schedules, weight-decay and Muon routing, the FLOP estimate and the Polar-Express iteration;
   * the padded MLM collator, the shard validators, the initialisation, every command / option / default of
-    the CLI, and ten optimizer steps of the reference's recipe step by step.
+    the CLI, and ten optimizer steps of the reference's recipe step by step (pretraining and distillation);
+  * one run directory handed from the reference's `run_pure_pretraining` to this package's `run_pretraining`
+    and back, each resuming the other's checkpoint.
 """
 import os
 import sys
@@ -906,3 +908,131 @@ def test_training_trajectory_follows_the_reference_recipe(ref):
     theirs, ours = rm.state_dict(), om.state_dict()
     worst = max(float((theirs[k].float() - ours[k].float()).abs().max()) for k in theirs)
     assert worst < 5e-4, worst
+
+
+def test_distillation_trajectory_follows_the_reference_recipe(ref):
+    """Eight optimizer steps of the distillation recipe: the reference's student, its trainer's loss
+    (distillation/trainer.py:8-40), `AdamW(model.parameters())` (weight decay 0.01 on every tensor,
+    distillation/pipeline.py:669), its cosine schedule and the trainer's clipping to 1.0, against this
+    package's student, `distillation_loss`, engine and schedule on the same batches."""
+    try:
+        from nanoplm.distillation.models.student.model import ProtX as RefProtX, ProtXConfig as RefCfg
+        from nanoplm.distillation.trainer import DistillationTrainer
+        import importlib
+        D = importlib.import_module("nanoplm.distillation.pipeline")
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference distillation import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.config.schema import StudentConfig
+    from nanoplm_b200.models.student import ProtX
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import schedule
+    from nanoplm_b200.runtime.distill import distillation_loss
+    torch.manual_seed(0)
+    geom = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2)
+    rm = RefProtX(RefCfg(**geom)).float()
+    with torch.no_grad():
+        for p in rm.parameters():
+            if p.ndim >= 2:
+                p.add_(torch.randn_like(p) * 0.05)
+    om = ProtX(StudentConfig(max_position_embeddings=8192, **geom)).float()
+    om.load_state_dict(rm.state_dict(), strict=True)
+    rm.train(); om.train()
+    steps, lr = 8, 2e-3
+    opt = torch.optim.AdamW(rm.parameters(), lr=lr)
+    sched_r = D._get_scheduler(opt, "cosine", {}, steps)
+    sched_o = schedule.make_distill_schedule("cosine", lr, int(steps * 0.05), steps)
+    eng = ShardedEngine(om, AdamWHyper(lr=lr, weight_decay=0.01, max_grad_norm=1.0), torch.device("cpu"),
+                        compute_dtype=torch.float32, decay_all=True)
+    assert all(s.decay for s in eng.slots)
+    sd = eng.optimizer_state_dict()
+    assert len(sd["param_groups"]) == 1 and len(sd["param_groups"][0]["params"]) == len(list(rm.parameters()))
+    assert len(sched_o.state_dict()["base_lrs"]) == len(sched_r.state_dict()["base_lrs"]) == 1
+    loss_of = DistillationTrainer._compute_distillation_loss
+    tok = rm.tokenizer
+    for step in range(steps):
+        seqs = _sequences(6, 10, 50, seed=300 + step)
+        enc = tok(seqs, padding=True, return_tensors="pt")
+        target = torch.randn(enc["input_ids"].shape[0], enc["input_ids"].shape[1], 1024,
+                             generator=torch.Generator().manual_seed(step))
+        out = rm(enc["input_ids"], enc["attention_mask"], training_mode=True).last_hidden_state
+        loss_r = loss_of(None, out, target, enc["attention_mask"])
+        loss_r.backward()
+        gn_r = float(torch.nn.utils.clip_grad_norm_(rm.parameters(), 1.0))
+        opt.step(); sched_r.step(); opt.zero_grad(set_to_none=True)
+        batch = {"input_ids": enc["input_ids"], "attention_mask": enc["attention_mask"], "teacher_embeddings": target}
+        loss_o = distillation_loss(om, batch)
+        loss_o.backward()
+        gn_o = float(eng.step(sched_o.get_lr(), grad_accum=1))
+        sched_o.step()
+        assert abs(float(loss_r.detach()) - float(loss_o.detach())) < 2e-4 * abs(float(loss_r.detach())), step
+        assert abs(gn_r - gn_o) < 1e-3 * gn_r, (step, gn_r, gn_o)
+        assert abs(sched_r.get_last_lr()[0] - sched_o.get_last_lr()[0]) < 1e-12
+    theirs, ours = rm.state_dict(), om.state_dict()
+    assert max(float((theirs[k] - ours[k]).abs().max()) for k in theirs) < 5e-4
+
+
+def test_a_run_moves_between_the_two_pipelines_mid_training(ref, tmp_path, monkeypatch):
+    """End to end through both public entry points on one run directory: the reference's
+    `run_pure_pretraining` (pure_pipeline.py:334-927) trains 10 steps on a dataset written here and
+    saves checkpoints 4 / 8 / 10; this package's `run_pretraining` resumes its checkpoint-4 (same run
+    directory, later checkpoints archived, same learning rates, losses that continue the curve) and
+    writes 8 / 10; the reference then resumes THAT checkpoint-8 for one more epoch."""
+    import json
+    import math
+
+    from nanoplm.pretraining.config import PretrainingConfig as RefPre, PureTorchConfig as RefPT, ResumeConfig as RefRes
+
+    from nanoplm_b200.config.schema import ModelConfig, PretrainingConfig, PureTorchConfig, ResumeConfig
+    from nanoplm_b200.data.synthetic import write_synthetic_dataset
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.runtime.pretrain import run_pretraining
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("WANDB_MODE", "disabled")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    root = write_synthetic_dataset(tmp_path / "ds", 120, 24, 10, 60, samples_per_shard=50)
+    geom = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+                max_position_embeddings=128)
+    common = dict(dataset_dir=str(root), ckp_dir="ckpt", micro_batch_size=8, global_batch_size=8 * 64 * 2,
+                  num_epochs=2, logging_steps=1, eval_steps=4, save_steps=4, num_workers=0, bf16=False, tf32=False)
+
+    def ref_model():
+        return ref.Model(ref.Config(**geom))
+
+    torch.manual_seed(0)
+    ref.pipeline.run_pure_pretraining(ref_model(), RefPre(**common), RefPT(use_compile=False, use_packing=False), None)
+    run = next((tmp_path / "ckpt").glob("run-*"))
+    files = {"optimizer.pt", "pytorch_model.bin", "rng_state.pth", "scheduler.pt", "training_state.json"}
+    assert all({p.name for p in (run / f"checkpoint-{n}").iterdir()} == files for n in (4, 8, 10))
+    ref_state = json.loads((run / "checkpoint-4" / "training_state.json").read_text())
+    ref_sched = torch.load(run / "checkpoint-8" / "scheduler.pt", weights_only=False)
+
+    res = run_pretraining(ProtEncoderMLM(ModelConfig(**geom), ProtTokenizer()), PretrainingConfig(**common),
+                          PureTorchConfig(use_compile=False, use_packing=False),
+                          ResumeConfig(True, str(run / "checkpoint-4"), 0))
+    assert Path(res["output_dir"]).resolve() == run.resolve() and res["global_step"] == 10
+    assert [s for s, _ in res["losses"]] == [5, 6, 7, 8, 9, 10]
+    # an untrained model of this size starts at ln(32) = 3.47; the resumed curve starts where the
+    # reference's step 4 left it and keeps falling
+    assert res["losses"][0][1] < 3.42 and res["losses"][-1][1] < res["losses"][0][1] + 0.02
+    archived = [p for p in run.glob("archived_*")]
+    assert len(archived) == 1 and sorted(p.name for p in archived[0].iterdir()) == ["checkpoint-10", "checkpoint-8"]
+    assert all({p.name for p in (run / f"checkpoint-{n}").iterdir()} >= files for n in (8, 10))
+    own_state = json.loads((run / "checkpoint-8" / "training_state.json").read_text())
+    assert set(ref_state) <= set(own_state) and own_state["global_step"] == 8
+    own_sched = torch.load(run / "checkpoint-8" / "scheduler.pt", weights_only=False)
+    assert own_sched["last_epoch"] == ref_sched["last_epoch"] == 8
+    assert len(own_sched["base_lrs"]) == len(ref_sched["base_lrs"]) == 2
+    assert all(math.isclose(a, b, rel_tol=1e-9) for a, b in zip(own_sched["_last_lr"], ref_sched["_last_lr"]))
+    assert (run / ".resume_counter").read_text().strip() == "1"
+
+    # and back: the reference continues from the checkpoint written here, one extra epoch
+    ref.pipeline.run_pure_pretraining(ref_model(), RefPre(**common), RefPT(use_compile=False, use_packing=False),
+                                      RefRes(True, str(run / "checkpoint-8"), 1))
+    assert (run / "checkpoint-15").exists() and (run / ".resume_counter").read_text().strip() == "2"
+    final = torch.load(run / "checkpoint-15" / "pytorch_model.bin", weights_only=True)
+    mine = torch.load(run / "checkpoint-8" / "pytorch_model.bin", weights_only=True)
+    assert set(final) == set(mine)
+    moved = max(float((final[k].float() - mine[k].float()).abs().max()) for k in final)
+    assert 0 < moved < 0.5
