@@ -76,6 +76,31 @@ def _hf_trainer_recipe(cfg, pt: PureTorchConfig) -> PureTorchConfig:
     return dataclasses.replace(pt, use_packing=False)
 
 
+@pretrain.command("supervise", help="Run `from-yaml` as N supervised ranks: when a rank fails or stalls, end the "
+                                    "others and restart from the latest complete checkpoint.")
+@click.argument("config", default="pretrain.yaml", type=click.Path(dir_okay=False, path_type=Path))
+@click.option("--nproc", type=int, default=1, show_default=True, help="Ranks to start (one per GPU).")
+@click.option("--max-restarts", type=int, default=3, show_default=True)
+@click.option("--stall-seconds", type=float, default=0.0,
+              help="With pretraining.heartbeat_seconds set: restart when a rank's step stops advancing this long.")
+@click.option("--grace-seconds", type=float, default=10.0, show_default=True,
+              help="Time between SIGTERM and SIGKILL for the ranks of a failed attempt.")
+@click.option("--log-dir", type=click.Path(path_type=Path), default=None,
+              help="Write every rank's output to <log-dir>/attempt-K-rank-R.log instead of the terminal.")
+def supervise(config: Path, nproc: int, max_restarts: int, stall_seconds: float, grace_seconds: float,
+              log_dir: Path | None) -> None:
+    from nanoplm_b200.runtime.supervisor import Supervisor
+    try:
+        sup = Supervisor(config if config.is_absolute() else Path.cwd() / config, nproc, max_restarts,
+                         stall_seconds, grace_seconds, log_dir=log_dir)
+    except (FileNotFoundError, ValueError) as exc:
+        raise click.ClickException(str(exc)) from exc
+    code = sup.run()
+    click.echo(f"attempts: {len(sup.attempts)}, restarts: {sup.restarts}, run directory: {sup.run_dir}")
+    if code != 0:
+        raise click.ClickException(f"job did not finish within {max_restarts} restart(s): {sup.attempts[-1].reason}")
+
+
 @pretrain.command("get-yaml", help="Write a pretraining YAML template.")
 @click.argument("output", required=False, type=click.Path(path_type=Path))
 @click.option("--force", is_flag=True, help="Overwrite an existing file.")

@@ -407,6 +407,9 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
             global_step += 1
             if heartbeat is not None:
                 heartbeat.step = global_step
+            if os.environ.get("NPLM_INJECT_FAULT"):     # host-side failure for recovery tests, between steps
+                from nanoplm_b200.runtime.faults import maybe_inject
+                maybe_inject(rank, global_step)
             window_loss += accum_loss / n_acc
             accum_loss.zero_()
             window_steps += 1
