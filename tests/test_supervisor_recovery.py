@@ -51,8 +51,9 @@ def test_job_restarts_from_the_latest_checkpoint_after_a_rank_dies(tmp_path, mon
     assert sup.run() == 0, [a.__dict__ for a in sup.attempts]
     assert sup.restarts == 1
     first, second = sup.attempts
-    assert first.exit_codes[1] == 17 and "rank 1 exited with code 17" in first.reason
-    assert first.exit_codes[0] not in (0, None)                  # the survivor was ended by the supervisor
+    assert first.exit_codes[1] == 17 and "1 exited with code 17" in first.reason
+    # the survivor was ended by the supervisor, or noticed the lost connection itself just before
+    assert first.exit_codes[0] not in (0, None)
     assert second.resumed_from.endswith("checkpoint-2") and second.exit_codes == [0, 0]
     run = Path(second.run_dir)
     assert run == Path(first.run_dir) and len(list((tmp_path / "ckpt").glob("run-*"))) == 1
