@@ -39,6 +39,26 @@ def from_yaml(config: Path) -> None:
     _launch(model_cfg, cfg, resume)
 
 
+@distill.command("supervise", help="Run `from-yaml` as N supervised ranks: when a rank fails, end the others and "
+                                   "restart from the latest complete checkpoint.")
+@click.argument("config", default="distill.yaml", type=click.Path(dir_okay=False, path_type=Path))
+@click.option("--nproc", type=int, default=1, show_default=True, help="Ranks to start (one per GPU).")
+@click.option("--max-restarts", type=int, default=3, show_default=True)
+@click.option("--grace-seconds", type=float, default=10.0, show_default=True)
+@click.option("--log-dir", type=click.Path(path_type=Path), default=None)
+def supervise(config: Path, nproc: int, max_restarts: int, grace_seconds: float, log_dir) -> None:
+    from nanoplm_b200.runtime.supervisor import Supervisor
+    try:
+        sup = Supervisor(config if config.is_absolute() else Path.cwd() / config, nproc, max_restarts,
+                         grace_seconds=grace_seconds, log_dir=log_dir, section="distillation")
+    except (FileNotFoundError, ValueError) as exc:
+        raise click.ClickException(str(exc)) from exc
+    code = sup.run()
+    click.echo(f"attempts: {len(sup.attempts)}, restarts: {sup.restarts}, run directory: {sup.run_dir}")
+    if code != 0:
+        raise click.ClickException(f"job did not finish within {max_restarts} restart(s): {sup.attempts[-1].reason}")
+
+
 @distill.command("get-yaml", help="Write a distillation YAML template.")
 @click.argument("output", required=False, type=click.Path(path_type=Path))
 @click.option("--force", is_flag=True)

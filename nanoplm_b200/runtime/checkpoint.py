@@ -171,6 +171,8 @@ def latest_checkpoint(run_dir: str | Path) -> Optional[Path]:
             s = int(d.name.split("-")[1])
         except (IndexError, ValueError):
             continue
-        if s > best_step and (d / STATE_FILE).exists():
+        # complete = its state file is there (the pretraining pipeline's, or the HF-style one the
+        # distillation pipeline writes); checkpoints are renamed into place after their last file
+        if s > best_step and ((d / STATE_FILE).exists() or (d / "trainer_state.json").exists()):
             best, best_step = d, s
     return best

@@ -291,6 +291,9 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
             gn = engine.step(lr, n_acc)
             sched.step()
             global_step += 1
+            if os.environ.get("NPLM_INJECT_FAULT"):     # host-side failure for recovery tests, between steps
+                from nanoplm_b200.runtime.faults import maybe_inject
+                maybe_inject(rank, global_step)
             win += acc / n_acc
             acc.zero_()
             win_n += 1

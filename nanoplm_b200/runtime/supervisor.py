@@ -3,7 +3,8 @@ stalls, and starts the job again from the latest complete checkpoint.
 
 The reference leaves recovery to the user: a lost rank is a collective that never returns, and the
 run is continued by hand with `resume.is_resume: true` (src/nanoplm/cli/pretrain.py:885-924). Here
-`nanoplm pretrain supervise pretrain.yaml --nproc N` does that loop:
+`nanoplm pretrain supervise pretrain.yaml --nproc N` (and `nanoplm distill supervise distill.yaml`)
+does that loop:
 
   1. start N rank processes of `nanoplm pretrain from-yaml` (one per GPU, or CPU ranks over gloo), each
      in a process group of its own, with RANK / LOCAL_RANK / WORLD_SIZE / MASTER_ADDR=127.0.0.1 and a
@@ -58,7 +59,8 @@ class Attempt:
 class Supervisor:
     def __init__(self, config: str | Path, nproc: int = 1, max_restarts: int = 3, stall_seconds: float = 0.0,
                  grace_seconds: float = 10.0, poll_seconds: float = 0.5, extra_env: Optional[dict] = None,
-                 command: Optional[Sequence[str]] = None, log_dir: Optional[str | Path] = None):
+                 command: Optional[Sequence[str]] = None, log_dir: Optional[str | Path] = None,
+                 section: str = "pretraining"):
         self.config = Path(config).resolve()
         if not self.config.exists():
             raise FileNotFoundError(f"Config file not found: {self.config}")
@@ -68,10 +70,14 @@ class Supervisor:
         self.stall_seconds, self.grace, self.poll = float(stall_seconds), float(grace_seconds), float(poll_seconds)
         self.extra_env = dict(extra_env or {})
         # the rank command; the attempt's YAML path is appended
-        self.command = list(command) if command else [sys.executable, "-m", "nanoplm_b200", "pretrain", "from-yaml"]
+        if section not in ("pretraining", "distillation"):
+            raise ValueError("section must be 'pretraining' or 'distillation'")
+        self.section = section
+        group = "pretrain" if section == "pretraining" else "distill"
+        self.command = list(command) if command else [sys.executable, "-m", "nanoplm_b200", group, "from-yaml"]
         self.raw = yaml.safe_load(self.config.read_text(encoding="utf-8")) or {}
-        pre = self.raw.get("pretraining") or {}
-        self.ckp_dir = Path(pre.get("ckp_dir", "output/pretraining"))
+        pre = self.raw.get(section) or {}
+        self.ckp_dir = Path(pre.get("ckp_dir", "output/" + section))
         if not self.ckp_dir.is_absolute():
             self.ckp_dir = Path.cwd() / self.ckp_dir
         self.log_dir = Path(log_dir) if log_dir else None
@@ -82,7 +88,7 @@ class Supervisor:
     # ---- one attempt -------------------------------------------------------------------------
     def _attempt_config(self, k: int, resume_from: Optional[Path]) -> Path:
         raw = {key: (dict(v) if isinstance(v, dict) else v) for key, v in self.raw.items()}
-        pre = raw.setdefault("pretraining", {})
+        pre = raw.setdefault(self.section, {})
         if self.nproc > 1:
             pre["multi_gpu"] = True
             pre["world_size"] = self.nproc

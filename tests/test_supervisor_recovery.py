@@ -108,3 +108,37 @@ def test_supervise_command_is_wired(tmp_path, monkeypatch):
     assert r.exit_code != 0 and "Config file not found" in r.output
     r = CliRunner().invoke(cli, ["pretrain", "supervise", "--help"])
     assert r.exit_code == 0 and "--max-restarts" in r.output and "--nproc" in r.output
+
+
+@pytest.mark.timeout(600)
+def test_distillation_job_restarts_after_a_rank_raises(tmp_path, monkeypatch):
+    from nanoplm_b200.config.templates import DISTILL_YAML
+    from nanoplm_b200.data.manifest import DistillationManifest, write_manifest
+    from nanoplm_b200.data.synthetic import write_synthetic_fasta
+    monkeypatch.chdir(tmp_path)
+    kd = tmp_path / "kd"
+    write_synthetic_fasta(kd / "train.fasta", 64, 10, 40, seed=1)
+    write_synthetic_fasta(kd / "val.fasta", 16, 10, 40, seed=2)
+    write_manifest(kd, DistillationManifest(
+        pipeline_mode="distillation", seqs_num=80, min_seq_len=10, max_seq_len=48, val_ratio=0.2, train_dir=".",
+        val_dir=".", train_sequences=64, val_sequences=16, teacher_model="prott5", on_the_fly=True,
+        train_fasta="train.fasta", val_fasta="val.fasta"))
+    cfg = yaml.safe_load(DISTILL_YAML)
+    cfg["model"].update(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2)
+    cfg["distillation"].update(dataset_dir=str(kd), ckp_dir=str(tmp_path / "dckpt"), num_epochs=2, batch_size=8,
+                               logging_steps=1, eval_steps=100, save_steps=2, bf16=False, fused_comm=False,
+                               teacher_random_init=True,
+                               teacher={"d_model": 1024, "d_kv": 8, "d_ff": 32, "num_layers": 1, "num_heads": 2})
+    path = tmp_path / "distill.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    sup = Supervisor(path, nproc=2, max_restarts=2, grace_seconds=5, log_dir=tmp_path / "logs", section="distillation",
+                     extra_env={**_env(), "NPLM_INJECT_FAULT": "1:3:raise:0"})
+    assert sup.run() == 0, [a.__dict__ for a in sup.attempts]
+    assert sup.restarts == 1 and sup.attempts[1].resumed_from.endswith("checkpoint-2")
+    assert sup.attempts[0].exit_codes[1] == 1 and sup.attempts[1].exit_codes == [0, 0]
+    run = Path(sup.attempts[1].run_dir)
+    steps = _steps(run)
+    # 2 epochs x 4 steps; what the first attempt logged past checkpoint-2 shows up again from the second
+    assert steps[-1] == 8 and sorted(set(steps)) == list(range(1, 9)) and (run / "checkpoint-8").exists()
+    assert steps[steps.index(2) + 1:].count(3) >= 1 and steps == sorted(steps)
+    assert (run / "model.safetensors").exists()
