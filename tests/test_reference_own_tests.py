@@ -1,0 +1,57 @@
+"""The reference's own live unit tests, run unmodified against this package.
+
+`tests/test_packing_collator.py` and `tests/test_pretraining_collator.py` of the reference checkout are
+its two test files that still import (the others name classes that no longer exist there). They
+import `nanoplm.pretraining.collator`, `...modern_bert.tokenizer` and `...modern_bert.modeling`; here
+those three module paths are provided by a throw-away package that re-exports this package's
+collators, tokenizer and position-id helper, and pytest runs the reference's files as they are, in a
+child process. Skipped when no reference checkout is found (`NANOPLM_REFERENCE_DIR`, default: a
+`reference` directory beside the repository)."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+REF_DIR = Path(os.environ.get("NANOPLM_REFERENCE_DIR", ROOT.parent / "reference"))
+FILES = ["test_packing_collator.py", "test_pretraining_collator.py"]
+
+SHIM = {
+    "nanoplm/__init__.py": "",
+    "nanoplm/pretraining/__init__.py": "",
+    "nanoplm/pretraining/models/__init__.py": "",
+    "nanoplm/pretraining/models/modern_bert/__init__.py": "",
+    "nanoplm/pretraining/collator.py":
+        "from nanoplm_b200.data.collators import PackingCollator, ProtDataCollatorForLM  # noqa: F401\n",
+    "nanoplm/pretraining/models/modern_bert/tokenizer.py":
+        "from nanoplm_b200.data.tokenizer import ProtTokenizer as ProtModernBertTokenizer  # noqa: F401\n",
+    "nanoplm/pretraining/models/modern_bert/modeling.py":
+        "from nanoplm_b200.models.encoder import position_ids_from_cu_seqlens as _position_ids_from_cu_seqlens"
+        "  # noqa: F401\n",
+}
+
+
+@pytest.mark.skipif(not all((REF_DIR / "tests" / f).exists() for f in FILES), reason="no reference checkout")
+def test_reference_collator_tests_pass_on_this_package(tmp_path):
+    shim = tmp_path / "shim"
+    for rel, text in SHIM.items():
+        p = shim / rel
+        p.parent.mkdir(parents=True, exist_ok=True)
+        p.write_text(text)
+    (tmp_path / "empty.ini").write_text("[pytest]\n")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(shim), str(ROOT)]), CUDA_VISIBLE_DEVICES="")
+    # no conftest, no ini file and importlib import mode: nothing of the reference's source tree gets on sys.path
+    cmd = [sys.executable, "-m", "pytest", *[str(REF_DIR / "tests" / f) for f in FILES], "--noconftest",
+           "-p", "no:cacheprovider", "-c", str(tmp_path / "empty.ini"), "--rootdir", str(tmp_path),
+           "--import-mode=importlib", "-q", "-rA"]
+    out = subprocess.run(cmd, cwd=tmp_path, env=env, capture_output=True, text=True, timeout=900)
+    text = out.stdout + out.stderr
+    assert out.returncode == 0, text[-4000:]
+    assert "24 passed" in text and "failed" not in text.split("short test summary info")[-1], text[-2000:]
+    # the classes under test came from this package, not from the reference
+    probe = subprocess.run([sys.executable, "-c", "import nanoplm.pretraining.collator as c; "
+                            "print(c.PackingCollator.__module__, c.ProtDataCollatorForLM.__module__)"],
+                           cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
+    assert probe.stdout.split() == ["nanoplm_b200.data.collators", "nanoplm_b200.data.collators"], probe.stderr[-2000:]
