@@ -87,6 +87,44 @@ class ShardWriter:
         return [Path(p) for p in paths]
 
 
+class LazyFastaDataset(torch.utils.data.Dataset):
+    """Tokenises the records of a FASTA file on access, without a sharding step: small datasets,
+    quick experiments, and the oracle the shards are compared with. Same examples as `ShardedDataset`
+    (`input_ids` / `attention_mask` of one sequence, truncated to `max_length`). The class left the
+    reference's package while its tests still describe it (tests/test_fasta_dataset.py:16-103,
+    236-265): three-argument constructor, `max_length` attribute, IndexError for negative and
+    out-of-range indices, ValueError for an empty file. Pickles to its arguments, so DataLoader
+    workers index the file themselves."""
+
+    def __init__(self, fasta_path, tokenizer: ProtTokenizer, max_length: int):
+        self.fasta_path, self.tokenizer, self.max_length = str(fasta_path), tokenizer, int(max_length)
+        p = Path(self.fasta_path)
+        if not p.exists():
+            raise FileNotFoundError(f"FASTA file not found: {self.fasta_path}")
+        if p.stat().st_size == 0:
+            raise ValueError(f"FASTA file is empty: {self.fasta_path}")
+        self._index = FastaIndex(self.fasta_path)
+        if len(self._index) == 0:
+            raise ValueError(f"FASTA file is empty: {self.fasta_path} holds no records")
+
+    def __getstate__(self):
+        return (self.fasta_path, self.tokenizer, self.max_length)
+
+    def __setstate__(self, state):
+        self.__init__(*state)
+
+    def __len__(self) -> int:
+        return len(self._index)
+
+    def __getitem__(self, idx: int) -> dict:
+        if idx < 0 or idx >= len(self):
+            raise IndexError(f"Index {idx} out of bounds for dataset of size {len(self)}")
+        _, seq = self._index.get(int(idx))
+        enc = self.tokenizer(seq, add_special_tokens=True, truncation=True, max_length=self.max_length)
+        ids = torch.as_tensor(enc["input_ids"], dtype=torch.long)
+        return {"input_ids": ids, "attention_mask": torch.ones_like(ids)}
+
+
 class ShardedDataset(torch.utils.data.Dataset):
     """Memory-mapped view over a directory of shards. Pickles to just the directory path so that
     DataLoader workers re-open the maps themselves."""

@@ -1,11 +1,12 @@
 """The reference's own live unit tests, run unmodified against this package.
 
 `tests/test_packing_collator.py` and `tests/test_pretraining_collator.py` of the reference checkout are
-its two test files that still import (the others name classes that no longer exist there). They
-import `nanoplm.pretraining.collator`, `...modern_bert.tokenizer` and `...modern_bert.modeling`; here
-those three module paths are provided by a throw-away package that re-exports this package's
-collators, tokenizer and position-id helper, and pytest runs the reference's files as they are, in a
-child process. Skipped when no reference checkout is found (`NANOPLM_REFERENCE_DIR`, default: a
+its two test files that still import there; `tests/test_fasta_dataset.py` no longer does, because it
+names a `LazyFastaDataset` the reference dropped, but its tests describe the shard writer, the sharded
+dataset and that lazy dataset, all of which exist here. The files import
+`nanoplm.pretraining.{collator, dataset}`, `...modern_bert.tokenizer` and `...modern_bert.modeling`; here
+those module paths are provided by a throw-away package that re-exports this package's classes, and
+pytest runs the reference's files as they are, in a child process. Skipped when no reference checkout is found (`NANOPLM_REFERENCE_DIR`, default: a
 `reference` directory beside the repository)."""
 import os
 import subprocess
@@ -16,7 +17,7 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 REF_DIR = Path(os.environ.get("NANOPLM_REFERENCE_DIR", ROOT.parent / "reference"))
-FILES = ["test_packing_collator.py", "test_pretraining_collator.py"]
+FILES = ["test_packing_collator.py", "test_pretraining_collator.py", "test_fasta_dataset.py"]
 
 SHIM = {
     "nanoplm/__init__.py": "",
@@ -25,6 +26,8 @@ SHIM = {
     "nanoplm/pretraining/models/modern_bert/__init__.py": "",
     "nanoplm/pretraining/collator.py":
         "from nanoplm_b200.data.collators import PackingCollator, ProtDataCollatorForLM  # noqa: F401\n",
+    "nanoplm/pretraining/dataset.py":
+        "from nanoplm_b200.data.shards import LazyFastaDataset, ShardedDataset, ShardWriter  # noqa: F401\n",
     "nanoplm/pretraining/models/modern_bert/tokenizer.py":
         "from nanoplm_b200.data.tokenizer import ProtTokenizer as ProtModernBertTokenizer  # noqa: F401\n",
     "nanoplm/pretraining/models/modern_bert/modeling.py":
@@ -34,7 +37,7 @@ SHIM = {
 
 
 @pytest.mark.skipif(not all((REF_DIR / "tests" / f).exists() for f in FILES), reason="no reference checkout")
-def test_reference_collator_tests_pass_on_this_package(tmp_path):
+def test_reference_unit_tests_pass_on_this_package(tmp_path):
     shim = tmp_path / "shim"
     for rel, text in SHIM.items():
         p = shim / rel
@@ -49,7 +52,7 @@ def test_reference_collator_tests_pass_on_this_package(tmp_path):
     out = subprocess.run(cmd, cwd=tmp_path, env=env, capture_output=True, text=True, timeout=900)
     text = out.stdout + out.stderr
     assert out.returncode == 0, text[-4000:]
-    assert "24 passed" in text and "failed" not in text.split("short test summary info")[-1], text[-2000:]
+    assert "34 passed" in text and "failed" not in text.split("short test summary info")[-1], text[-2000:]
     # the classes under test came from this package, not from the reference
     probe = subprocess.run([sys.executable, "-c", "import nanoplm.pretraining.collator as c; "
                             "print(c.PackingCollator.__module__, c.ProtDataCollatorForLM.__module__)"],
