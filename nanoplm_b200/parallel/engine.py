@@ -84,6 +84,9 @@ class ShardedEngine:
         self.rank = dist.get_rank(process_group) if self.distributed else 0
         self.on_cuda = self.device.type == "cuda"
         self.compute_dtype = compute_dtype if self.on_cuda else torch.float32
+        # the optimizer kernels write the bf16 compute copy; an fp32 compute copy on a GPU
+        # (`bf16: false`) takes the PyTorch restatement of the update instead
+        self.kernel_opt = self.on_cuda and self.compute_dtype == torch.bfloat16
         self.step_count = 0
         self.fused = None
         tied = getattr(model, "_tied_weights_keys", {}) or {}
@@ -118,7 +121,7 @@ class ShardedEngine:
 
         dev = self.device
         sym = None
-        if fused_comm and self.on_cuda and self.distributed:
+        if fused_comm and self.kernel_opt and self.distributed:
             from nanoplm_b200.comm.fused_optimizer import FusedShardedStep
             sym = FusedShardedStep.allocate(self.total, self.world, dev, self.pg, self.compute_dtype)
         if sym is not None:   # gradients and parameters live in peer-mapped memory
@@ -268,7 +271,7 @@ class ShardedEngine:
             if b <= a:
                 continue
             sl = slice(a - self.lo, b - self.lo)
-            if self.on_cuda:
+            if self.kernel_opt:
                 from nanoplm_b200.ops import kernels as K
                 K.adamw_(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], shard_grad[sl],
                          new_shard[sl], self._hyper_dev[i], self._sumsq, zero_grad=False)

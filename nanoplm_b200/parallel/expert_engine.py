@@ -142,7 +142,7 @@ class ExpertParallelEngine(ShardedEngine):
             dist.all_reduce(self._x_sumsq, op=dist.ReduceOp.SUM, group=self.ep_group)
         norm = super().step(lr, grad_accum, extra_sumsq=self._x_sumsq)   # leaves the global norm in _sumsq
         grad_scale = 1.0 / (grad_accum * self.world)
-        if self.on_cuda:
+        if self.kernel_opt:
             from nanoplm_b200.ops import kernels as K
             K.adamw_(self.x_master, self.x_exp_avg, self.x_exp_avg_sq, self.x_grad, self.x_params,
                      self._hyper_dev[0], self._sumsq, zero_grad=False)

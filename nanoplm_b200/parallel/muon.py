@@ -195,7 +195,7 @@ class MuonEngine(ShardedEngine):
                                   for s in self.muon_slots} if self.normuon else {}
         self.muon_lr = self.muon_lr0
         # CUDA kernels for the elementwise parts: matrices are whole float4 runs at aligned offsets
-        self._kernels = self.on_cuda and all(s.numel % 4 == 0 and s.offset % 4 == 0 for s in self.muon_slots)
+        self._kernels = self.kernel_opt and all(s.numel % 4 == 0 and s.offset % 4 == 0 for s in self.muon_slots)
         self._gsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self._gscale = 1.0
         self._adam_table = None

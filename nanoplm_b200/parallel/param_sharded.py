@@ -185,7 +185,7 @@ class ParamShardedEngine(ShardedEngine):
         for p in self.mine:
             sl = slice(p.local, p.local + (p.b - p.a))
             group = 0 if p.slot.decay else 1
-            if self.on_cuda:
+            if self.kernel_opt:
                 from nanoplm_b200.ops import kernels as K
                 K.adamw_(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], grad[sl], new_local[sl],
                          self._hyper_dev[group], self._sumsq, zero_grad=False)

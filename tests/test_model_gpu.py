@@ -208,3 +208,52 @@ def test_muon_engine_trains_on_gpu_like_cpu(optimizer, cuda_status):
     assert g[-1] < g[0] - 0.1, g
     for a, b in zip(c, g):
         assert abs(a - b) < 0.12, (c, g)
+
+
+def test_fp32_compute_copy_on_the_gpu_follows_the_cpu_engine(cuda_status):
+    """`bf16: false` on a GPU: the compute copy stays fp32, the optimizer kernels (which write a bf16
+    copy) are not used, and training follows the CPU engine step by step; the same for the one-group
+    optimizer of the distillation pipeline (`decay_all`)."""
+    from nanoplm_b200.config.schema import ModelConfig, StudentConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.models.student import ProtX
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    s = ProtX(StudentConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2))
+    c = copy.deepcopy(s)
+    hyper = AdamWHyper(lr=1e-3, weight_decay=0.01)
+    eg = ShardedEngine(s, hyper, dev, compute_dtype=torch.float32, decay_all=True)
+    ec = ShardedEngine(c, hyper, torch.device("cpu"), compute_dtype=torch.float32, decay_all=True)
+    assert not eg.kernel_opt and len(eg.optimizer_state_dict()["param_groups"]) == 1
+    g = torch.Generator().manual_seed(1)
+    for _ in range(3):
+        grad = torch.randn(ec.total, generator=g) * 0.01
+        ec.main_grad.copy_(grad)
+        eg.main_grad.copy_(grad.cuda())
+        a, b = float(ec.step(1e-3, 1)), float(eg.step(1e-3, 1))
+        assert abs(a - b) < 1e-4 * a
+    assert max(float((x.detach().cpu() - y.detach()).abs().max()) for x, y in zip(s.parameters(), c.parameters())) < 1e-5
+
+    m = ProtEncoderMLM(ModelConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                                   max_position_embeddings=128), ProtTokenizer())
+    with torch.no_grad():
+        for layer in m.model.layers:
+            layer.attn.Wo.weight.normal_(0, 0.05)
+            layer.mlp.Wo.weight.normal_(0, 0.05)
+    mc = copy.deepcopy(m)
+    hyper = AdamWHyper(lr=2e-3, weight_decay=0.05)
+    eg = ShardedEngine(m, hyper, dev, compute_dtype=torch.float32)
+    ec = ShardedEngine(mc, hyper, torch.device("cpu"), compute_dtype=torch.float32)
+    ids = torch.randint(4, 24, (150,))
+    cu = torch.tensor([0, 40, 90, 150], dtype=torch.int32)
+    lab = torch.full((150,), -100)
+    lab[::4] = ids[::4]
+    for _ in range(3):
+        lc = mc(input_ids=ids, labels=lab, cu_seqlens=cu)["loss"]
+        lc.backward()
+        lg = m(input_ids=ids.cuda(), labels=lab.cuda(), cu_seqlens=cu.cuda())["loss"]
+        lg.backward()
+        a, b = float(ec.step(2e-3, 1)), float(eg.step(2e-3, 1))
+        assert abs(float(lc.detach()) - float(lg.detach())) < 2e-3 and abs(a - b) < 2e-2 * a
