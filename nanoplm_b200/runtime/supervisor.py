@@ -96,6 +96,7 @@ class Supervisor:
             raw["resume"] = {"is_resume": True, "checkpoint_dir": str(resume_from),
                              "extra_epochs": (self.raw.get("resume") or {}).get("extra_epochs")
                              if (self.raw.get("resume") or {}).get("is_resume") else None}
+        self._work.mkdir(parents=True, exist_ok=True)
         path = self._work / f"attempt-{k}.yaml"
         path.write_text(yaml.safe_dump(raw), encoding="utf-8")
         return path
@@ -163,6 +164,13 @@ class Supervisor:
 
     # ---- the loop ----------------------------------------------------------------------------
     def run(self) -> int:
+        try:
+            return self._run()
+        finally:
+            import shutil
+            shutil.rmtree(self._work, ignore_errors=True)      # the per-attempt YAML files
+
+    def _run(self) -> int:
         resume_from: Optional[Path] = None
         user_resume = self.raw.get("resume") or {}
         if user_resume.get("is_resume") and user_resume.get("checkpoint_dir"):
