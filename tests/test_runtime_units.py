@@ -209,3 +209,39 @@ def test_checkpoint_with_hf_files_loads_through_the_hf_layout_alone(tmp_path):
     other = eng2.full_state_dict_model()
     for k, v in full.items():
         assert torch.equal(v, other[k]), k
+
+
+def test_checkpoint_written_from_a_compiled_module_loads(tmp_path):
+    """The reference saves the compiled wrapper's state dict when `use_compile` is on, so every key
+    carries an `_orig_mod.` prefix (pure_pipeline.py:56-58, 257); such a file resumes here, and so does
+    one that stores only one of the two tied embedding / decoder entries."""
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.parallel.engine import AdamWHyper, ShardedEngine
+    from nanoplm_b200.runtime import checkpoint as ckpt
+    from nanoplm_b200.runtime.schedule import WarmupLinearSchedule
+    cfg = ModelConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2,
+                      max_position_embeddings=64)
+    torch.manual_seed(0)
+    src = ProtEncoderMLM(cfg, ProtTokenizer())
+    with torch.no_grad():
+        for p in src.parameters():
+            p.add_(torch.randn_like(p) * 0.02)
+    eng = ShardedEngine(src, AdamWHyper(), torch.device("cpu"))
+    eng.main_grad.normal_()
+    eng.step(1e-3, 1)
+    path = ckpt.save_checkpoint(eng, WarmupLinearSchedule(1e-3, 1, 10), 1, 0, str(tmp_path), 1, 5, 5)
+    plain = torch.load(path / "pytorch_model.bin", weights_only=True)
+    for variant, sd in (("prefixed", {"_orig_mod." + k: v for k, v in plain.items()}),
+                        ("decoder only", {k: v for k, v in plain.items() if k != "model.embeddings.tok_embeddings.weight"}),
+                        ("embedding only", {k: v for k, v in plain.items() if k != "decoder.weight"})):
+        torch.save(sd, path / "pytorch_model.bin")
+        torch.manual_seed(1)
+        dst = ProtEncoderMLM(cfg, ProtTokenizer())
+        eng2 = ShardedEngine(dst, AdamWHyper(), torch.device("cpu"))
+        step, _ = ckpt.load_checkpoint(eng2, WarmupLinearSchedule(1e-3, 1, 10), str(path))
+        a, b = eng.full_state_dict_model(), eng2.full_state_dict_model()
+        assert step == 1 and set(a) == set(b), variant
+        assert all(torch.equal(a[k], b[k]) for k in a), variant
+        assert dst.decoder.weight.data_ptr() == dst.model.embeddings.tok_embeddings.weight.data_ptr(), variant
