@@ -1036,3 +1036,51 @@ def test_a_run_moves_between_the_two_pipelines_mid_training(ref, tmp_path, monke
     assert set(final) == set(mine)
     moved = max(float((final[k].float() - mine[k].float()).abs().max()) for k in final)
     assert 0 < moved < 0.5
+
+
+def test_hf_based_reference_model_gives_the_same_logits(ref, tmp_path):
+    """The reference's other model class (`ProtModernBertMLM`, models/modern_bert/model.py:43-82: HF's
+    `ModernBertForMaskedLM` with the SwiGLU MLP swapped in) has the same state-dict keys as this
+    package's encoder, gives the same logits and loss with the same weights, and what its
+    `save_pretrained` writes loads here."""
+    try:
+        from nanoplm.pretraining.models.modern_bert.model import ProtModernBertMLM
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference HF model import failed: {type(exc).__name__}: {exc}")
+    from safetensors.torch import load_file
+
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    torch.manual_seed(0)
+    try:
+        hf = ProtModernBertMLM(ref.Config(**GEOM)).float().eval()
+    except Exception as exc:  # pragma: no cover   (an incompatible transformers version)
+        pytest.skip(f"reference HF model does not build here: {type(exc).__name__}: {exc}")
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.add_(torch.randn_like(p) * 0.05)
+    om = ProtEncoderMLM(ModelConfig(**GEOM), ProtTokenizer()).float().eval()
+    assert set(hf.state_dict()) == set(om.state_dict())
+    om.load_state_dict(hf.state_dict(), strict=True)
+    tok = ProtTokenizer()
+    enc = tok(["MKTAYIAKQRQISFVKSHFSRQ", "ACDEFGHIKLMNPQRSTVWY" * 6, "MK"], padding=True, return_tensors="pt")
+    keep = enc["attention_mask"].bool()
+    labels = torch.where(keep & (torch.arange(enc["input_ids"].shape[1])[None, :] % 3 == 0), enc["input_ids"],
+                         torch.full_like(enc["input_ids"], -100))
+    with torch.no_grad():
+        theirs = hf(input_ids=enc["input_ids"], attention_mask=enc["attention_mask"], labels=labels)
+        mine = om(enc["input_ids"], enc["attention_mask"])["logits"]
+        mine_loss = om(enc["input_ids"], enc["attention_mask"], labels=labels)["loss"]
+    assert (theirs.logits[keep] - mine[keep]).abs().max().item() < 1e-4
+    assert abs(float(theirs.loss) - float(mine_loss)) < 1e-4 * max(1.0, float(theirs.loss))
+    # save_pretrained stores the tied decoder weight once; the file loads through the tied-key alias
+    hf.save_pretrained(tmp_path / "hf")
+    sd = load_file(str(tmp_path / "hf" / "model.safetensors"))
+    fresh = ProtEncoderMLM(ModelConfig(**GEOM), ProtTokenizer()).float().eval()
+    missing = fresh.load_state_dict(sd, strict=False)
+    assert not missing.unexpected_keys and set(missing.missing_keys) <= {"decoder.weight", "model.embeddings.tok_embeddings.weight"}
+    with torch.no_grad():
+        again = fresh(enc["input_ids"], enc["attention_mask"])["logits"]
+    assert (again[keep] - mine[keep]).abs().max().item() < 1e-6
