@@ -1084,3 +1084,42 @@ def test_hf_based_reference_model_gives_the_same_logits(ref, tmp_path):
     with torch.no_grad():
         again = fresh(enc["input_ids"], enc["attention_mask"])["logits"]
     assert (again[keep] - mine[keep]).abs().max().item() < 1e-6
+
+
+def test_download_and_extract_steps_behave_like_the_reference(ref, tmp_path):
+    """`Downloader` / `Extractor` (data/downloader.py:16-68, data/extractor.py:14-41): the same bytes
+    from the same URL and archive, and an `ExtractionError` from both for a file that is not gzip and
+    for an archive cut off in the middle."""
+    import gzip
+
+    try:
+        from nanoplm.data import downloader as ref_dl
+        from nanoplm.data import extractor as ref_ex
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference data modules import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.data import prep
+    from nanoplm_b200.data.synthetic import write_synthetic_fasta
+    fasta = write_synthetic_fasta(tmp_path / "src" / "x.fasta", 300, 20, 200, seed=9)
+    raw = Path(fasta).read_bytes()
+    gz = tmp_path / "src" / "x.fasta.gz"
+    with gzip.open(gz, "wb") as f:
+        f.write(raw)
+    url = gz.as_uri()
+    ref_dl.Downloader(url, tmp_path / "a" / "x.fasta.gz").download()
+    prep.Downloader(url, tmp_path / "b" / "x.fasta.gz").download()
+    assert (tmp_path / "a" / "x.fasta.gz").read_bytes() == (tmp_path / "b" / "x.fasta.gz").read_bytes() == gz.read_bytes()
+    with pytest.raises(Exception):
+        ref_dl.Downloader((tmp_path / "nothing.gz").as_uri(), tmp_path / "a" / "n.gz").download()
+    with pytest.raises(prep.DownloadError):
+        prep.Downloader((tmp_path / "nothing.gz").as_uri(), tmp_path / "b" / "n.gz").download()
+
+    ref_ex.Extractor(tmp_path / "a" / "x.fasta.gz", tmp_path / "a" / "x.fasta").extract()
+    prep.Extractor(tmp_path / "b" / "x.fasta.gz", tmp_path / "b" / "x.fasta").extract()
+    assert (tmp_path / "a" / "x.fasta").read_bytes() == (tmp_path / "b" / "x.fasta").read_bytes() == raw
+    (tmp_path / "plain.gz").write_bytes(raw[:4000])
+    (tmp_path / "cut.gz").write_bytes(gz.read_bytes()[: gz.stat().st_size // 2])
+    for bad in ("plain.gz", "cut.gz"):
+        with pytest.raises(ref_ex.ExtractionError):
+            ref_ex.Extractor(tmp_path / bad, tmp_path / "a" / "bad.fasta").extract()
+        with pytest.raises(prep.ExtractionError):
+            prep.Extractor(tmp_path / bad, tmp_path / "b" / "bad.fasta").extract()
