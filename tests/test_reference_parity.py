@@ -1123,3 +1123,26 @@ def test_download_and_extract_steps_behave_like_the_reference(ref, tmp_path):
             ref_ex.Extractor(tmp_path / bad, tmp_path / "a" / "bad.fasta").extract()
         with pytest.raises(prep.ExtractionError):
             prep.Extractor(tmp_path / bad, tmp_path / "b" / "bad.fasta").extract()
+
+
+def test_teacher_preprocessing_and_collator_keys_match(ref):
+    """`ProtT5.preprocess` (teacher/prott5.py:67-70) against this package's teacher preprocessing on odd
+    inputs, and the batch keys of the pre-computed distillation collator (distillation/collator.py:40-60)."""
+    try:
+        from nanoplm.distillation.collator import DistillDataCollator as RefCollator
+        from nanoplm.distillation.models.teacher.prott5 import ProtT5 as RefProtT5
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference distillation import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.data.tokenizer import TeacherTokenizer
+    from nanoplm_b200.models.teacher import ProtT5
+    from nanoplm_b200.runtime.distill import DistillDataCollator
+    theirs, ours = RefProtT5(device="cpu"), ProtT5(device="cpu", random_init=True)
+    for s in ("MKTAYIAK", " mkUzob \n", "", "ACDEFGHIKLMNPQRSTVWYX", "a", "BZ*-", None):
+        assert theirs.preprocess(s) == ours.preprocess(s) == TeacherTokenizer.preprocess(s or ""), repr(s)
+    feats = [{"input_ids": torch.randint(3, 27, (16,), dtype=torch.int8), "attention_mask": torch.ones(16, dtype=torch.int8),
+              "teacher_embeddings": torch.randn(16, 1024).half()} for _ in range(3)]
+    a = RefCollator(teacher_model=None, on_the_fly=False)(feats)
+    b = DistillDataCollator(False, 16)(feats)
+    assert set(a) == set(b) == {"input_ids", "attention_mask", "teacher_embeddings"}
+    for k in a:
+        assert a[k].shape == b[k].shape and torch.equal(a[k].float(), b[k].float()), k
