@@ -135,6 +135,14 @@ class _LutTokenizer:
             return {"input_ids": out_ids[0], "attention_mask": out_mask[0]}
         return {"input_ids": out_ids, "attention_mask": out_mask}
 
+    def batch_encode_plus(self, batch_text, **kwargs):
+        """The HF spelling for a list of texts (the reference's distillation collator calls it,
+        distillation/collator.py:49-68)."""
+        return self(list(batch_text), **kwargs)
+
+    def encode_plus(self, text: str, **kwargs):
+        return self(text, **kwargs)
+
     def pad(self, examples: list[dict], return_tensors: str = "pt", **_):
         import torch
         width = max(len(e["input_ids"]) for e in examples)

@@ -1146,3 +1146,40 @@ def test_teacher_preprocessing_and_collator_keys_match(ref):
     assert set(a) == set(b) == {"input_ids", "attention_mask", "teacher_embeddings"}
     for k in a:
         assert a[k].shape == b[k].shape and torch.equal(a[k].float(), b[k].float()), k
+
+
+def test_on_the_fly_distillation_targets_match_the_reference_collator(ref):
+    """On-the-fly distillation: the reference computes the teacher embeddings inside its collator
+    with HF's `T5EncoderModel` (distillation/collator.py:36-96); here the collator only tokenises and
+    the native T5 encoder runs inside the step. Same tiny teacher weights, same sequences: the student
+    inputs are identical and the targets agree on every real token."""
+    try:
+        from transformers import T5Config, T5EncoderModel
+
+        from nanoplm.distillation.collator import DistillDataCollator as RefCollator
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference distillation import failed: {type(exc).__name__}: {exc}")
+    from nanoplm_b200.config.schema import TeacherConfig
+    from nanoplm_b200.data.tokenizer import StudentTokenizer, TeacherTokenizer
+    from nanoplm_b200.models.teacher import T5EncoderTeacher
+    from nanoplm_b200.runtime.distill import DistillDataCollator
+    torch.manual_seed(0)
+    hf = T5EncoderModel(T5Config(vocab_size=128, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_heads=4,
+                                 relative_attention_num_buckets=32, relative_attention_max_distance=128,
+                                 feed_forward_proj="relu", is_encoder_decoder=False, use_cache=False)).float().eval()
+    own = T5EncoderTeacher(TeacherConfig(vocab_size=128, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_heads=4),
+                           random_init=False).float()
+    own.load_state_dict({k: v for k, v in hf.state_dict().items() if k != "encoder.embed_tokens.weight"}, strict=True)
+    seqs = _sequences(5, 8, 40, seed=77)
+    feats = [{"raw_sequence": s} for s in seqs]
+    # the reference's collator calls `batch_encode_plus`, which the installed transformers no longer has on
+    # its tokenizers; this package's tokenizers (same ids: test_student_protx_...) still answer to it
+    a = RefCollator(teacher_model=hf, teacher_tokenizer=TeacherTokenizer(128), student_tokenizer=StudentTokenizer(),
+                    on_the_fly=True, max_seq_len=48)(feats)
+    b = DistillDataCollator(True, 48)(feats)
+    assert torch.equal(a["input_ids"], b["input_ids"]) and torch.equal(a["attention_mask"], b["attention_mask"])
+    with torch.no_grad():
+        target = own(b["teacher_input_ids"], b["teacher_attention_mask"], lengths=b["teacher_lengths"])
+    keep = b["teacher_attention_mask"].bool()
+    assert a["teacher_embeddings"].shape == target.shape
+    assert (a["teacher_embeddings"][keep] - target[keep]).abs().max().item() < 2e-4
