@@ -5,8 +5,8 @@ its two test files that still import there; `tests/test_fasta_dataset.py` no lon
 names a `LazyFastaDataset` the reference dropped, but its tests describe the shard writer, the sharded
 dataset and that lazy dataset, all of which exist here. The files import
 `nanoplm.pretraining.{collator, dataset}`, `...modern_bert.tokenizer` and `...modern_bert.modeling`; here
-those module paths are provided by a throw-away package that re-exports this package's classes, and
-pytest runs the reference's files as they are, in a child process. Skipped when no reference checkout is found (`NANOPLM_REFERENCE_DIR`, default: a
+those module paths are served by `nanoplm_b200.compat` (its pytest plugin registers them before
+collection), and pytest runs the reference's files as they are, in a child process. Skipped when no reference checkout is found (`NANOPLM_REFERENCE_DIR`, default: a
 `reference` directory beside the repository)."""
 import os
 import subprocess
@@ -19,42 +19,22 @@ ROOT = Path(__file__).resolve().parent.parent
 REF_DIR = Path(os.environ.get("NANOPLM_REFERENCE_DIR", ROOT.parent / "reference"))
 FILES = ["test_packing_collator.py", "test_pretraining_collator.py", "test_fasta_dataset.py"]
 
-SHIM = {
-    "nanoplm/__init__.py": "",
-    "nanoplm/pretraining/__init__.py": "",
-    "nanoplm/pretraining/models/__init__.py": "",
-    "nanoplm/pretraining/models/modern_bert/__init__.py": "",
-    "nanoplm/pretraining/collator.py":
-        "from nanoplm_b200.data.collators import PackingCollator, ProtDataCollatorForLM  # noqa: F401\n",
-    "nanoplm/pretraining/dataset.py":
-        "from nanoplm_b200.data.shards import LazyFastaDataset, ShardedDataset, ShardWriter  # noqa: F401\n",
-    "nanoplm/pretraining/models/modern_bert/tokenizer.py":
-        "from nanoplm_b200.data.tokenizer import ProtTokenizer as ProtModernBertTokenizer  # noqa: F401\n",
-    "nanoplm/pretraining/models/modern_bert/modeling.py":
-        "from nanoplm_b200.models.encoder import position_ids_from_cu_seqlens as _position_ids_from_cu_seqlens"
-        "  # noqa: F401\n",
-}
-
-
 @pytest.mark.skipif(not all((REF_DIR / "tests" / f).exists() for f in FILES), reason="no reference checkout")
 def test_reference_unit_tests_pass_on_this_package(tmp_path):
-    shim = tmp_path / "shim"
-    for rel, text in SHIM.items():
-        p = shim / rel
-        p.parent.mkdir(parents=True, exist_ok=True)
-        p.write_text(text)
     (tmp_path / "empty.ini").write_text("[pytest]\n")
-    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(shim), str(ROOT)]), CUDA_VISIBLE_DEVICES="")
-    # no conftest, no ini file and importlib import mode: nothing of the reference's source tree gets on sys.path
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    # no conftest, no ini file and importlib import mode: nothing of the reference's source tree gets on
+    # sys.path; the plugin registers the `nanoplm.*` names before the test modules are imported
     cmd = [sys.executable, "-m", "pytest", *[str(REF_DIR / "tests" / f) for f in FILES], "--noconftest",
-           "-p", "no:cacheprovider", "-c", str(tmp_path / "empty.ini"), "--rootdir", str(tmp_path),
-           "--import-mode=importlib", "-q", "-rA"]
+           "-p", "no:cacheprovider", "-p", "nanoplm_b200.compat.pytest_plugin", "-c", str(tmp_path / "empty.ini"),
+           "--rootdir", str(tmp_path), "--import-mode=importlib", "-q", "-rA"]
     out = subprocess.run(cmd, cwd=tmp_path, env=env, capture_output=True, text=True, timeout=900)
     text = out.stdout + out.stderr
     assert out.returncode == 0, text[-4000:]
     assert "34 passed" in text and "failed" not in text.split("short test summary info")[-1], text[-2000:]
     # the classes under test came from this package, not from the reference
-    probe = subprocess.run([sys.executable, "-c", "import nanoplm.pretraining.collator as c; "
+    probe = subprocess.run([sys.executable, "-c", "import nanoplm_b200.compat as k; k.install(force=True); "
+                            "import nanoplm.pretraining.collator as c; "
                             "print(c.PackingCollator.__module__, c.ProtDataCollatorForLM.__module__)"],
                            cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
     assert probe.stdout.split() == ["nanoplm_b200.data.collators", "nanoplm_b200.data.collators"], probe.stderr[-2000:]

@@ -1183,3 +1183,119 @@ def test_on_the_fly_distillation_targets_match_the_reference_collator(ref):
     keep = b["teacher_attention_mask"].bool()
     assert a["teacher_embeddings"].shape == target.shape
     assert (a["teacher_embeddings"][keep] - target[keep]).abs().max().item() < 2e-4
+
+
+def test_compat_table_names_exist_in_the_reference_with_compatible_signatures(ref):
+    """Every `nanoplm.*` name that `nanoplm_b200.compat` serves exists in the reference under that
+    module path (except the few listed, which the reference dropped or never had), and what it resolves
+    to here accepts every parameter of the reference's callable, by keyword and, for the required
+    ones, in the same position."""
+    import importlib
+    import inspect
+
+    from nanoplm_b200 import compat
+    extras = {("nanoplm", "__version__"), ("nanoplm.cli", "main"), ("nanoplm.pretraining.dataset", "LazyFastaDataset"),
+              ("nanoplm.config.datasets", "get_supported_datasets")}
+
+    def params(obj):
+        f = obj.__init__ if inspect.isclass(obj) else obj
+        try:
+            sig = inspect.signature(f)
+        except (TypeError, ValueError):
+            return None, False
+        ps = [p for p in sig.parameters.values() if p.name != "self"]
+        return ([p for p in ps if p.kind not in (p.VAR_KEYWORD, p.VAR_POSITIONAL)],
+                any(p.kind == p.VAR_KEYWORD for p in ps))
+
+    checked = 0
+    for mod_name, table in compat.MODULES.items():
+        try:
+            theirs_mod = importlib.import_module(mod_name)
+        except Exception as exc:                                   # an optional dependency of the reference
+            if table:
+                pytest.fail(f"reference module {mod_name} does not import: {exc}")
+            continue
+        for name, target in table.items():
+            if (mod_name, name) in extras:
+                continue
+            assert hasattr(theirs_mod, name), f"{mod_name}.{name} is not a name of the reference"
+            theirs = getattr(theirs_mod, name)
+            where, _, what = target.partition(":")
+            ours = getattr(importlib.import_module(where), what or name)
+            if not callable(theirs) or mod_name.endswith(".modeling") or name in ("cli", "logger"):
+                continue
+            pr, _ = params(theirs)
+            po, ours_kwargs = params(ours)
+            if pr is None or po is None:
+                continue
+            own_names = [p.name for p in po]
+            for i, p in enumerate(pr):
+                assert p.name in own_names or ours_kwargs, f"{mod_name}.{name}: parameter {p.name!r} not accepted here"
+                if p.default is inspect.Parameter.empty and p.name in own_names:
+                    assert own_names.index(p.name) == i, f"{mod_name}.{name}: {p.name!r} is at another position"
+            checked += 1
+    assert checked > 45
+
+
+def test_one_script_runs_on_the_reference_and_on_this_package(ref, tmp_path):
+    """A training script written against the reference's Python API (`nanoplm.pretraining.*` imports,
+    `run_pure_pretraining(model, PretrainingConfig, PureTorchConfig, ResumeConfig)`) runs unchanged in
+    two child processes: with the reference package on the path, and with only
+    `nanoplm_b200.compat.install()` in front of it. Both train, save the same checkpoint files and resume."""
+    import subprocess
+    script = tmp_path / "train.py"
+    script.write_text('''
+import os, sys, types
+os.environ["WANDB_MODE"] = "disabled"
+if os.environ.get("USE_COMPAT") == "1":
+    import nanoplm_b200.compat
+    nanoplm_b200.compat.install()
+else:   # optional third-party modules the reference imports without using them here
+    for name, attrs in (("IPython", {"get_ipython": lambda: None}), ("h5py", {"File": object}), ("Bio", {}), ("Bio.SeqIO", {})):
+        try:
+            __import__(name)
+        except Exception:
+            m = types.ModuleType(name)
+            for k, v in attrs.items():
+                setattr(m, k, v)
+            sys.modules[name] = m
+    sys.modules["Bio"].SeqIO = sys.modules["Bio.SeqIO"]
+import torch
+from pathlib import Path
+from nanoplm.pretraining.pure_pipeline import run_pure_pretraining
+from nanoplm.pretraining.config import PretrainingConfig, PureTorchConfig, ResumeConfig
+from nanoplm.pretraining.models.modern_bert.model import ProtModernBertMLMConfig
+from nanoplm.pretraining.models.modern_bert.pure_model import PureProtModernBertMLM
+from nanoplm.data.validation import validate_pretrain_dataset
+from nanoplm.pretraining.dataset import ShardedDataset
+
+out = sys.argv[1]
+info = validate_pretrain_dataset("ds")
+assert len(ShardedDataset(data_dir="ds/train")) == info["manifest"].train_sequences == 96
+def model():
+    torch.manual_seed(0)
+    return PureProtModernBertMLM(ProtModernBertMLMConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                                                         num_attention_heads=2, max_position_embeddings=64))
+cfg = PretrainingConfig(dataset_dir="ds", ckp_dir=out, micro_batch_size=8, global_batch_size=8 * 64 * 2, num_epochs=1,
+                        logging_steps=1, eval_steps=2, save_steps=2, num_workers=0, bf16=False, tf32=False)
+run_pure_pretraining(model(), cfg, PureTorchConfig(use_compile=False, use_packing=False), None)
+run = next(Path(out).glob("run-*"))
+cfg.num_epochs = 1
+run_pure_pretraining(model(), cfg, PureTorchConfig(use_compile=False, use_packing=False),
+                     ResumeConfig(is_resume=True, checkpoint_dir=str(run / "checkpoint-2"), extra_epochs=1))
+print("RESULT", sorted(p.name for p in run.iterdir() if p.name.startswith("checkpoint-")),
+      sorted(p.name for p in (run / "checkpoint-2").iterdir()))
+''')
+    from nanoplm_b200.data.synthetic import write_synthetic_dataset
+    write_synthetic_dataset(tmp_path / "ds", 96, 16, 10, 60, samples_per_shard=48)
+    results = {}
+    for arm, path, flag in (("reference", os.pathsep.join([str(REF), str(ROOT)]), "0"), ("compat", str(ROOT), "1")):
+        env = dict(os.environ, PYTHONPATH=path, USE_COMPAT=flag, CUDA_VISIBLE_DEVICES="")
+        for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+            env.pop(k, None)
+        out = subprocess.run([sys.executable, str(script), f"ckpt_{arm}"], cwd=tmp_path, env=env, capture_output=True,
+                             text=True, timeout=900)
+        assert out.returncode == 0, f"{arm}: " + (out.stdout + out.stderr)[-3000:]
+        results[arm] = [l for l in out.stdout.splitlines() if l.startswith("RESULT")][-1]
+    assert results["reference"] == results["compat"], results
+    assert "checkpoint-6" in results["compat"] and "optimizer.pt" in results["compat"]

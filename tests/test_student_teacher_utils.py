@@ -121,3 +121,29 @@ def test_dataset_url_table_matches_the_reference_keys():
         resolve_dataset_url("pfam", None)
     with pytest.raises(KeyError):
         resolve_dataset_url(None, None)
+
+
+def test_compat_student_utilities_follow_the_reference_call_convention(tmp_path):
+    """`nanoplm.distillation.models.student.ProtX.<utility>` as served by `nanoplm_b200.compat`: static
+    methods taking (embed_dim, num_layers, num_heads, ...) or a checkpoint path, the embedding
+    generator yielding (sequence, tensor) pairs (student/model.py:111-497)."""
+    from safetensors.torch import save_file
+
+    from nanoplm_b200.compat.adapters import ProtX
+    m = _student()
+    save_file({k: v.contiguous() for k, v in m.state_dict().items()}, str(tmp_path / "model.safetensors"))
+    assert ProtX.inspect_checkpoint_architecture(str(tmp_path / "model.safetensors")) == (64, 3, 1)
+    with pytest.raises(FileNotFoundError):
+        ProtX.inspect_checkpoint_architecture(str(tmp_path / "missing.safetensors"))
+    n = ProtX.calculate_model_parameters(64, 3, 2)
+    assert n == sum(p.numel() for p in ProtX(StudentConfig(hidden_size=64, intermediate_size=256, num_hidden_layers=3,
+                                                           num_attention_heads=2)).parameters())
+    assert ProtX.calculate_model_parameters(64, 3, 2, projection_layer=False) == n - 64 * 1024 - 1024
+    ProtX.print_parameter_breakdown(64, 3, 2)
+    seqs = ["MKTAYIAKQRQISFVK", "ACDEFG"]
+    pooled = list(ProtX.load_and_generate_embeddings(str(tmp_path / "model.safetensors"), iter(seqs), batch_size=2,
+                                                     device="cpu"))
+    assert [s for s, _ in pooled] == seqs and all(tuple(e.shape) == (64,) for _, e in pooled)
+    per_tok = list(ProtX.load_and_generate_embeddings(str(tmp_path / "model.safetensors"), seqs, device="cpu",
+                                                      per_seq_embeddings=False, max_length=5))
+    assert [tuple(e.shape) for _, e in per_tok] == [(4, 64), (4, 64)]          # truncated to max_length - 1 residues
