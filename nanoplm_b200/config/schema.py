@@ -47,7 +47,10 @@ class ModelConfig:
     max_position_embeddings: int = 1024
     # --- fixed in the reference's internal config (modeling.py:39-96); exposed here -------------
     hidden_activation: str = "gelu"
+    initializer_range: float = 0.02      # std of the (tied) embedding / decoder initialisation
     norm_eps: float = 1e-5
+    norm_bias: bool = False              # a bias vector in every norm
+    classifier_bias: bool = False        # a bias in the prediction head's dense layer
     global_attn_every_n_layers: int = 3
     local_attention: int = 128
     global_rope_theta: float = 160_000.0
@@ -55,6 +58,7 @@ class ModelConfig:
     decoder_bias: bool = True
     tie_word_embeddings: bool = True
     sparse_prediction: bool = False
+    sparse_pred_ignore_index: int = -100  # label value of the positions that carry no target
     pad_token_id: int = 0
     eos_token_id: int = 1
     unk_token_id: int = 2

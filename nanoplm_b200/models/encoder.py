@@ -37,28 +37,34 @@ class Linear(nn.Module):
 
 
 class Norm(nn.Module):
-    def __init__(self, dim: int, eps: float, rms: bool = False):
+    def __init__(self, dim: int, eps: float, rms: bool = False, bias: bool = False):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(dim))
+        # the optional bias (`norm_bias`, off in every reference recipe) is a plain add after the kernel
+        self.bias = nn.Parameter(torch.zeros(dim)) if bias else None
         self.eps, self.rms = eps, rms
 
     def forward(self, x):
-        return ops.norm(x, self.weight, self.eps, self.rms)
+        y = ops.norm(x, self.weight, self.eps, self.rms)
+        return y if self.bias is None else y + self.bias.to(y.dtype)
 
     def with_residual(self, x):
         """(norm(x), x): the second value is the skip connection of a pre-norm block."""
-        return ops.norm_residual(x, self.weight, self.eps, self.rms)
+        y, skip = ops.norm_residual(x, self.weight, self.eps, self.rms)
+        return (y if self.bias is None else y + self.bias.to(y.dtype)), skip
 
 
 class Embeddings(nn.Module):
     def __init__(self, cfg: ModelConfig):
         super().__init__()
         self.tok_embeddings = nn.Embedding(cfg.vocab_size, cfg.hidden_size, padding_idx=cfg.pad_token_id)
-        self.norm = Norm(cfg.hidden_size, cfg.norm_eps, cfg.norm_type == "rmsnorm")
+        self.norm = Norm(cfg.hidden_size, cfg.norm_eps, cfg.norm_type == "rmsnorm", cfg.norm_bias)
         self.p_drop = float(cfg.embedding_dropout)
 
     def forward(self, ids):
         x = ops.embed_norm(ids, self.tok_embeddings.weight, self.norm.weight, self.norm.eps, self.norm.rms)
+        if self.norm.bias is not None:
+            x = x + self.norm.bias.to(x.dtype)
         if self.p_drop > 0.0 and self.training:     # reference: modeling.py:220-223
             x = F.dropout(x, self.p_drop, True)
         return x
@@ -130,9 +136,9 @@ class EncoderLayer(nn.Module):
         self.layer_idx = layer_idx
         self.attention_type = cfg.layer_types[layer_idx]
         rms = cfg.norm_type == "rmsnorm"
-        self.attn_norm = nn.Identity() if layer_idx == 0 else Norm(cfg.hidden_size, cfg.norm_eps, rms)
+        self.attn_norm = nn.Identity() if layer_idx == 0 else Norm(cfg.hidden_size, cfg.norm_eps, rms, cfg.norm_bias)
         self.attn = Attention(cfg)
-        self.mlp_norm = Norm(cfg.hidden_size, cfg.norm_eps, rms)
+        self.mlp_norm = Norm(cfg.hidden_size, cfg.norm_eps, rms, cfg.norm_bias)
         self.is_moe = cfg.is_moe_layer(layer_idx)
         if self.is_moe:
             from .moe import MoEMLP
@@ -191,7 +197,7 @@ class EncoderModel(nn.Module):
         self.config = cfg
         self.embeddings = Embeddings(cfg)
         self.layers = nn.ModuleList([EncoderLayer(cfg, i) for i in range(cfg.num_hidden_layers)])
-        self.final_norm = Norm(cfg.hidden_size, cfg.norm_eps, cfg.norm_type == "rmsnorm")
+        self.final_norm = Norm(cfg.hidden_size, cfg.norm_eps, cfg.norm_type == "rmsnorm", cfg.norm_bias)
         self._rope_cache: dict = {}
 
     def rope(self, device) -> dict:
@@ -231,8 +237,8 @@ class EncoderModel(nn.Module):
 class PredictionHead(nn.Module):
     def __init__(self, cfg: ModelConfig):
         super().__init__()
-        self.dense = Linear(cfg.hidden_size, cfg.hidden_size, False)
-        self.norm = Norm(cfg.hidden_size, cfg.norm_eps, cfg.norm_type == "rmsnorm")
+        self.dense = Linear(cfg.hidden_size, cfg.hidden_size, cfg.classifier_bias)
+        self.norm = Norm(cfg.hidden_size, cfg.norm_eps, cfg.norm_type == "rmsnorm", cfg.norm_bias)
         self.act = cfg.classifier_activation
 
     def forward(self, x):
@@ -272,11 +278,13 @@ class ProtEncoderMLM(nn.Module):
     def init_weights(self) -> None:
         cfg = self.config
         bound = math.sqrt(3.0 / cfg.hidden_size)
-        emb_std = 0.02 if cfg.tie_word_embeddings else 1.0
+        emb_std = float(cfg.initializer_range) if cfg.tie_word_embeddings else 1.0
         nn.init.normal_(self.model.embeddings.tok_embeddings.weight, 0.0, emb_std)
         for m in self.modules():
             if isinstance(m, Norm):
                 nn.init.ones_(m.weight)
+                if m.bias is not None:
+                    nn.init.zeros_(m.bias)
         for layer in self.model.layers:
             nn.init.uniform_(layer.attn.Wqkv.weight, -bound, bound)
             nn.init.zeros_(layer.attn.Wo.weight)
@@ -289,6 +297,8 @@ class ProtEncoderMLM(nn.Module):
                 if lin.bias is not None:
                     nn.init.zeros_(lin.bias)
         nn.init.uniform_(self.head.dense.weight, -bound, bound)
+        if self.head.dense.bias is not None:
+            nn.init.zeros_(self.head.dense.bias)
         nn.init.normal_(self.decoder.weight, 0.0, emb_std if cfg.tie_word_embeddings else 0.001)
         if self.decoder.bias is not None:
             nn.init.zeros_(self.decoder.bias)
@@ -362,7 +372,8 @@ class ProtEncoderMLM(nn.Module):
 
         # the head only sees positions that carry a label: same loss, a fraction of the work
         if masked_idx is None:
-            masked_idx = torch.nonzero(flat_labels != -100, as_tuple=False).flatten().to(torch.int32)
+            masked_idx = torch.nonzero(flat_labels != cfg.sparse_pred_ignore_index,
+                                       as_tuple=False).flatten().to(torch.int32)
             masked_labels = flat_labels[masked_idx.long()]
         want_logits = bool(return_logits)
         if masked_idx.numel() == 0:

@@ -1299,3 +1299,48 @@ print("RESULT", sorted(p.name for p in run.iterdir() if p.name.startswith("check
         results[arm] = [l for l in out.stdout.splitlines() if l.startswith("RESULT")][-1]
     assert results["reference"] == results["compat"], results
     assert "checkpoint-6" in results["compat"] and "optimizer.pt" in results["compat"]
+
+
+def test_internal_config_knobs_match_the_reference_model(ref):
+    """The knobs of the reference's internal `ModernBertConfig` that no YAML exposes
+    (modeling.py:39-96): with `norm_bias`, `classifier_bias`, `mlp_bias`, `attention_bias`, the GLU
+    MLP variant, a ReLU classifier, another global-attention period and window switched on, the
+    reference's `ModernBertForMaskedLM` and this package's encoder have the same keys and, with the same
+    weights, the same logits and loss."""
+    from nanoplm.pretraining.models.modern_bert import modeling as M
+
+    from nanoplm_b200.config.schema import ModelConfig
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    knobs = dict(hidden_size=64, intermediate_size=96, num_hidden_layers=5, num_attention_heads=4, vocab_size=32,
+                 max_position_embeddings=256, mlp_activation="glu", hidden_activation="gelu", mlp_bias=True,
+                 attention_bias=True, norm_bias=True, classifier_bias=True, classifier_activation="relu",
+                 global_attn_every_n_layers=2, local_attention=32, norm_eps=1e-6, decoder_bias=True,
+                 global_rope_theta=50000.0, local_rope_theta=5000.0)
+    torch.manual_seed(0)
+    rm = M.ModernBertForMaskedLM(M.ModernBertConfig(pad_token_id=0, eos_token_id=1, bos_token_id=None, unk_token_id=2,
+                                                    mask_token_id=3, **knobs)).float().eval()
+    with torch.no_grad():
+        for p in rm.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+    om = ProtEncoderMLM(ModelConfig(**knobs), ProtTokenizer()).float().eval()
+    assert set(om.state_dict()) == set(rm.state_dict())
+    assert om.config.layer_types == rm.config.layer_types and om.config.sliding_window == rm.config.sliding_window
+    om.load_state_dict(rm.state_dict(), strict=True)
+    tok = ProtTokenizer()
+    enc = tok(_sequences(4, 30, 120, seed=8), padding=True, return_tensors="pt")
+    keep = enc["attention_mask"].bool()
+    labels = torch.where(keep & (torch.arange(enc["input_ids"].shape[1])[None, :] % 4 == 1), enc["input_ids"],
+                         torch.full_like(enc["input_ids"], -100))
+    with torch.no_grad():
+        a = rm(input_ids=enc["input_ids"], attention_mask=enc["attention_mask"], labels=labels)
+        b_logits = om(enc["input_ids"], enc["attention_mask"])["logits"]
+        b_loss = om(enc["input_ids"], enc["attention_mask"], labels=labels)["loss"]
+    assert (a["logits"][keep] - b_logits[keep]).abs().max().item() < 2e-4 * max(1.0, a["logits"][keep].abs().max().item())
+    assert abs(float(a["loss"]) - float(b_loss)) < 2e-4 * max(1.0, float(a["loss"]))
+    # every bias starts at zero on both sides
+    fresh_r = M.ModernBertForMaskedLM(M.ModernBertConfig(**knobs)).state_dict()
+    fresh_o = ProtEncoderMLM(ModelConfig(**knobs), ProtTokenizer()).state_dict()
+    for k in fresh_r:
+        if k.endswith(".bias"):
+            assert float(fresh_r[k].abs().max()) == 0.0 and float(fresh_o[k].abs().max()) == 0.0, k
