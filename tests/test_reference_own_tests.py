@@ -38,3 +38,37 @@ def test_reference_unit_tests_pass_on_this_package(tmp_path):
                             "print(c.PackingCollator.__module__, c.ProtDataCollatorForLM.__module__)"],
                            cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
     assert probe.stdout.split() == ["nanoplm_b200.data.collators", "nanoplm_b200.data.collators"], probe.stderr[-2000:]
+
+
+@pytest.mark.skipif(not (REF_DIR / "README.md").exists(), reason="no reference checkout")
+def test_yaml_examples_of_the_reference_readme_load_here():
+    """The three YAML files printed in the reference's README (params.yaml, pretrain.yaml, distill.yaml;
+    README.md:91-333, whose values differ from the `get-yaml` templates) pass this package's strict
+    loaders unchanged."""
+    import re
+
+    import yaml
+
+    from nanoplm_b200.config import loaders
+    blocks = [yaml.safe_load(b) for b in re.findall(r"```ya?ml\n(.*?)```", (REF_DIR / "README.md").read_text(), flags=re.S)]
+    blocks = [b for b in blocks if isinstance(b, dict)]
+    kinds = set()
+    for doc in blocks:
+        if "pretraining" in doc:
+            model = loaders.load_model_config(doc["model"])
+            cfg = loaders.load_pretrain_config(doc["pretraining"])
+            enabled, pure = loaders.resolve_pure_torch_config(doc)
+            loaders.load_resume_config(doc.get("resume"))
+            assert model.hidden_size > 0 and cfg.global_batch_size > 0 and isinstance(enabled, bool) and pure is not None
+            kinds.add("pretrain")
+        elif "distillation" in doc:
+            student = loaders.load_student_config(doc["model"])
+            cfg = loaders.load_distill_config(doc["distillation"])
+            loaders.load_resume_config(doc.get("resume"))
+            assert student.projection_layer in (True, False) and cfg.batch_size > 0
+            kinds.add("distill")
+        elif "data_params" in doc:
+            assert {"pretrain_config", "distillation_config", "data_dirs"} <= set(doc)
+            assert doc["data_params"]["pipeline_mode"] in ("none", "pretrain", "distillation")
+            kinds.add("data")
+    assert kinds == {"pretrain", "distill", "data"}
