@@ -243,3 +243,34 @@ def test_cli_data_single_steps_with_the_reference_option_spellings(tmp_path, mon
                             "--total-sequences", str(n_val - 2)])
     assert r.exit_code == 0, r.output + str(r.exception)
     assert sum(count_kd_sequences(p) for p in (tmp_path / "kd_parts").iterdir()) == n_val - 2
+
+
+def test_cli_pretrain_run_with_options(tmp_path, monkeypatch):
+    """`pretrain run` takes the settings as options (the reference's spellings included:
+    --adam-warmup-ratio, --compile / --no-compile, --use-packing / --no-packing) and, with
+    --no-pure-torch, runs the HF-Trainer recipe."""
+    from nanoplm_b200.data.synthetic import write_synthetic_dataset
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("WANDB_MODE", "disabled")
+    write_synthetic_dataset(tmp_path / "ds", 64, 16, 10, 60, samples_per_shard=32)
+    runner = CliRunner()
+    base = ["pretrain", "run", "--dataset-dir", "ds", "--micro-batch-size", "8", "--global-batch-size", str(8 * 64),
+            "--num-epochs", "1", "--logging-steps", "1", "--eval-steps", "4", "--save-steps", "2", "--num-workers", "0",
+            "--no-bf16", "--hidden-size", "32", "--intermediate-size", "64", "--num-hidden-layers", "1",
+            "--num-attention-heads", "2", "--max-position-embeddings", "64", "--adam-warmup-ratio", "0.25",
+            "--no-compile"]
+    r = runner.invoke(cli, base + ["--ckp-dir", "a", "--use-packing", "--target-packed-rows", "3"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    run = next((tmp_path / "a").glob("run-*"))
+    # 64 sequences / 8 per micro-batch / 2 micro-batches per step = 4 steps, one of them warm-up
+    assert (run / "checkpoint-4" / "pytorch_model.bin").exists() and not (run / "checkpoint-4" / "model.safetensors").exists()
+    lines = [json.loads(l) for l in (run / "metrics.jsonl").read_text().splitlines() if "train/learning_rate" in l]
+    assert [l["train/learning_rate"] for l in lines[:2]] == [0.0, pytest.approx(1e-3)]
+    r = runner.invoke(cli, base + ["--ckp-dir", "b", "--no-packing", "--no-pure-torch"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    run = next((tmp_path / "b").glob("run-*"))
+    assert (run / "checkpoint-4" / "model.safetensors").exists() and (run / "checkpoint-4" / "trainer_state.json").exists()
+    r = runner.invoke(cli, base + ["--ckp-dir", "b", "--resume-from", str(run / "checkpoint-2"), "--extra-epochs", "1"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    assert (run / "checkpoint-8").exists() and len(list(run.glob("archived_*"))) == 1
+    assert runner.invoke(cli, base + ["--optimizer", "sgd"]).exit_code == 2
