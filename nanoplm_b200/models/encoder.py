@@ -384,6 +384,17 @@ class ProtEncoderMLM(nn.Module):
             hm = self.head(self.model.final_norm(xm))
             loss, logits = ops.mlm_cross_entropy(hm, self.decoder.weight, self.decoder.bias,
                                                  masked_labels, want_logits)
+        if want_logits and not cfg.sparse_prediction:
+            # asked for logits next to the loss: every position, in the input's layout, as the
+            # reference returns them (modeling.py:659-669, 713-725); with `sparse_prediction` only
+            # the rows that carry a label (modeling.py:707-711). Training never asks.
+            with torch.no_grad():
+                logits = self.decoder_logits(self.head(self.model.final_norm(x)))
+            if pad_info is not None:
+                indices, B, S = pad_info
+                full = torch.zeros((B * S, logits.shape[-1]), dtype=logits.dtype, device=logits.device)
+                full[indices] = logits
+                logits = full.view(B, S, -1)
         if aux is not None:
             loss = loss + cfg.moe.aux_loss_coef * aux
         return {"loss": loss, "logits": logits, "aux_loss": aux}

@@ -1338,6 +1338,20 @@ def test_internal_config_knobs_match_the_reference_model(ref):
         b_loss = om(enc["input_ids"], enc["attention_mask"], labels=labels)["loss"]
     assert (a["logits"][keep] - b_logits[keep]).abs().max().item() < 2e-4 * max(1.0, a["logits"][keep].abs().max().item())
     assert abs(float(a["loss"]) - float(b_loss)) < 2e-4 * max(1.0, float(a["loss"]))
+    # logits next to the loss: every position without `sparse_prediction`, the labelled rows only with it
+    with torch.no_grad():
+        both = om(enc["input_ids"], enc["attention_mask"], labels=labels, return_logits=True)
+        assert both["logits"].shape == a["logits"].shape
+        assert (a["logits"][keep] - both["logits"][keep]).abs().max().item() < 2e-4 * max(1.0, a["logits"][keep].abs().max().item())
+        rs = M.ModernBertForMaskedLM(M.ModernBertConfig(sparse_prediction=True, **knobs)).float().eval()
+        rs.load_state_dict(rm.state_dict())
+        os_ = ProtEncoderMLM(ModelConfig(sparse_prediction=True, **knobs), ProtTokenizer()).float().eval()
+        os_.load_state_dict(rm.state_dict())
+        sa = rs(input_ids=enc["input_ids"], attention_mask=enc["attention_mask"], labels=labels)
+        sb = os_(enc["input_ids"], enc["attention_mask"], labels=labels, return_logits=True)
+    assert sa["logits"].shape == sb["logits"].shape == (int((labels != -100).sum()), 32)
+    assert (sa["logits"] - sb["logits"]).abs().max().item() < 2e-4 * max(1.0, sa["logits"].abs().max().item())
+    assert abs(float(sa["loss"]) - float(sb["loss"])) < 2e-4 * max(1.0, float(sa["loss"]))
     # every bias starts at zero on both sides
     fresh_r = M.ModernBertForMaskedLM(M.ModernBertConfig(**knobs)).state_dict()
     fresh_o = ProtEncoderMLM(ModelConfig(**knobs), ProtTokenizer()).state_dict()
