@@ -50,6 +50,13 @@ class PureProtModernBertMLM(ProtEncoderMLM):
     def __init__(self, config: ModelConfig):
         super().__init__(config, ProtTokenizer())
 
+    def forward(self, *args, **kwargs):
+        # the reference returns logits together with the loss; in evaluation mode so does this class
+        # (in training mode they would only cost time: the training loop never reads them)
+        if kwargs.get("labels") is not None and kwargs.get("return_logits") is None and not self.training:
+            kwargs["return_logits"] = True
+        return super().forward(*args, **kwargs)
+
 
 class ProtX(_ProtX):
     """student/model.py:50-497: `ProtX(config)` and its static utilities with the reference's signatures."""
