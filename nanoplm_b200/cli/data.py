@@ -23,7 +23,6 @@ from nanoplm_b200.data.fasta import count_fasta
 from nanoplm_b200.data.manifest import DistillationManifest, PretrainManifest, write_manifest
 from nanoplm_b200.data.prep import (DownloadError, Downloader, ExtractionError, Extractor, FastaShuffler,
                                     FilterError, Filterer, ShufflingError, SplitError, Splitor)
-from nanoplm_b200.utils.logging import logger
 
 
 @click.group(help="Group of commands for dataset download and preparation.")
@@ -46,7 +45,7 @@ def _resolve(p, cwd: Path) -> Path:
 
 # ----------------------------------------------------------------------------------- simple steps
 @data.command("download", help="Download a dataset by key (see --help for keys) or from --url.")
-@click.argument("dataset", required=False)
+@click.argument("dataset", required=False, type=click.Choice(sorted(DATASET_URLS), case_sensitive=False))
 @click.option("--url", default=None, help="Explicit download URL (instead of a dataset key).")
 @click.option("-o", "--output", "output", default="downloaded_dataset", show_default=True,
               type=click.Path(path_type=Path), help="Target file, or a directory (the file keeps the URL's name).")

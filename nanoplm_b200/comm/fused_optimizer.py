@@ -25,7 +25,7 @@ from ctypes import c_double, c_int, c_longlong, c_uint, c_void_p
 import torch
 import torch.distributed as dist
 
-from nanoplm_b200.ops._lib import CommTimeout, check_rc, count_launch, lib, ptr, status_word, stream_ptr
+from nanoplm_b200.ops._lib import check_rc, count_launch, lib, ptr, status_word, stream_ptr
 from nanoplm_b200.utils.logging import logger
 
 MAX_PEERS = 8

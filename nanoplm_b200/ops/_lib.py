@@ -7,7 +7,6 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from pathlib import Path
 
 import torch
 

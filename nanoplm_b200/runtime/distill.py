@@ -23,7 +23,7 @@ from torch.utils.data import DataLoader
 
 from nanoplm_b200.config.schema import DistillationConfig, ResumeConfig, StudentConfig, as_plain_dict
 from nanoplm_b200.data.kd_dataset import KDDatasetOnTheFly, LoadKDDataset
-from nanoplm_b200.data.manifest import DistillationManifest, get_dataset_paths, read_manifest
+from nanoplm_b200.data.manifest import DistillationManifest, get_dataset_paths
 from nanoplm_b200.data.tokenizer import StudentTokenizer, TeacherTokenizer
 from nanoplm_b200.data.validation import validate_distillation_dataset
 from nanoplm_b200.models.student import ProtX

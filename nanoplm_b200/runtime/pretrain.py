@@ -27,8 +27,7 @@ import torch
 import torch.distributed as dist
 from torch.utils.data import DataLoader, Sampler
 
-from nanoplm_b200.config.schema import (ModelConfig, PretrainingConfig, PureTorchConfig, ResumeConfig,
-                                         as_plain_dict)
+from nanoplm_b200.config.schema import PretrainingConfig, PureTorchConfig, ResumeConfig, as_plain_dict
 from nanoplm_b200.data.collators import PackingCollator, ProtDataCollatorForLM
 from nanoplm_b200.data.manifest import read_manifest, validate_manifest_for_pipeline
 from nanoplm_b200.data.shards import ShardedDataset
