@@ -69,6 +69,15 @@ ds = LoadKDDataset(h5_path=out, device="cpu", seed=1, sharded=False)
 assert len(ds) == n_val - 1 and ds[0]["teacher_embeddings"].shape == (48, 32)
 parts = shard_h5_file(input_h5_path=out, n_sharded_files=2, output_dir=work / "kd2", total_sequences=len(ds))
 assert len(parts) == 2
+from nanoplm.data.validation import validate_hdf5_shards, ValidationError
+from nanoplm.pretraining.optim import is_muon_optimizer
+assert [Path(f).name for f in validate_hdf5_shards(work / "kd2", expected_count=2)] == sorted(Path(f).name for f in parts)
+try:
+    validate_hdf5_shards(work / "kd2", expected_count=3)
+    raise SystemExit("a wrong shard count must be refused")
+except ValidationError:
+    pass
+assert is_muon_optimizer(torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1)) is False
 feats = [ds[i] for i in range(3)]
 batch = DistillDataCollator(on_the_fly=False)(feats)
 assert batch["teacher_embeddings"].shape == (3, 48, 32)
@@ -83,6 +92,24 @@ student = ProtX(ProtXConfig(hidden_size=32, intermediate_size=64, num_hidden_lay
 h = student(fly["input_ids"], fly["attention_mask"], training_mode=True)
 h = h["last_hidden_state"] if isinstance(h, dict) else h.last_hidden_state
 assert h.shape == (3, 48, 1024)
+# distillation through the reference's entry point and keyword names
+import os
+os.environ["WANDB_MODE"] = "disabled"
+from nanoplm.distillation.pipeline import DistillationConfig, ResumeConfig as DResume, run_distillation
+from nanoplm.data.manifest import DistillationManifest, write_manifest
+kd = work / "kd_fly"
+write_synthetic_fasta(kd / "train.fasta", 32, 10, 40, seed=1)
+write_synthetic_fasta(kd / "val.fasta", 8, 10, 40, seed=2)
+write_manifest(kd, DistillationManifest(pipeline_mode="distillation", seqs_num=40, min_seq_len=10, max_seq_len=48,
+                                        val_ratio=0.2, train_dir=".", val_dir=".", train_sequences=32, val_sequences=8,
+                                        teacher_model="prott5", on_the_fly=True, train_fasta="train.fasta",
+                                        val_fasta="val.fasta"))
+dcfg = DistillationConfig(dataset_dir=str(kd), ckp_dir=str(work / "dck"), num_epochs=1, batch_size=8, logging_steps=1,
+                          eval_steps=2, save_steps=2, bf16=False, teacher_random_init=True,
+                          teacher=TeacherConfig(d_model=1024, d_kv=8, d_ff=32, num_layers=1, num_heads=2))
+res = run_distillation(model_config=ProtXConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2),
+                       distill_config=dcfg, resume_config=DResume(is_resume=False, checkpoint_dir="", extra_epochs=None))
+assert res["global_step"] == 4 and (Path(res["output_dir"]) / "checkpoint-4" / "model.safetensors").exists()
 (work / "c.yaml").write_text("a: {b: 1}\n")
 assert read_yaml(work / "c.yaml") == {"a": {"b": 1}} and get_device() in ("cpu", "cuda")
 try:
