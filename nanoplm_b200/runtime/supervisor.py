@@ -164,11 +164,21 @@ class Supervisor:
 
     # ---- the loop ----------------------------------------------------------------------------
     def run(self) -> int:
+        # the ranks live in sessions of their own, so a SIGTERM to the supervisor would orphan them:
+        # turn it into an exit that runs the `finally` blocks (which end the ranks)
+        import threading
+        previous = None
+        if threading.current_thread() is threading.main_thread():
+            def _terminate(signum, frame):
+                raise SystemExit(128 + signum)
+            previous = signal.signal(signal.SIGTERM, _terminate)
         try:
             return self._run()
         finally:
             import shutil
             shutil.rmtree(self._work, ignore_errors=True)      # the per-attempt YAML files
+            if previous is not None:
+                signal.signal(signal.SIGTERM, previous)
 
     def _run(self) -> int:
         resume_from: Optional[Path] = None

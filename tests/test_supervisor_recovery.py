@@ -142,3 +142,35 @@ def test_distillation_job_restarts_after_a_rank_raises(tmp_path, monkeypatch):
     assert steps[-1] == 8 and sorted(set(steps)) == list(range(1, 9)) and (run / "checkpoint-8").exists()
     assert steps[steps.index(2) + 1:].count(3) >= 1 and steps == sorted(steps)
     assert (run / "model.safetensors").exists()
+
+
+@pytest.mark.timeout(300)
+def test_sigterm_to_the_supervisor_ends_the_ranks(tmp_path):
+    """The ranks run in sessions of their own; a SIGTERM to the supervising process still ends them."""
+    import signal
+    import subprocess
+    import time
+    cfg = tmp_path / "c.yaml"
+    cfg.write_text("pretraining: {ckp_dir: ck}\n")
+    pidfile = tmp_path / "rank.pid"
+    child = f"import os, time; open({str(pidfile)!r}, 'w').write(str(os.getpid())); time.sleep(120)"
+    code = ("import sys; from nanoplm_b200.runtime.supervisor import Supervisor; "
+            f"sys.exit(Supervisor({str(cfg)!r}, nproc=1, max_restarts=0, grace_seconds=2, "
+            f"command=[sys.executable, '-c', {child!r}]).run())")
+    sup = subprocess.Popen([sys.executable, "-c", code], cwd=tmp_path, env={**os.environ, **_env()})
+    deadline = time.time() + 120
+    while not pidfile.exists() or not pidfile.read_text():
+        assert time.time() < deadline and sup.poll() is None
+        time.sleep(0.2)
+    rank_pid = int(pidfile.read_text())
+    sup.send_signal(signal.SIGTERM)
+    assert sup.wait(timeout=60) == 128 + signal.SIGTERM
+    for _ in range(100):
+        try:
+            os.kill(rank_pid, 0)
+        except ProcessLookupError:
+            break
+        time.sleep(0.1)
+    else:
+        os.kill(rank_pid, signal.SIGKILL)          # this exact process, started above
+        raise AssertionError("the rank outlived its supervisor")
