@@ -154,10 +154,17 @@ class Supervisor:
                     self.run_dir = max(new, key=lambda p: p.stat().st_mtime)
             if self.stall_seconds > 0 and self.run_dir is not None and (self.run_dir / "heartbeat").exists() \
                     and time.time() - started > self.stall_seconds:
-                stalled = find_stalled(self.run_dir / "heartbeat", self.nproc, max_age=self.stall_seconds,
-                                       max_step_age=self.stall_seconds)
-                # a rank that already left with code 0 no longer beats: not a stall
-                stalled = [r for r in stalled if codes[r] is None]
+                hb = self.run_dir / "heartbeat"
+                stalled = find_stalled(hb, self.nproc, max_age=self.stall_seconds, max_step_age=self.stall_seconds)
+                # a rank that already left with code 0 no longer beats: not a stall. Neither is a file
+                # left by an earlier attempt in the same run directory while this attempt is still
+                # starting up (imports, dataset set-up), within a generous allowance
+                starting = time.time() - started < max(120.0, 5 * self.stall_seconds)
+
+                def stale(r: int) -> bool:
+                    f = hb / f"rank-{r}"
+                    return (not f.exists()) or f.stat().st_mtime < started
+                stalled = [r for r in stalled if codes[r] is None and not (starting and stale(r))]
                 if stalled:
                     return f"no progress on ranks {stalled} for {self.stall_seconds:.0f} s"
             time.sleep(self.poll)
