@@ -44,13 +44,16 @@ def from_yaml(config: Path) -> None:
 @click.argument("config", default="distill.yaml", type=click.Path(dir_okay=False, path_type=Path))
 @click.option("--nproc", type=int, default=1, show_default=True, help="Ranks to start (one per GPU).")
 @click.option("--max-restarts", type=int, default=3, show_default=True)
+@click.option("--stall-seconds", type=float, default=0.0,
+              help="With distillation.heartbeat_seconds set: restart when a rank's step stops advancing this long.")
 @click.option("--grace-seconds", type=float, default=10.0, show_default=True)
 @click.option("--log-dir", type=click.Path(path_type=Path), default=None)
-def supervise(config: Path, nproc: int, max_restarts: int, grace_seconds: float, log_dir) -> None:
+def supervise(config: Path, nproc: int, max_restarts: int, stall_seconds: float, grace_seconds: float, log_dir) -> None:
     from nanoplm_b200.runtime.supervisor import Supervisor
     try:
         sup = Supervisor(config if config.is_absolute() else Path.cwd() / config, nproc, max_restarts,
-                         grace_seconds=grace_seconds, log_dir=log_dir, section="distillation")
+                         stall_seconds=stall_seconds, grace_seconds=grace_seconds, log_dir=log_dir,
+                         section="distillation")
     except (FileNotFoundError, ValueError) as exc:
         raise click.ClickException(str(exc)) from exc
     code = sup.run()

@@ -296,6 +296,8 @@ class DistillationConfig:
     teacher_random_init: bool = False    # benchmarks: random-init frozen teacher instead of HF weights
     max_grad_norm: float = 1.0
     fused_comm: bool = True              # P2P-fused optimizer step on multi-GPU NVLink nodes
+    heartbeat_seconds: float = 0.0       # > 0 enables the per-rank heartbeat / watchdog
+    heartbeat_stall_seconds: float = 0.0  # > 0: rank 0 ends the job when a rank's step stops advancing this long
 
     def __post_init__(self) -> None:
         if isinstance(self.teacher, dict):

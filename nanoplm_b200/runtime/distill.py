@@ -217,6 +217,14 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
              "model": as_plain_dict(model_config), "distillation": as_plain_dict(cfg),
              "total_steps": total_steps, "warmup_steps": warmup}, indent=2, default=str), encoding="utf-8")
     sink = MetricsSink(str(out_dir), cfg.project_name, plan.wandb_run_name, as_plain_dict(cfg), is_main)
+    heartbeat = watchdog = None
+    if cfg.heartbeat_seconds and cfg.heartbeat_seconds > 0:      # same scheme as the pretraining pipeline
+        from nanoplm_b200.runtime.watchdog import Heartbeat, Watchdog
+        heartbeat = Heartbeat(out_dir / "heartbeat", rank, cfg.heartbeat_seconds).start()
+        if is_main and distributed:
+            stall = float(cfg.heartbeat_stall_seconds or 0)
+            watchdog = Watchdog(out_dir / "heartbeat", world, max_age=6 * cfg.heartbeat_seconds + 30,
+                                max_step_age=stall if stall > 0 else None, interval=cfg.heartbeat_seconds).start()
 
     def to_dev(b):
         return {k: (v.to(device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in b.items()}
@@ -291,6 +299,8 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
             gn = engine.step(lr, n_acc)
             sched.step()
             global_step += 1
+            if heartbeat is not None:
+                heartbeat.step = global_step
             if os.environ.get("NPLM_INJECT_FAULT"):     # host-side failure for recovery tests, between steps
                 from nanoplm_b200.runtime.faults import maybe_inject
                 maybe_inject(rank, global_step)
@@ -328,6 +338,10 @@ def run_distillation(model_config: StudentConfig, cfg: DistillationConfig,
     ev = evaluate()
     sink.log({"train/global_step": global_step, "eval/loss": ev})
     sink.finish(str(out_dir))
+    if watchdog is not None:
+        watchdog.stop()
+    if heartbeat is not None:
+        heartbeat.stop()
     check_device_status()
     logger.info("Distillation complete.")
     return {"output_dir": str(out_dir), "losses": losses, "eval_losses": evals + [(global_step, ev)],
