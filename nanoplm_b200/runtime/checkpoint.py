@@ -79,6 +79,7 @@ def save_checkpoint(engine, scheduler, global_step: int, epoch: int, output_dir:
         (tmp / STATE_FILE).write_text(json.dumps(state, indent=2), encoding="utf-8")
         if hf_files:
             _write_hf_files(tmp, model_sd, global_step, epoch, logging_steps, eval_steps, save_steps, tied_keys)
+            _write_hf_config(tmp, getattr(engine.model, "config", None))
         if sharded:
             (tmp / "index.json").write_text(json.dumps(
                 {"world_size": engine.world, "total": engine.total, "shard": engine.shard,
@@ -105,6 +106,37 @@ def _write_hf_files(ckp: Path, model_sd: dict, global_step: int, epoch: int, log
                      "save_steps": int(save_steps), "log_history": [], "best_metric": None,
                      "best_model_checkpoint": None, "is_world_process_zero": True, "is_local_process_zero": True}
     (ckp / "trainer_state.json").write_text(json.dumps(trainer_state, indent=2), encoding="utf-8")
+
+
+def _write_hf_config(ckp: Path, cfg) -> None:
+    """`config.json` with the field names of HF's `ModernBertConfig`, filled the way the reference's
+    HF-based model fills them (models/modern_bert/model.py:52-70), so the directory reads like one
+    left by `save_pretrained`. Written as plain JSON: both the per-layer-type fields of recent
+    transformers releases (`layer_types`, `rope_parameters`) and the older scalar ones are present."""
+    if cfg is None or not hasattr(cfg, "global_attn_every_n_layers"):
+        return
+    data = {
+        "architectures": ["ModernBertForMaskedLM"], "model_type": "modernbert",
+        "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+        "num_hidden_layers": cfg.num_hidden_layers, "num_attention_heads": cfg.num_attention_heads,
+        "max_position_embeddings": cfg.max_position_embeddings, "hidden_activation": cfg.hidden_activation,
+        "initializer_range": cfg.initializer_range, "norm_eps": cfg.norm_eps, "norm_bias": cfg.norm_bias,
+        "mlp_bias": cfg.mlp_bias, "mlp_dropout": cfg.mlp_dropout, "attention_bias": cfg.attention_bias,
+        "attention_dropout": cfg.attention_dropout, "embedding_dropout": cfg.embedding_dropout,
+        "classifier_activation": cfg.classifier_activation, "classifier_bias": cfg.classifier_bias,
+        "classifier_pooling": "cls", "decoder_bias": cfg.decoder_bias, "sparse_prediction": cfg.sparse_prediction,
+        "sparse_pred_ignore_index": cfg.sparse_pred_ignore_index, "tie_word_embeddings": cfg.tie_word_embeddings,
+        "pad_token_id": cfg.pad_token_id, "eos_token_id": cfg.eos_token_id, "bos_token_id": None,
+        "unk_token_id": cfg.unk_token_id, "mask_token_id": cfg.mask_token_id, "loss_type": "ForMaskedLM",
+        "local_attention": cfg.local_attention, "layer_types": cfg.layer_types,
+        "rope_parameters": {"full_attention": {"rope_type": "default", "rope_theta": cfg.global_rope_theta},
+                            "sliding_attention": {"rope_type": "default", "rope_theta": cfg.local_rope_theta}},
+        "global_attn_every_n_layers": cfg.global_attn_every_n_layers, "global_rope_theta": cfg.global_rope_theta,
+        "local_rope_theta": cfg.local_rope_theta, "torch_dtype": "float32",
+        # what HF's config has no field for (the MLP variant matters to a loader)
+        "nanoplm": {"mlp_activation": cfg.mlp_activation, "norm_type": cfg.norm_type},
+    }
+    (ckp / "config.json").write_text(json.dumps(data, indent=2), encoding="utf-8")
 
 
 def load_checkpoint(engine, scheduler, checkpoint_dir: str, restore_rng: bool = True) -> tuple[int, int]:

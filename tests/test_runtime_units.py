@@ -200,6 +200,13 @@ def test_checkpoint_with_hf_files_loads_through_the_hf_layout_alone(tmp_path):
     assert set(st) == set(full) - {"decoder.weight"}
     import json
     assert json.loads((path / "trainer_state.json").read_text())["global_step"] == 7
+    # config.json with the field names of HF's ModernBertConfig
+    hf_cfg = json.loads((path / "config.json").read_text())
+    assert hf_cfg["model_type"] == "modernbert" and hf_cfg["architectures"] == ["ModernBertForMaskedLM"]
+    assert (hf_cfg["hidden_size"], hf_cfg["num_hidden_layers"], hf_cfg["vocab_size"], hf_cfg["pad_token_id"]) == (32, 1, 32, 0)
+    assert hf_cfg["layer_types"] == ["full_attention"] and hf_cfg["local_attention"] == 128
+    assert hf_cfg["nanoplm"]["mlp_activation"] == "swiglu" and hf_cfg["global_rope_theta"] == 160000.0
+    assert hf_cfg["rope_parameters"]["sliding_attention"]["rope_theta"] == 10000.0
     for name in ("pytorch_model.bin", "training_state.json", "rng_state.pth"):
         (path / name).unlink()
     torch.manual_seed(1)
