@@ -29,9 +29,11 @@ MODULES: dict[str, dict[str, str]] = {
     "nanoplm.config": {},
     "nanoplm.config.datasets": {"DATASET_URLS": "nanoplm_b200.config.datasets",
                                 "get_supported_datasets": "nanoplm_b200.config.datasets"},
-    "nanoplm.utils": {"logger": "nanoplm_b200.utils.logging", "log_stage": A, "create_dirs": A, "get_device": A},
+    "nanoplm.utils": {"logger": "nanoplm_b200.utils.logging", "log_stage": A, "create_dirs": A, "get_device": A,
+                      "get_caller_dir": A},
     "nanoplm.utils.logger": {"logger": "nanoplm_b200.utils.logging", "log_stage": A},
-    "nanoplm.utils.common": {"read_yaml": A, "create_dirs": A, "get_device": A,
+    "nanoplm.utils.common": {"read_yaml": A, "create_dirs": A, "get_device": A, "get_caller_dir": A,
+                             "is_flash_attention_available": A, "inside_git_repo": A, "is_git_subdir": A,
                              "resolve_world_size": "nanoplm_b200.runtime.run_dirs"},
     "nanoplm.data": {},
     "nanoplm.data.downloader": {"Downloader": "nanoplm_b200.data.prep", "DownloadError": "nanoplm_b200.data.prep"},

@@ -283,3 +283,27 @@ def create_dirs(path) -> None:
 def get_device() -> str:
     """utils/common.py: "cuda" when a GPU is visible, else "cpu"."""
     return "cuda" if torch.cuda.is_available() else "cpu"
+
+
+def is_flash_attention_available() -> bool:
+    """utils/common.py:16-27: whether the fast varlen attention path can run. Here that is this
+    package's own kernels, which need a CUDA device."""
+    return torch.cuda.is_available()
+
+
+def inside_git_repo(work_dir) -> bool:
+    """utils/common.py:112-130."""
+    from nanoplm_b200.cli.data import _inside_git_repo
+    return _inside_git_repo(Path(work_dir))
+
+
+def is_git_subdir(work_dir) -> bool:
+    """utils/common.py:143-165."""
+    from nanoplm_b200.cli.data import _is_git_subdir
+    return _is_git_subdir(Path(work_dir))
+
+
+def get_caller_dir() -> Path:
+    """utils/common.py:61-109: the directory relative paths are resolved against, i.e. the working
+    directory (the reference walks the call stack to the same effect for command-line use)."""
+    return Path.cwd()
