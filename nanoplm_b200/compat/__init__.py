@@ -26,6 +26,9 @@ A = "nanoplm_b200.compat.adapters"
 MODULES: dict[str, dict[str, str]] = {
     "nanoplm": {"__version__": "nanoplm_b200:__version__"},
     "nanoplm.cli": {"cli": "nanoplm_b200.cli", "main": "nanoplm_b200.cli"},
+    "nanoplm.cli.data": {"data": "nanoplm_b200.cli.data"},
+    "nanoplm.cli.pretrain": {"pretrain": "nanoplm_b200.cli.pretrain"},
+    "nanoplm.cli.distill": {"distill": "nanoplm_b200.cli.distill"},
     "nanoplm.config": {},
     "nanoplm.config.datasets": {"DATASET_URLS": "nanoplm_b200.config.datasets",
                                 "get_supported_datasets": "nanoplm_b200.config.datasets"},
