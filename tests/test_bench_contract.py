@@ -84,3 +84,28 @@ def test_reference_arm_answers_unavailable_without_the_installed_reference(tmp_p
     line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
     rec = json.loads(line)
     assert rec["impl"] == "reference" and "unavailable" in rec
+
+
+def test_data_bench_runs_both_arms(tmp_path):
+    """The host data pipeline benchmark prints one JSON line per measurement for this package and,
+    when the reference is installed under baseline/_ref, for the reference's classes on the same shards."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root), CUDA_VISIBLE_DEVICES="")
+    arms = ["own"] + (["reference"] if (root / "baseline" / "_ref" / "nanoplm").exists() else [])
+    for arm in arms:
+        out = subprocess.run([sys.executable, "-m", "nanoplm_b200.bench.data_bench", "--sequences", "600", "--batch", "52",
+                              "--rows", "32", "--workers", "0", "--impl", arm], cwd=tmp_path, env=env,
+                             capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, (out.stdout + out.stderr)[-3000:]
+        rows = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+        names = [r["bench"] for r in rows]
+        for want in ("read_every_sequence", "tokenize_one_by_one", "packing_collator_static", "padding_collator"):
+            assert want in names, (arm, names)
+        assert all(r.get("impl", arm) == arm for r in rows)
+        static = next(r for r in rows if r["bench"] == "packing_collator_static")
+        assert static["real_tokens_per_s"] > 0 and static["micro_batches"] >= 5
