@@ -15,7 +15,7 @@ from nanoplm_b200.models.encoder import position_ids_from_cu_seqlens
 LETTERS = "ALGVSREDTIPKFQNYMHWCXBOUZ"
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(st.lists(st.integers(1, 700), min_size=1, max_size=120), st.sampled_from([16, 64, 512]))
 def test_packer_matches_python_and_never_overfills(lengths, width):
     order, row_of, start_of, n_rows = pack_ffd(np.asarray(lengths), width)
@@ -32,7 +32,7 @@ def test_packer_matches_python_and_never_overfills(lengths, width):
     assert n_rows >= -(-int(np.minimum(lengths, width).sum()) // width)          # never below the volume bound
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(st.integers(1, 6), st.integers(1, 9), st.data())
 def test_rank_balancer_matches_python_and_fills_every_bin(n_bins, per_bin, data):
     lengths = data.draw(st.lists(st.integers(1, 1024), min_size=n_bins * per_bin, max_size=n_bins * per_bin))
@@ -42,7 +42,7 @@ def test_rank_balancer_matches_python_and_fills_every_bin(n_bins, per_bin, data)
     assert np.bincount(bin_of, minlength=n_bins).tolist() == [per_bin] * n_bins
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(st.lists(st.text(alphabet=LETTERS, min_size=1, max_size=90), min_size=1, max_size=24), st.booleans(),
        st.integers(0, 2 ** 31 - 1))
 def test_packing_collator_keeps_every_token_and_masks_only_residues(seqs, static, seed):
@@ -69,7 +69,7 @@ def test_packing_collator_keeps_every_token_and_masks_only_residues(seqs, static
         assert bool((base[total:] == tok.pad_token_id).all())
 
 
-@settings(max_examples=80, deadline=None)
+@settings(max_examples=80, deadline=None, derandomize=True)
 @given(st.text(alphabet=LETTERS + LETTERS.lower() + "*- 1", max_size=120), st.integers(2, 64))
 def test_tokenizers_are_total_and_respect_max_length(text, max_length):
     for tok in (ProtTokenizer(), StudentTokenizer()):
@@ -81,7 +81,7 @@ def test_tokenizers_are_total_and_respect_max_length(text, max_length):
     assert ProtTokenizer().encode(text) == ProtTokenizer().encode(text.upper())  # case is normalised away
 
 
-@settings(max_examples=30, deadline=None)
+@settings(max_examples=30, deadline=None, derandomize=True)
 @given(st.integers(1, 4), st.integers(1, 3), st.integers(1, 5), st.integers(0, 40), st.integers(0, 1000))
 def test_balanced_sampler_partitions_each_epoch(world, accum, mbs, extra, seed):
     window = world * accum * mbs
