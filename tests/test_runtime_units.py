@@ -252,3 +252,24 @@ def test_checkpoint_written_from_a_compiled_module_loads(tmp_path):
         assert step == 1 and set(a) == set(b), variant
         assert all(torch.equal(a[k], b[k]) for k in a), variant
         assert dst.decoder.weight.data_ptr() == dst.model.embeddings.tok_embeddings.weight.data_ptr(), variant
+
+
+def test_measured_peaks_and_mfu(tmp_path, monkeypatch):
+    """MFU against the H100 figure the reference hard-codes (pure_pipeline.py:79-82, 803-806) and against
+    the bf16 throughput measured on this pool (the fallback figures when the file is absent or unreadable)."""
+    from nanoplm_b200.runtime.metrics import H100_PEAK_TFLOPS, MetricsSink
+    from nanoplm_b200.utils import peaks
+    p = peaks.measured_peaks()
+    assert p["source"] in ("measured", "fallback") and p["hbm_gbs"] > 1000 and p["bf16_tflops"] > 100
+    monkeypatch.setattr(peaks, "__file__", str(tmp_path / "a" / "b" / "peaks.py"))
+    assert peaks.measured_peaks() == peaks.FALLBACK
+    (tmp_path / "MEASURED_PEAKS.json").write_text("{not json")
+    assert peaks.measured_peaks()["source"] == "fallback"
+    (tmp_path / "MEASURED_PEAKS.json").write_text('{"hbm_gbs": 7000.0, "bf16_tflops": 1600.0}')
+    assert peaks.measured_peaks() == {"hbm_gbs": 7000.0, "bf16_tflops": 1600.0, "source": "measured"}
+    assert H100_PEAK_TFLOPS == 989.4
+    monkeypatch.setenv("WANDB_MODE", "disabled")
+    sink = MetricsSink(str(tmp_path), "proj", "run", {}, True)
+    h100, b200 = sink.mfu(raw_tokens_per_sec=1.0e6, flops_per_token=10 ** 9, world=2)
+    assert abs(h100 - 0.5e15 / 989.4e12) < 1e-12 and 0 < b200 < h100     # the B200 denominator is the larger one
+    sink.finish(str(tmp_path))
