@@ -274,3 +274,57 @@ def test_cli_pretrain_run_with_options(tmp_path, monkeypatch):
     assert r.exit_code == 0, r.output + str(r.exception)
     assert (run / "checkpoint-8").exists() and len(list(run.glob("archived_*"))) == 1
     assert runner.invoke(cli, base + ["--optimizer", "sgd"]).exit_code == 2
+
+
+def test_loader_error_branches_and_coercions(tmp_path):
+    """What the strict loaders refuse and what they coerce (reference: cli/pretrain.py:742-924,
+    cli/distill.py:629-743): strings for numbers and booleans are converted, anything else is named
+    in the error."""
+    from nanoplm_b200.config.loaders import (load_distill_config, load_student_config, read_yaml)
+    base = yaml.safe_load(PRETRAIN_YAML)
+    pre = dict(base["pretraining"])
+    cfg = load_pretrain_config({**pre, "bf16": "yes", "tf32": 0, "micro_batch_size": "16", "global_batch_size": "2e6",
+                                "adam_learning_rate": "5e-4", "muon_nesterov": "FALSE"})
+    assert cfg.bf16 is True and cfg.tf32 is False and cfg.micro_batch_size == 16 and cfg.global_batch_size == 2_000_000
+    assert cfg.adam_learning_rate == 5e-4 and cfg.muon_nesterov is False
+    for key, bad, msg in (("bf16", "maybe", "Invalid boolean"), ("micro_batch_size", "many", "Must be an integer"),
+                          ("micro_batch_size", 2.5, "Must be an integer"), ("logging_steps", [1], "Must be an integer")):
+        with pytest.raises(ConfigError, match=msg):
+            load_pretrain_config({**pre, key: bad})
+    with pytest.raises(ConfigError, match="required"):
+        load_pretrain_config(None)
+    with pytest.raises(ConfigError, match="required"):
+        load_model_config(None)
+    with pytest.raises(ConfigError, match="model.moe"):
+        load_model_config({**base["model"], "moe": {"num_experts": 8, "nope": 1}})
+    both = load_pretrain_config({**pre, "learning_rate": 1e-3, "adam_learning_rate": "1e-3"})      # same value twice: fine
+    assert both.adam_learning_rate == 1e-3
+    assert load_pretrain_config({**pre, "learning_rate": 2e-3, "adam_learning_rate": 1e-3}).adam_learning_rate == 1e-3
+    with pytest.raises(ConfigError, match="Unexpected resume"):
+        load_resume_config({"is_resume": False, "nope": 1})
+
+    dis = yaml.safe_load(DISTILL_YAML)
+    with pytest.raises(ConfigError, match="required"):
+        load_student_config(None)
+    with pytest.raises(ConfigError, match="Unexpected model"):
+        load_student_config({**dis["model"], "nope": 1})
+    with pytest.raises(ConfigError, match="required"):
+        load_distill_config(None)
+    d = {**dis["distillation"], "dataset_dir": "x"}
+    with pytest.raises(ConfigError, match="dataset_dir is required"):
+        load_distill_config({k: v for k, v in d.items() if k != "dataset_dir"})
+    assert load_distill_config({k: v for k, v in d.items() if k != "dataset_dir"}, require_dataset_dir=False).dataset_dir is None
+    with pytest.raises(ConfigError, match="Unexpected distillation configuration"):
+        load_distill_config({**d, "nope": 1})
+    with pytest.raises(ConfigError, match="distillation.teacher"):
+        load_distill_config({**d, "teacher": {"d_model": 64, "nope": 1}})
+    got = load_distill_config({**d, "lr_scheduler_kwargs": '{"num_warmup_steps": 5}', "teacher": {"d_model": "64"},
+                               "learning_rate": "3e-4", "use_threading": "false"})
+    assert got.lr_scheduler_kwargs == {"num_warmup_steps": 5} and got.teacher.d_model == 64
+    assert got.learning_rate == 3e-4 and got.use_threading is False
+
+    with pytest.raises(FileNotFoundError):
+        read_yaml(tmp_path / "missing.yaml")
+    (tmp_path / "list.yaml").write_text("- 1\n- 2\n")
+    with pytest.raises(ConfigError, match="mapping"):
+        read_yaml(tmp_path / "list.yaml")

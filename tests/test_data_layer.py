@@ -165,3 +165,43 @@ def test_kd_dataset_save_load_shard(tmp_path):
     assert [count_kd_sequences(p) for p in parts] == [3, 3, 3]
     ds2 = LoadKDDataset(tmp_path / "kd_sharded" / "train_kd.kdz")
     assert len(ds2) == 9 and torch.equal(ds2[4]["teacher_embeddings"], ds[4]["teacher_embeddings"])
+
+
+def test_distillation_dataset_validation(tmp_path):
+    """`validate_distillation_dataset` for both forms of a distillation dataset (reference:
+    data/validation.py:357-458): FASTA files of the on-the-fly form, embedding files of the stored form."""
+    from nanoplm_b200.config.schema import TeacherConfig
+    from nanoplm_b200.data.kd_dataset import SaveKDDataset
+    from nanoplm_b200.data.validation import validate_distillation_dataset, validate_hdf5_shards
+    from nanoplm_b200.models.teacher import T5EncoderTeacher
+    common = dict(pipeline_mode="distillation", seqs_num=12, min_seq_len=8, max_seq_len=24, val_ratio=0.25, train_dir="train",
+                  val_dir="val", train_sequences=9, val_sequences=3, teacher_model="prott5")
+    fly = tmp_path / "fly"
+    write_synthetic_fasta(fly / "train.fasta", 9, 8, 20, seed=1)
+    write_manifest(fly, DistillationManifest(on_the_fly=True, train_fasta="train.fasta", val_fasta="val.fasta", **common))
+    with pytest.raises(ValidationError, match="val_fasta not found"):
+        validate_distillation_dataset(fly)
+    write_synthetic_fasta(fly / "val.fasta", 3, 8, 20, seed=2)
+    assert validate_distillation_dataset(fly)["manifest"].on_the_fly is True
+    with pytest.raises(ValueError, match="prepared for 'distillation'"):
+        validate_pretrain_dataset(fly)
+
+    stored = tmp_path / "stored"
+    teacher = T5EncoderTeacher(TeacherConfig(d_model=32, d_kv=8, d_ff=64, num_layers=1, num_heads=4))
+    for split, n in (("train", 9), ("val", 3)):
+        fasta = write_synthetic_fasta(tmp_path / f"{split}.fasta", n, 8, 20, seed=3)
+        SaveKDDataset(fasta, stored / split / f"{split}_kd_dataset.kdz", max_seq_len=24, batch_size=4, device="cpu",
+                      samples_per_shard=4, teacher=teacher).run()
+    write_manifest(stored, DistillationManifest(on_the_fly=False, sharded=True, samples_per_shard=4,
+                                                train_h5_prefix="train_kd_dataset.h5", val_h5_prefix="val_kd_dataset.h5",
+                                                **common))
+    info = validate_distillation_dataset(stored)
+    assert info["train"]["num_files"] == 3 and info["val"]["num_files"] == 1
+    assert info["train"]["num_sequences"] in (9, None)              # counted when the files can be opened
+    assert validate_hdf5_shards(stored / "train")["num_files"] == 3
+    with pytest.raises(ValidationError, match="No HDF5 files"):
+        validate_hdf5_shards(stored / "train", prefix="other.h5")
+    with pytest.raises(ValidationError, match="not found"):
+        validate_hdf5_shards(stored / "nowhere")
+    with pytest.raises(ValidationError, match="not a directory"):
+        validate_pretrain_shards(tmp_path / "train.fasta")

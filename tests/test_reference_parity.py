@@ -1358,3 +1358,39 @@ def test_internal_config_knobs_match_the_reference_model(ref):
     for k in fresh_r:
         if k.endswith(".bias"):
             assert float(fresh_r[k].abs().max()) == 0.0 and float(fresh_o[k].abs().max()) == 0.0, k
+
+
+def test_tokenizer_api_surface_matches(ref, tmp_path):
+    """The tokenizer methods user code calls besides encoding (tokenizer.py:8-72, student/tokenizer.py:4-107):
+    vocabulary look-ups in both directions, special-token masks, length, BOS mode, `save_vocabulary`."""
+    import json
+
+    from nanoplm.distillation.models.student.tokenizer import ProtXTokenizer
+
+    from nanoplm_b200.data.tokenizer import ProtTokenizer, StudentTokenizer
+    for theirs, ours in ((ref.Tokenizer(), ProtTokenizer()), (ref.Tokenizer(use_bos_token=True), ProtTokenizer(use_bos_token=True)),
+                         (ProtXTokenizer(), StudentTokenizer())):
+        assert theirs.get_vocab() == ours.get_vocab() and len(theirs) == len(ours) == ours.vocab_size
+        toks = ["A", "L", "X", "<pad>", "</s>", "<unk>", "Q", "not-a-token"]
+        assert theirs.convert_tokens_to_ids(toks) == ours.convert_tokens_to_ids(toks)
+        assert theirs.convert_tokens_to_ids("W") == ours.convert_tokens_to_ids("W")
+        ids = list(range(ours.vocab_size))
+        assert theirs.convert_ids_to_tokens(ids) == ours.convert_ids_to_tokens(ids)
+        assert theirs.convert_ids_to_tokens(5) == ours.convert_ids_to_tokens(5)
+        for name in ("pad_token_id", "eos_token_id", "unk_token_id", "pad_token", "eos_token", "unk_token"):
+            assert getattr(theirs, name) == getattr(ours, name), name
+        enc = theirs("MKTAYIAKQR")["input_ids"]
+        assert enc == ours("MKTAYIAKQR")["input_ids"] == ours.encode("MKTAYIAKQR")
+        assert theirs.get_special_tokens_mask(enc, already_has_special_tokens=True) == \
+            ours.get_special_tokens_mask(enc, already_has_special_tokens=True)
+        assert sorted(theirs.all_special_ids) == sorted(ours.all_special_ids)
+        assert theirs.decode(enc, skip_special_tokens=True).replace(" ", "") == ours.decode(enc, skip_special_tokens=True)
+    assert ref.Tokenizer(use_bos_token=True)("MK")["input_ids"][0] == ProtTokenizer(use_bos_token=True)("MK")["input_ids"][0] == 29
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    a = ProtXTokenizer().save_vocabulary(str(tmp_path / "a"))
+    b = StudentTokenizer().save_vocabulary(str(tmp_path / "b"))
+    assert json.loads(Path(a[0]).read_text()) == json.loads(Path(b[0]).read_text()) and Path(a[0]).name == Path(b[0]).name
+    ProtTokenizer().save_pretrained(tmp_path / "c")
+    assert json.loads((tmp_path / "c" / "vocab.json").read_text()) == ProtTokenizer().get_vocab()
+    assert json.loads((tmp_path / "c" / "tokenizer_config.json").read_text())["mask_token"] == "<mask>"
