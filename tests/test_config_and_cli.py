@@ -328,3 +328,47 @@ def test_loader_error_branches_and_coercions(tmp_path):
     (tmp_path / "list.yaml").write_text("- 1\n- 2\n")
     with pytest.raises(ConfigError, match="mapping"):
         read_yaml(tmp_path / "list.yaml")
+
+
+def test_cli_data_from_yaml_with_the_dvc_runner(tmp_path, monkeypatch):
+    """The dvc runner of `data from-yaml` (reference: cli/data.py:926-979), against a stand-in `dvc`
+    executable that records its arguments: `dvc init` happens once (--no-scm outside a git work
+    tree) unless --no-auto-init, `dvc repro` gets -f / -v / the target, a failing repro is reported, and
+    the in-process part (shards + manifest) follows."""
+    import stat
+    monkeypatch.chdir(tmp_path)
+    runner = CliRunner()
+    _write_params(tmp_path, "pretrain")
+    (tmp_path / "dvc.yaml").write_text("stages: {}\n")
+    # what the dvc stages would have produced
+    from nanoplm_b200.data.fasta import iter_fasta, write_fasta
+    recs = list(iter_fasta(tmp_path / "raw" / "x.fasta"))
+    write_fasta(recs[:40], tmp_path / "raw" / "split" / "train.fasta")
+    write_fasta(recs[40:50], tmp_path / "raw" / "split" / "val.fasta")
+    bindir = tmp_path / "bin"
+    bindir.mkdir()
+    log = tmp_path / "dvc_calls.txt"
+    fake = bindir / "dvc"
+    fake.write_text(f"#!/bin/sh\necho \"$@\" >> {log}\nif [ \"$1\" = init ]; then mkdir -p .dvc; fi\n"
+                    f"if [ -f {tmp_path}/fail_repro ] && [ \"$1\" = repro ]; then exit 3; fi\nexit 0\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(bindir) + os.pathsep + os.environ["PATH"])
+    monkeypatch.setenv("GIT_CEILING_DIRECTORIES", str(tmp_path.parent))      # tmp_path is not inside a git work tree
+
+    r = runner.invoke(cli, ["data", "from-yaml", "params.yaml", "--runner", "dvc", "--no-auto-init"])
+    assert r.exit_code != 0 and "DVC is not initialized" in r.output
+    r = runner.invoke(cli, ["data", "from-yaml", "params.yaml", "--runner", "dvc", "--force", "--verbose"])
+    assert r.exit_code == 0, r.output + str(r.exception)
+    calls = log.read_text().splitlines()
+    assert calls == ["init -q --no-scm", "repro -v -f split"]
+    manifest = yaml.safe_load((tmp_path / "out" / "shards" / ".data_manifest").read_text())
+    assert manifest["train_sequences"] == 40 and manifest["val_sequences"] == 10
+    r = runner.invoke(cli, ["data", "from-yaml", "params.yaml", "--target", "filter"])     # auto: dvc + dvc.yaml present
+    assert r.exit_code == 0 or "already exist" in r.output
+    assert log.read_text().splitlines()[-1] == "repro filter" and len(log.read_text().splitlines()) == 3   # no second init
+    (tmp_path / "fail_repro").write_text("")
+    r = runner.invoke(cli, ["data", "from-yaml", "params.yaml", "--runner", "dvc"])
+    assert r.exit_code != 0 and "dvc repro failed with exit code 3" in r.output
+    monkeypatch.setenv("PATH", str(tmp_path / "nothing"))
+    r = runner.invoke(cli, ["data", "from-yaml", "params.yaml", "--runner", "dvc"])
+    assert r.exit_code != 0 and "'dvc' command not found" in r.output
