@@ -273,3 +273,57 @@ def test_measured_peaks_and_mfu(tmp_path, monkeypatch):
     h100, b200 = sink.mfu(raw_tokens_per_sec=1.0e6, flops_per_token=10 ** 9, world=2)
     assert abs(h100 - 0.5e15 / 989.4e12) < 1e-12 and 0 < b200 < h100     # the B200 denominator is the larger one
     sink.finish(str(tmp_path))
+
+
+def test_metrics_sink_with_a_stand_in_for_wandb(tmp_path, monkeypatch):
+    """The W&B side of the metrics sink against a recording stand-in module: project / run name / config
+    at init, `train/global_step` as the x axis (reference: pure_pipeline.py:607-623), every payload
+    forwarded, the run id written at the end, and a failing backend that never stops training
+    (pure_pipeline.py:828-833)."""
+    import json
+    import sys
+    import types
+
+    from nanoplm_b200.runtime.metrics import MetricsSink
+    calls = []
+    fake = types.ModuleType("wandb")
+    fake.run = None
+
+    def init(**kw):
+        calls.append(("init", kw))
+        fake.run = types.SimpleNamespace(id="abc123")
+    fake.init = init
+    fake.define_metric = lambda *a, **kw: calls.append(("define_metric", a, kw))
+    fake.log = lambda payload: calls.append(("log", dict(payload)))
+    fake.finish = lambda: calls.append(("finish",))
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    monkeypatch.setenv("WANDB_MODE", "online")
+    sink = MetricsSink(str(tmp_path), "proj", "run-01010101-re2", {"lr": 1e-3}, is_main=True)
+    assert calls[0] == ("init", {"project": "proj", "name": "run-01010101-re2", "config": {"lr": 1e-3}})
+    assert ("define_metric", ("train/global_step",), {}) in calls
+    assert ("define_metric", ("*",), {"step_metric": "train/global_step", "step_sync": True}) in calls
+    sink.log({"train/global_step": 1, "train/loss": 2.5})
+    assert calls[-1] == ("log", {"train/global_step": 1, "train/loss": 2.5})
+    line = json.loads((tmp_path / "metrics.jsonl").read_text().splitlines()[-1])
+    assert line["train/loss"] == 2.5 and "time" in line
+
+    def broken(payload):
+        raise RuntimeError("network down")
+    fake.log = broken
+    sink.log({"train/global_step": 2, "train/loss": 2.4})           # swallowed; the backend is dropped
+    assert sink.wandb is None and len((tmp_path / "metrics.jsonl").read_text().splitlines()) == 2
+    sink.finish(str(tmp_path))
+    assert not (tmp_path / "wandb_run_id.txt").exists()
+
+    healthy = MetricsSink(str(tmp_path), "proj", "run", {}, is_main=True)
+    healthy.finish(str(tmp_path))
+    assert (tmp_path / "wandb_run_id.txt").read_text() == "abc123" and calls[-1] == ("finish",)
+    n = len(calls)
+    other_rank = MetricsSink(str(tmp_path), "proj", "run", {}, is_main=False)
+    other_rank.log({"train/global_step": 3})
+    assert len(calls) == n and other_rank.jsonl_path is None         # only the main rank talks to W&B / the file
+
+    def no_init(**kw):
+        raise RuntimeError("no credentials")
+    fake.init = no_init
+    assert MetricsSink(str(tmp_path), "proj", "run", {}, is_main=True).wandb is None
