@@ -205,3 +205,36 @@ def test_distillation_dataset_validation(tmp_path):
         validate_hdf5_shards(stored / "nowhere")
     with pytest.raises(ValidationError, match="not a directory"):
         validate_pretrain_shards(tmp_path / "train.fasta")
+
+
+def test_seqkit_backend_against_a_stand_in_binary(tmp_path, monkeypatch):
+    """`FastaShuffler(backend="seqkit")` (reference: data/shuffler.py:72-95) with a stand-in `seqkit`
+    that records its arguments and copies the input: the command line, a failing binary and a missing one."""
+    import os
+    import stat
+    from nanoplm_b200.data.prep import FastaShuffler, ShufflingError
+    fasta = write_synthetic_fasta(tmp_path / "in.fasta", 10, 8, 20, seed=1)
+    bindir = tmp_path / "bin"
+    bindir.mkdir()
+    log = tmp_path / "calls.txt"
+    fake = bindir / "seqkit"
+    fake.write_text(f"#!/bin/sh\necho \"$@\" >> {log}\nif [ -f {tmp_path}/fail ]; then echo boom >&2; exit 2; fi\n"
+                    "out=\"\"; last=\"\"\nwhile [ $# -gt 0 ]; do if [ \"$1\" = -o ]; then out=\"$2\"; shift; else last=\"$1\"; fi; shift; done\n"
+                    "cp \"$last\" \"$out\"\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(bindir) + os.pathsep + os.environ["PATH"])
+    out = FastaShuffler(fasta, tmp_path / "o" / "shuf.fasta", backend="seqkit", seed=11, threads=3).shuffle()
+    assert out.read_bytes() == Path(fasta).read_bytes()
+    words = log.read_text().split()
+    assert words[0] == "shuffle" and words[words.index("--threads") + 1] == "3" and "--two-pass" in words
+    assert words[words.index("--rand-seed") + 1] == "11"
+    (tmp_path / "fail").write_text("")
+    with pytest.raises(ShufflingError, match="boom"):
+        FastaShuffler(fasta, tmp_path / "o" / "again.fasta", backend="seqkit", seed=1).shuffle()
+    monkeypatch.setenv("PATH", str(tmp_path / "nothing"))
+    with pytest.raises(ShufflingError, match="not on PATH"):
+        FastaShuffler(fasta, tmp_path / "o" / "again.fasta", backend="seqkit", seed=1).shuffle()
+    with pytest.raises(ShufflingError, match="Unknown shuffle backend"):
+        FastaShuffler(fasta, tmp_path / "o" / "again.fasta", backend="sort").shuffle()
+    drawn = FastaShuffler(fasta, tmp_path / "o" / "x.fasta", seed=None)
+    assert 1 <= drawn.seed <= 1000                               # no seed given: one is drawn and kept
