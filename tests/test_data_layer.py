@@ -238,3 +238,53 @@ def test_seqkit_backend_against_a_stand_in_binary(tmp_path, monkeypatch):
         FastaShuffler(fasta, tmp_path / "o" / "again.fasta", backend="sort").shuffle()
     drawn = FastaShuffler(fasta, tmp_path / "o" / "x.fasta", seed=None)
     assert 1 <= drawn.seed <= 1000                               # no seed given: one is drawn and kept
+
+
+def test_kd_dataset_order_cache_pickling_and_errors(tmp_path):
+    """`LoadKDDataset` (reference: distillation/dataset.py:415-781): seeded order over the shards, the
+    prefetch cache returns the same items with and without threads, pickling for DataLoader workers,
+    statistics, and the refusals of `SaveKDDataset` / `shard_h5_file`."""
+    import pickle
+    import time
+    from nanoplm_b200.config.schema import TeacherConfig
+    from nanoplm_b200.data.kd_dataset import LoadKDDataset, SaveKDDataset, shard_h5_file
+    from nanoplm_b200.models.teacher import T5EncoderTeacher
+    fasta = write_synthetic_fasta(tmp_path / "a.fasta", 23, 8, 20, seed=3)
+    teacher = T5EncoderTeacher(TeacherConfig(d_model=16, d_kv=4, d_ff=32, num_layers=1, num_heads=4))
+    files = SaveKDDataset(fasta, tmp_path / "kd" / "t.kdz", max_seq_len=24, batch_size=5, device="cpu",
+                          samples_per_shard=6, teacher=teacher).run()
+    assert [f.name for f in files] == [f"t_shard_{k:04d}.kdz" for k in range(4)]
+    with pytest.raises(FileExistsError):
+        SaveKDDataset(fasta, tmp_path / "kd" / "t.kdz", max_seq_len=24, device="cpu", teacher=teacher).run()
+    again = SaveKDDataset(fasta, tmp_path / "kd" / "t.kdz", max_seq_len=24, batch_size=5, device="cpu", samples_per_shard=-1,
+                          teacher=teacher, force=True, skip_n=3).run()
+    assert len(again) == 1 and len(LoadKDDataset(again[0])) == 20 and not list((tmp_path / "kd").glob("t_shard_*"))
+    with pytest.raises(FileNotFoundError):
+        SaveKDDataset(tmp_path / "missing.fasta", tmp_path / "kd" / "u.kdz")
+    SaveKDDataset(fasta, tmp_path / "kd" / "t.kdz", max_seq_len=24, batch_size=5, device="cpu", samples_per_shard=6,
+                  teacher=teacher, force=True).run()
+
+    plain = LoadKDDataset(tmp_path / "kd" / "t.kdz", max_open_files=2, chunk_size=4, use_threading=False)
+    assert len(plain) == 23 and plain.stats()["files"] == 4 and plain.stats()["sequences"] == 23
+    a = LoadKDDataset(tmp_path / "kd" / "t.kdz", chunk_size=4, seed=7)
+    b = LoadKDDataset(tmp_path / "kd" / "t.kdz", chunk_size=4, seed=7, use_threading=False)
+    c = LoadKDDataset(tmp_path / "kd" / "t.kdz", chunk_size=4, seed=8, use_threading=False)
+    assert a._order.tolist() == b._order.tolist() != c._order.tolist() and sorted(a._order.tolist()) == list(range(23))
+    for i in range(23):
+        x, y = a[i], b[i]
+        assert all(torch.equal(x[k], y[k]) for k in x), i
+        assert torch.equal(y["input_ids"], plain[int(b._order[i])]["input_ids"])
+        if i % 4 == 0:
+            time.sleep(0.02)                                    # let the prefetch thread fill the cache
+    with pytest.raises(IndexError):
+        a[23]
+    with pytest.raises(IndexError):
+        a[-1]
+    clone = pickle.loads(pickle.dumps(a))
+    assert len(clone) == 23 and torch.equal(clone[5]["teacher_embeddings"], b[5]["teacher_embeddings"])
+    with pytest.raises(FileNotFoundError):
+        LoadKDDataset(tmp_path / "kd" / "nothing.kdz")
+    with pytest.raises(FileNotFoundError):
+        shard_h5_file(tmp_path / "kd" / "nothing.kdz", 2)
+    with pytest.raises(ValueError):
+        shard_h5_file(again[0] if again[0].exists() else files[0], 0)
