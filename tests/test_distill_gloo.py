@@ -104,3 +104,44 @@ def test_two_rank_distillation_runs_to_completion_and_resumes(tmp_path, on_the_f
                       if os.path.isabs(res2["output_dir"]) else
                       (Path(tmp_path) / res2["output_dir"] / "checkpoint-4" / "trainer_state.json").read_text()
                       )["global_step"] == 4
+
+
+def test_stored_embeddings_from_explicit_paths_with_heartbeat_and_mid_epoch_resume(tmp_path, monkeypatch):
+    """One process, no dataset directory: the explicit embedding-file prefixes of the configuration
+    (how a run resumed through the reference's `training_config.json` arrives, cli/distill.py:406-425),
+    heartbeat files while training, and a resume from a checkpoint in the middle of an epoch."""
+    from nanoplm_b200.config.schema import DistillationConfig, ResumeConfig, StudentConfig, TeacherConfig
+    from nanoplm_b200.data.kd_dataset import SaveKDDataset
+    from nanoplm_b200.data.synthetic import write_synthetic_fasta
+    from nanoplm_b200.models.teacher import T5EncoderTeacher
+    from nanoplm_b200.runtime.distill import run_distillation
+    from nanoplm_b200.runtime.watchdog import read_heartbeat
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("WANDB_MODE", "disabled")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    teacher = T5EncoderTeacher(TeacherConfig(d_model=1024, d_kv=8, d_ff=32, num_layers=1, num_heads=2))
+    for split, n in (("train", 40), ("val", 8)):
+        fasta = write_synthetic_fasta(tmp_path / f"{split}.fasta", n, 8, 20, seed=5)
+        SaveKDDataset(fasta, tmp_path / "kd" / split / f"{split}_kd.kdz", max_seq_len=24, batch_size=8, device="cpu",
+                      samples_per_shard=16, teacher=teacher).run()
+    model = StudentConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2)
+
+    def cfg():
+        return DistillationConfig(dataset_dir=None, train_h5_prefix=str(tmp_path / "kd" / "train" / "train_kd.kdz"),
+                                  val_h5_prefix=str(tmp_path / "kd" / "val" / "val_kd.kdz"), max_seq_len=24,
+                                  on_the_fly=False, ckp_dir="ck", num_epochs=2, batch_size=8, logging_steps=1,
+                                  eval_steps=100, save_steps=3, bf16=False, heartbeat_seconds=0.2)
+    res = run_distillation(model, cfg())
+    run = Path(res["output_dir"])
+    assert res["global_step"] == 10 and (run / "checkpoint-3").exists() and (run / "checkpoint-9").exists()   # 5 steps per epoch
+    beat = read_heartbeat(run / "heartbeat" / "rank-0")
+    assert beat is not None and beat[1] == 10
+    first = dict(res["losses"])
+    with pytest.raises(ValueError, match="dataset_dir is required unless"):
+        run_distillation(model, DistillationConfig(dataset_dir=None, on_the_fly=False, ckp_dir="ck2"))
+    # checkpoint-3 lies inside the first epoch: the resumed run skips three micro-batches and sees the same data
+    res2 = run_distillation(model, cfg(), ResumeConfig(True, str(run / "checkpoint-3"), None))
+    again = dict(res2["losses"])
+    assert res2["global_step"] == 10 and sorted(again) == list(range(4, 11))
+    assert all(abs(again[s] - first[s]) < 1e-4 * max(1.0, abs(first[s])) for s in again), (first, again)
