@@ -37,6 +37,7 @@ from nanoplm_b200.runtime import checkpoint as ckpt
 from nanoplm_b200.runtime.metrics import MetricsSink
 from nanoplm_b200.runtime.run_dirs import (compute_batch_setup, get_num_workers, prepare_run_and_steps,
                                            resolve_world_size)
+from nanoplm_b200.parallel.muon import is_muon_optimizer
 from nanoplm_b200.runtime.schedule import (WarmupLinearSchedule, get_warmup_steps,
                                            num_update_steps_per_epoch)
 from nanoplm_b200.utils.logging import logger
@@ -438,11 +439,17 @@ def run_pretraining(model: ProtEncoderMLM, pretrain_config: PretrainingConfig,
                            "train/tokens_per_sec": tps, "train/raw_tokens_per_sec": raw_tps,
                            "train/h100_mfu": h100, "train/b200_mfu": b200,
                            "train/step_ms_max_rank": 1e3 * float(stats[2]) / max(1, window_steps)}
+                # Muon / NorMuon: the matrices' rate, which follows the same schedule from its own base
+                # value (reference: pure_pipeline.py:766-772, 825-827)
+                muon_lr = float(engine.muon_lr) if is_muon_optimizer(engine) else None
+                if muon_lr is not None:
+                    payload["train/muon_lr"] = muon_lr
                 if moe_layers:      # rows dropped by full expert buffers (skewed routing), this rank, so far
                     payload["train/moe_dropped_rows"] = sum(m.dropped_rows() for m in moe_layers)
                 sink.log(payload)
                 if is_main:
                     logger.info(f"[step {global_step}/{total_steps}] loss={loss_val:.4f} lr={lr:.2e} "
+                                + (f"muon_lr={muon_lr:.2e} " if muon_lr is not None else "") +
                                 f"grad_norm={gn:.4f} tok/s={tps:,.0f} raw_tok/s={raw_tps:,.0f} "
                                 f"h100_mfu={h100:.2%} b200_mfu={b200:.2%}")
                 window_loss.zero_()

@@ -327,3 +327,50 @@ def test_metrics_sink_with_a_stand_in_for_wandb(tmp_path, monkeypatch):
         raise RuntimeError("no credentials")
     fake.init = no_init
     assert MetricsSink(str(tmp_path), "proj", "run", {}, is_main=True).wandb is None
+
+
+def test_pipeline_with_muon_optimizers_and_configuration_refusals(tmp_path, monkeypatch):
+    """`run_pretraining` in one process on the CPU with `optimizer: muon / normuon` (reference:
+    pure_pipeline.py:107-147, optim.py:121-184; logs `train/muon_lr` next to the AdamW rate,
+    pure_pipeline.py:766-772, 825-827), and the settings it refuses before training starts."""
+    import json
+    from pathlib import Path
+
+    from nanoplm_b200.config.schema import ModelConfig, PretrainingConfig, PureTorchConfig
+    from nanoplm_b200.data.synthetic import write_synthetic_dataset
+    from nanoplm_b200.data.tokenizer import ProtTokenizer
+    from nanoplm_b200.models.encoder import ProtEncoderMLM
+    from nanoplm_b200.runtime.pretrain import run_pretraining
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("WANDB_MODE", "disabled")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    root = write_synthetic_dataset(tmp_path / "ds", 64, 16, 10, 60, samples_per_shard=32)
+    geom = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, max_position_embeddings=64)
+
+    def cfg(**kw):
+        base = dict(dataset_dir=str(root), ckp_dir="ck", micro_batch_size=8, global_batch_size=8 * 64, num_epochs=2,
+                    logging_steps=1, eval_steps=100, save_steps=100, num_workers=0, bf16=False)
+        base.update(kw)
+        return PretrainingConfig(**base)
+
+    def model():
+        torch.manual_seed(0)
+        return ProtEncoderMLM(ModelConfig(**geom), ProtTokenizer())
+
+    for opt in ("muon", "normuon"):
+        res = run_pretraining(model(), cfg(optimizer=opt, ckp_dir=f"ck_{opt}", muon_learning_rate=0.02, adam_learning_rate=1e-3,
+                                           muon_use_polar_express=(opt == "normuon")),
+                              PureTorchConfig(use_packing=True, target_packed_rows=3))
+        losses = [l for _, l in res["losses"]]
+        assert len(losses) == 8 and losses[-1] < losses[0]
+        lines = [json.loads(l) for l in (Path(res["output_dir"]) / "metrics.jsonl").read_text().splitlines()]
+        rates = [(l["train/adamw_lr"], l["train/muon_lr"]) for l in lines if "train/muon_lr" in l]
+        assert len(rates) == 8 and all(abs(m - 20 * a) < 1e-12 for a, m in rates)          # one schedule, two base rates
+        assert (Path(res["output_dir"]) / "checkpoint-8" / "optimizer.pt").exists()
+    with pytest.raises(ValueError, match="Invalid optimizer"):
+        run_pretraining(model(), cfg(optimizer="sgd"))
+    with pytest.raises(ValueError, match="must divide the number of ranks"):
+        run_pretraining(model(), cfg(expert_parallel_size=2))
+    with pytest.raises(ValueError, match="fp8_recipe"):
+        run_pretraining(model(), cfg(fp8=True, fp8_recipe="per_tensor"))
