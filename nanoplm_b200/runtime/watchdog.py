@@ -67,6 +67,10 @@ class Heartbeat:
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout=self.interval + 1)
+        try:
+            self.beat()                 # the file ends with the last step this rank completed
+        except OSError:
+            pass
 
 
 def read_heartbeat(path: Path) -> Optional[tuple[float, int, int, float]]:
